@@ -1,0 +1,93 @@
+"""In-tree build of the native library (``dfccl_b200/lib/libdfccl.so``).
+
+Everything is compiled with nvcc for sm_100a only (``-gencode
+arch=compute_100a,code=sm_100a``): device code and the host runtime live in the
+same shared object, which is loaded through ctypes (``dfccl_b200.lib``).  Objects
+are cached under ``dfccl_b200/csrc/build`` and rebuilt when a source or any
+header is newer.  ``python -m dfccl_b200._build`` builds from the command line;
+``DFCCL_FAST_BUILD=1`` compiles only the float / bfloat16 reduction kernels
+(development shortcut, never used for a committed measurement).
+"""
+from __future__ import annotations
+
+import os
+import subprocess
+import sys
+from concurrent.futures import ThreadPoolExecutor
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+CSRC = ROOT / "csrc"
+OBJ = CSRC / "build"
+LIBDIR = ROOT / "lib"
+LIB = LIBDIR / "libdfccl.so"
+
+SOURCES = [
+    "src/common/log.cc", "src/common/param.cc", "src/common/socket.cc",
+    "src/bootstrap/bootstrap.cc",
+    "src/mem/heap.cu", "src/topo/topo.cu",
+    "src/daemon/daemon.cu", "src/daemon/standalone.cu", "src/daemon/daemon_host.cu",
+    "src/comm/comm.cu",
+    "src/api/nccl_api.cu", "src/api/p2p.cu", "src/api/ofccl_api.cu",
+]
+
+ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
+
+
+def nvcc() -> str:
+    for cand in (os.environ.get("NVCC"), "/usr/local/cuda/bin/nvcc", "nvcc"):
+        if cand and (os.path.isabs(cand) and os.path.exists(cand) or not os.path.isabs(cand)):
+            return cand
+    raise RuntimeError("nvcc not found")
+
+
+def _flags(verbose: bool) -> list:
+    f = ["-std=c++17", "-O3", "-lineinfo", "-Xcompiler", "-fPIC,-fvisibility=hidden,-Wall,-Wno-unused-function",
+         "-I", str(CSRC / "include"), "-Wno-deprecated-gpu-targets", "-x", "cu"] + ARCH
+    if os.environ.get("DFCCL_FAST_BUILD") == "1":
+        f.append("-DDF_FAST_BUILD")
+    if verbose:
+        f += ["-Xptxas", "-v"]
+    return f
+
+
+def _newest_header() -> float:
+    return max((p.stat().st_mtime for p in CSRC.rglob("*.h")), default=0.0)
+
+
+def _compile(src: str, verbose: bool, hdr_time: float) -> Path:
+    s = CSRC / src
+    o = OBJ / (src.replace("/", "_") + (".fast.o" if os.environ.get("DFCCL_FAST_BUILD") == "1" else ".o"))
+    if o.exists() and o.stat().st_mtime > max(s.stat().st_mtime, hdr_time):
+        return o
+    cmd = [nvcc()] + _flags(verbose) + ["-c", str(s), "-o", str(o)]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError(f"nvcc failed for {src}:\n{r.stdout}\n{r.stderr}")
+    if verbose:
+        sys.stderr.write(r.stderr)
+    return o
+
+
+def build(verbose: bool = False, force: bool = False, extra_sources=()) -> Path:
+    """Compile what is stale and link ``libdfccl.so``; returns its path."""
+    OBJ.mkdir(parents=True, exist_ok=True)
+    LIBDIR.mkdir(parents=True, exist_ok=True)
+    if force:
+        for o in OBJ.glob("*.o"):
+            o.unlink()
+    hdr = _newest_header()
+    srcs = [s for s in list(SOURCES) + list(extra_sources) if (CSRC / s).exists()]
+    with ThreadPoolExecutor(max_workers=min(8, os.cpu_count() or 4)) as ex:
+        objs = list(ex.map(lambda s: _compile(s, verbose, hdr), srcs))
+    if LIB.exists() and all(LIB.stat().st_mtime > o.stat().st_mtime for o in objs):
+        return LIB
+    cmd = [nvcc(), "-shared", "-o", str(LIB)] + [str(o) for o in objs] + ARCH + ["-lrt", "-lpthread", "-ldl", "-cudart", "static"]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")
+    return LIB
+
+
+if __name__ == "__main__":
+    print(build(verbose="-v" in sys.argv, force="--force" in sys.argv))

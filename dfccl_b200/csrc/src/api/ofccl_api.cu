@@ -1,0 +1,655 @@
+#include "rankctx.h"
+#include "../common/log.h"
+#include "../common/param.h"
+#include "../device/datapath.h"
+#include "../device/engine.h"
+#include "../device/launch.h"
+#include "../topo/topo.h"
+#include <algorithm>
+#include <chrono>
+#include <cstring>
+#include <cuda.h>
+#include <fstream>
+
+using namespace dfccl;
+
+#define DF_API extern "C" __attribute__((visibility("default")))
+
+namespace dfccl {
+
+__global__ void dfcclWriteWordKernel(volatile uint64_t* p, uint64_t v) {
+  __threadfence_system();
+  *p = v;
+}
+
+static uint32_t pow2ceil(uint32_t v) { uint32_t p = 1; while (p < v) p <<= 1; return p; }
+
+DaemonLauncher::~DaemonLauncher() {
+  {
+    std::lock_guard<std::mutex> l(mu);
+    stop = true;
+    cv.notify_all();
+  }
+  if (observer.joinable()) observer.join();
+  if (backend == dfcclBackendCuda) {
+    int prev = 0;
+    cudaGetDevice(&prev);
+    cudaSetDevice(device);
+    if (stream) { cudaStreamSynchronize(stream); cudaStreamDestroy(stream); }
+    if (devTable) cudaFree(devTable);
+    (void)cudaGetLastError();
+    cudaSetDevice(prev);
+  } else {
+    ::free(devTable);
+  }
+}
+
+static void wakeLauncher(DaemonLauncher* L) {
+  std::lock_guard<std::mutex> l(L->mu);
+  L->wake = true;
+  L->cv.notify_all();
+}
+
+// Launches (and relaunches) the daemon: the reference's observer thread.
+static void observerMain(DaemonLauncher* L) {
+  if (L->backend == dfcclBackendCuda) cudaSetDevice(L->device);
+  std::unique_lock<std::mutex> lk(L->mu);
+  for (;;) {
+    L->cv.wait(lk, [&] { return L->wake || L->stop; });
+    if (L->stop) break;
+    L->wake = false;
+    std::vector<ofcclRankCtx*> members = L->members;
+    lk.unlock();
+    // the previous instance must be completely gone: its blocks park state the next one restores
+    if (L->backend == dfcclBackendCuda) {
+      cudaError_t e = cudaStreamSynchronize(L->stream);
+      if (e != cudaSuccess) {
+        DF_WARN("daemon kernel failed: %s", cudaGetErrorString(e));
+        for (auto* m : members) m->asyncError = ncclUnhandledCudaError;
+        lk.lock();
+        break;
+      }
+    }
+    bool work = false, dead = false;
+    for (auto* m : members) {
+      if (m->remaining.load() > 0) work = true;
+      if (m->ctl->finalQuit || m->ctl->abortFlag) dead = true;
+    }
+    if (work && !dead) {
+      for (auto* m : members) { m->ctl->alive = 1; m->ctl->launches = m->ctl->launches + 1; }
+      std::atomic_thread_fence(std::memory_order_seq_cst);
+      ++L->launches;
+      DF_TRACE(SUB_DAEMON, "daemon launch #%llu (%zu ranks x %d blocks x %d threads)", (unsigned long long)L->launches, members.size(), L->blocks, L->threads);
+      if (L->backend == dfcclBackendCuda) {
+        ncclResult_t r = launchDaemonCuda(L->devTable, (int)members.size(), L->blocks, L->threads, L->stream);
+        if (r != ncclSuccess) for (auto* m : members) m->asyncError = r;
+      } else {
+        runDaemonHost(L->devTable, (int)members.size(), L->blocks);     // returns when every block has left
+        for (auto* m : members) if (m->remaining.load() > 0 && !m->ctl->finalQuit && !m->ctl->abortFlag) { lk.lock(); L->wake = true; lk.unlock(); break; }
+      }
+    }
+    lk.lock();
+  }
+}
+
+static void deliver(ofcclRankCtx* ctx, uint64_t entry) {
+  const int coll = (int)cqeColl(entry);
+  CallbackFunc cb = nullptr;
+  void* args = nullptr;
+  {
+    std::lock_guard<std::mutex> l(ctx->mu);
+    auto it = ctx->colls.find(coll);
+    if (it == ctx->colls.end()) { DF_WARN("completion for unknown collective %d", coll); return; }
+    it->second.lastStatus = cqeStatus(entry);
+    if (it->second.lastStatus != ST_OK && ctx->asyncError == ncclSuccess)
+      ctx->asyncError = it->second.lastStatus == ST_TIMEOUT ? dfcclTimeout : it->second.lastStatus == ST_ABORTED ? dfcclAborted : ncclInternalError;
+    cb = it->second.cb; args = it->second.cbArgs;
+  }
+  ctx->cqes++;
+  if (ctx->faultFreezeMs > 0) std::this_thread::sleep_for(std::chrono::milliseconds(ctx->faultFreezeMs));
+  if (cb) { cb(coll, args); ctx->cbs++; }
+  {
+    std::lock_guard<std::mutex> l(ctx->mu);
+    ctx->colls[coll].completed++;
+    ctx->remaining--;
+  }
+  ctx->doneCv.notify_all();
+}
+
+// Turns completion entries into callbacks: the reference's poller thread.
+static void pollerMain(ofcclRankCtx* ctx) {
+  logSetRank(ctx->rank);
+  int64_t empty = 0;
+  while (!ctx->stopPoller.load()) {
+    if (ctx->remaining.load() == 0) {
+      std::unique_lock<std::mutex> l(ctx->mu);
+      ctx->pollCv.wait_for(l, std::chrono::milliseconds(20), [&] { return ctx->remaining.load() > 0 || ctx->stopPoller.load(); });
+      continue;
+    }
+    const uint64_t slot = ctx->cqHead & (ctx->cqCap - 1);
+    const uint64_t e = __atomic_load_n((const uint64_t*)&ctx->hostCq[slot], __ATOMIC_ACQUIRE);
+    if (cqeGen(e) == (uint32_t)(ctx->cqHead / ctx->cqCap) + 1u) {
+      ++ctx->cqHead;
+      empty = 0;
+      deliver(ctx, e);
+      continue;
+    }
+    // nothing new: if the daemon left while work is outstanding, have it launched again
+    if (++empty % ctx->checkInterval == 0 || (empty & 63) == 0) {
+      if (!ctx->ctl->alive && ctx->remaining.load() > 0 && !ctx->ctl->abortFlag) wakeLauncher(ctx->launcher.get());
+    }
+    if (empty > 2000) std::this_thread::sleep_for(std::chrono::microseconds(20)); else sched_yield();
+  }
+}
+
+static ncclResult_t checkInfo(const dfcclCollInfo* info, ncclComm* comm) {
+  if (!info || !comm) { DF_WARN("null argument"); return ncclInvalidArgument; }
+  if (info->kind < 0 || info->kind >= dfcclCollNumKinds) { DF_WARN("invalid collective kind %d", info->kind); return ncclInvalidArgument; }
+  if ((int)info->inType < 0 || (int)info->inType >= ncclNumTypes || (int)info->outType < 0 || (int)info->outType >= ncclNumTypes) { DF_WARN("invalid datatype"); return ncclInvalidArgument; }
+  if (info->root < 0 || info->root >= comm->nranks) { DF_WARN("invalid root %d", info->root); return ncclInvalidArgument; }
+  const bool reduces = info->kind == dfcclCollAllReduce || info->kind == dfcclCollReduce || info->kind == dfcclCollReduceScatter;
+  if (!reduces && info->inType != info->outType) { DF_WARN("only reducing collectives can cast"); return ncclInvalidArgument; }
+  return ncclSuccess;
+}
+
+}  // namespace dfccl
+
+// ------------------------------------------------------------------ life cycle
+
+DF_API ncclResult_t dfcclInitRankCtxOnDevice(ofcclRankCtx_t* out, int rank, int device) {
+  if (!out) return ncclInvalidArgument;
+  auto* ctx = new ofcclRankCtx();
+  ctx->rank = rank; ctx->device = device; ctx->deviceChosen = device >= 0;
+  ctx->backend = defaultBackend();
+  *out = ctx;
+  return ncclSuccess;
+}
+DF_API ncclResult_t ofcclInitRankCtx(ofcclRankCtx_t* out, int rank) { return dfcclInitRankCtxOnDevice(out, rank, -1); }
+
+DF_API ncclResult_t dfcclPrepare(const dfcclCollInfo* info, ncclComm_t comm, int collId, ofcclRankCtx_t ctx) {
+  if (!ctx) return ncclInvalidArgument;
+  DFCHECK(checkInfo(info, comm));
+  std::lock_guard<std::mutex> l(ctx->mu);
+  if (ctx->finalized) { DF_WARN("collective %d registered after the context was finalized", collId); return ncclInvalidUsage; }
+  if (collId < 0 || collId >= DF_MAX_COLLS) { DF_WARN("collective id %d outside [0, %d)", collId, DF_MAX_COLLS); return ncclInvalidArgument; }
+  if (ctx->colls.count(collId)) { DF_WARN("collective id %d registered twice", collId); return ncclInvalidUsage; }
+  if (!ctx->colls.empty() && ctx->colls.begin()->second.comm->backend != comm->backend) { DF_WARN("all collectives of a context must use one backend"); return ncclInvalidUsage; }
+  if (!ctx->colls.empty() && ctx->colls.begin()->second.comm->device != comm->device) { DF_WARN("all collectives of a context must use communicators of one device"); return ncclInvalidUsage; }
+  CollEntry e;
+  e.info = *info;
+  e.comm = comm;
+  int devOp = OP_SUM;
+  double scale = 1.0;
+  int postDiv = 0;
+  const bool reduces = info->kind == dfcclCollAllReduce || info->kind == dfcclCollReduce || info->kind == dfcclCollReduceScatter;
+  if (reduces) DFCHECK(resolveRedOp(comm, info->op, info->inType, comm->nranks, &devOp, &scale, &postDiv));
+  if (info->scale != 0.f && info->scale != 1.f) scale *= (double)info->scale;
+  if (reduces && !reduceSupported(info->inType, info->outType, devOp)) { DF_WARN("no kernel for type %d -> %d with operator %d", (int)info->inType, (int)info->outType, (int)info->op); return ncclInvalidArgument; }
+  CollStatic& cs = e.cs;
+  memset(&cs, 0, sizeof(cs));
+  cs.kind = info->kind; cs.inType = info->inType; cs.outType = info->outType; cs.op = devOp;
+  cs.nranks = comm->nranks; cs.rank = comm->rank; cs.root = info->root; cs.count = info->count;
+  cs.scale = scale; cs.postDiv = postDiv;
+  ctx->colls[collId] = e;
+  ctx->maxCollId = std::max(ctx->maxCollId, collId);
+  if (paramI64("SHOW_ALL_PREPARED_COLL", 0)) DF_WARN("prepared coll %d kind %d count %zu type %d->%d", collId, info->kind, info->count, (int)info->inType, (int)info->outType);
+  return ncclSuccess;
+}
+
+struct FinalizeMsg { int32_t collId, nBlocks, algo, kind, inType, outType, pad0, pad1; uint64_t count, flagsOff; };
+
+DF_API ncclResult_t ofcclFinalizeRankCtx7StartHostThrds(ofcclRankCtx_t ctx) {
+  if (!ctx) return ncclInvalidArgument;
+  if (ctx->finalized) { DF_WARN("context finalized twice"); return ncclInvalidUsage; }
+  if (ctx->colls.empty()) { DF_WARN("no collective registered"); return ncclInvalidUsage; }
+  ncclComm* first = ctx->colls.begin()->second.comm;
+  ctx->backend = first->backend;
+  ctx->device = first->device;
+  const dfcclBackend_t be = ctx->backend;
+  int prevDev = 0;
+  if (be == dfcclBackendCuda) { cudaGetDevice(&prevDev); CUDACHECK(cudaSetDevice(ctx->device)); }
+  logSetRank(ctx->rank);
+  ctx->nBlocks = daemonBlocks(be);
+  ctx->checkInterval = std::max<int64_t>(1, paramI64("CHECK_REMAINING_SQE_INTERVAL", 10000));
+  const Topology* topo = nullptr;
+  DFCHECK(topoGet(&topo));
+
+  // 1. schedule + flag words of every collective
+  for (auto& kv : ctx->colls) {
+    CollEntry& e = kv.second;
+    const size_t bytes = e.info.count * (size_t)dtypeSize(e.info.inType);
+    TunerChoice ch = tunerChoose(*topo, e.info.kind, bytes, e.comm->nranks, ctx->nBlocks, false, e.info.algo, e.info.nBlocks);
+    e.cs.algo = ch.algo; e.cs.nBlocks = ch.nBlocks;
+    e.flagsBytes = sizeof(FlagSlot) * (size_t)ch.nBlocks * e.comm->nranks;
+    DFCHECK(e.comm->heap->alloc(e.flagsBytes, &e.flagsOff, true));
+  }
+  // 2. exchange, communicator by communicator in an order all ranks agree on (smallest id first)
+  std::vector<std::pair<int, ncclComm*>> order;
+  for (auto& kv : ctx->colls) {
+    bool seen = false;
+    for (auto& o : order) if (o.second == kv.second.comm) seen = true;
+    if (!seen) order.push_back({kv.first, kv.second.comm});
+  }
+  for (auto& oc : order) {
+    ncclComm* comm = oc.second;
+    std::vector<int> ids;
+    for (auto& kv : ctx->colls) if (kv.second.comm == comm) ids.push_back(kv.first);
+    const int n = comm->nranks;
+    std::vector<int32_t> cnt(n, 0);
+    cnt[comm->rank] = (int32_t)ids.size();
+    DFCHECK(comm->boot->allGather(cnt.data(), sizeof(int32_t)));
+    for (int j = 0; j < n; ++j) if (cnt[j] != (int32_t)ids.size()) { DF_WARN("rank %d registered %d collectives on this communicator, rank %d registered %zu", j, cnt[j], comm->rank, ids.size()); return ncclInvalidUsage; }
+    std::vector<FinalizeMsg> all((size_t)n * ids.size());
+    for (size_t i = 0; i < ids.size(); ++i) {
+      CollEntry& e = ctx->colls[ids[i]];
+      all[(size_t)comm->rank * ids.size() + i] = {ids[i], e.cs.nBlocks, e.cs.algo, e.cs.kind, e.cs.inType, e.cs.outType, 0, 0, e.cs.count, e.flagsOff};
+    }
+    DFCHECK(comm->boot->allGather(all.data(), sizeof(FinalizeMsg) * ids.size()));
+    for (size_t i = 0; i < ids.size(); ++i) {
+      CollEntry& e = ctx->colls[ids[i]];
+      e.cs.myFlags = (FlagSlot*)(comm->heap->base() + e.flagsOff);
+      for (int j = 0; j < n; ++j) {
+        const FinalizeMsg& m = all[(size_t)j * ids.size() + i];
+        if (m.collId != ids[i] || m.kind != e.cs.kind || m.count != e.cs.count || m.inType != e.cs.inType || m.outType != e.cs.outType || m.nBlocks != e.cs.nBlocks || m.algo != e.cs.algo) {
+          DF_WARN("collective %d is registered differently on rank %d", ids[i], j);
+          return ncclInvalidUsage;
+        }
+        e.cs.peerHeap[j] = comm->peerHeap[j];
+        e.cs.peerFlags[j] = (FlagSlot*)(comm->peerHeap[j] + m.flagsOff);
+      }
+      e.cs.valid = 1;
+    }
+  }
+  // 3. queues and device tables
+  const uint32_t maxColls = (uint32_t)ctx->maxCollId + 1;
+  ctx->sqCap = pow2ceil(std::max<uint32_t>(64, 2 * (uint32_t)ctx->colls.size() + 2));
+  ctx->cqCap = pow2ceil(std::max<uint32_t>(64, 2 * (uint32_t)ctx->colls.size() + 2));
+  DFCHECK(pinnedAlloc(be, (void**)&ctx->hostSq, sizeof(Sqe) * ctx->sqCap));
+  DFCHECK(pinnedAlloc(be, (void**)&ctx->hostSqTail, 64));
+  DFCHECK(pinnedAlloc(be, (void**)&ctx->hostSqHead, 64));
+  DFCHECK(pinnedAlloc(be, (void**)&ctx->hostCq, sizeof(uint64_t) * ctx->cqCap));
+  DFCHECK(pinnedAlloc(be, (void**)&ctx->ctl, sizeof(DaemonCtl)));
+  RankDev& rd = ctx->rdHost;
+  memset(&rd, 0, sizeof(rd));
+  rd.hostSq = ctx->hostSq; rd.hostSqTail = ctx->hostSqTail; rd.hostSqHead = ctx->hostSqHead;
+  rd.hostCq = ctx->hostCq; rd.ctl = ctx->ctl;
+  rd.sqCap = ctx->sqCap; rd.cqCap = ctx->cqCap; rd.nBlocks = (uint32_t)ctx->nBlocks; rd.maxColls = maxColls;
+  DFCHECK(devAlloc(be, (void**)&rd.devSq, sizeof(Sqe) * ctx->sqCap));
+  DFCHECK(devAlloc(be, (void**)&rd.colls, sizeof(CollStatic) * maxColls));
+  DFCHECK(devAlloc(be, (void**)&rd.dyn, sizeof(CollDyn) * (size_t)maxColls * ctx->nBlocks));
+  DFCHECK(devAlloc(be, (void**)&rd.doneCount, sizeof(uint32_t) * maxColls));
+  DFCHECK(devAlloc(be, (void**)&rd.failCount, sizeof(uint32_t) * maxColls));
+  DFCHECK(devAlloc(be, (void**)&rd.doneEpoch, sizeof(uint64_t) * maxColls));
+  DFCHECK(devAlloc(be, (void**)&rd.trigger, sizeof(uint64_t) * maxColls));
+  DFCHECK(devAlloc(be, (void**)&rd.saved, sizeof(BlockSaved) * ctx->nBlocks));
+  DFCHECK(devAlloc(be, (void**)&rd.stats, sizeof(DevStats) * ctx->nBlocks));
+  if (paramI64("TRACE", 0)) {
+    rd.traceCap = pow2ceil((uint32_t)paramI64("TRACE_EVENTS", 1 << 16));
+    DFCHECK(devAlloc(be, (void**)&rd.trace, sizeof(TraceEvent) * rd.traceCap));
+  }
+  // tunables; the un-prefixed names are the reference's (src/enqueue_ofccl.cc:1287-1297)
+  rd.spinBudget = (uint32_t)std::max<int64_t>(1, paramI64("BASE_CTX_SWITCH_THRESHOLD", 80));
+  rd.headTries = (uint32_t)std::max<int64_t>(1, paramI64("NUM_TRY_TASKQ_HEAD", 5));
+  rd.recvSuccessFactor = (uint32_t)paramI64("RECV_SUCCESS_FACTOR", 5);
+  const int64_t tolerant = paramI64("TOLERANT_UNPROGRESSED_CNT", 0);     // polls in the reference; here ~1 us each
+  rd.idleQuitNs = (uint64_t)paramI64("IDLE_QUIT_US", tolerant ? tolerant : 200) * 1000ull;
+  rd.stallQuitNs = (uint64_t)paramI64("STALL_QUIT_US", tolerant ? tolerant : 5000) * 1000ull;
+  rd.waitTimeoutNs = (uint64_t)paramI64("WAIT_TIMEOUT_MS", 0) * 1000000ull;
+  rd.sliceBytes = (uint64_t)paramI64("SLICE_BYTES", 0);
+  std::vector<CollStatic> table(maxColls);
+  memset(table.data(), 0, sizeof(CollStatic) * maxColls);
+  for (auto& kv : ctx->colls) table[kv.first] = kv.second.cs;
+  DFCHECK(devUpload(be, rd.colls, table.data(), sizeof(CollStatic) * maxColls));
+  DFCHECK(devAlloc(be, (void**)&ctx->rdDev, sizeof(RankDev)));
+  DFCHECK(devUpload(be, ctx->rdDev, &rd, sizeof(RankDev)));
+  if (be == dfcclBackendCuda) {
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuStreamWriteValue64", &ctx->fnWrite64, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess) ctx->fnWrite64 = nullptr;
+    if (cudaGetDriverEntryPoint("cuStreamWaitValue64", &ctx->fnWait64, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess) ctx->fnWait64 = nullptr;
+    (void)cudaGetLastError();
+    if (paramI64("NO_STREAM_MEMOPS", 0)) ctx->fnWrite64 = ctx->fnWait64 = nullptr;
+  }
+  // 4. launcher: shared by the ranks of a loopback group, private otherwise
+  std::shared_ptr<LoopGroup> loop = first->loop;
+  {
+    std::shared_ptr<DaemonLauncher> L;
+    if (loop) {
+      std::lock_guard<std::mutex> l(loop->mu);
+      if (!loop->launcher) { loop->launcher = std::make_shared<DaemonLauncher>(); loop->launcher->expected = loop->nranks; }
+      L = loop->launcher;
+    } else {
+      L = std::make_shared<DaemonLauncher>();
+      L->expected = 1;
+    }
+    std::lock_guard<std::mutex> l(L->mu);
+    L->backend = be; L->device = ctx->device; L->blocks = ctx->nBlocks; L->threads = daemonThreads(be);
+    ctx->launcherSlot = (int)L->members.size();
+    L->members.push_back(ctx);
+    ctx->launcher = L;
+    if ((int)L->members.size() == L->expected) {
+      std::vector<RankDev*> tab;
+      for (auto* m : L->members) tab.push_back(m->rdDev);
+      if (be == dfcclBackendCuda) {
+        int lo = 0, hi = 0;
+        cudaDeviceGetStreamPriorityRange(&lo, &hi);
+        CUDACHECK(cudaStreamCreateWithPriority(&L->stream, cudaStreamNonBlocking, hi));
+        CUDACHECK(cudaMalloc((void**)&L->devTable, sizeof(RankDev*) * tab.size()));
+        CUDACHECK(cudaMemcpy(L->devTable, tab.data(), sizeof(RankDev*) * tab.size(), cudaMemcpyHostToDevice));
+        if (L->expected > 1) {
+          int maxb = 0;
+          DFCHECK(daemonMaxResidentBlocks(ctx->device, L->threads, &maxb));
+          if (L->expected * L->blocks > maxb) { DF_WARN("%d ranks x %d blocks do not fit on device %d together (%d resident blocks); lower DFCCL_DAEMON_BLOCKS", L->expected, L->blocks, ctx->device, maxb); return ncclInvalidUsage; }
+        }
+      } else {
+        L->devTable = (RankDev**)malloc(sizeof(RankDev*) * tab.size());
+        memcpy(L->devTable, tab.data(), sizeof(RankDev*) * tab.size());
+      }
+      L->started = true;
+      L->observer = std::thread(observerMain, L.get());
+    }
+  }
+  ctx->poller = std::thread(pollerMain, ctx);
+  ctx->finalized = true;
+  if (be == dfcclBackendCuda) { CUDACHECK(cudaDeviceSynchronize()); cudaSetDevice(prevDev); }
+  DF_INFO(SUB_INIT, "rank context %d finalized: %zu collectives, %d daemon blocks", ctx->rank, ctx->colls.size(), ctx->nBlocks);
+  return ncclSuccess;
+}
+
+DF_API ncclResult_t ofcclPrepareDone(ofcclRankCtx_t ctx) {
+  DFCHECK(ofcclFinalizeRankCtx7StartHostThrds(ctx));
+  return ncclSuccess;          // the daemon starts with the first submission; an idle daemon would only hold SMs
+}
+
+// ------------------------------------------------------------------ submit
+
+static ncclResult_t submit(ofcclRankCtx* ctx, const void* send, void* recv, int collId, CallbackFunc cb, void* cbArgs,
+                           bool onStream, cudaStream_t stream) {
+  if (!ctx || !ctx->finalized || ctx->destroyed) { DF_WARN("context is not ready for submissions"); return ncclInvalidUsage; }
+  if (ctx->ctl->abortFlag) return dfcclAborted;
+  if (ctx->faultDelayUs > 0) std::this_thread::sleep_for(std::chrono::microseconds(ctx->faultDelayUs));
+  Sqe q;
+  memset(&q, 0, sizeof(q));
+  uint64_t trig = 0;
+  {
+    std::unique_lock<std::mutex> l(ctx->mu);
+    auto it = ctx->colls.find(collId);
+    if (it == ctx->colls.end()) { DF_WARN("collective %d was never prepared", collId); return ncclInvalidArgument; }
+    CollEntry& e = it->second;
+    if (e.submitted != e.completed) { DF_WARN("collective %d submitted again before its callback ran", collId); return ncclInvalidUsage; }
+    const CollStatic& cs = e.cs;
+    const bool needSend = !(cs.kind == dfcclCollBroadcast && cs.rank != cs.root);
+    const bool needRecv = !(cs.kind == dfcclCollReduce && cs.rank != cs.root);
+    if ((needSend && !send) || (needRecv && !recv)) { DF_WARN("null buffer for collective %d", collId); return ncclInvalidArgument; }
+    Heap* heap = e.comm->heap;
+    const size_t sB = sendBytes(&cs), rB = recvBytes(&cs);
+    q.collId = collId;
+    bool stageSend = needSend && !heap->contains(send, sB);
+    if (needSend && cs.kind == dfcclCollAllReduce && cs.algo == dfcclAlgoOneShot && send == recv && cs.nranks > 1) stageSend = true;
+    bool stageRecv = needRecv && !heap->contains(recv, rB);
+    // staging areas are created on first need; the static table on the device learns their offsets
+    bool tableDirty = false;
+    if (stageSend && e.stagingBytes[0] < sB) { if (e.stagingBytes[0]) heap->free(e.stagingOff[0]); DFCHECK(heap->alloc(sB, &e.stagingOff[0], false)); e.stagingBytes[0] = sB; e.cs.stagingSendOff = e.stagingOff[0]; tableDirty = true; }
+    if (stageRecv && e.stagingBytes[1] < rB) { if (e.stagingBytes[1]) heap->free(e.stagingOff[1]); DFCHECK(heap->alloc(rB, &e.stagingOff[1], false)); e.stagingBytes[1] = rB; e.cs.stagingRecvOff = e.stagingOff[1]; tableDirty = true; }
+    if (tableDirty) DFCHECK(devUpload(ctx->backend, &ctx->rdHost.colls[collId], &e.cs, sizeof(CollStatic)));
+    if (stageSend) { q.flags |= SQE_SEND_STAGED; q.send = (uint64_t)(uintptr_t)send; } else if (needSend) q.send = heap->offsetOf(send);
+    if (stageRecv) { q.flags |= SQE_RECV_STAGED; q.recv = (uint64_t)(uintptr_t)recv; } else if (needRecv) q.recv = heap->offsetOf(recv);
+    if (onStream) { q.flags |= SQE_TRIGGERED; q.trigger = trig = ++e.triggerSeq; }
+    // flow control: entries the device has not mirrored yet
+    uint64_t tail = *ctx->hostSqTail;
+    while (tail - __atomic_load_n((const uint64_t*)ctx->hostSqHead, __ATOMIC_ACQUIRE) >= ctx->sqCap) {
+      ctx->sqFull++;
+      l.unlock();
+      if (!ctx->ctl->alive) wakeLauncher(ctx->launcher.get());
+      sched_yield();
+      l.lock();
+      tail = *ctx->hostSqTail;
+    }
+    e.cb = cb; e.cbArgs = cbArgs;
+    e.submitted++;
+    ctx->remaining++;
+    ctx->sqes++;
+    if (ctx->faultDrop > 0) {          // accepted, counted, never published
+      --ctx->faultDrop;
+    } else {
+      ctx->hostSq[tail & (ctx->sqCap - 1)] = q;
+      __atomic_store_n((uint64_t*)ctx->hostSqTail, tail + 1, __ATOMIC_RELEASE);
+    }
+  }
+  ctx->pollCv.notify_one();
+  if (!ctx->ctl->alive) wakeLauncher(ctx->launcher.get());
+  if (onStream) {
+    volatile uint64_t* word = ctx->rdHost.trigger + collId;
+    if (ctx->backend == dfcclBackendCuda) {
+      if (ctx->fnWrite64) {
+        typedef CUresult (*Fn)(CUstream, CUdeviceptr, cuuint64_t, unsigned int);
+        CUresult r = ((Fn)ctx->fnWrite64)((CUstream)stream, (CUdeviceptr)(uintptr_t)word, trig, 0);
+        if (r != CUDA_SUCCESS) { DF_WARN("cuStreamWriteValue64 failed (%d)", (int)r); return ncclUnhandledCudaError; }
+      } else {
+        dfcclWriteWordKernel<<<1, 1, 0, stream>>>(word, trig);
+        CUDACHECK(cudaGetLastError());
+      }
+    } else {
+      __atomic_store_n((uint64_t*)word, trig, __ATOMIC_RELEASE);
+    }
+  }
+  return ncclSuccess;
+}
+
+DF_API ncclResult_t dfcclRun(const void* s, void* r, int collId, CallbackFunc cb, void* args, ofcclRankCtx_t ctx) {
+  return submit(ctx, s, r, collId, cb, args, false, nullptr);
+}
+DF_API ncclResult_t dfcclRunOnStream(const void* s, void* r, int collId, cudaStream_t stream, CallbackFunc cb, void* args, ofcclRankCtx_t ctx) {
+  return submit(ctx, s, r, collId, cb, args, true, stream);
+}
+
+DF_API ncclResult_t dfcclWait(int collId, int timeoutMs, ofcclRankCtx_t ctx) {
+  if (!ctx || !ctx->finalized) return ncclInvalidUsage;
+  std::unique_lock<std::mutex> l(ctx->mu);
+  auto it = ctx->colls.find(collId);
+  if (it == ctx->colls.end()) return ncclInvalidArgument;
+  CollEntry& e = it->second;
+  auto pred = [&] { return e.completed == e.submitted || ctx->ctl->abortFlag; };
+  if (timeoutMs < 0) ctx->doneCv.wait(l, pred);
+  else if (!ctx->doneCv.wait_for(l, std::chrono::milliseconds(timeoutMs), pred)) return dfcclTimeout;
+  if (ctx->ctl->abortFlag && e.completed != e.submitted) return dfcclAborted;
+  return e.lastStatus == ST_OK ? ncclSuccess : e.lastStatus == ST_TIMEOUT ? dfcclTimeout : e.lastStatus == ST_ABORTED ? dfcclAborted : ncclInternalError;
+}
+
+DF_API ncclResult_t dfcclWaitAll(int timeoutMs, ofcclRankCtx_t ctx) {
+  if (!ctx || !ctx->finalized) return ncclInvalidUsage;
+  std::unique_lock<std::mutex> l(ctx->mu);
+  auto pred = [&] { return ctx->remaining.load() == 0 || ctx->ctl->abortFlag; };
+  if (timeoutMs < 0) ctx->doneCv.wait(l, pred);
+  else if (!ctx->doneCv.wait_for(l, std::chrono::milliseconds(timeoutMs), pred)) return dfcclTimeout;
+  if (ctx->ctl->abortFlag && ctx->remaining.load()) return dfcclAborted;
+  return ctx->asyncError;
+}
+
+DF_API ncclResult_t dfcclStreamWait(int collId, cudaStream_t stream, ofcclRankCtx_t ctx) {
+  if (!ctx || !ctx->finalized) return ncclInvalidUsage;
+  uint64_t want;
+  {
+    std::lock_guard<std::mutex> l(ctx->mu);
+    auto it = ctx->colls.find(collId);
+    if (it == ctx->colls.end()) return ncclInvalidArgument;
+    want = it->second.submitted;
+  }
+  if (ctx->backend == dfcclBackendCuda && ctx->fnWait64) {
+    typedef CUresult (*Fn)(CUstream, CUdeviceptr, cuuint64_t, unsigned int);
+    // the flag holds (status << 56 | epoch): any finished submission >= want satisfies >=
+    CUresult r = ((Fn)ctx->fnWait64)((CUstream)stream, (CUdeviceptr)(uintptr_t)(ctx->rdHost.doneEpoch + collId), want, CU_STREAM_WAIT_VALUE_GEQ);
+    if (r != CUDA_SUCCESS) { DF_WARN("cuStreamWaitValue64 failed (%d)", (int)r); return ncclUnhandledCudaError; }
+    return ncclSuccess;
+  }
+  return dfcclWait(collId, -1, ctx);     // no stream memory operations: the host waits instead
+}
+
+DF_API ncclResult_t dfcclAbort(ofcclRankCtx_t ctx) {
+  if (!ctx) return ncclInvalidArgument;
+  if (ctx->ctl) ctx->ctl->abortFlag = 1;
+  ctx->doneCv.notify_all();
+  return ncclSuccess;
+}
+DF_API ncclResult_t dfcclGetAsyncError(ofcclRankCtx_t ctx, ncclResult_t* e) {
+  if (!ctx || !e) return ncclInvalidArgument;
+  *e = ctx->asyncError;
+  return ncclSuccess;
+}
+
+DF_API ncclResult_t dfcclGetStats(ofcclRankCtx_t ctx, dfcclStats* s) {
+  if (!ctx || !s) return ncclInvalidArgument;
+  memset(s, 0, sizeof(*s));
+  s->sqesSubmitted = ctx->sqes; s->cqesDelivered = ctx->cqes; s->callbacksRun = ctx->cbs; s->sqFullRetries = ctx->sqFull;
+  if (!ctx->finalized) return ncclSuccess;
+  s->daemonLaunches = ctx->ctl->launches; s->daemonVoluntaryQuits = ctx->ctl->voluntaryQuits;
+  std::vector<DevStats> d(ctx->nBlocks);
+  if (ctx->backend == dfcclBackendCuda) { int prev; cudaGetDevice(&prev); cudaSetDevice(ctx->device); cudaError_t e = cudaMemcpy(d.data(), ctx->rdHost.stats, sizeof(DevStats) * ctx->nBlocks, cudaMemcpyDeviceToHost); cudaSetDevice(prev); if (e != cudaSuccess) { (void)cudaGetLastError(); return ncclUnhandledCudaError; } }
+  else memcpy(d.data(), ctx->rdHost.stats, sizeof(DevStats) * ctx->nBlocks);
+  for (auto& b : d) {
+    s->ctxSwitches += b.ctxSwitches; s->ctxSaves += b.ctxSaves; s->ctxLoads += b.ctxLoads;
+    s->waitPolls += b.waitPolls; s->waitTimeouts += b.waitTimeouts;
+    s->bytesReduced += b.bytesReduced; s->bytesCopied += b.bytesCopied; s->totalSwitchNs += b.totalSwitchNs;
+    s->maxSwitchNs = std::max<uint64_t>(s->maxSwitchNs, b.maxSwitchNs);
+  }
+  if (ctx->rdHost.trace) {
+    uint64_t head = 0;
+    devDownload(ctx->backend, &head, (char*)ctx->rdDev + offsetof(RankDev, traceHead), sizeof(head));
+    s->deviceEvents = head;
+  }
+  return ncclSuccess;
+}
+
+DF_API ncclResult_t dfcclTraceDump(ofcclRankCtx_t ctx, const char* path) {
+  if (!ctx || !path || !ctx->finalized) return ncclInvalidArgument;
+  if (!ctx->rdHost.trace) { DF_WARN("tracing is off (set DFCCL_TRACE=1 before finalizing)"); return ncclInvalidUsage; }
+  uint64_t head = 0;
+  DFCHECK(devDownload(ctx->backend, &head, (char*)ctx->rdDev + offsetof(RankDev, traceHead), sizeof(head)));
+  const uint32_t cap = ctx->rdHost.traceCap;
+  std::vector<TraceEvent> ev(cap);
+  DFCHECK(devDownload(ctx->backend, ev.data(), ctx->rdHost.trace, sizeof(TraceEvent) * cap));
+  std::ofstream o(path);
+  if (!o) return ncclSystemError;
+  static const char* names[] = {"?", "sqe", "start", "stall", "resume", "data_begin", "data_end", "done", "quit", "launch"};
+  o << "{\"traceEvents\":[\n";
+  uint64_t n = std::min<uint64_t>(head, cap), first = head - n;
+  for (uint64_t i = 0; i < n; ++i) {
+    const TraceEvent& e = ev[(first + i) & (cap - 1)];
+    const char* ph = e.event == TR_DATA_BEGIN ? "B" : e.event == TR_DATA_END ? "E" : "i";
+    o << (i ? ",\n" : "") << "{\"name\":\"" << (e.event == TR_DATA_BEGIN || e.event == TR_DATA_END ? "data" : names[e.event < 10 ? e.event : 0])
+      << "\",\"ph\":\"" << ph << "\",\"ts\":" << (double)e.ns / 1000.0 << ",\"pid\":" << ctx->rank << ",\"tid\":" << e.block
+      << ",\"args\":{\"coll\":" << e.collId << "}}";
+  }
+  o << "\n]}\n";
+  return ncclSuccess;
+}
+
+DF_API ncclResult_t dfcclInjectFault(ofcclRankCtx_t ctx, dfcclFault_t fault, int64_t arg) {
+  if (!ctx) return ncclInvalidArgument;
+  std::lock_guard<std::mutex> l(ctx->mu);
+  switch (fault) {
+    case dfcclFaultNone: ctx->faultDrop = ctx->faultDelayUs = ctx->faultFreezeMs = 0; break;
+    case dfcclFaultDropSqe: ctx->faultDrop = arg; break;
+    case dfcclFaultDelaySqeUs: ctx->faultDelayUs = arg; break;
+    case dfcclFaultFreezePoller: ctx->faultFreezeMs = arg; break;
+    default: return ncclInvalidArgument;
+  }
+  return ncclSuccess;
+}
+
+DF_API ncclResult_t ofcclDestroy(ofcclRankCtx_t ctx) {
+  if (!ctx) return ncclSuccess;
+  const dfcclBackend_t be = ctx->backend;
+  if (ctx->finalized) {
+    int prev = 0;
+    if (be == dfcclBackendCuda) { cudaGetDevice(&prev); cudaSetDevice(ctx->device); }
+    ctx->destroyed = true;
+    // quit entry: a running daemon leaves for good; a parked one is simply never launched again
+    {
+      std::lock_guard<std::mutex> l(ctx->mu);
+      Sqe q;
+      memset(&q, 0, sizeof(q));
+      q.collId = -1; q.flags = SQE_QUIT;
+      uint64_t tail = *ctx->hostSqTail;
+      ctx->hostSq[tail & (ctx->sqCap - 1)] = q;
+      __atomic_store_n((uint64_t*)ctx->hostSqTail, tail + 1, __ATOMIC_RELEASE);
+    }
+    ctx->stopPoller = true;
+    ctx->pollCv.notify_all();
+    if (ctx->poller.joinable()) ctx->poller.join();
+    // the launcher goes with its last member
+    std::shared_ptr<DaemonLauncher> L = ctx->launcher;
+    ctx->launcher.reset();
+    bool last = false;
+    {
+      std::lock_guard<std::mutex> l(L->mu);
+      // a shared daemon keeps running for the other ranks; mine must be out before my tables go
+      L->members.erase(std::remove(L->members.begin(), L->members.end(), ctx), L->members.end());
+      last = L->members.empty();
+      if (!last) L->stop = true;     // the table of a shared daemon names my freed state: no further launches
+    }
+    if (be == dfcclBackendCuda) {
+      if (L->stream) cudaStreamSynchronize(L->stream);
+    } else {
+      // host backend: the daemon runs inside the observer thread; wait until my blocks have parked
+      for (int i = 0; i < 20000 && ctx->ctl->alive; ++i) std::this_thread::sleep_for(std::chrono::microseconds(100));
+    }
+    if (last) {
+      if (ctx->colls.begin()->second.comm->loop) { auto loop = ctx->colls.begin()->second.comm->loop; std::lock_guard<std::mutex> l(loop->mu); if (loop->launcher == L) loop->launcher.reset(); }
+      L.reset();
+    }
+    for (auto& kv : ctx->colls) {
+      CollEntry& e = kv.second;
+      e.comm->heap->free(e.flagsOff);
+      for (int k = 0; k < 2; ++k) if (e.stagingBytes[k]) e.comm->heap->free(e.stagingOff[k]);
+    }
+    RankDev& rd = ctx->rdHost;
+    devFree(be, rd.devSq); devFree(be, rd.colls); devFree(be, rd.dyn); devFree(be, rd.doneCount); devFree(be, rd.failCount);
+    devFree(be, (void*)rd.doneEpoch); devFree(be, (void*)rd.trigger); devFree(be, rd.saved); devFree(be, rd.stats); devFree(be, rd.trace);
+    devFree(be, ctx->rdDev);
+    pinnedFree(be, ctx->hostSq); pinnedFree(be, (void*)ctx->hostSqTail); pinnedFree(be, (void*)ctx->hostSqHead);
+    pinnedFree(be, (void*)ctx->hostCq); pinnedFree(be, ctx->ctl);
+    if (be == dfcclBackendCuda) cudaSetDevice(prev);
+  }
+  delete ctx;
+  return ncclSuccess;
+}
+
+// ------------------------------------------------------------------ per-collective wrappers
+
+static ncclResult_t prep(int kind, size_t count, ncclDataType_t t, ncclRedOp_t op, int root, ncclComm_t comm, int collId, ofcclRankCtx_t ctx) {
+  dfcclCollInfo i;
+  memset(&i, 0, sizeof(i));
+  i.kind = kind; i.count = count; i.inType = i.outType = t; i.op = op; i.root = root; i.scale = 1.f;
+  return dfcclPrepare(&i, comm, collId, ctx);
+}
+DF_API ncclResult_t ofcclPrepareAllReduce(size_t count, ncclDataType_t t, ncclRedOp_t op, ncclComm_t comm, int collId, ofcclRankCtx_t ctx) { return prep(dfcclCollAllReduce, count, t, op, 0, comm, collId, ctx); }
+DF_API ncclResult_t ofcclPrepareReduce(size_t count, ncclDataType_t t, ncclRedOp_t op, int root, ncclComm_t comm, int collId, ofcclRankCtx_t ctx) { return prep(dfcclCollReduce, count, t, op, root, comm, collId, ctx); }
+DF_API ncclResult_t ofcclPrepareReduceScatter(size_t recvcount, ncclDataType_t t, ncclRedOp_t op, ncclComm_t comm, int collId, ofcclRankCtx_t ctx) { return prep(dfcclCollReduceScatter, recvcount, t, op, 0, comm, collId, ctx); }
+DF_API ncclResult_t ofcclPrepareAllGather(size_t sendcount, ncclDataType_t t, ncclComm_t comm, int collId, ofcclRankCtx_t ctx) { return prep(dfcclCollAllGather, sendcount, t, ncclSum, 0, comm, collId, ctx); }
+DF_API ncclResult_t ofcclPrepareBroadcast(size_t count, ncclDataType_t t, int root, ncclComm_t comm, int collId, ofcclRankCtx_t ctx) { return prep(dfcclCollBroadcast, count, t, ncclSum, root, comm, collId, ctx); }
+DF_API ncclResult_t ofcclPrepareBcast(size_t count, ncclDataType_t t, int root, ncclComm_t comm, int collId, ofcclRankCtx_t ctx) { return prep(dfcclCollBroadcast, count, t, ncclSum, root, comm, collId, ctx); }
+
+DF_API ncclResult_t ofcclRunAllReduce(const void* s, void* r, int collId, CallbackFunc cb, void* a, ofcclRankCtx_t ctx) { return dfcclRun(s, r, collId, cb, a, ctx); }
+DF_API ncclResult_t ofcclRunReduce(const void* s, void* r, int collId, CallbackFunc cb, void* a, ofcclRankCtx_t ctx) { return dfcclRun(s, r, collId, cb, a, ctx); }
+DF_API ncclResult_t ofcclRunReduceScatter(const void* s, void* r, int collId, CallbackFunc cb, void* a, ofcclRankCtx_t ctx) { return dfcclRun(s, r, collId, cb, a, ctx); }
+DF_API ncclResult_t ofcclRunAllGather(const void* s, void* r, int collId, CallbackFunc cb, void* a, ofcclRankCtx_t ctx) { return dfcclRun(s, r, collId, cb, a, ctx); }
+DF_API ncclResult_t ofcclRunBroadcast(const void* s, void* r, int collId, CallbackFunc cb, void* a, ofcclRankCtx_t ctx) { return dfcclRun(s, r, collId, cb, a, ctx); }
+DF_API ncclResult_t ofcclRunBcast(void* b, int collId, CallbackFunc cb, void* a, ofcclRankCtx_t ctx) { return dfcclRun(b, b, collId, cb, a, ctx); }
+
+#define DF_ALIAS(name, params, args) DF_API ncclResult_t p##name params { return name args; }
+DF_ALIAS(ofcclInitRankCtx, (ofcclRankCtx_t* c, int r), (c, r))
+DF_ALIAS(ofcclFinalizeRankCtx7StartHostThrds, (ofcclRankCtx_t c), (c))
+DF_ALIAS(ofcclPrepareDone, (ofcclRankCtx_t c), (c))
+DF_ALIAS(ofcclDestroy, (ofcclRankCtx_t c), (c))
+DF_ALIAS(ofcclPrepareAllReduce, (size_t n, ncclDataType_t t, ncclRedOp_t o, ncclComm_t c, int i, ofcclRankCtx_t x), (n, t, o, c, i, x))
+DF_ALIAS(ofcclPrepareReduce, (size_t n, ncclDataType_t t, ncclRedOp_t o, int r, ncclComm_t c, int i, ofcclRankCtx_t x), (n, t, o, r, c, i, x))
+DF_ALIAS(ofcclPrepareReduceScatter, (size_t n, ncclDataType_t t, ncclRedOp_t o, ncclComm_t c, int i, ofcclRankCtx_t x), (n, t, o, c, i, x))
+DF_ALIAS(ofcclPrepareAllGather, (size_t n, ncclDataType_t t, ncclComm_t c, int i, ofcclRankCtx_t x), (n, t, c, i, x))
+DF_ALIAS(ofcclPrepareBroadcast, (size_t n, ncclDataType_t t, int r, ncclComm_t c, int i, ofcclRankCtx_t x), (n, t, r, c, i, x))
+DF_ALIAS(ofcclPrepareBcast, (size_t n, ncclDataType_t t, int r, ncclComm_t c, int i, ofcclRankCtx_t x), (n, t, r, c, i, x))
+DF_ALIAS(ofcclRunAllReduce, (const void* s, void* r, int i, CallbackFunc cb, void* a, ofcclRankCtx_t x), (s, r, i, cb, a, x))
+DF_ALIAS(ofcclRunReduce, (const void* s, void* r, int i, CallbackFunc cb, void* a, ofcclRankCtx_t x), (s, r, i, cb, a, x))
+DF_ALIAS(ofcclRunReduceScatter, (const void* s, void* r, int i, CallbackFunc cb, void* a, ofcclRankCtx_t x), (s, r, i, cb, a, x))
+DF_ALIAS(ofcclRunAllGather, (const void* s, void* r, int i, CallbackFunc cb, void* a, ofcclRankCtx_t x), (s, r, i, cb, a, x))
+DF_ALIAS(ofcclRunBroadcast, (const void* s, void* r, int i, CallbackFunc cb, void* a, ofcclRankCtx_t x), (s, r, i, cb, a, x))
+DF_ALIAS(ofcclRunBcast, (void* b, int i, CallbackFunc cb, void* a, ofcclRankCtx_t x), (b, i, cb, a, x))

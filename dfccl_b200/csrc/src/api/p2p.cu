@@ -1,0 +1,105 @@
+#include "p2p.h"
+#include "../common/log.h"
+#include "../device/p2p_impl.h"
+#include <cstring>
+#include <map>
+#include <thread>
+#include <vector>
+
+namespace dfccl {
+
+__global__ void __launch_bounds__(512, 1) dfcclP2pKernel(RankDev* rd, const P2pList* lists) {
+  __shared__ P2pShared sh;
+  p2pBlockMain(rd, &lists[blockIdx.x / DF_P2P_CHANNELS], blockIdx.x % DF_P2P_CHANNELS, &sh);
+}
+
+namespace {
+struct Pending { ncclComm* comm; bool isSend; void* buf; size_t bytes; int peer; cudaStream_t stream; };
+thread_local std::vector<Pending> t_pending;
+
+ncclResult_t launchFor(ncclComm* c, cudaStream_t stream, const std::vector<Pending>& ops) {
+  // lists keyed by (direction, peer), operations in program order
+  std::map<std::pair<int, int>, std::vector<const Pending*>> by;
+  for (auto& p : ops) by[{p.isSend ? 1 : 0, p.peer}].push_back(&p);
+  std::vector<P2pList> lists;
+  std::vector<uint64_t> temps;         // staging areas to release after the launch has run
+  std::lock_guard<std::mutex> l(c->mu);
+  for (auto& kv : by) {
+    const int isSend = kv.first.first, peer = kv.first.second;
+    size_t done = 0;
+    while (done < kv.second.size()) {
+      P2pList L;
+      memset(&L, 0, sizeof(L));
+      L.isSend = isSend; L.peer = peer;
+      // my slots: [dir][peer][chan]; dir 0 = "receiver ready" words (read by senders), dir 1 = "data done" words (read by receivers)
+      FlagSlot* mineBase = (FlagSlot*)(c->heap->base() + c->p2pFlagsOff);
+      FlagSlot* theirBase = (FlagSlot*)(c->peerHeap[peer] + c->peerP2pFlagsOff[peer]);
+      const int n = c->nranks;
+      L.mine = mineBase + ((isSend ? 0 : 1) * n + peer) * DF_P2P_CHANNELS;
+      L.theirs = theirBase + ((isSend ? 1 : 0) * n + c->rank) * DF_P2P_CHANNELS;
+      L.peerHeap = c->peerHeap[peer]; L.myHeap = c->heap->base();
+      size_t maxBytes = 0;
+      while (done < kv.second.size() && L.nOps < DF_P2P_MAX_OPS) {
+        const Pending* p = kv.second[done++];
+        P2pOp& o = L.ops[L.nOps++];
+        o.buf = (uint64_t)(uintptr_t)p->buf; o.bytes = p->bytes;
+        o.seq = isSend ? ++c->sendSeq[peer] : ++c->recvSeq[peer];
+        if (!isSend) {
+          if (c->heap->contains(p->buf, p->bytes)) o.stagingOff = c->heap->offsetOf(p->buf);
+          else { DFCHECK(c->heap->alloc(p->bytes, &o.stagingOff, false)); o.staged = 1; temps.push_back(o.stagingOff); }
+        }
+        maxBytes = std::max(maxBytes, p->bytes);
+      }
+      L.channels = (int)std::min<size_t>(DF_P2P_CHANNELS, std::max<size_t>(1, maxBytes / (256u << 10)));
+      lists.push_back(L);
+    }
+  }
+  if (lists.empty()) return ncclSuccess;
+  // both sides must agree on the channel count of a transfer: it is a function of the byte count only
+  if (c->backend == dfcclBackendCuda) {
+    int prev = 0;
+    cudaGetDevice(&prev);
+    if (prev != c->device) cudaSetDevice(c->device);
+    P2pList* dl = nullptr;
+    CUDACHECK(cudaMallocAsync((void**)&dl, sizeof(P2pList) * lists.size(), stream));
+    CUDACHECK(cudaMemcpyAsync(dl, lists.data(), sizeof(P2pList) * lists.size(), cudaMemcpyHostToDevice, stream));
+    dfcclP2pKernel<<<(unsigned)(lists.size() * DF_P2P_CHANNELS), 512, 0, stream>>>(c->saRd, dl);
+    CUDACHECK(cudaGetLastError());
+    CUDACHECK(cudaFreeAsync(dl, stream));
+    if (!temps.empty()) {               // staged receives: the heap pieces go back once the kernel is done
+      CUDACHECK(cudaStreamSynchronize(stream));
+      for (auto off : temps) c->heap->free(off);
+    }
+    if (prev != c->device) cudaSetDevice(prev);
+  } else {
+    std::vector<std::thread> ts;
+    for (size_t i = 0; i < lists.size(); ++i)
+      for (int ch = 0; ch < DF_P2P_CHANNELS; ++ch)
+        ts.emplace_back([&, i, ch] { P2pShared sh; p2pBlockMain(c->saRd, &lists[i], ch, &sh); });
+    for (auto& t : ts) t.join();
+    for (auto off : temps) c->heap->free(off);
+  }
+  return ncclSuccess;
+}
+}  // namespace
+
+ncclResult_t p2pEnqueue(ncclComm* comm, bool isSend, void* buf, size_t count, ncclDataType_t type, int peer, cudaStream_t stream) {
+  if (!comm) return ncclInvalidArgument;
+  if (peer < 0 || peer >= comm->nranks) { DF_WARN("invalid peer %d", peer); return ncclInvalidArgument; }
+  if ((int)type < 0 || (int)type >= ncclNumTypes) return ncclInvalidArgument;
+  if (count && !buf) return ncclInvalidArgument;
+  if (peer == comm->rank) { DF_WARN("send / recv to self is not supported"); return ncclInvalidUsage; }
+  t_pending.push_back({comm, isSend, buf, count * (size_t)dtypeSize(type), peer, stream});
+  return ncclSuccess;
+}
+
+ncclResult_t p2pFlush() {
+  std::vector<Pending> all;
+  all.swap(t_pending);
+  std::map<std::pair<ncclComm*, cudaStream_t>, std::vector<Pending>> by;
+  for (auto& p : all) by[{p.comm, p.stream}].push_back(p);
+  for (auto& kv : by) DFCHECK(launchFor(kv.first.first, kv.first.second, kv.second));
+  return ncclSuccess;
+}
+
+}  // namespace dfccl

@@ -1,0 +1,93 @@
+// Rank context of the register-then-submit interface and the host threads around
+// the daemon.
+//
+// Reference counterparts: struct ofcclRankCtx (src/include/enqueue_ofccl.h:95-173),
+// prepare / finalize (src/enqueue_ofccl.cc:750-845,1284-1557), sqWrite / cqRead
+// (:616-739), the poller thread (:908-965), the kernel-launching observer thread
+// (:847-906,967-985) and destroy (:1581-1662).  What is kept: the life cycle, the
+// two host threads and their roles, the relaunch handshake through a count of
+// outstanding submissions.  What is new: a launcher object that several rank
+// contexts of one device share (their daemons are one kernel), completion entries
+// that validate themselves by a generation number instead of a host-side CAS on
+// pinned memory, stream-ordered submit / wait through stream memory operations,
+// per-collective status and a blocking wait, statistics, host-side fault hooks.
+#pragma once
+#include <atomic>
+#include <condition_variable>
+#include <map>
+#include <memory>
+#include <mutex>
+#include <thread>
+#include <vector>
+#include "../comm/comm.h"
+#include "../device/types.h"
+
+namespace dfccl {
+
+struct CollEntry {
+  dfcclCollInfo info{};
+  ncclComm* comm = nullptr;
+  CollStatic cs{};
+  uint64_t flagsOff = 0, flagsBytes = 0;
+  uint64_t stagingOff[2] = {0, 0}, stagingBytes[2] = {0, 0};
+  CallbackFunc cb = nullptr;
+  void* cbArgs = nullptr;
+  uint64_t submitted = 0, completed = 0;     // guarded by ctx->mu
+  uint64_t triggerSeq = 0;
+  uint32_t lastStatus = 0;
+};
+
+struct DaemonLauncher {
+  dfcclBackend_t backend = dfcclBackendCuda;
+  int device = 0;
+  int expected = 1;                          // rank contexts that must attach before the first launch
+  int blocks = 1, threads = 1;
+  std::vector<ofcclRankCtx*> members;
+  RankDev** devTable = nullptr;              // device array of RankDev* (host array on the host backend)
+  cudaStream_t stream = nullptr;
+  std::thread observer;
+  std::mutex mu;
+  std::condition_variable cv;
+  bool wake = false, stop = false, started = false;
+  uint64_t launches = 0;
+  ~DaemonLauncher();
+};
+
+}  // namespace dfccl
+
+struct ofcclRankCtx {
+  int rank = 0, device = 0;
+  dfcclBackend_t backend = dfcclBackendCuda;
+  bool deviceChosen = false, finalized = false, destroyed = false;
+  std::map<int, dfccl::CollEntry> colls;
+  int maxCollId = -1;
+  // queues (pinned)
+  dfccl::Sqe* hostSq = nullptr;
+  volatile uint64_t* hostSqTail = nullptr;
+  volatile uint64_t* hostSqHead = nullptr;
+  volatile uint64_t* hostCq = nullptr;
+  dfccl::DaemonCtl* ctl = nullptr;
+  uint32_t sqCap = 0, cqCap = 0;
+  uint64_t cqHead = 0;
+  // device side
+  dfccl::RankDev rdHost{};
+  dfccl::RankDev* rdDev = nullptr;
+  int nBlocks = 1;
+  // threads
+  std::shared_ptr<dfccl::DaemonLauncher> launcher;
+  int launcherSlot = 0;
+  std::thread poller;
+  std::mutex mu;                      // submissions, callbacks table, counters
+  std::condition_variable pollCv;     // poller sleeps here while nothing is outstanding
+  std::condition_variable doneCv;     // dfcclWait
+  std::atomic<int64_t> remaining{0};  // submissions without a delivered completion
+  std::atomic<bool> stopPoller{false};
+  int64_t checkInterval = 10000;      // CHECK_REMAINING_SQE_INTERVAL
+  // stats / faults
+  std::atomic<uint64_t> sqes{0}, cqes{0}, cbs{0}, sqFull{0};
+  int64_t faultDrop = 0, faultDelayUs = 0, faultFreezeMs = 0;
+  ncclResult_t asyncError = ncclSuccess;
+  // stream memory operations (cuda backend)
+  void* fnWrite64 = nullptr;
+  void* fnWait64 = nullptr;
+};

@@ -1,0 +1,223 @@
+#include "comm.h"
+#include "../common/log.h"
+#include "../common/param.h"
+#include "../device/engine.h"
+#include "../device/launch.h"
+#include "../topo/topo.h"
+#include <atomic>
+#include <cstring>
+#include <map>
+#include <unistd.h>
+
+namespace dfccl {
+
+namespace {
+std::atomic<int> g_backend{-1};
+std::mutex g_heapMu;
+std::map<std::pair<int, int>, Heap*> g_heaps;     // (backend, device) -> process heap
+}  // namespace
+
+dfcclBackend_t defaultBackend() {
+  int b = g_backend.load();
+  if (b >= 0) return (dfcclBackend_t)b;
+  std::string s = paramStr("BACKEND", "");
+  if (s == "host" || s == "cpu") b = dfcclBackendHost;
+  else if (s == "cuda" || s == "gpu") b = dfcclBackendCuda;
+  else {
+    int n = 0;
+    if (cudaGetDeviceCount(&n) != cudaSuccess) { (void)cudaGetLastError(); n = 0; }
+    b = n > 0 ? dfcclBackendCuda : dfcclBackendHost;
+  }
+  g_backend = b;
+  return (dfcclBackend_t)b;
+}
+void setDefaultBackend(dfcclBackend_t b) { g_backend = (int)b; }
+
+int daemonThreads(dfcclBackend_t be) { return be == dfcclBackendCuda ? (int)paramI64("DAEMON_THREADS", 512) : 1; }
+int daemonBlocks(dfcclBackend_t be) {
+  int64_t v = paramI64("DAEMON_BLOCKS", be == dfcclBackendCuda ? 32 : 2);
+  if (v < 1) v = 1;
+  if (v > DF_MAX_BLOCKS) v = DF_MAX_BLOCKS;
+  return (int)v;
+}
+
+ncclResult_t processHeap(dfcclBackend_t backend, int device, Heap** out) {
+  std::lock_guard<std::mutex> l(g_heapMu);
+  auto key = std::make_pair((int)backend, device);
+  auto it = g_heaps.find(key);
+  if (it != g_heaps.end()) { *out = it->second; return ncclSuccess; }
+  size_t bytes = (size_t)paramI64("HEAP_BYTES", backend == dfcclBackendCuda ? (4ll << 30) : (256ll << 20));
+  Heap* h = nullptr;
+  DFCHECK(Heap::create(backend, device, bytes, &h));
+  g_heaps[key] = h;
+  *out = h;
+  return ncclSuccess;
+}
+
+ncclResult_t resolveRedOp(ncclComm* comm, ncclRedOp_t op, ncclDataType_t type, int nranks, int* devOp, double* scale, int* postDiv) {
+  *scale = 1.0; *postDiv = 0;
+  const bool isFloat = type == ncclFloat16 || type == ncclFloat32 || type == ncclFloat64 || type == ncclBfloat16;
+  switch ((int)op) {
+    case ncclSum: *devOp = OP_SUM; return ncclSuccess;
+    case ncclProd: *devOp = OP_PROD; return ncclSuccess;
+    case ncclMax: *devOp = OP_MAX; return ncclSuccess;
+    case ncclMin: *devOp = OP_MIN; return ncclSuccess;
+    case ncclAvg:                                    // floats: scaled sum; integers: sum then divide
+      *devOp = OP_SUM;
+      if (isFloat) *scale = 1.0 / nranks; else *postDiv = nranks;
+      return ncclSuccess;
+    default: break;
+  }
+  int idx = (int)op - (int)ncclNumOps;
+  if (!comm || idx < 0 || idx >= (int)comm->userOps.size() || !comm->userOps[idx].live) {
+    DF_WARN("invalid reduction operator %d", (int)op);
+    return ncclInvalidArgument;
+  }
+  *devOp = OP_SUM;
+  *scale = comm->userOps[idx].scalar;
+  return ncclSuccess;
+}
+
+struct PeerInfoMsg {
+  HeapHandle heap;
+  uint64_t saFlagsOff, p2pFlagsOff;
+  uint64_t commHash;
+  int32_t device, backend;
+};
+
+ncclResult_t commCreate(std::shared_ptr<Bootstrap> boot, dfcclBackend_t backend, int device, bool privateHeap,
+                        std::shared_ptr<LoopGroup> loop, ncclComm** out) {
+  const int n = boot->nranks(), r = boot->rank();
+  if (n > DF_MAX_RANKS) { DF_WARN("communicators of more than %d ranks are not supported by the direct-access engine", DF_MAX_RANKS); return ncclInvalidArgument; }
+  std::unique_ptr<ncclComm> c(new ncclComm());
+  c->rank = r; c->nranks = n; c->device = device; c->backend = backend; c->boot = boot; c->loop = loop;
+  logSetRank(r);
+  int prevDev = 0;
+  if (backend == dfcclBackendCuda) { cudaGetDevice(&prevDev); CUDACHECK(cudaSetDevice(device)); }
+  if (privateHeap) {
+    size_t bytes = (size_t)paramI64("HEAP_BYTES", backend == dfcclBackendCuda ? (1ll << 30) : (64ll << 20));
+    DFCHECK(Heap::create(backend, device, bytes, &c->heap));
+    c->ownsHeap = true;
+  } else {
+    DFCHECK(processHeap(backend, device, &c->heap));
+  }
+  DFCHECK(pinnedAlloc(backend, (void**)&c->ctl, sizeof(DaemonCtl)));
+  boot->setAbortFlag(&c->ctl->abortFlag);
+  // flag words of the stream-ordered engine and of send / recv
+  DFCHECK(c->heap->alloc(sizeof(FlagSlot) * DF_MAX_BLOCKS * n, &c->saFlagsOff));
+  DFCHECK(c->heap->alloc(sizeof(FlagSlot) * 2 * n * 8, &c->p2pFlagsOff));   // [direction][peer][channel]
+  std::vector<PeerInfoMsg> all(n);
+  PeerInfoMsg& me = all[r];
+  c->heap->exportHandle(&me.heap);
+  me.saFlagsOff = c->saFlagsOff; me.p2pFlagsOff = c->p2pFlagsOff; me.device = device; me.backend = backend;
+  me.commHash = r == 0 ? ((uint64_t)getpid() << 32) ^ (uint64_t)(uintptr_t)c.get() ^ hostHash() : 0;
+  DFCHECK(boot->allGather(all.data(), sizeof(PeerInfoMsg)));
+  c->commHash = all[0].commHash;
+  c->handles.resize(n); c->peerHeap.resize(n); c->peerSaFlagsOff.resize(n); c->peerP2pFlagsOff.resize(n);
+  c->sendSeq.assign(n, 0); c->recvSeq.assign(n, 0);
+  for (int j = 0; j < n; ++j) {
+    c->handles[j] = all[j].heap;
+    c->peerSaFlagsOff[j] = all[j].saFlagsOff;
+    c->peerP2pFlagsOff[j] = all[j].p2pFlagsOff;
+    if (j == r) c->peerHeap[j] = c->heap->base();
+    else DFCHECK(c->heap->importPeer(all[j].heap, &c->peerHeap[j]));
+  }
+  // minimal RankDev for stream-ordered kernels: control words and timeouts only
+  RankDev& rd = c->saRdHost;
+  memset(&rd, 0, sizeof(rd));
+  rd.ctl = c->ctl; rd.nBlocks = DF_MAX_BLOCKS; rd.maxColls = 1;
+  rd.spinBudget = 4096; rd.headTries = 1;
+  rd.waitTimeoutNs = (uint64_t)paramI64("WAIT_TIMEOUT_MS", 30000) * 1000000ull;
+  DFCHECK(devAlloc(backend, (void**)&rd.dyn, sizeof(CollDyn) * DF_MAX_BLOCKS));
+  DFCHECK(devAlloc(backend, (void**)&c->saRd, sizeof(RankDev)));
+  DFCHECK(devUpload(backend, c->saRd, &rd, sizeof(RankDev)));
+  DFCHECK(boot->barrier());          // every member has mapped everything before anyone uses it
+  if (backend == dfcclBackendCuda) cudaSetDevice(prevDev);
+  DF_INFO(SUB_INIT, "comm %llx rank %d/%d device %d backend %s heap %zu MiB", (unsigned long long)c->commHash, r, n, device,
+          backend == dfcclBackendCuda ? "cuda" : "host", c->heap->bytes() >> 20);
+  *out = c.release();
+  return ncclSuccess;
+}
+
+ncclResult_t commDestroy(ncclComm* c) {
+  if (!c) return ncclSuccess;
+  if (c->backend == dfcclBackendCuda) { int prev; cudaGetDevice(&prev); cudaSetDevice(c->device); cudaDeviceSynchronize(); (void)cudaGetLastError(); cudaSetDevice(prev); }
+  c->heap->free(c->saFlagsOff);
+  c->heap->free(c->p2pFlagsOff);
+  for (int k = 0; k < 2; ++k) if (c->scratchBytes[k]) c->heap->free(c->scratchOff[k]);
+  devFree(c->backend, c->saRdHost.dyn);
+  devFree(c->backend, c->saRd);
+  pinnedFree(c->backend, c->ctl);
+  if (c->ownsHeap) delete c->heap;
+  delete c;
+  return ncclSuccess;
+}
+
+static ncclResult_t ensureScratch(ncclComm* c, int which, size_t bytes) {
+  if (c->scratchBytes[which] >= bytes) return ncclSuccess;
+  if (c->scratchBytes[which]) {
+    // a previous stream-ordered collective may still read it: drain before growing
+    if (c->backend == dfcclBackendCuda) CUDACHECK(cudaDeviceSynchronize());
+    c->heap->free(c->scratchOff[which]);
+    c->scratchBytes[which] = 0;
+  }
+  size_t want = std::max<size_t>(bytes, 4u << 20);
+  DFCHECK(c->heap->alloc(want, &c->scratchOff[which], false));
+  c->scratchBytes[which] = want;
+  return ncclSuccess;
+}
+
+ncclResult_t commCollective(ncclComm* c, int kind, const void* send, void* recv, size_t count, ncclDataType_t type,
+                            ncclRedOp_t op, int root, cudaStream_t stream) {
+  if (!c) { DF_WARN("null communicator"); return ncclInvalidArgument; }
+  if (c->aborted) return ncclInvalidUsage;
+  if ((int)type < 0 || (int)type >= ncclNumTypes) { DF_WARN("invalid datatype %d", (int)type); return ncclInvalidArgument; }
+  if (root < 0 || root >= c->nranks) { DF_WARN("invalid root %d", root); return ncclInvalidArgument; }
+  if (count == 0) return ncclSuccess;
+  const bool needSend = !(kind == dfcclCollBroadcast && c->rank != root);
+  const bool needRecv = !(kind == dfcclCollReduce && c->rank != root);
+  if ((needSend && !send) || (needRecv && !recv)) { DF_WARN("null buffer"); return ncclInvalidArgument; }
+  std::lock_guard<std::mutex> l(c->mu);
+  CollStatic cs;
+  memset(&cs, 0, sizeof(cs));
+  cs.kind = kind; cs.inType = cs.outType = type; cs.nranks = c->nranks; cs.rank = c->rank; cs.root = root;
+  cs.count = count; cs.valid = 1; cs.scale = 1.0;
+  int devOp = OP_SUM;
+  if (kind == dfcclCollAllReduce || kind == dfcclCollReduce || kind == dfcclCollReduceScatter)
+    DFCHECK(resolveRedOp(c, op, type, c->nranks, &devOp, &cs.scale, &cs.postDiv));
+  cs.op = devOp;
+  const Topology* topo = nullptr;
+  DFCHECK(topoGet(&topo));
+  const size_t bytes = count * dtypeSize(type);
+  TunerChoice ch = tunerChoose(*topo, kind, bytes, c->nranks, daemonBlocks(c->backend), false);
+  cs.algo = ch.algo; cs.nBlocks = ch.nBlocks;
+  cs.myFlags = (FlagSlot*)(c->heap->base() + c->saFlagsOff);
+  for (int j = 0; j < c->nranks; ++j) {
+    cs.peerHeap[j] = c->peerHeap[j];
+    cs.peerFlags[j] = (FlagSlot*)(c->peerHeap[j] + c->peerSaFlagsOff[j]);
+  }
+  uint32_t flags = 0;
+  uint64_t s = 0, r = 0;
+  const size_t sBytes = sendBytes(&cs), rBytes = recvBytes(&cs);
+  bool stageSend = needSend && !c->heap->contains(send, sBytes);
+  // one-shot in place: peers read my input while I overwrite it, so they get a private copy
+  if (needSend && kind == dfcclCollAllReduce && cs.algo == dfcclAlgoOneShot && send == recv && c->nranks > 1) stageSend = true;
+  if (stageSend) { DFCHECK(ensureScratch(c, 0, sBytes)); flags |= SQE_SEND_STAGED; s = (uint64_t)(uintptr_t)send; cs.stagingSendOff = c->scratchOff[0]; }
+  else if (needSend) s = c->heap->offsetOf(send);
+  if (needRecv && !c->heap->contains(recv, rBytes)) { DFCHECK(ensureScratch(c, 1, rBytes)); flags |= SQE_RECV_STAGED; r = (uint64_t)(uintptr_t)recv; cs.stagingRecvOff = c->scratchOff[1]; }
+  else if (needRecv) r = c->heap->offsetOf(recv);
+  const uint32_t epoch = ++c->opCount;
+  if (c->backend == dfcclBackendCuda) {
+    int prev = 0;
+    cudaGetDevice(&prev);
+    if (prev != c->device) cudaSetDevice(c->device);
+    ncclResult_t res = launchStandaloneCuda(c->saRd, cs, s, r, epoch, flags, daemonThreads(c->backend), stream);
+    if (prev != c->device) cudaSetDevice(prev);
+    return res;
+  }
+  runStandaloneHost(c->saRd, cs, s, r, epoch, flags);
+  if (c->ctl->pad) { c->asyncError = c->ctl->pad == ST_TIMEOUT ? dfcclTimeout : dfcclAborted; return c->asyncError; }
+  return ncclSuccess;
+}
+
+}  // namespace dfccl

@@ -1,0 +1,83 @@
+// Communicator object behind ncclComm_t.
+//
+// Same user-visible role as the reference's ncclComm (src/include/comm.h:88-213,
+// created by src/init.cc:907-990): rank / size / device, rendezvous, error state,
+// user reduction ops.  What it owns is different: instead of channels, rings,
+// trees, proxy threads and per-peer connectors it holds the mapping of every
+// member's symmetric heap plus one small block of flag words for the
+// stream-ordered collectives, because every collective here is direct loads and
+// stores on peer memory.
+#pragma once
+#include <memory>
+#include <mutex>
+#include <vector>
+#include "dfccl.h"
+#include "../bootstrap/bootstrap.h"
+#include "../device/types.h"
+#include "../mem/heap.h"
+
+namespace dfccl {
+struct DaemonLauncher;
+
+// Ranks of one process that share a device (or are all on the host backend) and
+// therefore one daemon launch.
+struct LoopGroup {
+  int nranks = 0;
+  int device = 0;
+  dfcclBackend_t backend = dfcclBackendCuda;
+  std::shared_ptr<DaemonLauncher> launcher;
+  std::mutex mu;
+};
+
+struct UserRedOp { bool live = false; double scalar = 1.0; };
+
+}  // namespace dfccl
+
+struct ncclComm {
+  int rank = 0, nranks = 1, device = 0;
+  dfcclBackend_t backend = dfcclBackendCuda;
+  uint64_t commHash = 0;
+  std::shared_ptr<dfccl::Bootstrap> boot;
+  dfccl::Heap* heap = nullptr;
+  bool ownsHeap = false;
+  std::vector<dfccl::HeapHandle> handles;
+  std::vector<char*> peerHeap;                 // heap base of every member as mapped here
+  // stream-ordered engine
+  dfccl::RankDev* saRd = nullptr;              // device copy (host memory on the host backend)
+  dfccl::RankDev saRdHost{};
+  dfccl::DaemonCtl* ctl = nullptr;             // pinned
+  uint64_t saFlagsOff = 0;
+  std::vector<uint64_t> peerSaFlagsOff;
+  uint64_t p2pFlagsOff = 0;
+  std::vector<uint64_t> peerP2pFlagsOff;
+  std::vector<uint32_t> sendSeq, recvSeq;      // per peer
+  uint64_t scratchOff[2] = {0, 0};             // staging for buffers outside the heap (send, recv)
+  uint64_t scratchBytes[2] = {0, 0};
+  uint32_t opCount = 0;
+  uint32_t splitCount = 0;
+  std::mutex mu;
+  ncclResult_t asyncError = ncclSuccess;
+  std::vector<dfccl::UserRedOp> userOps;
+  std::shared_ptr<dfccl::LoopGroup> loop;      // set for loopback / InitAll groups
+  bool aborted = false;
+};
+
+namespace dfccl {
+
+ncclResult_t commCreate(std::shared_ptr<Bootstrap> boot, dfcclBackend_t backend, int device, bool privateHeap,
+                        std::shared_ptr<LoopGroup> loop, ncclComm** out);
+ncclResult_t commDestroy(ncclComm* comm);
+dfcclBackend_t defaultBackend();
+void setDefaultBackend(dfcclBackend_t b);
+int daemonThreads(dfcclBackend_t be);
+int daemonBlocks(dfcclBackend_t be);
+// Reduction operator bookkeeping shared by both interfaces: maps ncclAvg / user ops to (op, scale, postDiv).
+ncclResult_t resolveRedOp(ncclComm* comm, ncclRedOp_t op, ncclDataType_t type, int nranks, int* devOp, double* scale, int* postDiv);
+// Heap of (backend, device), created on first use and shared by all communicators of the process.
+ncclResult_t processHeap(dfcclBackend_t backend, int device, Heap** out);
+
+// The engine behind the stream-ordered entry points.
+ncclResult_t commCollective(ncclComm* comm, int kind, const void* send, void* recv, size_t count, ncclDataType_t type,
+                            ncclRedOp_t op, int root, cudaStream_t stream);
+
+}  // namespace dfccl

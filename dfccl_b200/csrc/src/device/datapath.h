@@ -1,0 +1,235 @@
+// Element-wise data path: N sources -> reduce -> scale / divide -> cast -> M destinations.
+//
+// Role of the reference's ReduceOrCopyMulti and its functors
+// (src/include/common_kernel.h:490-690, src/include/reduce_kernel.h:15-705), built
+// differently: sources and destinations are plain pointers into this GPU's or a
+// peer's symmetric heap (no FIFO slots), 16/32-bit floating inputs accumulate in
+// fp32 in a fixed rank order so every rank computes bit-identical results, and
+// the scale (gradient averaging, user PreMulSum scalar) and the output cast are
+// applied in registers before the only store - the "fused scale / cast".
+// The 16-byte packs are the unit of every vector access; a range whose pointers
+// are not 16-byte aligned takes the scalar path.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include "dfccl.h"
+#include "platform.h"
+#include "types.h"
+
+namespace dfccl {
+
+enum RedOp : int { OP_SUM = 0, OP_PROD = 1, OP_MAX = 2, OP_MIN = 3 };
+
+struct DataArgs {
+  int nsrc, ndst;
+  const char* src[DF_MAX_RANKS];
+  char* dst[DF_MAX_RANKS];
+  uint64_t n;            // elements
+  double scale;          // 1.0 = none
+  int postDiv;           // 0 = none
+};
+
+template <int N> struct BitsOf;
+template <> struct BitsOf<1> { typedef uint8_t type; };
+template <> struct BitsOf<2> { typedef uint16_t type; };
+template <> struct BitsOf<4> { typedef uint32_t type; };
+template <> struct BitsOf<8> { typedef uint64_t type; };
+
+template <typename T> DF_HD T ld_elem(const T* p) {
+  typedef typename BitsOf<sizeof(T)>::type B;
+  B b = *(const volatile B*)p;
+  T v;
+  __builtin_memcpy(&v, &b, sizeof(T));
+  return v;
+}
+template <typename T> DF_HD void st_elem(T* p, T v) {
+  typedef typename BitsOf<sizeof(T)>::type B;
+  B b;
+  __builtin_memcpy(&b, &v, sizeof(T));
+  *(volatile B*)p = b;
+}
+
+// accumulator type and conversions
+template <typename T> struct Elem { typedef T Acc; static DF_HD Acc up(T v) { return v; } static DF_HD T down(Acc a) { return a; } enum { isFloat = 0 }; };
+template <> struct Elem<int8_t> { typedef int32_t Acc; static DF_HD Acc up(int8_t v) { return v; } static DF_HD int8_t down(Acc a) { return (int8_t)a; } enum { isFloat = 0 }; };
+template <> struct Elem<uint8_t> { typedef uint32_t Acc; static DF_HD Acc up(uint8_t v) { return v; } static DF_HD uint8_t down(Acc a) { return (uint8_t)a; } enum { isFloat = 0 }; };
+template <> struct Elem<float> { typedef float Acc; static DF_HD Acc up(float v) { return v; } static DF_HD float down(Acc a) { return a; } enum { isFloat = 1 }; };
+template <> struct Elem<double> { typedef double Acc; static DF_HD Acc up(double v) { return v; } static DF_HD double down(Acc a) { return a; } enum { isFloat = 1 }; };
+template <> struct Elem<__half> { typedef float Acc; static DF_HD Acc up(__half v) { return __half2float(v); } static DF_HD __half down(Acc a) { return __float2half_rn(a); } enum { isFloat = 1 }; };
+template <> struct Elem<__nv_bfloat16> { typedef float Acc; static DF_HD Acc up(__nv_bfloat16 v) { return __bfloat162float(v); } static DF_HD __nv_bfloat16 down(Acc a) { return __float2bfloat16_rn(a); } enum { isFloat = 1 }; };
+
+template <int OP, typename A> DF_HD A red(A a, A b) {
+  if (OP == OP_SUM) return a + b;
+  if (OP == OP_PROD) return a * b;
+  if (OP == OP_MAX) return a > b ? a : b;
+  return a < b ? a : b;
+}
+
+template <typename Tin, typename Tout, typename A>
+DF_HD typename Elem<Tout>::Acc finish(A a, double scale, int postDiv) {
+  typedef typename Elem<Tout>::Acc AO;
+  if (Elem<Tin>::isFloat) {
+    if (scale != 1.0) a = (A)(a * (A)scale);
+  } else if (postDiv) {
+    a = a / (A)postDiv;
+  } else if (scale != 1.0) {
+    a = (A)((double)a * scale);
+  }
+  return (AO)a;
+}
+
+template <int BYTES> struct Pack;
+template <> struct Pack<16> { uint4 v; static DF_HD void st(void* p, const Pack& k) { st16(p, k.v); } };
+template <> struct Pack<32> { uint4 v[2]; static DF_HD void st(void* p, const Pack& k) { st16(p, k.v[0]); st16((char*)p + 16, k.v[1]); } };
+template <> struct Pack<8> { uint2 v; static DF_HD void st(void* p, const Pack& k) {
+#if DF_DEVICE_CODE
+  asm volatile("st.relaxed.sys.global.v2.u32 [%0], {%1,%2};" ::"l"(p), "r"(k.v.x), "r"(k.v.y) : "memory");
+#else
+  __builtin_memcpy(p, &k.v, 8);
+#endif
+} };
+
+// One noinline body per (input type, output type, operator): the daemon's register
+// budget is the maximum over what it inlines, so the variants stay out of line.
+template <typename Tin, typename Tout, int OP>
+DF_HD_NOINLINE void reduce_copy(const DataArgs* a) {
+  typedef typename Elem<Tin>::Acc A;
+  constexpr int V = 16 / (int)sizeof(Tin);
+  constexpr int OUTB = V * (int)sizeof(Tout);
+  constexpr int U = sizeof(Tin) >= 4 ? 4 : 2;
+  const int tid = df_tid(), nt = df_nthreads();
+  const int nsrc = a->nsrc, ndst = a->ndst;
+  const uint64_t n = a->n;
+  const double scale = a->scale;
+  const int postDiv = a->postDiv;
+
+  bool aligned = true;
+  for (int j = 0; j < nsrc; ++j) aligned &= ((uintptr_t)a->src[j] & 15) == 0;
+  for (int j = 0; j < ndst; ++j) aligned &= ((uintptr_t)a->dst[j] & (OUTB >= 16 ? 15 : OUTB - 1)) == 0;
+  const uint64_t nPacks = aligned ? n / V : 0;
+
+  for (uint64_t base = 0; base < nPacks; base += (uint64_t)nt * U) {
+    A acc[U][V];
+    uint64_t idx[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      idx[u] = base + (uint64_t)u * nt + tid;
+      if (idx[u] < nPacks) {
+        uint4 raw = ld16(a->src[0] + idx[u] * 16);
+        Tin e[V];
+        __builtin_memcpy(e, &raw, 16);          // bit copy, not a pointer cast: host compilers enforce strict aliasing
+#pragma unroll
+        for (int k = 0; k < V; ++k) acc[u][k] = Elem<Tin>::up(e[k]);
+      }
+    }
+    for (int j = 1; j < nsrc; ++j) {
+      uint4 raw[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) if (idx[u] < nPacks) raw[u] = ld16(a->src[j] + idx[u] * 16);
+#pragma unroll
+      for (int u = 0; u < U; ++u) if (idx[u] < nPacks) {
+        Tin e[V];
+        __builtin_memcpy(e, &raw[u], 16);
+#pragma unroll
+        for (int k = 0; k < V; ++k) acc[u][k] = red<OP>(acc[u][k], Elem<Tin>::up(e[k]));
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) if (idx[u] < nPacks) {
+      Pack<OUTB> out;
+      Tout o[V];
+#pragma unroll
+      for (int k = 0; k < V; ++k) o[k] = Elem<Tout>::down(finish<Tin, Tout>(acc[u][k], scale, postDiv));
+      __builtin_memcpy(&out, o, OUTB);
+      for (int d = 0; d < ndst; ++d) Pack<OUTB>::st(a->dst[d] + idx[u] * OUTB, out);
+    }
+  }
+  // ragged tail, or everything when a pointer is not 16-byte aligned
+  for (uint64_t i = nPacks * V + tid; i < n; i += nt) {
+    A acc = Elem<Tin>::up(ld_elem((const Tin*)a->src[0] + i));
+    for (int j = 1; j < nsrc; ++j) acc = red<OP>(acc, Elem<Tin>::up(ld_elem((const Tin*)a->src[j] + i)));
+    Tout o = Elem<Tout>::down(finish<Tin, Tout>(acc, scale, postDiv));
+    for (int d = 0; d < ndst; ++d) st_elem((Tout*)a->dst[d] + i, o);
+  }
+}
+
+// Byte copy of one source to M destinations (AllGather, Broadcast, staging).
+static DF_HD_NOINLINE void copy_multi(const DataArgs* a) {
+  constexpr int U = 8;
+  const int tid = df_tid(), nt = df_nthreads();
+  const int ndst = a->ndst;
+  const uint64_t nbytes = a->n;
+  bool aligned = ((uintptr_t)a->src[0] & 15) == 0;
+  for (int j = 0; j < ndst; ++j) aligned &= ((uintptr_t)a->dst[j] & 15) == 0;
+  const uint64_t nPacks = aligned ? nbytes / 16 : 0;
+  for (uint64_t base = 0; base < nPacks; base += (uint64_t)nt * U) {
+    uint4 raw[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) { uint64_t i = base + (uint64_t)u * nt + tid; if (i < nPacks) raw[u] = ld16(a->src[0] + i * 16); }
+    for (int d = 0; d < ndst; ++d) {
+#pragma unroll
+      for (int u = 0; u < U; ++u) { uint64_t i = base + (uint64_t)u * nt + tid; if (i < nPacks) st16(a->dst[d] + i * 16, raw[u]); }
+    }
+  }
+  for (uint64_t i = nPacks * 16 + tid; i < nbytes; i += nt) {
+    uint8_t b = ld_elem((const uint8_t*)a->src[0] + i);
+    for (int d = 0; d < ndst; ++d) st_elem((uint8_t*)a->dst[d] + i, b);
+  }
+}
+
+DF_HD int dtypeSize(int t) {
+  switch (t) {
+    case ncclInt8: case ncclUint8: return 1;
+    case ncclFloat16: case ncclBfloat16: return 2;
+    case ncclInt32: case ncclUint32: case ncclFloat32: return 4;
+    default: return 8;
+  }
+}
+
+template <typename T>
+DF_HD void reduce_same(int op, const DataArgs* a) {
+  switch (op) {
+    case OP_SUM: reduce_copy<T, T, OP_SUM>(a); break;
+    case OP_PROD: reduce_copy<T, T, OP_PROD>(a); break;
+    case OP_MAX: reduce_copy<T, T, OP_MAX>(a); break;
+    default: reduce_copy<T, T, OP_MIN>(a); break;
+  }
+}
+
+// Returns false when the (in, out, op) combination is not instantiated.
+static DF_HD_NOINLINE bool reduce_dispatch(int inType, int outType, int op, const DataArgs* a) {
+  if (inType == outType) {
+    switch (inType) {
+#ifndef DF_FAST_BUILD
+      case ncclInt8: reduce_same<int8_t>(op, a); return true;
+      case ncclUint8: reduce_same<uint8_t>(op, a); return true;
+      case ncclInt32: reduce_same<int32_t>(op, a); return true;
+      case ncclUint32: reduce_same<uint32_t>(op, a); return true;
+      case ncclInt64: reduce_same<int64_t>(op, a); return true;
+      case ncclUint64: reduce_same<uint64_t>(op, a); return true;
+      case ncclFloat16: reduce_same<__half>(op, a); return true;
+      case ncclFloat64: reduce_same<double>(op, a); return true;
+#endif
+      case ncclFloat32: reduce_same<float>(op, a); return true;
+      case ncclBfloat16: reduce_same<__nv_bfloat16>(op, a); return true;
+      default: return false;
+    }
+  }
+  if (op != OP_SUM) return false;   // fused casts exist for the gradient path only
+  if (inType == ncclBfloat16 && outType == ncclFloat32) { reduce_copy<__nv_bfloat16, float, OP_SUM>(a); return true; }
+  if (inType == ncclFloat16 && outType == ncclFloat32) { reduce_copy<__half, float, OP_SUM>(a); return true; }
+  if (inType == ncclFloat32 && outType == ncclBfloat16) { reduce_copy<float, __nv_bfloat16, OP_SUM>(a); return true; }
+  if (inType == ncclFloat32 && outType == ncclFloat16) { reduce_copy<float, __half, OP_SUM>(a); return true; }
+  return false;
+}
+
+// Host-callable check used at prepare time.
+inline bool reduceSupported(int inType, int outType, int op) {
+  if (inType < 0 || inType >= ncclNumTypes || outType < 0 || outType >= ncclNumTypes) return false;
+  if (inType == outType) return op >= OP_SUM && op <= OP_MIN;
+  if (op != OP_SUM) return false;
+  return ((inType == ncclBfloat16 || inType == ncclFloat16) && outType == ncclFloat32) ||
+         (inType == ncclFloat32 && (outType == ncclBfloat16 || outType == ncclFloat16));
+}
+
+}  // namespace dfccl

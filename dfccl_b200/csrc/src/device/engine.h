@@ -1,0 +1,426 @@
+// Step engine: one registered collective, executed by one block, as a resumable
+// sequence of phases (types.h: Phase).  Two kinds of phases exist:
+//   * bounded waits (PH_TRIGGER, PH_WAIT_ARRIVE, PH_WAIT_DONE) poll words in LOCAL
+//     memory that a peer, the host or a stream memory operation writes.  A wait
+//     that runs out of budget returns to the scheduler without side effects: it
+//     consumed nothing and wrote nothing, so parking the collective is saving
+//     (phase, cursor) - there is no connection state to unwind.
+//   * actions (posting flags, moving data) never wait for anybody.
+// This replaces the reference's preemptible ring primitives, where a context
+// switch had to unwind a half-executed slice and re-synchronise every thread role
+// (src/collectives_ofccl/device/ofccl_prims_simple.h:118-140,217-491 and the
+// resumable ring loops in ofccl_all_reduce.h:44-217): on an NVSwitch fabric every
+// peer is one hop away, so each collective is "everybody arrived -> direct loads
+// and stores of peer buffers -> everybody done" and the only blocking points are
+// the two rendezvous.
+//
+// Schedules (kind x algo), all expressed as N-source / M-destination reduce-copy:
+//   AllReduce two-shot  : block b, rank r owns shard r of slice b: reads it from all
+//                         ranks, reduces, scales, casts, writes it to all ranks.
+//   AllReduce one-shot  : every rank reads slice b from all ranks, writes only itself.
+//   AllGather           : rank r pushes its slice b into every rank's output.
+//   ReduceScatter       : rank r reads slice b of chunk r from all ranks.
+//   Broadcast           : non-roots pull slice b from the root.
+//   Reduce              : like two-shot AllReduce, but shards are written to the root only.
+#pragma once
+#include "datapath.h"
+#include "platform.h"
+#include "types.h"
+#if !defined(__CUDA_ARCH__)
+#include <cstdio>
+#include <cstdlib>
+#endif
+
+namespace dfccl {
+
+enum RunResult : int { RC_DONE = 0, RC_STALLED = 1, RC_YIELD = 2 };
+
+struct BlockShared {
+  CollStatic cs;                 // static context of the loaded collective
+  CollDyn dyn;                   // its dynamic context (authoritative copy while loaded)
+  DataArgs args;
+  int32_t loadedColl;            // -1 = nothing loaded
+  int32_t standalone;            // 1 = stream-ordered kernel: no queues, completion is the kernel's end
+  int32_t dynDirty;
+  int32_t waitOk;
+  uint32_t waitSpins;
+  int32_t ctl0, ctl1;
+  uint64_t ctl64;
+  DevStats stats;
+  uint64_t frontier;
+  uint32_t nActive;
+  uint32_t quit;                 // 1 = voluntary, 2 = final, 3 = abort
+  uint16_t active[DF_MAX_ACTIVE];
+};
+
+DF_HD void trace(RankDev* rd, int b, uint16_t ev, int coll) {
+  if (rd->trace == nullptr) return;
+  unsigned long long i = atomic_add_u64((unsigned long long*)&rd->traceHead, 1ull);
+  TraceEvent* e = &rd->trace[i & (rd->traceCap - 1)];
+  e->ns = df_now_ns(); e->block = (uint16_t)b; e->event = ev; e->collId = coll;
+}
+
+DF_HD uint64_t umin64(uint64_t a, uint64_t b) { return a < b ? a : b; }
+
+// [beg,end) of part idx when [0,total) is cut into nparts pieces on `align` boundaries
+DF_HD void partRange(uint64_t total, int nparts, int idx, uint64_t align, uint64_t* beg, uint64_t* end) {
+  uint64_t per = (total + nparts - 1) / nparts;
+  per = (per + align - 1) / align * align;
+  *beg = umin64(total, per * (uint64_t)idx);
+  *end = umin64(total, *beg + per);
+}
+
+// bytes of the user's send / recv buffer (staging copies)
+DF_HD uint64_t sendBytes(const CollStatic* c) {
+  uint64_t e = dtypeSize(c->inType);
+  switch (c->kind) {
+    case dfcclCollReduceScatter: return c->count * c->nranks * e;
+    default: return c->count * e;
+  }
+}
+DF_HD uint64_t recvBytes(const CollStatic* c) {
+  uint64_t e = dtypeSize(c->outType);
+  switch (c->kind) {
+    case dfcclCollAllGather: return c->count * c->nranks * e;
+    default: return c->count * e;
+  }
+}
+
+// ---- context switch: load / save the (static, dynamic) context of a collective
+DF_HD void loadColl(BlockShared* sh, RankDev* rd, int b, int coll) {
+  if (sh->loadedColl == coll) return;
+  const int tid = df_tid(), nt = df_nthreads();
+  uint64_t t0 = 0;
+  if (tid == 0) t0 = df_now_ns();
+  if (sh->loadedColl >= 0 && sh->dynDirty) {           // park the previous one
+    CollDyn* g = &rd->dyn[(uint64_t)b * rd->maxColls + sh->loadedColl];
+    const uint4* s = (const uint4*)&sh->dyn;
+    for (int i = tid; i < (int)(sizeof(CollDyn) / 16); i += nt) ((uint4*)g)[i] = s[i];
+    if (tid == 0) sh->stats.ctxSaves++;
+  }
+  df_sync();
+  {
+    const uint4* s = (const uint4*)&rd->colls[coll];
+    uint4* d = (uint4*)&sh->cs;
+    for (int i = tid; i < (int)(sizeof(CollStatic) / 16); i += nt) d[i] = s[i];
+    const uint4* sd = (const uint4*)&rd->dyn[(uint64_t)b * rd->maxColls + coll];
+    uint4* dd = (uint4*)&sh->dyn;
+    for (int i = tid; i < (int)(sizeof(CollDyn) / 16); i += nt) dd[i] = sd[i];
+  }
+  if (tid == 0) {
+    if (sh->loadedColl >= 0) {
+      sh->stats.ctxSwitches++;
+      uint64_t dt = df_now_ns() - t0;
+      sh->stats.totalSwitchNs += dt;
+      if (dt > sh->stats.maxSwitchNs) sh->stats.maxSwitchNs = dt;
+    }
+    sh->stats.ctxLoads++;
+    sh->loadedColl = coll;
+    sh->dynDirty = 0;
+  }
+  df_sync();
+}
+
+DF_HD void saveLoaded(BlockShared* sh, RankDev* rd, int b) {
+  if (sh->loadedColl >= 0 && sh->dynDirty && df_tid() == 0) {
+    rd->dyn[(uint64_t)b * rd->maxColls + sh->loadedColl] = sh->dyn;
+    sh->stats.ctxSaves++;
+    sh->dynDirty = 0;
+  }
+}
+
+DF_HD void setPhase(BlockShared* sh, int phase) {
+  df_sync();                                   // everybody is done reading the old phase
+  if (df_tid() == 0) { sh->dyn.phase = phase; sh->dyn.cursor = 0; sh->dyn.stallSinceNs = 0; sh->dynDirty = 1; }
+  df_sync();
+}
+
+// ---- bounded waits (first warp polls, everybody learns the outcome)
+// which: 0 = arrive flags, 1 = done flags, 2 = local trigger word
+DF_HD bool boundedWait(BlockShared* sh, RankDev* rd, int b, int which, uint32_t budget) {
+  if (df_tid() < df_warpsize()) {
+    const int lane = df_lane(), ws = df_warpsize();
+    const int n = sh->cs.nranks, me = sh->cs.rank;
+    const uint64_t epoch = sh->dyn.epoch;
+    FlagSlot* mine = sh->cs.myFlags + (uint64_t)b * n;
+    uint32_t spins = 0;
+    bool ok;
+    for (;;) {
+      bool laneOk = true;
+      if (which == 2) {
+        if (lane == 0) laneOk = ld_acquire_sys_u64(&rd->trigger[sh->loadedColl]) >= sh->dyn.trigger;
+      } else {
+        for (int j = lane; j < n; j += ws) {
+          if (j == me) continue;
+          uint64_t v = ld_acquire_sys_u64(which == 0 ? &mine[j].arrive : &mine[j].done);
+          laneOk = laneOk && v >= epoch;
+        }
+      }
+      bool laneStop = false;
+      if ((spins & 15) == 15 && lane == 0) laneStop = rd->ctl->abortFlag != 0;
+      ok = df_warp_all(laneOk);
+      const bool stop = !df_warp_all(!laneStop);      // uniform: every lane leaves the loop together
+      ++spins;
+      if (ok || stop || spins >= budget) break;
+    }
+    if (lane == 0) { sh->waitOk = ok ? 1 : 0; sh->waitSpins = spins; sh->stats.waitPolls += spins; }
+  }
+  df_sync();
+  return sh->waitOk != 0;
+}
+
+// Called by all threads when a wait ran out.  Returns true if the collective must fail now.
+DF_HD bool noteStall(BlockShared* sh, RankDev* rd) {
+  if (df_tid() == 0) {
+    uint64_t now = df_now_ns();
+    sh->ctl0 = 0;
+    if (rd->ctl->abortFlag) { sh->dyn.status = ST_ABORTED; sh->ctl0 = 1; }
+    else if (sh->dyn.stallSinceNs == 0) { sh->dyn.stallSinceNs = now; sh->dynDirty = 1; }
+    else if (rd->waitTimeoutNs && now - sh->dyn.stallSinceNs > rd->waitTimeoutNs) {
+      sh->dyn.status = ST_TIMEOUT; sh->ctl0 = 1; sh->stats.waitTimeouts++;
+    }
+  }
+  df_sync();
+  return sh->ctl0 != 0;
+}
+
+DF_HD uint64_t mySendOff(const BlockShared* sh) {
+  return (sh->dyn.sqeFlags & SQE_SEND_STAGED) ? sh->cs.stagingSendOff : sh->dyn.send;
+}
+DF_HD uint64_t myRecvOff(const BlockShared* sh) {
+  return (sh->dyn.sqeFlags & SQE_RECV_STAGED) ? sh->cs.stagingRecvOff : sh->dyn.recv;
+}
+DF_HD const char* sendPtrOf(const BlockShared* sh, int b, int j) {
+  const CollStatic* c = &sh->cs;
+  uint64_t off = j == c->rank ? mySendOff(sh) : ld_relaxed_sys_u64(&c->myFlags[(uint64_t)b * c->nranks + j].sendOff);
+  return c->peerHeap[j] + off;
+}
+DF_HD char* recvPtrOf(const BlockShared* sh, int b, int j) {
+  const CollStatic* c = &sh->cs;
+  uint64_t off = j == c->rank ? myRecvOff(sh) : ld_relaxed_sys_u64(&c->myFlags[(uint64_t)b * c->nranks + j].recvOff);
+  return c->peerHeap[j] + off;
+}
+
+// ---- PH_DATA: thread 0 builds the pointer lists, everybody moves the data
+DF_HD void dataPhase(BlockShared* sh, RankDev* rd, int b) {
+  const CollStatic* c = &sh->cs;
+  const int n = c->nranks, me = c->rank;
+  const uint64_t es = dtypeSize(c->inType), eo = dtypeSize(c->outType);
+  bool reduce = true;
+  if (df_tid() == 0) {
+    DataArgs* a = &sh->args;
+    a->scale = c->scale; a->postDiv = c->postDiv; a->nsrc = 0; a->ndst = 0; a->n = 0;
+    uint64_t bb, be;
+    switch (c->kind) {
+      case dfcclCollAllReduce: {
+        partRange(c->count, c->nBlocks, b, 16, &bb, &be);
+        if (c->algo == dfcclAlgoOneShot || n == 1) {
+          for (int j = 0; j < n; ++j) a->src[a->nsrc++] = sendPtrOf(sh, b, j) + bb * es;
+          a->dst[a->ndst++] = recvPtrOf(sh, b, me) + bb * eo;
+          a->n = be - bb;
+        } else {
+          uint64_t sb, se;
+          partRange(be - bb, n, me, 16, &sb, &se);
+          sb += bb; se += bb;
+          for (int k = 0; k < n; ++k) { int j = (me + k) % n; a->src[a->nsrc++] = sendPtrOf(sh, b, j) + sb * es; }
+          for (int k = 0; k < n; ++k) { int j = (me + k) % n; a->dst[a->ndst++] = recvPtrOf(sh, b, j) + sb * eo; }
+          a->n = se - sb;
+        }
+        break;
+      }
+      case dfcclCollReduce: {
+        partRange(c->count, c->nBlocks, b, 16, &bb, &be);
+        uint64_t sb, se;
+        partRange(be - bb, n, me, 16, &sb, &se);
+        sb += bb; se += bb;
+        for (int k = 0; k < n; ++k) { int j = (me + k) % n; a->src[a->nsrc++] = sendPtrOf(sh, b, j) + sb * es; }
+        a->dst[a->ndst++] = recvPtrOf(sh, b, c->root) + sb * eo;
+        a->n = se - sb;
+        break;
+      }
+      case dfcclCollReduceScatter: {
+        partRange(c->count, c->nBlocks, b, 16, &bb, &be);
+        for (int k = 0; k < n; ++k) { int j = (me + k) % n; a->src[a->nsrc++] = sendPtrOf(sh, b, j) + ((uint64_t)me * c->count + bb) * es; }
+        a->dst[a->ndst++] = recvPtrOf(sh, b, me) + bb * eo;
+        a->n = be - bb;
+        break;
+      }
+      case dfcclCollAllGather: {
+        reduce = false;
+        uint64_t bytes = c->count * es;
+        partRange(bytes, c->nBlocks, b, 16, &bb, &be);
+        a->src[0] = sendPtrOf(sh, b, me) + bb; a->nsrc = 1;
+        for (int k = 0; k < n; ++k) {
+          int j = (me + k) % n;
+          char* d = recvPtrOf(sh, b, j) + (uint64_t)me * bytes + bb;
+          if (d != a->src[0]) a->dst[a->ndst++] = d;          // in-place: my own slot already holds it
+        }
+        a->n = be - bb;
+        break;
+      }
+      case dfcclCollBroadcast: {
+        reduce = false;
+        uint64_t bytes = c->count * es;
+        partRange(bytes, c->nBlocks, b, 16, &bb, &be);
+        a->src[0] = sendPtrOf(sh, b, c->root) + bb; a->nsrc = 1;
+        char* d = recvPtrOf(sh, b, me) + bb;
+        if (d != a->src[0]) a->dst[a->ndst++] = d;
+        a->n = be - bb;
+        break;
+      }
+      default: break;
+    }
+    sh->ctl1 = reduce ? 1 : 0;
+    if (reduce) sh->stats.bytesReduced += a->n * es * a->nsrc; else sh->stats.bytesCopied += a->n * (a->ndst ? a->ndst : 0);
+  }
+  df_sync();
+#if !DF_DEVICE_CODE
+  if (getenv("DFCCL_DEBUG_DATA")) fprintf(stderr, "[r%d b%d] kind %d algo %d op %d in %d nsrc %d ndst %d n %llu src0 %p src1 %p dst0 %p scale %f\n", me, b, c->kind, c->algo, c->op, c->inType,
+      sh->args.nsrc, sh->args.ndst, (unsigned long long)sh->args.n, sh->args.src[0], sh->args.src[1], sh->args.dst[0], sh->args.scale);
+#endif
+  if (sh->args.n != 0 && sh->args.ndst != 0) {
+    if (sh->ctl1) {
+      if (!reduce_dispatch(c->inType, c->outType, c->op, &sh->args) && df_tid() == 0) sh->dyn.status = ST_BAD_ARG;
+    } else {
+      copy_multi(&sh->args);
+    }
+  }
+  df_sync();
+}
+
+// ---- staging copies for buffers outside the symmetric heap
+DF_HD void stageCopy(BlockShared* sh, int b, bool in) {
+  const CollStatic* c = &sh->cs;
+  const int segs = (!in && c->kind == dfcclCollAllGather) ? c->nranks : 1;
+  const uint64_t total = (in ? sendBytes(c) : recvBytes(c)) / segs;
+  for (int s = 0; s < segs; ++s) {
+    if (df_tid() == 0) {
+      uint64_t bb, be;
+      partRange(total, c->nBlocks, b, 16, &bb, &be);
+      DataArgs* a = &sh->args;
+      a->nsrc = 1; a->ndst = 1; a->n = be - bb;
+      uint64_t off = (uint64_t)s * total + bb;
+      if (in) { a->src[0] = (const char*)sh->dyn.send + off; a->dst[0] = c->peerHeap[c->rank] + c->stagingSendOff + off; }
+      else { a->src[0] = c->peerHeap[c->rank] + c->stagingRecvOff + off; a->dst[0] = (char*)sh->dyn.recv + off; }
+      sh->stats.bytesCopied += a->n;
+    }
+    df_sync();
+    if (sh->args.n) copy_multi(&sh->args);
+    df_sync();
+  }
+}
+
+// ---- completion: count blocks; the last one publishes the device flag and the CQE
+DF_HD void completeColl(BlockShared* sh, RankDev* rd, int b) {
+  if (sh->standalone) {                           // stream-ordered kernel: report errors only
+    if (df_tid() == 0 && sh->dyn.status != ST_OK) rd->ctl->pad = sh->dyn.status;
+    df_sync();
+    return;
+  }
+  if (df_tid() == 0) {
+    const int coll = sh->loadedColl;
+    uint32_t status = sh->dyn.status;
+    sh->dyn.phase = PH_COMPLETE;
+    rd->dyn[(uint64_t)b * rd->maxColls + coll] = sh->dyn;
+    sh->dynDirty = 0;
+    sh->stats.collsDone++;
+    if (status != ST_OK) atomic_add_u32(&rd->failCount[coll], status << 16 | 1u);
+    fence_gpu();
+    uint32_t prev = atomic_add_u32(&rd->doneCount[coll], 1u);
+    if (prev + 1 == (uint32_t)sh->cs.nBlocks) {
+      uint32_t fails = atomic_exch_u32(&rd->failCount[coll], 0u);
+      atomic_exch_u32(&rd->doneCount[coll], 0u);
+      uint32_t st = fails ? (fails >> 16) / (fails & 0xffff) : ST_OK;   // all failing blocks report the same cause
+      if (st > 255) st = ST_TIMEOUT;
+      fence_sys();
+      st_release_sys_u64(&rd->doneEpoch[coll], ((uint64_t)st << 56) | sh->dyn.epoch);
+      unsigned long long idx = atomic_add_u64((unsigned long long*)&rd->devCqTail, 1ull);
+      uint32_t gen = (uint32_t)(idx / rd->cqCap) + 1u;
+      st_release_sys_u64(&rd->hostCq[idx & (rd->cqCap - 1)], cqeEncode(gen, st, (uint32_t)coll));
+    }
+    trace(rd, b, TR_DONE, coll);
+  }
+  df_sync();
+}
+
+// Run the loaded-or-to-be-loaded collective until it completes or a wait runs out.
+// `budget` is the number of polls one wait may spend.
+// `*moved` is set when at least one phase was left behind during this visit.
+DF_HD int runColl(BlockShared* sh, RankDev* rd, int b, int coll, uint32_t budget, bool* moved) {
+  if (!sh->standalone) loadColl(sh, rd, b, coll);
+  const int n = sh->cs.nranks, me = sh->cs.rank;
+  const int tid = df_tid(), nt = df_nthreads();
+  const int entryPhase = sh->dyn.phase;
+  for (;;) {
+    const int phase = sh->dyn.phase;
+    if (phase != entryPhase) *moved = true;
+    switch (phase) {
+      case PH_TRIGGER:
+        if (sh->dyn.sqeFlags & SQE_TRIGGERED) {
+          if (!boundedWait(sh, rd, b, 2, budget)) { if (noteStall(sh, rd)) { setPhase(sh, PH_COMPLETE); break; } return RC_STALLED; }
+        }
+        setPhase(sh, PH_COPY_IN);
+        break;
+      case PH_COPY_IN:
+        if (sh->dyn.sqeFlags & SQE_SEND_STAGED) {
+          bool needed = !(sh->cs.kind == dfcclCollBroadcast && me != sh->cs.root);
+          if (needed) stageCopy(sh, b, true);
+          if (tid == 0) fence_sys();
+        }
+        setPhase(sh, PH_POST_ARRIVE);
+        break;
+      case PH_POST_ARRIVE: {
+        const uint64_t so = mySendOff(sh), ro = myRecvOff(sh), epoch = sh->dyn.epoch;
+        for (int j = tid; j < n; j += nt) {
+          if (j == me) continue;
+          FlagSlot* s = sh->cs.peerFlags[j] + (uint64_t)b * n + me;
+          st_relaxed_sys_u64(&s->sendOff, so);
+          st_relaxed_sys_u64(&s->recvOff, ro);
+          st_release_sys_u64(&s->arrive, epoch);
+        }
+        setPhase(sh, PH_WAIT_ARRIVE);
+        break;
+      }
+      case PH_WAIT_ARRIVE:
+        if (n > 1 && !boundedWait(sh, rd, b, 0, budget)) { if (noteStall(sh, rd)) { setPhase(sh, PH_COMPLETE); break; } return RC_STALLED; }
+        setPhase(sh, PH_DATA);
+        break;
+      case PH_DATA:
+        if (tid == 0) trace(rd, b, TR_DATA_BEGIN, coll);
+        dataPhase(sh, rd, b);
+        if (tid == 0) trace(rd, b, TR_DATA_END, coll);
+        setPhase(sh, PH_POST_DONE);
+        break;
+      case PH_POST_DONE: {
+        // all payload stores of this block were issued before the barrier inside setPhase;
+        // the fence makes them visible system-wide before any done flag is
+        if (tid == 0) fence_sys();
+        df_sync();
+        const uint64_t epoch = sh->dyn.epoch;
+        for (int j = tid; j < n; j += nt) {
+          if (j == me) continue;
+          fence_sys();
+          st_release_sys_u64(&(sh->cs.peerFlags[j] + (uint64_t)b * n + me)->done, epoch);
+        }
+        setPhase(sh, PH_WAIT_DONE);
+        break;
+      }
+      case PH_WAIT_DONE:
+        if (n > 1 && !boundedWait(sh, rd, b, 1, budget)) { if (noteStall(sh, rd)) { setPhase(sh, PH_COMPLETE); break; } return RC_STALLED; }
+        setPhase(sh, PH_COPY_OUT);
+        break;
+      case PH_COPY_OUT:
+        if (sh->dyn.sqeFlags & SQE_RECV_STAGED) {
+          bool needed = !(sh->cs.kind == dfcclCollReduce && me != sh->cs.root);
+          if (needed) stageCopy(sh, b, false);
+        }
+        setPhase(sh, PH_COMPLETE);
+        break;
+      default:  // PH_COMPLETE
+        completeColl(sh, rd, b);
+        return RC_DONE;
+    }
+  }
+}
+
+}  // namespace dfccl

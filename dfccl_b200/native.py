@@ -1,0 +1,282 @@
+"""ctypes binding of ``libdfccl.so`` (the C interface declared in
+``csrc/include/dfccl.h``) plus small Python conveniences.
+
+The library is built in-tree on first use if it is missing (``_build.build``).
+On a machine with a GPU the CUDA backend is the default and a missing or
+unloadable library is an error, never a silent fallback to Python code.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+import threading
+from typing import Callable, Dict, List, Optional, Sequence
+
+from . import _build
+
+# ---- enums (values of dfccl.h)
+SUCCESS, UNHANDLED_CUDA, SYSTEM_ERROR, INTERNAL_ERROR, INVALID_ARGUMENT, INVALID_USAGE, TIMEOUT, ABORTED = range(8)
+SUM, PROD, MAX, MIN, AVG = range(5)
+INT8, UINT8, INT32, UINT32, INT64, UINT64, FLOAT16, FLOAT32, FLOAT64, BFLOAT16 = range(10)
+ALLREDUCE, ALLGATHER, REDUCESCATTER, BROADCAST, REDUCE = range(5)
+ALGO_AUTO, ALGO_ONESHOT, ALGO_TWOSHOT, ALGO_NVLS = range(4)
+BACKEND_CUDA, BACKEND_HOST = 0, 1
+FAULT_NONE, FAULT_DROP_SQE, FAULT_DELAY_SQE_US, FAULT_FREEZE_POLLER = range(4)
+
+DTYPE_SIZE = {INT8: 1, UINT8: 1, INT32: 4, UINT32: 4, INT64: 8, UINT64: 8, FLOAT16: 2, FLOAT32: 4, FLOAT64: 8, BFLOAT16: 2}
+
+CALLBACK = C.CFUNCTYPE(C.c_int, C.c_int, C.c_void_p)
+
+
+class UniqueId(C.Structure):
+    _fields_ = [("internal", C.c_char * 128)]
+
+
+class CollInfo(C.Structure):
+    _fields_ = [("kind", C.c_int), ("count", C.c_size_t), ("inType", C.c_int), ("outType", C.c_int),
+                ("op", C.c_int), ("root", C.c_int), ("scale", C.c_float), ("algo", C.c_int), ("nBlocks", C.c_int)]
+
+
+class Stats(C.Structure):
+    _fields_ = [(n, C.c_uint64) for n in (
+        "sqesSubmitted", "cqesDelivered", "callbacksRun", "daemonLaunches", "daemonVoluntaryQuits",
+        "ctxSwitches", "ctxSaves", "ctxLoads", "waitPolls", "waitTimeouts", "bytesReduced", "bytesCopied",
+        "sqFullRetries", "maxSwitchNs", "totalSwitchNs", "deviceEvents")]
+
+    def as_dict(self) -> Dict[str, int]:
+        return {n: int(getattr(self, n)) for n, _ in self._fields_}
+
+
+class DfcclError(RuntimeError):
+    def __init__(self, code: int, what: str):
+        self.code = code
+        super().__init__(f"{what}: {error_string(code)} ({code})")
+
+
+_lib = None
+_lock = threading.Lock()
+
+
+def lib() -> C.CDLL:
+    """Load (building first if necessary) and return the native library."""
+    global _lib
+    with _lock:
+        if _lib is not None:
+            return _lib
+        path = _build.LIB
+        if not path.exists() or os.environ.get("DFCCL_REBUILD") == "1":
+            path = _build.build()
+        L = C.CDLL(str(path), mode=C.RTLD_GLOBAL)
+        vp, i, sz = C.c_void_p, C.c_int, C.c_size_t
+        sig = {
+            "ncclGetVersion": [C.POINTER(i)],
+            "ncclGetUniqueId": [C.POINTER(UniqueId)],
+            "ncclCommInitRank": [C.POINTER(vp), i, UniqueId, i],
+            "ncclCommInitAll": [C.POINTER(vp), i, C.POINTER(i)],
+            "dfcclCommInitLoopback": [C.POINTER(vp), i, i],
+            "dfcclCommSplit": [vp, i, i, C.POINTER(vp)],
+            "ncclCommDestroy": [vp], "ncclCommAbort": [vp],
+            "ncclCommGetAsyncError": [vp, C.POINTER(i)],
+            "ncclCommCount": [vp, C.POINTER(i)], "ncclCommCuDevice": [vp, C.POINTER(i)], "ncclCommUserRank": [vp, C.POINTER(i)],
+            "ncclRedOpCreatePreMulSum": [C.POINTER(i), vp, i, i, vp], "ncclRedOpDestroy": [i, vp],
+            "ncclAllReduce": [vp, vp, sz, i, i, vp, vp],
+            "ncclReduce": [vp, vp, sz, i, i, i, vp, vp],
+            "ncclBroadcast": [vp, vp, sz, i, i, vp, vp],
+            "ncclBcast": [vp, sz, i, i, vp, vp],
+            "ncclReduceScatter": [vp, vp, sz, i, i, vp, vp],
+            "ncclAllGather": [vp, vp, sz, i, vp, vp],
+            "ncclSend": [vp, sz, i, i, vp, vp], "ncclRecv": [vp, sz, i, i, vp, vp],
+            "ncclGroupStart": [], "ncclGroupEnd": [],
+            "dfcclSetBackend": [i], "dfcclGetBackend": [C.POINTER(i)],
+            "dfcclMemAlloc": [C.POINTER(vp), sz, vp], "dfcclMemFree": [vp, vp],
+            "dfcclHeapInfo": [vp, C.POINTER(vp), C.POINTER(sz), C.POINTER(sz)],
+            "ofcclInitRankCtx": [C.POINTER(vp), i], "dfcclInitRankCtxOnDevice": [C.POINTER(vp), i, i],
+            "ofcclFinalizeRankCtx7StartHostThrds": [vp], "ofcclPrepareDone": [vp], "ofcclDestroy": [vp],
+            "dfcclPrepare": [C.POINTER(CollInfo), vp, i, vp],
+            "ofcclPrepareAllReduce": [sz, i, i, vp, i, vp], "ofcclPrepareReduce": [sz, i, i, i, vp, i, vp],
+            "ofcclPrepareReduceScatter": [sz, i, i, vp, i, vp], "ofcclPrepareAllGather": [sz, i, vp, i, vp],
+            "ofcclPrepareBroadcast": [sz, i, i, vp, i, vp], "ofcclPrepareBcast": [sz, i, i, vp, i, vp],
+            "ofcclRunAllReduce": [vp, vp, i, CALLBACK, vp, vp], "ofcclRunReduce": [vp, vp, i, CALLBACK, vp, vp],
+            "ofcclRunReduceScatter": [vp, vp, i, CALLBACK, vp, vp], "ofcclRunAllGather": [vp, vp, i, CALLBACK, vp, vp],
+            "ofcclRunBroadcast": [vp, vp, i, CALLBACK, vp, vp], "ofcclRunBcast": [vp, i, CALLBACK, vp, vp],
+            "dfcclRun": [vp, vp, i, CALLBACK, vp, vp],
+            "dfcclRunOnStream": [vp, vp, i, vp, CALLBACK, vp, vp],
+            "dfcclStreamWait": [i, vp, vp], "dfcclWait": [i, i, vp], "dfcclWaitAll": [i, vp],
+            "dfcclAbort": [vp], "dfcclGetAsyncError": [vp, C.POINTER(i)],
+            "dfcclGetStats": [vp, C.POINTER(Stats)], "dfcclTraceDump": [vp, C.c_char_p],
+            "dfcclInjectFault": [vp, i, C.c_int64],
+        }
+        for name, args in sig.items():
+            f = getattr(L, name)
+            f.argtypes = args
+            f.restype = i
+        L.ncclGetErrorString.argtypes = [i]
+        L.ncclGetErrorString.restype = C.c_char_p
+        _lib = L
+        return L
+
+
+def error_string(code: int) -> str:
+    return lib().ncclGetErrorString(code).decode()
+
+
+def check(code: int, what: str = "dfccl call") -> None:
+    if code != SUCCESS:
+        raise DfcclError(code, what)
+
+
+def set_backend(name: str) -> None:
+    check(lib().dfcclSetBackend(BACKEND_HOST if name in ("host", "cpu") else BACKEND_CUDA), "dfcclSetBackend")
+
+
+def get_backend() -> str:
+    b = C.c_int()
+    check(lib().dfcclGetBackend(C.byref(b)))
+    return "host" if b.value == BACKEND_HOST else "cuda"
+
+
+def get_unique_id() -> bytes:
+    uid = UniqueId()
+    check(lib().ncclGetUniqueId(C.byref(uid)), "ncclGetUniqueId")
+    return bytes(uid.internal)
+
+
+class Comm:
+    """Owning wrapper of an ``ncclComm_t``."""
+
+    def __init__(self, handle: int):
+        self.handle = C.c_void_p(handle)
+        self._live = True
+
+    @staticmethod
+    def init_rank(nranks: int, uid: bytes, rank: int) -> "Comm":
+        u = UniqueId()
+        C.memmove(u.internal, uid, 128)
+        h = C.c_void_p()
+        check(lib().ncclCommInitRank(C.byref(h), nranks, u, rank), "ncclCommInitRank")
+        return Comm(h.value)
+
+    @staticmethod
+    def init_all(ndev: int, devices: Optional[Sequence[int]] = None) -> List["Comm"]:
+        arr = (C.c_void_p * ndev)()
+        devs = (C.c_int * ndev)(*devices) if devices is not None else None
+        check(lib().ncclCommInitAll(arr, ndev, devs), "ncclCommInitAll")
+        return [Comm(arr[k]) for k in range(ndev)]
+
+    @staticmethod
+    def init_loopback(nranks: int, device: int = 0) -> List["Comm"]:
+        arr = (C.c_void_p * nranks)()
+        check(lib().dfcclCommInitLoopback(arr, nranks, device), "dfcclCommInitLoopback")
+        return [Comm(arr[k]) for k in range(nranks)]
+
+    def split(self, color: int, key: int) -> Optional["Comm"]:
+        h = C.c_void_p()
+        check(lib().dfcclCommSplit(self.handle, color, key, C.byref(h)), "dfcclCommSplit")
+        return Comm(h.value) if h.value else None
+
+    @property
+    def rank(self) -> int:
+        v = C.c_int()
+        check(lib().ncclCommUserRank(self.handle, C.byref(v)))
+        return v.value
+
+    @property
+    def nranks(self) -> int:
+        v = C.c_int()
+        check(lib().ncclCommCount(self.handle, C.byref(v)))
+        return v.value
+
+    @property
+    def device(self) -> int:
+        v = C.c_int()
+        check(lib().ncclCommCuDevice(self.handle, C.byref(v)))
+        return v.value
+
+    def alloc(self, nbytes: int) -> int:
+        p = C.c_void_p()
+        check(lib().dfcclMemAlloc(C.byref(p), nbytes, self.handle), "dfcclMemAlloc")
+        return p.value
+
+    def free(self, ptr: int) -> None:
+        check(lib().dfcclMemFree(C.c_void_p(ptr), self.handle), "dfcclMemFree")
+
+    def heap_info(self):
+        base, nbytes, used = C.c_void_p(), C.c_size_t(), C.c_size_t()
+        check(lib().dfcclHeapInfo(self.handle, C.byref(base), C.byref(nbytes), C.byref(used)))
+        return base.value, nbytes.value, used.value
+
+    def async_error(self) -> int:
+        v = C.c_int()
+        check(lib().ncclCommGetAsyncError(self.handle, C.byref(v)))
+        return v.value
+
+    def destroy(self) -> None:
+        if self._live:
+            self._live = False
+            check(lib().ncclCommDestroy(self.handle), "ncclCommDestroy")
+
+
+class RankCtx:
+    """Owning wrapper of an ``ofcclRankCtx_t`` (register, finalize, submit, destroy)."""
+
+    def __init__(self, rank: int, device: int = -1):
+        h = C.c_void_p()
+        check(lib().dfcclInitRankCtxOnDevice(C.byref(h), rank, device), "ofcclInitRankCtx")
+        self.handle = h
+        self._callbacks: Dict[int, object] = {}
+        self._live = True
+
+    def prepare(self, coll_id: int, comm: Comm, kind: int, count: int, dtype: int, *, out_dtype: Optional[int] = None,
+                op: int = SUM, root: int = 0, scale: float = 1.0, algo: int = ALGO_AUTO, n_blocks: int = 0) -> None:
+        info = CollInfo(kind, count, dtype, dtype if out_dtype is None else out_dtype, op, root, scale, algo, n_blocks)
+        check(lib().dfcclPrepare(C.byref(info), comm.handle, coll_id, self.handle), f"dfcclPrepare({coll_id})")
+
+    def finalize(self) -> None:
+        check(lib().ofcclFinalizeRankCtx7StartHostThrds(self.handle), "ofcclFinalizeRankCtx7StartHostThrds")
+
+    def run(self, coll_id: int, send: int, recv: int, callback: Optional[Callable[[int], None]] = None) -> None:
+        cb = CALLBACK(0)
+        if callback is not None:
+            def tramp(cid, _args, _f=callback):
+                _f(cid)
+                return 0
+            cb = CALLBACK(tramp)
+            self._callbacks[coll_id] = cb          # keep the trampoline alive until the next submit of this id
+        check(lib().dfcclRun(C.c_void_p(send), C.c_void_p(recv), coll_id, cb, None, self.handle), f"dfcclRun({coll_id})")
+
+    def run_on_stream(self, coll_id: int, send: int, recv: int, stream: int) -> None:
+        check(lib().dfcclRunOnStream(C.c_void_p(send), C.c_void_p(recv), coll_id, C.c_void_p(stream), CALLBACK(0), None,
+                                     self.handle), f"dfcclRunOnStream({coll_id})")
+
+    def stream_wait(self, coll_id: int, stream: int) -> None:
+        check(lib().dfcclStreamWait(coll_id, C.c_void_p(stream), self.handle), f"dfcclStreamWait({coll_id})")
+
+    def wait(self, coll_id: int, timeout_ms: int = -1) -> int:
+        return lib().dfcclWait(coll_id, timeout_ms, self.handle)
+
+    def wait_all(self, timeout_ms: int = -1) -> int:
+        return lib().dfcclWaitAll(timeout_ms, self.handle)
+
+    def abort(self) -> None:
+        check(lib().dfcclAbort(self.handle))
+
+    def async_error(self) -> int:
+        v = C.c_int()
+        check(lib().dfcclGetAsyncError(self.handle, C.byref(v)))
+        return v.value
+
+    def stats(self) -> Dict[str, int]:
+        s = Stats()
+        check(lib().dfcclGetStats(self.handle, C.byref(s)), "dfcclGetStats")
+        return s.as_dict()
+
+    def trace_dump(self, path: str) -> None:
+        check(lib().dfcclTraceDump(self.handle, path.encode()), "dfcclTraceDump")
+
+    def inject_fault(self, fault: int, arg: int) -> None:
+        check(lib().dfcclInjectFault(self.handle, fault, arg))
+
+    def destroy(self) -> None:
+        if self._live:
+            self._live = False
+            check(lib().ofcclDestroy(self.handle), "ofcclDestroy")
