@@ -28,7 +28,7 @@ SOURCES = [
     "src/mem/heap.cu", "src/topo/topo.cu",
     "src/daemon/daemon.cu", "src/daemon/standalone.cu", "src/daemon/daemon_host.cu",
     "src/comm/comm.cu",
-    "src/api/nccl_api.cu", "src/api/p2p.cu", "src/api/ofccl_api.cu",
+    "src/api/nccl_api.cu", "src/api/p2p.cu", "src/api/ofccl_api.cu", "src/api/debug_api.cu",
 ]
 
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]

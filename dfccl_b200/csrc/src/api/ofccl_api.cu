@@ -59,6 +59,8 @@ static void observerMain(DaemonLauncher* L) {
     if (L->stop) break;
     L->wake = false;
     std::vector<ofcclRankCtx*> members = L->members;
+    std::vector<ofcclRankCtx*> everyone = L->members;       // the launch table also names retired ranks
+    everyone.insert(everyone.end(), L->retired.begin(), L->retired.end());
     lk.unlock();
     // the previous instance must be completely gone: its blocks park state the next one restores
     if (L->backend == dfcclBackendCuda) {
@@ -72,19 +74,19 @@ static void observerMain(DaemonLauncher* L) {
     }
     bool work = false, dead = false;
     for (auto* m : members) {
-      if (m->remaining.load() > 0) work = true;
-      if (m->ctl->finalQuit || m->ctl->abortFlag) dead = true;
+      if (m->remaining.load() > 0 && !m->ctl->finalQuit) work = true;
+      if (m->ctl->abortFlag) dead = true;
     }
     if (work && !dead) {
-      for (auto* m : members) { m->ctl->alive = 1; m->ctl->launches = m->ctl->launches + 1; }
+      for (auto* m : everyone) { m->ctl->alive = 1; m->ctl->launches = m->ctl->launches + 1; }
       std::atomic_thread_fence(std::memory_order_seq_cst);
       ++L->launches;
       DF_TRACE(SUB_DAEMON, "daemon launch #%llu (%zu ranks x %d blocks x %d threads)", (unsigned long long)L->launches, members.size(), L->blocks, L->threads);
       if (L->backend == dfcclBackendCuda) {
-        ncclResult_t r = launchDaemonCuda(L->devTable, (int)members.size(), L->blocks, L->threads, L->stream);
+        ncclResult_t r = launchDaemonCuda(L->devTable, L->expected, L->blocks, L->threads, L->stream);
         if (r != ncclSuccess) for (auto* m : members) m->asyncError = r;
       } else {
-        runDaemonHost(L->devTable, (int)members.size(), L->blocks);     // returns when every block has left
+        runDaemonHost(L->devTable, L->expected, L->blocks);     // returns when every block has left
         for (auto* m : members) if (m->remaining.load() > 0 && !m->ctl->finalQuit && !m->ctl->abortFlag) { lk.lock(); L->wake = true; lk.unlock(); break; }
       }
     }
@@ -556,61 +558,64 @@ DF_API ncclResult_t dfcclInjectFault(ofcclRankCtx_t ctx, dfcclFault_t fault, int
   return ncclSuccess;
 }
 
+static void releaseCtx(ofcclRankCtx* ctx) {
+  const dfcclBackend_t be = ctx->backend;
+  for (auto& kv : ctx->colls) {
+    CollEntry& e = kv.second;
+    e.comm->heap->free(e.flagsOff);
+    for (int k = 0; k < 2; ++k) if (e.stagingBytes[k]) e.comm->heap->free(e.stagingOff[k]);
+  }
+  RankDev& rd = ctx->rdHost;
+  devFree(be, rd.devSq); devFree(be, rd.colls); devFree(be, rd.dyn); devFree(be, rd.doneCount); devFree(be, rd.failCount);
+  devFree(be, (void*)rd.doneEpoch); devFree(be, (void*)rd.trigger); devFree(be, rd.saved); devFree(be, rd.stats); devFree(be, rd.trace);
+  devFree(be, ctx->rdDev);
+  pinnedFree(be, ctx->hostSq); pinnedFree(be, (void*)ctx->hostSqTail); pinnedFree(be, (void*)ctx->hostSqHead);
+  pinnedFree(be, (void*)ctx->hostCq); pinnedFree(be, ctx->ctl);
+  delete ctx;
+}
+
 DF_API ncclResult_t ofcclDestroy(ofcclRankCtx_t ctx) {
   if (!ctx) return ncclSuccess;
+  if (!ctx->finalized) { delete ctx; return ncclSuccess; }
   const dfcclBackend_t be = ctx->backend;
-  if (ctx->finalized) {
-    int prev = 0;
-    if (be == dfcclBackendCuda) { cudaGetDevice(&prev); cudaSetDevice(ctx->device); }
-    ctx->destroyed = true;
-    // quit entry: a running daemon leaves for good; a parked one is simply never launched again
-    {
-      std::lock_guard<std::mutex> l(ctx->mu);
-      Sqe q;
-      memset(&q, 0, sizeof(q));
-      q.collId = -1; q.flags = SQE_QUIT;
-      uint64_t tail = *ctx->hostSqTail;
-      ctx->hostSq[tail & (ctx->sqCap - 1)] = q;
-      __atomic_store_n((uint64_t*)ctx->hostSqTail, tail + 1, __ATOMIC_RELEASE);
-    }
-    ctx->stopPoller = true;
-    ctx->pollCv.notify_all();
-    if (ctx->poller.joinable()) ctx->poller.join();
-    // the launcher goes with its last member
-    std::shared_ptr<DaemonLauncher> L = ctx->launcher;
-    ctx->launcher.reset();
-    bool last = false;
-    {
-      std::lock_guard<std::mutex> l(L->mu);
-      // a shared daemon keeps running for the other ranks; mine must be out before my tables go
-      L->members.erase(std::remove(L->members.begin(), L->members.end(), ctx), L->members.end());
-      last = L->members.empty();
-      if (!last) L->stop = true;     // the table of a shared daemon names my freed state: no further launches
-    }
-    if (be == dfcclBackendCuda) {
-      if (L->stream) cudaStreamSynchronize(L->stream);
-    } else {
-      // host backend: the daemon runs inside the observer thread; wait until my blocks have parked
-      for (int i = 0; i < 20000 && ctx->ctl->alive; ++i) std::this_thread::sleep_for(std::chrono::microseconds(100));
-    }
-    if (last) {
-      if (ctx->colls.begin()->second.comm->loop) { auto loop = ctx->colls.begin()->second.comm->loop; std::lock_guard<std::mutex> l(loop->mu); if (loop->launcher == L) loop->launcher.reset(); }
-      L.reset();
-    }
-    for (auto& kv : ctx->colls) {
-      CollEntry& e = kv.second;
-      e.comm->heap->free(e.flagsOff);
-      for (int k = 0; k < 2; ++k) if (e.stagingBytes[k]) e.comm->heap->free(e.stagingOff[k]);
-    }
-    RankDev& rd = ctx->rdHost;
-    devFree(be, rd.devSq); devFree(be, rd.colls); devFree(be, rd.dyn); devFree(be, rd.doneCount); devFree(be, rd.failCount);
-    devFree(be, (void*)rd.doneEpoch); devFree(be, (void*)rd.trigger); devFree(be, rd.saved); devFree(be, rd.stats); devFree(be, rd.trace);
-    devFree(be, ctx->rdDev);
-    pinnedFree(be, ctx->hostSq); pinnedFree(be, (void*)ctx->hostSqTail); pinnedFree(be, (void*)ctx->hostSqHead);
-    pinnedFree(be, (void*)ctx->hostCq); pinnedFree(be, ctx->ctl);
-    if (be == dfcclBackendCuda) cudaSetDevice(prev);
+  int prev = 0;
+  if (be == dfcclBackendCuda) { cudaGetDevice(&prev); cudaSetDevice(ctx->device); }
+  ctx->destroyed = true;
+  // quit entry: a running daemon's blocks of this rank leave for good; a parked daemon is not launched for it again
+  {
+    std::lock_guard<std::mutex> l(ctx->mu);
+    Sqe q;
+    memset(&q, 0, sizeof(q));
+    q.collId = -1; q.flags = SQE_QUIT;
+    uint64_t tail = *ctx->hostSqTail;
+    ctx->hostSq[tail & (ctx->sqCap - 1)] = q;
+    __atomic_store_n((uint64_t*)ctx->hostSqTail, tail + 1, __ATOMIC_RELEASE);
   }
-  delete ctx;
+  ctx->stopPoller = true;
+  ctx->pollCv.notify_all();
+  if (ctx->poller.joinable()) ctx->poller.join();
+  std::shared_ptr<DaemonLauncher> L = ctx->launcher;
+  ctx->launcher.reset();
+  bool last = false;
+  {
+    std::lock_guard<std::mutex> l(L->mu);
+    L->members.erase(std::remove(L->members.begin(), L->members.end(), ctx), L->members.end());
+    last = L->members.empty();
+    // A shared daemon keeps serving the other ranks and its launch table still names this
+    // rank's device state, so that state lives on (its blocks leave at once on the quit entry)
+    // until the last rank of the group is destroyed.
+    if (!last) L->retired.push_back(ctx);
+  }
+  if (last) {
+    std::shared_ptr<LoopGroup> loop = ctx->colls.begin()->second.comm->loop;
+    if (loop) { std::lock_guard<std::mutex> l(loop->mu); if (loop->launcher == L) loop->launcher.reset(); }
+    std::vector<ofcclRankCtx*> retired;
+    retired.swap(L->retired);
+    L.reset();                      // joins the observer, drains the stream, frees the launch table
+    for (auto* z : retired) releaseCtx(z);
+    releaseCtx(ctx);
+  }
+  if (be == dfcclBackendCuda) cudaSetDevice(prev);
   return ncclSuccess;
 }
 

@@ -43,6 +43,7 @@ struct DaemonLauncher {
   int expected = 1;                          // rank contexts that must attach before the first launch
   int blocks = 1, threads = 1;
   std::vector<ofcclRankCtx*> members;
+  std::vector<ofcclRankCtx*> retired;        // destroyed members of a shared daemon, released with the launcher
   RankDev** devTable = nullptr;              // device array of RankDev* (host array on the host backend)
   cudaStream_t stream = nullptr;
   std::thread observer;
