@@ -297,6 +297,7 @@ DF_API ncclResult_t ofcclFinalizeRankCtx7StartHostThrds(ofcclRankCtx_t ctx) {
   rd.idleQuitNs = (uint64_t)paramI64("IDLE_QUIT_US", tolerant ? tolerant : 200) * 1000ull;
   rd.stallQuitNs = (uint64_t)paramI64("STALL_QUIT_US", tolerant ? tolerant : 5000) * 1000ull;
   rd.waitTimeoutNs = (uint64_t)paramI64("WAIT_TIMEOUT_MS", 0) * 1000000ull;
+  rd.maxLifetimeNs = (uint64_t)paramI64("MAX_LIFETIME_MS", 2000) * 1000000ull;
   rd.sliceBytes = (uint64_t)paramI64("SLICE_BYTES", 0);
   std::vector<CollStatic> table(maxColls);
   memset(table.data(), 0, sizeof(CollStatic) * maxColls);

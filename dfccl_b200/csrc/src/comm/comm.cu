@@ -127,7 +127,10 @@ ncclResult_t commCreate(std::shared_ptr<Bootstrap> boot, dfcclBackend_t backend,
   memset(&rd, 0, sizeof(rd));
   rd.ctl = c->ctl; rd.nBlocks = DF_MAX_BLOCKS; rd.maxColls = 1;
   rd.spinBudget = 4096; rd.headTries = 1;
-  rd.waitTimeoutNs = (uint64_t)paramI64("WAIT_TIMEOUT_MS", 30000) * 1000000ull;
+  // stream-ordered kernels cannot be preempted, so their waits always carry a limit
+  int64_t toMs = paramI64("WAIT_TIMEOUT_MS", 30000);
+  if (toMs <= 0) toMs = 30000;
+  rd.waitTimeoutNs = (uint64_t)toMs * 1000000ull;
   DFCHECK(devAlloc(backend, (void**)&rd.dyn, sizeof(CollDyn) * DF_MAX_BLOCKS));
   DFCHECK(devAlloc(backend, (void**)&c->saRd, sizeof(RankDev)));
   DFCHECK(devUpload(backend, c->saRd, &rd, sizeof(RankDev)));

@@ -135,6 +135,7 @@ DF_HD void daemonBlockMain(RankDev* rd, int b, BlockShared* sh) {
   blockRestore(sh, rd, b);
   if (tid == 0) trace(rd, b, TR_LAUNCH, 0);
   uint64_t lastUseful = df_now_ns();     // only thread 0's copy is ever consulted
+  const uint64_t bornNs = lastUseful;
   uint32_t idleBackoff = 32;
 
   for (;;) {
@@ -169,6 +170,11 @@ DF_HD void daemonBlockMain(RankDev* rd, int b, BlockShared* sh) {
       }
       const uint64_t now = df_now_ns();
       if (rd->ctl->abortFlag) sh->quit = 3;
+      else if (rd->maxLifetimeNs && now - bornNs > rd->maxLifetimeNs && !sh->quit) {
+        // safety net: no instance of the daemon outlives this, whatever its state; the host relaunches it
+        sh->quit = 1;
+        st_release_sys_u32(&rd->quitting, 1u);
+      }
       else if (progressed) lastUseful = now;
       else if (!sh->quit && (winding || now - lastUseful > (sh->nActive ? rd->stallQuitNs : rd->idleQuitNs))) {
         sh->quit = 1;
