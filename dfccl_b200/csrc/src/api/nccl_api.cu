@@ -96,7 +96,7 @@ DF_API ncclResult_t dfcclCommSplit(ncclComm_t comm, int color, int key, ncclComm
   int tagBase = (int)(((comm->splitCount++ & 0x3f) + 1) << 24) | ((color & 0x3f) << 18);
   std::unique_ptr<Bootstrap> sub;
   DFCHECK(bootstrapCreateSub(comm->boot, members, tagBase, &sub));
-  return commCreate(std::shared_ptr<Bootstrap>(std::move(sub)), comm->backend, comm->device, comm->ownsHeap ? false : false, comm->loop, newcomm);
+  return commCreate(std::shared_ptr<Bootstrap>(std::move(sub)), comm->backend, comm->device, false, comm->loop, newcomm, comm->heap);
 }
 
 DF_API ncclResult_t ncclCommDestroy(ncclComm_t comm) { return commDestroy(comm); }

@@ -559,13 +559,20 @@ DF_API ncclResult_t dfcclInjectFault(ofcclRankCtx_t ctx, dfcclFault_t fault, int
   return ncclSuccess;
 }
 
-static void releaseCtx(ofcclRankCtx* ctx) {
-  const dfcclBackend_t be = ctx->backend;
+// Heap pieces go back at destroy time (the communicators they came from may be destroyed right
+// after); nobody writes them any more: this rank completed every submission, which needed every
+// peer's last flag.
+static void releaseHeapParts(ofcclRankCtx* ctx) {
   for (auto& kv : ctx->colls) {
     CollEntry& e = kv.second;
     e.comm->heap->free(e.flagsOff);
     for (int k = 0; k < 2; ++k) if (e.stagingBytes[k]) e.comm->heap->free(e.stagingOff[k]);
+    e.comm = nullptr;
   }
+}
+
+static void releaseCtx(ofcclRankCtx* ctx) {
+  const dfcclBackend_t be = ctx->backend;
   RankDev& rd = ctx->rdHost;
   devFree(be, rd.devSq); devFree(be, rd.colls); devFree(be, rd.dyn); devFree(be, rd.doneCount); devFree(be, rd.failCount);
   devFree(be, (void*)rd.doneEpoch); devFree(be, (void*)rd.trigger); devFree(be, rd.saved); devFree(be, rd.stats); devFree(be, rd.trace);
@@ -597,6 +604,10 @@ DF_API ncclResult_t ofcclDestroy(ofcclRankCtx_t ctx) {
   if (ctx->poller.joinable()) ctx->poller.join();
   std::shared_ptr<DaemonLauncher> L = ctx->launcher;
   ctx->launcher.reset();
+  std::shared_ptr<LoopGroup> loop = ctx->colls.begin()->second.comm->loop;
+  // my blocks must have seen the quit entry (or be parked) before the flag words are reused
+  for (int i = 0; i < 50000 && ctx->ctl->alive && !ctx->ctl->finalQuit; ++i) std::this_thread::sleep_for(std::chrono::microseconds(100));
+  releaseHeapParts(ctx);
   bool last = false;
   {
     std::lock_guard<std::mutex> l(L->mu);
@@ -604,14 +615,14 @@ DF_API ncclResult_t ofcclDestroy(ofcclRankCtx_t ctx) {
     last = L->members.empty();
     // A shared daemon keeps serving the other ranks and its launch table still names this
     // rank's device state, so that state lives on (its blocks leave at once on the quit entry)
-    // until the last rank of the group is destroyed.
+    // until the last rank of the group is destroyed.  From here on this thread no longer
+    // touches ctx: the last rank's thread may free it at any time.
     if (!last) L->retired.push_back(ctx);
   }
   if (last) {
-    std::shared_ptr<LoopGroup> loop = ctx->colls.begin()->second.comm->loop;
     if (loop) { std::lock_guard<std::mutex> l(loop->mu); if (loop->launcher == L) loop->launcher.reset(); }
     std::vector<ofcclRankCtx*> retired;
-    retired.swap(L->retired);
+    { std::lock_guard<std::mutex> l(L->mu); retired.swap(L->retired); }
     L.reset();                      // joins the observer, drains the stream, frees the launch table
     for (auto* z : retired) releaseCtx(z);
     releaseCtx(ctx);

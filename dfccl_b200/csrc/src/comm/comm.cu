@@ -86,7 +86,7 @@ struct PeerInfoMsg {
 };
 
 ncclResult_t commCreate(std::shared_ptr<Bootstrap> boot, dfcclBackend_t backend, int device, bool privateHeap,
-                        std::shared_ptr<LoopGroup> loop, ncclComm** out) {
+                        std::shared_ptr<LoopGroup> loop, ncclComm** out, Heap* inherit) {
   const int n = boot->nranks(), r = boot->rank();
   if (n > DF_MAX_RANKS) { DF_WARN("communicators of more than %d ranks are not supported by the direct-access engine", DF_MAX_RANKS); return ncclInvalidArgument; }
   std::unique_ptr<ncclComm> c(new ncclComm());
@@ -94,7 +94,9 @@ ncclResult_t commCreate(std::shared_ptr<Bootstrap> boot, dfcclBackend_t backend,
   logSetRank(r);
   int prevDev = 0;
   if (backend == dfcclBackendCuda) { cudaGetDevice(&prevDev); CUDACHECK(cudaSetDevice(device)); }
-  if (privateHeap) {
+  if (inherit) {
+    c->heap = inherit;
+  } else if (privateHeap) {
     size_t bytes = (size_t)paramI64("HEAP_BYTES", backend == dfcclBackendCuda ? (1ll << 30) : (64ll << 20));
     DFCHECK(Heap::create(backend, device, bytes, &c->heap));
     c->ownsHeap = true;

@@ -64,8 +64,9 @@ struct ncclComm {
 
 namespace dfccl {
 
+// heap selection: `inherit` (a parent's heap, for split) > a private heap > the process heap of the device
 ncclResult_t commCreate(std::shared_ptr<Bootstrap> boot, dfcclBackend_t backend, int device, bool privateHeap,
-                        std::shared_ptr<LoopGroup> loop, ncclComm** out);
+                        std::shared_ptr<LoopGroup> loop, ncclComm** out, Heap* inherit = nullptr);
 ncclResult_t commDestroy(ncclComm* comm);
 dfcclBackend_t defaultBackend();
 void setDefaultBackend(dfcclBackend_t b);

@@ -7,6 +7,8 @@
 #include <string>
 #include <unistd.h>
 #include <sys/time.h>
+#include <execinfo.h>
+#include <signal.h>
 
 namespace dfccl {
 namespace {
@@ -25,7 +27,18 @@ const Name kSubsys[] = {{"INIT", SUB_INIT}, {"COLL", SUB_COLL}, {"P2P", SUB_P2P}
   {"CALL", SUB_CALL}, {"DAEMON", SUB_DAEMON}, {"QUEUE", SUB_QUEUE}, {"BOOT", SUB_BOOT},
   {"LEARN", SUB_LEARN}, {"ALL", SUB_ALL}};
 
+void segvHandler(int sig) {
+  void* frames[64];
+  int n = backtrace(frames, 64);
+  const char msg[] = "\nDFCCL: fatal signal, native backtrace:\n";
+  (void)!write(2, msg, sizeof(msg) - 1);
+  backtrace_symbols_fd(frames, n, 2);
+  signal(sig, SIG_DFL);
+  raise(sig);
+}
+
 void setup() {
+  if (const char* bt = envGet("DEBUG_BACKTRACE")) if (bt[0] == '1') { signal(SIGSEGV, segvHandler); signal(SIGBUS, segvHandler); signal(SIGABRT, segvHandler); }
   const char* lv = envGet("DEBUG");
   g_level = LOG_NONE;
   if (lv) {
