@@ -289,17 +289,23 @@ DF_HD void dataPhase(BlockShared* sh, RankDev* rd, int b) {
 }
 
 // ---- staging copies for buffers outside the symmetric heap
+// Block b copies exactly the bytes that block b of the peers (or of this rank) touches in
+// PH_DATA, because the flags of block b are the only ordering between the two: the same
+// partition as dataPhase, element-based for reducing kinds, byte-based for copying kinds.
 DF_HD void stageCopy(BlockShared* sh, int b, bool in) {
   const CollStatic* c = &sh->cs;
-  const int segs = (!in && c->kind == dfcclCollAllGather) ? c->nranks : 1;
-  const uint64_t total = (in ? sendBytes(c) : recvBytes(c)) / segs;
+  const bool reducing = c->kind == dfcclCollAllReduce || c->kind == dfcclCollReduce || c->kind == dfcclCollReduceScatter;
+  const uint64_t e = in ? dtypeSize(c->inType) : dtypeSize(c->outType);
+  const int segs = (in && c->kind == dfcclCollReduceScatter) || (!in && c->kind == dfcclCollAllGather) ? c->nranks : 1;
+  const uint64_t segBytes = c->count * e;
+  uint64_t bb, be;
+  if (reducing) { partRange(c->count, c->nBlocks, b, 16, &bb, &be); bb *= e; be *= e; }
+  else partRange(segBytes, c->nBlocks, b, 16, &bb, &be);
   for (int s = 0; s < segs; ++s) {
     if (df_tid() == 0) {
-      uint64_t bb, be;
-      partRange(total, c->nBlocks, b, 16, &bb, &be);
       DataArgs* a = &sh->args;
       a->nsrc = 1; a->ndst = 1; a->n = be - bb;
-      uint64_t off = (uint64_t)s * total + bb;
+      const uint64_t off = (uint64_t)s * segBytes + bb;
       if (in) { a->src[0] = (const char*)sh->dyn.send + off; a->dst[0] = c->peerHeap[c->rank] + c->stagingSendOff + off; }
       else { a->src[0] = c->peerHeap[c->rank] + c->stagingRecvOff + off; a->dst[0] = (char*)sh->dyn.recv + off; }
       sh->stats.bytesCopied += a->n;

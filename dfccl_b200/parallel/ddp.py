@@ -1,0 +1,201 @@
+"""Data parallelism over the daemon.
+
+Parameters are regrouped into flat buckets (default 25 MB of gradient each).  Every
+bucket owns
+  * a flat parameter array (the module's parameters become views into it),
+  * a flat gradient array in the symmetric heap (``param.grad`` are views into it, so the
+    backward pass writes gradients where the peers can read them - nothing is copied),
+  * an fp32 array the all-reduce writes the averaged gradient to: the 1/world scale and the
+    cast to fp32 happen inside the collective,
+  * fp32 master weights and momentum for the fused optimizer step.
+One all-reduce per bucket is registered with the daemon.  When the last gradient of a
+bucket has been accumulated the bucket is submitted *stream-ordered*: a stream memory
+operation releases it after the backward kernels already enqueued, no host thread waits.
+Submission order can be shuffled per rank (``randomize_order``) - ranks then issue the
+same collectives in different orders, which is exactly what the daemon makes safe.
+
+The reference has no training integration in its tree; its authors drove data-parallel
+training from an external framework through the register-then-submit calls
+(reference: src/nccl.h.in:318-333, debug constants for a 161-collective ResNet job in
+src/include/collectives_ofccl.h:63,78-100).
+"""
+from __future__ import annotations
+
+import ctypes as C
+import random
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional
+
+import torch
+import torch.nn as nn
+
+from .. import native as nv
+from ..utils.tensors import HeapTensorPool, nccl_dtype
+from .groups import Dist
+
+
+@dataclass(eq=False)
+class Bucket:
+    index: int
+    dtype: torch.dtype
+    params: List[nn.Parameter] = field(default_factory=list)
+    offsets: List[int] = field(default_factory=list)
+    numel: int = 0
+    flat_param: Optional[torch.Tensor] = None
+    grad: Optional[torch.Tensor] = None        # heap, param dtype
+    grad32: Optional[torch.Tensor] = None      # heap, fp32: all-reduce output
+    master: Optional[torch.Tensor] = None
+    momentum: Optional[torch.Tensor] = None
+    pending: int = 0
+    coll_id: int = 0
+
+
+def _view_like(flat: torch.Tensor, off: int, p: torch.Tensor) -> torch.Tensor:
+    """View of flat[off : off + p.numel()] with p's shape and memory format."""
+    seg = flat[off:off + p.numel()]
+    if p.dim() == 4 and p.is_contiguous(memory_format=torch.channels_last) and not p.is_contiguous():
+        n, c, h, w = p.shape
+        return seg.view(n, h, w, c).permute(0, 3, 1, 2)
+    return seg.view(p.shape)
+
+
+class DaemonDDP:
+    """Wraps ``module`` for data-parallel training through the daemon.
+
+    Typical step::
+
+        loss = criterion(ddp.module(x), y)
+        loss.backward()          # buckets are submitted from gradient hooks
+        ddp.finish_backward()    # the compute stream waits (on the device) for all buckets
+        ddp.step()               # fused SGD over the flat buckets, gradients zeroed
+    """
+
+    def __init__(self, module: nn.Module, dist: Dist, *, bucket_mb: float = 25.0, lr: float = 0.1, momentum: float = 0.9,
+                 weight_decay: float = 1e-4, randomize_order: bool = True, window: int = 2, seed: int = 0,
+                 coll_id_base: int = 0, comm: Optional[nv.Comm] = None, n_blocks: int = 0):
+        self.module = module
+        self.dist = dist
+        self.comm = comm or dist.comm
+        self.world = self.comm.nranks
+        self.device = dist.device
+        self.lr, self.mu, self.wd = lr, momentum, weight_decay
+        self.randomize = randomize_order
+        self.window = max(1, window)
+        self._rng = random.Random(seed * 7919 + dist.rank)
+        self._lib = nv.lib()
+        self._pool = HeapTensorPool(self.comm, self.device)
+        self._ready: List[Bucket] = []
+        self._submitted: List[Bucket] = []
+        self._first_step = True
+        self.launches = 0                       # kernels of this library launched by step()
+        self.buckets: List[Bucket] = []
+        self._build_buckets(int(bucket_mb * (1 << 20)))
+        self.ctx = nv.RankCtx(dist.rank, dist.local_rank if self.device.type == "cuda" else -1)
+        for b in self.buckets:
+            b.coll_id = coll_id_base + b.index
+            self.ctx.prepare(b.coll_id, self.comm, nv.ALLREDUCE, b.numel, nccl_dtype(b.dtype), out_dtype=nv.FLOAT32,
+                             op=nv.SUM, scale=1.0 / self.world, n_blocks=n_blocks)
+        self.ctx.finalize()
+        self._hooks = []
+        for b in self.buckets:
+            for p in b.params:
+                self._hooks.append(p.register_post_accumulate_grad_hook(self._make_hook(b)))
+
+    # ------------------------------------------------------------------ construction
+    def _build_buckets(self, bucket_bytes: int) -> None:
+        params = [p for p in self.module.parameters() if p.requires_grad]
+        by_dtype: Dict[torch.dtype, List[nn.Parameter]] = {}
+        for p in reversed(params):              # gradients arrive roughly in reverse registration order
+            by_dtype.setdefault(p.dtype, []).append(p)
+        for dt, plist in by_dtype.items():
+            cur: Optional[Bucket] = None
+            esize = torch.empty((), dtype=dt).element_size()
+            for p in plist:
+                if cur is None or (cur.numel + p.numel()) * esize > bucket_bytes and cur.numel > 0:
+                    cur = Bucket(len(self.buckets), dt)
+                    self.buckets.append(cur)
+                cur.offsets.append(cur.numel)
+                cur.params.append(p)
+                cur.numel += (p.numel() + 7) // 8 * 8      # keep every parameter 16-byte aligned
+        for b in self.buckets:
+            b.flat_param = torch.empty(b.numel, dtype=b.dtype, device=self.device)
+            b.grad = self._pool.zeros((b.numel,), b.dtype)
+            b.grad32 = self._pool.zeros((b.numel,), torch.float32)
+            b.flat_param.zero_()
+            with torch.no_grad():
+                for p, off in zip(b.params, b.offsets):
+                    v = _view_like(b.flat_param, off, p)
+                    v.copy_(p.data)
+                    p.data = v
+                    p.grad = _view_like(b.grad, off, p)
+            b.master = b.flat_param.float().clone()
+            b.momentum = torch.zeros_like(b.master)
+            b.pending = len(b.params)
+
+    def _make_hook(self, b: Bucket):
+        def hook(_param):
+            b.pending -= 1
+            if b.pending == 0:
+                self._bucket_ready(b)
+        return hook
+
+    # ------------------------------------------------------------------ per step
+    def _stream(self) -> int:
+        return torch.cuda.current_stream(self.device).cuda_stream if self.device.type == "cuda" else 0
+
+    def _bucket_ready(self, b: Bucket) -> None:
+        self._ready.append(b)
+        if len(self._ready) >= self.window:
+            self._flush()
+
+    def _flush(self) -> None:
+        batch, self._ready = self._ready, []
+        if self.randomize:
+            self._rng.shuffle(batch)
+        s = self._stream()
+        for b in batch:
+            self.ctx.run_on_stream(b.coll_id, b.grad.data_ptr(), b.grad32.data_ptr(), s)
+            self._submitted.append(b)
+
+    def finish_backward(self) -> None:
+        """Submit what is still queued and make the current stream wait for every bucket."""
+        for b in self.buckets:                   # buckets whose parameters did not all receive a gradient
+            if b not in self._submitted and b not in self._ready:
+                self._ready.append(b)
+        self._flush()
+        s = self._stream()
+        for b in self._submitted:
+            self.ctx.stream_wait(b.coll_id, s)
+        self._submitted = []
+        for b in self.buckets:
+            b.pending = len(b.params)
+
+    def step(self, lr: Optional[float] = None) -> None:
+        """Fused SGD with momentum over every flat bucket, then clear the gradients."""
+        lr = self.lr if lr is None else lr
+        s = self._stream()
+        for b in self.buckets:
+            if self.device.type == "cuda":
+                nv.check(self._lib.dfcclFusedSgdStep(
+                    C.c_void_p(b.master.data_ptr()), C.c_void_p(b.grad32.data_ptr()), C.c_void_p(b.momentum.data_ptr()),
+                    C.c_void_p(b.flat_param.data_ptr()), b.numel, nccl_dtype(b.dtype), lr, self.mu, self.wd,
+                    1 if self._first_step else 0, C.c_void_p(s)), "dfcclFusedSgdStep")
+                self.launches += 1
+            else:                                  # host backend (tests): the same arithmetic in PyTorch
+                g = b.grad32 + self.wd * b.master
+                b.momentum.mul_(0.0 if self._first_step else self.mu).add_(g)
+                b.master.sub_(lr * b.momentum)
+                b.flat_param.copy_(b.master)
+            b.grad.zero_()
+        self._first_step = False
+
+    def stats(self) -> Dict[str, int]:
+        return self.ctx.stats()
+
+    def close(self) -> None:
+        for h in self._hooks:
+            h.remove()
+        if self.device.type == "cuda":
+            torch.cuda.synchronize(self.device)
+        self.ctx.destroy()
+        self._pool.release()

@@ -1,0 +1,83 @@
+"""Data-parallel wrapper on the host backend: flat buckets, gradient views in the symmetric
+heap, fused scale / cast in the all-reduce, randomized bucket order, optimizer arithmetic."""
+import copy
+
+import numpy as np
+import pytest
+import torch
+import torch.nn as nn
+
+from helpers import run_ranks
+
+
+def _mlp():
+    torch.manual_seed(5)
+    return nn.Sequential(nn.Linear(32, 64), nn.ReLU(), nn.Linear(64, 64), nn.ReLU(), nn.Linear(64, 8))
+
+
+@pytest.mark.parametrize("world", [1, 2, 4])
+def test_ddp_matches_single_process_sgd(host_backend, world):
+    nv = host_backend
+    from dfccl_b200.parallel import DaemonDDP, Dist
+    comms = nv.Comm.init_loopback(world)
+    steps, lr, mu, wd = 4, 0.05, 0.9, 1e-3
+    xs = [[torch.randn(16, 32, generator=torch.Generator().manual_seed(10 * s + r)) for r in range(world)] for s in range(steps)]
+    ys = [[torch.randn(16, 8, generator=torch.Generator().manual_seed(99 + 10 * s + r)) for r in range(world)] for s in range(steps)]
+
+    # reference: one process, gradients averaged over the per-rank batches, classic momentum SGD
+    ref = _mlp()
+    bufs = [torch.zeros_like(p) for p in ref.parameters()]
+    for s in range(steps):
+        grads = [torch.zeros_like(p) for p in ref.parameters()]
+        for r in range(world):
+            ref.zero_grad()
+            nn.functional.mse_loss(ref(xs[s][r]), ys[s][r]).backward()
+            for g, p in zip(grads, ref.parameters()):
+                g += p.grad / world
+        with torch.no_grad():
+            for p, g, m in zip(ref.parameters(), grads, bufs):
+                g = g + wd * p
+                m.mul_(mu if s > 0 else 0.0).add_(g)
+                p.sub_(lr * m)
+
+    finals = {}
+    nets = [_mlp() for _ in range(world)]       # built here: the global RNG is not thread safe
+
+    def body(r):
+        d = Dist(r, world, 0, torch.device("cpu"), comms[r], False)
+        net = nets[r]
+        ddp = DaemonDDP(net, d, bucket_mb=0.004, lr=lr, momentum=mu, weight_decay=wd, randomize_order=True, window=2, seed=3)
+        assert len(ddp.buckets) >= 3                      # several buckets so that orders really differ
+        for s in range(steps):
+            nn.functional.mse_loss(net(xs[s][r]), ys[s][r]).backward()
+            ddp.finish_backward()
+            assert ddp.ctx.wait_all(30000) == nv.SUCCESS
+            ddp.step()
+        finals[r] = [p.detach().clone() for p in net.parameters()]
+        st = ddp.stats()
+        assert st["cqesDelivered"] == steps * len(ddp.buckets)
+        ddp.close()
+
+    run_ranks(world, body)
+    for c in comms:
+        c.destroy()
+    for r in range(world):
+        for got, exp in zip(finals[r], ref.parameters()):
+            torch.testing.assert_close(got, exp.detach(), rtol=1e-5, atol=1e-6)
+
+
+def test_parameters_and_gradients_are_views_of_flat_buckets(host_backend):
+    nv = host_backend
+    from dfccl_b200.parallel import DaemonDDP, Dist
+    (c,) = nv.Comm.init_loopback(1)
+    net = _mlp()
+    ddp = DaemonDDP(net, Dist(0, 1, 0, torch.device("cpu"), c, False), bucket_mb=1.0)
+    base, nbytes, _ = c.heap_info()
+    for b in ddp.buckets:
+        assert base <= b.grad.data_ptr() < base + nbytes and base <= b.grad32.data_ptr() < base + nbytes
+        for p, off in zip(b.params, b.offsets):
+            assert p.data_ptr() == b.flat_param.data_ptr() + off * p.element_size()
+            assert p.grad.data_ptr() == b.grad.data_ptr() + off * p.element_size()
+            assert off % 8 == 0
+    ddp.close()
+    c.destroy()
