@@ -109,6 +109,10 @@ class DaemonBackend:
 
 
 def run(args):
+    import faulthandler
+    # a stalled run prints every thread's stack and exits instead of sitting on the GPU
+    faulthandler.dump_traceback_later(int(os.environ.get("BENCH_WATCHDOG_S", "900")), exit=True)
+    os.environ.setdefault("DFCCL_WAIT_TIMEOUT_MS", "60000")
     world = int(os.environ.get("WORLD_SIZE", "1"))
     if world != args.gpus:
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch one rank per GPU with torchrun")

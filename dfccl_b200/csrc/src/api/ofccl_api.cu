@@ -378,7 +378,14 @@ static ncclResult_t submit(ofcclRankCtx* ctx, const void* send, void* recv, int 
     auto it = ctx->colls.find(collId);
     if (it == ctx->colls.end()) { DF_WARN("collective %d was never prepared", collId); return ncclInvalidArgument; }
     CollEntry& e = it->second;
-    if (e.submitted != e.completed) { DF_WARN("collective %d submitted again before its callback ran", collId); return ncclInvalidUsage; }
+    if (e.submitted != e.completed) {
+      if (!onStream) { DF_WARN("collective %d submitted again before its callback ran", collId); return ncclInvalidUsage; }
+      // Stream-ordered callers enqueue ahead of the GPU: the previous submission of this id is
+      // already ordered before this one on the device, so the host only has to wait for it.
+      const bool ok = ctx->doneCv.wait_for(l, std::chrono::seconds(120), [&] { return e.submitted == e.completed || ctx->ctl->abortFlag; });
+      if (!ok) { DF_WARN("collective %d: previous submission did not complete within 120 s", collId); return dfcclTimeout; }
+      if (ctx->ctl->abortFlag) return dfcclAborted;
+    }
     const CollStatic& cs = e.cs;
     const bool needSend = !(cs.kind == dfcclCollBroadcast && cs.rank != cs.root);
     const bool needRecv = !(cs.kind == dfcclCollReduce && cs.rank != cs.root);

@@ -62,19 +62,24 @@ DF_HD int consumeSubmissions(BlockShared* sh, RankDev* rd, int b) {
     __builtin_memcpy(&q, &w0, 16);
     __builtin_memcpy((char*)&q + 16, &w1, 16);
     if (q.flags & SQE_QUIT) { sh->quit = 2; break; }       // the frontier stays on the quit entry
+    const int coll = q.collId;
+    const bool mine = coll >= 0 && (uint32_t)coll < rd->maxColls && rd->colls[coll].valid && b < rd->colls[coll].nBlocks;
+    CollDyn* d = mine ? &rd->dyn[(uint64_t)b * rd->maxColls + coll] : nullptr;
+    if (mine) {
+      // A stream-ordered caller may publish the next submission of a collective while this block
+      // still runs the previous one.  The entry is never dropped: consumption stops here and
+      // resumes once the running submission has completed.
+      const CollDyn* cur = sh->loadedColl == coll ? &sh->dyn : d;
+      if (cur->epoch != 0 && cur->phase != PH_COMPLETE) break;
+      if (sh->loadedColl == coll) {                         // re-armed below in global memory: drop the cached copy
+        saveLoaded(sh, rd, b);
+        sh->loadedColl = -1;
+      }
+    }
     ++sh->frontier;
     ++got;
     sh->stats.sqesSeen++;
-    const int coll = q.collId;
-    if (coll < 0 || (uint32_t)coll >= rd->maxColls) continue;
-    const CollStatic* c = &rd->colls[coll];
-    if (!c->valid || b >= c->nBlocks) continue;
-    if (sh->loadedColl == coll) {                           // parked copy must be current before it is re-armed
-      saveLoaded(sh, rd, b);
-      sh->loadedColl = -1;
-    }
-    CollDyn* d = &rd->dyn[(uint64_t)b * rd->maxColls + coll];
-    if (d->epoch != 0 && d->phase != PH_COMPLETE) { sh->stats.waitTimeouts++; continue; }   // still running: caller broke the contract
+    if (!mine) continue;
     d->send = q.send; d->recv = q.recv; d->trigger = q.trigger; d->cursor = 0;
     d->epoch = d->epoch + 1; d->phase = PH_TRIGGER; d->sqeFlags = q.flags; d->status = ST_OK; d->stallSinceNs = 0;
     if (sh->nActive < DF_MAX_ACTIVE) sh->active[sh->nActive++] = (uint16_t)coll;

@@ -429,3 +429,39 @@ def test_comm_split_builds_tp_and_dp_groups(host_backend):
     run_ranks(4, body)
     for c in comms:
         c.destroy()
+
+
+def test_stream_ordered_submissions_may_run_ahead(host_backend):
+    """A stream-ordered caller re-submits an id without waiting for the previous completion
+    (the device timeline orders them): nothing is dropped, nothing is reordered."""
+    nv = host_backend
+    comms = nv.Comm.init_loopback(2)
+
+    def body(r):
+        ctx = nv.RankCtx(r)
+        ctx.prepare(0, comms[r], nv.ALLREDUCE, 512, nv.FLOAT32)
+        ctx.prepare(1, comms[r], nv.ALLREDUCE, 512, nv.FLOAT32)
+        ctx.finalize()
+        p, q = comms[r].alloc(2048), comms[r].alloc(2048)
+        host_array(p, 512, np.float32)[:] = 1.0
+        host_array(q, 512, np.float32)[:] = 1.0
+        for it in range(40):
+            for cid, buf in ((0, p), (1, q)) if (it + r) % 2 else ((1, q), (0, p)):
+                ctx.run_on_stream(cid, buf, buf, 0)          # in place: every round doubles the values
+        assert ctx.wait_all(60000) == nv.SUCCESS
+        assert ctx.stats()["cqesDelivered"] == 80
+        ctx.destroy()
+
+    run_ranks(2, body)
+    for c in comms:
+        c.destroy()
+
+
+def test_staged_buffers_with_several_blocks(host_backend):
+    """Unregistered buffers and more than one block per collective: the staging copies must use
+    the same partition as the data movement (block b's flags order only block b's bytes)."""
+    nv = host_backend
+    import test_host_collectives as T
+    with _env(DFCCL_DAEMON_BLOCKS=3, DFCCL_MIN_BYTES_PER_BLOCK=1024):
+        for kind in T.KINDS:
+            T._run_case(nv, kind, 4, 30011, nv.FLOAT32, heap=False, root=1, iters=2)
