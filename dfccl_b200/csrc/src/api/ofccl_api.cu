@@ -347,6 +347,20 @@ DF_API ncclResult_t ofcclFinalizeRankCtx7StartHostThrds(ofcclRankCtx_t ctx) {
         L->devTable = (RankDev**)malloc(sizeof(RankDev*) * tab.size());
         memcpy(L->devTable, tab.data(), sizeof(RankDev*) * tab.size());
       }
+      if (be == dfcclBackendCuda) {
+        // First launch now, while nothing depends on the daemon.  CUDA loads kernels lazily and the
+        // first launch of this one grows the context's local-memory pool, which needs an idle
+        // device: done later, with a user stream already blocked on a flag only the daemon sets,
+        // that launch (and every launch queued behind it) would never start.  With no submission
+        // pending every block leaves after the idle limit.
+        DFCHECK(warmRuntimeKernels());
+        cudaFuncAttributes fa;
+        CUDACHECK(cudaFuncGetAttributes(&fa, dfcclWriteWordKernel));
+        for (auto* m : L->members) m->ctl->alive = 1;
+        DFCHECK(launchDaemonCuda(L->devTable, L->expected, L->blocks, L->threads, L->stream));
+        CUDACHECK(cudaStreamSynchronize(L->stream));
+        for (auto* m : L->members) m->ctl->alive = 0;
+      }
       L->started = true;
       L->observer = std::thread(observerMain, L.get());
     }

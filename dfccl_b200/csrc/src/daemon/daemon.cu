@@ -25,6 +25,12 @@ ncclResult_t launchDaemonCuda(RankDev** devRankTable, int nRanks, int blocksPerR
   return ncclSuccess;
 }
 
+ncclResult_t warmDaemonKernel() {
+  cudaFuncAttributes a;
+  CUDACHECK(cudaFuncGetAttributes(&a, dfcclDaemonKernel));
+  return ncclSuccess;
+}
+
 ncclResult_t daemonMaxResidentBlocks(int device, int threads, int* blocks) {
   int perSm = 0, sms = 0;
   CUDACHECK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&perSm, dfcclDaemonKernel, threads, 0));

@@ -20,4 +20,11 @@ ncclResult_t launchStandaloneCuda(RankDev* rd, const CollStatic& cs, uint64_t se
   return ncclSuccess;
 }
 
+ncclResult_t warmDaemonKernel();
+ncclResult_t warmRuntimeKernels() {
+  cudaFuncAttributes a;
+  CUDACHECK(cudaFuncGetAttributes(&a, dfcclCollKernel));
+  return warmDaemonKernel();
+}
+
 }  // namespace dfccl

@@ -14,6 +14,9 @@ ncclResult_t launchDaemonCuda(RankDev** devRankTable, int nRanks, int blocksPerR
 ncclResult_t launchStandaloneCuda(RankDev* rd, const CollStatic& cs, uint64_t send, uint64_t recv, uint32_t epoch,
                                   uint32_t sqeFlags, int threads, cudaStream_t stream);
 
+// Force the lazily loaded kernels of the runtime into the context (no launch).
+ncclResult_t warmRuntimeKernels();
+
 // Largest grid of the daemon kernel that is guaranteed co-resident on `device`.
 ncclResult_t daemonMaxResidentBlocks(int device, int threads, int* blocks);
 

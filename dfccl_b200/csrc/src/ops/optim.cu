@@ -74,3 +74,11 @@ ncclResult_t dfcclFusedSgdStep(void* master, const void* grad, void* momentum, v
     return ncclInvalidArgument;
   return cudaGetLastError() == cudaSuccess ? ncclSuccess : ncclUnhandledCudaError;
 }
+
+// Load the kernels of this file into the current context without launching them.
+extern "C" __attribute__((visibility("default"))) ncclResult_t dfcclOpsWarm(void) {
+  cudaFuncAttributes a;
+  if (cudaFuncGetAttributes(&a, sgdKernel<__nv_bfloat16>) != cudaSuccess) return ncclUnhandledCudaError;
+  if (cudaFuncGetAttributes(&a, sgdKernel<float>) != cudaSuccess) return ncclUnhandledCudaError;
+  return ncclSuccess;
+}

@@ -106,6 +106,7 @@ def lib() -> C.CDLL:
             "dfcclGetStats": [vp, C.POINTER(Stats)], "dfcclTraceDump": [vp, C.c_char_p],
             "dfcclInjectFault": [vp, i, C.c_int64],
             "dfcclFusedSgdStep": [vp, vp, vp, vp, sz, i, C.c_float, C.c_float, C.c_float, i, vp],
+            "dfcclOpsWarm": [],
         }
         for name, args in sig.items():
             f = getattr(L, name)

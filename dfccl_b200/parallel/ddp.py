@@ -96,6 +96,8 @@ class DaemonDDP:
             self.ctx.prepare(b.coll_id, self.comm, nv.ALLREDUCE, b.numel, nccl_dtype(b.dtype), out_dtype=nv.FLOAT32,
                              op=nv.SUM, scale=1.0 / self.world, n_blocks=n_blocks)
         self.ctx.finalize()
+        if self.device.type == "cuda":
+            nv.check(self._lib.dfcclOpsWarm(), "dfcclOpsWarm")   # load the optimizer kernels before any stream can block
         self._hooks = []
         for b in self.buckets:
             for p in b.params:
