@@ -38,6 +38,7 @@ def parse():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="dfccl", choices=["dfccl", "reference"])
+    ap.add_argument("--graph", type=int, default=1, help="capture forward+backward in a CUDA graph (this library's arm only)")
     ap.add_argument("--batch", type=int, default=BATCH_PER_GPU, help=argparse.SUPPRESS)
     ap.add_argument("--model", default="resnet50", help=argparse.SUPPRESS)
     return ap.parse_args()
@@ -69,11 +70,21 @@ class Trainer:
         self.backend = backend
         backend.attach(self.net)
         self.batch = args.batch
+        self.graphed = None
+        self.use_graph = bool(args.graph) and args.impl == "dfccl"
+
+    def loss_fn(self, out, y):
+        return self.crit(out.float(), y)
 
     def step(self, x, y):
-        out = self.net(x)
-        loss = self.crit(out.float(), y)
-        loss.backward()
+        if self.use_graph:
+            if self.graphed is None:
+                from dfccl_b200.parallel import GraphedStep
+                self.graphed = GraphedStep(self.net, self.loss_fn, self.backend.ddp, x, y)
+            loss = self.graphed(x, y)
+        else:
+            loss = self.loss_fn(self.net(x), y)
+            loss.backward()
         self.backend.finish_backward()
         self.backend.step()
         return loss
@@ -164,7 +175,7 @@ def run(args):
         sync()
     ms = max_over_ranks(e0.elapsed_time(e1), world)
     launches = backend.launches() - launches0
-    final_loss = float(loss)
+    final_loss = float(loss.detach())
     clocks = clk.summary()
 
     # ---- timed region 2: end to end through the public API: H2D of each batch, D2H of each loss
@@ -217,7 +228,7 @@ def run(args):
             "impl": args.impl,
             "config": {"model": "ResNet-50 v1.5" if args.model == "resnet50" else args.model, "global_batch": gb,
                        "batch_per_gpu": B, "seq_len": None, "parallelism": f"dp{world}",
-                       "grad_buckets_mb": BUCKET_MB, "optimizer": "SGD momentum 0.9 wd 1e-4, fp32 master weights",
+                       "grad_buckets_mb": BUCKET_MB, "optimizer": "SGD momentum 0.9 wd 1e-4, fp32 master weights", "cuda_graph": bool(tr.use_graph),
                        "gradient_path": ("daemon all-reduce, fused 1/N scale + bf16->fp32 cast, per-rank randomized bucket order"
                                          if args.impl == "dfccl" else "reference library ncclAllReduce per bucket"),
                        "l2": "activations and gradients per step far exceed the 126 MB L2; no explicit flush"},

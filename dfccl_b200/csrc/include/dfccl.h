@@ -191,6 +191,10 @@ ncclResult_t dfcclMemFree(void* ptr, ncclComm_t comm);
 ncclResult_t dfcclHeapInfo(ncclComm_t comm, void** base, size_t* bytes, size_t* used);
 
 ncclResult_t dfcclInitRankCtxOnDevice(ofcclRankCtx_t* rankCtx, int rank, int device);
+/* Daemon grid of this context: thread blocks per rank and threads per block (multiple of 32, <= 512);
+ * 0 keeps the default (DFCCL_DAEMON_BLOCKS / DFCCL_DAEMON_THREADS).  Call before finalizing.  All ranks
+ * of a collective must use the same number of blocks. */
+ncclResult_t dfcclSetDaemonGeometry(ofcclRankCtx_t rankCtx, int blocks, int threads);
 
 /* Registration with the fused epilogue: out = cast<outType>(scale * reduce(in)).
  * `scale` multiplies the reduced value (ncclAvg sets it to 1/nranks by itself).

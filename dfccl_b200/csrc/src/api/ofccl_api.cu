@@ -22,6 +22,21 @@ __global__ void dfcclWriteWordKernel(volatile uint64_t* p, uint64_t v) {
   *p = v;
 }
 
+// Runs on a driver thread when a stream reaches the point right after a trigger write: only now
+// does the submission need a daemon, so only now is the launcher woken.  Waking it at enqueue
+// time would keep the daemon resident (and polling) while the GPU is still busy with the work
+// queued before the trigger.
+static void CUDART_CB triggerReached(void* arg) {
+  ofcclRankCtx* ctx = (ofcclRankCtx*)arg;
+  ctx->untriggered--;
+  std::shared_ptr<DaemonLauncher> L = ctx->launcher;
+  if (L && !ctx->ctl->alive) {
+    std::lock_guard<std::mutex> l(L->mu);
+    L->wake = true;
+    L->cv.notify_all();
+  }
+}
+
 static uint32_t pow2ceil(uint32_t v) { uint32_t p = 1; while (p < v) p <<= 1; return p; }
 
 DaemonLauncher::~DaemonLauncher() {
@@ -74,7 +89,7 @@ static void observerMain(DaemonLauncher* L) {
     }
     bool work = false, dead = false;
     for (auto* m : members) {
-      if (m->remaining.load() > 0 && !m->ctl->finalQuit) work = true;
+      if (m->remaining.load() - m->untriggered.load() > 0 && !m->ctl->finalQuit) work = true;
       if (m->ctl->abortFlag) dead = true;
     }
     if (work && !dead) {
@@ -87,7 +102,7 @@ static void observerMain(DaemonLauncher* L) {
         if (r != ncclSuccess) for (auto* m : members) m->asyncError = r;
       } else {
         runDaemonHost(L->devTable, L->expected, L->blocks);     // returns when every block has left
-        for (auto* m : members) if (m->remaining.load() > 0 && !m->ctl->finalQuit && !m->ctl->abortFlag) { lk.lock(); L->wake = true; lk.unlock(); break; }
+        for (auto* m : members) if (m->remaining.load() - m->untriggered.load() > 0 && !m->ctl->finalQuit && !m->ctl->abortFlag) { lk.lock(); L->wake = true; lk.unlock(); break; }
       }
     }
     lk.lock();
@@ -138,7 +153,7 @@ static void pollerMain(ofcclRankCtx* ctx) {
     }
     // nothing new: if the daemon left while work is outstanding, have it launched again
     if (++empty % ctx->checkInterval == 0 || (empty & 63) == 0) {
-      if (!ctx->ctl->alive && ctx->remaining.load() > 0 && !ctx->ctl->abortFlag) wakeLauncher(ctx->launcher.get());
+      if (!ctx->ctl->alive && ctx->remaining.load() - ctx->untriggered.load() > 0 && !ctx->ctl->abortFlag) wakeLauncher(ctx->launcher.get());
     }
     if (empty > 2000) std::this_thread::sleep_for(std::chrono::microseconds(20)); else sched_yield();
   }
@@ -164,6 +179,12 @@ DF_API ncclResult_t dfcclInitRankCtxOnDevice(ofcclRankCtx_t* out, int rank, int 
   ctx->rank = rank; ctx->device = device; ctx->deviceChosen = device >= 0;
   ctx->backend = defaultBackend();
   *out = ctx;
+  return ncclSuccess;
+}
+DF_API ncclResult_t dfcclSetDaemonGeometry(ofcclRankCtx_t ctx, int blocks, int threads) {
+  if (!ctx || ctx->finalized) return ncclInvalidUsage;
+  if (blocks < 0 || blocks > DF_MAX_BLOCKS || threads < 0 || threads > 512 || (threads % 32) != 0) return ncclInvalidArgument;
+  ctx->wantBlocks = blocks; ctx->wantThreads = threads;
   return ncclSuccess;
 }
 DF_API ncclResult_t ofcclInitRankCtx(ofcclRankCtx_t* out, int rank) { return dfcclInitRankCtxOnDevice(out, rank, -1); }
@@ -211,7 +232,7 @@ DF_API ncclResult_t ofcclFinalizeRankCtx7StartHostThrds(ofcclRankCtx_t ctx) {
   int prevDev = 0;
   if (be == dfcclBackendCuda) { cudaGetDevice(&prevDev); CUDACHECK(cudaSetDevice(ctx->device)); }
   logSetRank(ctx->rank);
-  ctx->nBlocks = daemonBlocks(be);
+  ctx->nBlocks = ctx->wantBlocks > 0 ? std::min(ctx->wantBlocks, DF_MAX_BLOCKS) : daemonBlocks(be);
   ctx->checkInterval = std::max<int64_t>(1, paramI64("CHECK_REMAINING_SQE_INTERVAL", 10000));
   const Topology* topo = nullptr;
   DFCHECK(topoGet(&topo));
@@ -325,7 +346,8 @@ DF_API ncclResult_t ofcclFinalizeRankCtx7StartHostThrds(ofcclRankCtx_t ctx) {
       L->expected = 1;
     }
     std::lock_guard<std::mutex> l(L->mu);
-    L->backend = be; L->device = ctx->device; L->blocks = ctx->nBlocks; L->threads = daemonThreads(be);
+    L->backend = be; L->device = ctx->device; L->blocks = ctx->nBlocks;
+    L->threads = (be == dfcclBackendCuda && ctx->wantThreads > 0) ? ctx->wantThreads : daemonThreads(be);
     ctx->launcherSlot = (int)L->members.size();
     L->members.push_back(ctx);
     ctx->launcher = L;
@@ -440,7 +462,9 @@ static ncclResult_t submit(ofcclRankCtx* ctx, const void* send, void* recv, int 
     }
   }
   ctx->pollCv.notify_one();
-  if (!ctx->ctl->alive) wakeLauncher(ctx->launcher.get());
+  const bool deferWake = onStream && ctx->backend == dfcclBackendCuda;
+  if (deferWake) ctx->untriggered++;
+  else if (!ctx->ctl->alive) wakeLauncher(ctx->launcher.get());
   if (onStream) {
     volatile uint64_t* word = ctx->rdHost.trigger + collId;
     if (ctx->backend == dfcclBackendCuda) {
@@ -452,6 +476,7 @@ static ncclResult_t submit(ofcclRankCtx* ctx, const void* send, void* recv, int 
         dfcclWriteWordKernel<<<1, 1, 0, stream>>>(word, trig);
         CUDACHECK(cudaGetLastError());
       }
+      CUDACHECK(cudaLaunchHostFunc(stream, triggerReached, ctx));
     } else {
       __atomic_store_n((uint64_t*)word, trig, __ATOMIC_RELEASE);
     }

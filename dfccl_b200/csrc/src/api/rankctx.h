@@ -74,6 +74,7 @@ struct ofcclRankCtx {
   dfccl::RankDev rdHost{};
   dfccl::RankDev* rdDev = nullptr;
   int nBlocks = 1;
+  int wantBlocks = 0, wantThreads = 0;   // dfcclSetDaemonGeometry; 0 = environment / default
   // threads
   std::shared_ptr<dfccl::DaemonLauncher> launcher;
   int launcherSlot = 0;
@@ -82,6 +83,7 @@ struct ofcclRankCtx {
   std::condition_variable pollCv;     // poller sleeps here while nothing is outstanding
   std::condition_variable doneCv;     // dfcclWait
   std::atomic<int64_t> remaining{0};  // submissions without a delivered completion
+  std::atomic<int64_t> untriggered{0};// of those, stream-ordered ones whose stream has not reached the trigger yet
   std::atomic<bool> stopPoller{false};
   int64_t checkInterval = 10000;      // CHECK_REMAINING_SQE_INTERVAL
   // stats / faults

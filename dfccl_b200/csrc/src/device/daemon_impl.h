@@ -146,6 +146,7 @@ DF_HD void daemonBlockMain(RankDev* rd, int b, BlockShared* sh) {
   for (;;) {
     // ---- 1. task queue traversal (every value steering control flow here is block-uniform)
     bool progressed = false;
+    uint32_t trigWaits = 0;          // collectives whose stream has not released them yet
     const uint32_t nAct = sh->nActive;
     for (uint32_t i = 0; i < nAct; ++i) {
       const int coll = sh->active[i];
@@ -155,6 +156,7 @@ DF_HD void daemonBlockMain(RankDev* rd, int b, BlockShared* sh) {
       bool moved = false;
       int rc = runColl(sh, rd, b, coll, budget, &moved);
       if (rc == RC_DONE || moved) progressed = true;
+      if (rc == RC_STALLED && sh->dyn.phase == PH_TRIGGER) ++trigWaits;
       if (tid == 0) {
         sh->stats.visits++;
         if (rc == RC_DONE) sh->active[i] = 0xffff;
@@ -181,7 +183,9 @@ DF_HD void daemonBlockMain(RankDev* rd, int b, BlockShared* sh) {
         st_release_sys_u32(&rd->quitting, 1u);
       }
       else if (progressed) lastUseful = now;
-      else if (!sh->quit && (winding || now - lastUseful > (sh->nActive ? rd->stallQuitNs : rd->idleQuitNs))) {
+      // only waiting for streams to release submissions: nothing a resident daemon can speed up, and
+      // the host relaunches it when a trigger fires, so leave as quickly as when idle
+      else if (!sh->quit && (winding || now - lastUseful > ((sh->nActive && trigWaits < nAct) ? rd->stallQuitNs : rd->idleQuitNs))) {
         sh->quit = 1;
         st_release_sys_u32(&rd->quitting, 1u);
       }

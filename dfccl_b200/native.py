@@ -107,6 +107,7 @@ def lib() -> C.CDLL:
             "dfcclInjectFault": [vp, i, C.c_int64],
             "dfcclFusedSgdStep": [vp, vp, vp, vp, sz, i, C.c_float, C.c_float, C.c_float, i, vp],
             "dfcclOpsWarm": [],
+            "dfcclSetDaemonGeometry": [vp, i, i],
         }
         for name, args in sig.items():
             f = getattr(L, name)
@@ -232,6 +233,9 @@ class RankCtx:
                 op: int = SUM, root: int = 0, scale: float = 1.0, algo: int = ALGO_AUTO, n_blocks: int = 0) -> None:
         info = CollInfo(kind, count, dtype, dtype if out_dtype is None else out_dtype, op, root, scale, algo, n_blocks)
         check(lib().dfcclPrepare(C.byref(info), comm.handle, coll_id, self.handle), f"dfcclPrepare({coll_id})")
+
+    def set_daemon_geometry(self, blocks: int = 0, threads: int = 0) -> None:
+        check(lib().dfcclSetDaemonGeometry(self.handle, blocks, threads), "dfcclSetDaemonGeometry")
 
     def finalize(self) -> None:
         check(lib().ofcclFinalizeRankCtx7StartHostThrds(self.handle), "ofcclFinalizeRankCtx7StartHostThrds")

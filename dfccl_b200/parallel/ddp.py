@@ -72,7 +72,8 @@ class DaemonDDP:
 
     def __init__(self, module: nn.Module, dist: Dist, *, bucket_mb: float = 25.0, lr: float = 0.1, momentum: float = 0.9,
                  weight_decay: float = 1e-4, randomize_order: bool = True, window: int = 2, seed: int = 0,
-                 coll_id_base: int = 0, comm: Optional[nv.Comm] = None, n_blocks: int = 0):
+                 coll_id_base: int = 0, comm: Optional[nv.Comm] = None, n_blocks: int = 0,
+                 daemon_blocks: int = 8, daemon_threads: int = 0):
         self.module = module
         self.dist = dist
         self.comm = comm or dist.comm
@@ -87,10 +88,14 @@ class DaemonDDP:
         self._ready: List[Bucket] = []
         self._submitted: List[Bucket] = []
         self._first_step = True
+        self.hooks_enabled = True               # switched off while a captured step runs (see graph.GraphedStep)
         self.launches = 0                       # kernels of this library launched by step()
         self.buckets: List[Bucket] = []
         self._build_buckets(int(bucket_mb * (1 << 20)))
         self.ctx = nv.RankCtx(dist.rank, dist.local_rank if self.device.type == "cuda" else -1)
+        # gradient buckets need a fraction of the fabric: a small grid leaves the SMs to the training kernels
+        if self.device.type == "cuda":
+            self.ctx.set_daemon_geometry(daemon_blocks, daemon_threads)
         for b in self.buckets:
             b.coll_id = coll_id_base + b.index
             self.ctx.prepare(b.coll_id, self.comm, nv.ALLREDUCE, b.numel, nccl_dtype(b.dtype), out_dtype=nv.FLOAT32,
@@ -136,6 +141,8 @@ class DaemonDDP:
 
     def _make_hook(self, b: Bucket):
         def hook(_param):
+            if not self.hooks_enabled:
+                return
             b.pending -= 1
             if b.pending == 0:
                 self._bucket_ready(b)
@@ -158,6 +165,15 @@ class DaemonDDP:
         for b in batch:
             self.ctx.run_on_stream(b.coll_id, b.grad.data_ptr(), b.grad32.data_ptr(), s)
             self._submitted.append(b)
+
+    def submit_all(self) -> None:
+        """Submit every bucket now (after a captured backward pass), in this rank's shuffled order."""
+        self._ready = [b for b in self.buckets if b not in self._submitted]
+        self._flush()
+
+    def zero_grads(self) -> None:
+        for b in self.buckets:
+            b.grad.zero_()
 
     def finish_backward(self) -> None:
         """Submit what is still queued and make the current stream wait for every bucket."""

@@ -1,0 +1,43 @@
+"""Whole-step CUDA graph: forward, loss and backward of a fixed-shape training step captured
+once and replayed, so that the several hundred short kernels of a step cost one launch.
+
+Works together with :class:`~dfccl_b200.parallel.ddp.DaemonDDP`: gradients are accumulated
+into the static, heap-resident bucket views (fixed addresses, so they can be captured),
+gradient hooks are switched off during capture and replay, and the buckets are submitted to
+the daemon right after the replay (``ddp.submit_all()``).
+"""
+from __future__ import annotations
+
+from typing import Callable
+
+import torch
+
+
+class GraphedStep:
+    def __init__(self, net: torch.nn.Module, loss_fn: Callable, ddp, x: torch.Tensor, y: torch.Tensor, warmup: int = 3):
+        self.ddp = ddp
+        self.x = x.clone()
+        self.y = y.clone()
+        dev = x.device
+        ddp.hooks_enabled = False
+        side = torch.cuda.Stream(device=dev)
+        side.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(side):
+            for _ in range(warmup):                   # cuDNN autotuning and allocator warm-up outside the capture
+                loss_fn(net(self.x), self.y).backward()
+        torch.cuda.current_stream(dev).wait_stream(side)
+        torch.cuda.synchronize(dev)
+        ddp.zero_grads()
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph):
+            self.loss = loss_fn(net(self.x), self.y)
+            self.loss.backward()
+        torch.cuda.synchronize(dev)
+        ddp.zero_grads()
+
+    def __call__(self, x: torch.Tensor, y: torch.Tensor) -> torch.Tensor:
+        self.x.copy_(x, non_blocking=True)
+        self.y.copy_(y, non_blocking=True)
+        self.graph.replay()
+        self.ddp.submit_all()
+        return self.loss
