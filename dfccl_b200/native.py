@@ -107,6 +107,7 @@ def lib() -> C.CDLL:
             "dfcclInjectFault": [vp, i, C.c_int64],
             "dfcclFusedSgdStep": [vp, vp, vp, vp, sz, i, C.c_float, C.c_float, C.c_float, i, vp],
             "dfcclOpsWarm": [],
+            "dfcclAllReduceNoAlloc": [vp, vp, sz, i, C.c_float, vp],
             "dfcclSetDaemonGeometry": [vp, i, i],
         }
         for name, args in sig.items():
