@@ -106,9 +106,9 @@ class ReferenceBackend:
             box = [None]
             if d.rank == 0:
                 self._check(L.ncclGetUniqueId(C.byref(uid)), "ncclGetUniqueId")
-                box = [bytes(uid.internal)]
+                box = [C.string_at(C.addressof(uid), 128)]
             dist.broadcast_object_list(box, src=0)
-            C.memmove(uid.internal, box[0], 128)
+            C.memmove(C.addressof(uid), box[0], 128)
         else:
             self._check(L.ncclGetUniqueId(C.byref(uid)), "ncclGetUniqueId")
         self.comm = vp()
@@ -164,9 +164,9 @@ class ReferenceBackend:
                 box = [None]
                 if self.d.rank == 0:
                     self._check(L.ncclGetUniqueId(C.byref(uid)), "ncclGetUniqueId")
-                    box = [bytes(uid.internal)]
+                    box = [C.string_at(C.addressof(uid), 128)]
                 dist.broadcast_object_list(box, src=0)
-                C.memmove(uid.internal, box[0], 128)
+                C.memmove(C.addressof(uid), box[0], 128)
             else:
                 self._check(L.ncclGetUniqueId(C.byref(uid)), "ncclGetUniqueId")
             c = vp()

@@ -142,7 +142,7 @@ def get_backend() -> str:
 def get_unique_id() -> bytes:
     uid = UniqueId()
     check(lib().ncclGetUniqueId(C.byref(uid)), "ncclGetUniqueId")
-    return bytes(uid.internal)
+    return C.string_at(C.addressof(uid), 128)       # the whole blob: the c_char field would stop at the first NUL
 
 
 class Comm:
@@ -155,7 +155,7 @@ class Comm:
     @staticmethod
     def init_rank(nranks: int, uid: bytes, rank: int) -> "Comm":
         u = UniqueId()
-        C.memmove(u.internal, uid, 128)
+        C.memmove(C.addressof(u), uid, 128)
         h = C.c_void_p()
         check(lib().ncclCommInitRank(C.byref(h), nranks, u, rank), "ncclCommInitRank")
         return Comm(h.value)

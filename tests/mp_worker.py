@@ -1,0 +1,180 @@
+"""Worker body for multi-process tests: one OS process per rank, rendezvous through this
+library's own TCP bootstrap (the unique id travels over a multiprocessing queue), memory
+shared through POSIX shm (host backend) or CUDA IPC (cuda backend)."""
+import ctypes as C
+import os
+import random
+import sys
+import traceback
+
+import numpy as np
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+
+
+def _view(nv, backend, ptr, n, npdt, tdt=None, dev=0):
+    if backend == "host":
+        from helpers import host_array
+        return host_array(ptr, n, npdt)
+    import torch
+    from dfccl_b200.utils import tensor_from_ptr
+    return tensor_from_ptr(ptr, (n,), tdt, f"cuda:{dev}")
+
+
+def worker(rank, world, backend, uid_q, res_q, scenario):
+    try:
+        os.environ.setdefault("DFCCL_WAIT_TIMEOUT_MS", "20000")
+        from dfccl_b200 import native as nv
+        nv.set_backend(backend)
+        if backend == "cuda":
+            import torch
+            torch.cuda.set_device(rank)
+        if rank == 0:
+            uid = nv.get_unique_id()
+            for _ in range(world - 1):
+                uid_q.put(uid)
+        else:
+            uid = uid_q.get(timeout=60)
+        comm = nv.Comm.init_rank(world, uid, rank)
+        assert comm.rank == rank and comm.nranks == world
+        out = globals()["scenario_" + scenario](nv, comm, rank, world, backend)
+        comm.destroy()
+        res_q.put((rank, "ok", out))
+    except BaseException:
+        res_q.put((rank, "fail", traceback.format_exc()))
+
+
+def _fill(v, value, backend):
+    if backend == "host":
+        v[:] = value
+    else:
+        v.fill_(value)
+
+
+def _all_equal(v, value, backend):
+    if backend == "host":
+        return bool(np.all(v == value))
+    return bool((v == value).all())
+
+
+def scenario_daemon(nv, comm, rank, world, backend):
+    """Register-then-submit across processes: mixed kinds, per-rank random order, several rounds."""
+    tdt = None
+    if backend == "cuda":
+        import torch
+        tdt = torch.float32
+    ncolls, iters = 12, 4
+    rng = random.Random(11)
+    kinds = [rng.choice([nv.ALLREDUCE, nv.ALLGATHER, nv.REDUCESCATTER, nv.BROADCAST, nv.REDUCE]) for _ in range(ncolls)]
+    counts = [rng.choice([32, 1000, 65536, 300001]) for _ in range(ncolls)]
+    ctx = nv.RankCtx(rank, rank if backend == "cuda" else -1)
+    bufs = []
+    for i in range(ncolls):
+        ctx.prepare(i, comm, kinds[i], counts[i], nv.FLOAT32, root=i % world)
+        sn = counts[i] * (world if kinds[i] == nv.REDUCESCATTER else 1)
+        rn = counts[i] * (world if kinds[i] == nv.ALLGATHER else 1)
+        sp, rp = comm.alloc(sn * 4), comm.alloc(rn * 4)
+        bufs.append((sp, rp, _view(nv, backend, sp, sn, np.float32, tdt, rank), _view(nv, backend, rp, rn, np.float32, tdt, rank)))
+    ctx.finalize()
+    orng = random.Random(1000 + rank)
+    for it in range(iters):
+        for i in range(ncolls):
+            _fill(bufs[i][2], float((rank + 1) * (i + 1) + it), backend)
+        if backend == "cuda":
+            import torch
+            torch.cuda.synchronize()
+        order = list(range(ncolls))
+        orng.shuffle(order)
+        for i in order:
+            ctx.run(i, bufs[i][0], bufs[i][1])
+        rc = ctx.wait_all(120000)
+        assert rc == nv.SUCCESS, rc
+        for i in range(ncolls):
+            vals = [float((q + 1) * (i + 1) + it) for q in range(world)]
+            out = bufs[i][3]
+            root = i % world
+            if kinds[i] in (nv.ALLREDUCE, nv.REDUCESCATTER):
+                assert _all_equal(out, sum(vals), backend), (i, kinds[i])
+            elif kinds[i] == nv.REDUCE:
+                if rank == root:
+                    assert _all_equal(out, sum(vals), backend), (i, "reduce")
+            elif kinds[i] == nv.BROADCAST:
+                assert _all_equal(out, vals[root], backend), (i, "bcast")
+            else:
+                for q in range(world):
+                    assert _all_equal(out[q * counts[i]:(q + 1) * counts[i]], vals[q], backend), (i, "ag", q)
+    st = ctx.stats()
+    ctx.destroy()
+    return st
+
+
+def scenario_stream(nv, comm, rank, world, backend):
+    """Stream-ordered nccl* interface across processes, plus send / recv."""
+    L = nv.lib()
+    vp = C.c_void_p
+    n = 100003
+    if backend == "cuda":
+        import torch
+        x = torch.full((n,), float(rank + 1), device=f"cuda:{rank}")
+        y = torch.zeros(n, device=f"cuda:{rank}")
+        st = vp(torch.cuda.current_stream().cuda_stream)
+        xp, yp = x.data_ptr(), y.data_ptr()
+        sync = torch.cuda.synchronize
+    else:
+        x = np.full(n, float(rank + 1), np.float32)
+        y = np.zeros(n, np.float32)
+        st, xp, yp, sync = None, x.ctypes.data, y.ctypes.data, (lambda: None)
+    tot = world * (world + 1) / 2
+    for _ in range(3):
+        nv.check(L.ncclAllReduce(vp(xp), vp(yp), n, nv.FLOAT32, nv.SUM, comm.handle, st))
+        sync()
+        assert _all_equal(y, tot, backend)
+    nv.check(L.ncclAllReduce(vp(yp), vp(yp), n, nv.FLOAT32, nv.AVG, comm.handle, st))   # in place
+    sync()
+    assert _all_equal(y, tot, backend)
+    nv.check(L.ncclBcast(vp(yp), n, nv.FLOAT32, world - 1, comm.handle, st))
+    sync()
+    # heap-resident buffers take the zero-copy path
+    hp = comm.alloc(4 * n)
+    hv = _view(nv, backend, hp, n, np.float32, None if backend == "host" else __import__("torch").float32, rank)
+    _fill(hv, float(rank), backend)
+    sync()
+    nv.check(L.ncclAllReduce(vp(hp), vp(hp), n, nv.FLOAT32, nv.MAX, comm.handle, st))
+    sync()
+    assert _all_equal(hv, world - 1, backend)
+    # ring send / recv
+    nxt, prv = (rank + 1) % world, (rank - 1) % world
+    _fill(x, float(rank), backend)
+    sync()
+    nv.check(L.ncclGroupStart())
+    nv.check(L.ncclSend(vp(xp), n, nv.FLOAT32, nxt, comm.handle, st))
+    nv.check(L.ncclRecv(vp(yp), n, nv.FLOAT32, prv, comm.handle, st))
+    nv.check(L.ncclGroupEnd())
+    sync()
+    assert _all_equal(y, prv, backend)
+    assert comm.async_error() == nv.SUCCESS
+    return {}
+
+
+def launch(world, backend, scenario, timeout=240):
+    """Spawn `world` ranks, return their results; raises on any failure or timeout."""
+    import multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    uid_q, res_q = ctx.Queue(), ctx.Queue()
+    procs = [ctx.Process(target=worker, args=(r, world, backend, uid_q, res_q, scenario), daemon=True) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = {}
+    try:
+        for _ in range(world):
+            r, status, payload = res_q.get(timeout=timeout)
+            if status != "ok":
+                raise AssertionError(f"rank {r} failed:\n{payload}")
+            results[r] = payload
+    finally:
+        for p in procs:
+            p.join(10)
+            if p.is_alive():
+                p.terminate()       # the exact children started above
+    return results

@@ -1,0 +1,31 @@
+"""One OS process per rank: TCP bootstrap with a unique id, peer memory across processes
+(POSIX shm on the host backend, CUDA IPC on GPUs), daemon and stream-ordered interfaces."""
+import pytest
+
+import mp_worker
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_host_processes_daemon(world):
+    res = mp_worker.launch(world, "host", "daemon")
+    assert all(s["cqesDelivered"] == 48 and s["waitTimeouts"] == 0 for s in res.values())
+
+
+def test_host_processes_stream_interface():
+    mp_worker.launch(3, "host", "stream")
+
+
+@pytest.mark.gpu
+@pytest.mark.multigpu
+def test_gpu_processes_daemon():
+    import torch
+    world = min(torch.cuda.device_count(), 4)
+    res = mp_worker.launch(world, "cuda", "daemon")
+    assert all(s["cqesDelivered"] == 48 for s in res.values())
+
+
+@pytest.mark.gpu
+@pytest.mark.multigpu
+def test_gpu_processes_stream_interface():
+    import torch
+    mp_worker.launch(min(torch.cuda.device_count(), 4), "cuda", "stream")
