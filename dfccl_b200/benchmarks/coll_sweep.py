@@ -2,7 +2,7 @@
 stream-ordered kernels) against NCCL as shipped with PyTorch, same buffers, same sizes.
 
     torchrun --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 -m dfccl_b200.benchmarks.coll_sweep \\
-        --kinds allreduce,allgather,reducescatter --dtypes bf16,fp32 --min 1024 --max 1073741824 --out sweep.json
+        --kinds allreduce,allgather,reducescatter --dtypes bf16,fp32 --min-bytes 1024 --max-bytes 1073741824 --out sweep.json
 
 Every number is device time (CUDA events on the launching stream, warm-up first, max over
 ranks).  Inputs are uniform(-1, 1) from a seed.  busBW follows the usual convention:
@@ -63,8 +63,8 @@ def main(argv=None):
     ap = argparse.ArgumentParser()
     ap.add_argument("--kinds", default="allreduce,allgather,reducescatter")
     ap.add_argument("--dtypes", default="bf16,fp32")
-    ap.add_argument("--min", type=int, default=1024)
-    ap.add_argument("--max", type=int, default=1 << 30)
+    ap.add_argument("--min-bytes", dest="min", type=int, default=1024)
+    ap.add_argument("--max-bytes", dest="max", type=int, default=1 << 30)
     ap.add_argument("--factor", type=int, default=4)
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
