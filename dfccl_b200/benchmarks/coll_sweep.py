@@ -70,6 +70,7 @@ def main(argv=None):
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--algo", default="auto", choices=["auto", "oneshot", "twoshot", "nvls"])
     ap.add_argument("--blocks", type=int, default=0, help="daemon blocks per rank (0 = default)")
+    ap.add_argument("--ids", type=int, default=4, help="registrations per case, used round-robin so that the host can enqueue ahead")
     ap.add_argument("--skip-nccl", action="store_true")
     ap.add_argument("--skip-stream-api", action="store_true")
     ap.add_argument("--out", default="")
@@ -102,7 +103,8 @@ def main(argv=None):
         count = total // world if k in ("allgather", "reducescatter") else total
         if count == 0:
             continue
-        ctx.prepare(cid, d.comm, KIND[k], count, ndt, algo=algo if k == "allreduce" else nv.ALGO_AUTO)
+        for j in range(a.ids):
+            ctx.prepare(cid * a.ids + j, d.comm, KIND[k], count, ndt, algo=algo if k == "allreduce" else nv.ALGO_AUTO)
         bufs[cid] = (count, total)
     ctx.finalize()
     stream = torch.cuda.current_stream()
@@ -121,9 +123,13 @@ def main(argv=None):
         torch.cuda.synchronize()
         iters = a.iters if sz <= (64 << 20) else max(3, a.iters // 4)
 
+        turn = [0]
+
         def daemon_op():
-            ctx.run_on_stream(cid, send_p, recv_p, stream.cuda_stream)
-            ctx.stream_wait(cid, stream.cuda_stream)
+            i = cid * a.ids + turn[0] % a.ids
+            turn[0] += 1
+            ctx.run_on_stream(i, send_p, recv_p, stream.cuda_stream)
+            ctx.stream_wait(i, stream.cuda_stream)
 
         row = {"kind": k, "dtype": dt, "bytes": sz, "n": world}
         us = time_loop(daemon_op, iters, a.warmup, world)

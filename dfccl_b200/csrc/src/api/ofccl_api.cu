@@ -315,7 +315,7 @@ DF_API ncclResult_t ofcclFinalizeRankCtx7StartHostThrds(ofcclRankCtx_t ctx) {
   rd.headTries = (uint32_t)std::max<int64_t>(1, paramI64("NUM_TRY_TASKQ_HEAD", 5));
   rd.recvSuccessFactor = (uint32_t)paramI64("RECV_SUCCESS_FACTOR", 5);
   const int64_t tolerant = paramI64("TOLERANT_UNPROGRESSED_CNT", 0);     // polls in the reference; here ~1 us each
-  rd.idleQuitNs = (uint64_t)paramI64("IDLE_QUIT_US", tolerant ? tolerant : 200) * 1000ull;
+  rd.idleQuitNs = (uint64_t)paramI64("IDLE_QUIT_US", tolerant ? tolerant : 1000) * 1000ull;
   rd.stallQuitNs = (uint64_t)paramI64("STALL_QUIT_US", tolerant ? tolerant : 5000) * 1000ull;
   rd.waitTimeoutNs = (uint64_t)paramI64("WAIT_TIMEOUT_MS", 0) * 1000000ull;
   rd.maxLifetimeNs = (uint64_t)paramI64("MAX_LIFETIME_MS", 2000) * 1000000ull;

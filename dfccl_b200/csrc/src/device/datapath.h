@@ -96,7 +96,7 @@ DF_HD_NOINLINE void reduce_copy(const DataArgs* a) {
   typedef typename Elem<Tin>::Acc A;
   constexpr int V = 16 / (int)sizeof(Tin);
   constexpr int OUTB = V * (int)sizeof(Tout);
-  constexpr int U = sizeof(Tin) >= 4 ? 4 : 2;
+  constexpr int U = 4;
   const int tid = df_tid(), nt = df_nthreads();
   const int nsrc = a->nsrc, ndst = a->ndst;
   const uint64_t n = a->n;
@@ -108,30 +108,33 @@ DF_HD_NOINLINE void reduce_copy(const DataArgs* a) {
   for (int j = 0; j < ndst; ++j) aligned &= ((uintptr_t)a->dst[j] & (OUTB >= 16 ? 15 : OUTB - 1)) == 0;
   const uint64_t nPacks = aligned ? n / V : 0;
 
+  // Software-pipelined over the sources: the U loads of source j+1 are issued before the U packs of
+  // source j are consumed, so 2*U 16-byte loads (128 B .. 256 B) are in flight per thread - what it
+  // takes to cover the round trip of a load from a peer's memory over NVLink.
   for (uint64_t base = 0; base < nPacks; base += (uint64_t)nt * U) {
     A acc[U][V];
     uint64_t idx[U];
+    uint4 cur[U], nxt[U];
 #pragma unroll
     for (int u = 0; u < U; ++u) {
       idx[u] = base + (uint64_t)u * nt + tid;
-      if (idx[u] < nPacks) {
-        uint4 raw = ld16(a->src[0] + idx[u] * 16);
-        Tin e[V];
-        __builtin_memcpy(e, &raw, 16);          // bit copy, not a pointer cast: host compilers enforce strict aliasing
-#pragma unroll
-        for (int k = 0; k < V; ++k) acc[u][k] = Elem<Tin>::up(e[k]);
-      }
+      if (idx[u] < nPacks) cur[u] = ld16(a->src[0] + idx[u] * 16);
     }
-    for (int j = 1; j < nsrc; ++j) {
-      uint4 raw[U];
+    for (int j = 1; j <= nsrc; ++j) {
+      if (j < nsrc) {
 #pragma unroll
-      for (int u = 0; u < U; ++u) if (idx[u] < nPacks) raw[u] = ld16(a->src[j] + idx[u] * 16);
+        for (int u = 0; u < U; ++u) if (idx[u] < nPacks) nxt[u] = ld16(a->src[j] + idx[u] * 16);
+      }
 #pragma unroll
       for (int u = 0; u < U; ++u) if (idx[u] < nPacks) {
         Tin e[V];
-        __builtin_memcpy(e, &raw[u], 16);
+        __builtin_memcpy(e, &cur[u], 16);          // bit copy, not a pointer cast: host compilers enforce strict aliasing
 #pragma unroll
-        for (int k = 0; k < V; ++k) acc[u][k] = red<OP>(acc[u][k], Elem<Tin>::up(e[k]));
+        for (int k = 0; k < V; ++k) acc[u][k] = j == 1 ? Elem<Tin>::up(e[k]) : red<OP>(acc[u][k], Elem<Tin>::up(e[k]));
+      }
+      if (j < nsrc) {
+#pragma unroll
+        for (int u = 0; u < U; ++u) cur[u] = nxt[u];
       }
     }
 #pragma unroll
