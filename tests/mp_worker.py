@@ -104,6 +104,8 @@ def scenario_daemon(nv, comm, rank, world, backend):
             else:
                 for q in range(world):
                     assert _all_equal(out[q * counts[i]:(q + 1) * counts[i]], vals[q], backend), (i, "ag", q)
+    import time
+    time.sleep(0.05)
     st = ctx.stats()
     ctx.destroy()
     return st

@@ -72,6 +72,7 @@ def test_disordered_issue_completes_and_preempts(host_backend):
                     assert np.all(out.reshape(nranks, -1) == np.array(vals, np.float32)[:, None])
                 else:
                     assert np.all(out == vals[i % nranks])
+        time.sleep(0.05)                           # device counters are folded in when the daemon parks
         stats[r] = ctx.stats()
         ctx.destroy()
 
@@ -102,6 +103,7 @@ def test_voluntary_quit_and_relaunch(host_backend):
             assert ctx.wait(0, 20000) == nv.SUCCESS
             assert np.all(v == 2.0)
             time.sleep(0.05)             # far longer than the idle limit: the daemon leaves in between
+        time.sleep(0.05)
         seen[r] = ctx.stats()
         ctx.destroy()
 
@@ -133,6 +135,7 @@ def test_bounded_wait_reports_timeout_instead_of_hanging(host_backend):
             out["dt"] = time.time() - t0
             out["fired"] = fired
             out["async"] = ctx.async_error()
+            time.sleep(0.05)                       # device counters are folded in when the daemon parks
             out["stats"] = ctx.stats()
             gate.set()
         else:
