@@ -107,6 +107,8 @@ def lib() -> C.CDLL:
             "dfcclInjectFault": [vp, i, C.c_int64],
             "dfcclFusedSgdStep": [vp, vp, vp, vp, sz, i, C.c_float, C.c_float, C.c_float, i, vp],
             "dfcclOpsWarm": [],
+            "dfcclProbePeerCopy": [vp, i, sz, i, i, i, i, i, C.POINTER(C.c_double)],
+            "dfcclProbeFlagRoundTrip": [vp, i, i, C.POINTER(C.c_double)],
             "dfcclAllReduceNoAlloc": [vp, vp, sz, i, C.c_float, vp],
             "dfcclSetDaemonGeometry": [vp, i, i],
         }
