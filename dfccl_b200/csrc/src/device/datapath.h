@@ -78,16 +78,77 @@ DF_HD typename Elem<Tout>::Acc finish(A a, double scale, int postDiv) {
   return (AO)a;
 }
 
-template <int BYTES> struct Pack;
-template <> struct Pack<16> { uint4 v; static DF_HD void st(void* p, const Pack& k) { st16(p, k.v); } };
-template <> struct Pack<32> { uint4 v[2]; static DF_HD void st(void* p, const Pack& k) { st16(p, k.v[0]); st16((char*)p + 16, k.v[1]); } };
-template <> struct Pack<8> { uint2 v; static DF_HD void st(void* p, const Pack& k) {
+DF_HD void st8(void* p, uint2 v) {
 #if DF_DEVICE_CODE
-  asm volatile("st.relaxed.sys.global.v2.u32 [%0], {%1,%2};" ::"l"(p), "r"(k.v.x), "r"(k.v.y) : "memory");
+  asm volatile("st.relaxed.sys.global.v2.u32 [%0], {%1,%2};" ::"l"(p), "r"(v.x), "r"(v.y) : "memory");
 #else
-  __builtin_memcpy(p, &k.v, 8);
+  __builtin_memcpy(p, &v, 8);
 #endif
-} };
+}
+
+// ---- 16-byte pack <-> V accumulators, in registers only on the device.  (Going through a local
+// array and memcpy is what the host build does; on the device an address-taken array can end up in
+// local memory, and a load whose result is stored right away cannot overlap with the next load.)
+DF_HD uint32_t packWord(const uint4& v, int i) { return i == 0 ? v.x : i == 1 ? v.y : i == 2 ? v.z : v.w; }
+DF_HD void setWord(uint4& v, int i, uint32_t w) { if (i == 0) v.x = w; else if (i == 1) v.y = w; else if (i == 2) v.z = w; else v.w = w; }
+
+template <typename T> struct Lane;     // element k of a 16-byte pack <-> accumulator
+#if DF_DEVICE_CODE
+template <> struct Lane<float> {
+  static DF_HD float get(const uint4& v, int k) { return __uint_as_float(packWord(v, k)); }
+  static DF_HD void put(uint4& v, int k, float a) { setWord(v, k, __float_as_uint(a)); }
+};
+template <> struct Lane<int32_t> {
+  static DF_HD int32_t get(const uint4& v, int k) { return (int32_t)packWord(v, k); }
+  static DF_HD void put(uint4& v, int k, int32_t a) { setWord(v, k, (uint32_t)a); }
+};
+template <> struct Lane<uint32_t> {
+  static DF_HD uint32_t get(const uint4& v, int k) { return packWord(v, k); }
+  static DF_HD void put(uint4& v, int k, uint32_t a) { setWord(v, k, a); }
+};
+template <> struct Lane<__nv_bfloat16> {
+  static DF_HD float get(const uint4& v, int k) { uint32_t w = packWord(v, k >> 1); return __uint_as_float((k & 1) ? (w & 0xffff0000u) : (w << 16)); }
+  static DF_HD void put(uint4& v, int k, float a) {
+    uint32_t h = (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(a));
+    uint32_t w = packWord(v, k >> 1);
+    setWord(v, k >> 1, (k & 1) ? ((w & 0x0000ffffu) | (h << 16)) : ((w & 0xffff0000u) | h));
+  }
+};
+template <> struct Lane<__half> {
+  static DF_HD float get(const uint4& v, int k) { uint32_t w = packWord(v, k >> 1); return __half2float(__ushort_as_half((unsigned short)((k & 1) ? (w >> 16) : (w & 0xffffu)))); }
+  static DF_HD void put(uint4& v, int k, float a) {
+    uint32_t h = (uint32_t)__half_as_ushort(__float2half_rn(a));
+    uint32_t w = packWord(v, k >> 1);
+    setWord(v, k >> 1, (k & 1) ? ((w & 0x0000ffffu) | (h << 16)) : ((w & 0xffff0000u) | h));
+  }
+};
+template <> struct Lane<int8_t> {
+  static DF_HD int32_t get(const uint4& v, int k) { return (int32_t)(int8_t)(packWord(v, k >> 2) >> (8 * (k & 3))); }
+  static DF_HD void put(uint4& v, int k, int32_t a) { uint32_t sh = 8 * (k & 3), w = packWord(v, k >> 2); setWord(v, k >> 2, (w & ~(0xffu << sh)) | (((uint32_t)a & 0xffu) << sh)); }
+};
+template <> struct Lane<uint8_t> {
+  static DF_HD uint32_t get(const uint4& v, int k) { return (packWord(v, k >> 2) >> (8 * (k & 3))) & 0xffu; }
+  static DF_HD void put(uint4& v, int k, uint32_t a) { uint32_t sh = 8 * (k & 3), w = packWord(v, k >> 2); setWord(v, k >> 2, (w & ~(0xffu << sh)) | ((a & 0xffu) << sh)); }
+};
+template <> struct Lane<double> {
+  static DF_HD double get(const uint4& v, int k) { return __hiloint2double((int)packWord(v, 2 * k + 1), (int)packWord(v, 2 * k)); }
+  static DF_HD void put(uint4& v, int k, double a) { setWord(v, 2 * k, (uint32_t)__double2loint(a)); setWord(v, 2 * k + 1, (uint32_t)__double2hiint(a)); }
+};
+template <> struct Lane<int64_t> {
+  static DF_HD int64_t get(const uint4& v, int k) { return (int64_t)(((uint64_t)packWord(v, 2 * k + 1) << 32) | packWord(v, 2 * k)); }
+  static DF_HD void put(uint4& v, int k, int64_t a) { setWord(v, 2 * k, (uint32_t)(uint64_t)a); setWord(v, 2 * k + 1, (uint32_t)((uint64_t)a >> 32)); }
+};
+template <> struct Lane<uint64_t> {
+  static DF_HD uint64_t get(const uint4& v, int k) { return ((uint64_t)packWord(v, 2 * k + 1) << 32) | packWord(v, 2 * k); }
+  static DF_HD void put(uint4& v, int k, uint64_t a) { setWord(v, 2 * k, (uint32_t)a); setWord(v, 2 * k + 1, (uint32_t)(a >> 32)); }
+};
+#else
+template <typename T> struct Lane {
+  typedef typename Elem<T>::Acc A;
+  static A get(const uint4& v, int k) { T e; __builtin_memcpy(&e, (const char*)&v + k * sizeof(T), sizeof(T)); return Elem<T>::up(e); }
+  static void put(uint4& v, int k, A a) { T e = Elem<T>::down(a); __builtin_memcpy((char*)&v + k * sizeof(T), &e, sizeof(T)); }
+};
+#endif
 
 // One noinline body per (input type, output type, operator): the daemon's register
 // budget is the maximum over what it inlines, so the variants stay out of line.
@@ -127,10 +188,8 @@ DF_HD_NOINLINE void reduce_copy(const DataArgs* a) {
       }
 #pragma unroll
       for (int u = 0; u < U; ++u) if (idx[u] < nPacks) {
-        Tin e[V];
-        __builtin_memcpy(e, &cur[u], 16);          // bit copy, not a pointer cast: host compilers enforce strict aliasing
 #pragma unroll
-        for (int k = 0; k < V; ++k) acc[u][k] = j == 1 ? Elem<Tin>::up(e[k]) : red<OP>(acc[u][k], Elem<Tin>::up(e[k]));
+        for (int k = 0; k < V; ++k) acc[u][k] = j == 1 ? (A)Lane<Tin>::get(cur[u], k) : red<OP>(acc[u][k], (A)Lane<Tin>::get(cur[u], k));
       }
       if (j < nsrc) {
 #pragma unroll
@@ -139,12 +198,20 @@ DF_HD_NOINLINE void reduce_copy(const DataArgs* a) {
     }
 #pragma unroll
     for (int u = 0; u < U; ++u) if (idx[u] < nPacks) {
-      Pack<OUTB> out;
-      Tout o[V];
+      constexpr int VO = 16 / (int)sizeof(Tout);          // elements per 16-byte output word group
+      uint4 ow[(OUTB + 15) / 16];
 #pragma unroll
-      for (int k = 0; k < V; ++k) o[k] = Elem<Tout>::down(finish<Tin, Tout>(acc[u][k], scale, postDiv));
-      __builtin_memcpy(&out, o, OUTB);
-      for (int d = 0; d < ndst; ++d) Pack<OUTB>::st(a->dst[d] + idx[u] * OUTB, out);
+      for (int w = 0; w < (OUTB + 15) / 16; ++w) ow[w] = make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+      for (int k = 0; k < V; ++k) Lane<Tout>::put(ow[k / VO], k % VO, finish<Tin, Tout>(acc[u][k], scale, postDiv));
+      for (int d = 0; d < ndst; ++d) {
+        char* o = a->dst[d] + idx[u] * OUTB;
+        if (OUTB == 8) st8(o, make_uint2(ow[0].x, ow[0].y));
+        else {
+#pragma unroll
+          for (int w = 0; w < OUTB / 16; ++w) st16(o + 16 * w, ow[w]);
+        }
+      }
     }
   }
   // ragged tail, or everything when a pointer is not 16-byte aligned
