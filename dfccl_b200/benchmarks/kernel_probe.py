@@ -3,7 +3,7 @@ kernel on a one-rank communicator (reduce / scale / cast data path over heap buf
 wait for) and the fused optimizer kernel.  Sized above the L2 capacity, a few launches, so that a
 profiler capture ends by itself.
 
-    python -m dfccl_b200.benchmarks.kernel_probe --mbytes 512 --iters 3
+    python -m dfccl_b200.benchmarks.kernel_probe --mbytes 256 --iters 3
 """
 from __future__ import annotations
 
@@ -19,7 +19,7 @@ from dfccl_b200.utils import tensor_from_ptr
 
 def main(argv=None):
     ap = argparse.ArgumentParser()
-    ap.add_argument("--mbytes", type=int, default=512)
+    ap.add_argument("--mbytes", type=int, default=256)
     ap.add_argument("--iters", type=int, default=3)
     a = ap.parse_args(argv)
     torch.cuda.set_device(0)
