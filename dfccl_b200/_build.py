@@ -26,7 +26,7 @@ SOURCES = [
     "src/common/log.cc", "src/common/param.cc", "src/common/socket.cc",
     "src/bootstrap/bootstrap.cc",
     "src/mem/heap.cu", "src/topo/topo.cu",
-    "src/daemon/daemon.cu", "src/daemon/standalone.cu", "src/daemon/daemon_host.cu",
+    "src/device/datapath.cu", "src/daemon/daemon.cu", "src/daemon/standalone.cu", "src/daemon/daemon_host.cu",
     "src/comm/comm.cu",
     "src/api/nccl_api.cu", "src/api/p2p.cu", "src/api/ofccl_api.cu", "src/api/debug_api.cu",
     "src/ops/optim.cu", "src/api/noalloc.cu", "src/api/probe.cu",
@@ -44,7 +44,7 @@ def nvcc() -> str:
 
 def _flags(verbose: bool) -> list:
     f = ["-std=c++17", "-O3", "-lineinfo", "-Xcompiler", "-fPIC,-fvisibility=hidden,-Wall,-Wno-unused-function",
-         "-I", str(CSRC / "include"), "-Wno-deprecated-gpu-targets", "-x", "cu"] + ARCH
+         "-I", str(CSRC / "include"), "-Wno-deprecated-gpu-targets", "-x", "cu", "-rdc=true"] + ARCH
     if os.environ.get("DFCCL_FAST_BUILD") == "1":
         f.append("-DDF_FAST_BUILD")
     if verbose:
@@ -61,7 +61,12 @@ def _compile(src: str, verbose: bool, hdr_time: float) -> Path:
     o = OBJ / (src.replace("/", "_") + (".fast.o" if os.environ.get("DFCCL_FAST_BUILD") == "1" else ".o"))
     if o.exists() and o.stat().st_mtime > max(s.stat().st_mtime, hdr_time):
         return o
-    cmd = [nvcc()] + _flags(verbose) + ["-c", str(s), "-o", str(o)]
+    extra = []
+    if src.endswith("device/datapath.cu"):
+        # out-of-line device functions do not inherit a kernel's launch bounds: cap them at what
+        # a 512-thread block leaves per thread (the reference caps its device code the same way)
+        extra = ["-maxrregcount=128"]
+    cmd = [nvcc()] + _flags(verbose) + extra + ["-c", str(s), "-o", str(o)]
     r = subprocess.run(cmd, capture_output=True, text=True)
     if r.returncode != 0:
         raise RuntimeError(f"nvcc failed for {src}:\n{r.stdout}\n{r.stderr}")
@@ -83,7 +88,7 @@ def build(verbose: bool = False, force: bool = False, extra_sources=()) -> Path:
         objs = list(ex.map(lambda s: _compile(s, verbose, hdr), srcs))
     if LIB.exists() and all(LIB.stat().st_mtime > o.stat().st_mtime for o in objs):
         return LIB
-    cmd = [nvcc(), "-shared", "-o", str(LIB)] + [str(o) for o in objs] + ARCH + ["-lrt", "-lpthread", "-ldl", "-cudart", "static"]
+    cmd = [nvcc(), "-shared", "-rdc=true", "-Xcompiler", "-fPIC", "-o", str(LIB)] + [str(o) for o in objs] + ARCH + ["-lrt", "-lpthread", "-ldl", "-cudart", "static"]
     r = subprocess.run(cmd, capture_output=True, text=True)
     if r.returncode != 0:
         raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")

@@ -50,13 +50,13 @@ template <typename T> DF_HD void st_elem(T* p, T v) {
 }
 
 // accumulator type and conversions
-template <typename T> struct Elem { typedef T Acc; static DF_HD Acc up(T v) { return v; } static DF_HD T down(Acc a) { return a; } enum { isFloat = 0 }; };
-template <> struct Elem<int8_t> { typedef int32_t Acc; static DF_HD Acc up(int8_t v) { return v; } static DF_HD int8_t down(Acc a) { return (int8_t)a; } enum { isFloat = 0 }; };
-template <> struct Elem<uint8_t> { typedef uint32_t Acc; static DF_HD Acc up(uint8_t v) { return v; } static DF_HD uint8_t down(Acc a) { return (uint8_t)a; } enum { isFloat = 0 }; };
-template <> struct Elem<float> { typedef float Acc; static DF_HD Acc up(float v) { return v; } static DF_HD float down(Acc a) { return a; } enum { isFloat = 1 }; };
-template <> struct Elem<double> { typedef double Acc; static DF_HD Acc up(double v) { return v; } static DF_HD double down(Acc a) { return a; } enum { isFloat = 1 }; };
-template <> struct Elem<__half> { typedef float Acc; static DF_HD Acc up(__half v) { return __half2float(v); } static DF_HD __half down(Acc a) { return __float2half_rn(a); } enum { isFloat = 1 }; };
-template <> struct Elem<__nv_bfloat16> { typedef float Acc; static DF_HD Acc up(__nv_bfloat16 v) { return __bfloat162float(v); } static DF_HD __nv_bfloat16 down(Acc a) { return __float2bfloat16_rn(a); } enum { isFloat = 1 }; };
+template <typename T> struct Elem { typedef T Acc; static DF_HD Acc up(T v) { return v; } static DF_HD T down(Acc a) { return a; } enum { isFloat = 0, isBf16 = 0 }; };
+template <> struct Elem<int8_t> { typedef int32_t Acc; static DF_HD Acc up(int8_t v) { return v; } static DF_HD int8_t down(Acc a) { return (int8_t)a; } enum { isFloat = 0, isBf16 = 0 }; };
+template <> struct Elem<uint8_t> { typedef uint32_t Acc; static DF_HD Acc up(uint8_t v) { return v; } static DF_HD uint8_t down(Acc a) { return (uint8_t)a; } enum { isFloat = 0, isBf16 = 0 }; };
+template <> struct Elem<float> { typedef float Acc; static DF_HD Acc up(float v) { return v; } static DF_HD float down(Acc a) { return a; } enum { isFloat = 1, isBf16 = 0 }; };
+template <> struct Elem<double> { typedef double Acc; static DF_HD Acc up(double v) { return v; } static DF_HD double down(Acc a) { return a; } enum { isFloat = 1, isBf16 = 0 }; };
+template <> struct Elem<__half> { typedef float Acc; static DF_HD Acc up(__half v) { return __half2float(v); } static DF_HD __half down(Acc a) { return __float2half_rn(a); } enum { isFloat = 1, isBf16 = 0 }; };
+template <> struct Elem<__nv_bfloat16> { typedef float Acc; static DF_HD Acc up(__nv_bfloat16 v) { return __bfloat162float(v); } static DF_HD __nv_bfloat16 down(Acc a) { return __float2bfloat16_rn(a); } enum { isFloat = 1, isBf16 = 1 }; };
 
 template <int OP, typename A> DF_HD A red(A a, A b) {
   if (OP == OP_SUM) return a + b;
@@ -150,72 +150,129 @@ template <typename T> struct Lane {
 };
 #endif
 
+// ---- whole-pack conversions: V accumulators <-> 16-byte words, few instructions per element
+template <typename Tout, typename A, int V>
+DF_HD void packAll(uint4* ow, const A* r) {
+#if DF_DEVICE_CODE
+  if (sizeof(Tout) == 2 && sizeof(A) == 4) {            // bf16 / fp16 from fp32: one convert per pair
+#pragma unroll
+    for (int k = 0; k < V; k += 2) {
+      uint32_t word;
+      if (Elem<Tout>::isBf16) { __nv_bfloat162 h = __floats2bfloat162_rn((float)r[k], (float)r[k + 1]); word = *reinterpret_cast<uint32_t*>(&h); }
+      else { __half2 h = __floats2half2_rn((float)r[k], (float)r[k + 1]); word = *reinterpret_cast<uint32_t*>(&h); }
+      setWord(ow[(k / 2) / 4], (k / 2) % 4, word);
+    }
+    return;
+  }
+#endif
+  constexpr int VO = 16 / (int)sizeof(Tout);
+#pragma unroll
+  for (int k = 0; k < V; ++k) Lane<Tout>::put(ow[k / VO], k % VO, (typename Elem<Tout>::Acc)r[k]);
+}
+
 // One noinline body per (input type, output type, operator): the daemon's register
 // budget is the maximum over what it inlines, so the variants stay out of line.
+// The hot loop is written for instruction count (it was issue-bound at 150 warp instructions
+// per 16-byte pack in its first form): pointers are read from shared memory once per source
+// and trip, indices are a base plus compile-time multiples of the stride, the bounds test is
+// hoisted out of full trips, the scale is a float decided once, outputs are packed pairwise.
+template <typename Tin, typename Tout, int OP, bool FULL, int U>
+DF_HD void reduceTrip(const DataArgs* a, uint64_t p0, uint64_t nPacks, uint32_t strideB, int nsrc, int ndst,
+                      typename Elem<Tin>::Acc mul, bool doMul, int postDiv, double dscale) {
+  typedef typename Elem<Tin>::Acc A;
+  constexpr int V = 16 / (int)sizeof(Tin);
+  constexpr int OUTB = V * (int)sizeof(Tout);
+  constexpr int NW = (OUTB + 15) / 16;
+  const uint32_t stride = strideB >> 4;
+  const uint64_t off = p0 * 16;
+  A acc[U][V];
+  uint4 cur[U], nxt[U];
+  {
+    const char* s0 = a->src[0] + off;
+#pragma unroll
+    for (int u = 0; u < U; ++u) if (FULL || p0 + (uint64_t)u * stride < nPacks) cur[u] = ld16(s0 + (uint64_t)u * strideB);
+  }
+  for (int j = 1; j <= nsrc; ++j) {
+    if (j < nsrc) {
+      const char* sj = a->src[j] + off;
+#pragma unroll
+      for (int u = 0; u < U; ++u) if (FULL || p0 + (uint64_t)u * stride < nPacks) nxt[u] = ld16(sj + (uint64_t)u * strideB);
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+#pragma unroll
+      for (int k = 0; k < V; ++k) {
+        const A e = (A)Lane<Tin>::get(cur[u], k);
+        acc[u][k] = j == 1 ? e : red<OP>(acc[u][k], e);
+      }
+    }
+    if (j < nsrc) {
+#pragma unroll
+      for (int u = 0; u < U; ++u) cur[u] = nxt[u];
+    }
+  }
+  uint4 ow[U][NW];
+#pragma unroll
+  for (int u = 0; u < U; ++u) {
+    if (Elem<Tin>::isFloat) {
+      if (doMul) {
+#pragma unroll
+        for (int k = 0; k < V; ++k) acc[u][k] = acc[u][k] * mul;
+      }
+    } else if (postDiv) {
+#pragma unroll
+      for (int k = 0; k < V; ++k) acc[u][k] = acc[u][k] / (A)postDiv;
+    } else if (doMul) {
+#pragma unroll
+      for (int k = 0; k < V; ++k) acc[u][k] = (A)((double)acc[u][k] * dscale);
+    }
+#pragma unroll
+    for (int w = 0; w < NW; ++w) ow[u][w] = make_uint4(0u, 0u, 0u, 0u);
+    packAll<Tout, A, V>(ow[u], acc[u]);
+  }
+  for (int d = 0; d < ndst; ++d) {
+    char* o = a->dst[d] + p0 * OUTB;
+#pragma unroll
+    for (int u = 0; u < U; ++u) if (FULL || p0 + (uint64_t)u * stride < nPacks) {
+      char* ou = o + (uint64_t)u * stride * OUTB;
+      if (OUTB == 8) st8(ou, make_uint2(ow[u][0].x, ow[u][0].y));
+      else {
+#pragma unroll
+        for (int w = 0; w < OUTB / 16; ++w) st16(ou + 16 * w, ow[u][w]);
+      }
+    }
+  }
+}
+
 template <typename Tin, typename Tout, int OP>
 DF_HD_NOINLINE void reduce_copy(const DataArgs* a) {
   typedef typename Elem<Tin>::Acc A;
   constexpr int V = 16 / (int)sizeof(Tin);
   constexpr int OUTB = V * (int)sizeof(Tout);
-  constexpr int U = 4;
+  constexpr int U = OP == OP_SUM ? 4 : 2;     // the sum carries the traffic; the rarer operators trade speed for code size
   const int tid = df_tid(), nt = df_nthreads();
   const int nsrc = a->nsrc, ndst = a->ndst;
   const uint64_t n = a->n;
   const double scale = a->scale;
   const int postDiv = a->postDiv;
+  const bool doMul = scale != 1.0;
+  const A mul = (A)scale;
 
   bool aligned = true;
   for (int j = 0; j < nsrc; ++j) aligned &= ((uintptr_t)a->src[j] & 15) == 0;
   for (int j = 0; j < ndst; ++j) aligned &= ((uintptr_t)a->dst[j] & (OUTB >= 16 ? 15 : OUTB - 1)) == 0;
   const uint64_t nPacks = aligned ? n / V : 0;
 
-  // Software-pipelined over the sources: the U loads of source j+1 are issued before the U packs of
-  // source j are consumed, so 2*U 16-byte loads (128 B .. 256 B) are in flight per thread - what it
-  // takes to cover the round trip of a load from a peer's memory over NVLink.
-  for (uint64_t base = 0; base < nPacks; base += (uint64_t)nt * U) {
-    A acc[U][V];
-    uint64_t idx[U];
-    uint4 cur[U], nxt[U];
-#pragma unroll
-    for (int u = 0; u < U; ++u) {
-      idx[u] = base + (uint64_t)u * nt + tid;
-      if (idx[u] < nPacks) cur[u] = ld16(a->src[0] + idx[u] * 16);
-    }
-    for (int j = 1; j <= nsrc; ++j) {
-      if (j < nsrc) {
-#pragma unroll
-        for (int u = 0; u < U; ++u) if (idx[u] < nPacks) nxt[u] = ld16(a->src[j] + idx[u] * 16);
-      }
-#pragma unroll
-      for (int u = 0; u < U; ++u) if (idx[u] < nPacks) {
-#pragma unroll
-        for (int k = 0; k < V; ++k) acc[u][k] = j == 1 ? (A)Lane<Tin>::get(cur[u], k) : red<OP>(acc[u][k], (A)Lane<Tin>::get(cur[u], k));
-      }
-      if (j < nsrc) {
-#pragma unroll
-        for (int u = 0; u < U; ++u) cur[u] = nxt[u];
-      }
-    }
-#pragma unroll
-    for (int u = 0; u < U; ++u) if (idx[u] < nPacks) {
-      constexpr int VO = 16 / (int)sizeof(Tout);          // elements per 16-byte output word group
-      uint4 ow[(OUTB + 15) / 16];
-#pragma unroll
-      for (int w = 0; w < (OUTB + 15) / 16; ++w) ow[w] = make_uint4(0u, 0u, 0u, 0u);
-#pragma unroll
-      for (int k = 0; k < V; ++k) Lane<Tout>::put(ow[k / VO], k % VO, finish<Tin, Tout>(acc[u][k], scale, postDiv));
-      for (int d = 0; d < ndst; ++d) {
-        char* o = a->dst[d] + idx[u] * OUTB;
-        if (OUTB == 8) st8(o, make_uint2(ow[0].x, ow[0].y));
-        else {
-#pragma unroll
-          for (int w = 0; w < OUTB / 16; ++w) st16(o + 16 * w, ow[w]);
-        }
-      }
-    }
-  }
-  // ragged tail, or everything when a pointer is not 16-byte aligned
-  for (uint64_t i = nPacks * V + tid; i < n; i += nt) {
+  // Software-pipelined over the sources inside a trip: the U loads of source j+1 are issued before
+  // the U packs of source j are consumed, so up to 2*U 16-byte loads are in flight per thread.
+  const uint64_t step = (uint64_t)nt * U;
+  const uint32_t strideB = (uint32_t)nt * 16u;
+  uint64_t base = 0;
+  for (; base + step <= nPacks; base += step)
+    reduceTrip<Tin, Tout, OP, true, U>(a, base + tid, nPacks, strideB, nsrc, ndst, mul, doMul, postDiv, scale);
+  // what full trips leave (less than one trip of packs), the ragged tail, or everything when a
+  // pointer is not 16-byte aligned: element by element
+  for (uint64_t i = base * V + tid; i < n; i += nt) {
     A acc = Elem<Tin>::up(ld_elem((const Tin*)a->src[0] + i));
     for (int j = 1; j < nsrc; ++j) acc = red<OP>(acc, Elem<Tin>::up(ld_elem((const Tin*)a->src[j] + i)));
     Tout o = Elem<Tout>::down(finish<Tin, Tout>(acc, scale, postDiv));
@@ -224,7 +281,22 @@ DF_HD_NOINLINE void reduce_copy(const DataArgs* a) {
 }
 
 // Byte copy of one source to M destinations (AllGather, Broadcast, staging).
-static DF_HD_NOINLINE void copy_multi(const DataArgs* a) {
+template <bool FULL, int U>
+DF_HD void copyTrip(const DataArgs* a, uint64_t p0, uint64_t nPacks, uint32_t strideB, int ndst) {
+  const uint32_t stride = strideB >> 4;
+  const char* s0 = a->src[0] + p0 * 16;
+  uint4 raw[U];
+#pragma unroll
+  for (int u = 0; u < U; ++u) if (FULL || p0 + (uint64_t)u * stride < nPacks) raw[u] = ld16(s0 + (uint64_t)u * strideB);
+  for (int d = 0; d < ndst; ++d) {
+    char* o = a->dst[d] + p0 * 16;
+#pragma unroll
+    for (int u = 0; u < U; ++u) if (FULL || p0 + (uint64_t)u * stride < nPacks) st16(o + (uint64_t)u * strideB, raw[u]);
+  }
+}
+
+#ifdef DF_DATAPATH_IMPL
+__host__ __device__ void copy_multi(const DataArgs* a) {
   constexpr int U = 8;
   const int tid = df_tid(), nt = df_nthreads();
   const int ndst = a->ndst;
@@ -232,20 +304,19 @@ static DF_HD_NOINLINE void copy_multi(const DataArgs* a) {
   bool aligned = ((uintptr_t)a->src[0] & 15) == 0;
   for (int j = 0; j < ndst; ++j) aligned &= ((uintptr_t)a->dst[j] & 15) == 0;
   const uint64_t nPacks = aligned ? nbytes / 16 : 0;
-  for (uint64_t base = 0; base < nPacks; base += (uint64_t)nt * U) {
-    uint4 raw[U];
-#pragma unroll
-    for (int u = 0; u < U; ++u) { uint64_t i = base + (uint64_t)u * nt + tid; if (i < nPacks) raw[u] = ld16(a->src[0] + i * 16); }
-    for (int d = 0; d < ndst; ++d) {
-#pragma unroll
-      for (int u = 0; u < U; ++u) { uint64_t i = base + (uint64_t)u * nt + tid; if (i < nPacks) st16(a->dst[d] + i * 16, raw[u]); }
-    }
-  }
-  for (uint64_t i = nPacks * 16 + tid; i < nbytes; i += nt) {
+  const uint64_t step = (uint64_t)nt * U;
+  const uint32_t strideB = (uint32_t)nt * 16u;
+  uint64_t base = 0;
+  for (; base + step <= nPacks; base += step) copyTrip<true, U>(a, base + tid, nPacks, strideB, ndst);
+  for (uint64_t i = base * 16 + tid; i < nbytes; i += nt) {
     uint8_t b = ld_elem((const uint8_t*)a->src[0] + i);
     for (int d = 0; d < ndst; ++d) st_elem((uint8_t*)a->dst[d] + i, b);
   }
 }
+
+#else
+__host__ __device__ void copy_multi(const DataArgs* a);
+#endif
 
 DF_HD int dtypeSize(int t) {
   switch (t) {
@@ -256,6 +327,7 @@ DF_HD int dtypeSize(int t) {
   }
 }
 
+#ifdef DF_DATAPATH_IMPL
 template <typename T>
 DF_HD void reduce_same(int op, const DataArgs* a) {
   switch (op) {
@@ -267,7 +339,7 @@ DF_HD void reduce_same(int op, const DataArgs* a) {
 }
 
 // Returns false when the (in, out, op) combination is not instantiated.
-static DF_HD_NOINLINE bool reduce_dispatch(int inType, int outType, int op, const DataArgs* a) {
+__host__ __device__ bool reduce_dispatch(int inType, int outType, int op, const DataArgs* a) {
   if (inType == outType) {
     switch (inType) {
 #ifndef DF_FAST_BUILD
@@ -292,6 +364,13 @@ static DF_HD_NOINLINE bool reduce_dispatch(int inType, int outType, int op, cons
   if (inType == ncclFloat32 && outType == ncclFloat16) { reduce_copy<float, __half, OP_SUM>(a); return true; }
   return false;
 }
+
+#else
+// Defined once, in device/datapath.cu (relocatable device code): every kernel of the library calls the
+// same out-of-line bodies instead of compiling its own copy of the 44 variants.
+// Returns false when the (in, out, op) combination is not instantiated.
+__host__ __device__ bool reduce_dispatch(int inType, int outType, int op, const DataArgs* a);
+#endif
 
 // Host-callable check used at prepare time.
 inline bool reduceSupported(int inType, int outType, int op) {
