@@ -332,6 +332,9 @@ DF_API ncclResult_t ofcclFinalizeRankCtx7StartHostThrds(ofcclRankCtx_t ctx) {
     if (cudaGetDriverEntryPoint("cuStreamWaitValue64", &ctx->fnWait64, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess) ctx->fnWait64 = nullptr;
     (void)cudaGetLastError();
     if (paramI64("NO_STREAM_MEMOPS", 0)) ctx->fnWrite64 = ctx->fnWait64 = nullptr;
+    CUDACHECK(cudaStreamCreateWithFlags(&ctx->wakeStream, cudaStreamNonBlocking));
+    ctx->wakeEvents.resize(256);
+    for (auto& e : ctx->wakeEvents) CUDACHECK(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
   }
   // 4. launcher: shared by the ranks of a loopback group, private otherwise
   std::shared_ptr<LoopGroup> loop = first->loop;
@@ -476,7 +479,11 @@ static ncclResult_t submit(ofcclRankCtx* ctx, const void* send, void* recv, int 
         dfcclWriteWordKernel<<<1, 1, 0, stream>>>(word, trig);
         CUDACHECK(cudaGetLastError());
       }
-      CUDACHECK(cudaLaunchHostFunc(stream, triggerReached, ctx));
+      cudaEvent_t ev;
+      { std::lock_guard<std::mutex> l(ctx->mu); ev = ctx->wakeEvents[ctx->wakeTurn++ % ctx->wakeEvents.size()]; }
+      CUDACHECK(cudaEventRecord(ev, stream));
+      CUDACHECK(cudaStreamWaitEvent(ctx->wakeStream, ev, 0));
+      CUDACHECK(cudaLaunchHostFunc(ctx->wakeStream, triggerReached, ctx));
     } else {
       __atomic_store_n((uint64_t*)word, trig, __ATOMIC_RELEASE);
     }
@@ -619,6 +626,8 @@ static void releaseHeapParts(ofcclRankCtx* ctx) {
 
 static void releaseCtx(ofcclRankCtx* ctx) {
   const dfcclBackend_t be = ctx->backend;
+  if (ctx->wakeStream) { cudaStreamSynchronize(ctx->wakeStream); cudaStreamDestroy(ctx->wakeStream); }
+  for (auto e : ctx->wakeEvents) cudaEventDestroy(e);
   RankDev& rd = ctx->rdHost;
   devFree(be, rd.devSq); devFree(be, rd.colls); devFree(be, rd.dyn); devFree(be, rd.doneCount); devFree(be, rd.failCount);
   devFree(be, (void*)rd.doneEpoch); devFree(be, (void*)rd.trigger); devFree(be, rd.saved); devFree(be, rd.stats); devFree(be, rd.trace);
@@ -645,6 +654,7 @@ DF_API ncclResult_t ofcclDestroy(ofcclRankCtx_t ctx) {
     ctx->hostSq[tail & (ctx->sqCap - 1)] = q;
     __atomic_store_n((uint64_t*)ctx->hostSqTail, tail + 1, __ATOMIC_RELEASE);
   }
+  if (ctx->wakeStream) cudaStreamSynchronize(ctx->wakeStream);     // no wake-up callback may outlive the context
   ctx->stopPoller = true;
   ctx->pollCv.notify_all();
   if (ctx->poller.joinable()) ctx->poller.join();

@@ -93,4 +93,9 @@ struct ofcclRankCtx {
   // stream memory operations (cuda backend)
   void* fnWrite64 = nullptr;
   void* fnWait64 = nullptr;
+  // wake-up path of stream-ordered submits: an event after the trigger, a side stream that waits for it
+  // and runs the host function, so that the caller's stream never waits for a CPU thread
+  cudaStream_t wakeStream = nullptr;
+  std::vector<cudaEvent_t> wakeEvents;
+  uint64_t wakeTurn = 0;
 };

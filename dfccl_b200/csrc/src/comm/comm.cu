@@ -194,7 +194,9 @@ ncclResult_t commCollective(ncclComm* c, int kind, const void* send, void* recv,
   const Topology* topo = nullptr;
   DFCHECK(topoGet(&topo));
   const size_t bytes = count * dtypeSize(type);
-  TunerChoice ch = tunerChoose(*topo, kind, bytes, c->nranks, daemonBlocks(c->backend), false);
+  // a stream-ordered kernel shares the GPU with nothing persistent: it may take more blocks than the daemon does
+  const int maxBlocks = c->backend == dfcclBackendCuda ? (int)std::min<int64_t>(DF_MAX_BLOCKS, std::max<int64_t>(1, paramI64("STREAM_MAX_BLOCKS", 64))) : daemonBlocks(c->backend);
+  TunerChoice ch = tunerChoose(*topo, kind, bytes, c->nranks, maxBlocks, false);
   cs.algo = ch.algo; cs.nBlocks = ch.nBlocks;
   cs.myFlags = (FlagSlot*)(c->heap->base() + c->saFlagsOff);
   for (int j = 0; j < c->nranks; ++j) {

@@ -270,9 +270,13 @@ DF_HD_NOINLINE void reduce_copy(const DataArgs* a) {
   uint64_t base = 0;
   for (; base + step <= nPacks; base += step)
     reduceTrip<Tin, Tout, OP, true, U>(a, base + tid, nPacks, strideB, nsrc, ndst, mul, doMul, postDiv, scale);
-  // what full trips leave (less than one trip of packs), the ragged tail, or everything when a
-  // pointer is not 16-byte aligned: element by element
-  for (uint64_t i = base * V + tid; i < n; i += nt) {
+  // what the unrolled trips leave: one pack per thread per trip, the last trip partly filled
+  for (; base + nt <= nPacks; base += nt)
+    reduceTrip<Tin, Tout, OP, true, 1>(a, base + tid, nPacks, strideB, nsrc, ndst, mul, doMul, postDiv, scale);
+  if (base + tid < nPacks)
+    reduceTrip<Tin, Tout, OP, false, 1>(a, base + tid, nPacks, strideB, nsrc, ndst, mul, doMul, postDiv, scale);
+  // the ragged tail, or everything when a pointer is not 16-byte aligned: element by element
+  for (uint64_t i = nPacks * V + tid; i < n; i += nt) {
     A acc = Elem<Tin>::up(ld_elem((const Tin*)a->src[0] + i));
     for (int j = 1; j < nsrc; ++j) acc = red<OP>(acc, Elem<Tin>::up(ld_elem((const Tin*)a->src[j] + i)));
     Tout o = Elem<Tout>::down(finish<Tin, Tout>(acc, scale, postDiv));
@@ -308,7 +312,9 @@ __host__ __device__ void copy_multi(const DataArgs* a) {
   const uint32_t strideB = (uint32_t)nt * 16u;
   uint64_t base = 0;
   for (; base + step <= nPacks; base += step) copyTrip<true, U>(a, base + tid, nPacks, strideB, ndst);
-  for (uint64_t i = base * 16 + tid; i < nbytes; i += nt) {
+  for (; base + nt <= nPacks; base += nt) copyTrip<true, 1>(a, base + tid, nPacks, strideB, ndst);
+  if (base + tid < nPacks) copyTrip<false, 1>(a, base + tid, nPacks, strideB, ndst);
+  for (uint64_t i = nPacks * 16 + tid; i < nbytes; i += nt) {
     uint8_t b = ld_elem((const uint8_t*)a->src[0] + i);
     for (int d = 0; d < ndst; ++d) st_elem((uint8_t*)a->dst[d] + i, b);
   }
