@@ -73,10 +73,13 @@ def main(argv=None):
     ap.add_argument("--ids", type=int, default=4, help="registrations per case, used round-robin so that the host can enqueue ahead")
     ap.add_argument("--skip-nccl", action="store_true")
     ap.add_argument("--skip-stream-api", action="store_true")
+    ap.add_argument("--trace", default="", help="write the device trace of rank 0 (Chrome trace JSON) here")
     ap.add_argument("--out", default="")
     a = ap.parse_args(argv)
 
     os.environ.setdefault("DFCCL_WAIT_TIMEOUT_MS", "30000")
+    if a.trace:
+        os.environ["DFCCL_TRACE"] = "1"
     d = init_distributed()
     world, rank, dev = d.world, d.rank, d.device
     L = nv.lib()
@@ -165,6 +168,10 @@ def main(argv=None):
         if rank == 0:
             print(json.dumps(row), flush=True)
     st = ctx.stats()
+    if a.trace:
+        import time
+        time.sleep(0.05)
+        ctx.trace_dump(a.trace + (f".rank{rank}" if rank else ""))
     ctx.destroy()
     if rank == 0 and a.out:
         with open(a.out, "w") as fh:

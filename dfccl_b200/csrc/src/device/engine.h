@@ -365,6 +365,7 @@ DF_HD int runColl(BlockShared* sh, RankDev* rd, int b, int coll, uint32_t budget
         if (sh->dyn.sqeFlags & SQE_TRIGGERED) {
           if (!boundedWait(sh, rd, b, 2, budget)) { if (noteStall(sh, rd)) { setPhase(sh, PH_COMPLETE); break; } return RC_STALLED; }
         }
+        if (tid == 0) trace(rd, b, TR_START, coll);          // released by its stream (or not stream-ordered)
         setPhase(sh, PH_COPY_IN);
         break;
       case PH_COPY_IN:
@@ -389,6 +390,7 @@ DF_HD int runColl(BlockShared* sh, RankDev* rd, int b, int coll, uint32_t budget
       }
       case PH_WAIT_ARRIVE:
         if (n > 1 && !boundedWait(sh, rd, b, 0, budget)) { if (noteStall(sh, rd)) { setPhase(sh, PH_COMPLETE); break; } return RC_STALLED; }
+        if (tid == 0) trace(rd, b, TR_RESUME, coll);         // every peer has arrived
         setPhase(sh, PH_DATA);
         break;
       case PH_DATA:
@@ -413,6 +415,7 @@ DF_HD int runColl(BlockShared* sh, RankDev* rd, int b, int coll, uint32_t budget
       }
       case PH_WAIT_DONE:
         if (n > 1 && !boundedWait(sh, rd, b, 1, budget)) { if (noteStall(sh, rd)) { setPhase(sh, PH_COMPLETE); break; } return RC_STALLED; }
+        if (tid == 0) trace(rd, b, TR_STALL, coll);          // every peer is done (event name kept for the dump: 'stall' = end of the done wait)
         setPhase(sh, PH_COPY_OUT);
         break;
       case PH_COPY_OUT:
