@@ -586,6 +586,8 @@ DF_API ncclResult_t dfcclTraceDump(ofcclRankCtx_t ctx, const char* path) {
   std::ofstream o(path);
   if (!o) return ncclSystemError;
   static const char* names[] = {"?", "sqe", "start", "stall", "resume", "data_begin", "data_end", "done", "quit", "launch"};
+  o.setf(std::ios::fixed);
+  o.precision(3);                 // microseconds with nanosecond resolution; the default would round the absolute stamps
   o << "{\"traceEvents\":[\n";
   uint64_t n = std::min<uint64_t>(head, cap), first = head - n;
   for (uint64_t i = 0; i < n; ++i) {
