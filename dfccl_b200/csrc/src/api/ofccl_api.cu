@@ -311,7 +311,7 @@ DF_API ncclResult_t ofcclFinalizeRankCtx7StartHostThrds(ofcclRankCtx_t ctx) {
     DFCHECK(devAlloc(be, (void**)&rd.trace, sizeof(TraceEvent) * rd.traceCap));
   }
   // tunables; the un-prefixed names are the reference's (src/enqueue_ofccl.cc:1287-1297)
-  rd.spinBudget = (uint32_t)std::max<int64_t>(1, paramI64("BASE_CTX_SWITCH_THRESHOLD", 80));
+  rd.spinBudget = (uint32_t)std::max<int64_t>(1, paramI64("BASE_CTX_SWITCH_THRESHOLD", 32));
   rd.headTries = (uint32_t)std::max<int64_t>(1, paramI64("NUM_TRY_TASKQ_HEAD", 5));
   rd.recvSuccessFactor = (uint32_t)paramI64("RECV_SUCCESS_FACTOR", 5);
   const int64_t tolerant = paramI64("TOLERANT_UNPROGRESSED_CNT", 0);     // polls in the reference; here ~1 us each

@@ -152,7 +152,8 @@ DF_HD void daemonBlockMain(RankDev* rd, int b, BlockShared* sh) {
       const int coll = sh->active[i];
       if (coll == 0xffff) continue;
       // the head of the queue is the oldest submission: give it more patience
-      const uint32_t budget = rd->spinBudget * (i == 0 ? rd->headTries : 1u);
+      // with nothing else queued there is nothing to switch to: polling longer is free
+      const uint32_t budget = rd->spinBudget * ((i == 0 || nAct == 1) ? rd->headTries : 1u);
       bool moved = false;
       int rc = runColl(sh, rd, b, coll, budget, &moved);
       if (rc == RC_DONE || moved) progressed = true;

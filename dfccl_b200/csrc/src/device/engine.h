@@ -363,7 +363,9 @@ DF_HD int runColl(BlockShared* sh, RankDev* rd, int b, int coll, uint32_t budget
     switch (phase) {
       case PH_TRIGGER:
         if (sh->dyn.sqeFlags & SQE_TRIGGERED) {
-          if (!boundedWait(sh, rd, b, 2, budget)) { if (noteStall(sh, rd)) { setPhase(sh, PH_COMPLETE); break; } return RC_STALLED; }
+          // one look is enough: the word is local, nobody is closer to writing it because this block
+          // keeps polling, and every poll spent here delays the collectives queued behind this one
+          if (!boundedWait(sh, rd, b, 2, sh->standalone ? budget : 1u)) { if (noteStall(sh, rd)) { setPhase(sh, PH_COMPLETE); break; } return RC_STALLED; }
         }
         if (tid == 0) trace(rd, b, TR_START, coll);          // released by its stream (or not stream-ordered)
         setPhase(sh, PH_COPY_IN);
