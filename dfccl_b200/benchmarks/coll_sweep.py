@@ -46,9 +46,12 @@ def time_loop(fn, iters: int, warm: int, world: int) -> float:
     if world > 1:
         dist.barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    import time
     e0.record()
+    h0 = time.perf_counter()
     for _ in range(iters):
         fn()
+    time_loop.host_us = (time.perf_counter() - h0) * 1e6 / iters     # host time to enqueue one call
     e1.record()
     torch.cuda.synchronize()
     us = e0.elapsed_time(e1) * 1e3 / iters
@@ -138,6 +141,7 @@ def main(argv=None):
         us = time_loop(daemon_op, iters, a.warmup, world)
         assert ctx.wait_all(60000) == nv.SUCCESS
         row["daemon_us"] = us
+        row["daemon_host_enqueue_us"] = time_loop.host_us
         row["daemon_busbw_gbs"] = sz / us / 1e3 * bus_factor(k, world)
         # correctness spot check against torch on the same data
         if k == "allreduce" and world > 1:

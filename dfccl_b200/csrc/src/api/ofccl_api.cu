@@ -22,19 +22,13 @@ __global__ void dfcclWriteWordKernel(volatile uint64_t* p, uint64_t v) {
   *p = v;
 }
 
-// Runs on a driver thread when a stream reaches the point right after a trigger write: only now
-// does the submission need a daemon, so only now is the launcher woken.  Waking it at enqueue
-// time would keep the daemon resident (and polling) while the GPU is still busy with the work
-// queued before the trigger.
+// Fallback of the wake-up path when stream memory operations are unavailable: a host function (on a
+// side stream) publishes the host mirror of a trigger word once the caller's stream has passed the
+// trigger.  Normally the stream writes the mirror itself (see submit).
 static void CUDART_CB triggerReached(void* arg) {
-  ofcclRankCtx* ctx = (ofcclRankCtx*)arg;
-  ctx->untriggered--;
-  std::shared_ptr<DaemonLauncher> L = ctx->launcher;
-  if (L && !ctx->ctl->alive) {
-    std::lock_guard<std::mutex> l(L->mu);
-    L->wake = true;
-    L->cv.notify_all();
-  }
+  auto* p = (std::pair<ofcclRankCtx*, std::pair<int, uint64_t>>*)arg;
+  __atomic_store_n((uint64_t*)&p->first->hostTrig[p->second.first], p->second.second, __ATOMIC_RELEASE);
+  delete p;
 }
 
 static uint32_t pow2ceil(uint32_t v) { uint32_t p = 1; while (p < v) p <<= 1; return p; }
@@ -142,6 +136,21 @@ static void pollerMain(ofcclRankCtx* ctx) {
       std::unique_lock<std::mutex> l(ctx->mu);
       ctx->pollCv.wait_for(l, std::chrono::milliseconds(20), [&] { return ctx->remaining.load() > 0 || ctx->stopPoller.load(); });
       continue;
+    }
+    if (ctx->untriggered.load() > 0) {          // stream-ordered submissions whose release has not been seen yet
+      int fired = 0;
+      {
+        std::lock_guard<std::mutex> l(ctx->mu);
+        auto& pt = ctx->pendingTrig;
+        for (size_t i = 0; i < pt.size();) {
+          if (__atomic_load_n((const uint64_t*)&ctx->hostTrig[pt[i].first], __ATOMIC_ACQUIRE) >= pt[i].second) { pt[i] = pt.back(); pt.pop_back(); ++fired; }
+          else ++i;
+        }
+      }
+      if (fired) {
+        ctx->untriggered -= fired;
+        if (!ctx->ctl->alive && !ctx->ctl->abortFlag) wakeLauncher(ctx->launcher.get());
+      }
     }
     const uint64_t slot = ctx->cqHead & (ctx->cqCap - 1);
     const uint64_t e = __atomic_load_n((const uint64_t*)&ctx->hostCq[slot], __ATOMIC_ACQUIRE);
@@ -292,6 +301,7 @@ DF_API ncclResult_t ofcclFinalizeRankCtx7StartHostThrds(ofcclRankCtx_t ctx) {
   DFCHECK(pinnedAlloc(be, (void**)&ctx->hostSqHead, 64));
   DFCHECK(pinnedAlloc(be, (void**)&ctx->hostCq, sizeof(uint64_t) * ctx->cqCap));
   DFCHECK(pinnedAlloc(be, (void**)&ctx->ctl, sizeof(DaemonCtl)));
+  DFCHECK(pinnedAlloc(be, (void**)&ctx->hostTrig, sizeof(uint64_t) * ((size_t)ctx->maxCollId + 1)));
   RankDev& rd = ctx->rdHost;
   memset(&rd, 0, sizeof(rd));
   rd.hostSq = ctx->hostSq; rd.hostSqTail = ctx->hostSqTail; rd.hostSqHead = ctx->hostSqHead;
@@ -332,6 +342,9 @@ DF_API ncclResult_t ofcclFinalizeRankCtx7StartHostThrds(ofcclRankCtx_t ctx) {
     if (cudaGetDriverEntryPoint("cuStreamWaitValue64", &ctx->fnWait64, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess) ctx->fnWait64 = nullptr;
     (void)cudaGetLastError();
     if (paramI64("NO_STREAM_MEMOPS", 0)) ctx->fnWrite64 = ctx->fnWait64 = nullptr;
+    if (cudaGetDriverEntryPoint("cuStreamBatchMemOp", &ctx->fnBatch, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess) ctx->fnBatch = nullptr;
+    (void)cudaGetLastError();
+    if (!ctx->fnWrite64) ctx->fnBatch = nullptr;
     CUDACHECK(cudaStreamCreateWithFlags(&ctx->wakeStream, cudaStreamNonBlocking));
     ctx->wakeEvents.resize(256);
     for (auto& e : ctx->wakeEvents) CUDACHECK(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
@@ -466,24 +479,44 @@ static ncclResult_t submit(ofcclRankCtx* ctx, const void* send, void* recv, int 
   }
   ctx->pollCv.notify_one();
   const bool deferWake = onStream && ctx->backend == dfcclBackendCuda;
-  if (deferWake) ctx->untriggered++;
-  else if (!ctx->ctl->alive) wakeLauncher(ctx->launcher.get());
+  if (deferWake) {
+    std::lock_guard<std::mutex> l(ctx->mu);
+    ctx->pendingTrig.emplace_back(collId, trig);
+    ctx->untriggered++;
+  } else if (!ctx->ctl->alive) wakeLauncher(ctx->launcher.get());
   if (onStream) {
     volatile uint64_t* word = ctx->rdHost.trigger + collId;
     if (ctx->backend == dfcclBackendCuda) {
-      if (ctx->fnWrite64) {
+      volatile uint64_t* mirror = ctx->hostTrig + collId;
+      if (ctx->fnBatch) {
+        // device trigger word and its host mirror in one driver call
+        typedef CUresult (*Fn)(CUstream, unsigned int, CUstreamBatchMemOpParams*, unsigned int);
+        CUstreamBatchMemOpParams ops[2];
+        memset(ops, 0, sizeof(ops));
+        ops[0].writeValue.operation = CU_STREAM_MEM_OP_WRITE_VALUE_64;
+        ops[0].writeValue.address = (CUdeviceptr)(uintptr_t)word;
+        ops[0].writeValue.value64 = trig;
+        ops[1].writeValue.operation = CU_STREAM_MEM_OP_WRITE_VALUE_64;
+        ops[1].writeValue.address = (CUdeviceptr)(uintptr_t)mirror;
+        ops[1].writeValue.value64 = trig;
+        CUresult r = ((Fn)ctx->fnBatch)((CUstream)stream, 2, ops, 0);
+        if (r != CUDA_SUCCESS) { DF_WARN("cuStreamBatchMemOp failed (%d)", (int)r); return ncclUnhandledCudaError; }
+      } else if (ctx->fnWrite64) {
         typedef CUresult (*Fn)(CUstream, CUdeviceptr, cuuint64_t, unsigned int);
         CUresult r = ((Fn)ctx->fnWrite64)((CUstream)stream, (CUdeviceptr)(uintptr_t)word, trig, 0);
+        if (r == CUDA_SUCCESS) r = ((Fn)ctx->fnWrite64)((CUstream)stream, (CUdeviceptr)(uintptr_t)mirror, trig, 0);
         if (r != CUDA_SUCCESS) { DF_WARN("cuStreamWriteValue64 failed (%d)", (int)r); return ncclUnhandledCudaError; }
       } else {
+        // no stream memory operations: a one-thread kernel writes the word, a host function (on a side
+        // stream, so that the caller's stream never waits for a CPU thread) publishes the mirror
         dfcclWriteWordKernel<<<1, 1, 0, stream>>>(word, trig);
         CUDACHECK(cudaGetLastError());
+        cudaEvent_t ev;
+        { std::lock_guard<std::mutex> l(ctx->mu); ev = ctx->wakeEvents[ctx->wakeTurn++ % ctx->wakeEvents.size()]; }
+        CUDACHECK(cudaEventRecord(ev, stream));
+        CUDACHECK(cudaStreamWaitEvent(ctx->wakeStream, ev, 0));
+        CUDACHECK(cudaLaunchHostFunc(ctx->wakeStream, triggerReached, new std::pair<ofcclRankCtx*, std::pair<int, uint64_t>>(ctx, {collId, trig})));
       }
-      cudaEvent_t ev;
-      { std::lock_guard<std::mutex> l(ctx->mu); ev = ctx->wakeEvents[ctx->wakeTurn++ % ctx->wakeEvents.size()]; }
-      CUDACHECK(cudaEventRecord(ev, stream));
-      CUDACHECK(cudaStreamWaitEvent(ctx->wakeStream, ev, 0));
-      CUDACHECK(cudaLaunchHostFunc(ctx->wakeStream, triggerReached, ctx));
     } else {
       __atomic_store_n((uint64_t*)word, trig, __ATOMIC_RELEASE);
     }
@@ -635,7 +668,7 @@ static void releaseCtx(ofcclRankCtx* ctx) {
   devFree(be, (void*)rd.doneEpoch); devFree(be, (void*)rd.trigger); devFree(be, rd.saved); devFree(be, rd.stats); devFree(be, rd.trace);
   devFree(be, ctx->rdDev);
   pinnedFree(be, ctx->hostSq); pinnedFree(be, (void*)ctx->hostSqTail); pinnedFree(be, (void*)ctx->hostSqHead);
-  pinnedFree(be, (void*)ctx->hostCq); pinnedFree(be, ctx->ctl);
+  pinnedFree(be, (void*)ctx->hostCq); pinnedFree(be, ctx->ctl); pinnedFree(be, (void*)ctx->hostTrig);
   delete ctx;
 }
 

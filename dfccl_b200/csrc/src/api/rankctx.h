@@ -93,6 +93,11 @@ struct ofcclRankCtx {
   // stream memory operations (cuda backend)
   void* fnWrite64 = nullptr;
   void* fnWait64 = nullptr;
+  void* fnBatch = nullptr;
+  // host-visible mirror of the trigger words: the stream writes both, the poller watches the mirror and
+  // wakes the launcher when a released submission finds the daemon parked
+  volatile uint64_t* hostTrig = nullptr;                    // pinned, [maxColls]
+  std::vector<std::pair<int, uint64_t>> pendingTrig;        // (collId, value) not yet seen in the mirror; guarded by mu
   // wake-up path of stream-ordered submits: an event after the trigger, a side stream that waits for it
   // and runs the host function, so that the caller's stream never waits for a CPU thread
   cudaStream_t wakeStream = nullptr;
