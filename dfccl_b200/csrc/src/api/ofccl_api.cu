@@ -31,6 +31,9 @@ static void CUDART_CB triggerReached(void* arg) {
   delete p;
 }
 
+static std::atomic<uint64_t> g_prof[6];
+static inline uint64_t nowNs() { return (uint64_t)std::chrono::duration_cast<std::chrono::nanoseconds>(std::chrono::steady_clock::now().time_since_epoch()).count(); }
+
 static uint32_t pow2ceil(uint32_t v) { uint32_t p = 1; while (p < v) p <<= 1; return p; }
 
 DaemonLauncher::~DaemonLauncher() {
@@ -425,8 +428,11 @@ static ncclResult_t submit(ofcclRankCtx* ctx, const void* send, void* recv, int 
   Sqe q;
   memset(&q, 0, sizeof(q));
   uint64_t trig = 0;
+  const uint64_t tp0 = nowNs();
+  uint64_t tp1 = 0, tp2 = 0;
   {
     std::unique_lock<std::mutex> l(ctx->mu);
+    tp1 = nowNs();
     auto it = ctx->colls.find(collId);
     if (it == ctx->colls.end()) { DF_WARN("collective %d was never prepared", collId); return ncclInvalidArgument; }
     CollEntry& e = it->second;
@@ -438,6 +444,7 @@ static ncclResult_t submit(ofcclRankCtx* ctx, const void* send, void* recv, int 
       if (!ok) { DF_WARN("collective %d: previous submission did not complete within 120 s", collId); return dfcclTimeout; }
       if (ctx->ctl->abortFlag) return dfcclAborted;
     }
+    tp2 = nowNs();
     const CollStatic& cs = e.cs;
     const bool needSend = !(cs.kind == dfcclCollBroadcast && cs.rank != cs.root);
     const bool needRecv = !(cs.kind == dfcclCollReduce && cs.rank != cs.root);
@@ -477,6 +484,7 @@ static ncclResult_t submit(ofcclRankCtx* ctx, const void* send, void* recv, int 
       __atomic_store_n((uint64_t*)ctx->hostSqTail, tail + 1, __ATOMIC_RELEASE);
     }
   }
+  const uint64_t tp3 = nowNs();
   ctx->pollCv.notify_one();
   const bool deferWake = onStream && ctx->backend == dfcclBackendCuda;
   if (deferWake) {
@@ -521,6 +529,7 @@ static ncclResult_t submit(ofcclRankCtx* ctx, const void* send, void* recv, int 
       __atomic_store_n((uint64_t*)word, trig, __ATOMIC_RELEASE);
     }
   }
+  { const uint64_t tp4 = nowNs(); g_prof[0] += tp1 - tp0; g_prof[1] += tp2 - tp1; g_prof[2] += tp3 - tp2; g_prof[3] += tp4 - tp3; g_prof[4]++; }
   return ncclSuccess;
 }
 
@@ -571,6 +580,15 @@ DF_API ncclResult_t dfcclStreamWait(int collId, cudaStream_t stream, ofcclRankCt
     return ncclSuccess;
   }
   return dfcclWait(collId, -1, ctx);     // no stream memory operations: the host waits instead
+}
+
+// Mean host nanoseconds per submit spent in: taking the context lock, waiting for the previous
+// submission of the id, building and publishing the entry, wake-up and stream operations.
+DF_API ncclResult_t dfcclSubmitProfile(uint64_t out[5]) {
+  uint64_t n = g_prof[4].load();
+  for (int i = 0; i < 4; ++i) out[i] = n ? g_prof[i].load() / n : 0;
+  out[4] = n;
+  return ncclSuccess;
 }
 
 DF_API ncclResult_t dfcclAbort(ofcclRankCtx_t ctx) {

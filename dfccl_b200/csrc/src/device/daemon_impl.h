@@ -93,7 +93,7 @@ DF_HD void blockRestore(BlockShared* sh, RankDev* rd, int b) {
   const int tid = df_tid(), nt = df_nthreads();
   BlockSaved* sv = &rd->saved[b];
   if (tid == 0) {
-    sh->loadedColl = -1; sh->standalone = 0; sh->dynDirty = 0; sh->quit = 0;
+    sh->loadedColl = -1; sh->standalone = 0; sh->dynDirty = 0; sh->quit = 0; sh->abortSeen = 0;
     sh->frontier = sv->frontier; sh->nActive = sv->nActive;
     DevStats z = {};
     sh->stats = z;
@@ -177,7 +177,8 @@ DF_HD void daemonBlockMain(RankDev* rd, int b, BlockShared* sh) {
         if (consumeSubmissions(sh, rd, b) > 0) progressed = true;
       }
       const uint64_t now = df_now_ns();
-      if (rd->ctl->abortFlag) sh->quit = 3;
+      sh->abortSeen = rd->ctl->abortFlag;
+      if (sh->abortSeen) sh->quit = 3;
       else if (rd->maxLifetimeNs && now - bornNs > rd->maxLifetimeNs && !sh->quit) {
         // safety net: no instance of the daemon outlives this, whatever its state; the host relaunches it
         sh->quit = 1;
@@ -214,7 +215,7 @@ DF_HD void standaloneBlockMain(RankDev* rd, int b, BlockShared* sh, const CollSt
     for (int i = tid; i < (int)(sizeof(CollStatic) / 16); i += nt) d[i] = s[i];
   }
   if (tid == 0) {
-    sh->loadedColl = 0; sh->standalone = 1; sh->dynDirty = 0; sh->quit = 0;
+    sh->loadedColl = 0; sh->standalone = 1; sh->dynDirty = 0; sh->quit = 0; sh->abortSeen = 0;
     DevStats z = {};
     sh->stats = z;
     CollDyn d = {};

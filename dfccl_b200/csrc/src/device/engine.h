@@ -50,6 +50,8 @@ struct BlockShared {
   uint64_t frontier;
   uint32_t nActive;
   uint32_t quit;                 // 1 = voluntary, 2 = final, 3 = abort
+  uint32_t abortSeen;            // the host's abort flag as last read by thread 0 (the flag lives in host memory: one
+                                 // read costs a PCIe round trip, so it is sampled once per scheduler pass, not per wait)
   uint16_t active[DF_MAX_ACTIVE];
 };
 
@@ -157,7 +159,7 @@ DF_HD bool boundedWait(BlockShared* sh, RankDev* rd, int b, int which, uint32_t 
         }
       }
       bool laneStop = false;
-      if ((spins & 15) == 15 && lane == 0) laneStop = rd->ctl->abortFlag != 0;
+      if ((spins & 255) == 255 && lane == 0) laneStop = rd->ctl->abortFlag != 0;
       ok = df_warp_all(laneOk);
       const bool stop = !df_warp_all(!laneStop);      // uniform: every lane leaves the loop together
       ++spins;
@@ -174,7 +176,7 @@ DF_HD bool noteStall(BlockShared* sh, RankDev* rd) {
   if (df_tid() == 0) {
     uint64_t now = df_now_ns();
     sh->ctl0 = 0;
-    if (rd->ctl->abortFlag) { sh->dyn.status = ST_ABORTED; sh->ctl0 = 1; }
+    if (sh->standalone ? (rd->ctl->abortFlag != 0) : (sh->abortSeen != 0)) { sh->dyn.status = ST_ABORTED; sh->ctl0 = 1; }
     else if (sh->dyn.stallSinceNs == 0) { sh->dyn.stallSinceNs = now; sh->dynDirty = 1; }
     else if (rd->waitTimeoutNs && now - sh->dyn.stallSinceNs > rd->waitTimeoutNs) {
       sh->dyn.status = ST_TIMEOUT; sh->ctl0 = 1; sh->stats.waitTimeouts++;
