@@ -150,11 +150,11 @@ DF_HD bool boundedWait(BlockShared* sh, RankDev* rd, int b, int which, uint32_t 
     for (;;) {
       bool laneOk = true;
       if (which == 2) {
-        if (lane == 0) laneOk = ld_acquire_sys_u64(&rd->trigger[sh->loadedColl]) >= sh->dyn.trigger;
+        if (lane == 0) laneOk = ld_relaxed_sys_u64(&rd->trigger[sh->loadedColl]) >= sh->dyn.trigger;
       } else {
         for (int j = lane; j < n; j += ws) {
           if (j == me) continue;
-          uint64_t v = ld_acquire_sys_u64(which == 0 ? &mine[j].arrive : &mine[j].done);
+          uint64_t v = ld_relaxed_sys_u64(which == 0 ? &mine[j].arrive : &mine[j].done);
           laneOk = laneOk && v >= epoch;
         }
       }
@@ -165,6 +165,9 @@ DF_HD bool boundedWait(BlockShared* sh, RankDev* rd, int b, int which, uint32_t 
       ++spins;
       if (ok || stop || spins >= budget) break;
     }
+    // polls are relaxed loads (an acquire at system scope per poll costs a fence each time); the one
+    // fence that orders the payload accesses after the flags is paid when the wait succeeds
+    if (ok && lane == 0) fence_sys();
     if (lane == 0) { sh->waitOk = ok ? 1 : 0; sh->waitSpins = spins; sh->stats.waitPolls += spins; }
   }
   df_sync();
@@ -340,11 +343,11 @@ DF_HD void completeColl(BlockShared* sh, RankDev* rd, int b) {
       atomic_exch_u32(&rd->doneCount[coll], 0u);
       uint32_t st = fails ? (fails >> 16) / (fails & 0xffff) : ST_OK;   // all failing blocks report the same cause
       if (st > 255) st = ST_TIMEOUT;
-      fence_sys();
-      st_release_sys_u64(&rd->doneEpoch[coll], ((uint64_t)st << 56) | sh->dyn.epoch);
       unsigned long long idx = atomic_add_u64((unsigned long long*)&rd->devCqTail, 1ull);
       uint32_t gen = (uint32_t)(idx / rd->cqCap) + 1u;
-      st_release_sys_u64(&rd->hostCq[idx & (rd->cqCap - 1)], cqeEncode(gen, st, (uint32_t)coll));
+      fence_sys();                  // everything every block did for this submission, before either word below
+      st_relaxed_sys_u64(&rd->doneEpoch[coll], ((uint64_t)st << 56) | sh->dyn.epoch);
+      st_relaxed_sys_u64(&rd->hostCq[idx & (rd->cqCap - 1)], cqeEncode(gen, st, (uint32_t)coll));
     }
     trace(rd, b, TR_DONE, coll);
   }
@@ -404,15 +407,15 @@ DF_HD int runColl(BlockShared* sh, RankDev* rd, int b, int coll, uint32_t budget
         setPhase(sh, PH_POST_DONE);
         break;
       case PH_POST_DONE: {
-        // all payload stores of this block were issued before the barrier inside setPhase;
-        // the fence makes them visible system-wide before any done flag is
-        if (tid == 0) fence_sys();
-        df_sync();
-        const uint64_t epoch = sh->dyn.epoch;
-        for (int j = tid; j < n; j += nt) {
-          if (j == me) continue;
-          fence_sys();
-          st_release_sys_u64(&(sh->cs.peerFlags[j] + (uint64_t)b * n + me)->done, epoch);
+        if (n > 1) {
+          // all payload stores of this block were issued before the barrier inside setPhase; one fence
+          // by the posting thread makes them visible system-wide before any done flag is
+          const uint64_t epoch = sh->dyn.epoch;
+          if (tid == 0) {
+            fence_sys();
+            for (int j = 0; j < n; ++j)
+              if (j != me) st_relaxed_sys_u64(&(sh->cs.peerFlags[j] + (uint64_t)b * n + me)->done, epoch);
+          }
         }
         setPhase(sh, PH_WAIT_DONE);
         break;
