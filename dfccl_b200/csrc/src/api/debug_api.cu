@@ -2,6 +2,7 @@
 #include "../common/log.h"
 #include "../common/param.h"
 #include "../topo/topo.h"
+#include "../comm/comm.h"
 #include <cstring>
 
 using namespace dfccl;
@@ -39,3 +40,11 @@ DF_API double dfcclTunerPredictUs(int kind, int algo, size_t bytes, int nranks, 
 DF_API void dfcclLogReset(void) { logReset(); }
 DF_API const char* dfcclLastError(void) { return lastError(); }
 DF_API long long dfcclParam(const char* name, long long dflt) { return paramI64(name, dflt); }
+
+// Base address of `peer`'s symmetric heap as mapped in this process (own base for peer == rank):
+// a buffer at offset o of the peer's heap is at base + o here.
+DF_API ncclResult_t dfcclHeapPeerBase(ncclComm_t comm, int peer, void** base) {
+  if (!comm || !base || peer < 0 || peer >= comm->nranks) return ncclInvalidArgument;
+  *base = comm->peerHeap[peer];
+  return ncclSuccess;
+}

@@ -1,0 +1,444 @@
+// bf16 GEMM on the 5th-generation tensor cores, hand-written for sm_100a:
+//     C[M,N] = A[M,K] * B[N,K]^T        (both operands K-major: y = x W^T of a linear layer)
+// and its two communication-fused forms for tensor parallelism over NVLink peer memory:
+//   * all-gather -> GEMM : A is row-sharded over the ranks.  Extra warps of the SAME kernel pull
+//     the peers' row blocks into the local A buffer (plain peer loads) and publish one flag per
+//     128-row block; the TMA producer waits for the flag of the block it is about to load, so the
+//     transfer of block i+1.. overlaps the tensor-core work on block i.
+//   * GEMM -> reduce-scatter : C is a partial sum whose row blocks belong to different ranks.  The
+//     epilogue stores each finished tile straight into its owner's receive slot (peer stores) and
+//     publishes a per-tile flag there; the owner sums the n slots of a tile as soon as all have
+//     arrived, in the same kernel, while other CTAs are still on the tensor cores.
+// Structure of a CTA (persistent, one per SM): warp 0 = TMA producer (one elected thread), warp 1 =
+// tensor-memory owner and MMA issuer (one elected thread, tcgen05.mma, 128 x 256 x 16 per
+// instruction), warps 2-5 = epilogue (tcgen05.ld from a double-buffered 2 x 256-column accumulator),
+// warps 6-9 = communication.  4 shared-memory stages of 48 KB (A 128x64, B 256x64, 128-byte swizzle)
+// filled by TMA (no cluster multicast anywhere), full/empty mbarriers, tcgen05.commit to release
+// stages and to hand accumulators over.  Every wait is bounded and ends in an error word.
+#include "tc_common.h"
+#include "dfccl.h"
+#include "../common/log.h"
+#include <mutex>
+
+namespace dfccl {
+namespace {
+
+using namespace tc;
+
+constexpr int BM = 128, BN = 256, BK = 64, STAGES = 4, UMMA_K = 16;
+constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int TMEM_COLS = 512;                       // two accumulators of BN fp32 columns
+constexpr int NUM_THREADS = 320;                     // 10 warps
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+
+struct FusedArgs {
+  // ---- all-gather -> GEMM
+  int nranks, rank;                 // nranks <= 1: plain GEMM
+  int rowsPerRank;                  // rows of A each rank contributes (multiple of BM)
+  const __nv_bfloat16* peerA[8];    // each rank's shard [rowsPerRank, K] as mapped here (own entry unused)
+  __nv_bfloat16* gathered;          // local [M, K] buffer the tensor map of A covers
+  uint32_t* blockReady;             // [M / BM] local flags, value = epoch when the row block is in place
+  // ---- GEMM -> reduce-scatter
+  __nv_bfloat16* slot[8];           // owner j's receive area for MY partial tiles: [rowsPerRank, N] bf16, as mapped here
+  uint32_t* tileFlag[8];            // owner j's flags [nranks][tilesPerOwner] as mapped here (I write row `rank`)
+  const __nv_bfloat16* mySlots;     // my receive areas: [nranks][rowsPerRank, N]
+  const uint32_t* myTileFlags;      // my flags [nranks][tilesPerOwner]
+  __nv_bfloat16* reduced;           // my output [rowsPerRank, N]
+  // ---- rendezvous words (symmetric heap), written by peers
+  volatile uint64_t* arrive;        // [nranks] local: peer j posted epoch -> its buffers are ready
+  volatile uint64_t* done;          // [nranks] local: peer j posted epoch -> it no longer reads my buffers
+  volatile uint64_t* peerArrive[8]; // where I post for peer j (its arrive[rank])
+  volatile uint64_t* peerDone[8];
+  uint32_t* doneCount;              // local counter of CTAs that finished their communication work
+  uint64_t epoch;
+  int mode;                         // 0 plain, 1 all-gather -> GEMM, 2 GEMM -> reduce-scatter
+};
+
+struct GemmArgs {
+  __nv_bfloat16* C;
+  int M, N, K, ldc;
+  uint32_t* err;                    // device word: non-zero = a bounded wait ran out
+  FusedArgs f;
+};
+
+__device__ __forceinline__ uint64_t ld_acq_sys(const volatile uint64_t* p) {
+  uint64_t v;
+  asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ uint32_t ld_acq_gpu_u32(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ uint32_t ld_acq_sys_u32(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_rel_sys(volatile uint64_t* p, uint64_t v) {
+  asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+__device__ __forceinline__ void st_rel_sys_u32(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ void st_rel_gpu_u32(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint4 ld_peer16(const void* p) {
+  uint4 v;
+  asm volatile("ld.relaxed.sys.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_peer16(void* p, uint4 v) {
+  asm volatile("st.relaxed.sys.global.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+
+// Bounded spin on a 64-bit flag in local memory written by a peer.
+__device__ __forceinline__ bool wait_flag64(const volatile uint64_t* p, uint64_t want, volatile uint32_t* giveUp) {
+  for (uint32_t i = 0; i < 40000000u; ++i) {
+    if (ld_acq_sys(p) >= want) return true;
+    if ((i & 255) == 255 && *giveUp) return false;
+  }
+  *giveUp = 1;
+  return false;
+}
+__device__ __forceinline__ bool wait_flag32(const uint32_t* p, uint32_t want, volatile uint32_t* giveUp, bool sys) {
+  for (uint32_t i = 0; i < 40000000u; ++i) {
+    if ((sys ? ld_acq_sys_u32(p) : ld_acq_gpu_u32(p)) >= want) return true;
+    if ((i & 255) == 255 && *giveUp) return false;
+  }
+  *giveUp = 1;
+  return false;
+}
+
+// m-tile visiting order: own row blocks first, then the peers' in ring order, so that the
+// tensor cores start on data that is already here while the rest is in flight.
+__device__ __forceinline__ int orderedMTile(const FusedArgs& f, int i, int mTiles) {
+  if (f.nranks <= 1 || f.mode == 0) return i;
+  const int per = mTiles / f.nranks;
+  const int owner = (f.rank + (f.mode == 2 ? 1 : 0) + i / per) % f.nranks;   // reduce-scatter: other ranks' rows first, mine last
+  return owner * per + i % per;
+}
+
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+dfcclGemmKernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB, const GemmArgs g) {
+  extern __shared__ uint8_t smemRaw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smemRaw + 1023) & ~(uintptr_t)1023);
+  uint64_t* fullBar = (uint64_t*)(smem + STAGES * STAGE_BYTES);
+  uint64_t* emptyBar = fullBar + STAGES;
+  uint64_t* accFull = emptyBar + STAGES;            // [2]
+  uint64_t* accEmpty = accFull + 2;                 // [2]
+  uint32_t* tmemBaseSlot = (uint32_t*)(accEmpty + 2);
+  volatile uint32_t* giveUp = tmemBaseSlot + 1;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int mTiles = g.M / BM, nTiles = g.N / BN, kBlocks = g.K / BK;
+  const int numTiles = mTiles * nTiles;
+  const FusedArgs& f = g.f;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) { mbar_init(&fullBar[s], 1); mbar_init(&emptyBar[s], 1); }
+    for (int a = 0; a < 2; ++a) { mbar_init(&accFull[a], 1); mbar_init(&accEmpty[a], 4); }
+    *giveUp = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&mapA);
+    tma_prefetch_desc(&mapB);
+  }
+  if (warp == 1) tmem_alloc(tmemBaseSlot, TMEM_COLS);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmemBase = *tmemBaseSlot;
+  if (f.mode == 2 && f.nranks > 1) {
+    // the owners must have finished reducing the previous call before this one overwrites their slots
+    if (warp == 2 && lane < f.nranks && lane != f.rank) wait_flag64(&f.done[lane], f.epoch - 1, giveUp);
+    __syncthreads();
+  }
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (elect_one()) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < numTiles && ok; t += gridDim.x) {
+        const int mt = orderedMTile(f, t / nTiles, mTiles), nt = t % nTiles;
+        if (f.mode == 1 && f.nranks > 1 && mt / (f.rowsPerRank / BM) != f.rank) {
+          // this row block comes from a peer: wait until the communication warps have placed it
+          ok = wait_flag32(&f.blockReady[mt], (uint32_t)f.epoch, giveUp, false);
+          asm volatile("fence.proxy.async.global;" ::: "memory");   // their generic-proxy stores before my async-proxy loads
+          if (!ok) break;
+        }
+        for (int kb = 0; kb < kBlocks; ++kb) {
+          if (!mbar_wait(&emptyBar[stage], phase ^ 1, giveUp)) { ok = false; break; }
+          mbar_expect_tx(&fullBar[stage], STAGE_BYTES);
+          uint8_t* sa = smem + stage * STAGE_BYTES;
+          tma_load_2d(sa, &mapA, kb * BK, mt * BM, &fullBar[stage]);
+          tma_load_2d(sa + A_BYTES, &mapB, kb * BK, nt * BN, &fullBar[stage]);
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+      if (!ok) {
+        // let the copies already issued land before the block goes away (bounded)
+        for (int i = 0; i < 20000; ++i) __nanosleep(200);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (elect_one()) {
+      constexpr uint32_t idesc = umma_idesc_bf16(BM, BN);
+      int stage = 0;
+      uint32_t phase = 0;
+      int it = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < numTiles && ok; t += gridDim.x, ++it) {
+        const int ab = it & 1;
+        if (!mbar_wait(&accEmpty[ab], ((it >> 1) & 1) ^ 1, giveUp)) break;
+        tc_fence_after();
+        const uint32_t d = tmemBase + ab * BN;
+        for (int kb = 0; kb < kBlocks; ++kb) {
+          if (!mbar_wait(&fullBar[stage], phase, giveUp)) { ok = false; break; }
+          tc_fence_after();
+          const uint64_t da = umma_smem_desc_sw128(smem + stage * STAGE_BYTES);
+          const uint64_t db = umma_smem_desc_sw128(smem + stage * STAGE_BYTES + A_BYTES);
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k)       // +32 bytes of K per step: +2 in the 16-byte address field
+            umma_bf16(d, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0);
+          umma_commit(&emptyBar[stage]);              // the stage is free once these MMAs have read it
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (ok) umma_commit(&accFull[ab]);            // accumulator complete
+      }
+    }
+  } else if (warp < 6) {
+    // ------------------------------------------------------------ epilogue: TMEM -> bf16 -> global (local or peer)
+    const int quarter = warp & 3;                     // the 32 TMEM lanes this warp may read
+    int it = 0;
+    for (int t = blockIdx.x; t < numTiles; t += gridDim.x, ++it) {
+      const int mt = orderedMTile(f, t / nTiles, mTiles), nt = t % nTiles;
+      const int ab = it & 1;
+      if (!mbar_wait(&accFull[ab], (it >> 1) & 1, giveUp)) break;
+      tc_fence_after();
+      const int row = mt * BM + quarter * 32 + lane;
+      __nv_bfloat16* crow;
+      int owner = 0, tileInOwner = 0;
+      if (f.mode == 2 && f.nranks > 1) {
+        owner = row / f.rowsPerRank;
+        tileInOwner = ((mt * BM - owner * f.rowsPerRank) / BM) * nTiles + nt;
+        crow = f.slot[owner] + (size_t)(row - owner * f.rowsPerRank) * g.N + nt * BN;
+      } else {
+        crow = g.C + (size_t)row * g.ldc + nt * BN;
+      }
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld32(tmemBase + ((uint32_t)(quarter * 32) << 16) + ab * BN + c * 32, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int v = 0; v < 4; ++v) {
+          uint4 o;
+          o.x = pack_bf16x2(__uint_as_float(r[8 * v + 0]), __uint_as_float(r[8 * v + 1]));
+          o.y = pack_bf16x2(__uint_as_float(r[8 * v + 2]), __uint_as_float(r[8 * v + 3]));
+          o.z = pack_bf16x2(__uint_as_float(r[8 * v + 4]), __uint_as_float(r[8 * v + 5]));
+          o.w = pack_bf16x2(__uint_as_float(r[8 * v + 6]), __uint_as_float(r[8 * v + 7]));
+          st_peer16(crow + c * 32 + v * 8, o);
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&accEmpty[ab]);      // 4 epilogue warps release the accumulator
+      if (f.mode == 2 && f.nranks > 1) {
+        // publish the tile in its owner's memory once all four warps have stored their rows
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (warp == 2 && lane == 0) {
+          __threadfence_system();
+          st_rel_sys_u32(f.tileFlag[owner] + (size_t)f.rank * (f.rowsPerRank / BM) * nTiles + tileInOwner, (uint32_t)f.epoch);
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ communication warps (6..9)
+    const int ct = threadIdx.x - 6 * 32;              // 0..127
+    if (f.mode == 1 && f.nranks > 1) {
+      const int blocksPerRank = f.rowsPerRank / BM;
+      const size_t blockBytes = (size_t)BM * g.K * 2;
+      if (blockIdx.x == 0 && ct < f.nranks && ct != f.rank) st_rel_sys(f.peerArrive[ct], f.epoch);   // my shard is ready
+      // remote row blocks in the order the tiles will need them, dealt round-robin to the CTAs
+      const int remote = (f.nranks - 1) * blocksPerRank;
+      bool ok = true;
+      for (int i = blockIdx.x; i < remote && ok; i += gridDim.x) {
+        const int owner = (f.rank + 1 + i / blocksPerRank) % f.nranks;
+        const int blk = i % blocksPerRank;
+        if (ct == 0) ok = wait_flag64(&f.arrive[owner], f.epoch, giveUp);
+        asm volatile("bar.sync 2, 128;" ::: "memory");
+        if (*giveUp) break;
+        const uint4* src = (const uint4*)((const char*)f.peerA[owner] + (size_t)blk * blockBytes);
+        uint4* dst = (uint4*)((char*)f.gathered + ((size_t)owner * blocksPerRank + blk) * blockBytes);
+        const size_t n16 = blockBytes / 16;
+        for (size_t p = ct; p < n16; p += 128 * 4) {
+          uint4 v[4];
+#pragma unroll
+          for (int u = 0; u < 4; ++u) if (p + u * 128 < n16) v[u] = ld_peer16(src + p + u * 128);
+#pragma unroll
+          for (int u = 0; u < 4; ++u) if (p + u * 128 < n16) dst[p + u * 128] = v[u];
+        }
+        asm volatile("fence.proxy.async.global;" ::: "memory");
+        __threadfence();
+        asm volatile("bar.sync 2, 128;" ::: "memory");
+        if (ct == 0) st_rel_gpu_u32(&f.blockReady[owner * blocksPerRank + blk], (uint32_t)f.epoch);
+      }
+      // when every CTA is through, the peers may reuse their shards
+      asm volatile("bar.sync 2, 128;" ::: "memory");
+      if (ct == 0) {
+        __threadfence();
+        if (atomicAdd(f.doneCount, 1u) == gridDim.x - 1) {
+          *f.doneCount = 0;
+          __threadfence_system();
+          for (int j = 0; j < f.nranks; ++j) if (j != f.rank) st_rel_sys(f.peerDone[j], f.epoch);
+        }
+      }
+      if (blockIdx.x == 0 && ct < f.nranks && ct != f.rank) wait_flag64(&f.done[ct], f.epoch, giveUp);   // my shard stays put until read
+    } else if (f.mode == 2 && f.nranks > 1) {
+      // reduce the tiles I own as their n partial copies arrive: slot[j] written by rank j's epilogue
+      const int tilesMine = (f.rowsPerRank / BM) * nTiles;
+      for (int i = blockIdx.x; i < tilesMine; i += gridDim.x) {
+        const int tm = i / nTiles, tn = i % nTiles;
+        if (ct < f.nranks) wait_flag32(f.myTileFlags + (size_t)ct * tilesMine + i, (uint32_t)f.epoch, giveUp, true);
+        asm volatile("bar.sync 2, 128;" ::: "memory");
+        if (*giveUp) break;
+        // 128 rows x 256 columns: thread ct sums row ct of the tile over the n slots
+        const size_t rowOff = (size_t)(tm * BM + ct) * g.N + tn * BN;
+        for (int c = 0; c < BN; c += 8) {
+          float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+          for (int j = 0; j < f.nranks; ++j) {
+            uint4 v = ld_peer16(f.mySlots + (size_t)j * f.rowsPerRank * g.N + rowOff + c);
+            const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int q = 0; q < 4; ++q) { acc[2 * q] += __uint_as_float(w[q] << 16); acc[2 * q + 1] += __uint_as_float(w[q] & 0xffff0000u); }
+          }
+          uint4 o;
+          o.x = pack_bf16x2(acc[0], acc[1]); o.y = pack_bf16x2(acc[2], acc[3]);
+          o.z = pack_bf16x2(acc[4], acc[5]); o.w = pack_bf16x2(acc[6], acc[7]);
+          *(uint4*)(f.reduced + rowOff + c) = o;
+        }
+      }
+      // all my tiles reduced in every CTA: the peers may write the next call's partial tiles
+      asm volatile("bar.sync 2, 128;" ::: "memory");
+      if (ct == 0) {
+        __threadfence();
+        if (atomicAdd(f.doneCount, 1u) == gridDim.x - 1) {
+          *f.doneCount = 0;
+          __threadfence_system();
+          for (int j = 0; j < f.nranks; ++j) if (j != f.rank) st_rel_sys(f.peerDone[j], f.epoch);
+        }
+      }
+    }
+  }
+
+  // ---------------------------------------------------------------- leave
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmemBase, TMEM_COLS);
+  if (threadIdx.x == 0 && *giveUp) atomicExch(g.err, 1u);
+}
+
+// ---- host side
+typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiled encodeFn() {
+  static EncodeTiled fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess) fn = (EncodeTiled)p;
+    (void)cudaGetLastError();
+  });
+  return fn;
+}
+
+// rows x cols bf16, row-major (cols contiguous), tiles of boxRows x 64 columns, 128-byte swizzle
+ncclResult_t makeMap(CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols, uint32_t boxRows) {
+  EncodeTiled fn = encodeFn();
+  if (!fn) { DF_WARN("cuTensorMapEncodeTiled is not available"); return ncclSystemError; }
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {cols * 2};
+  cuuint32_t box[2] = {BK, boxRows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (void*)base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) { DF_WARN("cuTensorMapEncodeTiled failed (%d) for %llu x %llu at %p", (int)r, (unsigned long long)rows, (unsigned long long)cols, base); return ncclInvalidArgument; }
+  return ncclSuccess;
+}
+
+uint32_t* errWord() {                       // one device word per device, created on first use
+  static uint32_t* w[64] = {nullptr};
+  static std::mutex mu;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  std::lock_guard<std::mutex> l(mu);
+  if (!w[dev]) { cudaMalloc((void**)&w[dev], 4); cudaMemset(w[dev], 0, 4); }
+  return w[dev];
+}
+
+ncclResult_t launch(const void* A, const void* B, void* C, int M, int N, int K, const FusedArgs* f, cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0 || M % BM || N % BN || K % BK) {
+    DF_WARN("tcgen05 GEMM needs M %% %d == 0, N %% %d == 0, K %% %d == 0 (got %d x %d x %d)", BM, BN, BK, M, N, K);
+    return ncclInvalidArgument;
+  }
+  if (((uintptr_t)A | (uintptr_t)B | (uintptr_t)C) & 15) return ncclInvalidArgument;
+  CUtensorMap ma, mb;
+  DFCHECK(makeMap(&ma, A, (uint64_t)M, (uint64_t)K, BM));
+  DFCHECK(makeMap(&mb, B, (uint64_t)N, (uint64_t)K, BN));
+  static std::once_flag once;
+  std::call_once(once, [] { cudaFuncSetAttribute(dfcclGemmKernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES); });
+  GemmArgs g;
+  memset(&g, 0, sizeof(g));
+  g.C = (__nv_bfloat16*)C; g.M = M; g.N = N; g.K = K; g.ldc = N; g.err = errWord();
+  if (f) g.f = *f; else { g.f.nranks = 1; g.f.mode = 0; }
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const int tiles = (M / BM) * (N / BN);
+  // fused modes keep one CTA per SM even with few tiles: the communication warps of idle CTAs still work
+  const int grid = (g.f.mode == 0) ? (tiles < sms ? tiles : sms) : sms;
+  dfcclGemmKernel<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(ma, mb, g);
+  CUDACHECK(cudaGetLastError());
+  return ncclSuccess;
+}
+
+}  // namespace
+}  // namespace dfccl
+
+using namespace dfccl;
+#define DF_API extern "C" __attribute__((visibility("default")))
+
+// C[M,N] (bf16, row-major) = A[M,K] * B[N,K]^T, fp32 accumulation in tensor memory.
+DF_API ncclResult_t dfcclGemmBf16(const void* A, const void* B, void* C, int M, int N, int K, cudaStream_t stream) {
+  return launch(A, B, C, M, N, K, nullptr, stream);
+}
+
+// Non-zero after a kernel of this file gave up on a bounded wait (reads and clears the word).
+DF_API ncclResult_t dfcclGemmCheck(int* failed) {
+  uint32_t v = 0;
+  uint32_t* w = errWord();
+  CUDACHECK(cudaMemcpy(&v, w, 4, cudaMemcpyDeviceToHost));
+  if (v) CUDACHECK(cudaMemset(w, 0, 4));
+  if (failed) *failed = (int)v;
+  return ncclSuccess;
+}
+
+// The fused forms are driven from dfccl_b200/ops/fused_linear.py, which owns the symmetric buffers
+// and the rendezvous words; it passes them here packed in this struct (same layout as FusedArgs).
+DF_API ncclResult_t dfcclGemmFused(const void* A, const void* B, void* C, int M, int N, int K, const void* fusedArgs, size_t fusedBytes,
+                                   cudaStream_t stream) {
+  if (!fusedArgs || fusedBytes != sizeof(FusedArgs)) { DF_WARN("dfcclGemmFused: argument block of %zu bytes, expected %zu", fusedBytes, sizeof(FusedArgs)); return ncclInvalidArgument; }
+  FusedArgs f;
+  memcpy(&f, fusedArgs, sizeof(f));
+  if (f.nranks < 1 || f.nranks > 8 || f.rank < 0 || f.rank >= f.nranks) return ncclInvalidArgument;
+  if (f.nranks > 1 && (f.rowsPerRank % BM || f.rowsPerRank * f.nranks != M)) { DF_WARN("dfcclGemmFused: rows per rank must be a multiple of %d and sum to M", BM); return ncclInvalidArgument; }
+  return launch(A, B, C, M, N, K, &f, stream);
+}
+DF_API size_t dfcclGemmFusedArgsSize(void) { return sizeof(FusedArgs); }

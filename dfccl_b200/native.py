@@ -107,6 +107,10 @@ def lib() -> C.CDLL:
             "dfcclInjectFault": [vp, i, C.c_int64],
             "dfcclFusedSgdStep": [vp, vp, vp, vp, sz, i, C.c_float, C.c_float, C.c_float, i, vp],
             "dfcclOpsWarm": [],
+            "dfcclGemmBf16": [vp, vp, vp, i, i, i, vp],
+            "dfcclGemmCheck": [C.POINTER(i)],
+            "dfcclGemmFused": [vp, vp, vp, i, i, i, vp, sz, vp],
+            "dfcclHeapPeerBase": [vp, i, C.POINTER(vp)],
             "dfcclProbePeerCopy": [vp, i, sz, i, i, i, i, i, C.POINTER(C.c_double)],
             "dfcclProbeFlagRoundTrip": [vp, i, i, C.POINTER(C.c_double)],
             "dfcclAllReduceNoAlloc": [vp, vp, sz, i, C.c_float, vp],
@@ -116,6 +120,8 @@ def lib() -> C.CDLL:
             f = getattr(L, name)
             f.argtypes = args
             f.restype = i
+        L.dfcclGemmFusedArgsSize.argtypes = []
+        L.dfcclGemmFusedArgsSize.restype = C.c_size_t
         L.ncclGetErrorString.argtypes = [i]
         L.ncclGetErrorString.restype = C.c_char_p
         _lib = L
@@ -205,6 +211,11 @@ class Comm:
 
     def free(self, ptr: int) -> None:
         check(lib().dfcclMemFree(C.c_void_p(ptr), self.handle), "dfcclMemFree")
+
+    def peer_base(self, peer: int) -> int:
+        b = C.c_void_p()
+        check(lib().dfcclHeapPeerBase(self.handle, peer, C.byref(b)), "dfcclHeapPeerBase")
+        return b.value
 
     def heap_info(self):
         base, nbytes, used = C.c_void_p(), C.c_size_t(), C.c_size_t()

@@ -1,0 +1,1 @@
+from .gemm import matmul_nt, gemm_supported

@@ -1,0 +1,60 @@
+"""The hand-written tcgen05 / TMEM / TMA GEMM against a PyTorch fp32 reference."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("m,n,k", [(128, 256, 64), (128, 256, 512), (256, 512, 1024), (1024, 1024, 1024),
+                                    (2048, 3072, 1024), (4096, 1024, 4096), (8192, 2048, 1024)])
+def test_gemm_matches_fp32_reference(m, n, k):
+    from dfccl_b200.ops import gemm
+    torch.manual_seed(m + n + k)
+    a = torch.randn(m, k, device="cuda", dtype=torch.bfloat16)
+    b = torch.randn(n, k, device="cuda", dtype=torch.bfloat16)
+    c = gemm.matmul_nt(a, b)
+    torch.cuda.synchronize()
+    assert gemm.check_kernels()
+    ref = a.float() @ b.float().t()
+    err = (c.float() - ref).abs().max().item()
+    scale = ref.abs().max().item()
+    assert err <= 1e-2 * scale + 1e-2, (err, scale)
+    # the second call reuses tensor memory and barriers of a fresh launch
+    c2 = gemm.matmul_nt(a, b)
+    torch.cuda.synchronize()
+    assert torch.equal(c, c2)
+
+
+def test_gemm_rejects_shapes_it_cannot_tile():
+    from dfccl_b200.ops import gemm
+    a = torch.randn(100, 64, device="cuda", dtype=torch.bfloat16)
+    b = torch.randn(256, 64, device="cuda", dtype=torch.bfloat16)
+    with pytest.raises(ValueError):
+        gemm.matmul_nt(a, b)
+
+
+def test_gemm_throughput_report():
+    """Not an assertion on speed: prints achieved TFLOP/s next to cuBLAS for the record."""
+    from dfccl_b200.ops import gemm
+    m = n = k = 8192
+    a = torch.randn(m, k, device="cuda", dtype=torch.bfloat16)
+    b = torch.randn(n, k, device="cuda", dtype=torch.bfloat16)
+    out = torch.empty(m, n, device="cuda", dtype=torch.bfloat16)
+
+    def bench(fn):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(10):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / 10
+
+    ours = bench(lambda: gemm.matmul_nt(a, b, out))
+    cublas = bench(lambda: torch.matmul(a, b.t(), out=out))
+    flops = 2.0 * m * n * k
+    print(f"tcgen05 gemm 8192^3: {ours:.3f} ms = {flops / ours / 1e9:.0f} TFLOP/s; cuBLAS {cublas:.3f} ms = {flops / cublas / 1e9:.0f} TFLOP/s")
+    assert gemm.check_kernels()
