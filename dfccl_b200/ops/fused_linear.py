@@ -1,0 +1,150 @@
+"""Tensor-parallel linear layers whose collective runs inside the GEMM kernel.
+
+``AllGatherGemm``   y = all_gather(x_shard) @ W_local^T     (sequence-parallel column-parallel layer)
+``GemmReduceScatter`` y_shard = reduce_scatter(x_local @ W_local^T)   (row-parallel layer, sequence-sharded output)
+
+Both own their symmetric-heap buffers and rendezvous words and drive the fused modes of
+``dfcclGemmFused`` (csrc/src/gemm/tcgen05_gemm.cu): peers' shards are pulled by communication
+warps of the GEMM kernel block by block while the tensor cores work on blocks already present;
+partial output tiles are stored straight into their owner's memory and reduced there as they
+arrive.  Heap offsets are exchanged once at construction over ``torch.distributed``.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import List, Optional
+
+import torch
+import torch.distributed as dist
+
+from .. import native as nv
+from ..utils.tensors import tensor_from_ptr
+from .gemm import BM, BN, BK
+
+
+class _FusedArgs(C.Structure):
+    _fields_ = [
+        ("nranks", C.c_int), ("rank", C.c_int), ("rowsPerRank", C.c_int),
+        ("peerA", C.c_void_p * 8), ("gathered", C.c_void_p), ("blockReady", C.c_void_p),
+        ("slot", C.c_void_p * 8), ("tileFlag", C.c_void_p * 8), ("mySlots", C.c_void_p), ("myTileFlags", C.c_void_p),
+        ("reduced", C.c_void_p),
+        ("arrive", C.c_void_p), ("done", C.c_void_p), ("peerArrive", C.c_void_p * 8), ("peerDone", C.c_void_p * 8),
+        ("doneCount", C.c_void_p), ("epoch", C.c_uint64), ("mode", C.c_int),
+    ]
+
+
+class TpGroup:
+    """A tensor-parallel group: this library's communicator over the group plus the matching
+    ``torch.distributed`` group (used only to exchange offsets at construction)."""
+
+    def __init__(self, comm: nv.Comm, pg: Optional["dist.ProcessGroup"], device: torch.device):
+        self.comm, self.pg, self.device = comm, pg, device
+        self.rank, self.n = comm.rank, comm.nranks
+        assert nv.lib().dfcclGemmFusedArgsSize() == C.sizeof(_FusedArgs), "argument block layout mismatch"
+        self._base = [comm.peer_base(j) for j in range(self.n)]
+        self._mybase = comm.heap_info()[0]
+
+    def alloc(self, nbytes: int, zero: bool = True):
+        """Allocate in the symmetric heap; returns (local pointer, [address of every rank's copy as mapped here])."""
+        p = self.comm.alloc(max(nbytes, 16))            # heap memory is zeroed on allocation
+        off = p - self._mybase
+        if self.n > 1:
+            offs: List[int] = [0] * self.n
+            dist.all_gather_object(offs, off, group=self.pg)
+        else:
+            offs = [off]
+        return p, [self._base[j] + offs[j] for j in range(self.n)]
+
+    def barrier(self):
+        if self.n > 1:
+            dist.barrier(group=self.pg)
+
+
+class _Rendezvous:
+    def __init__(self, tp: TpGroup):
+        n = tp.n
+        self.p, peers = tp.alloc(8 * n * 2 + 64)
+        self.arrive, self.done = self.p, self.p + 8 * n
+        self.peer_arrive = [peers[j] + 8 * tp.rank for j in range(n)]
+        self.peer_done = [peers[j] + 8 * n + 8 * tp.rank for j in range(n)]
+        self.done_count = torch.zeros(1, dtype=torch.int32, device=tp.device)
+        self.epoch = 0
+
+
+class AllGatherGemm:
+    """y[M, N] = concat_over_ranks(x_shard)[M, K] @ w[N, K]^T with the all-gather inside the GEMM."""
+
+    def __init__(self, tp: TpGroup, rows_per_rank: int, k: int, n_out: int):
+        assert rows_per_rank % BM == 0 and k % BK == 0 and n_out % BN == 0
+        self.tp, self.rows, self.k, self.n_out = tp, rows_per_rank, k, n_out
+        self.m = rows_per_rank * tp.n
+        gp, peers = tp.alloc(self.m * k * 2)
+        self.gathered = tensor_from_ptr(gp, (self.m, k), torch.bfloat16, tp.device)
+        self.shard = self.gathered[tp.rank * rows_per_rank:(tp.rank + 1) * rows_per_rank]   # write the input here
+        self._peer_shard = [peers[j] + j * rows_per_rank * k * 2 for j in range(tp.n)]
+        self.block_ready = torch.zeros(self.m // BM, dtype=torch.int32, device=tp.device)
+        self.rv = _Rendezvous(tp)
+        tp.barrier()
+
+    def __call__(self, x_shard: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        tp = self.tp
+        if x_shard.data_ptr() != self.shard.data_ptr():
+            self.shard.copy_(x_shard)
+        if out is None:
+            out = torch.empty(self.m, self.n_out, dtype=torch.bfloat16, device=tp.device)
+        self.rv.epoch += 1
+        a = _FusedArgs()
+        a.nranks, a.rank, a.rowsPerRank, a.mode, a.epoch = tp.n, tp.rank, self.rows, 1, self.rv.epoch
+        for j in range(tp.n):
+            a.peerA[j] = self._peer_shard[j]
+            a.peerArrive[j] = self.rv.peer_arrive[j]
+            a.peerDone[j] = self.rv.peer_done[j]
+        a.gathered, a.blockReady = self.gathered.data_ptr(), self.block_ready.data_ptr()
+        a.arrive, a.done, a.doneCount = self.rv.arrive, self.rv.done, self.rv.done_count.data_ptr()
+        w = w.contiguous()
+        nv.check(nv.lib().dfcclGemmFused(self.gathered.data_ptr(), w.data_ptr(), out.data_ptr(), self.m, self.n_out, self.k,
+                                         C.byref(a), C.sizeof(a), torch.cuda.current_stream(tp.device).cuda_stream), "dfcclGemmFused(ag)")
+        return out
+
+
+class GemmReduceScatter:
+    """y_shard[M/n, N] = sum_over_ranks(x[M, K_local] @ w[N, K_local]^T)[my rows] with the reduce-scatter
+    inside the GEMM: the epilogue stores partial tiles into their owner's memory, the owner sums them."""
+
+    def __init__(self, tp: TpGroup, m: int, k_local: int, n_out: int):
+        assert m % (BM * tp.n) == 0 and k_local % BK == 0 and n_out % BN == 0
+        self.tp, self.m, self.k, self.n_out = tp, m, k_local, n_out
+        self.rows = m // tp.n
+        self.tiles_mine = (self.rows // BM) * (n_out // BN)
+        sp, speers = tp.alloc(tp.n * self.rows * n_out * 2)
+        fp, fpeers = tp.alloc(tp.n * self.tiles_mine * 4)
+        self._slots, self._flags = sp, fp
+        # where MY partial tiles go in owner j's memory: its slot number tp.rank
+        self._slot_at = [speers[j] + tp.rank * self.rows * n_out * 2 for j in range(tp.n)]
+        self._flag_at = list(fpeers)
+        self.rv = _Rendezvous(tp)
+        self._dummy = torch.empty(16, dtype=torch.bfloat16, device=tp.device)
+        tp.barrier()
+
+    def __call__(self, x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        tp = self.tp
+        x, w = x.contiguous(), w.contiguous()
+        if out is None:
+            out = torch.empty(self.rows, self.n_out, dtype=torch.bfloat16, device=tp.device)
+        if tp.n == 1:
+            nv.check(nv.lib().dfcclGemmBf16(x.data_ptr(), w.data_ptr(), out.data_ptr(), self.m, self.n_out, self.k,
+                                            torch.cuda.current_stream(tp.device).cuda_stream), "dfcclGemmBf16")
+            return out
+        self.rv.epoch += 1
+        a = _FusedArgs()
+        a.nranks, a.rank, a.rowsPerRank, a.mode, a.epoch = tp.n, tp.rank, self.rows, 2, self.rv.epoch
+        for j in range(tp.n):
+            a.slot[j] = self._slot_at[j]
+            a.tileFlag[j] = self._flag_at[j]
+            a.peerArrive[j] = self.rv.peer_arrive[j]
+            a.peerDone[j] = self.rv.peer_done[j]
+        a.mySlots, a.myTileFlags, a.reduced = self._slots, self._flags, out.data_ptr()
+        a.arrive, a.done, a.doneCount = self.rv.arrive, self.rv.done, self.rv.done_count.data_ptr()
+        nv.check(nv.lib().dfcclGemmFused(x.data_ptr(), w.data_ptr(), self._dummy.data_ptr(), self.m, self.n_out, self.k,
+                                         C.byref(a), C.sizeof(a), torch.cuda.current_stream(tp.device).cuda_stream), "dfcclGemmFused(rs)")
+        return out

@@ -180,3 +180,49 @@ def launch(world, backend, scenario, timeout=240):
             if p.is_alive():
                 p.terminate()       # the exact children started above
     return results
+
+
+def scenario_fused_tp(nv, comm, rank, world, backend):
+    """all-gather -> GEMM and GEMM -> reduce-scatter fused kernels against PyTorch fp32 references."""
+    import torch
+    import torch.distributed as dist
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    os.environ.setdefault("MASTER_PORT", "29577")
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from dfccl_b200.ops.fused_linear import AllGatherGemm, GemmReduceScatter, TpGroup
+    from dfccl_b200.ops import gemm
+    dev = torch.device("cuda", rank)
+    tp = TpGroup(comm, dist.group.WORLD, dev)
+    out = {}
+    for rows, k, n_out in ((256, 1024, 1536), (1024, 1024, 2048)):
+        g = torch.Generator(device="cpu").manual_seed(5)
+        x_full = torch.randn(rows * world, k, generator=g).to(torch.bfloat16)
+        w = torch.randn(n_out, k, generator=torch.Generator().manual_seed(100 + rank)).to(torch.bfloat16).to(dev)
+        op = AllGatherGemm(tp, rows, k, n_out)
+        for it in range(3):
+            xs = (x_full[rank * rows:(rank + 1) * rows] * (it + 1)).to(dev)
+            y = op(xs, w)
+            torch.cuda.synchronize()
+            ref = (x_full.to(dev).float() * (it + 1)) @ w.float().t()
+            err = (y.float() - ref).abs().max().item() / (ref.abs().max().item() + 1e-6)
+            assert err < 1e-2, ("ag-gemm", rows, k, n_out, it, err)
+        # row-parallel: every rank holds a K-slice of x and w, output rows are scattered
+        m = rows * world
+        kl = k // world
+        xr = torch.randn(m, k, generator=torch.Generator().manual_seed(7)).to(torch.bfloat16)
+        wr = torch.randn(n_out, k, generator=torch.Generator().manual_seed(8)).to(torch.bfloat16)
+        op2 = GemmReduceScatter(tp, m, kl, n_out)
+        for it in range(3):
+            xl = (xr[:, rank * kl:(rank + 1) * kl] * (it + 1)).contiguous().to(dev)
+            wl = wr[:, rank * kl:(rank + 1) * kl].contiguous().to(dev)
+            ys = op2(xl, wl)
+            torch.cuda.synchronize()
+            # reference with the same rounding points: per-rank partial products in bf16, summed in fp32
+            parts = [((xr[:, q * kl:(q + 1) * kl].to(dev).float() * (it + 1)) @ wr[:, q * kl:(q + 1) * kl].to(dev).float().t()).to(torch.bfloat16).float() for q in range(world)]
+            ref = sum(parts)[rank * rows:(rank + 1) * rows]
+            err = (ys.float() - ref).abs().max().item() / (ref.abs().max().item() + 1e-6)
+            assert err < 1e-2, ("gemm-rs", rows, k, n_out, it, err)
+        assert gemm.check_kernels()
+    dist.barrier()
+    dist.destroy_process_group()
+    return out

@@ -29,3 +29,10 @@ def test_gpu_processes_daemon():
 def test_gpu_processes_stream_interface():
     import torch
     mp_worker.launch(min(torch.cuda.device_count(), 4), "cuda", "stream")
+
+
+@pytest.mark.gpu
+@pytest.mark.multigpu
+def test_fused_tensor_parallel_gemms():
+    import torch
+    mp_worker.launch(2 if torch.cuda.device_count() < 4 else 4, "cuda", "fused_tp", timeout=300)
