@@ -21,11 +21,14 @@ from dfccl_b200.parallel import init_distributed
 
 
 def timeit(fn, iters, world):
+    """Device time per call.  A 2 ms kernel is queued first so that the host is well ahead of the GPU
+    when the timed calls start: what is measured is the kernels, not Python's enqueue rate."""
     for _ in range(5):
         fn()
     torch.cuda.synchronize()
     dist.barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda._sleep(4_000_000)
     e0.record()
     for _ in range(iters):
         fn()

@@ -18,7 +18,9 @@
 #include "tc_common.h"
 #include "dfccl.h"
 #include "../common/log.h"
+#include <map>
 #include <mutex>
+#include <tuple>
 
 namespace dfccl {
 namespace {
@@ -360,7 +362,28 @@ EncodeTiled encodeFn() {
 }
 
 // rows x cols bf16, row-major (cols contiguous), tiles of boxRows x 64 columns, 128-byte swizzle
+ncclResult_t makeMapUncached(CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols, uint32_t boxRows);
+
+// Encoding a tensor map costs microseconds of host time per call; layers call with the same few
+// (pointer, shape) pairs every step, so the encoded maps are kept.
 ncclResult_t makeMap(CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols, uint32_t boxRows) {
+  struct Key { const void* p; uint64_t r, c; uint32_t b; bool operator<(const Key& o) const { return std::tie(p, r, c, b) < std::tie(o.p, o.r, o.c, o.b); } };
+  static std::map<Key, CUtensorMap> cache;
+  static std::mutex mu;
+  Key k{base, rows, cols, boxRows};
+  {
+    std::lock_guard<std::mutex> l(mu);
+    auto it = cache.find(k);
+    if (it != cache.end()) { *m = it->second; return ncclSuccess; }
+  }
+  DFCHECK(makeMapUncached(m, base, rows, cols, boxRows));
+  std::lock_guard<std::mutex> l(mu);
+  if (cache.size() > 4096) cache.clear();
+  cache[k] = *m;
+  return ncclSuccess;
+}
+
+ncclResult_t makeMapUncached(CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols, uint32_t boxRows) {
   EncodeTiled fn = encodeFn();
   if (!fn) { DF_WARN("cuTensorMapEncodeTiled is not available"); return ncclSystemError; }
   cuuint64_t dims[2] = {cols, rows};

@@ -84,6 +84,7 @@ class AllGatherGemm:
         self._peer_shard = [peers[j] + j * rows_per_rank * k * 2 for j in range(tp.n)]
         self.block_ready = torch.zeros(self.m // BM, dtype=torch.int32, device=tp.device)
         self.rv = _Rendezvous(tp)
+        self._args = None
         tp.barrier()
 
     def __call__(self, x_shard: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
@@ -93,14 +94,18 @@ class AllGatherGemm:
         if out is None:
             out = torch.empty(self.m, self.n_out, dtype=torch.bfloat16, device=tp.device)
         self.rv.epoch += 1
-        a = _FusedArgs()
-        a.nranks, a.rank, a.rowsPerRank, a.mode, a.epoch = tp.n, tp.rank, self.rows, 1, self.rv.epoch
-        for j in range(tp.n):
-            a.peerA[j] = self._peer_shard[j]
-            a.peerArrive[j] = self.rv.peer_arrive[j]
-            a.peerDone[j] = self.rv.peer_done[j]
-        a.gathered, a.blockReady = self.gathered.data_ptr(), self.block_ready.data_ptr()
-        a.arrive, a.done, a.doneCount = self.rv.arrive, self.rv.done, self.rv.done_count.data_ptr()
+        a = self._args
+        if a is None:                                   # built once: only the epoch changes between calls
+            a = self._args = _FusedArgs()
+            a.nranks, a.rank, a.rowsPerRank, a.mode = tp.n, tp.rank, self.rows, 1
+            for j in range(tp.n):
+                a.peerA[j] = self._peer_shard[j]
+                a.peerArrive[j] = self.rv.peer_arrive[j]
+                a.peerDone[j] = self.rv.peer_done[j]
+            a.gathered, a.blockReady = self.gathered.data_ptr(), self.block_ready.data_ptr()
+            a.arrive, a.done, a.doneCount = self.rv.arrive, self.rv.done, self.rv.done_count.data_ptr()
+            self._fn, self._sz, self._gp = nv.lib().dfcclGemmFused, C.sizeof(a), self.gathered.data_ptr()
+        a.epoch = self.rv.epoch
         w = w.contiguous()
         nv.check(nv.lib().dfcclGemmFused(self.gathered.data_ptr(), w.data_ptr(), out.data_ptr(), self.m, self.n_out, self.k,
                                          C.byref(a), C.sizeof(a), torch.cuda.current_stream(tp.device).cuda_stream), "dfcclGemmFused(ag)")
@@ -124,6 +129,7 @@ class GemmReduceScatter:
         self._flag_at = list(fpeers)
         self.rv = _Rendezvous(tp)
         self._dummy = torch.empty(16, dtype=torch.bfloat16, device=tp.device)
+        self._args = None
         tp.barrier()
 
     def __call__(self, x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
@@ -136,15 +142,18 @@ class GemmReduceScatter:
                                             torch.cuda.current_stream(tp.device).cuda_stream), "dfcclGemmBf16")
             return out
         self.rv.epoch += 1
-        a = _FusedArgs()
-        a.nranks, a.rank, a.rowsPerRank, a.mode, a.epoch = tp.n, tp.rank, self.rows, 2, self.rv.epoch
-        for j in range(tp.n):
-            a.slot[j] = self._slot_at[j]
-            a.tileFlag[j] = self._flag_at[j]
-            a.peerArrive[j] = self.rv.peer_arrive[j]
-            a.peerDone[j] = self.rv.peer_done[j]
-        a.mySlots, a.myTileFlags, a.reduced = self._slots, self._flags, out.data_ptr()
-        a.arrive, a.done, a.doneCount = self.rv.arrive, self.rv.done, self.rv.done_count.data_ptr()
+        a = self._args
+        if a is None:
+            a = self._args = _FusedArgs()
+            a.nranks, a.rank, a.rowsPerRank, a.mode = tp.n, tp.rank, self.rows, 2
+            for j in range(tp.n):
+                a.slot[j] = self._slot_at[j]
+                a.tileFlag[j] = self._flag_at[j]
+                a.peerArrive[j] = self.rv.peer_arrive[j]
+                a.peerDone[j] = self.rv.peer_done[j]
+            a.mySlots, a.myTileFlags = self._slots, self._flags
+            a.arrive, a.done, a.doneCount = self.rv.arrive, self.rv.done, self.rv.done_count.data_ptr()
+        a.epoch, a.reduced = self.rv.epoch, out.data_ptr()
         nv.check(nv.lib().dfcclGemmFused(x.data_ptr(), w.data_ptr(), self._dummy.data_ptr(), self.m, self.n_out, self.k,
                                          C.byref(a), C.sizeof(a), torch.cuda.current_stream(tp.device).cuda_stream), "dfcclGemmFused(rs)")
         return out
