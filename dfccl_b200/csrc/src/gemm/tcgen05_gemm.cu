@@ -31,6 +31,7 @@ constexpr int BM = 128, BN = 256, BK = 64, STAGES = 4, UMMA_K = 16;
 constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr int TMEM_COLS = 512;                       // two accumulators of BN fp32 columns
 constexpr int NUM_THREADS = 320;                     // 10 warps
+constexpr int GATHER_PIECES = 8;                     // pieces a 128-row block is pulled in (all-gather -> GEMM)
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
 
 struct FusedArgs {
@@ -39,7 +40,7 @@ struct FusedArgs {
   int rowsPerRank;                  // rows of A each rank contributes (multiple of BM)
   const __nv_bfloat16* peerA[8];    // each rank's shard [rowsPerRank, K] as mapped here (own entry unused)
   __nv_bfloat16* gathered;          // local [M, K] buffer the tensor map of A covers
-  uint32_t* blockReady;             // [M / BM] local flags, value = epoch when the row block is in place
+  uint32_t* blockReady;             // [M / BM] local counters: a block is in place when it reaches epoch * GATHER_PIECES
   // ---- GEMM -> reduce-scatter
   __nv_bfloat16* slot[8];           // owner j's receive area for MY partial tiles: [rowsPerRank, N] bf16, as mapped here
   uint32_t* tileFlag[8];            // owner j's flags [nranks][tilesPerOwner] as mapped here (I write row `rank`)
@@ -168,7 +169,7 @@ dfcclGemmKernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
         const int mt = orderedMTile(f, t / nTiles, mTiles), nt = t % nTiles;
         if (f.mode == 1 && f.nranks > 1 && mt / (f.rowsPerRank / BM) != f.rank) {
           // this row block comes from a peer: wait until the communication warps have placed it
-          ok = wait_flag32(&f.blockReady[mt], (uint32_t)f.epoch, giveUp, false);
+          ok = wait_flag32(&f.blockReady[mt], (uint32_t)f.epoch * GATHER_PIECES, giveUp, false);
           asm volatile("fence.proxy.async.global;" ::: "memory");   // their generic-proxy stores before my async-proxy loads
           if (!ok) break;
         }
@@ -266,29 +267,32 @@ dfcclGemmKernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
       const int blocksPerRank = f.rowsPerRank / BM;
       const size_t blockBytes = (size_t)BM * g.K * 2;
       if (blockIdx.x == 0 && ct < f.nranks && ct != f.rank) st_rel_sys(f.peerArrive[ct], f.epoch);   // my shard is ready
-      // remote row blocks in the order the tiles will need them, dealt round-robin to the CTAs
-      const int remote = (f.nranks - 1) * blocksPerRank;
+      // remote row blocks in the order the tiles will need them, each cut into PIECES so that every CTA
+      // has loads in flight (one CTA alone moves a few GB/s); a block is ready when all its pieces are
+      const int remote = (f.nranks - 1) * blocksPerRank * GATHER_PIECES;
+      const size_t pieceBytes = blockBytes / GATHER_PIECES;
       bool ok = true;
       for (int i = blockIdx.x; i < remote && ok; i += gridDim.x) {
-        const int owner = (f.rank + 1 + i / blocksPerRank) % f.nranks;
-        const int blk = i % blocksPerRank;
+        const int bi = i / GATHER_PIECES, piece = i % GATHER_PIECES;
+        const int owner = (f.rank + 1 + bi / blocksPerRank) % f.nranks;
+        const int blk = bi % blocksPerRank;
         if (ct == 0) ok = wait_flag64(&f.arrive[owner], f.epoch, giveUp);
         asm volatile("bar.sync 2, 128;" ::: "memory");
         if (*giveUp) break;
-        const uint4* src = (const uint4*)((const char*)f.peerA[owner] + (size_t)blk * blockBytes);
-        uint4* dst = (uint4*)((char*)f.gathered + ((size_t)owner * blocksPerRank + blk) * blockBytes);
-        const size_t n16 = blockBytes / 16;
-        for (size_t p = ct; p < n16; p += 128 * 4) {
-          uint4 v[4];
+        const uint4* src = (const uint4*)((const char*)f.peerA[owner] + (size_t)blk * blockBytes + (size_t)piece * pieceBytes);
+        uint4* dst = (uint4*)((char*)f.gathered + ((size_t)owner * blocksPerRank + blk) * blockBytes + (size_t)piece * pieceBytes);
+        const size_t n16 = pieceBytes / 16;
+        for (size_t p = ct; p < n16; p += 128 * 8) {
+          uint4 v[8];
 #pragma unroll
-          for (int u = 0; u < 4; ++u) if (p + u * 128 < n16) v[u] = ld_peer16(src + p + u * 128);
+          for (int u = 0; u < 8; ++u) if (p + u * 128 < n16) v[u] = ld_peer16(src + p + u * 128);
 #pragma unroll
-          for (int u = 0; u < 4; ++u) if (p + u * 128 < n16) dst[p + u * 128] = v[u];
+          for (int u = 0; u < 8; ++u) if (p + u * 128 < n16) dst[p + u * 128] = v[u];
         }
         asm volatile("fence.proxy.async.global;" ::: "memory");
         __threadfence();
         asm volatile("bar.sync 2, 128;" ::: "memory");
-        if (ct == 0) st_rel_gpu_u32(&f.blockReady[owner * blocksPerRank + blk], (uint32_t)f.epoch);
+        if (ct == 0) atomicAdd(&f.blockReady[owner * blocksPerRank + blk], 1u);     // release: the fence above
       }
       // when every CTA is through, the peers may reuse their shards
       asm volatile("bar.sync 2, 128;" ::: "memory");
@@ -309,20 +313,37 @@ dfcclGemmKernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
         if (ct < f.nranks) wait_flag32(f.myTileFlags + (size_t)ct * tilesMine + i, (uint32_t)f.epoch, giveUp, true);
         asm volatile("bar.sync 2, 128;" ::: "memory");
         if (*giveUp) break;
-        // 128 rows x 256 columns: thread ct sums row ct of the tile over the n slots
-        const size_t rowOff = (size_t)(tm * BM + ct) * g.N + tn * BN;
-        for (int c = 0; c < BN; c += 8) {
-          float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-          for (int j = 0; j < f.nranks; ++j) {
-            uint4 v = ld_peer16(f.mySlots + (size_t)j * f.rowsPerRank * g.N + rowOff + c);
-            const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+        // 128 rows x 256 columns = 4096 chunks of 16 bytes; consecutive threads take consecutive chunks of a
+        // row (coalesced), four chunks in flight per thread and slot
+        const size_t tileOff = (size_t)(tm * BM) * g.N + tn * BN;
+        for (int p = ct; p < BM * (BN / 8); p += 128 * 4) {
+          float acc[4][8];
+          size_t off[4];
 #pragma unroll
-            for (int q = 0; q < 4; ++q) { acc[2 * q] += __uint_as_float(w[q] << 16); acc[2 * q + 1] += __uint_as_float(w[q] & 0xffff0000u); }
+          for (int u = 0; u < 4; ++u) {
+            const int q = p + u * 128;                       // chunk index: row = q / 32, 16-byte column = q % 32
+            off[u] = tileOff + (size_t)(q >> 5) * g.N + (q & 31) * 8;
+#pragma unroll
+            for (int e = 0; e < 8; ++e) acc[u][e] = 0.f;
           }
-          uint4 o;
-          o.x = pack_bf16x2(acc[0], acc[1]); o.y = pack_bf16x2(acc[2], acc[3]);
-          o.z = pack_bf16x2(acc[4], acc[5]); o.w = pack_bf16x2(acc[6], acc[7]);
-          *(uint4*)(f.reduced + rowOff + c) = o;
+          for (int j = 0; j < f.nranks; ++j) {
+            uint4 v[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) v[u] = ld_peer16(f.mySlots + (size_t)j * f.rowsPerRank * g.N + off[u]);
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+              const uint32_t w[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
+#pragma unroll
+              for (int q = 0; q < 4; ++q) { acc[u][2 * q] += __uint_as_float(w[q] << 16); acc[u][2 * q + 1] += __uint_as_float(w[q] & 0xffff0000u); }
+            }
+          }
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            uint4 o;
+            o.x = pack_bf16x2(acc[u][0], acc[u][1]); o.y = pack_bf16x2(acc[u][2], acc[u][3]);
+            o.z = pack_bf16x2(acc[u][4], acc[u][5]); o.w = pack_bf16x2(acc[u][6], acc[u][7]);
+            *(uint4*)(f.reduced + off[u]) = o;
+          }
         }
       }
       // all my tiles reduced in every CTA: the peers may write the next call's partial tiles
