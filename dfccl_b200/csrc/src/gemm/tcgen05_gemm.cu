@@ -32,7 +32,9 @@ constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTE
 constexpr int TMEM_COLS = 512;                       // two accumulators of BN fp32 columns
 constexpr int NUM_THREADS = 320;                     // 10 warps
 constexpr int GATHER_PIECES = 8;                     // pieces a 128-row block is pulled in (all-gather -> GEMM)
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+constexpr int EPI_ROW_BYTES = 64 * 2 + 16;            // one staged row: 64 bf16 columns + 16 bytes so that rows start in different banks
+constexpr int EPI_WARP_BYTES = 32 * EPI_ROW_BYTES;   // 32 rows per epilogue warp
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 4 * EPI_WARP_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
 
 struct FusedArgs {
   // ---- all-gather -> GEMM
@@ -128,7 +130,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
 dfcclGemmKernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB, const GemmArgs g) {
   extern __shared__ uint8_t smemRaw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smemRaw + 1023) & ~(uintptr_t)1023);
-  uint64_t* fullBar = (uint64_t*)(smem + STAGES * STAGE_BYTES);
+  uint8_t* epiSmem = smem + STAGES * STAGE_BYTES;
+  uint64_t* fullBar = (uint64_t*)(epiSmem + 4 * EPI_WARP_BYTES);
   uint64_t* emptyBar = fullBar + STAGES;
   uint64_t* accFull = emptyBar + STAGES;            // [2]
   uint64_t* accEmpty = accFull + 2;                 // [2]
@@ -233,20 +236,38 @@ dfcclGemmKernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
       } else {
         crow = g.C + (size_t)row * g.ldc + nt * BN;
       }
+      // 64 columns at a time: registers -> this warp's staging rows in shared memory -> global, so that
+      // every store instruction writes whole 128-byte row segments (what NVLink and DRAM both want)
+      // instead of 32 scattered 16-byte pieces
+      uint8_t* stage = epiSmem + (warp - 2) * EPI_WARP_BYTES;
+      __nv_bfloat16* cbase = crow - (size_t)lane * (f.mode == 2 && f.nranks > 1 ? g.N : g.ldc);    // row 0 of this warp's 32 rows
+      const size_t rowStride = (f.mode == 2 && f.nranks > 1) ? (size_t)g.N : (size_t)g.ldc;
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld32(tmemBase + ((uint32_t)(quarter * 32) << 16) + ab * BN + c * 32, r);
-        tmem_ld_wait();
+      for (int c4 = 0; c4 < BN / 64; ++c4) {
 #pragma unroll
-        for (int v = 0; v < 4; ++v) {
-          uint4 o;
-          o.x = pack_bf16x2(__uint_as_float(r[8 * v + 0]), __uint_as_float(r[8 * v + 1]));
-          o.y = pack_bf16x2(__uint_as_float(r[8 * v + 2]), __uint_as_float(r[8 * v + 3]));
-          o.z = pack_bf16x2(__uint_as_float(r[8 * v + 4]), __uint_as_float(r[8 * v + 5]));
-          o.w = pack_bf16x2(__uint_as_float(r[8 * v + 6]), __uint_as_float(r[8 * v + 7]));
-          st_peer16(crow + c * 32 + v * 8, o);
+        for (int h = 0; h < 2; ++h) {
+          uint32_t r[32];
+          tmem_ld32(tmemBase + ((uint32_t)(quarter * 32) << 16) + ab * BN + c4 * 64 + h * 32, r);
+          tmem_ld_wait();
+          uint4* srow = (uint4*)(stage + lane * EPI_ROW_BYTES + h * 64);
+#pragma unroll
+          for (int v = 0; v < 4; ++v) {
+            uint4 o;
+            o.x = pack_bf16x2(__uint_as_float(r[8 * v + 0]), __uint_as_float(r[8 * v + 1]));
+            o.y = pack_bf16x2(__uint_as_float(r[8 * v + 2]), __uint_as_float(r[8 * v + 3]));
+            o.z = pack_bf16x2(__uint_as_float(r[8 * v + 4]), __uint_as_float(r[8 * v + 5]));
+            o.w = pack_bf16x2(__uint_as_float(r[8 * v + 6]), __uint_as_float(r[8 * v + 7]));
+            srow[v] = o;
+          }
         }
+        __syncwarp();
+#pragma unroll
+        for (int t = 0; t < 8; ++t) {                 // 32 rows x 8 chunks of 16 bytes; 8 lanes cover one row segment
+          const int chunk = t * 32 + lane, rr = chunk >> 3, cc = chunk & 7;
+          const uint4 o = *(const uint4*)(stage + rr * EPI_ROW_BYTES + cc * 16);
+          st_peer16(cbase + (size_t)rr * rowStride + c4 * 64 + cc * 8, o);
+        }
+        __syncwarp();
       }
       tc_fence_before();
       __syncwarp();
