@@ -24,7 +24,7 @@ from __future__ import annotations
 import ctypes as C
 import random
 from dataclasses import dataclass, field
-from typing import Dict, List, Optional
+from typing import Dict, List, Optional, Sequence
 
 import torch
 import torch.nn as nn
@@ -48,6 +48,8 @@ class Bucket:
     momentum: Optional[torch.Tensor] = None
     pending: int = 0
     coll_id: int = 0
+    comm: Optional[nv.Comm] = None             # the group this bucket is reduced over
+    scale: float = 1.0
 
 
 def _view_like(flat: torch.Tensor, off: int, p: torch.Tensor) -> torch.Tensor:
@@ -73,7 +75,10 @@ class DaemonDDP:
     def __init__(self, module: nn.Module, dist: Dist, *, bucket_mb: float = 25.0, lr: float = 0.1, momentum: float = 0.9,
                  weight_decay: float = 1e-4, randomize_order: bool = True, window: int = 2, seed: int = 0,
                  coll_id_base: int = 0, comm: Optional[nv.Comm] = None, n_blocks: int = 0,
-                 daemon_blocks: int = 8, daemon_threads: int = 0):
+                 daemon_blocks: int = 8, daemon_threads: int = 0, param_groups: Optional[Sequence[dict]] = None):
+        """``param_groups`` (hybrid parallelism): a list of ``{"params": [...], "comm": Comm, "scale": float}``;
+        every group gets its own buckets, reduced over its own communicator (sum times ``scale``).  All
+        groups share this rank's one daemon, so ranks may submit them in any order."""
         self.module = module
         self.dist = dist
         self.comm = comm or dist.comm
@@ -91,15 +96,19 @@ class DaemonDDP:
         self.hooks_enabled = True               # switched off while a captured step runs (see graph.GraphedStep)
         self.launches = 0                       # kernels of this library launched by step()
         self.buckets: List[Bucket] = []
-        self._build_buckets(int(bucket_mb * (1 << 20)))
+        if param_groups is None:
+            param_groups = [{"params": [p for p in module.parameters() if p.requires_grad], "comm": self.comm,
+                             "scale": 1.0 / self.world}]
+        for g in param_groups:
+            self._build_buckets(int(bucket_mb * (1 << 20)), g["params"], g.get("comm") or self.comm, float(g["scale"]))
         self.ctx = nv.RankCtx(dist.rank, dist.local_rank if self.device.type == "cuda" else -1)
         # gradient buckets need a fraction of the fabric: a small grid leaves the SMs to the training kernels
         if self.device.type == "cuda":
             self.ctx.set_daemon_geometry(daemon_blocks, daemon_threads)
         for b in self.buckets:
             b.coll_id = coll_id_base + b.index
-            self.ctx.prepare(b.coll_id, self.comm, nv.ALLREDUCE, b.numel, nccl_dtype(b.dtype), out_dtype=nv.FLOAT32,
-                             op=nv.SUM, scale=1.0 / self.world, n_blocks=n_blocks)
+            self.ctx.prepare(b.coll_id, b.comm, nv.ALLREDUCE, b.numel, nccl_dtype(b.dtype), out_dtype=nv.FLOAT32,
+                             op=nv.SUM, scale=b.scale, n_blocks=n_blocks)
         self.ctx.finalize()
         if self.device.type == "cuda":
             nv.check(self._lib.dfcclOpsWarm(), "dfcclOpsWarm")   # load the optimizer kernels before any stream can block
@@ -109,8 +118,9 @@ class DaemonDDP:
                 self._hooks.append(p.register_post_accumulate_grad_hook(self._make_hook(b)))
 
     # ------------------------------------------------------------------ construction
-    def _build_buckets(self, bucket_bytes: int) -> None:
-        params = [p for p in self.module.parameters() if p.requires_grad]
+    def _build_buckets(self, bucket_bytes: int, params, comm, scale: float) -> None:
+        first = len(self.buckets)
+        params = [p for p in params if p.requires_grad]
         by_dtype: Dict[torch.dtype, List[nn.Parameter]] = {}
         for p in reversed(params):              # gradients arrive roughly in reverse registration order
             by_dtype.setdefault(p.dtype, []).append(p)
@@ -124,7 +134,8 @@ class DaemonDDP:
                 cur.offsets.append(cur.numel)
                 cur.params.append(p)
                 cur.numel += (p.numel() + 7) // 8 * 8      # keep every parameter 16-byte aligned
-        for b in self.buckets:
+        for b in self.buckets[first:]:
+            b.comm, b.scale = comm, scale
             b.flat_param = torch.empty(b.numel, dtype=b.dtype, device=self.device)
             b.grad = self._pool.zeros((b.numel,), b.dtype)
             b.grad32 = self._pool.zeros((b.numel,), torch.float32)

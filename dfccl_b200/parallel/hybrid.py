@@ -1,0 +1,145 @@
+"""Hybrid tensor x pipeline x data parallel training on one daemon per rank.
+
+Rank layout (tensor-parallel ranks adjacent, then pipeline stages, then replicas):
+
+    rank = dp_rank * (pp * tp) + pp_rank * tp + tp_rank
+
+Communicators of this library are split from the world communicator: the tensor-parallel group (fused
+GEMM + collective kernels and the backward collectives), the data-parallel group (gradients of the
+sharded weights) and the "stage" group = every rank holding the same stage (gradients of the
+replicated parameters: layer norms, row-parallel biases, embeddings - summed over the tensor-parallel
+ranks, averaged over the replicas).  All gradient all-reduces of a rank, whatever their group, are
+registered with the rank's one daemon and submitted stream-ordered in a per-rank shuffled order:
+collectives of overlapping groups issued in different orders by different ranks is the situation the
+reference's simulator shows deadlocking in-order libraries (reference: simulator/simulator.py:434-493)
+and the daemon makes safe.  Activations and their gradients move between stages with
+``torch.distributed`` point-to-point (NCCL on GPUs, gloo in the CPU tests).
+
+Schedule: all micro-batches forward, then all backward (GPipe), gradients accumulated in the flat
+buckets; the buckets are released to the daemon from the gradient hooks of the last micro-batch.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import List, Optional
+
+import torch
+import torch.distributed as dist
+
+from .. import native as nv
+from ..ops.fused_linear import TpGroup
+from ..utils.tensors import nccl_dtype
+from .ddp import DaemonDDP
+from .groups import Dist
+
+
+@dataclass
+class Mesh:
+    tp: int
+    pp: int
+    dp: int
+    tp_rank: int
+    pp_rank: int
+    dp_rank: int
+    tp_group: TpGroup
+    dp_comm: nv.Comm
+    stage_comm: nv.Comm
+
+    def close(self) -> None:
+        for c in (self.tp_group.comm, self.dp_comm, self.stage_comm):
+            c.destroy()
+
+
+def build_mesh(d: Dist, tp: int, pp: int, dp: int) -> Mesh:
+    assert tp * pp * dp == d.world, f"tp {tp} x pp {pp} x dp {dp} != world {d.world}"
+    r = d.rank
+    tp_rank, pp_rank, dp_rank = r % tp, (r // tp) % pp, r // (tp * pp)
+    tp_comm = d.comm.split(r // tp, r)
+    dp_comm = d.comm.split(r % (tp * pp), r)
+    stage_comm = d.comm.split(pp_rank, r)
+    pg = None
+    if d.world > 1 and tp > 1:
+        for g in range(d.world // tp):                      # every rank creates every group, in the same order
+            ranks = list(range(g * tp, (g + 1) * tp))
+            h = dist.new_group(ranks)
+            if g == r // tp:
+                pg = h
+    return Mesh(tp, pp, dp, tp_rank, pp_rank, dp_rank, TpGroup(tp_comm, pg, d.device), dp_comm, stage_comm)
+
+
+class HybridTrainer:
+    """One optimizer step = ``n_micro`` micro-batches of ``micro_batch`` sequences per replica."""
+
+    def __init__(self, d: Dist, mesh: Mesh, stage: torch.nn.Module, *, n_micro: int, bucket_mb: float = 25.0, lr: float = 0.01,
+                 momentum: float = 0.9, weight_decay: float = 0.0, seed: int = 0, daemon_blocks: int = 8):
+        self.d, self.mesh, self.stage, self.n_micro = d, mesh, stage, n_micro
+        params = [p for p in stage.parameters() if p.requires_grad]
+        sharded = [p for p in params if not getattr(p, "tp_replicated", False)]
+        replicated = [p for p in params if getattr(p, "tp_replicated", False)]
+        groups = [{"params": sharded, "comm": mesh.dp_comm, "scale": 1.0 / mesh.dp},
+                  {"params": replicated, "comm": mesh.stage_comm, "scale": 1.0 / mesh.dp}]
+        self.ddp = DaemonDDP(stage, d, bucket_mb=bucket_mb, lr=lr, momentum=momentum, weight_decay=weight_decay,
+                             randomize_order=True, seed=seed, param_groups=groups, daemon_blocks=daemon_blocks)
+        self.ddp.hooks_enabled = False
+        self.prev = d.rank - mesh.tp if mesh.pp_rank > 0 else None
+        self.next = d.rank + mesh.tp if mesh.pp_rank < mesh.pp - 1 else None
+        self._loss = torch.zeros(1, dtype=torch.float32, device=d.device)
+        self.pp_bytes = 0
+
+    def _hidden(self) -> torch.Tensor:
+        st = self.stage
+        return torch.empty(st.rows, st.cfg.d_model, dtype=torch.bfloat16, device=self.d.device)
+
+    def _send(self, t: torch.Tensor, dst: int):
+        self.pp_bytes += t.numel() * t.element_size()
+        return dist.isend(t.contiguous(), dst)
+
+    def step(self, tokens: Optional[torch.Tensor], targets: Optional[torch.Tensor]) -> torch.Tensor:
+        """``tokens`` / ``targets``: [n_micro, micro_batch, seq] of this replica (tokens are read by the first
+        stage, targets by the last).  Returns the mean loss over all replicas as a 1-element tensor on every rank."""
+        st, n, ddp = self.stage, self.n_micro, self.ddp
+        ins: List[torch.Tensor] = []
+        outs: List[torch.Tensor] = []
+        sends = []
+        for i in range(n):                                   # ---- forward
+            if self.prev is None:
+                x = tokens[i]
+            else:
+                x = self._hidden()
+                dist.irecv(x, self.prev).wait()
+                x.requires_grad_(True)
+            y = st(x, targets[i] if self.next is None else None)
+            if self.next is not None:
+                sends.append(self._send(y.detach(), self.next))
+            ins.append(x)
+            outs.append(y)
+        self._loss.zero_()
+        for i in range(n):                                   # ---- backward
+            ddp.hooks_enabled = i == n - 1                   # buckets go to the daemon as the last micro-batch fills them
+            if self.next is None:
+                loss = outs[i] / n
+                self._loss += loss.detach()
+                loss.backward()
+            else:
+                g = self._hidden()
+                dist.irecv(g, self.next).wait()
+                outs[i].backward(g)
+            if self.prev is not None:
+                sends.append(self._send(ins[i].grad, self.prev))
+            ins[i] = outs[i] = None
+        ddp.hooks_enabled = False
+        ddp.finish_backward()
+        ddp.step()
+        for w in sends:
+            w.wait()
+        # mean loss over the replicas: the last-stage ranks hold tensor-parallel shares of their replica's loss
+        m = self.mesh
+        if self.d.world > 1:
+            self._loss.mul_(1.0 / m.dp)
+            s = torch.cuda.current_stream(self.d.device).cuda_stream if self.d.device.type == "cuda" else 0
+            nv.check(nv.lib().ncclAllReduce(self._loss.data_ptr(), self._loss.data_ptr(), 1, nccl_dtype(torch.float32), nv.SUM,
+                                            self.d.comm.handle, s), "ncclAllReduce(loss)")
+        return self._loss
+
+    def close(self) -> None:
+        self.ddp.close()

@@ -226,3 +226,66 @@ def scenario_fused_tp(nv, comm, rank, world, backend):
     dist.barrier()
     dist.destroy_process_group()
     return out
+
+
+def _gpt_hybrid(nv, comm, rank, world, backend, tp, pp, dp, port):
+    """Hybrid tp x pp x dp training of a small GPT-2 against the same model on one rank: the loss of
+    every step must agree (the second and third steps depend on the gradients and the update)."""
+    import torch
+    import torch.distributed as dist
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    os.environ.setdefault("MASTER_PORT", str(port))
+    cuda = backend == "cuda"
+    dev = torch.device("cuda", rank) if cuda else torch.device("cpu")
+    dist.init_process_group("nccl" if cuda else "gloo", rank=rank, world_size=world, device_id=dev if cuda else None)
+    from dfccl_b200.models.gpt2 import GPT2Config, GPT2Stage
+    from dfccl_b200.parallel.groups import Dist
+    from dfccl_b200.parallel.hybrid import HybridTrainer, build_mesh
+    cfg = GPT2Config(n_layer=4, d_model=256, n_head=4, seq_len=128, vocab=512) if cuda else \
+        GPT2Config(n_layer=2, d_model=64, n_head=4, seq_len=32, vocab=96)
+    micro_batch, n_micro, steps = 2, 2, 3
+    d = Dist(rank, world, rank if cuda else 0, dev, comm, True)
+    mesh = build_mesh(d, tp, pp, dp)
+    stage = GPT2Stage(cfg, mesh.tp_group, mesh.pp_rank, pp, micro_batch)
+    tr = HybridTrainer(d, mesh, stage, n_micro=n_micro, lr=0.3, bucket_mb=0.25, seed=3)
+    g = torch.Generator().manual_seed(11)
+    data = torch.randint(0, cfg.vocab, (dp, n_micro, micro_batch, cfg.seq_len + 1), generator=g)
+    tok, tgt = data[mesh.dp_rank, ..., :-1].to(dev), data[mesh.dp_rank, ..., 1:].to(dev)
+    losses = []
+    for _ in range(steps):
+        losses.append(float(tr.step(tok, tgt)))
+    if cuda:
+        torch.cuda.synchronize()
+    st = tr.ddp.stats()
+    tr.close()
+    if rank == 0:                                           # the same model, unsharded, on this rank alone
+        (c1,) = nv.Comm.init_loopback(1, rank if cuda else 0)
+        d1 = Dist(0, 1, rank if cuda else 0, dev, c1, False)
+        m1 = build_mesh(d1, 1, 1, 1)
+        s1 = GPT2Stage(cfg, m1.tp_group, 0, 1, micro_batch)
+        t1 = HybridTrainer(d1, m1, s1, n_micro=n_micro * dp, lr=0.3, bucket_mb=0.25, seed=3)
+        flat = data.reshape(dp * n_micro, micro_batch, cfg.seq_len + 1)
+        ref = [float(t1.step(flat[..., :-1].to(dev), flat[..., 1:].to(dev))) for _ in range(steps)]
+        t1.close()
+        for a, b in zip(losses, ref):
+            assert abs(a - b) < 3e-2 * max(1.0, abs(b)), (losses, ref)
+        assert ref[-1] < ref[0] - 0.05, ref
+    dist.barrier()
+    dist.destroy_process_group()
+    return {"losses": losses, "cqes": st["cqesDelivered"]}
+
+
+def scenario_gpt_tp2(nv, comm, rank, world, backend):
+    return _gpt_hybrid(nv, comm, rank, world, backend, 2, 1, 1, 29581)
+
+
+def scenario_gpt_tp2pp2(nv, comm, rank, world, backend):
+    return _gpt_hybrid(nv, comm, rank, world, backend, 2, 2, 1, 29582)
+
+
+def scenario_gpt_pp2dp2(nv, comm, rank, world, backend):
+    return _gpt_hybrid(nv, comm, rank, world, backend, 1, 2, 2, 29583)
+
+
+def scenario_gpt_tp2pp2dp2(nv, comm, rank, world, backend):
+    return _gpt_hybrid(nv, comm, rank, world, backend, 2, 2, 2, 29584)

@@ -36,3 +36,21 @@ def test_gpu_processes_stream_interface():
 def test_fused_tensor_parallel_gemms():
     import torch
     mp_worker.launch(2 if torch.cuda.device_count() < 4 else 4, "cuda", "fused_tp", timeout=300)
+
+
+@pytest.mark.parametrize("layout,world", [("tp2", 2), ("tp2pp2", 4), ("pp2dp2", 4), ("tp2pp2dp2", 8)])
+def test_host_gpt2_hybrid_parallel(layout, world):
+    """Tensor x pipeline x data parallel GPT-2 steps on CPU ranks match the unsharded model."""
+    res = mp_worker.launch(world, "host", "gpt_" + layout, timeout=300)
+    assert all(r["cqes"] > 0 for r in res.values())
+    losses = [tuple(round(x, 3) for x in r["losses"]) for r in res.values()]
+    assert len(set(losses)) == 1, losses                     # every rank reports the same global loss
+
+
+@pytest.mark.gpu
+@pytest.mark.multigpu
+def test_gpu_gpt2_hybrid_parallel():
+    import torch
+    n = torch.cuda.device_count()
+    layout, world = ("tp2pp2dp2", 8) if n >= 8 else ("tp2pp2", 4) if n >= 4 else ("tp2", 2)
+    mp_worker.launch(world, "cuda", "gpt_" + layout, timeout=600)
