@@ -14,7 +14,7 @@
  *                the in-process CPU backend and loopback rank groups used by tests.
  *
  * Every p-prefixed profiling alias of the reference (pncclAllReduce, pofcclRun...)
- * is exported as well; see dfccl_prof.h.
+ * is exported as well; see.
  */
 #ifndef DFCCL_H_
 #define DFCCL_H_
@@ -189,6 +189,18 @@ ncclResult_t dfcclCommSplit(ncclComm_t comm, int color, int key, ncclComm_t* new
 ncclResult_t dfcclMemAlloc(void** ptr, size_t bytes, ncclComm_t comm);
 ncclResult_t dfcclMemFree(void* ptr, ncclComm_t comm);
 ncclResult_t dfcclHeapInfo(ncclComm_t comm, void** base, size_t* bytes, size_t* used);
+
+/* NVLS arena (opt-in): `bytes` of every member's device memory bound to one NVLink-switch multicast
+ * object.  All-reduces (sum; f32, bf16, f16) of at least DFCCL_NVLS_MIN_BYTES then run as
+ * multimem.ld_reduce + multimem.st; buffers from dfcclNvlsAlloc are used in place, others are copied
+ * through the arena.  dfcclNvlsInit is collective over the communicator (DFCCL_NVLS=1 does the same at
+ * communicator creation with DFCCL_NVLS_BYTES); *available is 0 when the devices, the driver or the
+ * process layout cannot do it, and nothing changes then.  dfcclNvlsAlloc must be called with the same
+ * sizes in the same order by every member (offsets are symmetric); the memory lives as long as the
+ * communicator. */
+ncclResult_t dfcclNvlsInit(ncclComm_t comm, size_t bytes, int* available);
+ncclResult_t dfcclNvlsAlloc(void** ptr, size_t bytes, ncclComm_t comm);
+ncclResult_t dfcclNvlsInfo(ncclComm_t comm, void** unicastBase, void** multicastBase, size_t* bytes, size_t* used);
 
 ncclResult_t dfcclInitRankCtxOnDevice(ofcclRankCtx_t* rankCtx, int rank, int device);
 /* Daemon grid of this context: thread blocks per rank and threads per block (multiple of 32, <= 512);

@@ -226,6 +226,30 @@ DF_API ncclResult_t dfcclMemFree(void* ptr, ncclComm_t comm) {
   if (!comm->heap->contains(ptr)) { DF_WARN("dfcclMemFree: pointer is not from the symmetric heap"); return ncclInvalidArgument; }
   return comm->heap->free(comm->heap->offsetOf(ptr));
 }
+DF_API ncclResult_t dfcclNvlsInit(ncclComm_t comm, size_t bytes, int* available) {
+  if (!comm) return ncclInvalidArgument;
+  if (!comm->nvls && comm->nranks > 1 && (!comm->loop || comm->backend != dfcclBackendCuda)) DFCHECK(nvlsArenaCreate(comm, bytes ? bytes : (size_t)(512u << 20), &comm->nvls));
+  if (available) *available = comm->nvls ? 1 : 0;
+  return ncclSuccess;
+}
+DF_API ncclResult_t dfcclNvlsAlloc(void** ptr, size_t bytes, ncclComm_t comm) {
+  if (!comm || !ptr) return ncclInvalidArgument;
+  if (!comm->nvls) { DF_WARN("this communicator has no NVLS arena"); return ncclInvalidUsage; }
+  uint64_t off = 0;
+  ncclResult_t r = comm->nvls->alloc(bytes, &off);
+  if (r != ncclSuccess) { DF_WARN("NVLS arena exhausted: %zu bytes requested, %zu of %zu in use (raise DFCCL_NVLS_BYTES)", bytes, comm->nvls->bump, comm->nvls->bytes); return r; }
+  *ptr = comm->nvls->uc + off;
+  return ncclSuccess;
+}
+DF_API ncclResult_t dfcclNvlsInfo(ncclComm_t comm, void** uc, void** mc, size_t* bytes, size_t* used) {
+  if (!comm) return ncclInvalidArgument;
+  dfccl::NvlsArena* a = comm->nvls;
+  if (uc) *uc = a ? a->uc : nullptr;
+  if (mc) *mc = a ? a->mc : nullptr;
+  if (bytes) *bytes = a ? a->bytes : 0;
+  if (used) *used = a ? a->bump : 0;
+  return ncclSuccess;
+}
 DF_API ncclResult_t dfcclHeapInfo(ncclComm_t comm, void** base, size_t* bytes, size_t* used) {
   if (!comm) return ncclInvalidArgument;
   if (base) *base = comm->heap->base();

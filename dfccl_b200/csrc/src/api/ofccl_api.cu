@@ -253,7 +253,22 @@ DF_API ncclResult_t ofcclFinalizeRankCtx7StartHostThrds(ofcclRankCtx_t ctx) {
   for (auto& kv : ctx->colls) {
     CollEntry& e = kv.second;
     const size_t bytes = e.info.count * (size_t)dtypeSize(e.info.inType);
-    TunerChoice ch = tunerChoose(*topo, e.info.kind, bytes, e.comm->nranks, ctx->nBlocks, false, e.info.algo, e.info.nBlocks);
+    bool nv = nvlsEligible(e.comm, e.cs.kind, e.cs.inType, e.cs.outType, e.cs.op, e.cs.postDiv, e.cs.count);
+    TunerChoice ch = tunerChoose(*topo, e.info.kind, bytes, e.comm->nranks, ctx->nBlocks, nv, e.info.algo, e.info.nBlocks);
+    if (ch.algo == dfcclAlgoNvls) {
+      // staging slots in the arena; every member walks its collectives in id order, so the offsets agree
+      NvlsArena* a = e.comm->nvls;
+      const size_t inB = bytes, outB = e.info.count * (size_t)dtypeSize(e.info.outType);
+      uint64_t in = 0, out = 0;
+      if (a->alloc(inB, &in) == ncclSuccess && a->alloc(outB, &out) == ncclSuccess) {
+        e.cs.mcHeap = a->mc; e.cs.nvlsPeers = a->peersDev; e.cs.nvlsIn = in; e.cs.nvlsOut = out;
+        e.cs.stagingSendOff = (uint64_t)(a->uc + in - e.comm->heap->base());
+        e.cs.stagingRecvOff = (uint64_t)(a->uc + out - e.comm->heap->base());
+      } else {
+        DF_INFO(SUB_TUNING, "collective %d: NVLS arena full, using peer loads and stores", kv.first);
+        ch = tunerChoose(*topo, e.info.kind, bytes, e.comm->nranks, ctx->nBlocks, false, e.info.algo == dfcclAlgoNvls ? dfcclAlgoAuto : e.info.algo, e.info.nBlocks);
+      }
+    }
     e.cs.algo = ch.algo; e.cs.nBlocks = ch.nBlocks;
     e.flagsBytes = sizeof(FlagSlot) * (size_t)ch.nBlocks * e.comm->nranks;
     DFCHECK(e.comm->heap->alloc(e.flagsBytes, &e.flagsOff, true));
@@ -452,16 +467,25 @@ static ncclResult_t submit(ofcclRankCtx* ctx, const void* send, void* recv, int 
     Heap* heap = e.comm->heap;
     const size_t sB = sendBytes(&cs), rB = recvBytes(&cs);
     q.collId = collId;
-    bool stageSend = needSend && !heap->contains(send, sB);
+    const bool viaArena = cs.algo == dfcclAlgoNvls;
+    if (viaArena) {          // in place when the buffer lives in the arena, else through this collective's slots
+      NvlsArena* a = e.comm->nvls;
+      if (a->contains(send, sB)) q.send = (uint64_t)((const char*)send - a->uc); else { q.flags |= SQE_SEND_STAGED; q.send = (uint64_t)(uintptr_t)send; }
+      if (a->contains(recv, rB)) q.recv = (uint64_t)((char*)recv - a->uc); else { q.flags |= SQE_RECV_STAGED; q.recv = (uint64_t)(uintptr_t)recv; }
+    }
+    bool stageSend = !viaArena && needSend && !heap->contains(send, sB);
     if (needSend && cs.kind == dfcclCollAllReduce && cs.algo == dfcclAlgoOneShot && send == recv && cs.nranks > 1) stageSend = true;
-    bool stageRecv = needRecv && !heap->contains(recv, rB);
+    bool stageRecv = !viaArena && needRecv && !heap->contains(recv, rB);
     // staging areas are created on first need; the static table on the device learns their offsets
     bool tableDirty = false;
     if (stageSend && e.stagingBytes[0] < sB) { if (e.stagingBytes[0]) heap->free(e.stagingOff[0]); DFCHECK(heap->alloc(sB, &e.stagingOff[0], false)); e.stagingBytes[0] = sB; e.cs.stagingSendOff = e.stagingOff[0]; tableDirty = true; }
     if (stageRecv && e.stagingBytes[1] < rB) { if (e.stagingBytes[1]) heap->free(e.stagingOff[1]); DFCHECK(heap->alloc(rB, &e.stagingOff[1], false)); e.stagingBytes[1] = rB; e.cs.stagingRecvOff = e.stagingOff[1]; tableDirty = true; }
     if (tableDirty) DFCHECK(devUpload(ctx->backend, &ctx->rdHost.colls[collId], &e.cs, sizeof(CollStatic)));
-    if (stageSend) { q.flags |= SQE_SEND_STAGED; q.send = (uint64_t)(uintptr_t)send; } else if (needSend) q.send = heap->offsetOf(send);
-    if (stageRecv) { q.flags |= SQE_RECV_STAGED; q.recv = (uint64_t)(uintptr_t)recv; } else if (needRecv) q.recv = heap->offsetOf(recv);
+    if (viaArena) {
+    } else {
+      if (stageSend) { q.flags |= SQE_SEND_STAGED; q.send = (uint64_t)(uintptr_t)send; } else if (needSend) q.send = heap->offsetOf(send);
+      if (stageRecv) { q.flags |= SQE_RECV_STAGED; q.recv = (uint64_t)(uintptr_t)recv; } else if (needRecv) q.recv = heap->offsetOf(recv);
+    }
     if (onStream) { q.flags |= SQE_TRIGGERED; q.trigger = trig = ++e.triggerSeq; }
     // flow control: entries the device has not mirrored yet
     uint64_t tail = *ctx->hostSqTail;
@@ -669,6 +693,11 @@ DF_API ncclResult_t dfcclInjectFault(ofcclRankCtx_t ctx, dfcclFault_t fault, int
 // after); nobody writes them any more: this rank completed every submission, which needed every
 // peer's last flag.
 static void releaseHeapParts(ofcclRankCtx* ctx) {
+  // arena slots were taken in ascending id order; giving them back in descending order unwinds the bump allocator
+  for (auto it = ctx->colls.rbegin(); it != ctx->colls.rend(); ++it) {
+    CollEntry& e = it->second;
+    if (e.cs.algo == dfcclAlgoNvls && e.comm && e.comm->nvls) { e.comm->nvls->release(e.cs.nvlsOut); e.comm->nvls->release(e.cs.nvlsIn); }
+  }
   for (auto& kv : ctx->colls) {
     CollEntry& e = kv.second;
     e.comm->heap->free(e.flagsOff);

@@ -137,6 +137,8 @@ ncclResult_t commCreate(std::shared_ptr<Bootstrap> boot, dfcclBackend_t backend,
   DFCHECK(devAlloc(backend, (void**)&c->saRd, sizeof(RankDev)));
   DFCHECK(devUpload(backend, c->saRd, &rd, sizeof(RankDev)));
   DFCHECK(boot->barrier());          // every member has mapped everything before anyone uses it
+  // switch multicast is opt-in: binding memory to a multicast object ties the members' fates together
+  if (n > 1 && (!loop || backend != dfcclBackendCuda) && paramI64("NVLS", 0)) DFCHECK(nvlsArenaCreate(c.get(), (size_t)paramI64("NVLS_BYTES", 512ll << 20), &c->nvls));
   if (backend == dfcclBackendCuda) cudaSetDevice(prevDev);
   DF_INFO(SUB_INIT, "comm %llx rank %d/%d device %d backend %s heap %zu MiB", (unsigned long long)c->commHash, r, n, device,
           backend == dfcclBackendCuda ? "cuda" : "host", c->heap->bytes() >> 20);
@@ -147,6 +149,7 @@ ncclResult_t commCreate(std::shared_ptr<Bootstrap> boot, dfcclBackend_t backend,
 ncclResult_t commDestroy(ncclComm* c) {
   if (!c) return ncclSuccess;
   if (c->backend == dfcclBackendCuda) { int prev; cudaGetDevice(&prev); cudaSetDevice(c->device); cudaDeviceSynchronize(); (void)cudaGetLastError(); cudaSetDevice(prev); }
+  if (c->nvls) { nvlsArenaDestroy(c, c->nvls); c->nvls = nullptr; }
   c->heap->free(c->saFlagsOff);
   c->heap->free(c->p2pFlagsOff);
   for (int k = 0; k < 2; ++k) if (c->scratchBytes[k]) c->heap->free(c->scratchOff[k]);
@@ -156,6 +159,11 @@ ncclResult_t commDestroy(ncclComm* c) {
   if (c->ownsHeap) delete c->heap;
   delete c;
   return ncclSuccess;
+}
+
+bool nvlsEligible(const ncclComm* c, int kind, int inType, int outType, int devOp, int postDiv, size_t count) {
+  return c->nvls && c->nranks > 1 && kind == dfcclCollAllReduce && devOp == OP_SUM && postDiv == 0 && nvlsTypesOk(inType, outType) &&
+         (count * (size_t)dtypeSize(inType)) % 16 == 0;
 }
 
 static ncclResult_t ensureScratch(ncclComm* c, int which, size_t bytes) {
@@ -182,7 +190,7 @@ ncclResult_t commCollective(ncclComm* c, int kind, const void* send, void* recv,
   const bool needSend = !(kind == dfcclCollBroadcast && c->rank != root);
   const bool needRecv = !(kind == dfcclCollReduce && c->rank != root);
   if ((needSend && !send) || (needRecv && !recv)) { DF_WARN("null buffer"); return ncclInvalidArgument; }
-  std::lock_guard<std::mutex> l(c->mu);
+  std::unique_lock<std::mutex> l(c->mu);
   CollStatic cs;
   memset(&cs, 0, sizeof(cs));
   cs.kind = kind; cs.inType = cs.outType = type; cs.nranks = c->nranks; cs.rank = c->rank; cs.root = root;
@@ -196,8 +204,23 @@ ncclResult_t commCollective(ncclComm* c, int kind, const void* send, void* recv,
   const size_t bytes = count * dtypeSize(type);
   // a stream-ordered kernel shares the GPU with nothing persistent: it may take more blocks than the daemon does
   const int maxBlocks = c->backend == dfcclBackendCuda ? (int)std::min<int64_t>(DF_MAX_BLOCKS, std::max<int64_t>(1, paramI64("STREAM_MAX_BLOCKS", 64))) : daemonBlocks(c->backend);
-  TunerChoice ch = tunerChoose(*topo, kind, bytes, c->nranks, maxBlocks, false);
+  const bool nvlsOk = nvlsEligible(c, kind, type, type, devOp, cs.postDiv, count);
+  TunerChoice ch = tunerChoose(*topo, kind, bytes, c->nranks, maxBlocks, nvlsOk);
   cs.algo = ch.algo; cs.nBlocks = ch.nBlocks;
+  if (cs.algo == dfcclAlgoNvls) {
+    NvlsArena* a = c->nvls;
+    const size_t half = a->streamBytes / 2;
+    const bool inArena = a->contains(send, bytes), outArena = a->contains(recv, bytes);
+    if ((!inArena || !outArena) && bytes > half) {
+      // staged through the front of the arena, a piece at a time (element ranges of an all-reduce are independent)
+      const size_t es = dtypeSize(type), step = half / 1024 * 1024 / es;
+      l.unlock();
+      for (size_t done = 0; done < count; done += step)
+        DFCHECK(commCollective(c, kind, (const char*)send + done * es, (char*)recv + done * es, std::min(step, count - done), type, op, root, stream));
+      return ncclSuccess;
+    }
+    cs.mcHeap = a->mc; cs.nvlsPeers = a->peersDev; cs.nvlsIn = 0; cs.nvlsOut = half;
+  }
   cs.myFlags = (FlagSlot*)(c->heap->base() + c->saFlagsOff);
   for (int j = 0; j < c->nranks; ++j) {
     cs.peerHeap[j] = c->peerHeap[j];
@@ -206,12 +229,23 @@ ncclResult_t commCollective(ncclComm* c, int kind, const void* send, void* recv,
   uint32_t flags = 0;
   uint64_t s = 0, r = 0;
   const size_t sBytes = sendBytes(&cs), rBytes = recvBytes(&cs);
-  bool stageSend = needSend && !c->heap->contains(send, sBytes);
+  if (cs.algo == dfcclAlgoNvls) {
+    // buffers inside the arena are used in place (their offsets are symmetric by contract); anything else is
+    // copied through the staging slots, addressed relative to the heap base like every other staging area
+    NvlsArena* a = c->nvls;
+    if (a->contains(send, sBytes)) s = (uint64_t)((const char*)send - a->uc);
+    else { flags |= SQE_SEND_STAGED; s = (uint64_t)(uintptr_t)send; cs.stagingSendOff = (uint64_t)(a->uc + cs.nvlsIn - c->heap->base()); }
+    if (a->contains(recv, rBytes)) r = (uint64_t)((char*)recv - a->uc);
+    else { flags |= SQE_RECV_STAGED; r = (uint64_t)(uintptr_t)recv; cs.stagingRecvOff = (uint64_t)(a->uc + cs.nvlsOut - c->heap->base()); }
+  }
+  const bool viaArena = cs.algo == dfcclAlgoNvls;
+  bool stageSend = !viaArena && needSend && !c->heap->contains(send, sBytes);
   // one-shot in place: peers read my input while I overwrite it, so they get a private copy
   if (needSend && kind == dfcclCollAllReduce && cs.algo == dfcclAlgoOneShot && send == recv && c->nranks > 1) stageSend = true;
   if (stageSend) { DFCHECK(ensureScratch(c, 0, sBytes)); flags |= SQE_SEND_STAGED; s = (uint64_t)(uintptr_t)send; cs.stagingSendOff = c->scratchOff[0]; }
-  else if (needSend) s = c->heap->offsetOf(send);
-  if (needRecv && !c->heap->contains(recv, rBytes)) { DFCHECK(ensureScratch(c, 1, rBytes)); flags |= SQE_RECV_STAGED; r = (uint64_t)(uintptr_t)recv; cs.stagingRecvOff = c->scratchOff[1]; }
+  else if (needSend && !viaArena) s = c->heap->offsetOf(send);
+  if (viaArena) {
+  } else if (needRecv && !c->heap->contains(recv, rBytes)) { DFCHECK(ensureScratch(c, 1, rBytes)); flags |= SQE_RECV_STAGED; r = (uint64_t)(uintptr_t)recv; cs.stagingRecvOff = c->scratchOff[1]; }
   else if (needRecv) r = c->heap->offsetOf(recv);
   const uint32_t epoch = ++c->opCount;
   if (c->backend == dfcclBackendCuda) {

@@ -15,6 +15,7 @@
 #include "../bootstrap/bootstrap.h"
 #include "../device/types.h"
 #include "../mem/heap.h"
+#include "../mem/mcast.h"
 
 namespace dfccl {
 struct DaemonLauncher;
@@ -60,6 +61,7 @@ struct ncclComm {
   std::vector<dfccl::UserRedOp> userOps;
   std::shared_ptr<dfccl::LoopGroup> loop;      // set for loopback / InitAll groups
   bool aborted = false;
+  dfccl::NvlsArena* nvls = nullptr;            // switch-multicast arena (opt-in), null when absent
 };
 
 namespace dfccl {
@@ -76,6 +78,9 @@ int daemonBlocks(dfcclBackend_t be);
 ncclResult_t resolveRedOp(ncclComm* comm, ncclRedOp_t op, ncclDataType_t type, int nranks, int* devOp, double* scale, int* postDiv);
 // Heap of (backend, device), created on first use and shared by all communicators of the process.
 ncclResult_t processHeap(dfcclBackend_t backend, int device, Heap** out);
+
+// Can this all-reduce run on the NVLS schedule of this communicator?  (arena present, sum, supported types, 16-byte multiple)
+bool nvlsEligible(const ncclComm* comm, int kind, int inType, int outType, int devOp, int postDiv, size_t count);
 
 // The engine behind the stream-ordered entry points.
 ncclResult_t commCollective(ncclComm* comm, int kind, const void* send, void* recv, size_t count, ncclDataType_t type,

@@ -24,6 +24,7 @@
 //   Reduce              : like two-shot AllReduce, but shards are written to the root only.
 #pragma once
 #include "datapath.h"
+#include "nvls.h"
 #include "platform.h"
 #include "types.h"
 #if !defined(__CUDA_ARCH__)
@@ -211,7 +212,7 @@ DF_HD void dataPhase(BlockShared* sh, RankDev* rd, int b) {
   const CollStatic* c = &sh->cs;
   const int n = c->nranks, me = c->rank;
   const uint64_t es = dtypeSize(c->inType), eo = dtypeSize(c->outType);
-  bool reduce = true;
+  bool reduce = true, nvls = false;
   if (df_tid() == 0) {
     DataArgs* a = &sh->args;
     a->scale = c->scale; a->postDiv = c->postDiv; a->nsrc = 0; a->ndst = 0; a->n = 0;
@@ -219,7 +220,18 @@ DF_HD void dataPhase(BlockShared* sh, RankDev* rd, int b) {
     switch (c->kind) {
       case dfcclCollAllReduce: {
         partRange(c->count, c->nBlocks, b, 16, &bb, &be);
-        if (c->algo == dfcclAlgoOneShot || n == 1) {
+        if (c->algo == dfcclAlgoNvls && n > 1) {
+          // my slice of this block's range, as byte offsets into the arena (symmetric on all members)
+          uint64_t sb, se;
+          partRange(be - bb, n, me, 16, &sb, &se);
+          sb += bb; se += bb;
+          const uint64_t in = (sh->dyn.sqeFlags & SQE_SEND_STAGED) ? c->nvlsIn : sh->dyn.send;
+          const uint64_t out = (sh->dyn.sqeFlags & SQE_RECV_STAGED) ? c->nvlsOut : sh->dyn.recv;
+          a->src[0] = (const char*)(uintptr_t)(in + sb * es); a->nsrc = 1;
+          a->dst[0] = (char*)(uintptr_t)(out + sb * eo); a->ndst = 1;
+          a->n = se - sb;
+          nvls = true;
+        } else if (c->algo == dfcclAlgoOneShot || n == 1) {
           for (int j = 0; j < n; ++j) a->src[a->nsrc++] = sendPtrOf(sh, b, j) + bb * es;
           a->dst[a->ndst++] = recvPtrOf(sh, b, me) + bb * eo;
           a->n = be - bb;
@@ -275,7 +287,7 @@ DF_HD void dataPhase(BlockShared* sh, RankDev* rd, int b) {
       }
       default: break;
     }
-    sh->ctl1 = reduce ? 1 : 0;
+    sh->ctl1 = nvls ? 2 : reduce ? 1 : 0;
     if (reduce) sh->stats.bytesReduced += a->n * es * a->nsrc; else sh->stats.bytesCopied += a->n * (a->ndst ? a->ndst : 0);
   }
   df_sync();
@@ -284,7 +296,10 @@ DF_HD void dataPhase(BlockShared* sh, RankDev* rd, int b) {
       sh->args.nsrc, sh->args.ndst, (unsigned long long)sh->args.n, sh->args.src[0], sh->args.src[1], sh->args.dst[0], sh->args.scale);
 #endif
   if (sh->args.n != 0 && sh->args.ndst != 0) {
-    if (sh->ctl1) {
+    if (sh->ctl1 == 2) {
+      if (!nvlsDispatch(c->inType, c->outType, c->mcHeap, c->nvlsPeers, n, (uint64_t)(uintptr_t)sh->args.src[0],
+                        (uint64_t)(uintptr_t)sh->args.dst[0], sh->args.n, (float)c->scale) && df_tid() == 0) sh->dyn.status = ST_BAD_ARG;
+    } else if (sh->ctl1) {
       if (!reduce_dispatch(c->inType, c->outType, c->op, &sh->args) && df_tid() == 0) sh->dyn.status = ST_BAD_ARG;
     } else {
       copy_multi(&sh->args);

@@ -87,7 +87,11 @@ struct alignas(16) CollStatic {
   FlagSlot* myFlags;                            // [nBlocks][nranks] in my heap
   FlagSlot* peerFlags[DF_MAX_RANKS];            // the same block of member j, as mapped here
   char* peerHeap[DF_MAX_RANKS];                 // heap base of member j, as mapped here
-  char* mcHeap;                                 // multicast mapping of the heaps (NVLS) or null
+  // NVLS schedule: the arena's multicast mapping (null where the view is emulated), the members' arena
+  // blocks for the emulation (host backend; null on GPUs), and this collective's staging slots in the arena
+  char* mcHeap;
+  char** nvlsPeers;
+  uint64_t nvlsIn, nvlsOut;
 };
 
 // ---- mutable per (block, collective) state; what a context switch saves and loads

@@ -239,6 +239,7 @@ TunerChoice tunerChoose(const Topology& t, int kind, size_t bytes, int n, int ma
   for (int a : algos) {
     if (pinnedAlgo != dfcclAlgoAuto && a != pinnedAlgo) continue;
     if (a == dfcclAlgoNvls && !(nvls && kind == dfcclCollAllReduce)) continue;
+    if (a == dfcclAlgoNvls && pinnedAlgo != dfcclAlgoNvls && bytes < (size_t)paramI64("NVLS_MIN_BYTES", 256 << 10)) continue;
     if (a == dfcclAlgoOneShot && kind != dfcclCollAllReduce) continue;
     size_t work = bytes * (kind == dfcclCollAllGather || kind == dfcclCollReduceScatter ? 1 : 1);
     int nb = pinnedBlocks ? pinnedBlocks : (int)std::min<size_t>(maxBlocks, std::max<size_t>(1, work / minPerBlock));

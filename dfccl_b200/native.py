@@ -90,6 +90,8 @@ def lib() -> C.CDLL:
             "dfcclSetBackend": [i], "dfcclGetBackend": [C.POINTER(i)],
             "dfcclMemAlloc": [C.POINTER(vp), sz, vp], "dfcclMemFree": [vp, vp],
             "dfcclHeapInfo": [vp, C.POINTER(vp), C.POINTER(sz), C.POINTER(sz)],
+            "dfcclNvlsInit": [vp, sz, C.POINTER(i)], "dfcclNvlsAlloc": [C.POINTER(vp), sz, vp],
+            "dfcclNvlsInfo": [vp, C.POINTER(vp), C.POINTER(vp), C.POINTER(sz), C.POINTER(sz)],
             "ofcclInitRankCtx": [C.POINTER(vp), i], "dfcclInitRankCtxOnDevice": [C.POINTER(vp), i, i],
             "ofcclFinalizeRankCtx7StartHostThrds": [vp], "ofcclPrepareDone": [vp], "ofcclDestroy": [vp],
             "dfcclPrepare": [C.POINTER(CollInfo), vp, i, vp],
@@ -211,6 +213,23 @@ class Comm:
 
     def free(self, ptr: int) -> None:
         check(lib().dfcclMemFree(C.c_void_p(ptr), self.handle), "dfcclMemFree")
+
+    def nvls_init(self, nbytes: int = 0) -> bool:
+        """Collective: bind ``nbytes`` per member to a switch-multicast object.  False when unavailable."""
+        ok = C.c_int(0)
+        check(lib().dfcclNvlsInit(self.handle, nbytes, C.byref(ok)), "dfcclNvlsInit")
+        return bool(ok.value)
+
+    def nvls_alloc(self, nbytes: int) -> int:
+        """Symmetric allocation in the NVLS arena (same sizes, same order on every member)."""
+        p = C.c_void_p()
+        check(lib().dfcclNvlsAlloc(C.byref(p), nbytes, self.handle), "dfcclNvlsAlloc")
+        return p.value
+
+    def nvls_info(self):
+        uc, mc, b, u = C.c_void_p(), C.c_void_p(), C.c_size_t(), C.c_size_t()
+        check(lib().dfcclNvlsInfo(self.handle, C.byref(uc), C.byref(mc), C.byref(b), C.byref(u)), "dfcclNvlsInfo")
+        return uc.value, mc.value, b.value, u.value
 
     def peer_base(self, peer: int) -> int:
         b = C.c_void_p()

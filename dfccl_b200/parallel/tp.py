@@ -14,6 +14,7 @@ from __future__ import annotations
 from typing import Dict, Tuple
 
 import torch
+import torch.distributed as dist
 import torch.nn as nn
 
 from .. import native as nv
@@ -38,12 +39,20 @@ def shared_op(kind, tp: TpGroup, *shape):
     return _OPS[key]
 
 
+def _fused(tp: TpGroup) -> bool:
+    """Fused kernels on GPUs; collective + plain GEMM on the host backend (tests) and on the comparison arm."""
+    return tp.device.type == "cuda" and getattr(tp, "library", "dfccl") == "dfccl"
+
+
 def tp_all_gather(tp: TpGroup, x: torch.Tensor) -> torch.Tensor:
     """Concatenate the ranks' tensors along dim 0 with this library's stream-ordered all-gather."""
     if tp.n == 1:
         return x
     x = x.contiguous()
     out = torch.empty((x.shape[0] * tp.n,) + tuple(x.shape[1:]), dtype=x.dtype, device=x.device)
+    if getattr(tp, "library", "dfccl") == "torch":         # comparison arm: the collective library behind torch.distributed
+        dist.all_gather_into_tensor(out, x, group=tp.pg)
+        return out
     nv.check(nv.lib().ncclAllGather(x.data_ptr(), out.data_ptr(), x.numel(), nccl_dtype(x.dtype), tp.comm.handle,
                                     _stream(x)), "ncclAllGather")
     return out
@@ -56,6 +65,9 @@ def tp_reduce_scatter(tp: TpGroup, x: torch.Tensor) -> torch.Tensor:
     x = x.contiguous()
     rows = x.shape[0] // tp.n
     out = torch.empty((rows,) + tuple(x.shape[1:]), dtype=x.dtype, device=x.device)
+    if getattr(tp, "library", "dfccl") == "torch":
+        dist.reduce_scatter_tensor(out, x, group=tp.pg)
+        return out
     nv.check(nv.lib().ncclReduceScatter(x.data_ptr(), out.data_ptr(), out.numel(), nccl_dtype(x.dtype), nv.SUM, tp.comm.handle,
                                         _stream(x)), "ncclReduceScatter")
     return out
@@ -112,7 +124,7 @@ class ColumnParallelLinear(nn.Module):
         w = full_weight.view(parts, tp.n, out_features // (parts * tp.n), in_features)[:, tp.rank]
         self.weight = nn.Parameter(w.reshape(nl, in_features).to(torch.bfloat16).contiguous())
         self.bias = nn.Parameter(torch.zeros(nl, dtype=torch.bfloat16, device=tp.device))
-        self.op = shared_op(AllGatherGemm, tp, rows_per_rank, in_features, nl) if tp.device.type == "cuda" else None
+        self.op = shared_op(AllGatherGemm, tp, rows_per_rank, in_features, nl) if _fused(tp) else None
 
     def forward(self, x_shard):
         return _ColumnFn.apply(x_shard, self.weight, self) + self.bias
@@ -131,7 +143,7 @@ class RowParallelLinear(nn.Module):
         self.weight = nn.Parameter(full_weight[:, tp.rank * kl:(tp.rank + 1) * kl].to(torch.bfloat16).contiguous())
         self.bias = nn.Parameter(torch.zeros(out_features, dtype=torch.bfloat16, device=tp.device))
         self.bias.tp_replicated = True
-        self.op = shared_op(GemmReduceScatter, tp, m, kl, out_features) if tp.device.type == "cuda" else None
+        self.op = shared_op(GemmReduceScatter, tp, m, kl, out_features) if _fused(tp) else None
 
     def forward(self, x):
         return _RowFn.apply(x, self.weight, self) + self.bias

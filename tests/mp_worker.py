@@ -289,3 +289,63 @@ def scenario_gpt_pp2dp2(nv, comm, rank, world, backend):
 
 def scenario_gpt_tp2pp2dp2(nv, comm, rank, world, backend):
     return _gpt_hybrid(nv, comm, rank, world, backend, 2, 2, 2, 29584)
+
+
+def scenario_nvls(nv, comm, rank, world, backend):
+    """All-reduce through the switch-multicast arena: daemon (fused scale + cast, arena-resident and staged
+    buffers) and the stream-ordered entry point (in place in the arena, and staged in pieces)."""
+    os.environ["DFCCL_NVLS_MIN_BYTES"] = "4096"
+    small = backend == "host"                               # the shared-memory heap of the CPU runs is small
+    if small:
+        os.environ["DFCCL_NVLS_STREAM_BYTES"] = str(8 << 20)
+    arena = (48 << 20) if small else (256 << 20)
+    if not comm.nvls_init(arena):
+        return {"available": False}
+    uc, mc, nbytes, used = comm.nvls_info()
+    assert uc and nbytes >= arena and (backend == "host" or mc)
+    import torch
+    cuda = backend == "cuda"
+    dev = torch.device("cuda", rank) if cuda else torch.device("cpu")
+    from dfccl_b200.utils import tensor_from_ptr
+    out = {"available": True}
+    ctx = nv.RankCtx(rank, rank if cuda else -1)
+    count = (256 * 1024 if small else 3 * 1024 * 1024) + 4096
+    ctx.prepare(1, comm, nv.ALLREDUCE, count, nv.BFLOAT16, out_dtype=nv.FLOAT32, op=nv.SUM, scale=1.0 / world, algo=nv.ALGO_NVLS)
+    ctx.prepare(2, comm, nv.ALLREDUCE, count, nv.FLOAT32, op=nv.SUM, algo=nv.ALGO_NVLS)
+    ctx.finalize()
+    g = torch.Generator().manual_seed(9)
+    full = torch.rand(world, count, generator=g) * 2 - 1
+    # 1: bf16 gradients averaged into fp32, buffers in the arena (zero copy)
+    sp, rp = comm.nvls_alloc(count * 2), comm.nvls_alloc(count * 4)
+    s, r = tensor_from_ptr(sp, (count,), torch.bfloat16, dev), tensor_from_ptr(rp, (count,), torch.float32, dev)
+    ref = full.to(torch.bfloat16).float().sum(0) / world
+    for it in range(3):
+        s.copy_(full[rank].to(torch.bfloat16))
+        r.zero_()
+        if cuda:
+            torch.cuda.synchronize()
+        ctx.run(1, sp, rp)
+        assert ctx.wait(1, 30000) == nv.SUCCESS
+        err = (r.cpu() - ref).abs().max().item()
+        assert err < 2e-2, ("nvls bf16->f32", it, err)
+    # 2: fp32 sum, ordinary device tensors (staged through the arena slots)
+    a = full[rank].to(dev).contiguous()
+    b = torch.zeros(count, device=dev)
+    if cuda:
+        torch.cuda.synchronize()
+    ctx.run(2, a.data_ptr(), b.data_ptr())
+    assert ctx.wait(2, 30000) == nv.SUCCESS
+    err = (b.cpu() - full.sum(0)).abs().max().item()
+    assert err < 1e-4, ("nvls f32 staged", err)
+    out["daemon"] = ctx.stats()["cqesDelivered"]
+    ctx.destroy()
+    # stream-ordered: a tensor larger than the staging front of the arena goes through it in pieces
+    n2 = (3 if small else 24) * 1024 * 1024
+    x = torch.full((n2,), float(rank + 1), device=dev)
+    stream = torch.cuda.current_stream().cuda_stream if cuda else None
+    nv.check(nv.lib().ncclAllReduce(x.data_ptr(), x.data_ptr(), n2, nv.FLOAT32, nv.SUM, comm.handle, stream))
+    if cuda:
+        torch.cuda.synchronize()
+    want = world * (world + 1) / 2
+    assert float(x.min()) == want and float(x.max()) == want, (float(x.min()), float(x.max()), want)
+    return out

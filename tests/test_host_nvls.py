@@ -1,0 +1,124 @@
+"""The NVLS all-reduce schedule on the host backend: the switch's multicast view is emulated by a loop
+over the members' arena blocks, everything around it (slots, staging, rendezvous, in-place buffers,
+fused scale and cast, fall-back when the arena is full) is the code that runs on GPUs."""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+from helpers import bf16_bits_to_f32, f32_to_bf16_bits, host_array, np_dtype, run_ranks
+
+
+def _inputs(nv, dt, n, nranks, seed):
+    out = []
+    for r in range(nranks):
+        x = np.random.default_rng(seed + r).uniform(-1, 1, n).astype(np.float32)
+        out.append(f32_to_bf16_bits(x) if dt == nv.BFLOAT16 else x.astype(np_dtype(nv, dt)))
+    return out
+
+
+def _f32(nv, dt, a):
+    return bf16_bits_to_f32(a) if dt == nv.BFLOAT16 else a.astype(np.float32)
+
+
+@pytest.mark.parametrize("dt_name,out_name", [("FLOAT32", "FLOAT32"), ("BFLOAT16", "BFLOAT16"), ("BFLOAT16", "FLOAT32"),
+                                              ("FLOAT16", "FLOAT16"), ("FLOAT16", "FLOAT32")])
+@pytest.mark.parametrize("where", ["arena", "heap", "user"])
+def test_daemon_allreduce_nvls(host_backend, dt_name, out_name, where):
+    nv = host_backend
+    dt, odt = getattr(nv, dt_name), getattr(nv, out_name)
+    nranks, count, scale = 4, 40 * 1024, 0.25
+    comms = nv.Comm.init_loopback(nranks)
+    ins = _inputs(nv, dt, count, nranks, 7)
+    exp = sum(_f32(nv, dt, a).astype(np.float64) for a in ins) * scale
+    got = {}
+
+    def body(r):
+        c = comms[r]
+        assert c.nvls_init(8 << 20)
+        ctx = nv.RankCtx(r)
+        ctx.prepare(3, c, nv.ALLREDUCE, count, dt, out_dtype=odt, op=nv.SUM, scale=scale, algo=nv.ALGO_NVLS)
+        ctx.finalize()
+        es, eo = nv.DTYPE_SIZE[dt], nv.DTYPE_SIZE[odt]
+        keep = []
+        if where == "arena":
+            sp, rp = c.nvls_alloc(count * es), c.nvls_alloc(count * eo)
+        elif where == "heap":
+            sp, rp = c.alloc(count * es), c.alloc(count * eo)
+        else:
+            a, b = np.zeros(count, np_dtype(nv, dt)), np.zeros(count, np_dtype(nv, odt))
+            keep += [a, b]
+            sp, rp = a.ctypes.data, b.ctypes.data
+        sv, rv = host_array(sp, count, np_dtype(nv, dt)), host_array(rp, count, np_dtype(nv, odt))
+        for it in range(3):
+            sv[:] = ins[r]
+            rv[:] = 0
+            ctx.run(3, sp, rp)
+            assert ctx.wait(3, 30000) == nv.SUCCESS
+        got[r] = rv.copy()
+        st = ctx.stats()
+        ctx.destroy()
+        assert st["waitTimeouts"] == 0
+
+    run_ranks(nranks, body)
+    for c in comms:
+        c.destroy()
+    tol = 2e-2 if odt != nv.FLOAT32 or dt != nv.FLOAT32 else 1e-5
+    for r in range(nranks):
+        np.testing.assert_allclose(_f32(nv, odt, got[r]), exp, rtol=tol, atol=tol)
+
+
+def test_stream_allreduce_nvls_chunked_and_in_place(host_backend, monkeypatch):
+    """ncclAllReduce picks the schedule by size; a message larger than the staging slots goes in pieces;
+    a buffer from the arena is reduced in place."""
+    nv = host_backend
+    monkeypatch.setenv("DFCCL_NVLS_STREAM_BYTES", str(1 << 20))
+    monkeypatch.setenv("DFCCL_NVLS_MIN_BYTES", "4096")
+    monkeypatch.setenv("DFCCL_ALGO", "nvls")
+    nranks, count = 2, 600 * 1024 + 64          # 2.4 MB of fp32: 5 pieces of 512 KB
+    comms = nv.Comm.init_loopback(nranks)
+    ins = _inputs(nv, nv.FLOAT32, count, nranks, 3)
+    exp = ins[0].astype(np.float64) + ins[1]
+    got = {}
+
+    def body(r):
+        c = comms[r]
+        assert c.nvls_init(16 << 20)
+        a, b = ins[r].copy(), np.zeros(count, np.float32)
+        nv.check(nv.lib().ncclAllReduce(a.ctypes.data, b.ctypes.data, count, nv.FLOAT32, nv.SUM, c.handle, None))
+        p = c.nvls_alloc(count * 4)
+        v = host_array(p, count, np.float32)
+        v[:] = ins[r]
+        nv.check(nv.lib().ncclAllReduce(p, p, count, nv.FLOAT32, nv.SUM, c.handle, None))
+        got[r] = (b, v.copy())
+
+    run_ranks(nranks, body)
+    for c in comms:
+        c.destroy()
+    for r in range(nranks):
+        np.testing.assert_allclose(got[r][0], exp, rtol=1e-5, atol=1e-5)
+        np.testing.assert_allclose(got[r][1], exp, rtol=1e-5, atol=1e-5)
+
+
+def test_arena_full_falls_back(host_backend):
+    nv = host_backend
+    nranks, count = 2, 1 << 20
+    comms = nv.Comm.init_loopback(nranks)
+    ins = _inputs(nv, nv.FLOAT32, count, nranks, 5)
+    exp = ins[0] + ins[1]
+
+    def body(r):
+        c = comms[r]
+        assert c.nvls_init(2 << 20)                # too small for 4 MB in + 4 MB out
+        ctx = nv.RankCtx(r)
+        ctx.prepare(0, c, nv.ALLREDUCE, count, nv.FLOAT32, algo=nv.ALGO_NVLS)
+        ctx.finalize()
+        a, b = ins[r].copy(), np.zeros(count, np.float32)
+        ctx.run(0, a.ctypes.data, b.ctypes.data)
+        assert ctx.wait(0, 30000) == nv.SUCCESS
+        ctx.destroy()
+        np.testing.assert_allclose(b, exp, rtol=1e-5, atol=1e-5)
+
+    run_ranks(nranks, body)
+    for c in comms:
+        c.destroy()

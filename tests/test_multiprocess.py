@@ -54,3 +54,19 @@ def test_gpu_gpt2_hybrid_parallel():
     n = torch.cuda.device_count()
     layout, world = ("tp2pp2dp2", 8) if n >= 8 else ("tp2pp2", 4) if n >= 4 else ("tp2", 2)
     mp_worker.launch(world, "cuda", "gpt_" + layout, timeout=600)
+
+
+def test_host_processes_nvls_schedule():
+    res = mp_worker.launch(2, "host", "nvls", timeout=200)
+    assert all(r["available"] and r["daemon"] == 4 for r in res.values())
+
+
+@pytest.mark.gpu
+@pytest.mark.multigpu
+def test_gpu_nvls_allreduce():
+    """multimem.ld_reduce / multimem.st all-reduce; skipped by the library itself (available = False) on
+    machines whose devices or driver cannot create a multicast object."""
+    import torch
+    res = mp_worker.launch(min(torch.cuda.device_count(), 4), "cuda", "nvls", timeout=300)
+    if not all(r["available"] for r in res.values()):
+        pytest.skip("no NVLink-switch multicast on this machine")
