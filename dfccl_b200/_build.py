@@ -88,7 +88,7 @@ def build(verbose: bool = False, force: bool = False, extra_sources=()) -> Path:
         objs = list(ex.map(lambda s: _compile(s, verbose, hdr), srcs))
     if LIB.exists() and all(LIB.stat().st_mtime > o.stat().st_mtime for o in objs):
         return LIB
-    cmd = [nvcc(), "-shared", "-rdc=true", "-Xcompiler", "-fPIC", "-o", str(LIB)] + [str(o) for o in objs] + ARCH + ["-lrt", "-lpthread", "-ldl", "-cudart", "static"]
+    cmd = [nvcc(), "-shared", "-rdc=true", "-Xcompiler", "-fPIC", "-o", str(LIB)] + [str(o) for o in objs] + ARCH + ["-lrt", "-lpthread", "-ldl", "-cudart", "static", "-Xlinker", "-Bsymbolic"]
     r = subprocess.run(cmd, capture_output=True, text=True)
     if r.returncode != 0:
         raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")

@@ -16,8 +16,11 @@ copy of each step's tokens and the device -> host read of its loss.
 from __future__ import annotations
 
 import argparse
+import faulthandler
 import json
 import os
+import threading
+import time
 
 import torch
 import torch.distributed as dist
@@ -50,6 +53,7 @@ class TorchGradSync:
             for g, f in zip(grads, torch._utils._unflatten_dense_tensors(flat, grads)):
                 g.copy_(f)
 
+    @torch.no_grad()
     def step(self):
         for params, _, _ in self.groups:
             ps = [p for p in params if p.grad is not None]
@@ -96,7 +100,6 @@ def main(argv=None):
     ap.add_argument("--impl", default="dfccl", choices=["dfccl", "nccl"])
     ap.add_argument("--out", default="")
     a = ap.parse_args(argv)
-    import faulthandler
     faulthandler.dump_traceback_later(int(os.environ.get("BENCH_WATCHDOG_S", "600")), exit=True)
     os.environ.setdefault("DFCCL_WAIT_TIMEOUT_MS", "60000")
     d = init_distributed()
@@ -128,8 +131,30 @@ def main(argv=None):
         d.barrier()
         torch.cuda.synchronize()
 
+    progress = {"step": 0, "t": time.time()}
+
+    def monitor():                                          # a stalled run says where the daemon stands, then leaves
+        limit = float(os.environ.get("BENCH_STALL_S", "60"))
+        while True:
+            time.sleep(2.0)
+            if progress["step"] < 0:
+                return
+            if time.time() - progress["t"] > limit:
+                print(f"[rank {d.rank}] no step finished for {limit:.0f} s at step {progress['step']}; daemon: {tr.ddp.stats()}", flush=True)
+                faulthandler.dump_traceback()
+                os._exit(3)
+
+    threading.Thread(target=monitor, daemon=True).start()
+
+    def one_step(tok, tgt):
+        out = tr.step(tok, tgt)
+        progress["step"] += 1
+        progress["t"] = time.time()
+        return out
+
     for _ in range(max(a.warmup, 3)):
-        tr.step(dtok, dtgt)
+        one_step(dtok, dtgt)
+        torch.cuda.synchronize()
     sync()
     l0 = tr.ddp.stats().get("daemonLaunches", 0) + tr.ddp.launches
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -137,7 +162,7 @@ def main(argv=None):
         sync()
         e0.record()
         for _ in range(a.steps):
-            loss = tr.step(dtok, dtgt)
+            loss = one_step(dtok, dtgt)
         e1.record()
         sync()
     t = torch.tensor([e0.elapsed_time(e1)], device=dev, dtype=torch.float64)
@@ -154,7 +179,7 @@ def main(argv=None):
     for i in range(a.steps):
         hb = host[i % len(host)]
         db = hb.to(dev, non_blocking=True)
-        loss = tr.step(db[..., :-1], db[..., 1:])
+        loss = one_step(db[..., :-1], db[..., 1:])
         loss_host[i:i + 1].copy_(loss, non_blocking=True)
     e3.record()
     sync()
@@ -165,6 +190,7 @@ def main(argv=None):
     tokens = a.dp * a.n_micro * a.micro_batch * cfg.seq_len
     flops = 6.0 * cfg.n_params() * tokens + 12.0 * cfg.n_layer * cfg.d_model * cfg.seq_len * tokens
     stats = tr.ddp.stats()
+    progress["step"] = -1
     tr.close()
     if d.rank == 0:
         out = {"metric": "gpt2_medium_train_tokens_per_s" if a.model == "medium" else "gpt2_tiny_train_tokens_per_s",

@@ -184,6 +184,8 @@ ncclResult_t commCollective(ncclComm* c, int kind, const void* send, void* recv,
                             ncclRedOp_t op, int root, cudaStream_t stream) {
   if (!c) { DF_WARN("null communicator"); return ncclInvalidArgument; }
   if (c->aborted) return ncclInvalidUsage;
+  // a stream-ordered kernel that gave up left its verdict in pinned memory: fail at the next call instead of queueing more waits
+  if (c->ctl->pad) { c->asyncError = c->ctl->pad == ST_TIMEOUT ? dfcclTimeout : dfcclAborted; DF_WARN("an earlier stream-ordered collective of this communicator failed (%s)", c->ctl->pad == ST_TIMEOUT ? "timed out" : "aborted"); return c->asyncError; }
   if ((int)type < 0 || (int)type >= ncclNumTypes) { DF_WARN("invalid datatype %d", (int)type); return ncclInvalidArgument; }
   if (root < 0 || root >= c->nranks) { DF_WARN("invalid root %d", root); return ncclInvalidArgument; }
   if (count == 0) return ncclSuccess;

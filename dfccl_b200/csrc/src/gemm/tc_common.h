@@ -49,11 +49,20 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
-// Bounded wait: false when the limit ran out or another role already gave up.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile uint32_t* giveUp, uint32_t limit = 20000000u) {
-  for (uint32_t i = 0; i < limit; ++i) {
+// Bounded wait: false when the time limit ran out or another role already gave up.  The limit is
+// generous because a role may legitimately wait as long as the slowest peer GPU is late; the waits on
+// peers carry the caller's own (shorter) limit and raise giveUp first.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile uint32_t* giveUp, uint64_t limitNs = 120000000000ull) {
+  uint64_t t0 = 0;
+  for (uint32_t i = 0;; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
-    if ((i & 1023) == 1023 && *giveUp) return false;
+    if ((i & 1023) == 1023) {
+      if (*giveUp) return false;
+      uint64_t t;
+      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+      if (t0 == 0) t0 = t;
+      else if (t - t0 > limitNs) break;
+    }
   }
   *giveUp = 1;
   return false;

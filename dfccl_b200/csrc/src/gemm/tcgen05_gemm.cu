@@ -16,6 +16,7 @@
 // filled by TMA (no cluster multicast anywhere), full/empty mbarriers, tcgen05.commit to release
 // stages and to hand accumulators over.  Every wait is bounded and ends in an error word.
 #include "tc_common.h"
+#include "../common/param.h"
 #include "dfccl.h"
 #include "../common/log.h"
 #include <map>
@@ -62,7 +63,9 @@ struct FusedArgs {
 struct GemmArgs {
   __nv_bfloat16* C;
   int M, N, K, ldc;
-  uint32_t* err;                    // device word: non-zero = a bounded wait ran out
+  uint32_t* err;                    // device word: non-zero = a bounded wait ran out (later launches return at once)
+  uint64_t waitNs;                  // limit of every wait on a word another GPU or CTA writes
+  uint32_t* errHost;                // the same verdict in pinned host memory, read by the host without a synchronisation
   FusedArgs f;
 };
 
@@ -100,18 +103,33 @@ __device__ __forceinline__ void st_peer16(void* p, uint4 v) {
 }
 
 // Bounded spin on a 64-bit flag in local memory written by a peer.
-__device__ __forceinline__ bool wait_flag64(const volatile uint64_t* p, uint64_t want, volatile uint32_t* giveUp) {
-  for (uint32_t i = 0; i < 40000000u; ++i) {
+// Waits on words that another GPU (or another CTA) writes are bounded by time, not by polls: a peer may
+// legitimately be seconds late (its host was slow to launch), but never forever.
+__device__ __forceinline__ uint64_t now_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+__device__ __forceinline__ bool wait_flag64(const volatile uint64_t* p, uint64_t want, volatile uint32_t* giveUp, uint64_t limitNs) {
+  const uint64_t t0 = now_ns();
+  for (uint32_t i = 0;; ++i) {
     if (ld_acq_sys(p) >= want) return true;
-    if ((i & 255) == 255 && *giveUp) return false;
+    if ((i & 255) == 255) {
+      if (*giveUp) return false;
+      if (now_ns() - t0 > limitNs) break;
+    }
   }
   *giveUp = 1;
   return false;
 }
-__device__ __forceinline__ bool wait_flag32(const uint32_t* p, uint32_t want, volatile uint32_t* giveUp, bool sys) {
-  for (uint32_t i = 0; i < 40000000u; ++i) {
+__device__ __forceinline__ bool wait_flag32(const uint32_t* p, uint32_t want, volatile uint32_t* giveUp, bool sys, uint64_t limitNs) {
+  const uint64_t t0 = now_ns();
+  for (uint32_t i = 0;; ++i) {
     if ((sys ? ld_acq_sys_u32(p) : ld_acq_gpu_u32(p)) >= want) return true;
-    if ((i & 255) == 255 && *giveUp) return false;
+    if ((i & 255) == 255) {
+      if (*giveUp) return false;
+      if (now_ns() - t0 > limitNs) break;
+    }
   }
   *giveUp = 1;
   return false;
@@ -146,7 +164,7 @@ dfcclGemmKernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) { mbar_init(&fullBar[s], 1); mbar_init(&emptyBar[s], 1); }
     for (int a = 0; a < 2; ++a) { mbar_init(&accFull[a], 1); mbar_init(&accEmpty[a], 4); }
-    *giveUp = 0;
+    *giveUp = *(volatile uint32_t*)g.err;          // an earlier launch gave up: its flags and counters are stale, do nothing
     mbar_fence_init();
     tma_prefetch_desc(&mapA);
     tma_prefetch_desc(&mapB);
@@ -156,13 +174,15 @@ dfcclGemmKernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
   __syncthreads();
   tc_fence_after();
   const uint32_t tmemBase = *tmemBaseSlot;
-  if (f.mode == 2 && f.nranks > 1) {
+  const bool dead = *giveUp != 0;
+  if (!dead && f.mode == 2 && f.nranks > 1) {
     // the owners must have finished reducing the previous call before this one overwrites their slots
-    if (warp == 2 && lane < f.nranks && lane != f.rank) wait_flag64(&f.done[lane], f.epoch - 1, giveUp);
+    if (warp == 2 && lane < f.nranks && lane != f.rank) wait_flag64(&f.done[lane], f.epoch - 1, giveUp, g.waitNs);
     __syncthreads();
   }
 
-  if (warp == 0) {
+  if (dead) {
+  } else if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
     if (elect_one()) {
       int stage = 0;
@@ -172,7 +192,7 @@ dfcclGemmKernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
         const int mt = orderedMTile(f, t / nTiles, mTiles), nt = t % nTiles;
         if (f.mode == 1 && f.nranks > 1 && mt / (f.rowsPerRank / BM) != f.rank) {
           // this row block comes from a peer: wait until the communication warps have placed it
-          ok = wait_flag32(&f.blockReady[mt], (uint32_t)f.epoch * GATHER_PIECES, giveUp, false);
+          ok = wait_flag32(&f.blockReady[mt], (uint32_t)f.epoch * GATHER_PIECES, giveUp, false, g.waitNs);
           asm volatile("fence.proxy.async.global;" ::: "memory");   // their generic-proxy stores before my async-proxy loads
           if (!ok) break;
         }
@@ -297,7 +317,7 @@ dfcclGemmKernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
         const int bi = i / GATHER_PIECES, piece = i % GATHER_PIECES;
         const int owner = (f.rank + 1 + bi / blocksPerRank) % f.nranks;
         const int blk = bi % blocksPerRank;
-        if (ct == 0) ok = wait_flag64(&f.arrive[owner], f.epoch, giveUp);
+        if (ct == 0) ok = wait_flag64(&f.arrive[owner], f.epoch, giveUp, g.waitNs);
         asm volatile("bar.sync 2, 128;" ::: "memory");
         if (*giveUp) break;
         const uint4* src = (const uint4*)((const char*)f.peerA[owner] + (size_t)blk * blockBytes + (size_t)piece * pieceBytes);
@@ -325,13 +345,13 @@ dfcclGemmKernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
           for (int j = 0; j < f.nranks; ++j) if (j != f.rank) st_rel_sys(f.peerDone[j], f.epoch);
         }
       }
-      if (blockIdx.x == 0 && ct < f.nranks && ct != f.rank) wait_flag64(&f.done[ct], f.epoch, giveUp);   // my shard stays put until read
+      if (blockIdx.x == 0 && ct < f.nranks && ct != f.rank) wait_flag64(&f.done[ct], f.epoch, giveUp, g.waitNs);   // my shard stays put until read
     } else if (f.mode == 2 && f.nranks > 1) {
       // reduce the tiles I own as their n partial copies arrive: slot[j] written by rank j's epilogue
       const int tilesMine = (f.rowsPerRank / BM) * nTiles;
       for (int i = blockIdx.x; i < tilesMine; i += gridDim.x) {
         const int tm = i / nTiles, tn = i % nTiles;
-        if (ct < f.nranks) wait_flag32(f.myTileFlags + (size_t)ct * tilesMine + i, (uint32_t)f.epoch, giveUp, true);
+        if (ct < f.nranks) wait_flag32(f.myTileFlags + (size_t)ct * tilesMine + i, (uint32_t)f.epoch, giveUp, true, g.waitNs);
         asm volatile("bar.sync 2, 128;" ::: "memory");
         if (*giveUp) break;
         // 128 rows x 256 columns = 4096 chunks of 16 bytes; consecutive threads take consecutive chunks of a
@@ -384,7 +404,7 @@ dfcclGemmKernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
   tc_fence_before();
   __syncthreads();
   if (warp == 1) tmem_dealloc(tmemBase, TMEM_COLS);
-  if (threadIdx.x == 0 && *giveUp) atomicExch(g.err, 1u);
+  if (threadIdx.x == 0 && *giveUp && !dead) { atomicExch(g.err, 1u); *(volatile uint32_t*)g.errHost = 1u; __threadfence_system(); }
 }
 
 // ---- host side
@@ -438,13 +458,21 @@ ncclResult_t makeMapUncached(CUtensorMap* m, const void* base, uint64_t rows, ui
   return ncclSuccess;
 }
 
-uint32_t* errWord() {                       // one device word per device, created on first use
-  static uint32_t* w[64] = {nullptr};
+struct ErrWords { uint32_t* dev = nullptr; volatile uint32_t* host = nullptr; };
+ErrWords errWords() {                       // one pair per device, created on first use
+  static ErrWords w[64];
   static std::mutex mu;
   int dev = 0;
   cudaGetDevice(&dev);
   std::lock_guard<std::mutex> l(mu);
-  if (!w[dev]) { cudaMalloc((void**)&w[dev], 4); cudaMemset(w[dev], 0, 4); }
+  if (!w[dev].dev) {
+    cudaMalloc((void**)&w[dev].dev, 4);
+    cudaMemset(w[dev].dev, 0, 4);
+    uint32_t* h = nullptr;
+    cudaHostAlloc((void**)&h, 4, cudaHostAllocMapped | cudaHostAllocPortable);
+    *h = 0;
+    w[dev].host = h;
+  }
   return w[dev];
 }
 
@@ -454,6 +482,8 @@ ncclResult_t launch(const void* A, const void* B, void* C, int M, int N, int K, 
     return ncclInvalidArgument;
   }
   if (((uintptr_t)A | (uintptr_t)B | (uintptr_t)C) & 15) return ncclInvalidArgument;
+  const ErrWords ew = errWords();
+  if (*ew.host) { DF_WARN("an earlier tensor-core kernel on this device gave up on a bounded wait; call dfcclGemmCheck to clear"); return dfcclTimeout; }
   CUtensorMap ma, mb;
   DFCHECK(makeMap(&ma, A, (uint64_t)M, (uint64_t)K, BM));
   DFCHECK(makeMap(&mb, B, (uint64_t)N, (uint64_t)K, BN));
@@ -461,7 +491,8 @@ ncclResult_t launch(const void* A, const void* B, void* C, int M, int N, int K, 
   std::call_once(once, [] { cudaFuncSetAttribute(dfcclGemmKernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES); });
   GemmArgs g;
   memset(&g, 0, sizeof(g));
-  g.C = (__nv_bfloat16*)C; g.M = M; g.N = N; g.K = K; g.ldc = N; g.err = errWord();
+  g.C = (__nv_bfloat16*)C; g.M = M; g.N = N; g.K = K; g.ldc = N; g.err = ew.dev; g.errHost = (uint32_t*)ew.host;
+  { int64_t ms = paramI64("WAIT_TIMEOUT_MS", 30000); g.waitNs = (uint64_t)(ms > 0 ? ms : 30000) * 1000000ull; }
   if (f) g.f = *f; else { g.f.nranks = 1; g.f.mode = 0; }
   int dev = 0, sms = 148;
   cudaGetDevice(&dev);
@@ -488,9 +519,9 @@ DF_API ncclResult_t dfcclGemmBf16(const void* A, const void* B, void* C, int M, 
 // Non-zero after a kernel of this file gave up on a bounded wait (reads and clears the word).
 DF_API ncclResult_t dfcclGemmCheck(int* failed) {
   uint32_t v = 0;
-  uint32_t* w = errWord();
-  CUDACHECK(cudaMemcpy(&v, w, 4, cudaMemcpyDeviceToHost));
-  if (v) CUDACHECK(cudaMemset(w, 0, 4));
+  const ErrWords ew = errWords();
+  CUDACHECK(cudaMemcpy(&v, ew.dev, 4, cudaMemcpyDeviceToHost));
+  if (v) { CUDACHECK(cudaMemset(ew.dev, 0, 4)); *ew.host = 0; }
   if (failed) *failed = (int)v;
   return ncclSuccess;
 }

@@ -66,7 +66,7 @@ def lib() -> C.CDLL:
         path = _build.LIB
         if not path.exists() or os.environ.get("DFCCL_REBUILD") == "1":
             path = _build.build()
-        L = C.CDLL(str(path), mode=C.RTLD_GLOBAL)
+        L = C.CDLL(str(path))       # local scope: the nccl* names must not shadow another collective library's
         vp, i, sz = C.c_void_p, C.c_int, C.c_size_t
         sig = {
             "ncclGetVersion": [C.POINTER(i)],

@@ -241,7 +241,7 @@ def _gpt_hybrid(nv, comm, rank, world, backend, tp, pp, dp, port):
     from dfccl_b200.models.gpt2 import GPT2Config, GPT2Stage
     from dfccl_b200.parallel.groups import Dist
     from dfccl_b200.parallel.hybrid import HybridTrainer, build_mesh
-    cfg = GPT2Config(n_layer=4, d_model=256, n_head=4, seq_len=128, vocab=512) if cuda else \
+    cfg = GPT2Config(n_layer=4, d_model=512, n_head=8, seq_len=128, vocab=512) if cuda else \
         GPT2Config(n_layer=2, d_model=64, n_head=4, seq_len=32, vocab=96)
     micro_batch, n_micro, steps = 2, 2, 3
     d = Dist(rank, world, rank if cuda else 0, dev, comm, True)
@@ -256,6 +256,9 @@ def _gpt_hybrid(nv, comm, rank, world, backend, tp, pp, dp, port):
         losses.append(float(tr.step(tok, tgt)))
     if cuda:
         torch.cuda.synchronize()
+        bad = C.c_int(0)
+        nv.check(nv.lib().dfcclGemmCheck(C.byref(bad)))
+        assert bad.value == 0, "a fused GEMM kernel gave up on a wait"
     st = tr.ddp.stats()
     tr.close()
     if rank == 0:                                           # the same model, unsharded, on this rank alone
