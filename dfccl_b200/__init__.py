@@ -7,3 +7,12 @@
 ``ops``        fused compute + collective operators
 """
 __version__ = "0.1.0"
+
+import os as _os
+
+# A kernel that CUDA loads lazily takes its first launch through a module load, which can wait for the
+# device to go idle.  If that happens while a stream is parked on a completion word that only the daemon
+# sets, and the daemon in turn needs a (re)launch from its observer thread, the two wait for each other.
+# Loading every kernel when its module is loaded removes the case.  Only effective when the package is
+# imported before the process creates its CUDA context; an explicit setting of the variable wins.
+_os.environ.setdefault("CUDA_MODULE_LOADING", "EAGER")

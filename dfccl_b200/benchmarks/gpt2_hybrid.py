@@ -92,7 +92,7 @@ def main(argv=None):
     ap.add_argument("--tp", type=int, default=0)
     ap.add_argument("--pp", type=int, default=0)
     ap.add_argument("--dp", type=int, default=0)
-    ap.add_argument("--micro-batch", type=int, default=4)
+    ap.add_argument("--micro-batch", type=int, default=8)
     ap.add_argument("--n-micro", type=int, default=4)
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
@@ -140,7 +140,8 @@ def main(argv=None):
             if progress["step"] < 0:
                 return
             if time.time() - progress["t"] > limit:
-                print(f"[rank {d.rank}] no step finished for {limit:.0f} s at step {progress['step']}; daemon: {tr.ddp.stats()}", flush=True)
+                hs = tr.ddp.ctx.host_stats() if hasattr(tr.ddp, "ctx") else {}
+                print(f"[rank {d.rank}] no step finished for {limit:.0f} s at step {progress['step']}; daemon (host view): {hs}", flush=True)
                 faulthandler.dump_traceback()
                 os._exit(3)
 

@@ -258,6 +258,9 @@ typedef struct {
   uint64_t deviceEvents;                          /* entries drained from the device trace ring */
 } dfcclStats;
 ncclResult_t dfcclGetStats(ofcclRankCtx_t rankCtx, dfcclStats* stats);
+/* Host-memory counters only (submissions, completions, launches, quits; deviceEvents = daemon believed alive):
+ * never touches the device, so it answers while the GPU is busy or stuck. */
+ncclResult_t dfcclGetHostStats(ofcclRankCtx_t rankCtx, dfcclStats* stats);
 
 /* Device trace ring: (globaltimer ns, block, collId, event) tuples written by the
  * daemon when DFCCL_TRACE=1; drained by the poller into a Chrome-trace JSON file. */

@@ -627,6 +627,17 @@ DF_API ncclResult_t dfcclGetAsyncError(ofcclRankCtx_t ctx, ncclResult_t* e) {
   return ncclSuccess;
 }
 
+// The counters that live in host memory only: safe to read while the device is busy or stuck.
+DF_API ncclResult_t dfcclGetHostStats(ofcclRankCtx_t ctx, dfcclStats* s) {
+  if (!ctx || !s) return ncclInvalidArgument;
+  memset(s, 0, sizeof(*s));
+  s->sqesSubmitted = ctx->sqes; s->cqesDelivered = ctx->cqes; s->callbacksRun = ctx->cbs; s->sqFullRetries = ctx->sqFull;
+  if (!ctx->finalized) return ncclSuccess;
+  s->daemonLaunches = ctx->ctl->launches; s->daemonVoluntaryQuits = ctx->ctl->voluntaryQuits;
+  s->deviceEvents = ctx->ctl->alive;               // 1 while an instance of the daemon is (believed to be) running
+  return ncclSuccess;
+}
+
 DF_API ncclResult_t dfcclGetStats(ofcclRankCtx_t ctx, dfcclStats* s) {
   if (!ctx || !s) return ncclInvalidArgument;
   memset(s, 0, sizeof(*s));

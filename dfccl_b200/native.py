@@ -105,7 +105,7 @@ def lib() -> C.CDLL:
             "dfcclRunOnStream": [vp, vp, i, vp, CALLBACK, vp, vp],
             "dfcclStreamWait": [i, vp, vp], "dfcclWait": [i, i, vp], "dfcclWaitAll": [i, vp],
             "dfcclAbort": [vp], "dfcclGetAsyncError": [vp, C.POINTER(i)],
-            "dfcclGetStats": [vp, C.POINTER(Stats)], "dfcclTraceDump": [vp, C.c_char_p],
+            "dfcclGetStats": [vp, C.POINTER(Stats)], "dfcclGetHostStats": [vp, C.POINTER(Stats)], "dfcclTraceDump": [vp, C.c_char_p],
             "dfcclInjectFault": [vp, i, C.c_int64],
             "dfcclFusedSgdStep": [vp, vp, vp, vp, sz, i, C.c_float, C.c_float, C.c_float, i, vp],
             "dfcclOpsWarm": [],
@@ -308,6 +308,12 @@ class RankCtx:
         s = Stats()
         check(lib().dfcclGetStats(self.handle, C.byref(s)), "dfcclGetStats")
         return s.as_dict()
+
+    def host_stats(self) -> Dict[str, int]:
+        """Host-side counters only; safe while the device is busy."""
+        s = Stats()
+        check(lib().dfcclGetHostStats(self.handle, C.byref(s)), "dfcclGetHostStats")
+        return {k: v for k, v in s.as_dict().items() if k in ("sqesSubmitted", "cqesDelivered", "daemonLaunches", "daemonVoluntaryQuits", "deviceEvents")}
 
     def trace_dump(self, path: str) -> None:
         check(lib().dfcclTraceDump(self.handle, path.encode()), "dfcclTraceDump")

@@ -85,6 +85,7 @@ class HybridTrainer:
         self.next = d.rank + mesh.tp if mesh.pp_rank < mesh.pp - 1 else None
         self._loss = torch.zeros(1, dtype=torch.float32, device=d.device)
         self.pp_bytes = 0
+        self._step_done = None
 
     def _hidden(self) -> torch.Tensor:
         st = self.stage
@@ -98,6 +99,12 @@ class HybridTrainer:
         """``tokens`` / ``targets``: [n_micro, micro_batch, seq] of this replica (tokens are read by the first
         stage, targets by the last).  Returns the mean loss over all replicas as a 1-element tensor on every rank."""
         st, n, ddp = self.stage, self.n_micro, self.ddp
+        # Eager steps are thousands of launches: a host that runs a whole step ahead sits blocked in a launch
+        # (queue full) exactly when the GPU reaches the bucket waits of the previous step, and the daemon's
+        # relaunch from its observer thread then queues behind that blocked launch.  Keeping the host within
+        # one step of the GPU costs nothing at these step times and removes the dependency.
+        if self._step_done is not None:
+            self._step_done.synchronize()
         ins: List[torch.Tensor] = []
         outs: List[torch.Tensor] = []
         sends = []
@@ -139,6 +146,9 @@ class HybridTrainer:
             s = torch.cuda.current_stream(self.d.device).cuda_stream if self.d.device.type == "cuda" else 0
             nv.check(nv.lib().ncclAllReduce(self._loss.data_ptr(), self._loss.data_ptr(), 1, nccl_dtype(torch.float32), nv.SUM,
                                             self.d.comm.handle, s), "ncclAllReduce(loss)")
+        if self.d.device.type == "cuda":
+            self._step_done = torch.cuda.Event()
+            self._step_done.record()
         return self._loss
 
     def close(self) -> None:
