@@ -4,6 +4,7 @@ wait for) and the fused optimizer kernel.  Sized above the L2 capacity, a few la
 profiler capture ends by itself.
 
     python -m dfccl_b200.benchmarks.kernel_probe --mbytes 256 --iters 3
+    python -m dfccl_b200.benchmarks.kernel_probe --gemm 8192 8192 8192 --iters 20     # tcgen05 GEMM vs cuBLAS
 """
 from __future__ import annotations
 
@@ -17,14 +18,48 @@ from dfccl_b200 import native as nv
 from dfccl_b200.utils import tensor_from_ptr
 
 
+def gemm_probe(mnk, iters):
+    """C[M,N] = A[M,K] B[N,K]^T in bf16: this library's tcgen05 kernel and cuBLAS (through torch.matmul).  Between
+    timed launches a 256 MB buffer is rewritten so that no launch finds its operands in L2."""
+    from dfccl_b200.ops.gemm import matmul_nt
+    m, n, k = mnk
+    a = torch.randn(m, k, device="cuda", dtype=torch.bfloat16)
+    b = torch.randn(n, k, device="cuda", dtype=torch.bfloat16)
+    c = torch.empty(m, n, device="cuda", dtype=torch.bfloat16)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    out = {"M": m, "N": n, "K": k}
+    for name, fn in (("tcgen05", lambda: matmul_nt(a, b, c)), ("cublas", lambda: torch.matmul(a, b.t(), out=c))):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        tot = 0.0
+        for _ in range(iters):
+            flush.fill_(1)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            torch.cuda.synchronize()
+            tot += e0.elapsed_time(e1)
+        us = tot * 1e3 / iters
+        out[name] = {"us": us, "tflops": 2.0 * m * n * k / us / 1e6}
+    ref = a.float() @ b.float().t()
+    matmul_nt(a, b, c)
+    out["max_rel_err"] = float((c.float() - ref).abs().max() / ref.abs().max())
+    print(json.dumps(out))
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser()
     ap.add_argument("--mbytes", type=int, default=256)
     ap.add_argument("--iters", type=int, default=3)
+    ap.add_argument("--gemm", type=int, nargs=3, metavar=("M", "N", "K"), help="time the plain tcgen05 GEMM of this size instead")
     a = ap.parse_args(argv)
     torch.cuda.set_device(0)
     nv.set_backend("cuda")
     L = nv.lib()
+    if a.gemm:
+        return gemm_probe(a.gemm, a.iters)
     (comm,) = nv.Comm.init_loopback(1, 0)
     n = a.mbytes * (1 << 20) // 2                    # bf16 elements
     p, q = comm.alloc(2 * n), comm.alloc(2 * n)

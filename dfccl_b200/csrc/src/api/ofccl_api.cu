@@ -86,7 +86,7 @@ static void observerMain(DaemonLauncher* L) {
     }
     bool work = false, dead = false;
     for (auto* m : members) {
-      if (m->remaining.load() - m->untriggered.load() > 0 && !m->ctl->finalQuit) work = true;
+      if ((m->ctl->hold ? m->remaining.load() : m->remaining.load() - m->untriggered.load()) > 0 && !m->ctl->finalQuit) work = true;
       if (m->ctl->abortFlag) dead = true;
     }
     if (work && !dead) {
@@ -126,6 +126,7 @@ static void deliver(ofcclRankCtx* ctx, uint64_t entry) {
     std::lock_guard<std::mutex> l(ctx->mu);
     ctx->colls[coll].completed++;
     ctx->remaining--;
+    if (ctx->remaining.load() == 0) ctx->ctl->hold = 0;
   }
   ctx->doneCv.notify_all();
 }
@@ -165,7 +166,8 @@ static void pollerMain(ofcclRankCtx* ctx) {
     }
     // nothing new: if the daemon left while work is outstanding, have it launched again
     if (++empty % ctx->checkInterval == 0 || (empty & 63) == 0) {
-      if (!ctx->ctl->alive && ctx->remaining.load() - ctx->untriggered.load() > 0 && !ctx->ctl->abortFlag) wakeLauncher(ctx->launcher.get());
+      const int64_t ready = ctx->ctl->hold ? ctx->remaining.load() : ctx->remaining.load() - ctx->untriggered.load();
+      if (!ctx->ctl->alive && ready > 0 && !ctx->ctl->abortFlag) wakeLauncher(ctx->launcher.get());
     }
     if (empty > 2000) std::this_thread::sleep_for(std::chrono::microseconds(20)); else sched_yield();
   }
@@ -587,6 +589,28 @@ DF_API ncclResult_t dfcclWaitAll(int timeoutMs, ofcclRankCtx_t ctx) {
   return ctx->asyncError;
 }
 
+// Launch an instance of the daemon from the calling thread (cuda backend).  Launches share one stream, so an
+// instance that is still leaving is simply followed by this one; a surplus instance finds nothing and leaves.
+static ncclResult_t launchFromCaller(ofcclRankCtx* ctx) {
+  DaemonLauncher* L = ctx->launcher.get();
+  std::vector<ofcclRankCtx*> everyone;
+  {
+    std::lock_guard<std::mutex> l(L->mu);
+    if (L->stop || ctx->ctl->alive || ctx->ctl->abortFlag || ctx->ctl->finalQuit) return ncclSuccess;
+    everyone = L->members;
+    everyone.insert(everyone.end(), L->retired.begin(), L->retired.end());
+    for (auto* m : everyone) { m->ctl->alive = 1; m->ctl->launches = m->ctl->launches + 1; }
+    ++L->launches;
+  }
+  std::atomic_thread_fence(std::memory_order_seq_cst);
+  int prev = 0;
+  cudaGetDevice(&prev);
+  if (prev != L->device) cudaSetDevice(L->device);
+  ncclResult_t r = launchDaemonCuda(L->devTable, L->expected, L->blocks, L->threads, L->stream);
+  if (prev != L->device) cudaSetDevice(prev);
+  return r;
+}
+
 DF_API ncclResult_t dfcclStreamWait(int collId, cudaStream_t stream, ofcclRankCtx_t ctx) {
   if (!ctx || !ctx->finalized) return ncclInvalidUsage;
   uint64_t want;
@@ -597,6 +621,17 @@ DF_API ncclResult_t dfcclStreamWait(int collId, cudaStream_t stream, ofcclRankCt
     want = it->second.submitted;
   }
   if (ctx->backend == dfcclBackendCuda && ctx->fnWait64) {
+    // The stream is about to park on a word only the daemon sets.  Outside a capture, make sure an instance is
+    // queued BEFORE the wait in host order and that it stays until the work is done: the release of the stream
+    // then never depends on another host thread getting a launch through while this one may be blocked in the
+    // driver (full launch queue, module load).  Captured steps keep the poller-driven wake-up.
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(stream, &cap) != cudaSuccess) { (void)cudaGetLastError(); cap = cudaStreamCaptureStatusNone; }
+    if (cap == cudaStreamCaptureStatusNone && ctx->remaining.load() > 0) {
+      ctx->ctl->hold = 1;
+      std::atomic_thread_fence(std::memory_order_seq_cst);
+      if (!ctx->ctl->alive) DFCHECK(launchFromCaller(ctx));
+    }
     typedef CUresult (*Fn)(CUstream, CUdeviceptr, cuuint64_t, unsigned int);
     // the flag holds (status << 56 | epoch): any finished submission >= want satisfies >=
     CUresult r = ((Fn)ctx->fnWait64)((CUstream)stream, (CUdeviceptr)(uintptr_t)(ctx->rdHost.doneEpoch + collId), want, CU_STREAM_WAIT_VALUE_GEQ);

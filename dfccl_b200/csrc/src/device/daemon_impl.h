@@ -188,8 +188,13 @@ DF_HD void daemonBlockMain(RankDev* rd, int b, BlockShared* sh) {
       // only waiting for streams to release submissions: nothing a resident daemon can speed up, and
       // the host relaunches it when a trigger fires, so leave as quickly as when idle
       else if (!sh->quit && (winding || now - lastUseful > ((sh->nActive && trigWaits < nAct) ? rd->stallQuitNs : rd->idleQuitNs))) {
-        sh->quit = 1;
-        st_release_sys_u32(&rd->quitting, 1u);
+        // a stream parked on one of this context's completion words must not depend on a host thread's
+        // relaunch: while the host holds the instance it only leaves by age (or with the others)
+        if (!winding && rd->ctl->hold) lastUseful = now;
+        else {
+          sh->quit = 1;
+          st_release_sys_u32(&rd->quitting, 1u);
+        }
       }
       sh->ctl0 = progressed ? 1 : 0;
     }

@@ -114,6 +114,11 @@ struct DaemonCtl {
   volatile uint32_t pad;           // stream-ordered kernels store a non-zero CollStatus here on failure
   volatile uint64_t launches;
   volatile uint64_t voluntaryQuits;
+  // host sets while a stream is (or will be) parked on a completion word of this context: the running
+  // instance then stays resident instead of leaving when it is idle or stalled, so that no relaunch
+  // from a host thread is needed at the moment the GPU waits; cleared when nothing is outstanding
+  volatile uint32_t hold;
+  volatile uint32_t pad1;
 };
 
 struct DevStats {                  // per block, device memory
