@@ -22,6 +22,27 @@ from dfccl_b200.parallel import init_distributed
 from dfccl_b200.utils import tensor_from_ptr
 
 
+def inorder_verdict(colls: int, iters: int, world: int, seed: int) -> dict:
+    """What a library that executes each rank's collectives strictly in launch order would do with the very
+    orders this run uses (they are functions of the seed and the rank): per iteration, build the wait-for
+    graph of the in-order model and look for a cycle.  Pure host arithmetic, nothing is launched."""
+    from dfccl_b200.simulator.waitgraph import build_fifo_wait_for_graph, find_cycle
+    rngs = [random.Random(seed * 31 + r) for r in range(world)]
+    dead, first = 0, None
+    for it in range(iters):
+        orders = {}
+        for r in range(world):
+            o = list(range(colls))
+            rngs[r].shuffle(o)
+            orders[r] = o
+        cyc = find_cycle(build_fifo_wait_for_graph(orders))
+        if cyc is not None:
+            dead += 1
+            if first is None:
+                first = {"iteration": it, "cycle_length": len(cyc)}
+    return {"iterations_with_incompatible_orders": dead, "of": iters, "first": first}
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser()
     ap.add_argument("--colls", type=int, default=64)
@@ -113,7 +134,8 @@ def main(argv=None):
                "bytes_min": a.min_bytes, "bytes_max": a.max_bytes, "dtype": "bf16",
                "device_ms_per_iter": e0.elapsed_time(e1) / max(done_iters, 1), "wall_s": wall,
                "collective_bytes_per_iter_per_rank": int(sum(sizes)),
-               "hangs": 0 if min(float(r[0]) for r in allres) == a.iters else 1}
+               "hangs": 0 if min(float(r[0]) for r in allres) == a.iters else 1,
+               "inorder_library_model": inorder_verdict(a.colls, a.iters, world, a.seed)}
         print(json.dumps(out), flush=True)
         if a.out:
             json.dump(out, open(a.out, "w"), indent=1)
