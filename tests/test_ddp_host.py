@@ -81,3 +81,50 @@ def test_parameters_and_gradients_are_views_of_flat_buckets(host_backend):
             assert off % 8 == 0
     ddp.close()
     c.destroy()
+
+
+def test_parameter_groups_reduce_over_their_own_communicators(host_backend):
+    """Two groups of parameters on one daemon: the first is averaged over pairs of ranks (a split
+    communicator), the second summed over all four ranks."""
+    nv = host_backend
+    from dfccl_b200.parallel import DaemonDDP, Dist
+    world = 4
+    comms = nv.Comm.init_loopback(world)
+    out = {}
+    nets = []
+    for r in range(world):
+        torch.manual_seed(1)
+        nets.append(nn.Sequential(nn.Linear(8, 8, bias=False), nn.Linear(8, 4, bias=False)))
+
+    def body(r):
+        pair = comms[r].split(r // 2, r)
+        d = Dist(r, world, 0, torch.device("cpu"), comms[r], False)
+        net = nets[r]
+        groups = [{"params": [net[0].weight], "comm": pair, "scale": 0.5},
+                  {"params": [net[1].weight], "comm": comms[r], "scale": 1.0}]
+        ddp = DaemonDDP(net, d, lr=1.0, momentum=0.0, weight_decay=0.0, param_groups=groups, seed=r)
+        w0, w1 = net[0].weight.detach().clone(), net[1].weight.detach().clone()
+        net[0].weight.grad.fill_(float(r + 1))             # gradients are views of the flat buckets
+        net[1].weight.grad.fill_(float(10 * (r + 1)))
+        ddp.submit_all()
+        ddp.finish_backward()
+        assert ddp.ctx.wait_all(30000) == nv.SUCCESS
+        ddp.step()
+        out[r] = ((w0 - net[0].weight.detach()).mean().item(), (w1 - net[1].weight.detach()).mean().item())
+        ddp.close()
+        pair.destroy()
+
+    run_ranks(world, body)
+    for c in comms:
+        c.destroy()
+    for r in range(world):
+        mate = r ^ 1
+        assert abs(out[r][0] - ((r + 1) + (mate + 1)) / 2) < 1e-5, out      # lr 1, no momentum: the update is the reduced gradient
+        assert abs(out[r][1] - 10 * (1 + 2 + 3 + 4)) < 1e-4, out
+
+
+def test_stress_orders_deadlock_an_inorder_library():
+    from dfccl_b200.benchmarks.stress import inorder_verdict
+    v = inorder_verdict(64, 20, 8, 2024)
+    assert v["iterations_with_incompatible_orders"] == 20 and v["first"]["iteration"] == 0
+    assert inorder_verdict(16, 5, 1, 7)["iterations_with_incompatible_orders"] == 0     # one rank cannot disagree with itself
