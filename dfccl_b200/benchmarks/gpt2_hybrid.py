@@ -62,8 +62,16 @@ class TorchGradSync:
             torch._foreach_mul_(ms, self.mu)
             torch._foreach_add_(ms, gs)
             torch._foreach_add_(ps, ms, alpha=-self.lr)
-            for p in ps:
-                p.grad = None
+            torch._foreach_zero_(gs)                      # kept allocated: a captured backward pass accumulates in place
+
+    def submit_all(self):
+        pass
+
+    def zero_grads(self):
+        for params, _, _ in self.groups:
+            gs = [p.grad for p in params if p.grad is not None]
+            if gs:
+                torch._foreach_zero_(gs)
 
     def stats(self):
         return {}
@@ -98,6 +106,7 @@ def main(argv=None):
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--model", default="medium", choices=["medium", "tiny"])
     ap.add_argument("--impl", default="dfccl", choices=["dfccl", "nccl"])
+    ap.add_argument("--graph", type=int, default=0, help="capture forward + backward of the whole step in one CUDA graph")
     ap.add_argument("--out", default="")
     a = ap.parse_args(argv)
     faulthandler.dump_traceback_later(int(os.environ.get("BENCH_WATCHDOG_S", "600")), exit=True)
@@ -110,7 +119,7 @@ def main(argv=None):
     mesh = build_mesh(d, a.tp, a.pp, a.dp)
     mesh.tp_group.library = "dfccl" if a.impl == "dfccl" else "torch"
     stage = GPT2Stage(cfg, mesh.tp_group, mesh.pp_rank, a.pp, a.micro_batch)
-    tr = HybridTrainer(d, mesh, stage, n_micro=a.n_micro, lr=0.01, seed=5)
+    tr = HybridTrainer(d, mesh, stage, n_micro=a.n_micro, lr=0.01, seed=5, use_graph=bool(a.graph))
     if a.impl == "nccl":
         tr.ddp.close()
         params = [p for p in stage.parameters()]
@@ -200,7 +209,7 @@ def main(argv=None):
                "data": "uniform random token ids; random-init weights",
                "model_tflops_per_gpu": flops / (ms / 1e3) / 1e12 / w,
                "config": {"model": f"GPT-2 {a.model}", "parallelism": f"tp{a.tp} x pp{a.pp} x dp{a.dp}", "micro_batch": a.micro_batch,
-                          "n_micro": a.n_micro, "global_batch": a.dp * a.n_micro * a.micro_batch, "seq_len": cfg.seq_len,
+                          "n_micro": a.n_micro, "global_batch": a.dp * a.n_micro * a.micro_batch, "seq_len": cfg.seq_len, "cuda_graph": bool(a.graph),
                           "schedule": "GPipe", "optimizer": "SGD momentum 0.9, fp32 master weights" if a.impl == "dfccl" else "SGD momentum 0.9 (bf16)"},
                "clocks": clk.summary(),
                "e2e": {"value": tokens / (e2e_ms / 1e3), "unit": "tokens/s", "ms_per_step": e2e_ms,

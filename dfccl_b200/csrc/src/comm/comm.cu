@@ -166,8 +166,16 @@ bool nvlsEligible(const ncclComm* c, int kind, int inType, int outType, int devO
          (count * (size_t)dtypeSize(inType)) % 16 == 0;
 }
 
-static ncclResult_t ensureScratch(ncclComm* c, int which, size_t bytes) {
+static ncclResult_t ensureScratch(ncclComm* c, int which, size_t bytes, cudaStream_t stream) {
   if (c->scratchBytes[which] >= bytes) return ncclSuccess;
+  if (c->backend == dfcclBackendCuda) {      // growing needs a device synchronisation: impossible inside a capture
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(stream, &cap) == cudaSuccess && cap != cudaStreamCaptureStatusNone) {
+      DF_WARN("staging area of %zu bytes needed inside a stream capture: run the same collective once before capturing, or use heap buffers", bytes);
+      return ncclInvalidUsage;
+    }
+    (void)cudaGetLastError();
+  }
   if (c->scratchBytes[which]) {
     // a previous stream-ordered collective may still read it: drain before growing
     if (c->backend == dfcclBackendCuda) CUDACHECK(cudaDeviceSynchronize());
@@ -244,12 +252,13 @@ ncclResult_t commCollective(ncclComm* c, int kind, const void* send, void* recv,
   bool stageSend = !viaArena && needSend && !c->heap->contains(send, sBytes);
   // one-shot in place: peers read my input while I overwrite it, so they get a private copy
   if (needSend && kind == dfcclCollAllReduce && cs.algo == dfcclAlgoOneShot && send == recv && c->nranks > 1) stageSend = true;
-  if (stageSend) { DFCHECK(ensureScratch(c, 0, sBytes)); flags |= SQE_SEND_STAGED; s = (uint64_t)(uintptr_t)send; cs.stagingSendOff = c->scratchOff[0]; }
+  if (stageSend) { DFCHECK(ensureScratch(c, 0, sBytes, stream)); flags |= SQE_SEND_STAGED; s = (uint64_t)(uintptr_t)send; cs.stagingSendOff = c->scratchOff[0]; }
   else if (needSend && !viaArena) s = c->heap->offsetOf(send);
   if (viaArena) {
-  } else if (needRecv && !c->heap->contains(recv, rBytes)) { DFCHECK(ensureScratch(c, 1, rBytes)); flags |= SQE_RECV_STAGED; r = (uint64_t)(uintptr_t)recv; cs.stagingRecvOff = c->scratchOff[1]; }
+  } else if (needRecv && !c->heap->contains(recv, rBytes)) { DFCHECK(ensureScratch(c, 1, rBytes, stream)); flags |= SQE_RECV_STAGED; r = (uint64_t)(uintptr_t)recv; cs.stagingRecvOff = c->scratchOff[1]; }
   else if (needRecv) r = c->heap->offsetOf(recv);
-  const uint32_t epoch = ++c->opCount;
+  ++c->opCount;
+  const uint32_t epoch = 0;            // the kernel reads the communicator's device-side count: works under graph replay too
   if (c->backend == dfcclBackendCuda) {
     int prev = 0;
     cudaGetDevice(&prev);

@@ -224,13 +224,25 @@ DF_HD void standaloneBlockMain(RankDev* rd, int b, BlockShared* sh, const CollSt
     DevStats z = {};
     sh->stats = z;
     CollDyn d = {};
-    d.send = send; d.recv = recv; d.epoch = epoch; d.phase = PH_COPY_IN; d.sqeFlags = sqeFlags; d.status = ST_OK;
+    // epoch 0 = take it from the device: one more than the collectives this communicator has finished
+    d.send = send; d.recv = recv; d.epoch = epoch ? epoch : rd->saEpoch + 1u; d.phase = PH_COPY_IN; d.sqeFlags = sqeFlags; d.status = ST_OK;
     sh->dyn = d;
   }
   df_sync();
   for (;;) {
     bool moved = false;
     if (runColl(sh, rd, b, 0, 4096u, &moved) == RC_DONE) break;
+  }
+  if (epoch == 0) {                       // the last block out publishes the new count (every block has read the old one by now)
+    df_sync();
+    if (tid == 0) {
+      const uint32_t mine = sh->dyn.epoch;
+      if (atomic_add_u32(&rd->exitedBlocks, 1u) + 1u == (uint32_t)sh->cs.nBlocks) {
+        atomic_exch_u32(&rd->exitedBlocks, 0u);
+        rd->saEpoch = mine;
+        fence_sys();
+      }
+    }
   }
 }
 

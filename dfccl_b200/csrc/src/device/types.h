@@ -175,7 +175,8 @@ struct RankDev {
   uint32_t recvSuccessFactor;      // RECV_SUCCESS_FACTOR
   uint32_t exitedBlocks;
   volatile uint32_t quitting;      // a block left voluntarily during this launch
-  uint32_t pad1;
+  uint32_t saEpoch;                // stream-ordered kernels: number of collectives this communicator has finished (their epoch
+                                   // lives on the device so that a captured launch finds the right one at every replay)
   uint64_t idleQuitNs;             // leave after this long with an empty task queue and no new entry
   uint64_t stallQuitNs;            // leave after this long with only stalled collectives
   uint64_t waitTimeoutNs;          // a single wait older than this fails with ST_TIMEOUT (0 = never)

@@ -56,7 +56,9 @@ struct FusedArgs {
   volatile uint64_t* peerArrive[8]; // where I post for peer j (its arrive[rank])
   volatile uint64_t* peerDone[8];
   uint32_t* doneCount;              // local counter of CTAs that finished their communication work
-  uint64_t epoch;
+  uint64_t epoch;                   // this call's number (used when epochCounter is null)
+  uint64_t* epochCounter;           // local device word: calls finished so far; this call is that + 1.  Kept on the device
+                                    // so that a launch captured in a CUDA graph finds the right number at every replay.
   int mode;                         // 0 plain, 1 all-gather -> GEMM, 2 GEMM -> reduce-scatter
 };
 
@@ -155,6 +157,7 @@ dfcclGemmKernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
   uint64_t* accEmpty = accFull + 2;                 // [2]
   uint32_t* tmemBaseSlot = (uint32_t*)(accEmpty + 2);
   volatile uint32_t* giveUp = tmemBaseSlot + 1;
+  uint64_t* epochSlot = (uint64_t*)(tmemBaseSlot + 2);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int mTiles = g.M / BM, nTiles = g.N / BN, kBlocks = g.K / BK;
@@ -165,6 +168,7 @@ dfcclGemmKernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
     for (int s = 0; s < STAGES; ++s) { mbar_init(&fullBar[s], 1); mbar_init(&emptyBar[s], 1); }
     for (int a = 0; a < 2; ++a) { mbar_init(&accFull[a], 1); mbar_init(&accEmpty[a], 4); }
     *giveUp = *(volatile uint32_t*)g.err;          // an earlier launch gave up: its flags and counters are stale, do nothing
+    *epochSlot = g.f.epochCounter ? *(volatile uint64_t*)g.f.epochCounter + 1 : g.f.epoch;
     mbar_fence_init();
     tma_prefetch_desc(&mapA);
     tma_prefetch_desc(&mapB);
@@ -175,9 +179,10 @@ dfcclGemmKernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
   tc_fence_after();
   const uint32_t tmemBase = *tmemBaseSlot;
   const bool dead = *giveUp != 0;
+  const uint64_t epoch = *epochSlot;
   if (!dead && f.mode == 2 && f.nranks > 1) {
     // the owners must have finished reducing the previous call before this one overwrites their slots
-    if (warp == 2 && lane < f.nranks && lane != f.rank) wait_flag64(&f.done[lane], f.epoch - 1, giveUp, g.waitNs);
+    if (warp == 2 && lane < f.nranks && lane != f.rank) wait_flag64(&f.done[lane], epoch - 1, giveUp, g.waitNs);
     __syncthreads();
   }
 
@@ -192,7 +197,7 @@ dfcclGemmKernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
         const int mt = orderedMTile(f, t / nTiles, mTiles), nt = t % nTiles;
         if (f.mode == 1 && f.nranks > 1 && mt / (f.rowsPerRank / BM) != f.rank) {
           // this row block comes from a peer: wait until the communication warps have placed it
-          ok = wait_flag32(&f.blockReady[mt], (uint32_t)f.epoch * GATHER_PIECES, giveUp, false, g.waitNs);
+          ok = wait_flag32(&f.blockReady[mt], (uint32_t)epoch * GATHER_PIECES, giveUp, false, g.waitNs);
           asm volatile("fence.proxy.async.global;" ::: "memory");   // their generic-proxy stores before my async-proxy loads
           if (!ok) break;
         }
@@ -297,7 +302,7 @@ dfcclGemmKernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
         asm volatile("bar.sync 1, 128;" ::: "memory");
         if (warp == 2 && lane == 0) {
           __threadfence_system();
-          st_rel_sys_u32(f.tileFlag[owner] + (size_t)f.rank * (f.rowsPerRank / BM) * nTiles + tileInOwner, (uint32_t)f.epoch);
+          st_rel_sys_u32(f.tileFlag[owner] + (size_t)f.rank * (f.rowsPerRank / BM) * nTiles + tileInOwner, (uint32_t)epoch);
         }
       }
     }
@@ -307,7 +312,7 @@ dfcclGemmKernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
     if (f.mode == 1 && f.nranks > 1) {
       const int blocksPerRank = f.rowsPerRank / BM;
       const size_t blockBytes = (size_t)BM * g.K * 2;
-      if (blockIdx.x == 0 && ct < f.nranks && ct != f.rank) st_rel_sys(f.peerArrive[ct], f.epoch);   // my shard is ready
+      if (blockIdx.x == 0 && ct < f.nranks && ct != f.rank) st_rel_sys(f.peerArrive[ct], epoch);   // my shard is ready
       // remote row blocks in the order the tiles will need them, each cut into PIECES so that every CTA
       // has loads in flight (one CTA alone moves a few GB/s); a block is ready when all its pieces are
       const int remote = (f.nranks - 1) * blocksPerRank * GATHER_PIECES;
@@ -317,7 +322,7 @@ dfcclGemmKernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
         const int bi = i / GATHER_PIECES, piece = i % GATHER_PIECES;
         const int owner = (f.rank + 1 + bi / blocksPerRank) % f.nranks;
         const int blk = bi % blocksPerRank;
-        if (ct == 0) ok = wait_flag64(&f.arrive[owner], f.epoch, giveUp, g.waitNs);
+        if (ct == 0) ok = wait_flag64(&f.arrive[owner], epoch, giveUp, g.waitNs);
         asm volatile("bar.sync 2, 128;" ::: "memory");
         if (*giveUp) break;
         const uint4* src = (const uint4*)((const char*)f.peerA[owner] + (size_t)blk * blockBytes + (size_t)piece * pieceBytes);
@@ -341,17 +346,18 @@ dfcclGemmKernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
         __threadfence();
         if (atomicAdd(f.doneCount, 1u) == gridDim.x - 1) {
           *f.doneCount = 0;
+          if (f.epochCounter) *f.epochCounter = epoch;     // every CTA has read the old value long ago
           __threadfence_system();
-          for (int j = 0; j < f.nranks; ++j) if (j != f.rank) st_rel_sys(f.peerDone[j], f.epoch);
+          for (int j = 0; j < f.nranks; ++j) if (j != f.rank) st_rel_sys(f.peerDone[j], epoch);
         }
       }
-      if (blockIdx.x == 0 && ct < f.nranks && ct != f.rank) wait_flag64(&f.done[ct], f.epoch, giveUp, g.waitNs);   // my shard stays put until read
+      if (blockIdx.x == 0 && ct < f.nranks && ct != f.rank) wait_flag64(&f.done[ct], epoch, giveUp, g.waitNs);   // my shard stays put until read
     } else if (f.mode == 2 && f.nranks > 1) {
       // reduce the tiles I own as their n partial copies arrive: slot[j] written by rank j's epilogue
       const int tilesMine = (f.rowsPerRank / BM) * nTiles;
       for (int i = blockIdx.x; i < tilesMine; i += gridDim.x) {
         const int tm = i / nTiles, tn = i % nTiles;
-        if (ct < f.nranks) wait_flag32(f.myTileFlags + (size_t)ct * tilesMine + i, (uint32_t)f.epoch, giveUp, true, g.waitNs);
+        if (ct < f.nranks) wait_flag32(f.myTileFlags + (size_t)ct * tilesMine + i, (uint32_t)epoch, giveUp, true, g.waitNs);
         asm volatile("bar.sync 2, 128;" ::: "memory");
         if (*giveUp) break;
         // 128 rows x 256 columns = 4096 chunks of 16 bytes; consecutive threads take consecutive chunks of a
@@ -393,8 +399,9 @@ dfcclGemmKernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
         __threadfence();
         if (atomicAdd(f.doneCount, 1u) == gridDim.x - 1) {
           *f.doneCount = 0;
+          if (f.epochCounter) *f.epochCounter = epoch;     // every CTA has read the old value long ago
           __threadfence_system();
-          for (int j = 0; j < f.nranks; ++j) if (j != f.rank) st_rel_sys(f.peerDone[j], f.epoch);
+          for (int j = 0; j < f.nranks; ++j) if (j != f.rank) st_rel_sys(f.peerDone[j], epoch);
         }
       }
     }

@@ -29,7 +29,7 @@ class _FusedArgs(C.Structure):
         ("slot", C.c_void_p * 8), ("tileFlag", C.c_void_p * 8), ("mySlots", C.c_void_p), ("myTileFlags", C.c_void_p),
         ("reduced", C.c_void_p),
         ("arrive", C.c_void_p), ("done", C.c_void_p), ("peerArrive", C.c_void_p * 8), ("peerDone", C.c_void_p * 8),
-        ("doneCount", C.c_void_p), ("epoch", C.c_uint64), ("mode", C.c_int),
+        ("doneCount", C.c_void_p), ("epoch", C.c_uint64), ("epochCounter", C.c_void_p), ("mode", C.c_int),
     ]
 
 
@@ -68,6 +68,8 @@ class _Rendezvous:
         self.peer_arrive = [peers[j] + 8 * tp.rank for j in range(n)]
         self.peer_done = [peers[j] + 8 * n + 8 * tp.rank for j in range(n)]
         self.done_count = torch.zeros(1, dtype=torch.int32, device=tp.device)
+        # calls finished so far, counted by the kernel itself: a launch captured in a CUDA graph stays valid on replay
+        self.epoch_counter = torch.zeros(1, dtype=torch.int64, device=tp.device)
         self.epoch = 0
 
 
@@ -104,6 +106,7 @@ class AllGatherGemm:
                 a.peerDone[j] = self.rv.peer_done[j]
             a.gathered, a.blockReady = self.gathered.data_ptr(), self.block_ready.data_ptr()
             a.arrive, a.done, a.doneCount = self.rv.arrive, self.rv.done, self.rv.done_count.data_ptr()
+            a.epochCounter = self.rv.epoch_counter.data_ptr()
             self._fn, self._sz, self._gp = nv.lib().dfcclGemmFused, C.sizeof(a), self.gathered.data_ptr()
         a.epoch = self.rv.epoch
         w = w.contiguous()
@@ -153,6 +156,7 @@ class GemmReduceScatter:
                 a.peerDone[j] = self.rv.peer_done[j]
             a.mySlots, a.myTileFlags = self._slots, self._flags
             a.arrive, a.done, a.doneCount = self.rv.arrive, self.rv.done, self.rv.done_count.data_ptr()
+            a.epochCounter = self.rv.epoch_counter.data_ptr()
         a.epoch, a.reduced = self.rv.epoch, out.data_ptr()
         nv.check(nv.lib().dfcclGemmFused(x.data_ptr(), w.data_ptr(), self._dummy.data_ptr(), self.m, self.n_out, self.k,
                                          C.byref(a), C.sizeof(a), torch.cuda.current_stream(tp.device).cuda_stream), "dfcclGemmFused(rs)")
