@@ -25,7 +25,7 @@ LIB = LIBDIR / "libdfccl.so"
 SOURCES = [
     "src/common/log.cc", "src/common/param.cc", "src/common/socket.cc",
     "src/bootstrap/bootstrap.cc",
-    "src/mem/heap.cu", "src/mem/mcast.cu", "src/topo/topo.cu",
+    "src/mem/heap.cu", "src/mem/mcast.cu", "src/topo/topo.cu", "src/net/net_socket.cc", "src/net/net_ring.cu",
     "src/device/datapath.cu", "src/daemon/daemon.cu", "src/daemon/standalone.cu", "src/daemon/daemon_host.cu",
     "src/comm/comm.cu",
     "src/api/nccl_api.cu", "src/api/p2p.cu", "src/api/ofccl_api.cu", "src/api/debug_api.cu",

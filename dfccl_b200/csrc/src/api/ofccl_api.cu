@@ -86,7 +86,7 @@ static void observerMain(DaemonLauncher* L) {
     }
     bool work = false, dead = false;
     for (auto* m : members) {
-      if ((m->ctl->hold ? m->remaining.load() : m->remaining.load() - m->untriggered.load()) > 0 && !m->ctl->finalQuit) work = true;
+      if ((m->ctl->hold ? m->remaining.load() : m->remaining.load() - m->untriggered.load()) - m->netPending.load() > 0 && !m->ctl->finalQuit) work = true;
       if (m->ctl->abortFlag) dead = true;
     }
     if (work && !dead) {
@@ -99,7 +99,7 @@ static void observerMain(DaemonLauncher* L) {
         if (r != ncclSuccess) for (auto* m : members) m->asyncError = r;
       } else {
         runDaemonHost(L->devTable, L->expected, L->blocks);     // returns when every block has left
-        for (auto* m : members) if (m->remaining.load() - m->untriggered.load() > 0 && !m->ctl->finalQuit && !m->ctl->abortFlag) { lk.lock(); L->wake = true; lk.unlock(); break; }
+        for (auto* m : members) if (m->remaining.load() - m->untriggered.load() - m->netPending.load() > 0 && !m->ctl->finalQuit && !m->ctl->abortFlag) { lk.lock(); L->wake = true; lk.unlock(); break; }
       }
     }
     lk.lock();
@@ -166,7 +166,7 @@ static void pollerMain(ofcclRankCtx* ctx) {
     }
     // nothing new: if the daemon left while work is outstanding, have it launched again
     if (++empty % ctx->checkInterval == 0 || (empty & 63) == 0) {
-      const int64_t ready = ctx->ctl->hold ? ctx->remaining.load() : ctx->remaining.load() - ctx->untriggered.load();
+      const int64_t ready = (ctx->ctl->hold ? ctx->remaining.load() : ctx->remaining.load() - ctx->untriggered.load()) - ctx->netPending.load();
       if (!ctx->ctl->alive && ready > 0 && !ctx->ctl->abortFlag) wakeLauncher(ctx->launcher.get());
     }
     if (empty > 2000) std::this_thread::sleep_for(std::chrono::microseconds(20)); else sched_yield();
@@ -254,6 +254,7 @@ DF_API ncclResult_t ofcclFinalizeRankCtx7StartHostThrds(ofcclRankCtx_t ctx) {
   // 1. schedule + flag words of every collective
   for (auto& kv : ctx->colls) {
     CollEntry& e = kv.second;
+    if (e.comm->netMode) continue;               // runs on the host over its own ring (created in step 2)
     const size_t bytes = e.info.count * (size_t)dtypeSize(e.info.inType);
     bool nv = nvlsEligible(e.comm, e.cs.kind, e.cs.inType, e.cs.outType, e.cs.op, e.cs.postDiv, e.cs.count);
     TunerChoice ch = tunerChoose(*topo, e.info.kind, bytes, e.comm->nranks, ctx->nBlocks, nv, e.info.algo, e.info.nBlocks);
@@ -291,6 +292,17 @@ DF_API ncclResult_t ofcclFinalizeRankCtx7StartHostThrds(ofcclRankCtx_t ctx) {
     cnt[comm->rank] = (int32_t)ids.size();
     DFCHECK(comm->boot->allGather(cnt.data(), sizeof(int32_t)));
     for (int j = 0; j < n; ++j) if (cnt[j] != (int32_t)ids.size()) { DF_WARN("rank %d registered %d collectives on this communicator, rank %d registered %zu", j, cnt[j], comm->rank, ids.size()); return ncclInvalidUsage; }
+    if (comm->netMode) {
+      // one ring of connections per collective (ascending id on every member): collectives submitted in
+      // different orders on different ranks then never meet in one FIFO
+      for (int id : ids) {
+        std::unique_ptr<NetRing> ring;
+        DFCHECK(NetRing::create(comm->boot.get(), &ring));
+        ctx->colls[id].ring = std::shared_ptr<NetRing>(ring.release());
+        ctx->colls[id].cs.valid = 0;             // the daemon never sees it
+      }
+      continue;
+    }
     std::vector<FinalizeMsg> all((size_t)n * ids.size());
     for (size_t i = 0; i < ids.size(); ++i) {
       CollEntry& e = ctx->colls[ids[i]];
@@ -466,6 +478,27 @@ static ncclResult_t submit(ofcclRankCtx* ctx, const void* send, void* recv, int 
     const bool needSend = !(cs.kind == dfcclCollBroadcast && cs.rank != cs.root);
     const bool needRecv = !(cs.kind == dfcclCollReduce && cs.rank != cs.root);
     if ((needSend && !send) || (needRecv && !recv)) { DF_WARN("null buffer for collective %d", collId); return ncclInvalidArgument; }
+    if (e.comm->netMode) {
+      if (onStream) { DF_WARN("collective %d: stream-ordered submission is not available on communicators that go through the network path", collId); return ncclInvalidUsage; }
+      e.cb = cb; e.cbArgs = cbArgs;
+      e.submitted++;
+      ctx->remaining++;
+      ctx->netPending++;
+      ctx->sqes++;
+      NetCollDesc d{cs.kind, cs.inType, cs.outType, cs.op, cs.root, cs.postDiv, cs.scale, (size_t)cs.count};
+      ncclComm* comm = e.comm;
+      std::shared_ptr<NetRing> ring = e.ring;
+      std::lock_guard<std::mutex> nl(ctx->netMu);
+      ctx->netThreads.emplace_back([ctx, comm, ring, d, send, recv, collId] {
+        logSetRank(ctx->rank);
+        ncclResult_t r = netStagedCollective(comm, ring.get(), d, send, recv, nullptr);
+        const uint32_t st = r == ncclSuccess ? ST_OK : r == dfcclAborted ? ST_ABORTED : r == dfcclTimeout ? ST_TIMEOUT : ST_BAD_ARG;
+        ctx->netPending--;
+        deliver(ctx, ((uint64_t)st << 24) | (uint64_t)(uint32_t)collId);
+      });
+      ctx->pollCv.notify_one();
+      return ncclSuccess;
+    }
     Heap* heap = e.comm->heap;
     const size_t sB = sendBytes(&cs), rB = recvBytes(&cs);
     q.collId = collId;
@@ -746,7 +779,8 @@ static void releaseHeapParts(ofcclRankCtx* ctx) {
   }
   for (auto& kv : ctx->colls) {
     CollEntry& e = kv.second;
-    e.comm->heap->free(e.flagsOff);
+    e.ring.reset();
+    if (e.flagsBytes) e.comm->heap->free(e.flagsOff);
     for (int k = 0; k < 2; ++k) if (e.stagingBytes[k]) e.comm->heap->free(e.stagingOff[k]);
     e.comm = nullptr;
   }
@@ -785,6 +819,11 @@ DF_API ncclResult_t ofcclDestroy(ofcclRankCtx_t ctx) {
   if (ctx->wakeStream) cudaStreamSynchronize(ctx->wakeStream);     // no wake-up callback may outlive the context
   ctx->stopPoller = true;
   ctx->pollCv.notify_all();
+  {
+    std::vector<std::thread> ts;
+    { std::lock_guard<std::mutex> nl(ctx->netMu); ts.swap(ctx->netThreads); }
+    for (auto& t : ts) if (t.joinable()) t.join();
+  }
   if (ctx->poller.joinable()) ctx->poller.join();
   std::shared_ptr<DaemonLauncher> L = ctx->launcher;
   ctx->launcher.reset();

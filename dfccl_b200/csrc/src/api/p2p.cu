@@ -89,6 +89,7 @@ ncclResult_t p2pEnqueue(ncclComm* comm, bool isSend, void* buf, size_t count, nc
   if ((int)type < 0 || (int)type >= ncclNumTypes) return ncclInvalidArgument;
   if (count && !buf) return ncclInvalidArgument;
   if (peer == comm->rank) { DF_WARN("send / recv to self is not supported"); return ncclInvalidUsage; }
+  if (comm->netMode) { DF_WARN("send / recv is not available on communicators that go through the network path"); return ncclInvalidUsage; }
   t_pending.push_back({comm, isSend, buf, count * (size_t)dtypeSize(type), peer, stream});
   return ncclSuccess;
 }

@@ -35,6 +35,7 @@ struct CollEntry {
   uint64_t submitted = 0, completed = 0;     // guarded by ctx->mu
   uint64_t triggerSeq = 0;
   uint32_t lastStatus = 0;
+  std::shared_ptr<NetRing> ring;             // network-mode communicators: this collective's own ring of connections
 };
 
 struct DaemonLauncher {
@@ -79,6 +80,9 @@ struct ofcclRankCtx {
   std::shared_ptr<dfccl::DaemonLauncher> launcher;
   int launcherSlot = 0;
   std::thread poller;
+  std::vector<std::thread> netThreads;        // one per submission on a network-mode communicator (joined at destroy)
+  std::mutex netMu;
+  std::atomic<int64_t> netPending{0};         // submissions running on the host network path (not the daemon's business)
   std::mutex mu;                      // submissions, callbacks table, counters
   std::condition_variable pollCv;     // poller sleeps here while nothing is outstanding
   std::condition_variable doneCv;     // dfcclWait

@@ -117,12 +117,20 @@ ncclResult_t commCreate(std::shared_ptr<Bootstrap> boot, dfcclBackend_t backend,
   c->commHash = all[0].commHash;
   c->handles.resize(n); c->peerHeap.resize(n); c->peerSaFlagsOff.resize(n); c->peerP2pFlagsOff.resize(n);
   c->sendSeq.assign(n, 0); c->recvSeq.assign(n, 0);
+  // members on another host cannot be mapped: the whole communicator then goes through the network path
+  c->netMode = n > 1 && paramI64("FORCE_NET", 0) != 0;
+  for (int j = 0; j < n; ++j) if (all[j].heap.hostHash != all[r].heap.hostHash) c->netMode = true;
   for (int j = 0; j < n; ++j) {
     c->handles[j] = all[j].heap;
     c->peerSaFlagsOff[j] = all[j].saFlagsOff;
     c->peerP2pFlagsOff[j] = all[j].p2pFlagsOff;
     if (j == r) c->peerHeap[j] = c->heap->base();
+    else if (c->netMode) c->peerHeap[j] = nullptr;
     else DFCHECK(c->heap->importPeer(all[j].heap, &c->peerHeap[j]));
+  }
+  if (c->netMode) {
+    DFCHECK(NetRing::create(boot.get(), &c->netRing));
+    DF_INFO(SUB_INIT | SUB_NET, "communicator of %d ranks spans hosts (or DFCCL_FORCE_NET): collectives are staged through host memory over '%s'", n, netGet()->name);
   }
   // minimal RankDev for stream-ordered kernels: control words and timeouts only
   RankDev& rd = c->saRdHost;
@@ -138,7 +146,7 @@ ncclResult_t commCreate(std::shared_ptr<Bootstrap> boot, dfcclBackend_t backend,
   DFCHECK(devUpload(backend, c->saRd, &rd, sizeof(RankDev)));
   DFCHECK(boot->barrier());          // every member has mapped everything before anyone uses it
   // switch multicast is opt-in: binding memory to a multicast object ties the members' fates together
-  if (n > 1 && (!loop || backend != dfcclBackendCuda) && paramI64("NVLS", 0)) DFCHECK(nvlsArenaCreate(c.get(), (size_t)paramI64("NVLS_BYTES", 512ll << 20), &c->nvls));
+  if (n > 1 && !c->netMode && (!loop || backend != dfcclBackendCuda) && paramI64("NVLS", 0)) DFCHECK(nvlsArenaCreate(c.get(), (size_t)paramI64("NVLS_BYTES", 512ll << 20), &c->nvls));
   if (backend == dfcclBackendCuda) cudaSetDevice(prevDev);
   DF_INFO(SUB_INIT, "comm %llx rank %d/%d device %d backend %s heap %zu MiB", (unsigned long long)c->commHash, r, n, device,
           backend == dfcclBackendCuda ? "cuda" : "host", c->heap->bytes() >> 20);
@@ -188,6 +196,31 @@ static ncclResult_t ensureScratch(ncclComm* c, int which, size_t bytes, cudaStre
   return ncclSuccess;
 }
 
+ncclResult_t netStagedCollective(ncclComm* c, NetRing* ring, const NetCollDesc& d, const void* send, void* recv, cudaStream_t stream) {
+  CollStatic cs;
+  memset(&cs, 0, sizeof(cs));
+  cs.kind = d.kind; cs.inType = d.inType; cs.outType = d.outType; cs.nranks = c->nranks; cs.count = d.count;
+  const size_t sB = sendBytes(&cs), rB = recvBytes(&cs);
+  const bool needSend = !(d.kind == dfcclCollBroadcast && c->rank != d.root);
+  const bool needRecv = !(d.kind == dfcclCollReduce && c->rank != d.root);
+  std::vector<char> hs(needSend ? sB : 0), hr(needRecv ? rB : 0);
+  const bool cuda = c->backend == dfcclBackendCuda;
+  int prev = 0;
+  if (cuda) {
+    cudaGetDevice(&prev);
+    if (prev != c->device) cudaSetDevice(c->device);
+    CUDACHECK(cudaStreamSynchronize(stream));
+    if (needSend) CUDACHECK(cudaMemcpy(hs.data(), send, sB, cudaMemcpyDeviceToHost));
+  } else if (needSend) memcpy(hs.data(), send, sB);
+  ncclResult_t res = netCollective(ring, d, needSend ? hs.data() : nullptr, needRecv ? hr.data() : nullptr, &c->ctl->abortFlag);
+  if (res == ncclSuccess && needRecv) {
+    if (cuda) { cudaError_t e = cudaMemcpy(recv, hr.data(), rB, cudaMemcpyHostToDevice); if (e != cudaSuccess) res = ncclUnhandledCudaError; }
+    else memcpy(recv, hr.data(), rB);
+  }
+  if (cuda && prev != c->device) cudaSetDevice(prev);
+  return res;
+}
+
 ncclResult_t commCollective(ncclComm* c, int kind, const void* send, void* recv, size_t count, ncclDataType_t type,
                             ncclRedOp_t op, int root, cudaStream_t stream) {
   if (!c) { DF_WARN("null communicator"); return ncclInvalidArgument; }
@@ -200,6 +233,13 @@ ncclResult_t commCollective(ncclComm* c, int kind, const void* send, void* recv,
   const bool needSend = !(kind == dfcclCollBroadcast && c->rank != root);
   const bool needRecv = !(kind == dfcclCollReduce && c->rank != root);
   if ((needSend && !send) || (needRecv && !recv)) { DF_WARN("null buffer"); return ncclInvalidArgument; }
+  if (c->netMode) {
+    NetCollDesc d{kind, (int)type, (int)type, OP_SUM, root, 0, 1.0, count};
+    if (kind == dfcclCollAllReduce || kind == dfcclCollReduce || kind == dfcclCollReduceScatter)
+      DFCHECK(resolveRedOp(c, op, type, c->nranks, &d.op, &d.scale, &d.postDiv));
+    std::lock_guard<std::mutex> nl(c->mu);
+    return netStagedCollective(c, c->netRing.get(), d, send, recv, stream);
+  }
   std::unique_lock<std::mutex> l(c->mu);
   CollStatic cs;
   memset(&cs, 0, sizeof(cs));

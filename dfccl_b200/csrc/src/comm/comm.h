@@ -16,6 +16,7 @@
 #include "../device/types.h"
 #include "../mem/heap.h"
 #include "../mem/mcast.h"
+#include "../net/net.h"
 
 namespace dfccl {
 struct DaemonLauncher;
@@ -62,6 +63,10 @@ struct ncclComm {
   std::shared_ptr<dfccl::LoopGroup> loop;      // set for loopback / InitAll groups
   bool aborted = false;
   dfccl::NvlsArena* nvls = nullptr;            // switch-multicast arena (opt-in), null when absent
+  // network mode: members that cannot map each other's memory (other hosts, or DFCCL_FORCE_NET=1);
+  // collectives are staged through host memory and run over rings of network connections
+  bool netMode = false;
+  std::unique_ptr<dfccl::NetRing> netRing;     // ring of the stream-ordered entry points
 };
 
 namespace dfccl {
@@ -81,6 +86,10 @@ ncclResult_t processHeap(dfcclBackend_t backend, int device, Heap** out);
 
 // Can this all-reduce run on the NVLS schedule of this communicator?  (arena present, sum, supported types, 16-byte multiple)
 bool nvlsEligible(const ncclComm* comm, int kind, int inType, int outType, int devOp, int postDiv, size_t count);
+
+// Network mode: copy the operands to the host, run the ring algorithm over `ring`, copy the result back.
+// `stream` (cuda backend) is drained first; the call returns when the result is in `recv`.
+ncclResult_t netStagedCollective(ncclComm* comm, NetRing* ring, const NetCollDesc& d, const void* send, void* recv, cudaStream_t stream);
 
 // The engine behind the stream-ordered entry points.
 ncclResult_t commCollective(ncclComm* comm, int kind, const void* send, void* recv, size_t count, ncclDataType_t type,
