@@ -100,8 +100,18 @@ def main(argv=None):
         ctx.set_daemon_geometry(a.blocks, 0)
     bufs = {}
     max_bytes = max(sizes)
-    send_p = d.comm.alloc(max_bytes * (world if "reducescatter" in a.kinds else 1) + 256)
-    recv_p = d.comm.alloc(max_bytes * (world if "allgather" in a.kinds else 1) + 256)
+    nvls = False
+    if a.algo == "nvls" and world > 1:
+        # operands live in the switch-multicast arena, so the schedule works on them in place
+        os.environ.setdefault("DFCCL_NVLS_MIN_BYTES", "4096")
+        nvls = d.comm.nvls_init(2 * max_bytes + (96 << 20))
+        if rank == 0:
+            print(json.dumps({"nvls_available": bool(nvls)}), flush=True)
+    if nvls:
+        send_p, recv_p = d.comm.nvls_alloc(max_bytes + 256), d.comm.nvls_alloc(max_bytes + 256)
+    else:
+        send_p = d.comm.alloc(max_bytes * (world if "reducescatter" in a.kinds else 1) + 256)
+        recv_p = d.comm.alloc(max_bytes * (world if "allgather" in a.kinds else 1) + 256)
     for cid, (k, dt, sz) in enumerate(cases):
         tdt, ndt = DT[dt]
         es = torch.empty((), dtype=tdt).element_size()
