@@ -56,9 +56,9 @@ def _newest_header() -> float:
     return max((p.stat().st_mtime for p in CSRC.rglob("*.h")), default=0.0)
 
 
-def _compile(src: str, verbose: bool, hdr_time: float) -> Path:
+def _compile(src: str, verbose: bool, hdr_time: float, sanitize: str = "") -> Path:
     s = CSRC / src
-    o = OBJ / (src.replace("/", "_") + (".fast.o" if os.environ.get("DFCCL_FAST_BUILD") == "1" else ".o"))
+    o = OBJ / (src.replace("/", "_") + (f".{sanitize}.o" if sanitize else ".fast.o" if os.environ.get("DFCCL_FAST_BUILD") == "1" else ".o"))
     if o.exists() and o.stat().st_mtime > max(s.stat().st_mtime, hdr_time):
         return o
     extra = []
@@ -66,6 +66,8 @@ def _compile(src: str, verbose: bool, hdr_time: float) -> Path:
         # out-of-line device functions do not inherit a kernel's launch bounds: cap them at what
         # a 512-thread block leaves per thread (the reference caps its device code the same way)
         extra = ["-maxrregcount=128"]
+    if sanitize:                                     # host code only: the device code is the same as in the plain build
+        extra += ["-Xcompiler", f"-fsanitize={sanitize},-fno-omit-frame-pointer,-g", "-DDF_FAST_BUILD"]
     cmd = [nvcc()] + _flags(verbose) + extra + ["-c", str(s), "-o", str(o)]
     r = subprocess.run(cmd, capture_output=True, text=True)
     if r.returncode != 0:
@@ -75,8 +77,12 @@ def _compile(src: str, verbose: bool, hdr_time: float) -> Path:
     return o
 
 
-def build(verbose: bool = False, force: bool = False, extra_sources=()) -> Path:
-    """Compile what is stale and link ``libdfccl.so``; returns its path."""
+def build(verbose: bool = False, force: bool = False, extra_sources=(), sanitize: str = "") -> Path:
+    """Compile what is stale and link ``libdfccl.so``; returns its path.
+
+    ``sanitize="thread"`` or ``"address"`` builds ``libdfccl_<sanitize>.so`` instead, with the host code (the
+    runtime, and the scheduler / engine / data path as compiled for the host backend) instrumented by the
+    compiler's sanitizer: the race and memory checks of the library run on the CPU twin of the device code."""
     OBJ.mkdir(parents=True, exist_ok=True)
     LIBDIR.mkdir(parents=True, exist_ok=True)
     if force:
@@ -85,14 +91,16 @@ def build(verbose: bool = False, force: bool = False, extra_sources=()) -> Path:
     hdr = _newest_header()
     srcs = [s for s in list(SOURCES) + list(extra_sources) if (CSRC / s).exists()]
     with ThreadPoolExecutor(max_workers=min(8, os.cpu_count() or 4)) as ex:
-        objs = list(ex.map(lambda s: _compile(s, verbose, hdr), srcs))
-    if LIB.exists() and all(LIB.stat().st_mtime > o.stat().st_mtime for o in objs):
-        return LIB
-    cmd = [nvcc(), "-shared", "-rdc=true", "-Xcompiler", "-fPIC", "-o", str(LIB)] + [str(o) for o in objs] + ARCH + ["-lrt", "-lpthread", "-ldl", "-cudart", "static", "-Xlinker", "-Bsymbolic"]
+        objs = list(ex.map(lambda s: _compile(s, verbose, hdr, sanitize), srcs))
+    lib = LIBDIR / f"libdfccl_{sanitize}.so" if sanitize else LIB
+    if lib.exists() and all(lib.stat().st_mtime > o.stat().st_mtime for o in objs):
+        return lib
+    san = ["-Xcompiler", f"-fsanitize={sanitize}"] if sanitize else []
+    cmd = [nvcc(), "-shared", "-rdc=true", "-Xcompiler", "-fPIC", "-o", str(lib)] + san + [str(o) for o in objs] + ARCH + ["-lrt", "-lpthread", "-ldl", "-cudart", "static", "-Xlinker", "-Bsymbolic"]
     r = subprocess.run(cmd, capture_output=True, text=True)
     if r.returncode != 0:
         raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")
-    return LIB
+    return lib
 
 
 if __name__ == "__main__":

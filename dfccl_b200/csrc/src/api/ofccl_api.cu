@@ -86,11 +86,11 @@ static void observerMain(DaemonLauncher* L) {
     }
     bool work = false, dead = false;
     for (auto* m : members) {
-      if ((m->ctl->hold ? m->remaining.load() : m->remaining.load() - m->untriggered.load()) - m->netPending.load() > 0 && !m->ctl->finalQuit) work = true;
-      if (m->ctl->abortFlag) dead = true;
+      if ((ctl_load(&m->ctl->hold) ? m->remaining.load() : m->remaining.load() - m->untriggered.load()) - m->netPending.load() > 0 && !ctl_load(&m->ctl->finalQuit)) work = true;
+      if (ctl_load(&m->ctl->abortFlag)) dead = true;
     }
     if (work && !dead) {
-      for (auto* m : everyone) { m->ctl->alive = 1; m->ctl->launches = m->ctl->launches + 1; }
+      for (auto* m : everyone) { ctl_store(&m->ctl->alive, 1); m->ctl->launches = m->ctl->launches + 1; }
       std::atomic_thread_fence(std::memory_order_seq_cst);
       ++L->launches;
       DF_TRACE(SUB_DAEMON, "daemon launch #%llu (%zu ranks x %d blocks x %d threads)", (unsigned long long)L->launches, members.size(), L->blocks, L->threads);
@@ -99,7 +99,7 @@ static void observerMain(DaemonLauncher* L) {
         if (r != ncclSuccess) for (auto* m : members) m->asyncError = r;
       } else {
         runDaemonHost(L->devTable, L->expected, L->blocks);     // returns when every block has left
-        for (auto* m : members) if (m->remaining.load() - m->untriggered.load() - m->netPending.load() > 0 && !m->ctl->finalQuit && !m->ctl->abortFlag) { lk.lock(); L->wake = true; lk.unlock(); break; }
+        for (auto* m : members) if (m->remaining.load() - m->untriggered.load() - m->netPending.load() > 0 && !ctl_load(&m->ctl->finalQuit) && !ctl_load(&m->ctl->abortFlag)) { lk.lock(); L->wake = true; lk.unlock(); break; }
       }
     }
     lk.lock();
@@ -126,7 +126,7 @@ static void deliver(ofcclRankCtx* ctx, uint64_t entry) {
     std::lock_guard<std::mutex> l(ctx->mu);
     ctx->colls[coll].completed++;
     ctx->remaining--;
-    if (ctx->remaining.load() == 0) ctx->ctl->hold = 0;
+    if (ctx->remaining.load() == 0) ctl_store(&ctx->ctl->hold, 0);
   }
   ctx->doneCv.notify_all();
 }
@@ -153,7 +153,7 @@ static void pollerMain(ofcclRankCtx* ctx) {
       }
       if (fired) {
         ctx->untriggered -= fired;
-        if (!ctx->ctl->alive && !ctx->ctl->abortFlag) wakeLauncher(ctx->launcher.get());
+        if (!ctl_load(&ctx->ctl->alive) && !ctl_load(&ctx->ctl->abortFlag)) wakeLauncher(ctx->launcher.get());
       }
     }
     const uint64_t slot = ctx->cqHead & (ctx->cqCap - 1);
@@ -166,8 +166,8 @@ static void pollerMain(ofcclRankCtx* ctx) {
     }
     // nothing new: if the daemon left while work is outstanding, have it launched again
     if (++empty % ctx->checkInterval == 0 || (empty & 63) == 0) {
-      const int64_t ready = (ctx->ctl->hold ? ctx->remaining.load() : ctx->remaining.load() - ctx->untriggered.load()) - ctx->netPending.load();
-      if (!ctx->ctl->alive && ready > 0 && !ctx->ctl->abortFlag) wakeLauncher(ctx->launcher.get());
+      const int64_t ready = (ctl_load(&ctx->ctl->hold) ? ctx->remaining.load() : ctx->remaining.load() - ctx->untriggered.load()) - ctx->netPending.load();
+      if (!ctl_load(&ctx->ctl->alive) && ready > 0 && !ctl_load(&ctx->ctl->abortFlag)) wakeLauncher(ctx->launcher.get());
     }
     if (empty > 2000) std::this_thread::sleep_for(std::chrono::microseconds(20)); else sched_yield();
   }
@@ -426,10 +426,10 @@ DF_API ncclResult_t ofcclFinalizeRankCtx7StartHostThrds(ofcclRankCtx_t ctx) {
         DFCHECK(warmRuntimeKernels());
         cudaFuncAttributes fa;
         CUDACHECK(cudaFuncGetAttributes(&fa, dfcclWriteWordKernel));
-        for (auto* m : L->members) m->ctl->alive = 1;
+        for (auto* m : L->members) ctl_store(&m->ctl->alive, 1);
         DFCHECK(launchDaemonCuda(L->devTable, L->expected, L->blocks, L->threads, L->stream));
         CUDACHECK(cudaStreamSynchronize(L->stream));
-        for (auto* m : L->members) m->ctl->alive = 0;
+        for (auto* m : L->members) ctl_store(&m->ctl->alive, 0);
       }
       L->started = true;
       L->observer = std::thread(observerMain, L.get());
@@ -452,7 +452,7 @@ DF_API ncclResult_t ofcclPrepareDone(ofcclRankCtx_t ctx) {
 static ncclResult_t submit(ofcclRankCtx* ctx, const void* send, void* recv, int collId, CallbackFunc cb, void* cbArgs,
                            bool onStream, cudaStream_t stream) {
   if (!ctx || !ctx->finalized || ctx->destroyed) { DF_WARN("context is not ready for submissions"); return ncclInvalidUsage; }
-  if (ctx->ctl->abortFlag) return dfcclAborted;
+  if (ctl_load(&ctx->ctl->abortFlag)) return dfcclAborted;
   if (ctx->faultDelayUs > 0) std::this_thread::sleep_for(std::chrono::microseconds(ctx->faultDelayUs));
   Sqe q;
   memset(&q, 0, sizeof(q));
@@ -469,9 +469,9 @@ static ncclResult_t submit(ofcclRankCtx* ctx, const void* send, void* recv, int 
       if (!onStream) { DF_WARN("collective %d submitted again before its callback ran", collId); return ncclInvalidUsage; }
       // Stream-ordered callers enqueue ahead of the GPU: the previous submission of this id is
       // already ordered before this one on the device, so the host only has to wait for it.
-      const bool ok = ctx->doneCv.wait_for(l, std::chrono::seconds(120), [&] { return e.submitted == e.completed || ctx->ctl->abortFlag; });
+      const bool ok = ctx->doneCv.wait_for(l, std::chrono::seconds(120), [&] { return e.submitted == e.completed || ctl_load(&ctx->ctl->abortFlag); });
       if (!ok) { DF_WARN("collective %d: previous submission did not complete within 120 s", collId); return dfcclTimeout; }
-      if (ctx->ctl->abortFlag) return dfcclAborted;
+      if (ctl_load(&ctx->ctl->abortFlag)) return dfcclAborted;
     }
     tp2 = nowNs();
     const CollStatic& cs = e.cs;
@@ -527,7 +527,7 @@ static ncclResult_t submit(ofcclRankCtx* ctx, const void* send, void* recv, int 
     while (tail - __atomic_load_n((const uint64_t*)ctx->hostSqHead, __ATOMIC_ACQUIRE) >= ctx->sqCap) {
       ctx->sqFull++;
       l.unlock();
-      if (!ctx->ctl->alive) wakeLauncher(ctx->launcher.get());
+      if (!ctl_load(&ctx->ctl->alive)) wakeLauncher(ctx->launcher.get());
       sched_yield();
       l.lock();
       tail = *ctx->hostSqTail;
@@ -550,7 +550,7 @@ static ncclResult_t submit(ofcclRankCtx* ctx, const void* send, void* recv, int 
     std::lock_guard<std::mutex> l(ctx->mu);
     ctx->pendingTrig.emplace_back(collId, trig);
     ctx->untriggered++;
-  } else if (!ctx->ctl->alive) wakeLauncher(ctx->launcher.get());
+  } else if (!ctl_load(&ctx->ctl->alive)) wakeLauncher(ctx->launcher.get());
   if (onStream) {
     volatile uint64_t* word = ctx->rdHost.trigger + collId;
     if (ctx->backend == dfcclBackendCuda) {
@@ -605,20 +605,20 @@ DF_API ncclResult_t dfcclWait(int collId, int timeoutMs, ofcclRankCtx_t ctx) {
   auto it = ctx->colls.find(collId);
   if (it == ctx->colls.end()) return ncclInvalidArgument;
   CollEntry& e = it->second;
-  auto pred = [&] { return e.completed == e.submitted || ctx->ctl->abortFlag; };
+  auto pred = [&] { return e.completed == e.submitted || ctl_load(&ctx->ctl->abortFlag); };
   if (timeoutMs < 0) ctx->doneCv.wait(l, pred);
   else if (!ctx->doneCv.wait_for(l, std::chrono::milliseconds(timeoutMs), pred)) return dfcclTimeout;
-  if (ctx->ctl->abortFlag && e.completed != e.submitted) return dfcclAborted;
+  if (ctl_load(&ctx->ctl->abortFlag) && e.completed != e.submitted) return dfcclAborted;
   return e.lastStatus == ST_OK ? ncclSuccess : e.lastStatus == ST_TIMEOUT ? dfcclTimeout : e.lastStatus == ST_ABORTED ? dfcclAborted : ncclInternalError;
 }
 
 DF_API ncclResult_t dfcclWaitAll(int timeoutMs, ofcclRankCtx_t ctx) {
   if (!ctx || !ctx->finalized) return ncclInvalidUsage;
   std::unique_lock<std::mutex> l(ctx->mu);
-  auto pred = [&] { return ctx->remaining.load() == 0 || ctx->ctl->abortFlag; };
+  auto pred = [&] { return ctx->remaining.load() == 0 || ctl_load(&ctx->ctl->abortFlag); };
   if (timeoutMs < 0) ctx->doneCv.wait(l, pred);
   else if (!ctx->doneCv.wait_for(l, std::chrono::milliseconds(timeoutMs), pred)) return dfcclTimeout;
-  if (ctx->ctl->abortFlag && ctx->remaining.load()) return dfcclAborted;
+  if (ctl_load(&ctx->ctl->abortFlag) && ctx->remaining.load()) return dfcclAborted;
   return ctx->asyncError;
 }
 
@@ -629,10 +629,10 @@ static ncclResult_t launchFromCaller(ofcclRankCtx* ctx) {
   std::vector<ofcclRankCtx*> everyone;
   {
     std::lock_guard<std::mutex> l(L->mu);
-    if (L->stop || ctx->ctl->alive || ctx->ctl->abortFlag || ctx->ctl->finalQuit) return ncclSuccess;
+    if (L->stop || ctl_load(&ctx->ctl->alive) || ctl_load(&ctx->ctl->abortFlag) || ctl_load(&ctx->ctl->finalQuit)) return ncclSuccess;
     everyone = L->members;
     everyone.insert(everyone.end(), L->retired.begin(), L->retired.end());
-    for (auto* m : everyone) { m->ctl->alive = 1; m->ctl->launches = m->ctl->launches + 1; }
+    for (auto* m : everyone) { ctl_store(&m->ctl->alive, 1); m->ctl->launches = m->ctl->launches + 1; }
     ++L->launches;
   }
   std::atomic_thread_fence(std::memory_order_seq_cst);
@@ -661,9 +661,9 @@ DF_API ncclResult_t dfcclStreamWait(int collId, cudaStream_t stream, ofcclRankCt
     cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
     if (cudaStreamIsCapturing(stream, &cap) != cudaSuccess) { (void)cudaGetLastError(); cap = cudaStreamCaptureStatusNone; }
     if (cap == cudaStreamCaptureStatusNone && ctx->remaining.load() > 0) {
-      ctx->ctl->hold = 1;
+      ctl_store(&ctx->ctl->hold, 1);
       std::atomic_thread_fence(std::memory_order_seq_cst);
-      if (!ctx->ctl->alive) DFCHECK(launchFromCaller(ctx));
+      if (!ctl_load(&ctx->ctl->alive)) DFCHECK(launchFromCaller(ctx));
     }
     typedef CUresult (*Fn)(CUstream, CUdeviceptr, cuuint64_t, unsigned int);
     // the flag holds (status << 56 | epoch): any finished submission >= want satisfies >=
@@ -685,7 +685,7 @@ DF_API ncclResult_t dfcclSubmitProfile(uint64_t out[5]) {
 
 DF_API ncclResult_t dfcclAbort(ofcclRankCtx_t ctx) {
   if (!ctx) return ncclInvalidArgument;
-  if (ctx->ctl) ctx->ctl->abortFlag = 1;
+  if (ctx->ctl) ctl_store(&ctx->ctl->abortFlag, 1);
   ctx->doneCv.notify_all();
   return ncclSuccess;
 }
@@ -702,7 +702,7 @@ DF_API ncclResult_t dfcclGetHostStats(ofcclRankCtx_t ctx, dfcclStats* s) {
   s->sqesSubmitted = ctx->sqes; s->cqesDelivered = ctx->cqes; s->callbacksRun = ctx->cbs; s->sqFullRetries = ctx->sqFull;
   if (!ctx->finalized) return ncclSuccess;
   s->daemonLaunches = ctx->ctl->launches; s->daemonVoluntaryQuits = ctx->ctl->voluntaryQuits;
-  s->deviceEvents = ctx->ctl->alive;               // 1 while an instance of the daemon is (believed to be) running
+  s->deviceEvents = ctl_load(&ctx->ctl->alive);               // 1 while an instance of the daemon is (believed to be) running
   return ncclSuccess;
 }
 
@@ -829,7 +829,7 @@ DF_API ncclResult_t ofcclDestroy(ofcclRankCtx_t ctx) {
   ctx->launcher.reset();
   std::shared_ptr<LoopGroup> loop = ctx->colls.begin()->second.comm->loop;
   // my blocks must have seen the quit entry (or be parked) before the flag words are reused
-  for (int i = 0; i < 50000 && ctx->ctl->alive && !ctx->ctl->finalQuit; ++i) std::this_thread::sleep_for(std::chrono::microseconds(100));
+  for (int i = 0; i < 50000 && ctl_load(&ctx->ctl->alive) && !ctl_load(&ctx->ctl->finalQuit); ++i) std::this_thread::sleep_for(std::chrono::microseconds(100));
   releaseHeapParts(ctx);
   bool last = false;
   {

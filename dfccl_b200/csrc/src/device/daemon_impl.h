@@ -127,7 +127,7 @@ DF_HD void blockPark(BlockShared* sh, RankDev* rd, int b) {
     if (prev + 1 == rd->nBlocks) {                     // last block of this rank out: tell the host
       atomic_exch_u32(&rd->exitedBlocks, 0u);
       st_release_sys_u32(&rd->quitting, 0u);
-      if (sh->quit == 2) rd->ctl->finalQuit = 1;
+      if (sh->quit == 2) ctl_store(&rd->ctl->finalQuit, 1);
       if (sh->quit == 1) rd->ctl->voluntaryQuits = rd->ctl->voluntaryQuits + 1;
       fence_sys();
       st_release_sys_u32(&rd->ctl->alive, 0u);
@@ -177,7 +177,7 @@ DF_HD void daemonBlockMain(RankDev* rd, int b, BlockShared* sh) {
         if (consumeSubmissions(sh, rd, b) > 0) progressed = true;
       }
       const uint64_t now = df_now_ns();
-      sh->abortSeen = rd->ctl->abortFlag;
+      sh->abortSeen = ctl_load(&rd->ctl->abortFlag);
       if (sh->abortSeen) sh->quit = 3;
       else if (rd->maxLifetimeNs && now - bornNs > rd->maxLifetimeNs && !sh->quit) {
         // safety net: no instance of the daemon outlives this, whatever its state; the host relaunches it
@@ -190,7 +190,7 @@ DF_HD void daemonBlockMain(RankDev* rd, int b, BlockShared* sh) {
       else if (!sh->quit && (winding || now - lastUseful > ((sh->nActive && trigWaits < nAct) ? rd->stallQuitNs : rd->idleQuitNs))) {
         // a stream parked on one of this context's completion words must not depend on a host thread's
         // relaunch: while the host holds the instance it only leaves by age (or with the others)
-        if (!winding && rd->ctl->hold) lastUseful = now;
+        if (!winding && ctl_load(&rd->ctl->hold)) lastUseful = now;
         else {
           sh->quit = 1;
           st_release_sys_u32(&rd->quitting, 1u);

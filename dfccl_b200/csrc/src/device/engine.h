@@ -160,7 +160,7 @@ DF_HD bool boundedWait(BlockShared* sh, RankDev* rd, int b, int which, uint32_t 
         }
       }
       bool laneStop = false;
-      if ((spins & 255) == 255 && lane == 0) laneStop = rd->ctl->abortFlag != 0;
+      if ((spins & 255) == 255 && lane == 0) laneStop = ctl_load(&rd->ctl->abortFlag) != 0;
       ok = df_warp_all(laneOk);
       const bool stop = !df_warp_all(!laneStop);      // uniform: every lane leaves the loop together
       ++spins;
@@ -180,7 +180,7 @@ DF_HD bool noteStall(BlockShared* sh, RankDev* rd) {
   if (df_tid() == 0) {
     uint64_t now = df_now_ns();
     sh->ctl0 = 0;
-    if (sh->standalone ? (rd->ctl->abortFlag != 0) : (sh->abortSeen != 0)) { sh->dyn.status = ST_ABORTED; sh->ctl0 = 1; }
+    if (sh->standalone ? (ctl_load(&rd->ctl->abortFlag) != 0) : (sh->abortSeen != 0)) { sh->dyn.status = ST_ABORTED; sh->ctl0 = 1; }
     else if (sh->dyn.stallSinceNs == 0) { sh->dyn.stallSinceNs = now; sh->dynDirty = 1; }
     else if (rd->waitTimeoutNs && now - sh->dyn.stallSinceNs > rd->waitTimeoutNs) {
       sh->dyn.status = ST_TIMEOUT; sh->ctl0 = 1; sh->stats.waitTimeouts++;

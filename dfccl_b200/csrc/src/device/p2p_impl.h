@@ -39,7 +39,7 @@ DF_HD bool p2pWait(P2pShared* sh, RankDev* rd, const volatile uint64_t* word, ui
     int ok = 1;
     while (ld_acquire_sys_u64(word) < want) {
       if ((++spins & 255) == 0) {
-        if (rd->ctl->abortFlag) { ok = 0; rd->ctl->pad = ST_ABORTED; break; }
+        if (ctl_load(&rd->ctl->abortFlag)) { ok = 0; rd->ctl->pad = ST_ABORTED; break; }
         if (rd->waitTimeoutNs && df_now_ns() - t0 > rd->waitTimeoutNs) { ok = 0; rd->ctl->pad = ST_TIMEOUT; break; }
       }
     }

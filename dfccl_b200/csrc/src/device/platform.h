@@ -72,6 +72,33 @@ DF_HD void df_warp_sync() {
 #endif
 }
 
+// ThreadSanitizer understands acquire / release pairs but not stand-alone fences.  The engine orders payload
+// accesses with "relaxed flag access + one fence"; in a sanitizer build of the host twin the relaxed flag
+// accesses are promoted to acquire / release, which is stronger, so that the tool sees the same ordering.
+#if defined(__SANITIZE_THREAD__)
+#define DF_HOST_RELAXED_LD __ATOMIC_ACQUIRE
+#define DF_HOST_RELAXED_ST __ATOMIC_RELEASE
+#else
+#define DF_HOST_RELAXED_LD __ATOMIC_RELAXED
+#define DF_HOST_RELAXED_ST __ATOMIC_RELAXED
+#endif
+
+// Control words shared between host threads and the (host twin of the) device code.
+DF_HD uint32_t ctl_load(const volatile uint32_t* p) {
+#if DF_DEVICE_CODE
+  return *p;
+#else
+  return __atomic_load_n((const uint32_t*)p, __ATOMIC_ACQUIRE);
+#endif
+}
+DF_HD void ctl_store(volatile uint32_t* p, uint32_t v) {
+#if DF_DEVICE_CODE
+  *p = v;
+#else
+  __atomic_store_n((uint32_t*)p, v, __ATOMIC_RELEASE);
+#endif
+}
+
 DF_HD uint64_t ld_acquire_sys_u64(const volatile uint64_t* p) {
 #if DF_DEVICE_CODE
   uint64_t v;
@@ -87,7 +114,7 @@ DF_HD uint64_t ld_relaxed_sys_u64(const volatile uint64_t* p) {
   asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
   return v;
 #else
-  return __atomic_load_n((const uint64_t*)p, __ATOMIC_RELAXED);
+  return __atomic_load_n((const uint64_t*)p, DF_HOST_RELAXED_LD);
 #endif
 }
 DF_HD uint32_t ld_acquire_sys_u32(const volatile uint32_t* p) {
@@ -110,7 +137,7 @@ DF_HD void st_relaxed_sys_u64(volatile uint64_t* p, uint64_t v) {
 #if DF_DEVICE_CODE
   asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
 #else
-  __atomic_store_n((uint64_t*)p, v, __ATOMIC_RELAXED);
+  __atomic_store_n((uint64_t*)p, v, DF_HOST_RELAXED_ST);
 #endif
 }
 DF_HD void st_release_sys_u32(volatile uint32_t* p, uint32_t v) {

@@ -64,7 +64,9 @@ def lib() -> C.CDLL:
         if _lib is not None:
             return _lib
         path = _build.LIB
-        if not path.exists() or os.environ.get("DFCCL_REBUILD") == "1":
+        if os.environ.get("DFCCL_LIBRARY"):             # e.g. a sanitizer build (see _build.build(sanitize=...))
+            path = type(path)(os.environ["DFCCL_LIBRARY"])
+        elif not path.exists() or os.environ.get("DFCCL_REBUILD") == "1":
             path = _build.build()
         L = C.CDLL(str(path))       # local scope: the nccl* names must not shadow another collective library's
         vp, i, sz = C.c_void_p, C.c_int, C.c_size_t
