@@ -1,4 +1,5 @@
 #include "rankctx.h"
+#include "../common/nvtx.h"
 #include "../common/log.h"
 #include "../common/param.h"
 #include "../device/datapath.h"
@@ -237,6 +238,7 @@ struct FinalizeMsg { int32_t collId, nBlocks, algo, kind, inType, outType, pad0,
 
 DF_API ncclResult_t ofcclFinalizeRankCtx7StartHostThrds(ofcclRankCtx_t ctx) {
   if (!ctx) return ncclInvalidArgument;
+  NvtxRange range("dfccl:finalize");
   if (ctx->finalized) { DF_WARN("context finalized twice"); return ncclInvalidUsage; }
   if (ctx->colls.empty()) { DF_WARN("no collective registered"); return ncclInvalidUsage; }
   ncclComm* first = ctx->colls.begin()->second.comm;
@@ -452,6 +454,7 @@ DF_API ncclResult_t ofcclPrepareDone(ofcclRankCtx_t ctx) {
 static ncclResult_t submit(ofcclRankCtx* ctx, const void* send, void* recv, int collId, CallbackFunc cb, void* cbArgs,
                            bool onStream, cudaStream_t stream) {
   if (!ctx || !ctx->finalized || ctx->destroyed) { DF_WARN("context is not ready for submissions"); return ncclInvalidUsage; }
+  NvtxRange range(onStream ? "dfccl:submit(stream)" : "dfccl:submit");
   if (ctl_load(&ctx->ctl->abortFlag)) return dfcclAborted;
   if (ctx->faultDelayUs > 0) std::this_thread::sleep_for(std::chrono::microseconds(ctx->faultDelayUs));
   Sqe q;

@@ -1,4 +1,5 @@
 #include "comm.h"
+#include "../common/nvtx.h"
 #include "../common/log.h"
 #include "../common/param.h"
 #include "../device/engine.h"
@@ -224,6 +225,8 @@ ncclResult_t netStagedCollective(ncclComm* c, NetRing* ring, const NetCollDesc& 
 ncclResult_t commCollective(ncclComm* c, int kind, const void* send, void* recv, size_t count, ncclDataType_t type,
                             ncclRedOp_t op, int root, cudaStream_t stream) {
   if (!c) { DF_WARN("null communicator"); return ncclInvalidArgument; }
+  static const char* const kindName[] = {"dfccl:AllReduce", "dfccl:AllGather", "dfccl:ReduceScatter", "dfccl:Broadcast", "dfccl:Reduce"};
+  NvtxRange range(kind >= 0 && kind < 5 ? kindName[kind] : "dfccl:collective");
   if (c->aborted) return ncclInvalidUsage;
   // a stream-ordered kernel that gave up left its verdict in pinned memory: fail at the next call instead of queueing more waits
   if (c->ctl->pad) { c->asyncError = c->ctl->pad == ST_TIMEOUT ? dfcclTimeout : dfcclAborted; DF_WARN("an earlier stream-ordered collective of this communicator failed (%s)", c->ctl->pad == ST_TIMEOUT ? "timed out" : "aborted"); return c->asyncError; }
