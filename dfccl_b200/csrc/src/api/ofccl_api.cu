@@ -663,7 +663,10 @@ DF_API ncclResult_t dfcclStreamWait(int collId, cudaStream_t stream, ofcclRankCt
     // driver (full launch queue, module load).  Captured steps keep the poller-driven wake-up.
     cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
     if (cudaStreamIsCapturing(stream, &cap) != cudaSuccess) { (void)cudaGetLastError(); cap = cudaStreamCaptureStatusNone; }
-    if (cap == cudaStreamCaptureStatusNone && ctx->remaining.load() > 0) {
+    // (only where this context has the daemon launch to itself: ranks that share one launch - several ranks
+    // of one process on one device - must keep leaving when stalled, or one rank's held blocks would keep the
+    // shared kernel alive in front of the relaunch another rank is waiting for)
+    if (cap == cudaStreamCaptureStatusNone && ctx->remaining.load() > 0 && ctx->launcher && ctx->launcher->expected == 1) {
       ctl_store(&ctx->ctl->hold, 1);
       std::atomic_thread_fence(std::memory_order_seq_cst);
       if (!ctl_load(&ctx->ctl->alive)) DFCHECK(launchFromCaller(ctx));
