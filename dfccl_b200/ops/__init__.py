@@ -1,1 +1,2 @@
 from .gemm import matmul_nt, gemm_supported
+from . import collectives

@@ -468,3 +468,31 @@ def test_staged_buffers_with_several_blocks(host_backend):
     with _env(DFCCL_DAEMON_BLOCKS=3, DFCCL_MIN_BYTES_PER_BLOCK=1024):
         for kind in T.KINDS:
             T._run_case(nv, kind, 4, 30011, nv.FLOAT32, heap=False, root=1, iters=2)
+
+
+def test_functional_collectives_on_torch_tensors(host_backend):
+    """The torch-tensor layer over the stream-ordered entry points (host backend: CPU tensors)."""
+    import torch
+    from helpers import run_ranks
+    from dfccl_b200.ops import collectives as coll
+    nv = host_backend
+    world = 3
+    comms = nv.Comm.init_loopback(world)
+    res = {}
+
+    def body(r):
+        c = comms[r]
+        x = torch.full((6, 4), float(r + 1))
+        out = {"ar": coll.all_reduce(c, x.clone()), "avg": coll.all_reduce(c, x.clone(), op="avg"),
+               "ag": coll.all_gather(c, x[:2].contiguous()), "rs": coll.reduce_scatter(c, x.clone()),
+               "bc": coll.broadcast(c, x.clone(), root=2), "rd": coll.reduce(c, x.clone(), root=1, op="max")}
+        res[r] = out
+
+    run_ranks(world, body)
+    for c in comms:
+        c.destroy()
+    for r in range(world):
+        assert torch.all(res[r]["ar"] == 6) and torch.all(res[r]["avg"] == 2) and torch.all(res[r]["bc"] == 3)
+        assert res[r]["ag"].shape == (6, 4) and torch.equal(res[r]["ag"][:, 0], torch.tensor([1., 1, 2, 2, 3, 3]))
+        assert res[r]["rs"].shape == (2, 4) and torch.all(res[r]["rs"] == 6)
+    assert torch.all(res[1]["rd"] == 3) and res[0]["rd"] is None
