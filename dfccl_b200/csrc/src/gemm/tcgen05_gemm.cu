@@ -19,6 +19,8 @@
 #include "../common/param.h"
 #include "dfccl.h"
 #include "../common/log.h"
+#include <algorithm>
+#include <atomic>
 #include <map>
 #include <mutex>
 #include <tuple>
@@ -465,6 +467,8 @@ ncclResult_t makeMapUncached(CUtensorMap* m, const void* base, uint64_t rows, ui
   return ncclSuccess;
 }
 
+std::atomic<int> g_reservedSms{0};
+
 struct ErrWords { uint32_t* dev = nullptr; volatile uint32_t* host = nullptr; };
 ErrWords errWords() {                       // one pair per device, created on first use
   static ErrWords w[64];
@@ -505,8 +509,11 @@ ncclResult_t launch(const void* A, const void* B, void* C, int M, int N, int K, 
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   const int tiles = (M / BM) * (N / BN);
-  // fused modes keep one CTA per SM even with few tiles: the communication warps of idle CTAs still work
-  const int grid = (g.f.mode == 0) ? (tiles < sms ? tiles : sms) : sms;
+  // The CTAs of a fused launch serve one another (gathered pieces, partial tiles), so all of them must be resident
+  // at once: SMs that a co-running persistent kernel (the daemon) may occupy are left out of the grid.
+  const int usable = std::max(1, sms - g_reservedSms.load());
+  // fused modes keep one CTA per usable SM even with few tiles: the communication warps of idle CTAs still work
+  const int grid = (g.f.mode == 0) ? (tiles < sms ? tiles : sms) : usable;
   dfcclGemmKernel<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(ma, mb, g);
   CUDACHECK(cudaGetLastError());
   return ncclSuccess;
@@ -521,6 +528,13 @@ using namespace dfccl;
 // C[M,N] (bf16, row-major) = A[M,K] * B[N,K]^T, fp32 accumulation in tensor memory.
 DF_API ncclResult_t dfcclGemmBf16(const void* A, const void* B, void* C, int M, int N, int K, cudaStream_t stream) {
   return launch(A, B, C, M, N, K, nullptr, stream);
+}
+
+// SMs the fused launches leave free for a persistent kernel that runs beside them (e.g. the daemon's blocks).
+DF_API ncclResult_t dfcclGemmReserveSms(int n) {
+  if (n < 0 || n > 128) return ncclInvalidArgument;
+  g_reservedSms.store(n);
+  return ncclSuccess;
 }
 
 // Non-zero after a kernel of this file gave up on a bounded wait (reads and clears the word).

@@ -107,7 +107,7 @@ def lib() -> C.CDLL:
             "dfcclRunOnStream": [vp, vp, i, vp, CALLBACK, vp, vp],
             "dfcclStreamWait": [i, vp, vp], "dfcclWait": [i, i, vp], "dfcclWaitAll": [i, vp],
             "dfcclAbort": [vp], "dfcclGetAsyncError": [vp, C.POINTER(i)],
-            "dfcclGetStats": [vp, C.POINTER(Stats)], "dfcclGetHostStats": [vp, C.POINTER(Stats)], "dfcclTraceDump": [vp, C.c_char_p],
+            "dfcclGemmReserveSms": [i], "dfcclGetStats": [vp, C.POINTER(Stats)], "dfcclGetHostStats": [vp, C.POINTER(Stats)], "dfcclTraceDump": [vp, C.c_char_p],
             "dfcclInjectFault": [vp, i, C.c_int64],
             "dfcclFusedSgdStep": [vp, vp, vp, vp, sz, i, C.c_float, C.c_float, C.c_float, i, vp],
             "dfcclOpsWarm": [],

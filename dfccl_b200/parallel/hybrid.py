@@ -81,6 +81,10 @@ class HybridTrainer:
         self.ddp = DaemonDDP(stage, d, bucket_mb=bucket_mb, lr=lr, momentum=momentum, weight_decay=weight_decay,
                              randomize_order=True, seed=seed, param_groups=groups, daemon_blocks=daemon_blocks)
         self.ddp.hooks_enabled = False
+        if d.device.type == "cuda":
+            # the fused GEMM launches need all their CTAs resident together: keep them off the SMs a daemon
+            # instance may still hold when the next forward pass starts
+            nv.check(nv.lib().dfcclGemmReserveSms(daemon_blocks), "dfcclGemmReserveSms")
         self.prev = d.rank - mesh.tp if mesh.pp_rank > 0 else None
         self.next = d.rank + mesh.tp if mesh.pp_rank < mesh.pp - 1 else None
         self._loss = torch.zeros(1, dtype=torch.float32, device=d.device)
@@ -232,6 +236,10 @@ class HybridTrainer:
         self.ddp = DaemonDDP(stage, d, bucket_mb=bucket_mb, lr=lr, momentum=momentum, weight_decay=weight_decay,
                              randomize_order=True, seed=seed, param_groups=groups, daemon_blocks=daemon_blocks)
         self.ddp.hooks_enabled = False
+        if d.device.type == "cuda":
+            # the fused GEMM launches need all their CTAs resident together: keep them off the SMs a daemon
+            # instance may still hold when the next forward pass starts
+            nv.check(nv.lib().dfcclGemmReserveSms(daemon_blocks), "dfcclGemmReserveSms")
         self.prev = d.rank - mesh.tp if mesh.pp_rank > 0 else None
         self.next = d.rank + mesh.tp if mesh.pp_rank < mesh.pp - 1 else None
         self._loss = torch.zeros(1, dtype=torch.float32, device=d.device)
