@@ -2,9 +2,11 @@
 
 Forward passes run the fused kernels: the column-parallel layer is an all-gather -> GEMM, the
 row-parallel layer a GEMM -> reduce-scatter, both one tcgen05 kernel each with the collective
-inside (``dfccl_b200.ops.fused_linear``).  Backward passes use the library's stream-ordered
-collectives (``ncclAllGather`` / ``ncclReduceScatter`` of this library, not of NCCL) around plain
-GEMMs; the weight-gradient and data-gradient GEMMs need transposed operands and stay on cuBLAS.
+inside (``dfccl_b200.ops.fused_linear``).  The data-gradient GEMMs of the backward passes are the same
+two kernels with the roles swapped (the column-parallel layer's is a GEMM -> reduce-scatter, the
+row-parallel layer's an all-gather -> GEMM, each on the transposed weight); the weight-gradient
+GEMMs contract over the token dimension and stay on cuBLAS.  On the host backend (tests) the layers
+fall back to this library's stream-ordered collectives around plain GEMMs.
 
 The reference has no tensor-parallel code; its simulator only generates the group structure of
 such jobs (reference: simulator/simulator.py:434-493).
@@ -74,26 +76,38 @@ def tp_reduce_scatter(tp: TpGroup, x: torch.Tensor) -> torch.Tensor:
 
 
 class _ColumnFn(torch.autograd.Function):
+    """y = all_gather(x_shard) W^T.  Backward: gW = gy^T x_full, gx_shard = reduce_scatter(gy W)."""
+
     @staticmethod
     def forward(ctx, x_shard, weight, layer):
         ctx.layer = layer
-        ctx.save_for_backward(x_shard, weight)
-        if layer.op is None:                                # host backend (tests): library collective + plain GEMM
+        if layer.op is None:                                # host backend (tests) / comparison arm: collective + plain GEMM
+            ctx.save_for_backward(x_shard, weight)
             return tp_all_gather(layer.tp, x_shard) @ weight.t()
-        return layer.op(x_shard, weight)
+        y = layer.op(x_shard, weight)
+        # the gathered activations are needed again for the weight gradient: keep a copy (the operator's buffer
+        # is shared by every layer of this shape) instead of gathering a second time in the backward pass
+        ctx.save_for_backward(layer.op.gathered.clone(), weight)
+        return y
 
     @staticmethod
     def backward(ctx, gy):
-        x_shard, weight = ctx.saved_tensors
-        tp = ctx.layer.tp
+        saved, weight = ctx.saved_tensors
+        layer = ctx.layer
+        tp = layer.tp
         gy = gy.contiguous()
-        x_full = tp_all_gather(tp, x_shard)                 # re-gathered: the forward buffer belongs to later micro-batches
-        gw = gy.t() @ x_full
-        gx = tp_reduce_scatter(tp, gy @ weight)
+        if layer.op is None:
+            x_full = tp_all_gather(tp, saved)
+            return tp_reduce_scatter(tp, gy @ weight), gy.t() @ x_full, None
+        gw = gy.t() @ saved
+        # data gradient with the reduce-scatter inside the GEMM: gx = RS(gy [M, N/n] @ W [N/n, K]), B operand = W^T
+        gx = layer.bwd_op(gy, weight.t().contiguous())
         return gx, gw, None
 
 
 class _RowFn(torch.autograd.Function):
+    """y_shard = reduce_scatter(x W^T).  Backward: gy = all_gather(gy_shard), gx = gy W, gW = gy^T x."""
+
     @staticmethod
     def forward(ctx, x, weight, layer):
         ctx.layer = layer
@@ -105,8 +119,16 @@ class _RowFn(torch.autograd.Function):
     @staticmethod
     def backward(ctx, gy_shard):
         x, weight = ctx.saved_tensors
-        gy = tp_all_gather(ctx.layer.tp, gy_shard.contiguous())
-        return gy @ weight, gy.t() @ x, None
+        layer = ctx.layer
+        gy_shard = gy_shard.contiguous()
+        if layer.op is None:
+            gy = tp_all_gather(layer.tp, gy_shard)
+            return gy @ weight, gy.t() @ x, None
+        # data gradient with the all-gather inside the GEMM: gx = AG(gy_shard) [M, N] @ W [N, K/n], B operand = W^T;
+        # the operator's gathered buffer then holds the full output gradient for the weight gradient
+        gx = layer.bwd_op(gy_shard, weight.t().contiguous())
+        gw = layer.bwd_op.gathered.t() @ x
+        return gx, gw, None
 
 
 class ColumnParallelLinear(nn.Module):
@@ -125,6 +147,7 @@ class ColumnParallelLinear(nn.Module):
         self.weight = nn.Parameter(w.reshape(nl, in_features).to(torch.bfloat16).contiguous())
         self.bias = nn.Parameter(torch.zeros(nl, dtype=torch.bfloat16, device=tp.device))
         self.op = shared_op(AllGatherGemm, tp, rows_per_rank, in_features, nl) if _fused(tp) else None
+        self.bwd_op = shared_op(GemmReduceScatter, tp, rows_per_rank * tp.n, nl, in_features) if _fused(tp) else None
 
     def forward(self, x_shard):
         return _ColumnFn.apply(x_shard, self.weight, self) + self.bias
@@ -144,6 +167,7 @@ class RowParallelLinear(nn.Module):
         self.bias = nn.Parameter(torch.zeros(out_features, dtype=torch.bfloat16, device=tp.device))
         self.bias.tp_replicated = True
         self.op = shared_op(GemmReduceScatter, tp, m, kl, out_features) if _fused(tp) else None
+        self.bwd_op = shared_op(AllGatherGemm, tp, m // tp.n, out_features, kl) if _fused(tp) else None
 
     def forward(self, x):
         return _RowFn.apply(x, self.weight, self) + self.bias
