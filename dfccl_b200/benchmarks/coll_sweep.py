@@ -147,11 +147,24 @@ def main(argv=None):
             ctx.run_on_stream(i, send_p, recv_p, stream.cuda_stream)
             ctx.stream_wait(i, stream.cuda_stream)
 
+        def daemon_window():
+            # the way a trainer uses the daemon: several registered collectives released back to back, waited for
+            # together - the daemon works on all of them at once instead of one round trip at a time
+            base = cid * a.ids
+            for j in range(a.ids):
+                ctx.run_on_stream(base + j, send_p, recv_p, stream.cuda_stream)
+            for j in range(a.ids):
+                ctx.stream_wait(base + j, stream.cuda_stream)
+
         row = {"kind": k, "dtype": dt, "bytes": sz, "n": world}
         us = time_loop(daemon_op, iters, a.warmup, world)
         assert ctx.wait_all(60000) == nv.SUCCESS
         row["daemon_us"] = us
         row["daemon_host_enqueue_us"] = time_loop.host_us
+        if a.ids > 1 and sz <= (16 << 20):
+            usw = time_loop(daemon_window, max(3, iters // a.ids), max(2, a.warmup // 2), world)
+            assert ctx.wait_all(60000) == nv.SUCCESS
+            row["daemon_window_us_per_op"] = usw / a.ids
         row["daemon_busbw_gbs"] = sz / us / 1e3 * bus_factor(k, world)
         # correctness spot check against torch on the same data
         if k == "allreduce" and world > 1:

@@ -141,6 +141,7 @@ DF_HD void daemonBlockMain(RankDev* rd, int b, BlockShared* sh) {
   if (tid == 0) trace(rd, b, TR_LAUNCH, 0);
   uint64_t lastUseful = df_now_ns();     // only thread 0's copy is ever consulted
   const uint64_t bornNs = lastUseful;
+  uint64_t lastAbortCheck = 0;
   uint32_t idleBackoff = 32;
 
   for (;;) {
@@ -177,7 +178,9 @@ DF_HD void daemonBlockMain(RankDev* rd, int b, BlockShared* sh) {
         if (consumeSubmissions(sh, rd, b) > 0) progressed = true;
       }
       const uint64_t now = df_now_ns();
-      sh->abortSeen = ctl_load(&rd->ctl->abortFlag);
+      // the abort word lives in host memory: one read over PCIe costs more than a whole pass over a short
+      // task queue, so it is sampled every 20 us instead of every pass
+      if (now - lastAbortCheck > 20000) { sh->abortSeen = ctl_load(&rd->ctl->abortFlag); lastAbortCheck = now; }
       if (sh->abortSeen) sh->quit = 3;
       else if (rd->maxLifetimeNs && now - bornNs > rd->maxLifetimeNs && !sh->quit) {
         // safety net: no instance of the daemon outlives this, whatever its state; the host relaunches it
