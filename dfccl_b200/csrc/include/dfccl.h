@@ -167,7 +167,8 @@ typedef enum {
   dfcclAlgoAuto = 0,
   dfcclAlgoOneShot = 1,  /* every rank reads all inputs, reduces locally */
   dfcclAlgoTwoShot = 2,  /* owner reduces its shard from all peers and writes it to all peers */
-  dfcclAlgoNvls = 3      /* switch-side reduce / broadcast through a multicast mapping */
+  dfcclAlgoNvls = 3,     /* switch-side reduce / broadcast through a multicast mapping */
+  dfcclAlgoPush = 4      /* small all-reduce in one hop: every rank writes its input into slots at every peer, then reduces locally */
 } dfcclAlgo_t;
 
 /* Select the backend for communicators created afterwards by this thread's process
@@ -235,6 +236,12 @@ ncclResult_t dfcclRun(const void* sendbuff, void* recvbuff, int collId, Callback
 ncclResult_t dfcclRunOnStream(const void* sendbuff, void* recvbuff, int collId, cudaStream_t stream,
                               CallbackFunc callback, void* callbackArgs, ofcclRankCtx_t rankCtx);
 ncclResult_t dfcclStreamWait(int collId, cudaStream_t stream, ofcclRankCtx_t rankCtx);
+/* By default dfcclStreamWait (outside a stream capture) launches an instance of the daemon before the wait and
+ * keeps it resident until nothing is outstanding, so that a stream parked on a completion never depends on a
+ * relaunch from a host thread - the safe choice for eager steps of thousands of launches, at the price of the
+ * daemon's SMs from the moment the host enqueues the wait.  A step that is enqueued with a handful of calls
+ * (a replayed CUDA graph) can switch it off and leave the wake-up to the poller. */
+ncclResult_t dfcclSetHoldOnWait(ofcclRankCtx_t rankCtx, int on);
 
 /* Host-side wait for the last submission of collId (status of that execution is returned). */
 ncclResult_t dfcclWait(int collId, int timeoutMs, ofcclRankCtx_t rankCtx);

@@ -234,7 +234,7 @@ DF_API ncclResult_t dfcclPrepare(const dfcclCollInfo* info, ncclComm_t comm, int
   return ncclSuccess;
 }
 
-struct FinalizeMsg { int32_t collId, nBlocks, algo, kind, inType, outType, pad0, pad1; uint64_t count, flagsOff; };
+struct FinalizeMsg { int32_t collId, nBlocks, algo, kind, inType, outType, pad0, pad1; uint64_t count, flagsOff, pushOff; };
 
 DF_API ncclResult_t ofcclFinalizeRankCtx7StartHostThrds(ofcclRankCtx_t ctx) {
   if (!ctx) return ncclInvalidArgument;
@@ -275,6 +275,14 @@ DF_API ncclResult_t ofcclFinalizeRankCtx7StartHostThrds(ofcclRankCtx_t ctx) {
       }
     }
     e.cs.algo = ch.algo; e.cs.nBlocks = ch.nBlocks;
+    if (ch.algo != dfcclAlgoNvls && pushEligible(e.comm, e.cs.kind, bytes, e.info.algo)) {
+      // small all-reduce: one hop through slots at the peers ([2 parities][n writers][bytes]); a pure function of
+      // what every member registered, so all members decide alike
+      e.cs.algo = dfcclAlgoPush;
+      e.cs.pushSlotBytes = (bytes + 511) & ~(size_t)511;
+      e.pushBytes = 2 * (size_t)e.comm->nranks * e.cs.pushSlotBytes;
+      DFCHECK(e.comm->heap->alloc(e.pushBytes, &e.pushOff, false));
+    }
     e.flagsBytes = sizeof(FlagSlot) * (size_t)ch.nBlocks * e.comm->nranks;
     DFCHECK(e.comm->heap->alloc(e.flagsBytes, &e.flagsOff, true));
   }
@@ -308,7 +316,7 @@ DF_API ncclResult_t ofcclFinalizeRankCtx7StartHostThrds(ofcclRankCtx_t ctx) {
     std::vector<FinalizeMsg> all((size_t)n * ids.size());
     for (size_t i = 0; i < ids.size(); ++i) {
       CollEntry& e = ctx->colls[ids[i]];
-      all[(size_t)comm->rank * ids.size() + i] = {ids[i], e.cs.nBlocks, e.cs.algo, e.cs.kind, e.cs.inType, e.cs.outType, 0, 0, e.cs.count, e.flagsOff};
+      all[(size_t)comm->rank * ids.size() + i] = {ids[i], e.cs.nBlocks, e.cs.algo, e.cs.kind, e.cs.inType, e.cs.outType, 0, 0, e.cs.count, e.flagsOff, e.pushOff};
     }
     DFCHECK(comm->boot->allGather(all.data(), sizeof(FinalizeMsg) * ids.size()));
     for (size_t i = 0; i < ids.size(); ++i) {
@@ -322,6 +330,7 @@ DF_API ncclResult_t ofcclFinalizeRankCtx7StartHostThrds(ofcclRankCtx_t ctx) {
         }
         e.cs.peerHeap[j] = comm->peerHeap[j];
         e.cs.peerFlags[j] = (FlagSlot*)(comm->peerHeap[j] + m.flagsOff);
+        e.cs.peerPush[j] = e.pushBytes ? comm->peerHeap[j] + m.pushOff : nullptr;
       }
       e.cs.valid = 1;
     }
@@ -505,8 +514,11 @@ static ncclResult_t submit(ofcclRankCtx* ctx, const void* send, void* recv, int 
     Heap* heap = e.comm->heap;
     const size_t sB = sendBytes(&cs), rB = recvBytes(&cs);
     q.collId = collId;
-    const bool viaArena = cs.algo == dfcclAlgoNvls;
-    if (viaArena) {          // in place when the buffer lives in the arena, else through this collective's slots
+    const bool viaArena = cs.algo == dfcclAlgoNvls || cs.algo == dfcclAlgoPush;
+    if (cs.algo == dfcclAlgoPush) {          // the user's buffers are touched by this rank only: used where they are
+      if (heap->contains(send, sB)) q.send = heap->offsetOf(send); else { q.flags |= SQE_SEND_STAGED; q.send = (uint64_t)(uintptr_t)send; }
+      if (heap->contains(recv, rB)) q.recv = heap->offsetOf(recv); else { q.flags |= SQE_RECV_STAGED; q.recv = (uint64_t)(uintptr_t)recv; }
+    } else if (viaArena) {          // in place when the buffer lives in the arena, else through this collective's slots
       NvlsArena* a = e.comm->nvls;
       if (a->contains(send, sB)) q.send = (uint64_t)((const char*)send - a->uc); else { q.flags |= SQE_SEND_STAGED; q.send = (uint64_t)(uintptr_t)send; }
       if (a->contains(recv, rB)) q.recv = (uint64_t)((char*)recv - a->uc); else { q.flags |= SQE_RECV_STAGED; q.recv = (uint64_t)(uintptr_t)recv; }
@@ -647,6 +659,12 @@ static ncclResult_t launchFromCaller(ofcclRankCtx* ctx) {
   return r;
 }
 
+DF_API ncclResult_t dfcclSetHoldOnWait(ofcclRankCtx_t ctx, int on) {
+  if (!ctx) return ncclInvalidArgument;
+  ctx->holdOnWait = on != 0;
+  return ncclSuccess;
+}
+
 DF_API ncclResult_t dfcclStreamWait(int collId, cudaStream_t stream, ofcclRankCtx_t ctx) {
   if (!ctx || !ctx->finalized) return ncclInvalidUsage;
   uint64_t want;
@@ -666,7 +684,7 @@ DF_API ncclResult_t dfcclStreamWait(int collId, cudaStream_t stream, ofcclRankCt
     // (only where this context has the daemon launch to itself: ranks that share one launch - several ranks
     // of one process on one device - must keep leaving when stalled, or one rank's held blocks would keep the
     // shared kernel alive in front of the relaunch another rank is waiting for)
-    if (cap == cudaStreamCaptureStatusNone && ctx->remaining.load() > 0 && ctx->launcher && ctx->launcher->expected == 1) {
+    if (ctx->holdOnWait && cap == cudaStreamCaptureStatusNone && ctx->remaining.load() > 0 && ctx->launcher && ctx->launcher->expected == 1) {
       ctl_store(&ctx->ctl->hold, 1);
       std::atomic_thread_fence(std::memory_order_seq_cst);
       if (!ctl_load(&ctx->ctl->alive)) DFCHECK(launchFromCaller(ctx));
@@ -787,6 +805,7 @@ static void releaseHeapParts(ofcclRankCtx* ctx) {
     CollEntry& e = kv.second;
     e.ring.reset();
     if (e.flagsBytes) e.comm->heap->free(e.flagsOff);
+    if (e.pushBytes) e.comm->heap->free(e.pushOff);
     for (int k = 0; k < 2; ++k) if (e.stagingBytes[k]) e.comm->heap->free(e.stagingOff[k]);
     e.comm = nullptr;
   }

@@ -29,6 +29,7 @@ struct CollEntry {
   ncclComm* comm = nullptr;
   CollStatic cs{};
   uint64_t flagsOff = 0, flagsBytes = 0;
+  uint64_t pushOff = 0, pushBytes = 0;       // slots of the push schedule (small all-reduces)
   uint64_t stagingOff[2] = {0, 0}, stagingBytes[2] = {0, 0};
   CallbackFunc cb = nullptr;
   void* cbArgs = nullptr;
@@ -79,6 +80,7 @@ struct ofcclRankCtx {
   // threads
   std::shared_ptr<dfccl::DaemonLauncher> launcher;
   int launcherSlot = 0;
+  bool holdOnWait = true;                     // dfcclStreamWait keeps an instance of the daemon resident (see dfcclSetHoldOnWait)
   std::thread poller;
   std::vector<std::thread> netThreads;        // one per submission on a network-mode communicator (joined at destroy)
   std::mutex netMu;

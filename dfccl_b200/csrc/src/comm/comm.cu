@@ -8,6 +8,7 @@
 #include <atomic>
 #include <cstring>
 #include <map>
+#include <strings.h>
 #include <unistd.h>
 
 namespace dfccl {
@@ -81,7 +82,7 @@ ncclResult_t resolveRedOp(ncclComm* comm, ncclRedOp_t op, ncclDataType_t type, i
 
 struct PeerInfoMsg {
   HeapHandle heap;
-  uint64_t saFlagsOff, p2pFlagsOff;
+  uint64_t saFlagsOff, p2pFlagsOff, pushOff;
   uint64_t commHash;
   int32_t device, backend;
 };
@@ -109,14 +110,18 @@ ncclResult_t commCreate(std::shared_ptr<Bootstrap> boot, dfcclBackend_t backend,
   // flag words of the stream-ordered engine and of send / recv
   DFCHECK(c->heap->alloc(sizeof(FlagSlot) * DF_MAX_BLOCKS * n, &c->saFlagsOff));
   DFCHECK(c->heap->alloc(sizeof(FlagSlot) * 2 * n * 8, &c->p2pFlagsOff));   // [direction][peer][channel]
+  if (n > 1) {                        // slots of the push schedule: [2 parities][n writers][pushMaxBytes]
+    c->pushSlotBytes = (pushMaxBytes() + 511) & ~(size_t)511;
+    DFCHECK(c->heap->alloc(2 * (size_t)n * c->pushSlotBytes, &c->pushOff, false));
+  }
   std::vector<PeerInfoMsg> all(n);
   PeerInfoMsg& me = all[r];
   c->heap->exportHandle(&me.heap);
-  me.saFlagsOff = c->saFlagsOff; me.p2pFlagsOff = c->p2pFlagsOff; me.device = device; me.backend = backend;
+  me.saFlagsOff = c->saFlagsOff; me.p2pFlagsOff = c->p2pFlagsOff; me.pushOff = c->pushOff; me.device = device; me.backend = backend;
   me.commHash = r == 0 ? ((uint64_t)getpid() << 32) ^ (uint64_t)(uintptr_t)c.get() ^ hostHash() : 0;
   DFCHECK(boot->allGather(all.data(), sizeof(PeerInfoMsg)));
   c->commHash = all[0].commHash;
-  c->handles.resize(n); c->peerHeap.resize(n); c->peerSaFlagsOff.resize(n); c->peerP2pFlagsOff.resize(n);
+  c->handles.resize(n); c->peerHeap.resize(n); c->peerSaFlagsOff.resize(n); c->peerP2pFlagsOff.resize(n); c->peerPushOff.resize(n);
   c->sendSeq.assign(n, 0); c->recvSeq.assign(n, 0);
   // members on another host cannot be mapped: the whole communicator then goes through the network path
   c->netMode = n > 1 && paramI64("FORCE_NET", 0) != 0;
@@ -125,6 +130,7 @@ ncclResult_t commCreate(std::shared_ptr<Bootstrap> boot, dfcclBackend_t backend,
     c->handles[j] = all[j].heap;
     c->peerSaFlagsOff[j] = all[j].saFlagsOff;
     c->peerP2pFlagsOff[j] = all[j].p2pFlagsOff;
+    c->peerPushOff[j] = all[j].pushOff;
     if (j == r) c->peerHeap[j] = c->heap->base();
     else if (c->netMode) c->peerHeap[j] = nullptr;
     else DFCHECK(c->heap->importPeer(all[j].heap, &c->peerHeap[j]));
@@ -161,6 +167,7 @@ ncclResult_t commDestroy(ncclComm* c) {
   if (c->nvls) { nvlsArenaDestroy(c, c->nvls); c->nvls = nullptr; }
   c->heap->free(c->saFlagsOff);
   c->heap->free(c->p2pFlagsOff);
+  if (c->pushSlotBytes) c->heap->free(c->pushOff);
   for (int k = 0; k < 2; ++k) if (c->scratchBytes[k]) c->heap->free(c->scratchOff[k]);
   devFree(c->backend, c->saRdHost.dyn);
   devFree(c->backend, c->saRd);
@@ -168,6 +175,17 @@ ncclResult_t commDestroy(ncclComm* c) {
   if (c->ownsHeap) delete c->heap;
   delete c;
   return ncclSuccess;
+}
+
+size_t pushMaxBytes() { return (size_t)std::max<int64_t>(0, paramI64("PUSH_MAX_BYTES", 256 << 10)); }
+
+bool pushEligible(const ncclComm* c, int kind, size_t bytes, int pinnedAlgo) {
+  if (kind != dfcclCollAllReduce || c->nranks < 2 || c->netMode || bytes == 0 || bytes > pushMaxBytes()) return false;
+  if (pinnedAlgo == dfcclAlgoPush) return true;
+  if (pinnedAlgo != dfcclAlgoAuto) return false;
+  std::string env = paramStr("ALGO", "");
+  if (!env.empty()) return strcasecmp(env.c_str(), "push") == 0;
+  return paramI64("PUSH", 1) != 0;
 }
 
 bool nvlsEligible(const ncclComm* c, int kind, int inType, int outType, int devOp, int postDiv, size_t count) {
@@ -260,6 +278,11 @@ ncclResult_t commCollective(ncclComm* c, int kind, const void* send, void* recv,
   const bool nvlsOk = nvlsEligible(c, kind, type, type, devOp, cs.postDiv, count);
   TunerChoice ch = tunerChoose(*topo, kind, bytes, c->nranks, maxBlocks, nvlsOk);
   cs.algo = ch.algo; cs.nBlocks = ch.nBlocks;
+  if (pushEligible(c, kind, bytes, dfcclAlgoAuto) && c->pushSlotBytes >= bytes) {
+    cs.algo = dfcclAlgoPush;
+    cs.pushSlotBytes = c->pushSlotBytes;
+    for (int j = 0; j < c->nranks; ++j) cs.peerPush[j] = c->peerHeap[j] + c->peerPushOff[j];
+  }
   if (cs.algo == dfcclAlgoNvls) {
     NvlsArena* a = c->nvls;
     const size_t half = a->streamBytes / 2;
@@ -291,7 +314,11 @@ ncclResult_t commCollective(ncclComm* c, int kind, const void* send, void* recv,
     if (a->contains(recv, rBytes)) r = (uint64_t)((char*)recv - a->uc);
     else { flags |= SQE_RECV_STAGED; r = (uint64_t)(uintptr_t)recv; cs.stagingRecvOff = (uint64_t)(a->uc + cs.nvlsOut - c->heap->base()); }
   }
-  const bool viaArena = cs.algo == dfcclAlgoNvls;
+  if (cs.algo == dfcclAlgoPush) {        // nobody but this rank touches the user's buffers: raw addresses, nothing staged
+    if (c->heap->contains(send, sBytes)) s = c->heap->offsetOf(send); else { flags |= SQE_SEND_STAGED; s = (uint64_t)(uintptr_t)send; }
+    if (c->heap->contains(recv, rBytes)) r = c->heap->offsetOf(recv); else { flags |= SQE_RECV_STAGED; r = (uint64_t)(uintptr_t)recv; }
+  }
+  const bool viaArena = cs.algo == dfcclAlgoNvls || cs.algo == dfcclAlgoPush;
   bool stageSend = !viaArena && needSend && !c->heap->contains(send, sBytes);
   // one-shot in place: peers read my input while I overwrite it, so they get a private copy
   if (needSend && kind == dfcclCollAllReduce && cs.algo == dfcclAlgoOneShot && send == recv && c->nranks > 1) stageSend = true;

@@ -53,6 +53,8 @@ struct ncclComm {
   uint64_t p2pFlagsOff = 0;
   std::vector<uint64_t> peerP2pFlagsOff;
   std::vector<uint32_t> sendSeq, recvSeq;      // per peer
+  uint64_t pushOff = 0, pushSlotBytes = 0;     // slots of the push schedule of the stream-ordered entry points
+  std::vector<uint64_t> peerPushOff;
   uint64_t scratchOff[2] = {0, 0};             // staging for buffers outside the heap (send, recv)
   uint64_t scratchBytes[2] = {0, 0};
   uint32_t opCount = 0;
@@ -83,6 +85,10 @@ int daemonBlocks(dfcclBackend_t be);
 ncclResult_t resolveRedOp(ncclComm* comm, ncclRedOp_t op, ncclDataType_t type, int nranks, int* devOp, double* scale, int* postDiv);
 // Heap of (backend, device), created on first use and shared by all communicators of the process.
 ncclResult_t processHeap(dfcclBackend_t backend, int device, Heap** out);
+
+// Small all-reduces go out in one hop (push schedule) unless a schedule was pinned or DFCCL_PUSH=0.
+bool pushEligible(const ncclComm* comm, int kind, size_t bytes, int pinnedAlgo);
+size_t pushMaxBytes();
 
 // Can this all-reduce run on the NVLS schedule of this communicator?  (arena present, sum, supported types, 16-byte multiple)
 bool nvlsEligible(const ncclComm* comm, int kind, int inType, int outType, int devOp, int postDiv, size_t count);

@@ -9,7 +9,13 @@
 namespace dfccl {
 
 inline bool nvtxOn() {
-  static const bool on = paramI64("NVTX", 1) != 0;
+  // NVTX binds to an attached tool lazily at the first call and does so without synchronisation; making that
+  // first call here, under the guard of the static initialiser, keeps it to one thread
+  static const bool on = [] {
+    const bool v = paramI64("NVTX", 1) != 0;
+    if (v) { nvtxRangePushA("dfccl:init"); nvtxRangePop(); }
+    return v;
+  }();
   return on;
 }
 

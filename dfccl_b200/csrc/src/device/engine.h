@@ -14,7 +14,9 @@
 // and stores of peer buffers -> everybody done" and the only blocking points are
 // the two rendezvous.
 //
-// Schedules (kind x algo), all expressed as N-source / M-destination reduce-copy:
+// Schedules (kind x algo), all expressed as N-source / M-destination reduce-copy
+// (plus the push schedule of small all-reduces: inputs are written into slots at the peers together with the arrival
+// flag, every rank reduces locally and is done - one NVLink hop, no staging, no done handshake):
 //   AllReduce two-shot  : block b, rank r owns shard r of slice b: reads it from all
 //                         ranks, reduces, scales, casts, writes it to all ranks.
 //   AllReduce one-shot  : every rank reads slice b from all ranks, writes only itself.
@@ -207,6 +209,36 @@ DF_HD char* recvPtrOf(const BlockShared* sh, int b, int j) {
   return c->peerHeap[j] + off;
 }
 
+// Push schedule: the user's buffers are only touched by this rank, so they are used where they are.
+DF_HD const char* pushSendPtr(const BlockShared* sh) {
+  return (sh->dyn.sqeFlags & SQE_SEND_STAGED) ? (const char*)(uintptr_t)sh->dyn.send : sh->cs.peerHeap[sh->cs.rank] + sh->dyn.send;
+}
+DF_HD char* pushRecvPtr(const BlockShared* sh) {
+  return (sh->dyn.sqeFlags & SQE_RECV_STAGED) ? (char*)(uintptr_t)sh->dyn.recv : sh->cs.peerHeap[sh->cs.rank] + sh->dyn.recv;
+}
+// slot that `writer` fills at member `owner` for this epoch's parity
+DF_HD char* pushSlot(const BlockShared* sh, int owner, int writer) {
+  const CollStatic* c = &sh->cs;
+  return c->peerPush[owner] + ((uint64_t)(sh->dyn.epoch & 1u) * c->nranks + writer) * c->pushSlotBytes;
+}
+// my input -> my slot at every peer (block b moves its part of the range)
+DF_HD void pushOut(BlockShared* sh, int b) {
+  const CollStatic* c = &sh->cs;
+  if (df_tid() == 0) {
+    DataArgs* a = &sh->args;
+    const uint64_t es = dtypeSize(c->inType);
+    uint64_t bb, be;
+    partRange(c->count, c->nBlocks, b, 16, &bb, &be);
+    a->nsrc = 1; a->ndst = 0; a->n = (be - bb) * es;
+    a->src[0] = pushSendPtr(sh) + bb * es;
+    for (int k = 1; k < c->nranks; ++k) { const int j = (c->rank + k) % c->nranks; a->dst[a->ndst++] = pushSlot(sh, j, c->rank) + bb * es; }
+    sh->stats.bytesCopied += a->n * a->ndst;
+  }
+  df_sync();
+  if (sh->args.n && sh->args.ndst) copy_multi(&sh->args);
+  df_sync();
+}
+
 // ---- PH_DATA: thread 0 builds the pointer lists, everybody moves the data
 DF_HD void dataPhase(BlockShared* sh, RankDev* rd, int b) {
   const CollStatic* c = &sh->cs;
@@ -220,7 +252,13 @@ DF_HD void dataPhase(BlockShared* sh, RankDev* rd, int b) {
     switch (c->kind) {
       case dfcclCollAllReduce: {
         partRange(c->count, c->nBlocks, b, 16, &bb, &be);
-        if (c->algo == dfcclAlgoNvls && n > 1) {
+        if (c->algo == dfcclAlgoPush && n > 1) {
+          // everything is here: my own input plus the slots the peers filled
+          a->src[a->nsrc++] = pushSendPtr(sh) + bb * es;
+          for (int k = 1; k < n; ++k) a->src[a->nsrc++] = pushSlot(sh, me, (me + k) % n) + bb * es;
+          a->dst[a->ndst++] = pushRecvPtr(sh) + bb * eo;
+          a->n = be - bb;
+        } else if (c->algo == dfcclAlgoNvls && n > 1) {
           // my slice of this block's range, as byte offsets into the arena (symmetric on all members)
           uint64_t sb, se;
           partRange(be - bb, n, me, 16, &sb, &se);
@@ -391,7 +429,7 @@ DF_HD int runColl(BlockShared* sh, RankDev* rd, int b, int coll, uint32_t budget
         setPhase(sh, PH_COPY_IN);
         break;
       case PH_COPY_IN:
-        if (sh->dyn.sqeFlags & SQE_SEND_STAGED) {
+        if ((sh->dyn.sqeFlags & SQE_SEND_STAGED) && sh->cs.algo != dfcclAlgoPush) {
           bool needed = !(sh->cs.kind == dfcclCollBroadcast && me != sh->cs.root);
           if (needed) stageCopy(sh, b, true);
           if (tid == 0) fence_sys();
@@ -399,6 +437,12 @@ DF_HD int runColl(BlockShared* sh, RankDev* rd, int b, int coll, uint32_t budget
         setPhase(sh, PH_POST_ARRIVE);
         break;
       case PH_POST_ARRIVE: {
+        if (sh->cs.algo == dfcclAlgoPush && n > 1) {
+          // the payload travels with the arrival flag: stores to a peer, one fence, then the flag
+          pushOut(sh, b);
+          if (tid == 0) fence_sys();
+          df_sync();
+        }
         const uint64_t so = mySendOff(sh), ro = myRecvOff(sh), epoch = sh->dyn.epoch;
         for (int j = tid; j < n; j += nt) {
           if (j == me) continue;
@@ -419,7 +463,8 @@ DF_HD int runColl(BlockShared* sh, RankDev* rd, int b, int coll, uint32_t budget
         if (tid == 0) trace(rd, b, TR_DATA_BEGIN, coll);
         dataPhase(sh, rd, b);
         if (tid == 0) trace(rd, b, TR_DATA_END, coll);
-        setPhase(sh, PH_POST_DONE);
+        // push schedule: nobody reads my buffers and my slots are not reused before the peers' next-but-one call
+        setPhase(sh, (sh->cs.algo == dfcclAlgoPush && n > 1) ? PH_COMPLETE : PH_POST_DONE);
         break;
       case PH_POST_DONE: {
         if (n > 1) {
@@ -441,7 +486,7 @@ DF_HD int runColl(BlockShared* sh, RankDev* rd, int b, int coll, uint32_t budget
         setPhase(sh, PH_COPY_OUT);
         break;
       case PH_COPY_OUT:
-        if (sh->dyn.sqeFlags & SQE_RECV_STAGED) {
+        if ((sh->dyn.sqeFlags & SQE_RECV_STAGED) && sh->cs.algo != dfcclAlgoPush) {
           bool needed = !(sh->cs.kind == dfcclCollReduce && me != sh->cs.root);
           if (needed) stageCopy(sh, b, false);
         }

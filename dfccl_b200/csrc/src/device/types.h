@@ -92,6 +92,9 @@ struct alignas(16) CollStatic {
   char* mcHeap;
   char** nvlsPeers;
   uint64_t nvlsIn, nvlsOut;
+  // push schedule: slot area of member j as mapped here, laid out [2 parities][nranks writers][pushSlotBytes]
+  char* peerPush[DF_MAX_RANKS];
+  uint64_t pushSlotBytes;
 };
 
 // ---- mutable per (block, collective) state; what a context switch saves and loads

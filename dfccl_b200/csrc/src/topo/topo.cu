@@ -230,8 +230,10 @@ TunerChoice tunerChoose(const Topology& t, int kind, size_t bytes, int n, int ma
     if (!strcasecmp(envAlgo.c_str(), "oneshot")) pinnedAlgo = dfcclAlgoOneShot;
     else if (!strcasecmp(envAlgo.c_str(), "twoshot")) pinnedAlgo = dfcclAlgoTwoShot;
     else if (!strcasecmp(envAlgo.c_str(), "nvls")) pinnedAlgo = dfcclAlgoNvls;
-    else DF_INFO(SUB_TUNING, "ALGO=%s names no schedule of this engine (oneshot|twoshot|nvls); ignored", envAlgo.c_str());
+    else if (!strcasecmp(envAlgo.c_str(), "push")) pinnedAlgo = dfcclAlgoAuto;      // chosen by the callers, by size
+    else DF_INFO(SUB_TUNING, "ALGO=%s names no schedule of this engine (oneshot|twoshot|nvls|push); ignored", envAlgo.c_str());
   }
+  if (pinnedAlgo == dfcclAlgoPush) pinnedAlgo = dfcclAlgoAuto;                      // block count as for the size; the callers switch the schedule
   if (pinnedBlocks == 0) pinnedBlocks = (int)paramI64("NBLOCKS", 0);
   const size_t minPerBlock = (size_t)paramI64("MIN_BYTES_PER_BLOCK", 32 << 10);
   TunerChoice best{dfcclAlgoTwoShot, 1, 1e30};

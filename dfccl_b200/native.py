@@ -19,7 +19,7 @@ SUCCESS, UNHANDLED_CUDA, SYSTEM_ERROR, INTERNAL_ERROR, INVALID_ARGUMENT, INVALID
 SUM, PROD, MAX, MIN, AVG = range(5)
 INT8, UINT8, INT32, UINT32, INT64, UINT64, FLOAT16, FLOAT32, FLOAT64, BFLOAT16 = range(10)
 ALLREDUCE, ALLGATHER, REDUCESCATTER, BROADCAST, REDUCE = range(5)
-ALGO_AUTO, ALGO_ONESHOT, ALGO_TWOSHOT, ALGO_NVLS = range(4)
+ALGO_AUTO, ALGO_ONESHOT, ALGO_TWOSHOT, ALGO_NVLS, ALGO_PUSH = range(5)
 BACKEND_CUDA, BACKEND_HOST = 0, 1
 FAULT_NONE, FAULT_DROP_SQE, FAULT_DELAY_SQE_US, FAULT_FREEZE_POLLER = range(4)
 
@@ -107,7 +107,7 @@ def lib() -> C.CDLL:
             "dfcclRunOnStream": [vp, vp, i, vp, CALLBACK, vp, vp],
             "dfcclStreamWait": [i, vp, vp], "dfcclWait": [i, i, vp], "dfcclWaitAll": [i, vp],
             "dfcclAbort": [vp], "dfcclGetAsyncError": [vp, C.POINTER(i)],
-            "dfcclGemmReserveSms": [i], "dfcclGetStats": [vp, C.POINTER(Stats)], "dfcclGetHostStats": [vp, C.POINTER(Stats)], "dfcclTraceDump": [vp, C.c_char_p],
+            "dfcclGemmReserveSms": [i], "dfcclSetHoldOnWait": [vp, i], "dfcclGetStats": [vp, C.POINTER(Stats)], "dfcclGetHostStats": [vp, C.POINTER(Stats)], "dfcclTraceDump": [vp, C.c_char_p],
             "dfcclInjectFault": [vp, i, C.c_int64],
             "dfcclFusedSgdStep": [vp, vp, vp, vp, sz, i, C.c_float, C.c_float, C.c_float, i, vp],
             "dfcclOpsWarm": [],
@@ -310,6 +310,9 @@ class RankCtx:
         s = Stats()
         check(lib().dfcclGetStats(self.handle, C.byref(s)), "dfcclGetStats")
         return s.as_dict()
+
+    def set_hold_on_wait(self, on: bool) -> None:
+        check(lib().dfcclSetHoldOnWait(self.handle, 1 if on else 0), "dfcclSetHoldOnWait")
 
     def host_stats(self) -> Dict[str, int]:
         """Host-side counters only; safe while the device is busy."""

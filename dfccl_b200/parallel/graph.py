@@ -16,6 +16,9 @@ import torch
 class GraphedStep:
     def __init__(self, net: torch.nn.Module, loss_fn: Callable, ddp, x: torch.Tensor, y: torch.Tensor, warmup: int = 3):
         self.ddp = ddp
+        # a replayed step is enqueued with a handful of calls: the daemon is woken by the poller when the first
+        # bucket is released instead of being held on its SMs from the moment the waits are enqueued
+        ddp.ctx.set_hold_on_wait(False)
         self.x = x.clone()
         self.y = y.clone()
         dev = x.device

@@ -141,6 +141,8 @@ class HybridTrainer:
         their collectives inside, the pipeline transfers) into one CUDA graph.  The fused kernels and the
         stream-ordered collectives count their calls on the device, so the captured launches stay valid."""
         dev = self.d.device
+        if hasattr(self.ddp, "ctx"):
+            self.ddp.ctx.set_hold_on_wait(False)             # a replayed step is a handful of host calls (see GraphedStep)
         self._tok = tokens.clone() if tokens is not None else None
         self._tgt = targets.clone() if targets is not None else None
         side = torch.cuda.Stream(device=dev)
