@@ -185,7 +185,7 @@ bool pushEligible(const ncclComm* c, int kind, size_t bytes, int pinnedAlgo) {
   if (pinnedAlgo != dfcclAlgoAuto) return false;
   std::string env = paramStr("ALGO", "");
   if (!env.empty()) return strcasecmp(env.c_str(), "push") == 0;
-  return paramI64("PUSH", 0) != 0;   // opt-in until measured on every GPU count
+  return paramI64("PUSH", 1) != 0;
 }
 
 bool nvlsEligible(const ncclComm* c, int kind, int inType, int outType, int devOp, int postDiv, size_t count) {
