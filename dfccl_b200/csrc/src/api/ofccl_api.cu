@@ -144,13 +144,14 @@ static void pollerMain(ofcclRankCtx* ctx) {
     }
     if (ctx->untriggered.load() > 0) {          // stream-ordered submissions whose release has not been seen yet
       int fired = 0;
-      {
-        std::lock_guard<std::mutex> l(ctx->mu);
+      std::unique_lock<std::mutex> l(ctx->mu, std::try_to_lock);     // never make a submitting thread wait for this scan
+      if (l.owns_lock()) {
         auto& pt = ctx->pendingTrig;
         for (size_t i = 0; i < pt.size();) {
           if (__atomic_load_n((const uint64_t*)&ctx->hostTrig[pt[i].first], __ATOMIC_ACQUIRE) >= pt[i].second) { pt[i] = pt.back(); pt.pop_back(); ++fired; }
           else ++i;
         }
+        l.unlock();
       }
       if (fired) {
         ctx->untriggered -= fired;
