@@ -125,23 +125,39 @@ static void deliver(ofcclRankCtx* ctx, uint64_t entry) {
   if (cb) { cb(coll, args); ctx->cbs++; }
   {
     std::lock_guard<std::mutex> l(ctx->mu);
-    ctx->colls[coll].completed++;
+    { uint64_t* w = &ctx->colls[coll].completed; __atomic_store_n(w, *w + 1, __ATOMIC_RELEASE); }   // also read lock-free by spinning waiters
     ctx->remaining--;
     if (ctx->remaining.load() == 0) ctl_store(&ctx->ctl->hold, 0);
   }
   ctx->doneCv.notify_all();
 }
 
+// Short waits are polled (yielding the CPU, dropping the lock between looks) before the caller is put to
+// sleep on the condition variable: being woken costs tens of microseconds, a completion usually arrives sooner.
+template <typename Quick, typename Pred>
+static bool spinFirst(std::unique_lock<std::mutex>& l, Quick quick, Pred pred, int spins = 4000) {
+  if (pred()) return true;
+  l.unlock();                                   // `quick` reads atomics only: the poller is not slowed by lock traffic
+  for (int i = 0; i < spins && !quick(); ++i) sched_yield();
+  l.lock();
+  return pred();
+}
+
 // Turns completion entries into callbacks: the reference's poller thread.
 static void pollerMain(ofcclRankCtx* ctx) {
   logSetRank(ctx->rank);
   int64_t empty = 0;
+  int idleSpins = 0;
   while (!ctx->stopPoller.load()) {
     if (ctx->remaining.load() == 0) {
+      // stay awake for a moment: a caller that submits again right away then finds nobody to wake (waking a
+      // sleeping thread costs the submitter a system call)
+      if (++idleSpins < 4000) { sched_yield(); continue; }
       std::unique_lock<std::mutex> l(ctx->mu);
       ctx->pollCv.wait_for(l, std::chrono::milliseconds(20), [&] { return ctx->remaining.load() > 0 || ctx->stopPoller.load(); });
       continue;
     }
+    idleSpins = 0;
     if (ctx->untriggered.load() > 0) {          // stream-ordered submissions whose release has not been seen yet
       int fired = 0;
       std::unique_lock<std::mutex> l(ctx->mu, std::try_to_lock);     // never make a submitting thread wait for this scan
@@ -482,7 +498,11 @@ static ncclResult_t submit(ofcclRankCtx* ctx, const void* send, void* recv, int 
       if (!onStream) { DF_WARN("collective %d submitted again before its callback ran", collId); return ncclInvalidUsage; }
       // Stream-ordered callers enqueue ahead of the GPU: the previous submission of this id is
       // already ordered before this one on the device, so the host only has to wait for it.
-      const bool ok = ctx->doneCv.wait_for(l, std::chrono::seconds(120), [&] { return e.submitted == e.completed || ctl_load(&ctx->ctl->abortFlag); });
+      auto prevDone = [&] { return e.submitted == e.completed || ctl_load(&ctx->ctl->abortFlag); };
+      uint64_t* completedWord = &e.completed;
+      const uint64_t wantDone = e.submitted;
+      const bool ok = spinFirst(l, [&] { return __atomic_load_n(completedWord, __ATOMIC_ACQUIRE) >= wantDone || ctl_load(&ctx->ctl->abortFlag); }, prevDone) ||
+                      ctx->doneCv.wait_for(l, std::chrono::seconds(120), prevDone);
       if (!ok) { DF_WARN("collective %d: previous submission did not complete within 120 s", collId); return dfcclTimeout; }
       if (ctl_load(&ctx->ctl->abortFlag)) return dfcclAborted;
     }
@@ -622,7 +642,10 @@ DF_API ncclResult_t dfcclWait(int collId, int timeoutMs, ofcclRankCtx_t ctx) {
   if (it == ctx->colls.end()) return ncclInvalidArgument;
   CollEntry& e = it->second;
   auto pred = [&] { return e.completed == e.submitted || ctl_load(&ctx->ctl->abortFlag); };
-  if (timeoutMs < 0) ctx->doneCv.wait(l, pred);
+  uint64_t* completedWord = &e.completed;
+  const uint64_t wantDone = e.submitted;
+  if (spinFirst(l, [&] { return __atomic_load_n(completedWord, __ATOMIC_ACQUIRE) >= wantDone || ctl_load(&ctx->ctl->abortFlag); }, pred)) {}
+  else if (timeoutMs < 0) ctx->doneCv.wait(l, pred);
   else if (!ctx->doneCv.wait_for(l, std::chrono::milliseconds(timeoutMs), pred)) return dfcclTimeout;
   if (ctl_load(&ctx->ctl->abortFlag) && e.completed != e.submitted) return dfcclAborted;
   return e.lastStatus == ST_OK ? ncclSuccess : e.lastStatus == ST_TIMEOUT ? dfcclTimeout : e.lastStatus == ST_ABORTED ? dfcclAborted : ncclInternalError;
@@ -632,7 +655,8 @@ DF_API ncclResult_t dfcclWaitAll(int timeoutMs, ofcclRankCtx_t ctx) {
   if (!ctx || !ctx->finalized) return ncclInvalidUsage;
   std::unique_lock<std::mutex> l(ctx->mu);
   auto pred = [&] { return ctx->remaining.load() == 0 || ctl_load(&ctx->ctl->abortFlag); };
-  if (timeoutMs < 0) ctx->doneCv.wait(l, pred);
+  if (spinFirst(l, pred, pred)) {}
+  else if (timeoutMs < 0) ctx->doneCv.wait(l, pred);
   else if (!ctx->doneCv.wait_for(l, std::chrono::milliseconds(timeoutMs), pred)) return dfcclTimeout;
   if (ctl_load(&ctx->ctl->abortFlag) && ctx->remaining.load()) return dfcclAborted;
   return ctx->asyncError;
