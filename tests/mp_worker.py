@@ -242,7 +242,7 @@ def _gpt_hybrid(nv, comm, rank, world, backend, tp, pp, dp, port):
     from dfccl_b200.parallel.groups import Dist
     from dfccl_b200.parallel.hybrid import HybridTrainer, build_mesh
     cfg = GPT2Config(n_layer=4, d_model=512, n_head=8, seq_len=128, vocab=512) if cuda else \
-        GPT2Config(n_layer=2, d_model=64, n_head=4, seq_len=32, vocab=96)
+        GPT2Config(n_layer=2 if pp < 3 else pp, d_model=64, n_head=4, seq_len=32, vocab=96)
     micro_batch, n_micro, steps = 2, 2, 3
     d = Dist(rank, world, rank if cuda else 0, dev, comm, True)
     mesh = build_mesh(d, tp, pp, dp)
@@ -288,6 +288,10 @@ def scenario_gpt_tp2pp2(nv, comm, rank, world, backend):
 
 def scenario_gpt_pp2dp2(nv, comm, rank, world, backend):
     return _gpt_hybrid(nv, comm, rank, world, backend, 1, 2, 2, 29583)
+
+
+def scenario_gpt_pp3(nv, comm, rank, world, backend):
+    return _gpt_hybrid(nv, comm, rank, world, backend, 1, 3, 1, 29585)
 
 
 def scenario_gpt_tp2pp2dp2(nv, comm, rank, world, backend):

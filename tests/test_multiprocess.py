@@ -38,7 +38,7 @@ def test_fused_tensor_parallel_gemms():
     mp_worker.launch(2 if torch.cuda.device_count() < 4 else 4, "cuda", "fused_tp", timeout=300)
 
 
-@pytest.mark.parametrize("layout,world", [("tp2", 2), ("tp2pp2", 4), ("pp2dp2", 4), ("tp2pp2dp2", 8)])
+@pytest.mark.parametrize("layout,world", [("tp2", 2), ("tp2pp2", 4), ("pp2dp2", 4), ("pp3", 3), ("tp2pp2dp2", 8)])
 def test_host_gpt2_hybrid_parallel(layout, world):
     """Tensor x pipeline x data parallel GPT-2 steps on CPU ranks match the unsharded model."""
     res = mp_worker.launch(world, "host", "gpt_" + layout, timeout=300)
