@@ -221,6 +221,27 @@ class DaemonDDP:
     def stats(self) -> Dict[str, int]:
         return self.ctx.stats()
 
+    # ------------------------------------------------------------------ checkpoint / resume
+    def state_dict(self) -> Dict[str, object]:
+        """Optimizer state of this rank (fp32 master weights and momentum per bucket), for ``torch.save``.  The
+        bucket layout is a function of the module and the bucket size, so a wrapper built the same way loads it."""
+        return {"first_step": self._first_step, "lr": self.lr, "momentum": self.mu, "weight_decay": self.wd,
+                "buckets": [{"numel": b.numel, "dtype": str(b.dtype), "master": b.master.detach().cpu().clone(),
+                             "momentum": b.momentum.detach().cpu().clone()} for b in self.buckets]}
+
+    def load_state_dict(self, state: Dict[str, object]) -> None:
+        bs = state["buckets"]
+        if len(bs) != len(self.buckets) or any(x["numel"] != b.numel or x["dtype"] != str(b.dtype) for x, b in zip(bs, self.buckets)):
+            raise ValueError("checkpoint was written with another bucket layout (module or bucket size differ)")
+        with torch.no_grad():
+            for x, b in zip(bs, self.buckets):
+                b.master.copy_(x["master"])
+                b.momentum.copy_(x["momentum"])
+                b.flat_param.copy_(b.master)          # the module's parameters are views of the flat array
+                b.grad.zero_()
+        self._first_step = bool(state["first_step"])
+        self.lr, self.mu, self.wd = float(state["lr"]), float(state["momentum"]), float(state["weight_decay"])
+
     def close(self) -> None:
         for h in self._hooks:
             h.remove()

@@ -128,3 +128,37 @@ def test_stress_orders_deadlock_an_inorder_library():
     v = inorder_verdict(64, 20, 8, 2024)
     assert v["iterations_with_incompatible_orders"] == 20 and v["first"]["iteration"] == 0
     assert inorder_verdict(16, 5, 1, 7)["iterations_with_incompatible_orders"] == 0     # one rank cannot disagree with itself
+
+
+def test_checkpoint_resume_continues_the_same_trajectory(host_backend, tmp_path):
+    """Save after two steps, rebuild the wrapper from scratch, load, continue: same weights as an uninterrupted run."""
+    nv = host_backend
+    from dfccl_b200.parallel import DaemonDDP, Dist
+    xs = [torch.randn(16, 32, generator=torch.Generator().manual_seed(s)) for s in range(4)]
+    ys = [torch.randn(16, 8, generator=torch.Generator().manual_seed(50 + s)) for s in range(4)]
+
+    def run(steps, state=None):
+        (c,) = nv.Comm.init_loopback(1)
+        d = Dist(0, 1, 0, torch.device("cpu"), c, False)
+        net = _mlp()
+        ddp = DaemonDDP(net, d, bucket_mb=0.004, lr=0.05, momentum=0.9, weight_decay=1e-3)
+        if state is not None:
+            ddp.load_state_dict(torch.load(state, weights_only=False))
+        for s in steps:
+            nn.functional.mse_loss(net(xs[s]), ys[s]).backward()
+            ddp.finish_backward()
+            assert ddp.ctx.wait_all(30000) == nv.SUCCESS
+            ddp.step()
+        out = [p.detach().clone() for p in net.parameters()]
+        sd = ddp.state_dict()
+        ddp.close()
+        c.destroy()
+        return out, sd
+
+    full, _ = run([0, 1, 2, 3])
+    _, sd = run([0, 1])
+    path = tmp_path / "ckpt.pt"
+    torch.save(sd, path)
+    resumed, _ = run([2, 3], state=path)
+    for a, b in zip(full, resumed):
+        torch.testing.assert_close(a, b, rtol=0, atol=0)
