@@ -32,6 +32,9 @@ ncclResult_t dfcclGemmReserveSms(int n);
  * param = cast(master).  paramType: ncclBfloat16 or ncclFloat32.  All arrays 16-byte aligned. */
 ncclResult_t dfcclFusedSgdStep(void* master, const void* grad, void* momentum, void* param, size_t n, int paramType,
                                float lr, float mu, float wd, int firstStep, cudaStream_t stream);
+/* AdamW (decoupled weight decay) over the same flat arrays; `step` counts from 1, both moment arrays start at zero. */
+ncclResult_t dfcclFusedAdamWStep(void* master, const void* grad, void* moment1, void* moment2, void* param, size_t n, int paramType,
+                                 float lr, float beta1, float beta2, float eps, float wd, int step, cudaStream_t stream);
 ncclResult_t dfcclOpsWarm(void);   /* load these kernels now (before any stream can block) */
 
 /* ---- fabric probes (roofline inputs): mean device time in microseconds */

@@ -5,12 +5,14 @@
 // all-reduce already wrote the averaged gradient in fp32 (scale and cast fused into
 // the collective), so the whole update of a bucket is one streaming pass:
 //   g = grad + wd * w ; m = mu * m + g ; w -= lr * m ; param = cast(w)
+// (SGD with momentum; an AdamW variant of the same shape follows it)
 // 16 bytes in flight per array per thread, grid sized to the SM count.  No
 // counterpart in the reference, which has no optimizer (it is a collective library);
 // this kernel exists so that the gradient path of the benchmarks never leaves flat,
 // heap-resident buffers.
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
+#include <math.h>
 #include <stdint.h>
 #include "dfccl.h"
 
@@ -52,6 +54,56 @@ __global__ void __launch_bounds__(256) sgdKernel(float* __restrict__ master, con
   }
 }
 
+// AdamW over the same flat arrays (decoupled weight decay; bias correction folded into the two scalars the host
+// passes: stepSize = lr / (1 - beta1^t), invBias2Sqrt = 1 / sqrt(1 - beta2^t)):
+//   m = b1 m + (1 - b1) g ; v = b2 v + (1 - b2) g^2 ; w = w (1 - lr wd) - stepSize * m / (sqrt(v) * invBias2Sqrt + eps)
+template <typename P>
+__global__ void __launch_bounds__(256) adamwKernel(float* __restrict__ master, const float* __restrict__ grad,
+                                                   float* __restrict__ m1, float* __restrict__ m2, P* __restrict__ param, size_t n,
+                                                   float lr, float b1, float b2, float eps, float wd, float stepSize, float invBias2Sqrt) {
+  const size_t stride = (size_t)gridDim.x * blockDim.x * 4;
+  const float decay = 1.f - lr * wd;
+  for (size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 4; i < n; i += stride) {
+    float w[4], g[4], m[4], v[4];
+    const int cnt = i + 4 <= n ? 4 : (int)(n - i);
+    if (cnt == 4) {
+      *reinterpret_cast<float4*>(w) = *reinterpret_cast<const float4*>(master + i);
+      *reinterpret_cast<float4*>(g) = *reinterpret_cast<const float4*>(grad + i);
+      *reinterpret_cast<float4*>(m) = *reinterpret_cast<const float4*>(m1 + i);
+      *reinterpret_cast<float4*>(v) = *reinterpret_cast<const float4*>(m2 + i);
+    } else {
+      for (int k = 0; k < cnt; ++k) { w[k] = master[i + k]; g[k] = grad[i + k]; m[k] = m1[i + k]; v[k] = m2[i + k]; }
+    }
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      if (k < cnt) {
+        m[k] = b1 * m[k] + (1.f - b1) * g[k];
+        v[k] = b2 * v[k] + (1.f - b2) * g[k] * g[k];
+        w[k] = w[k] * decay - stepSize * m[k] / (sqrtf(v[k]) * invBias2Sqrt + eps);
+      }
+    }
+    if (cnt == 4) {
+      *reinterpret_cast<float4*>(master + i) = *reinterpret_cast<float4*>(w);
+      *reinterpret_cast<float4*>(m1 + i) = *reinterpret_cast<float4*>(m);
+      *reinterpret_cast<float4*>(m2 + i) = *reinterpret_cast<float4*>(v);
+      if (sizeof(P) == 2) {
+        __nv_bfloat162 lo = __floats2bfloat162_rn(w[0], w[1]), hi = __floats2bfloat162_rn(w[2], w[3]);
+        uint2 pk;
+        pk.x = *reinterpret_cast<uint32_t*>(&lo);
+        pk.y = *reinterpret_cast<uint32_t*>(&hi);
+        *reinterpret_cast<uint2*>(param + i) = pk;
+      } else {
+        *reinterpret_cast<float4*>(param + i) = *reinterpret_cast<float4*>(w);
+      }
+    } else {
+      for (int k = 0; k < cnt; ++k) {
+        master[i + k] = w[k]; m1[i + k] = m[k]; m2[i + k] = v[k];
+        if (sizeof(P) == 2) param[i + k] = (P)__float2bfloat16_rn(w[k]); else reinterpret_cast<float*>(param)[i + k] = w[k];
+      }
+    }
+  }
+}
+
 }  // namespace
 
 // paramType: ncclBfloat16 or ncclFloat32 (then `param` may alias `master`).  All arrays 16-byte aligned.
@@ -75,10 +127,37 @@ ncclResult_t dfcclFusedSgdStep(void* master, const void* grad, void* momentum, v
   return cudaGetLastError() == cudaSuccess ? ncclSuccess : ncclUnhandledCudaError;
 }
 
+// `step` counts from 1.  State arrays (first and second moment) start at zero.
+extern "C" __attribute__((visibility("default")))
+ncclResult_t dfcclFusedAdamWStep(void* master, const void* grad, void* moment1, void* moment2, void* param, size_t n, int paramType,
+                                 float lr, float beta1, float beta2, float eps, float wd, int step, cudaStream_t stream) {
+  if (n == 0) return ncclSuccess;
+  if (!master || !grad || !moment1 || !moment2 || !param || step < 1) return ncclInvalidArgument;
+  if ((((uintptr_t)master | (uintptr_t)grad | (uintptr_t)moment1 | (uintptr_t)moment2 | (uintptr_t)param) & 15) != 0) return ncclInvalidArgument;
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  size_t want = (n / 4 + 255) / 256;
+  int grid = (int)(want < (size_t)sms * 8 ? (want ? want : 1) : (size_t)sms * 8);
+  const float stepSize = lr / (1.f - powf(beta1, (float)step));
+  const float invBias2Sqrt = 1.f / sqrtf(1.f - powf(beta2, (float)step));
+  if (paramType == ncclBfloat16)
+    adamwKernel<__nv_bfloat16><<<grid, 256, 0, stream>>>((float*)master, (const float*)grad, (float*)moment1, (float*)moment2, (__nv_bfloat16*)param, n,
+                                                         lr, beta1, beta2, eps, wd, stepSize, invBias2Sqrt);
+  else if (paramType == ncclFloat32)
+    adamwKernel<float><<<grid, 256, 0, stream>>>((float*)master, (const float*)grad, (float*)moment1, (float*)moment2, (float*)param, n,
+                                                 lr, beta1, beta2, eps, wd, stepSize, invBias2Sqrt);
+  else
+    return ncclInvalidArgument;
+  return cudaGetLastError() == cudaSuccess ? ncclSuccess : ncclUnhandledCudaError;
+}
+
 // Load the kernels of this file into the current context without launching them.
 extern "C" __attribute__((visibility("default"))) ncclResult_t dfcclOpsWarm(void) {
   cudaFuncAttributes a;
   if (cudaFuncGetAttributes(&a, sgdKernel<__nv_bfloat16>) != cudaSuccess) return ncclUnhandledCudaError;
   if (cudaFuncGetAttributes(&a, sgdKernel<float>) != cudaSuccess) return ncclUnhandledCudaError;
+  if (cudaFuncGetAttributes(&a, adamwKernel<__nv_bfloat16>) != cudaSuccess) return ncclUnhandledCudaError;
+  if (cudaFuncGetAttributes(&a, adamwKernel<float>) != cudaSuccess) return ncclUnhandledCudaError;
   return ncclSuccess;
 }

@@ -110,6 +110,7 @@ def lib() -> C.CDLL:
             "dfcclGemmReserveSms": [i], "dfcclSetHoldOnWait": [vp, i], "dfcclGetStats": [vp, C.POINTER(Stats)], "dfcclGetHostStats": [vp, C.POINTER(Stats)], "dfcclTraceDump": [vp, C.c_char_p],
             "dfcclInjectFault": [vp, i, C.c_int64],
             "dfcclFusedSgdStep": [vp, vp, vp, vp, sz, i, C.c_float, C.c_float, C.c_float, i, vp],
+            "dfcclFusedAdamWStep": [vp, vp, vp, vp, vp, sz, i, C.c_float, C.c_float, C.c_float, C.c_float, C.c_float, i, vp],
             "dfcclOpsWarm": [],
             "dfcclGemmBf16": [vp, vp, vp, i, i, i, vp],
             "dfcclGemmCheck": [C.POINTER(i)],

@@ -45,7 +45,8 @@ class Bucket:
     grad: Optional[torch.Tensor] = None        # heap, param dtype
     grad32: Optional[torch.Tensor] = None      # heap, fp32: all-reduce output
     master: Optional[torch.Tensor] = None
-    momentum: Optional[torch.Tensor] = None
+    momentum: Optional[torch.Tensor] = None    # SGD momentum, or AdamW first moment
+    moment2: Optional[torch.Tensor] = None     # AdamW second moment
     pending: int = 0
     coll_id: int = 0
     comm: Optional[nv.Comm] = None             # the group this bucket is reduced over
@@ -75,7 +76,8 @@ class DaemonDDP:
     def __init__(self, module: nn.Module, dist: Dist, *, bucket_mb: float = 25.0, lr: float = 0.1, momentum: float = 0.9,
                  weight_decay: float = 1e-4, randomize_order: bool = True, window: int = 2, seed: int = 0,
                  coll_id_base: int = 0, comm: Optional[nv.Comm] = None, n_blocks: int = 0,
-                 daemon_blocks: int = 8, daemon_threads: int = 0, param_groups: Optional[Sequence[dict]] = None):
+                 daemon_blocks: int = 8, daemon_threads: int = 0, param_groups: Optional[Sequence[dict]] = None,
+                 optimizer: str = "sgd", betas=(0.9, 0.999), eps: float = 1e-8):
         """``param_groups`` (hybrid parallelism): a list of ``{"params": [...], "comm": Comm, "scale": float}``;
         every group gets its own buckets, reduced over its own communicator (sum times ``scale``).  All
         groups share this rank's one daemon, so ranks may submit them in any order."""
@@ -85,6 +87,10 @@ class DaemonDDP:
         self.world = self.comm.nranks
         self.device = dist.device
         self.lr, self.mu, self.wd = lr, momentum, weight_decay
+        if optimizer not in ("sgd", "adamw"):
+            raise ValueError("optimizer must be 'sgd' or 'adamw'")
+        self.optimizer, self.betas, self.eps = optimizer, (float(betas[0]), float(betas[1])), float(eps)
+        self._t = 0                              # optimizer steps taken (AdamW bias correction)
         self.randomize = randomize_order
         self.window = max(1, window)
         self._rng = random.Random(seed * 7919 + dist.rank)
@@ -148,6 +154,7 @@ class DaemonDDP:
                     p.grad = _view_like(b.grad, off, p)
             b.master = b.flat_param.float().clone()
             b.momentum = torch.zeros_like(b.master)
+            b.moment2 = torch.zeros_like(b.master) if self.optimizer == "adamw" else None
             b.pending = len(b.params)
 
     def _make_hook(self, b: Bucket):
@@ -200,17 +207,33 @@ class DaemonDDP:
             b.pending = len(b.params)
 
     def step(self, lr: Optional[float] = None) -> None:
-        """Fused SGD with momentum over every flat bucket, then clear the gradients."""
+        """One fused optimizer kernel per flat bucket (SGD with momentum, or AdamW), then clear the gradients."""
         lr = self.lr if lr is None else lr
         s = self._stream()
+        self._t += 1
+        b1, b2 = self.betas
         for b in self.buckets:
             if self.device.type == "cuda":
-                nv.check(self._lib.dfcclFusedSgdStep(
-                    C.c_void_p(b.master.data_ptr()), C.c_void_p(b.grad32.data_ptr()), C.c_void_p(b.momentum.data_ptr()),
-                    C.c_void_p(b.flat_param.data_ptr()), b.numel, nccl_dtype(b.dtype), lr, self.mu, self.wd,
-                    1 if self._first_step else 0, C.c_void_p(s)), "dfcclFusedSgdStep")
+                if self.optimizer == "adamw":
+                    nv.check(self._lib.dfcclFusedAdamWStep(
+                        C.c_void_p(b.master.data_ptr()), C.c_void_p(b.grad32.data_ptr()), C.c_void_p(b.momentum.data_ptr()),
+                        C.c_void_p(b.moment2.data_ptr()), C.c_void_p(b.flat_param.data_ptr()), b.numel, nccl_dtype(b.dtype),
+                        lr, b1, b2, self.eps, self.wd, self._t, C.c_void_p(s)), "dfcclFusedAdamWStep")
+                else:
+                    nv.check(self._lib.dfcclFusedSgdStep(
+                        C.c_void_p(b.master.data_ptr()), C.c_void_p(b.grad32.data_ptr()), C.c_void_p(b.momentum.data_ptr()),
+                        C.c_void_p(b.flat_param.data_ptr()), b.numel, nccl_dtype(b.dtype), lr, self.mu, self.wd,
+                        1 if self._first_step else 0, C.c_void_p(s)), "dfcclFusedSgdStep")
                 self.launches += 1
-            else:                                  # host backend (tests): the same arithmetic in PyTorch
+            elif self.optimizer == "adamw":        # host backend (tests): the same arithmetic in PyTorch
+                g = b.grad32
+                b.momentum.mul_(b1).add_(g, alpha=1 - b1)
+                b.moment2.mul_(b2).addcmul_(g, g, value=1 - b2)
+                step_size = lr / (1 - b1 ** self._t)
+                denom = b.moment2.sqrt() / (1 - b2 ** self._t) ** 0.5 + self.eps
+                b.master.mul_(1 - lr * self.wd).addcdiv_(b.momentum, denom, value=-step_size)
+                b.flat_param.copy_(b.master)
+            else:
                 g = b.grad32 + self.wd * b.master
                 b.momentum.mul_(0.0 if self._first_step else self.mu).add_(g)
                 b.master.sub_(lr * b.momentum)
@@ -226,20 +249,27 @@ class DaemonDDP:
         """Optimizer state of this rank (fp32 master weights and momentum per bucket), for ``torch.save``.  The
         bucket layout is a function of the module and the bucket size, so a wrapper built the same way loads it."""
         return {"first_step": self._first_step, "lr": self.lr, "momentum": self.mu, "weight_decay": self.wd,
+                "optimizer": self.optimizer, "t": self._t,
                 "buckets": [{"numel": b.numel, "dtype": str(b.dtype), "master": b.master.detach().cpu().clone(),
-                             "momentum": b.momentum.detach().cpu().clone()} for b in self.buckets]}
+                             "momentum": b.momentum.detach().cpu().clone(),
+                             "moment2": None if b.moment2 is None else b.moment2.detach().cpu().clone()} for b in self.buckets]}
 
     def load_state_dict(self, state: Dict[str, object]) -> None:
         bs = state["buckets"]
+        if state.get("optimizer", "sgd") != self.optimizer:
+            raise ValueError("checkpoint was written by another optimizer")
         if len(bs) != len(self.buckets) or any(x["numel"] != b.numel or x["dtype"] != str(b.dtype) for x, b in zip(bs, self.buckets)):
             raise ValueError("checkpoint was written with another bucket layout (module or bucket size differ)")
         with torch.no_grad():
             for x, b in zip(bs, self.buckets):
                 b.master.copy_(x["master"])
                 b.momentum.copy_(x["momentum"])
+                if b.moment2 is not None:
+                    b.moment2.copy_(x["moment2"])
                 b.flat_param.copy_(b.master)          # the module's parameters are views of the flat array
                 b.grad.zero_()
         self._first_step = bool(state["first_step"])
+        self._t = int(state.get("t", 0))
         self.lr, self.mu, self.wd = float(state["lr"]), float(state["momentum"]), float(state["weight_decay"])
 
     def close(self) -> None:

@@ -162,3 +162,40 @@ def test_checkpoint_resume_continues_the_same_trajectory(host_backend, tmp_path)
     resumed, _ = run([2, 3], state=path)
     for a, b in zip(full, resumed):
         torch.testing.assert_close(a, b, rtol=0, atol=0)
+
+
+def test_adamw_matches_torch_optim(host_backend):
+    """AdamW over the flat buckets (host arithmetic of the fused kernel) against torch.optim.AdamW, two ranks."""
+    nv = host_backend
+    from dfccl_b200.parallel import DaemonDDP, Dist
+    world, steps = 2, 4
+    comms = nv.Comm.init_loopback(world)
+    xs = [[torch.randn(16, 32, generator=torch.Generator().manual_seed(10 * s + r)) for r in range(world)] for s in range(steps)]
+    ys = [[torch.randn(16, 8, generator=torch.Generator().manual_seed(99 + 10 * s + r)) for r in range(world)] for s in range(steps)]
+    ref = _mlp()
+    opt = torch.optim.AdamW(ref.parameters(), lr=1e-2, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1)
+    for s in range(steps):
+        opt.zero_grad()
+        for r in range(world):
+            (nn.functional.mse_loss(ref(xs[s][r]), ys[s][r]) / world).backward()
+        opt.step()
+    finals = {}
+    nets = [_mlp() for _ in range(world)]
+
+    def body(r):
+        d = Dist(r, world, 0, torch.device("cpu"), comms[r], False)
+        ddp = DaemonDDP(nets[r], d, bucket_mb=0.004, lr=1e-2, weight_decay=0.1, optimizer="adamw", betas=(0.9, 0.95), eps=1e-8)
+        for s in range(steps):
+            nn.functional.mse_loss(nets[r](xs[s][r]), ys[s][r]).backward()
+            ddp.finish_backward()
+            assert ddp.ctx.wait_all(30000) == nv.SUCCESS
+            ddp.step()
+        finals[r] = [p.detach().clone() for p in nets[r].parameters()]
+        ddp.close()
+
+    run_ranks(world, body)
+    for c in comms:
+        c.destroy()
+    for r in range(world):
+        for got, exp in zip(finals[r], ref.parameters()):
+            torch.testing.assert_close(got, exp.detach(), rtol=1e-4, atol=1e-6)

@@ -286,3 +286,47 @@ def test_stream_ordered_submit_and_wait(nv):
     assert st["sqesSubmitted"] == 5
     ctx.destroy()
     c.destroy()
+
+
+@pytest.mark.parametrize("ptype", ["BFLOAT16", "FLOAT32"])
+@pytest.mark.parametrize("n", [4096, 1000003])
+def test_fused_optimizer_kernels_match_pytorch(nv, ptype, n):
+    """dfcclFusedSgdStep and dfcclFusedAdamWStep against the same updates written in PyTorch fp32."""
+    import ctypes as C
+    torch.cuda.set_device(0)
+    L = nv.lib()
+    pt = TORCH_OF[ptype]
+    g = torch.Generator(device="cuda").manual_seed(3)
+    st = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+    def ptr(t):
+        return C.c_void_p(t.data_ptr())
+
+    # SGD with momentum and weight decay, two steps (the first one initialises the momentum)
+    w = torch.randn(n, device="cuda", generator=g)
+    m = torch.empty(n, device="cuda")
+    p = torch.empty(n, device="cuda", dtype=pt)
+    rw, rm = w.clone(), torch.zeros(n, device="cuda")
+    for step in range(2):
+        grad = torch.randn(n, device="cuda", generator=g)
+        nv.check(L.dfcclFusedSgdStep(ptr(w), ptr(grad), ptr(m), ptr(p), n, getattr(nv, ptype), 0.1, 0.9, 1e-2, 1 if step == 0 else 0, st))
+        gg = grad + 1e-2 * rw
+        rm = gg if step == 0 else 0.9 * rm + gg
+        rw = rw - 0.1 * rm
+        torch.cuda.synchronize()
+        torch.testing.assert_close(w, rw, rtol=1e-5, atol=1e-6)
+        torch.testing.assert_close(p.float(), rw.to(pt).float(), rtol=0, atol=0)
+    # AdamW, three steps
+    w = torch.randn(n, device="cuda", generator=g)
+    m1, m2 = torch.zeros(n, device="cuda"), torch.zeros(n, device="cuda")
+    rw, r1, r2 = w.clone(), torch.zeros(n, device="cuda"), torch.zeros(n, device="cuda")
+    lr, b1, b2, eps, wd = 1e-2, 0.9, 0.95, 1e-8, 0.1
+    for t in range(1, 4):
+        grad = torch.randn(n, device="cuda", generator=g)
+        nv.check(L.dfcclFusedAdamWStep(ptr(w), ptr(grad), ptr(m1), ptr(m2), ptr(p), n, getattr(nv, ptype), lr, b1, b2, eps, wd, t, st))
+        r1 = b1 * r1 + (1 - b1) * grad
+        r2 = b2 * r2 + (1 - b2) * grad * grad
+        rw = rw * (1 - lr * wd) - (lr / (1 - b1 ** t)) * r1 / (r2.sqrt() / (1 - b2 ** t) ** 0.5 + eps)
+        torch.cuda.synchronize()
+        torch.testing.assert_close(w, rw, rtol=2e-5, atol=1e-6)
+        torch.testing.assert_close(p.float(), w.to(pt).float(), rtol=0, atol=0)
