@@ -315,7 +315,7 @@ def test_fused_optimizer_kernels_match_pytorch(nv, ptype, n):
         rw = rw - 0.1 * rm
         torch.cuda.synchronize()
         torch.testing.assert_close(w, rw, rtol=1e-5, atol=1e-6)
-        torch.testing.assert_close(p.float(), rw.to(pt).float(), rtol=0, atol=0)
+        torch.testing.assert_close(p.float(), w.to(pt).float(), rtol=0, atol=0)
     # AdamW, three steps
     w = torch.randn(n, device="cuda", generator=g)
     m1, m2 = torch.zeros(n, device="cuda"), torch.zeros(n, device="cuda")
