@@ -106,6 +106,7 @@ def main(argv=None):
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--model", default="medium", choices=["medium", "tiny"])
     ap.add_argument("--impl", default="dfccl", choices=["dfccl", "nccl"])
+    ap.add_argument("--optimizer", default="sgd", choices=["sgd", "adamw"], help="fused optimizer of this library's arm")
     ap.add_argument("--graph", type=int, default=0, help="capture forward + backward of the whole step in one CUDA graph")
     ap.add_argument("--out", default="")
     a = ap.parse_args(argv)
@@ -119,7 +120,7 @@ def main(argv=None):
     mesh = build_mesh(d, a.tp, a.pp, a.dp)
     mesh.tp_group.library = "dfccl" if a.impl == "dfccl" else "torch"
     stage = GPT2Stage(cfg, mesh.tp_group, mesh.pp_rank, a.pp, a.micro_batch)
-    tr = HybridTrainer(d, mesh, stage, n_micro=a.n_micro, lr=0.01, seed=5, use_graph=bool(a.graph))
+    tr = HybridTrainer(d, mesh, stage, n_micro=a.n_micro, lr=0.01 if a.optimizer == "sgd" else 3e-4, seed=5, use_graph=bool(a.graph), optimizer=a.optimizer)
     if a.impl == "nccl":
         tr.ddp.close()
         params = [p for p in stage.parameters()]

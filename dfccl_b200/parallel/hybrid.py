@@ -71,7 +71,8 @@ class HybridTrainer:
     """One optimizer step = ``n_micro`` micro-batches of ``micro_batch`` sequences per replica."""
 
     def __init__(self, d: Dist, mesh: Mesh, stage: torch.nn.Module, *, n_micro: int, bucket_mb: float = 25.0, lr: float = 0.01,
-                 momentum: float = 0.9, weight_decay: float = 0.0, seed: int = 0, daemon_blocks: int = 8, use_graph: bool = False):
+                 momentum: float = 0.9, weight_decay: float = 0.0, seed: int = 0, daemon_blocks: int = 8, use_graph: bool = False,
+                 optimizer: str = "sgd"):
         self.d, self.mesh, self.stage, self.n_micro = d, mesh, stage, n_micro
         params = [p for p in stage.parameters() if p.requires_grad]
         sharded = [p for p in params if not getattr(p, "tp_replicated", False)]
@@ -79,7 +80,7 @@ class HybridTrainer:
         groups = [{"params": sharded, "comm": mesh.dp_comm, "scale": 1.0 / mesh.dp},
                   {"params": replicated, "comm": mesh.stage_comm, "scale": 1.0 / mesh.dp}]
         self.ddp = DaemonDDP(stage, d, bucket_mb=bucket_mb, lr=lr, momentum=momentum, weight_decay=weight_decay,
-                             randomize_order=True, seed=seed, param_groups=groups, daemon_blocks=daemon_blocks)
+                             randomize_order=True, seed=seed, param_groups=groups, daemon_blocks=daemon_blocks, optimizer=optimizer)
         self.ddp.hooks_enabled = False
         if d.device.type == "cuda":
             # the fused GEMM launches need all their CTAs resident together: keep them off the SMs a daemon
@@ -228,7 +229,8 @@ class HybridTrainer:
     """One optimizer step = ``n_micro`` micro-batches of ``micro_batch`` sequences per replica."""
 
     def __init__(self, d: Dist, mesh: Mesh, stage: torch.nn.Module, *, n_micro: int, bucket_mb: float = 25.0, lr: float = 0.01,
-                 momentum: float = 0.9, weight_decay: float = 0.0, seed: int = 0, daemon_blocks: int = 8, use_graph: bool = False):
+                 momentum: float = 0.9, weight_decay: float = 0.0, seed: int = 0, daemon_blocks: int = 8, use_graph: bool = False,
+                 optimizer: str = "sgd"):
         self.d, self.mesh, self.stage, self.n_micro = d, mesh, stage, n_micro
         params = [p for p in stage.parameters() if p.requires_grad]
         sharded = [p for p in params if not getattr(p, "tp_replicated", False)]
@@ -236,7 +238,7 @@ class HybridTrainer:
         groups = [{"params": sharded, "comm": mesh.dp_comm, "scale": 1.0 / mesh.dp},
                   {"params": replicated, "comm": mesh.stage_comm, "scale": 1.0 / mesh.dp}]
         self.ddp = DaemonDDP(stage, d, bucket_mb=bucket_mb, lr=lr, momentum=momentum, weight_decay=weight_decay,
-                             randomize_order=True, seed=seed, param_groups=groups, daemon_blocks=daemon_blocks)
+                             randomize_order=True, seed=seed, param_groups=groups, daemon_blocks=daemon_blocks, optimizer=optimizer)
         self.ddp.hooks_enabled = False
         if d.device.type == "cuda":
             # the fused GEMM launches need all their CTAs resident together: keep them off the SMs a daemon
@@ -315,6 +317,13 @@ class HybridTrainer:
             self._step_done = torch.cuda.Event()
             self._step_done.record()
         return self._loss
+
+    def state_dict(self):
+        """This rank's optimizer state (its shard of the weights in fp32 plus the moments)."""
+        return self.ddp.state_dict()
+
+    def load_state_dict(self, state) -> None:
+        self.ddp.load_state_dict(state)
 
     def close(self) -> None:
         self.ddp.close()
