@@ -162,6 +162,13 @@ def scenario_stream(nv, comm, rank, world, backend):
 def launch(world, backend, scenario, timeout=240):
     """Spawn `world` ranks, return their results; raises on any failure or timeout."""
     import multiprocessing as mp
+    import socket
+    # a fresh rendezvous port for whatever the scenario sets up with torch.distributed: a fixed one can still be
+    # in TIME_WAIT from the previous run of the same test
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        os.environ["MASTER_PORT"] = str(s.getsockname()[1])
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
     ctx = mp.get_context("spawn")
     uid_q, res_q = ctx.Queue(), ctx.Queue()
     procs = [ctx.Process(target=worker, args=(r, world, backend, uid_q, res_q, scenario), daemon=True) for r in range(world)]
