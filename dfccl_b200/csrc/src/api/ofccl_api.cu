@@ -277,12 +277,16 @@ DF_API ncclResult_t ofcclFinalizeRankCtx7StartHostThrds(ofcclRankCtx_t ctx) {
     const size_t bytes = e.info.count * (size_t)dtypeSize(e.info.inType);
     bool nv = nvlsEligible(e.comm, e.cs.kind, e.cs.inType, e.cs.outType, e.cs.op, e.cs.postDiv, e.cs.count);
     TunerChoice ch = tunerChoose(*topo, e.info.kind, bytes, e.comm->nranks, ctx->nBlocks, nv, e.info.algo, e.info.nBlocks);
+    // reduce-scatter and all-gather take the multimem schedule only when it is pinned at registration
+    if (e.info.algo == dfcclAlgoNvls && nvlsEligibleRsAg(e.comm, e.cs.kind, e.cs.inType, e.cs.outType, e.cs.op, e.cs.postDiv, e.cs.count)) ch.algo = dfcclAlgoNvls;
     if (ch.algo == dfcclAlgoNvls) {
-      // staging slots in the arena; every member walks its collectives in id order, so the offsets agree
+      // staging slots in the arena; every member walks its collectives in id order, so the offsets agree.
+      // (the output of a reduce-scatter and the input of an all-gather are local to the rank and need no slot)
       NvlsArena* a = e.comm->nvls;
-      const size_t inB = bytes, outB = e.info.count * (size_t)dtypeSize(e.info.outType);
+      const size_t inB = e.cs.kind == dfcclCollAllGather ? 0 : sendBytes(&e.cs);
+      const size_t outB = e.cs.kind == dfcclCollReduceScatter ? 0 : recvBytes(&e.cs);
       uint64_t in = 0, out = 0;
-      if (a->alloc(inB, &in) == ncclSuccess && a->alloc(outB, &out) == ncclSuccess) {
+      if ((inB == 0 || a->alloc(inB, &in) == ncclSuccess) && (outB == 0 || a->alloc(outB, &out) == ncclSuccess)) {
         e.cs.mcHeap = a->mc; e.cs.nvlsPeers = a->peersDev; e.cs.nvlsIn = in; e.cs.nvlsOut = out;
         e.cs.stagingSendOff = (uint64_t)(a->uc + in - e.comm->heap->base());
         e.cs.stagingRecvOff = (uint64_t)(a->uc + out - e.comm->heap->base());
@@ -541,8 +545,10 @@ static ncclResult_t submit(ofcclRankCtx* ctx, const void* send, void* recv, int 
       if (heap->contains(recv, rB)) q.recv = heap->offsetOf(recv); else { q.flags |= SQE_RECV_STAGED; q.recv = (uint64_t)(uintptr_t)recv; }
     } else if (viaArena) {          // in place when the buffer lives in the arena, else through this collective's slots
       NvlsArena* a = e.comm->nvls;
-      if (a->contains(send, sB)) q.send = (uint64_t)((const char*)send - a->uc); else { q.flags |= SQE_SEND_STAGED; q.send = (uint64_t)(uintptr_t)send; }
-      if (a->contains(recv, rB)) q.recv = (uint64_t)((char*)recv - a->uc); else { q.flags |= SQE_RECV_STAGED; q.recv = (uint64_t)(uintptr_t)recv; }
+      if (rawSend(&cs)) { if (heap->contains(send, sB)) q.send = heap->offsetOf(send); else { q.flags |= SQE_SEND_STAGED; q.send = (uint64_t)(uintptr_t)send; } }
+      else if (a->contains(send, sB)) q.send = (uint64_t)((const char*)send - a->uc); else { q.flags |= SQE_SEND_STAGED; q.send = (uint64_t)(uintptr_t)send; }
+      if (rawRecv(&cs)) { if (heap->contains(recv, rB)) q.recv = heap->offsetOf(recv); else { q.flags |= SQE_RECV_STAGED; q.recv = (uint64_t)(uintptr_t)recv; } }
+      else if (a->contains(recv, rB)) q.recv = (uint64_t)((char*)recv - a->uc); else { q.flags |= SQE_RECV_STAGED; q.recv = (uint64_t)(uintptr_t)recv; }
     }
     bool stageSend = !viaArena && needSend && !heap->contains(send, sB);
     if (needSend && cs.kind == dfcclCollAllReduce && cs.algo == dfcclAlgoOneShot && send == recv && cs.nranks > 1) stageSend = true;
@@ -824,7 +830,10 @@ static void releaseHeapParts(ofcclRankCtx* ctx) {
   // arena slots were taken in ascending id order; giving them back in descending order unwinds the bump allocator
   for (auto it = ctx->colls.rbegin(); it != ctx->colls.rend(); ++it) {
     CollEntry& e = it->second;
-    if (e.cs.algo == dfcclAlgoNvls && e.comm && e.comm->nvls) { e.comm->nvls->release(e.cs.nvlsOut); e.comm->nvls->release(e.cs.nvlsIn); }
+    if (e.cs.algo == dfcclAlgoNvls && e.comm && e.comm->nvls) {
+      if (e.cs.kind != dfcclCollReduceScatter) e.comm->nvls->release(e.cs.nvlsOut);
+      if (e.cs.kind != dfcclCollAllGather) e.comm->nvls->release(e.cs.nvlsIn);
+    }
   }
   for (auto& kv : ctx->colls) {
     CollEntry& e = kv.second;

@@ -193,6 +193,12 @@ bool nvlsEligible(const ncclComm* c, int kind, int inType, int outType, int devO
          (count * (size_t)dtypeSize(inType)) % 16 == 0;
 }
 
+bool nvlsEligibleRsAg(const ncclComm* c, int kind, int inType, int outType, int devOp, int postDiv, size_t count) {
+  if (!c->nvls || c->nranks < 2 || (count * (size_t)dtypeSize(inType)) % 16 != 0) return false;
+  if (kind == dfcclCollAllGather) return true;
+  return kind == dfcclCollReduceScatter && devOp == OP_SUM && postDiv == 0 && nvlsTypesOk(inType, outType);
+}
+
 static ncclResult_t ensureScratch(ncclComm* c, int which, size_t bytes, cudaStream_t stream) {
   if (c->scratchBytes[which] >= bytes) return ncclSuccess;
   if (c->backend == dfcclBackendCuda) {      // growing needs a device synchronisation: impossible inside a capture

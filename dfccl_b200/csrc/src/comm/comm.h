@@ -97,6 +97,9 @@ bool nvlsEligible(const ncclComm* comm, int kind, int inType, int outType, int d
 // `stream` (cuda backend) is drained first; the call returns when the result is in `recv`.
 ncclResult_t netStagedCollective(ncclComm* comm, NetRing* ring, const NetCollDesc& d, const void* send, void* recv, cudaStream_t stream);
 
+// Reduce-scatter (sum; f32 / bf16 / f16) and all-gather on the multimem schedule: only when pinned at registration.
+bool nvlsEligibleRsAg(const ncclComm* comm, int kind, int inType, int outType, int devOp, int postDiv, size_t count);
+
 // The engine behind the stream-ordered entry points.
 ncclResult_t commCollective(ncclComm* comm, int kind, const void* send, void* recv, size_t count, ncclDataType_t type,
                             ncclRedOp_t op, int root, cudaStream_t stream);

@@ -209,6 +209,12 @@ DF_HD char* recvPtrOf(const BlockShared* sh, int b, int j) {
   return c->peerHeap[j] + off;
 }
 
+// Schedules in which a user buffer is touched by this rank only use it where it is (no staging copy even when it
+// lies outside the symmetric heap): both buffers of the push schedule, the input of a multimem all-gather, the
+// output of a multimem reduce-scatter.
+DF_HD bool rawSend(const CollStatic* c) { return c->algo == dfcclAlgoPush || (c->algo == dfcclAlgoNvls && c->kind == dfcclCollAllGather); }
+DF_HD bool rawRecv(const CollStatic* c) { return c->algo == dfcclAlgoPush || (c->algo == dfcclAlgoNvls && c->kind == dfcclCollReduceScatter); }
+
 // Push schedule: the user's buffers are only touched by this rank, so they are used where they are.
 DF_HD const char* pushSendPtr(const BlockShared* sh) {
   return (sh->dyn.sqeFlags & SQE_SEND_STAGED) ? (const char*)(uintptr_t)sh->dyn.send : sh->cs.peerHeap[sh->cs.rank] + sh->dyn.send;
@@ -245,6 +251,7 @@ DF_HD void dataPhase(BlockShared* sh, RankDev* rd, int b) {
   const int n = c->nranks, me = c->rank;
   const uint64_t es = dtypeSize(c->inType), eo = dtypeSize(c->outType);
   bool reduce = true, nvls = false;
+  int nvlsKind = 0;          // 3 = reduce-scatter, 4 = all-gather on the multimem schedule
   if (df_tid() == 0) {
     DataArgs* a = &sh->args;
     a->scale = c->scale; a->postDiv = c->postDiv; a->nsrc = 0; a->ndst = 0; a->n = 0;
@@ -295,6 +302,15 @@ DF_HD void dataPhase(BlockShared* sh, RankDev* rd, int b) {
       }
       case dfcclCollReduceScatter: {
         partRange(c->count, c->nBlocks, b, 16, &bb, &be);
+        if (c->algo == dfcclAlgoNvls && n > 1) {
+          // the switch reduces my block of every member's input (arena); the result stays here
+          const uint64_t in = (sh->dyn.sqeFlags & SQE_SEND_STAGED) ? c->nvlsIn : sh->dyn.send;
+          a->src[0] = (const char*)(uintptr_t)(in + ((uint64_t)me * c->count + bb) * es); a->nsrc = 1;
+          a->dst[0] = pushRecvPtr(sh) + bb * eo; a->ndst = 1;
+          a->n = be - bb;
+          nvlsKind = 3;
+          break;
+        }
         for (int k = 0; k < n; ++k) { int j = (me + k) % n; a->src[a->nsrc++] = sendPtrOf(sh, b, j) + ((uint64_t)me * c->count + bb) * es; }
         a->dst[a->ndst++] = recvPtrOf(sh, b, me) + bb * eo;
         a->n = be - bb;
@@ -304,6 +320,15 @@ DF_HD void dataPhase(BlockShared* sh, RankDev* rd, int b) {
         reduce = false;
         uint64_t bytes = c->count * es;
         partRange(bytes, c->nBlocks, b, 16, &bb, &be);
+        if (c->algo == dfcclAlgoNvls && n > 1) {
+          // one multicast store puts my piece into every member's output (arena)
+          const uint64_t out = (sh->dyn.sqeFlags & SQE_RECV_STAGED) ? c->nvlsOut : sh->dyn.recv;
+          a->src[0] = pushSendPtr(sh) + bb; a->nsrc = 1;
+          a->dst[0] = (char*)(uintptr_t)(out + (uint64_t)me * bytes + bb); a->ndst = 1;
+          a->n = be - bb;
+          nvlsKind = 4;
+          break;
+        }
         a->src[0] = sendPtrOf(sh, b, me) + bb; a->nsrc = 1;
         for (int k = 0; k < n; ++k) {
           int j = (me + k) % n;
@@ -325,7 +350,7 @@ DF_HD void dataPhase(BlockShared* sh, RankDev* rd, int b) {
       }
       default: break;
     }
-    sh->ctl1 = nvls ? 2 : reduce ? 1 : 0;
+    sh->ctl1 = nvlsKind ? nvlsKind : nvls ? 2 : reduce ? 1 : 0;
     if (reduce) sh->stats.bytesReduced += a->n * es * a->nsrc; else sh->stats.bytesCopied += a->n * (a->ndst ? a->ndst : 0);
   }
   df_sync();
@@ -337,6 +362,11 @@ DF_HD void dataPhase(BlockShared* sh, RankDev* rd, int b) {
     if (sh->ctl1 == 2) {
       if (!nvlsDispatch(c->inType, c->outType, c->mcHeap, c->nvlsPeers, n, (uint64_t)(uintptr_t)sh->args.src[0],
                         (uint64_t)(uintptr_t)sh->args.dst[0], sh->args.n, (float)c->scale) && df_tid() == 0) sh->dyn.status = ST_BAD_ARG;
+    } else if (sh->ctl1 == 3) {
+      if (!nvlsDispatchToLocal(c->inType, c->outType, c->mcHeap, c->nvlsPeers, n, (uint64_t)(uintptr_t)sh->args.src[0], sh->args.dst[0],
+                               sh->args.n, (float)c->scale) && df_tid() == 0) sh->dyn.status = ST_BAD_ARG;
+    } else if (sh->ctl1 == 4) {
+      nvlsBroadcastBytes(c->mcHeap, c->nvlsPeers, n, sh->args.src[0], (uint64_t)(uintptr_t)sh->args.dst[0], sh->args.n);
     } else if (sh->ctl1) {
       if (!reduce_dispatch(c->inType, c->outType, c->op, &sh->args) && df_tid() == 0) sh->dyn.status = ST_BAD_ARG;
     } else {
@@ -429,7 +459,7 @@ DF_HD int runColl(BlockShared* sh, RankDev* rd, int b, int coll, uint32_t budget
         setPhase(sh, PH_COPY_IN);
         break;
       case PH_COPY_IN:
-        if ((sh->dyn.sqeFlags & SQE_SEND_STAGED) && sh->cs.algo != dfcclAlgoPush) {
+        if ((sh->dyn.sqeFlags & SQE_SEND_STAGED) && !rawSend(&sh->cs)) {
           bool needed = !(sh->cs.kind == dfcclCollBroadcast && me != sh->cs.root);
           if (needed) stageCopy(sh, b, true);
           if (tid == 0) fence_sys();
@@ -486,7 +516,7 @@ DF_HD int runColl(BlockShared* sh, RankDev* rd, int b, int coll, uint32_t budget
         setPhase(sh, PH_COPY_OUT);
         break;
       case PH_COPY_OUT:
-        if ((sh->dyn.sqeFlags & SQE_RECV_STAGED) && sh->cs.algo != dfcclAlgoPush) {
+        if ((sh->dyn.sqeFlags & SQE_RECV_STAGED) && !rawRecv(&sh->cs)) {
           bool needed = !(sh->cs.kind == dfcclCollReduce && me != sh->cs.root);
           if (needed) stageCopy(sh, b, false);
         }

@@ -1,4 +1,4 @@
-// NVLS all-reduce body: every rank owns a slice; it reads the slice reduced over all members with
+// NVLS bodies.  All-reduce: every rank owns a slice; it reads the slice reduced over all members with
 // multimem.ld_reduce (the NVLink switch adds the members' copies on the way), applies the scale and
 // the output cast, and writes the result to all members with multimem.st.  Sum only, on f32, bf16
 // and f16 inputs (bf16 / f16 accumulate in fp32 inside the switch); the output may be fp32.
@@ -99,6 +99,32 @@ DF_HD void nvlsSlice(char* mc, char* const* peers, int n, uint64_t inOff, uint64
   }
 }
 
+// Reduce-scatter form: the reduced slice is kept locally (plain 16-byte stores to `dst`) instead of being broadcast.
+template <typename Tin, typename Tout>
+DF_HD void nvlsSliceToLocal(char* mc, char* const* peers, int n, uint64_t inOff, char* dst, uint64_t nElems, float scale) {
+  constexpr int V = 16 / (int)sizeof(Tin);
+  constexpr int W = (int)(sizeof(Tout) / sizeof(Tin));
+  const uint64_t packs = nElems / V;
+  const bool plain = scale == 1.0f && W == 1;
+  for (uint64_t p = (uint64_t)df_tid(); p < packs; p += (uint64_t)df_nthreads()) {
+    const uint4 v = nvlsLoad<Tin>(mc, peers, n, inOff + p * 16);
+    if (plain) { st16(dst + p * 16, v); continue; }
+    uint4 o[W];
+#pragma unroll
+    for (int w = 0; w < W; ++w) o[w] = make_uint4(0, 0, 0, 0);
+#pragma unroll
+    for (int k = 0; k < V; ++k) Lane<Tout>::put(o[k / (V / W)], k % (V / W), (float)Lane<Tin>::get(v, k) * scale);
+#pragma unroll
+    for (int w = 0; w < W; ++w) st16(dst + (p * W + w) * 16, o[w]);
+  }
+}
+
+// All-gather form: `bytes` (a multiple of 16) from local `src` to offset `outOff` of every member's arena.
+DF_HD void nvlsBroadcastBytes(char* mc, char* const* peers, int n, const char* src, uint64_t outOff, uint64_t bytes) {
+  const uint64_t packs = bytes / 16;
+  for (uint64_t p = (uint64_t)df_tid(); p < packs; p += (uint64_t)df_nthreads()) nvlsStore(mc, peers, n, outOff + p * 16, ld16(src + p * 16));
+}
+
 // Which (input, output) pairs the schedule exists for.
 DF_HD bool nvlsTypesOk(int inType, int outType) {
   if (inType == ncclFloat32) return outType == ncclFloat32;
@@ -112,6 +138,16 @@ DF_HD bool nvlsDispatch(int inType, int outType, char* mc, char* const* peers, i
   else if (inType == ncclBfloat16 && outType == ncclFloat32) nvlsSlice<__nv_bfloat16, float>(mc, peers, n, inOff, outOff, nElems, scale);
   else if (inType == ncclFloat16 && outType == ncclFloat16) nvlsSlice<__half, __half>(mc, peers, n, inOff, outOff, nElems, scale);
   else if (inType == ncclFloat16 && outType == ncclFloat32) nvlsSlice<__half, float>(mc, peers, n, inOff, outOff, nElems, scale);
+  else return false;
+  return true;
+}
+
+DF_HD bool nvlsDispatchToLocal(int inType, int outType, char* mc, char* const* peers, int n, uint64_t inOff, char* dst, uint64_t nElems, float scale) {
+  if (inType == ncclFloat32 && outType == ncclFloat32) nvlsSliceToLocal<float, float>(mc, peers, n, inOff, dst, nElems, scale);
+  else if (inType == ncclBfloat16 && outType == ncclBfloat16) nvlsSliceToLocal<__nv_bfloat16, __nv_bfloat16>(mc, peers, n, inOff, dst, nElems, scale);
+  else if (inType == ncclBfloat16 && outType == ncclFloat32) nvlsSliceToLocal<__nv_bfloat16, float>(mc, peers, n, inOff, dst, nElems, scale);
+  else if (inType == ncclFloat16 && outType == ncclFloat16) nvlsSliceToLocal<__half, __half>(mc, peers, n, inOff, dst, nElems, scale);
+  else if (inType == ncclFloat16 && outType == ncclFloat32) nvlsSliceToLocal<__half, float>(mc, peers, n, inOff, dst, nElems, scale);
   else return false;
   return true;
 }

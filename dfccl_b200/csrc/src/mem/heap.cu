@@ -3,7 +3,9 @@
 #include "../common/param.h"
 #include <atomic>
 #include <cstring>
+#include <dirent.h>
 #include <fcntl.h>
+#include <signal.h>
 #include <fstream>
 #include <sys/mman.h>
 #include <unistd.h>
@@ -27,6 +29,46 @@ uint64_t hostHash() {
 
 static std::atomic<int> g_heapSeq{0};
 
+// ---- shared-memory segments of the host backend outlive a process that is killed (or that never destroys its
+// process-wide heap).  Names carry the owner's pid, so (a) every live name of this process is unlinked at exit and
+// (b) the first heap of a process removes segments whose owner no longer exists - otherwise a recycled pid would
+// find "its" name taken.
+static std::mutex g_namesMu;
+static std::vector<std::string> g_liveNames;
+
+static void unlinkLiveNames() {
+  std::lock_guard<std::mutex> l(g_namesMu);
+  for (auto& n : g_liveNames) shm_unlink(n.c_str());
+  g_liveNames.clear();
+}
+static void rememberName(const std::string& n) {
+  static std::once_flag once;
+  std::call_once(once, [] { atexit(unlinkLiveNames); });
+  std::lock_guard<std::mutex> l(g_namesMu);
+  g_liveNames.push_back(n);
+}
+static void forgetName(const std::string& n) {
+  std::lock_guard<std::mutex> l(g_namesMu);
+  for (size_t i = 0; i < g_liveNames.size(); ++i) if (g_liveNames[i] == n) { g_liveNames[i] = g_liveNames.back(); g_liveNames.pop_back(); break; }
+}
+static void reapStaleSegments() {
+  static std::once_flag once;
+  std::call_once(once, [] {
+    DIR* d = opendir("/dev/shm");
+    if (!d) return;
+    int reaped = 0;
+    while (dirent* e = readdir(d)) {
+      int pid = 0, id = 0;
+      if (sscanf(e->d_name, "dfccl-%d-%d", &pid, &id) != 2 || pid <= 0) continue;
+      if (kill((pid_t)pid, 0) == 0 || errno != ESRCH) continue;      // owner alive (or not ours to judge)
+      std::string name = std::string("/") + e->d_name;
+      if (shm_unlink(name.c_str()) == 0) ++reaped;
+    }
+    closedir(d);
+    if (reaped) DF_INFO(SUB_ALLOC, "removed %d shared-memory segments of processes that no longer exist", reaped);
+  });
+}
+
 ncclResult_t Heap::create(dfcclBackend_t backend, int device, size_t bytes, Heap** out) {
   Heap* h = new Heap();
   h->backend_ = backend; h->device_ = device; h->heapId_ = g_heapSeq++;
@@ -48,7 +90,12 @@ ncclResult_t Heap::create(dfcclBackend_t backend, int device, size_t bytes, Heap
   } else {
     char name[64];
     snprintf(name, sizeof(name), "/dfccl-%d-%d", (int)getpid(), h->heapId_);
+    reapStaleSegments();
     int fd = shm_open(name, O_CREAT | O_RDWR | O_EXCL, 0600);
+    if (fd < 0 && errno == EEXIST) {          // a segment carrying my own pid can only be the leftover of a dead process
+      shm_unlink(name);
+      fd = shm_open(name, O_CREAT | O_RDWR | O_EXCL, 0600);
+    }
     if (fd < 0 || ftruncate(fd, (off_t)bytes) != 0) {
       DF_WARN("symmetric heap: shm_open/ftruncate(%s, %zu) failed: %s", name, bytes, strerror(errno));
       if (fd >= 0) { close(fd); shm_unlink(name); }
@@ -60,6 +107,7 @@ ncclResult_t Heap::create(dfcclBackend_t backend, int device, size_t bytes, Heap
     if (p == MAP_FAILED) { shm_unlink(name); delete h; return ncclSystemError; }
     h->base_ = (char*)p;
     h->shmName_ = name;
+    rememberName(h->shmName_);
   }
   h->free_[0] = bytes;
   DF_INFO(SUB_ALLOC, "symmetric heap %d: %zu MiB at %p (%s)", h->heapId_, bytes >> 20, (void*)h->base_,
@@ -76,7 +124,7 @@ Heap::~Heap() {
   }
   if (!base_) return;
   if (backend_ == dfcclBackendCuda) { cudaFree(base_); (void)cudaGetLastError(); }
-  else { munmap(base_, bytes_); shm_unlink(shmName_.c_str()); }
+  else { munmap(base_, bytes_); shm_unlink(shmName_.c_str()); forgetName(shmName_); }
 }
 
 ncclResult_t Heap::alloc(size_t bytes, uint64_t* off, bool zero) {

@@ -122,3 +122,63 @@ def test_arena_full_falls_back(host_backend):
     run_ranks(nranks, body)
     for c in comms:
         c.destroy()
+
+
+@pytest.mark.parametrize("kind", ["reducescatter", "allgather"])
+@pytest.mark.parametrize("where", ["arena", "heap", "user"])
+def test_daemon_reducescatter_allgather_nvls(host_backend, kind, where):
+    """The multimem forms of reduce-scatter (switch reduces, result stays local) and all-gather (one multicast store
+    per piece), pinned at registration; the member-side buffer (reduce-scatter output, all-gather input) is used
+    where it is, the shared side lives in the arena or is staged through the collective's slot."""
+    nv = host_backend
+    nranks, count, scale = 4, 12 * 1024, 0.5
+    rs = kind == "reducescatter"
+    dt, odt = (nv.BFLOAT16, nv.FLOAT32) if rs else (nv.FLOAT32, nv.FLOAT32)
+    comms = nv.Comm.init_loopback(nranks)
+    send_n = count * nranks if rs else count
+    recv_n = count if rs else count * nranks
+    ins = _inputs(nv, dt, send_n, nranks, 21)
+    got = {}
+
+    def body(r):
+        c = comms[r]
+        assert c.nvls_init(8 << 20)
+        ctx = nv.RankCtx(r)
+        ctx.prepare(5, c, nv.REDUCESCATTER if rs else nv.ALLGATHER, count, dt, out_dtype=odt, op=nv.SUM,
+                    scale=scale if rs else 1.0, algo=nv.ALGO_NVLS)
+        ctx.finalize()
+        es, eo = nv.DTYPE_SIZE[dt], nv.DTYPE_SIZE[odt]
+        keep = []
+
+        def buf(n, e, npdt, shared):
+            if where == "arena" and shared:
+                return c.nvls_alloc(n * e)
+            if where in ("arena", "heap"):
+                return c.alloc(n * e)
+            a = np.zeros(n, npdt)
+            keep.append(a)
+            return a.ctypes.data
+        sp = buf(send_n, es, np_dtype(nv, dt), shared=rs)          # the reduce-scatter input is what the switch reads
+        rp = buf(recv_n, eo, np_dtype(nv, odt), shared=not rs)     # the all-gather output is what the switch writes
+        sv, rv = host_array(sp, send_n, np_dtype(nv, dt)), host_array(rp, recv_n, np_dtype(nv, odt))
+        for it in range(3):
+            sv[:] = ins[r]
+            rv[:] = 0
+            ctx.run(5, sp, rp)
+            assert ctx.wait(5, 30000) == nv.SUCCESS
+        got[r] = rv.copy()
+        st = ctx.stats()
+        ctx.destroy()
+        assert st["waitTimeouts"] == 0
+
+    run_ranks(nranks, body)
+    for c in comms:
+        c.destroy()
+    if rs:
+        tot = sum(_f32(nv, dt, a).astype(np.float64) for a in ins) * scale
+        for r in range(nranks):
+            np.testing.assert_allclose(got[r], tot[r * count:(r + 1) * count], rtol=2e-2, atol=2e-2)
+    else:
+        exp = np.concatenate(ins)
+        for r in range(nranks):
+            np.testing.assert_array_equal(got[r], exp)
