@@ -363,3 +363,46 @@ def scenario_nvls(nv, comm, rank, world, backend):
     want = world * (world + 1) / 2
     assert float(x.min()) == want and float(x.max()) == want, (float(x.min()), float(x.max()), want)
     return out
+
+
+def scenario_nvls_rsag(nv, comm, rank, world, backend):
+    """Reduce-scatter and all-gather on the multimem schedule (pinned at registration), arena-resident shared side."""
+    arena = (24 << 20) if backend == "host" else (128 << 20)
+    if not comm.nvls_init(arena):
+        return {"available": False}
+    import torch
+    cuda = backend == "cuda"
+    dev = torch.device("cuda", rank) if cuda else torch.device("cpu")
+    from dfccl_b200.utils import tensor_from_ptr
+    count = 64 * 1024 if backend == "host" else 1024 * 1024
+    ctx = nv.RankCtx(rank, rank if cuda else -1)
+    ctx.prepare(1, comm, nv.REDUCESCATTER, count, nv.BFLOAT16, out_dtype=nv.FLOAT32, op=nv.SUM, scale=0.5, algo=nv.ALGO_NVLS)
+    ctx.prepare(2, comm, nv.ALLGATHER, count, nv.FLOAT32, algo=nv.ALGO_NVLS)
+    ctx.finalize()
+    g = torch.Generator().manual_seed(4)
+    full = (torch.rand(world, world * count, generator=g) * 2 - 1).to(torch.bfloat16)
+    sp = comm.nvls_alloc(world * count * 2)                       # what the switch reads: in the arena
+    s = tensor_from_ptr(sp, (world * count,), torch.bfloat16, dev)
+    r = torch.zeros(count, dtype=torch.float32, device=dev)      # the result stays local: an ordinary tensor
+    ref = 0.5 * full.float().sum(0)[rank * count:(rank + 1) * count]
+    for it in range(2):
+        s.copy_(full[rank])
+        r.zero_()
+        if cuda:
+            torch.cuda.synchronize()
+        ctx.run(1, sp, r.data_ptr())
+        assert ctx.wait(1, 30000) == nv.SUCCESS
+        err = (r.cpu() - ref).abs().max().item()
+        assert err < 3e-2, ("nvls reduce-scatter", it, err)
+    x = torch.full((count,), float(rank + 1), device=dev)         # local input: an ordinary tensor
+    op = comm.nvls_alloc(world * count * 4)                       # what the switch writes: in the arena
+    o = tensor_from_ptr(op, (world * count,), torch.float32, dev)
+    o.zero_()
+    if cuda:
+        torch.cuda.synchronize()
+    ctx.run(2, x.data_ptr(), op)
+    assert ctx.wait(2, 30000) == nv.SUCCESS
+    got = o.view(world, count).cpu()
+    assert all(float(got[j].min()) == j + 1 and float(got[j].max()) == j + 1 for j in range(world)), "nvls all-gather"
+    ctx.destroy()
+    return {"available": True}

@@ -70,3 +70,8 @@ def test_gpu_nvls_allreduce():
     res = mp_worker.launch(min(torch.cuda.device_count(), 4), "cuda", "nvls", timeout=300)
     if not all(r["available"] for r in res.values()):
         pytest.skip("no NVLink-switch multicast on this machine")
+
+
+def test_host_processes_nvls_reducescatter_allgather():
+    res = mp_worker.launch(2, "host", "nvls_rsag", timeout=200)
+    assert all(r["available"] for r in res.values())
