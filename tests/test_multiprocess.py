@@ -75,3 +75,12 @@ def test_gpu_nvls_allreduce():
 def test_host_processes_nvls_reducescatter_allgather():
     res = mp_worker.launch(2, "host", "nvls_rsag", timeout=200)
     assert all(r["available"] for r in res.values())
+
+
+@pytest.mark.gpu
+@pytest.mark.multigpu
+def test_gpu_nvls_reducescatter_allgather():
+    """multimem.ld_reduce into local memory (reduce-scatter) and multimem.st of the local piece (all-gather)."""
+    res = mp_worker.launch(2, "cuda", "nvls_rsag", timeout=200)
+    if not all(r["available"] for r in res.values()):
+        pytest.skip("no NVLink-switch multicast on this machine")
