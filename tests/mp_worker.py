@@ -406,3 +406,29 @@ def scenario_nvls_rsag(nv, comm, rank, world, backend):
     assert all(float(got[j].min()) == j + 1 and float(got[j].max()) == j + 1 for j in range(world)), "nvls all-gather"
     ctx.destroy()
     return {"available": True}
+
+
+def scenario_net_path(nv, comm, rank, world, backend):
+    """Network path (set DFCCL_FORCE_NET=1 before launching): the stream-ordered entry point and a registered
+    collective on buffers of the backend's memory (device tensors on the cuda backend: staged through the host)."""
+    import torch
+    cuda = backend == "cuda"
+    dev = torch.device("cuda", rank) if cuda else torch.device("cpu")
+    n = 100003
+    x = torch.full((n,), float(rank + 1), device=dev)
+    stream = torch.cuda.current_stream().cuda_stream if cuda else None
+    nv.check(nv.lib().ncclAllReduce(x.data_ptr(), x.data_ptr(), n, nv.FLOAT32, nv.SUM, comm.handle, stream))
+    want = world * (world + 1) / 2
+    assert float(x.min()) == want and float(x.max()) == want
+    ctx = nv.RankCtx(rank, rank if cuda else -1)
+    ctx.prepare(0, comm, nv.ALLREDUCE, n, nv.BFLOAT16, out_dtype=nv.FLOAT32, op=nv.SUM, scale=0.5)
+    ctx.finalize()
+    a = torch.full((n,), float(rank + 1), device=dev, dtype=torch.bfloat16)
+    b = torch.zeros(n, device=dev)
+    if cuda:
+        torch.cuda.synchronize()
+    ctx.run(0, a.data_ptr(), b.data_ptr())
+    assert ctx.wait(0, 60000) == nv.SUCCESS
+    assert float(b.min()) == 0.5 * want and float(b.max()) == 0.5 * want
+    ctx.destroy()
+    return {"ok": True}

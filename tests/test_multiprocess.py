@@ -84,3 +84,19 @@ def test_gpu_nvls_reducescatter_allgather():
     res = mp_worker.launch(2, "cuda", "nvls_rsag", timeout=200)
     if not all(r["available"] for r in res.values()):
         pytest.skip("no NVLink-switch multicast on this machine")
+
+
+def test_host_processes_network_path(monkeypatch):
+    """Ranks in separate processes forced through the network path (TCP rings, host-staged collectives)."""
+    monkeypatch.setenv("DFCCL_FORCE_NET", "1")
+    res = mp_worker.launch(3, "host", "net_path", timeout=200)
+    assert all(r["ok"] for r in res.values())
+
+
+@pytest.mark.gpu
+@pytest.mark.multigpu
+def test_gpu_network_path(monkeypatch):
+    """The same path on device buffers: operands staged through host memory around the TCP rings."""
+    monkeypatch.setenv("DFCCL_FORCE_NET", "1")
+    res = mp_worker.launch(2, "cuda", "net_path", timeout=200)
+    assert all(r["ok"] for r in res.values())
