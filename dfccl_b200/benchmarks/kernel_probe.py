@@ -5,6 +5,7 @@ profiler capture ends by itself.
 
     python -m dfccl_b200.benchmarks.kernel_probe --mbytes 256 --iters 3
     python -m dfccl_b200.benchmarks.kernel_probe --gemm 8192 8192 8192 --iters 20     # tcgen05 GEMM vs cuBLAS
+    python -m dfccl_b200.benchmarks.kernel_probe --stream-ops --iters 200             # stream <-> resident kernel round trip
 """
 from __future__ import annotations
 
@@ -49,15 +50,36 @@ def gemm_probe(mnk, iters):
     print(json.dumps(out))
 
 
+def stream_ops_probe(iters):
+    """Round trip stream -> resident kernel -> stream in its eight forms (see dfcclProbeStreamRoundTrip)."""
+    L = nv.lib()
+    names = {0: "memop_write+memop_wait", 1: "kernel_write+memop_wait", 2: "memop_write+kernel_wait", 3: "kernel_write+kernel_wait"}
+    ns = (C.c_uint64 * 8)()
+    if L.dfcclProbeMemoryOps(200, ns) == nv.SUCCESS:
+        names_ops = ("ld_host", "st_host", "st_host+fence_sys", "st_dev+fence_sys", "st_dev+fence_gpu", "fence_sys", "atomic_dev", "ld_dev")
+        print(json.dumps({"control_path_op_ns": dict(zip(names_ops, [int(v) for v in ns]))}))
+    for delay in (0, 10, 50):
+        out = {}
+        for mode in range(8):
+            us = C.c_double(0)
+            rc = L.dfcclProbeStreamRoundTrip(mode, iters, delay, C.byref(us))      # first call warms the kernels up
+            rc = L.dfcclProbeStreamRoundTrip(mode, iters, delay, C.byref(us))
+            out[names[mode & 3] + ("+host_mirror" if mode & 4 else "")] = round(us.value - delay, 2) if rc == nv.SUCCESS else f"error {rc}"
+        print(json.dumps({"answer_delay_us": delay, "stream_round_trip_minus_delay_us": out}))
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser()
     ap.add_argument("--mbytes", type=int, default=256)
     ap.add_argument("--iters", type=int, default=3)
     ap.add_argument("--gemm", type=int, nargs=3, metavar=("M", "N", "K"), help="time the plain tcgen05 GEMM of this size instead")
+    ap.add_argument("--stream-ops", action="store_true", help="time the stream <-> resident kernel round trip instead")
     a = ap.parse_args(argv)
     torch.cuda.set_device(0)
     nv.set_backend("cuda")
     L = nv.lib()
+    if a.stream_ops:
+        return stream_ops_probe(a.iters)
     if a.gemm:
         return gemm_probe(a.gemm, a.iters)
     (comm,) = nv.Comm.init_loopback(1, 0)

@@ -14,7 +14,8 @@
  *                the in-process CPU backend and loopback rank groups used by tests.
  *
  * Every p-prefixed profiling alias of the reference (pncclAllReduce, pofcclRun...)
- * is exported as well; see.
+ * is exported as well, so that a tool can interpose on the plain names
+ * (reference: PROFAPI in src/include/core.h:17-31).
  */
 #ifndef DFCCL_H_
 #define DFCCL_H_
@@ -236,6 +237,15 @@ ncclResult_t dfcclRun(const void* sendbuff, void* recvbuff, int collId, Callback
 ncclResult_t dfcclRunOnStream(const void* sendbuff, void* recvbuff, int collId, cudaStream_t stream,
                               CallbackFunc callback, void* callbackArgs, ofcclRankCtx_t rankCtx);
 ncclResult_t dfcclStreamWait(int collId, cudaStream_t stream, ofcclRankCtx_t rankCtx);
+/* The same in two steps, for steps that are captured in a CUDA graph.  dfcclRunDeferred publishes the submission
+ * (buffers, callback) without touching any stream; dfcclTriggerOnStream enqueues its release on `stream` as a
+ * one-thread kernel that counts the releases of `collId` on the device.  That kernel can be captured: every replay
+ * of the graph releases the next published submission of the id, at the point of the captured step where the
+ * collective's input is complete - a gradient bucket is reduced while the rest of the backward pass still runs.
+ * Each submission must be released exactly once; which of the two calls comes first does not matter. */
+ncclResult_t dfcclRunDeferred(const void* sendbuff, void* recvbuff, int collId, CallbackFunc callback,
+                              void* callbackArgs, ofcclRankCtx_t rankCtx);
+ncclResult_t dfcclTriggerOnStream(int collId, cudaStream_t stream, ofcclRankCtx_t rankCtx);
 /* By default dfcclStreamWait (outside a stream capture) launches an instance of the daemon before the wait and
  * keeps it resident until nothing is outstanding, so that a stream parked on a completion never depends on a
  * relaunch from a host thread - the safe choice for eager steps of thousands of launches, at the price of the
@@ -263,6 +273,9 @@ typedef struct {
   uint64_t sqFullRetries;
   uint64_t maxSwitchNs, totalSwitchNs;            /* measured cost of one preemption on the device */
   uint64_t deviceEvents;                          /* entries drained from the device trace ring */
+  uint64_t dataYields;                            /* data phases left at a slice boundary for other queued work */
+  uint64_t schedulerPasses;                       /* passes of the per-block scheduler loop, summed over blocks */
+  uint64_t nsTriggers, nsWalk, nsQueues;          /* time of those passes by part: trigger list, task-queue walk, queue upkeep */
 } dfcclStats;
 ncclResult_t dfcclGetStats(ofcclRankCtx_t rankCtx, dfcclStats* stats);
 /* Host-memory counters only (submissions, completions, launches, quits; deviceEvents = daemon believed alive):

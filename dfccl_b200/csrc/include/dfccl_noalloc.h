@@ -26,8 +26,9 @@
  *
  * Rules.
  *   - The first call on a device looks up the array's device address, clears its
- *     control words and writes the kernel's control block (synchronous copies, no
- *     allocation).  Make that first call before any stream capture is begun.
+ *     control words, writes the kernel's control block (synchronous copies, no
+ *     allocation) and waits for the device once, so that the block is in place whatever
+ *     stream the kernel runs on.  Make that first call before any stream capture is begun.
  *   - All calls on a device share the array, and it keeps whatever the previous call
  *     left: each call overwrites the staging bytes it uses before reading them, and
  *     the set-up clears the words that must start at zero.  Two calls that overlap on
@@ -53,6 +54,11 @@ extern "C" {
  * null buffer, an unknown datatype or more than DFCCL_NOALLOC_MAX_BYTES of payload. */
 ncclResult_t dfcclAllReduceNoAlloc(const void* sendbuff, void* recvbuff, size_t count, ncclDataType_t datatype,
                                    float scale, cudaStream_t stream);
+
+/* 0, or the failure code of the first kernel of dfcclAllReduceNoAlloc that gave up on the current device (1 = a wait
+ * ran out, 2 = aborted, 3 = no kernel for the datatype).  The kernels leave it in the static array; this call copies
+ * four bytes back (synchronously, allocating nothing) and covers the kernels that have finished by then. */
+ncclResult_t dfcclNoAllocStatus(uint32_t* status);
 
 #ifdef __cplusplus
 }

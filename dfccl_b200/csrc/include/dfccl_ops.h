@@ -44,6 +44,14 @@ ncclResult_t dfcclProbePeerCopy(ncclComm_t comm, int peer, size_t bytes, int dir
                                 int iters, double* usOut);
 /* Round trip of one flag word between this rank and `peer` (both call it). */
 ncclResult_t dfcclProbeFlagRoundTrip(ncclComm_t comm, int peer, int iters, double* usOut);
+/* Round trip "the stream releases a word, a resident kernel answers, the stream goes on" on the current device: what one
+ * stream-ordered submission costs before any collective runs.  mode bit 0: the write is a one-thread kernel instead of a
+ * stream memory operation; bit 1: so is the wait; bit 2: the write also stores a mirror word in pinned host memory. */
+/* Cost in nanoseconds of the single memory operations the daemon's control path is made of, timed by one thread on the
+ * current device: [0] load of a pinned host word, [1] store to it, [2] that store + system fence, [3] device store +
+ * system fence, [4] device store + device fence, [5] system fence alone, [6] device atomic, [7] device load. */
+ncclResult_t dfcclProbeMemoryOps(int iters, uint64_t nsOut[8]);
+ncclResult_t dfcclProbeStreamRoundTrip(int mode, int iters, int delayUs, double* usOut);   /* the kernel answers delayUs late */
 
 /* ---- introspection */
 int dfcclTopoXml(char* buf, int cap);          /* the detected (or injected) topology as XML; returns the length */

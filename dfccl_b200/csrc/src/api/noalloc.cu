@@ -65,6 +65,10 @@ ncclResult_t setUp(int dev, unsigned char** out) {
   CUDACHECK(cudaMemcpy(ptr + kRdOff, &rd, sizeof(rd), cudaMemcpyHostToDevice));
   cudaFuncAttributes fa;                      // load the kernel now rather than at its first launch
   CUDACHECK(cudaFuncGetAttributes(&fa, dfcclNoAllocKernel));
+  // The clear and the copy above ran on the legacy default stream; the caller's stream may be a non-blocking one
+  // that is not ordered after it.  Wait here (allocates nothing) so that no kernel can start before the control
+  // block is in place.
+  CUDACHECK(cudaDeviceSynchronize());
   g_base[dev] = ptr;
   *out = ptr;
   return ncclSuccess;
@@ -107,5 +111,24 @@ ncclResult_t dfcclAllReduceNoAlloc(const void* sendbuff, void* recvbuff, size_t 
   dfcclNoAllocKernel<<<cs.nBlocks, 512, 0, stream>>>(base, cs, (uint64_t)(uintptr_t)sendbuff, (uint64_t)(uintptr_t)recvbuff,
                                                      epoch, SQE_SEND_STAGED | SQE_RECV_STAGED);
   CUDACHECK(cudaGetLastError());
+  return ncclSuccess;
+}
+
+// Status word of the calls made so far on the current device: 0, or the CollStatus of the first kernel that gave
+// up (the kernels keep it in the array's control block).  Reads four bytes with a synchronous copy; it reports on
+// every kernel that has finished by then, so synchronise the streams you care about first.  Allocates nothing.
+extern "C" __attribute__((visibility("default")))
+ncclResult_t dfcclNoAllocStatus(uint32_t* status) {
+  if (!status) return ncclInvalidArgument;
+  int dev = 0;
+  CUDACHECK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices) return ncclInvalidArgument;
+  unsigned char* base = nullptr;
+  { std::lock_guard<std::mutex> l(g_mu); base = g_base[dev]; }
+  *status = 0;
+  if (!base) return ncclSuccess;              // no call was made on this device yet
+  DaemonCtl ctl;
+  CUDACHECK(cudaMemcpy(&ctl, base + kCtlOff, sizeof(ctl), cudaMemcpyDeviceToHost));
+  *status = ctl.pad;
   return ncclSuccess;
 }

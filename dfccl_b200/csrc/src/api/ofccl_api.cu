@@ -32,8 +32,107 @@ static void CUDART_CB triggerReached(void* arg) {
   delete p;
 }
 
-static std::atomic<uint64_t> g_prof[6];
-static inline uint64_t nowNs() { return (uint64_t)std::chrono::duration_cast<std::chrono::nanoseconds>(std::chrono::steady_clock::now().time_since_epoch()).count(); }
+// Stream-ordered release of a trigger word that can be captured in a CUDA graph: the word counts the releases of
+// its collective, so a replayed launch releases the next submission whatever its number is.
+__global__ void dfcclBumpWordKernel(volatile uint64_t* word, volatile uint64_t* mirror) {
+  __threadfence_system();                // what this stream's kernels produced, before the release
+  const uint64_t v = *word + 1;
+  *word = v;
+  if (mirror) *mirror = v;
+}
+
+// Fallback of the ring fill when stream memory operations are unavailable: one thread writes the entry, then the tail.
+__global__ void dfcclPushSqeKernel(Sqe* slot, Sqe q, volatile uint64_t* tail, uint64_t newTail) {
+  *slot = q;
+  __threadfence_system();
+  *tail = newTail;
+}
+
+// Append one entry to the device-resident submission ring (caller holds ctx->mu).  The host writes the ring: four
+// 64-bit words of the entry and then the tail, as one batch of stream memory operations on a stream that carries
+// nothing else, so the daemon finds its work in device memory.  (The reference's daemon polls a ring in pinned host
+// memory, src/collectives_ofccl/device/enqueue_ofccl_dev.cu:85-173; here a load of host memory by a block costs a
+// PCIe round trip, and such loads from tens of blocks queue behind one another.)
+static ncclResult_t pushSqe(ofcclRankCtx* ctx, const Sqe& q) {
+  const uint64_t tail = ctx->sqTail;
+  Sqe* slot = ctx->rdHost.devSq + (tail & (ctx->sqCap - 1));
+  volatile uint64_t* tailWord = (volatile uint64_t*)((char*)ctx->rdDev + offsetof(RankDev, devSqTail));
+  if (ctx->backend != dfcclBackendCuda) {
+    *slot = q;
+    __atomic_store_n((uint64_t*)tailWord, tail + 1, __ATOMIC_RELEASE);
+  } else if (ctx->fnBatch) {
+    typedef CUresult (*Fn)(CUstream, unsigned int, CUstreamBatchMemOpParams*, unsigned int);
+    uint64_t w[4];
+    memcpy(w, &q, sizeof(w));
+    CUstreamBatchMemOpParams ops[5];
+    memset(ops, 0, sizeof(ops));
+    for (int i = 0; i < 4; ++i) {
+      ops[i].writeValue.operation = CU_STREAM_MEM_OP_WRITE_VALUE_64;
+      ops[i].writeValue.address = (CUdeviceptr)(uintptr_t)((uint64_t*)slot + i);
+      ops[i].writeValue.value64 = w[i];
+    }
+    ops[4].writeValue.operation = CU_STREAM_MEM_OP_WRITE_VALUE_64;      // every write is preceded by a fence: the entry is there before the tail
+    ops[4].writeValue.address = (CUdeviceptr)(uintptr_t)tailWord;
+    ops[4].writeValue.value64 = tail + 1;
+    CUresult r = ((Fn)ctx->fnBatch)((CUstream)ctx->sqStream, 5, ops, 0);
+    if (r != CUDA_SUCCESS) { DF_WARN("cuStreamBatchMemOp failed (%d)", (int)r); return ncclUnhandledCudaError; }
+  } else {
+    int prev = 0;
+    cudaGetDevice(&prev);
+    if (prev != ctx->device) cudaSetDevice(ctx->device);
+    dfcclPushSqeKernel<<<1, 1, 0, ctx->sqStream>>>(slot, q, tailWord, tail + 1);
+    cudaError_t e = cudaGetLastError();
+    if (prev != ctx->device) cudaSetDevice(prev);
+    if (e != cudaSuccess) { DF_WARN("submission ring fill failed: %s", cudaGetErrorString(e)); return ncclUnhandledCudaError; }
+  }
+  ctx->sqTail = tail + 1;
+  return ncclSuccess;
+}
+
+// Entries the slowest block has consumed, as the blocks report it (pinned words they store to).
+static uint64_t minFrontier(ofcclRankCtx* ctx) {
+  uint64_t m = ~0ull;
+  for (int b = 0; b < ctx->nBlocks; ++b) m = std::min<uint64_t>(m, __atomic_load_n((const uint64_t*)&ctx->hostFrontier[b], __ATOMIC_ACQUIRE));
+  return m;
+}
+
+bool NetWorkers::post(std::function<void()> job) {
+  std::lock_guard<std::mutex> l(mu);
+  jobs.push_back(std::move(job));
+  if ((int)jobs.size() > idle) {
+    try {
+      threads.emplace_back([this] {
+        std::unique_lock<std::mutex> lk(mu);
+        for (;;) {
+          ++idle;
+          cv.wait(lk, [&] { return stop || !jobs.empty(); });
+          --idle;
+          if (jobs.empty()) return;              // stop, and nothing left to run
+          std::function<void()> j = std::move(jobs.front());
+          jobs.pop_front();
+          lk.unlock();
+          j();
+          lk.lock();
+        }
+      });
+    } catch (const std::system_error&) {
+      if ((int)jobs.size() > idle) { jobs.pop_back(); return false; }     // nobody would ever run it
+    }
+  }
+  cv.notify_one();
+  return true;
+}
+
+void NetWorkers::shutdown() {
+  std::vector<std::thread> ts;
+  {
+    std::lock_guard<std::mutex> l(mu);
+    stop = true;
+    ts.swap(threads);
+  }
+  cv.notify_all();
+  for (auto& t : ts) if (t.joinable()) t.join();
+}
 
 static uint32_t pow2ceil(uint32_t v) { uint32_t p = 1; while (p < v) p <<= 1; return p; }
 
@@ -113,19 +212,19 @@ static void deliver(ofcclRankCtx* ctx, uint64_t entry) {
   void* args = nullptr;
   {
     std::lock_guard<std::mutex> l(ctx->mu);
-    auto it = ctx->colls.find(coll);
-    if (it == ctx->colls.end()) { DF_WARN("completion for unknown collective %d", coll); return; }
-    it->second.lastStatus = cqeStatus(entry);
-    if (it->second.lastStatus != ST_OK && ctx->asyncError == ncclSuccess)
-      ctx->asyncError = it->second.lastStatus == ST_TIMEOUT ? dfcclTimeout : it->second.lastStatus == ST_ABORTED ? dfcclAborted : ncclInternalError;
-    cb = it->second.cb; args = it->second.cbArgs;
+    CollEntry* e = coll >= 0 && coll < (int)ctx->byId.size() ? ctx->byId[coll] : nullptr;
+    if (!e) { DF_WARN("completion for unknown collective %d", coll); return; }
+    e->lastStatus = cqeStatus(entry);
+    if (e->lastStatus != ST_OK && ctx->asyncError == ncclSuccess)
+      ctx->asyncError = e->lastStatus == ST_TIMEOUT ? dfcclTimeout : e->lastStatus == ST_ABORTED ? dfcclAborted : ncclInternalError;
+    cb = e->cb; args = e->cbArgs;
   }
   ctx->cqes++;
   if (ctx->faultFreezeMs > 0) std::this_thread::sleep_for(std::chrono::milliseconds(ctx->faultFreezeMs));
   if (cb) { cb(coll, args); ctx->cbs++; }
   {
     std::lock_guard<std::mutex> l(ctx->mu);
-    { uint64_t* w = &ctx->colls[coll].completed; __atomic_store_n(w, *w + 1, __ATOMIC_RELEASE); }   // also read lock-free by spinning waiters
+    { uint64_t* w = &ctx->byId[coll]->completed; __atomic_store_n(w, *w + 1, __ATOMIC_RELEASE); }   // also read lock-free by spinning waiters
     ctx->remaining--;
     if (ctx->remaining.load() == 0) ctl_store(&ctx->ctl->hold, 0);
   }
@@ -358,17 +457,19 @@ DF_API ncclResult_t ofcclFinalizeRankCtx7StartHostThrds(ofcclRankCtx_t ctx) {
   }
   // 3. queues and device tables
   const uint32_t maxColls = (uint32_t)ctx->maxCollId + 1;
+  ctx->byId.assign(maxColls, nullptr);
+  for (auto& kv : ctx->colls) ctx->byId[kv.first] = &kv.second;
   ctx->sqCap = pow2ceil(std::max<uint32_t>(64, 2 * (uint32_t)ctx->colls.size() + 2));
   ctx->cqCap = pow2ceil(std::max<uint32_t>(64, 2 * (uint32_t)ctx->colls.size() + 2));
-  DFCHECK(pinnedAlloc(be, (void**)&ctx->hostSq, sizeof(Sqe) * ctx->sqCap));
-  DFCHECK(pinnedAlloc(be, (void**)&ctx->hostSqTail, 64));
-  DFCHECK(pinnedAlloc(be, (void**)&ctx->hostSqHead, 64));
+  DFCHECK(pinnedAlloc(be, (void**)&ctx->hostFrontier, sizeof(uint64_t) * ctx->nBlocks));
   DFCHECK(pinnedAlloc(be, (void**)&ctx->hostCq, sizeof(uint64_t) * ctx->cqCap));
   DFCHECK(pinnedAlloc(be, (void**)&ctx->ctl, sizeof(DaemonCtl)));
   DFCHECK(pinnedAlloc(be, (void**)&ctx->hostTrig, sizeof(uint64_t) * ((size_t)ctx->maxCollId + 1)));
   RankDev& rd = ctx->rdHost;
   memset(&rd, 0, sizeof(rd));
-  rd.hostSq = ctx->hostSq; rd.hostSqTail = ctx->hostSqTail; rd.hostSqHead = ctx->hostSqHead;
+  rd.hostFrontier = ctx->hostFrontier;
+  if (be == dfcclBackendCuda) { DFCHECK(devAlloc(be, (void**)&ctx->devAbort, 64)); rd.abortWord = ctx->devAbort; }
+  else rd.abortWord = &ctx->ctl->abortFlag;
   rd.hostCq = ctx->hostCq; rd.ctl = ctx->ctl;
   rd.sqCap = ctx->sqCap; rd.cqCap = ctx->cqCap; rd.nBlocks = (uint32_t)ctx->nBlocks; rd.maxColls = maxColls;
   DFCHECK(devAlloc(be, (void**)&rd.devSq, sizeof(Sqe) * ctx->sqCap));
@@ -393,7 +494,9 @@ DF_API ncclResult_t ofcclFinalizeRankCtx7StartHostThrds(ofcclRankCtx_t ctx) {
   rd.stallQuitNs = (uint64_t)paramI64("STALL_QUIT_US", tolerant ? tolerant : 5000) * 1000ull;
   rd.waitTimeoutNs = (uint64_t)paramI64("WAIT_TIMEOUT_MS", 0) * 1000000ull;
   rd.maxLifetimeNs = (uint64_t)paramI64("MAX_LIFETIME_MS", 2000) * 1000000ull;
-  rd.sliceBytes = (uint64_t)paramI64("SLICE_BYTES", 0);
+  // a block's data phase is left after this many bytes when other work is queued (the reference parks a
+  // collective at its 1 MiB slices: src/include/collectives.h:112-113)
+  rd.sliceBytes = (uint64_t)std::max<int64_t>(0, paramI64("SLICE_BYTES", 1 << 20));
   std::vector<CollStatic> table(maxColls);
   memset(table.data(), 0, sizeof(CollStatic) * maxColls);
   for (auto& kv : ctx->colls) table[kv.first] = kv.second.cs;
@@ -410,6 +513,7 @@ DF_API ncclResult_t ofcclFinalizeRankCtx7StartHostThrds(ofcclRankCtx_t ctx) {
     (void)cudaGetLastError();
     if (!ctx->fnWrite64) ctx->fnBatch = nullptr;
     CUDACHECK(cudaStreamCreateWithFlags(&ctx->wakeStream, cudaStreamNonBlocking));
+    { int lo = 0, hi = 0; cudaDeviceGetStreamPriorityRange(&lo, &hi); CUDACHECK(cudaStreamCreateWithPriority(&ctx->sqStream, cudaStreamNonBlocking, hi)); }
     ctx->wakeEvents.resize(256);
     for (auto& e : ctx->wakeEvents) CUDACHECK(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
   }
@@ -481,23 +585,29 @@ DF_API ncclResult_t ofcclPrepareDone(ofcclRankCtx_t ctx) {
 
 // ------------------------------------------------------------------ submit
 
+// How a submission is released to the daemon.
+enum SubmitMode {
+  SUBMIT_HOST = 0,        // at once
+  SUBMIT_STREAM = 1,      // by a stream memory operation enqueued now, after the work already in `stream`
+  SUBMIT_DEFERRED = 2,    // by a later dfcclTriggerOnStream (or by the replay of a graph that captured one)
+};
+
 static ncclResult_t submit(ofcclRankCtx* ctx, const void* send, void* recv, int collId, CallbackFunc cb, void* cbArgs,
-                           bool onStream, cudaStream_t stream) {
+                           SubmitMode mode, cudaStream_t stream) {
   if (!ctx || !ctx->finalized || ctx->destroyed) { DF_WARN("context is not ready for submissions"); return ncclInvalidUsage; }
+  const bool onStream = mode != SUBMIT_HOST;
   NvtxRange range(onStream ? "dfccl:submit(stream)" : "dfccl:submit");
   if (ctl_load(&ctx->ctl->abortFlag)) return dfcclAborted;
   if (ctx->faultDelayUs > 0) std::this_thread::sleep_for(std::chrono::microseconds(ctx->faultDelayUs));
   Sqe q;
   memset(&q, 0, sizeof(q));
   uint64_t trig = 0;
-  const uint64_t tp0 = nowNs();
-  uint64_t tp1 = 0, tp2 = 0;
+  const bool deferWake = onStream && ctx->backend == dfcclBackendCuda;
   {
     std::unique_lock<std::mutex> l(ctx->mu);
-    tp1 = nowNs();
-    auto it = ctx->colls.find(collId);
-    if (it == ctx->colls.end()) { DF_WARN("collective %d was never prepared", collId); return ncclInvalidArgument; }
-    CollEntry& e = it->second;
+    CollEntry* ep = collId >= 0 && collId < (int)ctx->byId.size() ? ctx->byId[collId] : nullptr;
+    if (!ep) { DF_WARN("collective %d was never prepared", collId); return ncclInvalidArgument; }
+    CollEntry& e = *ep;
     if (e.submitted != e.completed) {
       if (!onStream) { DF_WARN("collective %d submitted again before its callback ran", collId); return ncclInvalidUsage; }
       // Stream-ordered callers enqueue ahead of the GPU: the previous submission of this id is
@@ -510,29 +620,35 @@ static ncclResult_t submit(ofcclRankCtx* ctx, const void* send, void* recv, int 
       if (!ok) { DF_WARN("collective %d: previous submission did not complete within 120 s", collId); return dfcclTimeout; }
       if (ctl_load(&ctx->ctl->abortFlag)) return dfcclAborted;
     }
-    tp2 = nowNs();
     const CollStatic& cs = e.cs;
     const bool needSend = !(cs.kind == dfcclCollBroadcast && cs.rank != cs.root);
     const bool needRecv = !(cs.kind == dfcclCollReduce && cs.rank != cs.root);
     if ((needSend && !send) || (needRecv && !recv)) { DF_WARN("null buffer for collective %d", collId); return ncclInvalidArgument; }
     if (e.comm->netMode) {
       if (onStream) { DF_WARN("collective %d: stream-ordered submission is not available on communicators that go through the network path", collId); return ncclInvalidUsage; }
+      NetCollDesc d{cs.kind, cs.inType, cs.outType, cs.op, cs.root, cs.postDiv, cs.scale, (size_t)cs.count};
+      ncclComm* comm = e.comm;
+      std::shared_ptr<NetRing> ring = e.ring;
+      CallbackFunc prevCb = e.cb;
+      void* prevArgs = e.cbArgs;
       e.cb = cb; e.cbArgs = cbArgs;
       e.submitted++;
       ctx->remaining++;
       ctx->netPending++;
       ctx->sqes++;
-      NetCollDesc d{cs.kind, cs.inType, cs.outType, cs.op, cs.root, cs.postDiv, cs.scale, (size_t)cs.count};
-      ncclComm* comm = e.comm;
-      std::shared_ptr<NetRing> ring = e.ring;
-      std::lock_guard<std::mutex> nl(ctx->netMu);
-      ctx->netThreads.emplace_back([ctx, comm, ring, d, send, recv, collId] {
+      const bool posted = ctx->netWorkers.post([ctx, comm, ring, d, send, recv, collId] {
         logSetRank(ctx->rank);
         ncclResult_t r = netStagedCollective(comm, ring.get(), d, send, recv, nullptr);
         const uint32_t st = r == ncclSuccess ? ST_OK : r == dfcclAborted ? ST_ABORTED : r == dfcclTimeout ? ST_TIMEOUT : ST_BAD_ARG;
         ctx->netPending--;
         deliver(ctx, ((uint64_t)st << 24) | (uint64_t)(uint32_t)collId);
       });
+      if (!posted) {                        // no thread to run it on: undo the bookkeeping, the caller may try again
+        e.cb = prevCb; e.cbArgs = prevArgs;
+        e.submitted--; ctx->remaining--; ctx->netPending--; ctx->sqes--;
+        DF_WARN("collective %d: no worker thread could be created for the network path", collId);
+        return ncclSystemError;
+      }
       ctx->pollCv.notify_one();
       return ncclSuccess;
     }
@@ -558,42 +674,36 @@ static ncclResult_t submit(ofcclRankCtx* ctx, const void* send, void* recv, int 
     if (stageSend && e.stagingBytes[0] < sB) { if (e.stagingBytes[0]) heap->free(e.stagingOff[0]); DFCHECK(heap->alloc(sB, &e.stagingOff[0], false)); e.stagingBytes[0] = sB; e.cs.stagingSendOff = e.stagingOff[0]; tableDirty = true; }
     if (stageRecv && e.stagingBytes[1] < rB) { if (e.stagingBytes[1]) heap->free(e.stagingOff[1]); DFCHECK(heap->alloc(rB, &e.stagingOff[1], false)); e.stagingBytes[1] = rB; e.cs.stagingRecvOff = e.stagingOff[1]; tableDirty = true; }
     if (tableDirty) DFCHECK(devUpload(ctx->backend, &ctx->rdHost.colls[collId], &e.cs, sizeof(CollStatic)));
-    if (viaArena) {
-    } else {
+    if (!viaArena) {
       if (stageSend) { q.flags |= SQE_SEND_STAGED; q.send = (uint64_t)(uintptr_t)send; } else if (needSend) q.send = heap->offsetOf(send);
       if (stageRecv) { q.flags |= SQE_RECV_STAGED; q.recv = (uint64_t)(uintptr_t)recv; } else if (needRecv) q.recv = heap->offsetOf(recv);
     }
     if (onStream) { q.flags |= SQE_TRIGGERED; q.trigger = trig = ++e.triggerSeq; }
-    // flow control: entries the device has not mirrored yet
-    uint64_t tail = *ctx->hostSqTail;
-    while (tail - __atomic_load_n((const uint64_t*)ctx->hostSqHead, __ATOMIC_ACQUIRE) >= ctx->sqCap) {
+    // flow control: never overwrite an entry some block has not consumed yet
+    while (ctx->sqTail - ctx->sqMinFrontier >= ctx->sqCap && (ctx->sqMinFrontier = minFrontier(ctx), ctx->sqTail - ctx->sqMinFrontier >= ctx->sqCap)) {
       ctx->sqFull++;
       l.unlock();
       if (!ctl_load(&ctx->ctl->alive)) wakeLauncher(ctx->launcher.get());
       sched_yield();
       l.lock();
-      tail = *ctx->hostSqTail;
     }
     e.cb = cb; e.cbArgs = cbArgs;
     e.submitted++;
     ctx->remaining++;
     ctx->sqes++;
+    if (deferWake) {                   // the poller watches the trigger's host mirror and wakes a parked daemon
+      ctx->pendingTrig.emplace_back(collId, trig);
+      ctx->untriggered++;
+    }
     if (ctx->faultDrop > 0) {          // accepted, counted, never published
       --ctx->faultDrop;
     } else {
-      ctx->hostSq[tail & (ctx->sqCap - 1)] = q;
-      __atomic_store_n((uint64_t*)ctx->hostSqTail, tail + 1, __ATOMIC_RELEASE);
+      DFCHECK(pushSqe(ctx, q));
     }
   }
-  const uint64_t tp3 = nowNs();
   ctx->pollCv.notify_one();
-  const bool deferWake = onStream && ctx->backend == dfcclBackendCuda;
-  if (deferWake) {
-    std::lock_guard<std::mutex> l(ctx->mu);
-    ctx->pendingTrig.emplace_back(collId, trig);
-    ctx->untriggered++;
-  } else if (!ctl_load(&ctx->ctl->alive)) wakeLauncher(ctx->launcher.get());
-  if (onStream) {
+  if (!deferWake && !ctl_load(&ctx->ctl->alive)) wakeLauncher(ctx->launcher.get());
+  if (mode == SUBMIT_STREAM) {
     volatile uint64_t* word = ctx->rdHost.trigger + collId;
     if (ctx->backend == dfcclBackendCuda) {
       volatile uint64_t* mirror = ctx->hostTrig + collId;
@@ -630,15 +740,34 @@ static ncclResult_t submit(ofcclRankCtx* ctx, const void* send, void* recv, int 
       __atomic_store_n((uint64_t*)word, trig, __ATOMIC_RELEASE);
     }
   }
-  { const uint64_t tp4 = nowNs(); g_prof[0] += tp1 - tp0; g_prof[1] += tp2 - tp1; g_prof[2] += tp3 - tp2; g_prof[3] += tp4 - tp3; g_prof[4]++; }
   return ncclSuccess;
 }
 
 DF_API ncclResult_t dfcclRun(const void* s, void* r, int collId, CallbackFunc cb, void* args, ofcclRankCtx_t ctx) {
-  return submit(ctx, s, r, collId, cb, args, false, nullptr);
+  return submit(ctx, s, r, collId, cb, args, SUBMIT_HOST, nullptr);
 }
 DF_API ncclResult_t dfcclRunOnStream(const void* s, void* r, int collId, cudaStream_t stream, CallbackFunc cb, void* args, ofcclRankCtx_t ctx) {
-  return submit(ctx, s, r, collId, cb, args, true, stream);
+  return submit(ctx, s, r, collId, cb, args, SUBMIT_STREAM, stream);
+}
+DF_API ncclResult_t dfcclRunDeferred(const void* s, void* r, int collId, CallbackFunc cb, void* args, ofcclRankCtx_t ctx) {
+  return submit(ctx, s, r, collId, cb, args, SUBMIT_DEFERRED, nullptr);
+}
+
+// Release, in stream order, the oldest submission of `collId` that dfcclRunDeferred published (or will publish: the
+// trigger word counts releases, so the order of the two calls does not matter).  The release is a one-thread kernel
+// and may be captured in a CUDA graph; every replay releases one more submission.
+DF_API ncclResult_t dfcclTriggerOnStream(int collId, cudaStream_t stream, ofcclRankCtx_t ctx) {
+  if (!ctx || !ctx->finalized || ctx->destroyed) return ncclInvalidUsage;
+  if (collId < 0 || collId >= (int)ctx->byId.size() || !ctx->byId[collId]) return ncclInvalidArgument;
+  if (ctx->byId[collId]->comm->netMode) return ncclInvalidUsage;
+  volatile uint64_t* word = ctx->rdHost.trigger + collId;
+  if (ctx->backend == dfcclBackendCuda) {
+    dfcclBumpWordKernel<<<1, 1, 0, stream>>>(word, ctx->hostTrig + collId);
+    CUDACHECK(cudaGetLastError());
+  } else {
+    __atomic_fetch_add((uint64_t*)word, 1, __ATOMIC_ACQ_REL);
+  }
+  return ncclSuccess;
 }
 
 DF_API ncclResult_t dfcclWait(int collId, int timeoutMs, ofcclRankCtx_t ctx) {
@@ -729,18 +858,21 @@ DF_API ncclResult_t dfcclStreamWait(int collId, cudaStream_t stream, ofcclRankCt
   return dfcclWait(collId, -1, ctx);     // no stream memory operations: the host waits instead
 }
 
-// Mean host nanoseconds per submit spent in: taking the context lock, waiting for the previous
-// submission of the id, building and publishing the entry, wake-up and stream operations.
-DF_API ncclResult_t dfcclSubmitProfile(uint64_t out[5]) {
-  uint64_t n = g_prof[4].load();
-  for (int i = 0; i < 4; ++i) out[i] = n ? g_prof[i].load() / n : 0;
-  out[4] = n;
-  return ncclSuccess;
-}
-
 DF_API ncclResult_t dfcclAbort(ofcclRankCtx_t ctx) {
   if (!ctx) return ncclInvalidArgument;
   if (ctx->ctl) ctl_store(&ctx->ctl->abortFlag, 1);
+  if (ctx->devAbort && ctx->sqStream) {
+    // the daemon polls a word in device memory; the write goes through the stream that fills the ring (a stream
+    // memory operation needs no SM, so it lands whatever the kernels are doing)
+    std::lock_guard<std::mutex> l(ctx->mu);
+    typedef CUresult (*Fn)(CUstream, CUdeviceptr, cuuint32_t, unsigned int);
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (!paramI64("NO_STREAM_MEMOPS", 0) && cudaGetDriverEntryPoint("cuStreamWriteValue32", &fn, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess && fn)
+      ((Fn)fn)((CUstream)ctx->sqStream, (CUdeviceptr)(uintptr_t)ctx->devAbort, 1u, 0);
+    else { uint32_t one = 1; cudaMemcpyAsync(ctx->devAbort, &one, sizeof(one), cudaMemcpyHostToDevice, ctx->sqStream); cudaStreamSynchronize(ctx->sqStream); }
+    (void)cudaGetLastError();
+  }
   ctx->doneCv.notify_all();
   return ncclSuccess;
 }
@@ -775,6 +907,8 @@ DF_API ncclResult_t dfcclGetStats(ofcclRankCtx_t ctx, dfcclStats* s) {
     s->waitPolls += b.waitPolls; s->waitTimeouts += b.waitTimeouts;
     s->bytesReduced += b.bytesReduced; s->bytesCopied += b.bytesCopied; s->totalSwitchNs += b.totalSwitchNs;
     s->maxSwitchNs = std::max<uint64_t>(s->maxSwitchNs, b.maxSwitchNs);
+    s->dataYields += b.yields; s->schedulerPasses += b.passes;
+    s->nsTriggers += b.nsTriggers; s->nsWalk += b.nsWalk; s->nsQueues += b.nsQueues;
   }
   if (ctx->rdHost.trace) {
     uint64_t head = 0;
@@ -794,7 +928,7 @@ DF_API ncclResult_t dfcclTraceDump(ofcclRankCtx_t ctx, const char* path) {
   DFCHECK(devDownload(ctx->backend, ev.data(), ctx->rdHost.trace, sizeof(TraceEvent) * cap));
   std::ofstream o(path);
   if (!o) return ncclSystemError;
-  static const char* names[] = {"?", "sqe", "start", "stall", "resume", "data_begin", "data_end", "done", "quit", "launch"};
+  static const char* names[] = {"?", "sqe", "start", "stall", "arrived", "data_begin", "data_end", "done", "quit", "launch", "peers_done", "yield"};
   o.setf(std::ios::fixed);
   o.precision(3);                 // microseconds with nanosecond resolution; the default would round the absolute stamps
   o << "{\"traceEvents\":[\n";
@@ -802,7 +936,7 @@ DF_API ncclResult_t dfcclTraceDump(ofcclRankCtx_t ctx, const char* path) {
   for (uint64_t i = 0; i < n; ++i) {
     const TraceEvent& e = ev[(first + i) & (cap - 1)];
     const char* ph = e.event == TR_DATA_BEGIN ? "B" : e.event == TR_DATA_END ? "E" : "i";
-    o << (i ? ",\n" : "") << "{\"name\":\"" << (e.event == TR_DATA_BEGIN || e.event == TR_DATA_END ? "data" : names[e.event < 10 ? e.event : 0])
+    o << (i ? ",\n" : "") << "{\"name\":\"" << (e.event == TR_DATA_BEGIN || e.event == TR_DATA_END ? "data" : names[e.event < 12 ? e.event : 0])
       << "\",\"ph\":\"" << ph << "\",\"ts\":" << (double)e.ns / 1000.0 << ",\"pid\":" << ctx->rank << ",\"tid\":" << e.block
       << ",\"args\":{\"coll\":" << e.collId << "}}";
   }
@@ -853,7 +987,9 @@ static void releaseCtx(ofcclRankCtx* ctx) {
   devFree(be, rd.devSq); devFree(be, rd.colls); devFree(be, rd.dyn); devFree(be, rd.doneCount); devFree(be, rd.failCount);
   devFree(be, (void*)rd.doneEpoch); devFree(be, (void*)rd.trigger); devFree(be, rd.saved); devFree(be, rd.stats); devFree(be, rd.trace);
   devFree(be, ctx->rdDev);
-  pinnedFree(be, ctx->hostSq); pinnedFree(be, (void*)ctx->hostSqTail); pinnedFree(be, (void*)ctx->hostSqHead);
+  pinnedFree(be, (void*)ctx->hostFrontier);
+  if (ctx->sqStream) { cudaStreamSynchronize(ctx->sqStream); cudaStreamDestroy(ctx->sqStream); }
+  if (ctx->devAbort) devFree(be, ctx->devAbort);
   pinnedFree(be, (void*)ctx->hostCq); pinnedFree(be, ctx->ctl); pinnedFree(be, (void*)ctx->hostTrig);
   delete ctx;
 }
@@ -871,18 +1007,13 @@ DF_API ncclResult_t ofcclDestroy(ofcclRankCtx_t ctx) {
     Sqe q;
     memset(&q, 0, sizeof(q));
     q.collId = -1; q.flags = SQE_QUIT;
-    uint64_t tail = *ctx->hostSqTail;
-    ctx->hostSq[tail & (ctx->sqCap - 1)] = q;
-    __atomic_store_n((uint64_t*)ctx->hostSqTail, tail + 1, __ATOMIC_RELEASE);
+    (void)pushSqe(ctx, q);
   }
+  if (ctx->sqStream) cudaStreamSynchronize(ctx->sqStream);         // the quit entry is in the ring
   if (ctx->wakeStream) cudaStreamSynchronize(ctx->wakeStream);     // no wake-up callback may outlive the context
   ctx->stopPoller = true;
   ctx->pollCv.notify_all();
-  {
-    std::vector<std::thread> ts;
-    { std::lock_guard<std::mutex> nl(ctx->netMu); ts.swap(ctx->netThreads); }
-    for (auto& t : ts) if (t.joinable()) t.join();
-  }
+  ctx->netWorkers.shutdown();          // jobs already posted still run to their completion entry
   if (ctx->poller.joinable()) ctx->poller.join();
   std::shared_ptr<DaemonLauncher> L = ctx->launcher;
   ctx->launcher.reset();

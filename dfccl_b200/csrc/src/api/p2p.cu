@@ -3,6 +3,7 @@
 #include "../device/p2p_impl.h"
 #include <cstring>
 #include <map>
+#include <memory>
 #include <thread>
 #include <vector>
 
@@ -17,7 +18,24 @@ namespace {
 struct Pending { ncclComm* comm; bool isSend; void* buf; size_t bytes; int peer; cudaStream_t stream; };
 thread_local std::vector<Pending> t_pending;
 
-ncclResult_t launchFor(ncclComm* c, cudaStream_t stream, const std::vector<Pending>& ops) {
+// Staging pieces of receives into buffers outside the heap go back to the heap once the kernel that used them has
+// run: from a host function enqueued behind the kernel (cuda backend), never by making the caller wait.
+struct FreeLater { Heap* heap; std::vector<uint64_t> offs; };
+void CUDART_CB freeStaging(void* arg) {
+  FreeLater* f = (FreeLater*)arg;
+  for (auto off : f->offs) f->heap->free(off);      // host bookkeeping only: no CUDA call in here
+  delete f;
+}
+
+// What one (communicator, stream) of a flush has started on the host backend and not yet waited for.
+struct HostLaunch {
+  ncclComm* comm = nullptr;
+  std::shared_ptr<std::vector<P2pList>> lists;
+  std::vector<std::thread> threads;
+  std::vector<uint64_t> temps;
+};
+
+ncclResult_t launchFor(ncclComm* c, cudaStream_t stream, const std::vector<Pending>& ops, HostLaunch* host) {
   // lists keyed by (direction, peer), operations in program order
   std::map<std::pair<int, int>, std::vector<const Pending*>> by;
   for (auto& p : ops) by[{p.isSend ? 1 : 0, p.peer}].push_back(&p);
@@ -66,18 +84,19 @@ ncclResult_t launchFor(ncclComm* c, cudaStream_t stream, const std::vector<Pendi
     dfcclP2pKernel<<<(unsigned)(lists.size() * DF_P2P_CHANNELS), 512, 0, stream>>>(c->saRd, dl);
     CUDACHECK(cudaGetLastError());
     CUDACHECK(cudaFreeAsync(dl, stream));
-    if (!temps.empty()) {               // staged receives: the heap pieces go back once the kernel is done
-      CUDACHECK(cudaStreamSynchronize(stream));
-      for (auto off : temps) c->heap->free(off);
-    }
+    if (!temps.empty()) CUDACHECK(cudaLaunchHostFunc(stream, freeStaging, new FreeLater{c->heap, temps}));
     if (prev != c->device) cudaSetDevice(prev);
   } else {
-    std::vector<std::thread> ts;
-    for (size_t i = 0; i < lists.size(); ++i)
+    // the "kernels" of every communicator of the flush are started before any of them is waited for (p2pFlush): one
+    // thread may hold both ends of a transfer (ncclCommInitAll, then a group with send / recv on every communicator)
+    host->comm = c;
+    host->lists = std::make_shared<std::vector<P2pList>>(lists);
+    host->temps = temps;
+    auto shared = host->lists;
+    RankDev* rd = c->saRd;
+    for (size_t i = 0; i < shared->size(); ++i)
       for (int ch = 0; ch < DF_P2P_CHANNELS; ++ch)
-        ts.emplace_back([&, i, ch] { P2pShared sh; p2pBlockMain(c->saRd, &lists[i], ch, &sh); });
-    for (auto& t : ts) t.join();
-    for (auto off : temps) c->heap->free(off);
+        host->threads.emplace_back([shared, rd, i, ch] { P2pShared sh; p2pBlockMain(rd, &(*shared)[i], ch, &sh); });
   }
   return ncclSuccess;
 }
@@ -99,8 +118,20 @@ ncclResult_t p2pFlush() {
   all.swap(t_pending);
   std::map<std::pair<ncclComm*, cudaStream_t>, std::vector<Pending>> by;
   for (auto& p : all) by[{p.comm, p.stream}].push_back(p);
-  for (auto& kv : by) DFCHECK(launchFor(kv.first.first, kv.first.second, kv.second));
-  return ncclSuccess;
+  // launch everything first: a kernel of one communicator may be the partner of a kernel of another one in this very
+  // flush, so nothing here waits between two launches
+  std::vector<HostLaunch> started(by.size());
+  ncclResult_t res = ncclSuccess;
+  size_t k = 0;
+  for (auto& kv : by) {
+    res = launchFor(kv.first.first, kv.first.second, kv.second, &started[k++]);
+    if (res != ncclSuccess) break;
+  }
+  for (auto& h : started) {
+    for (auto& t : h.threads) t.join();
+    for (auto off : h.temps) h.comm->heap->free(off);
+  }
+  return res;
 }
 
 }  // namespace dfccl

@@ -150,3 +150,181 @@ ncclResult_t dfcclProbeFlagRoundTrip(ncclComm_t comm, int peer, int iters, doubl
   *usOut = (double)ms * 1e3 / iters;
   return ncclSuccess;
 }
+
+// ---------------------------------------------------------------------------------------------------------------
+// Round trip "stream releases a word -> a resident kernel answers -> stream continues": the cost of one
+// stream-ordered submission as the daemon sees it, without any collective in between.  An echo kernel (one thread)
+// waits for word A to reach k and answers by writing k to word B; the timed stream alternates "write A = k" and
+// "wait until B >= k".  Both steps exist in two forms: a stream memory operation, or a one-thread kernel.
+//   mode bit 0: the write is a kernel (else cuStreamWriteValue64)
+//   mode bit 1: the wait is a kernel  (else cuStreamWaitValue64)
+//   mode bit 2: the write also stores a mirror word in pinned host memory (batched with the device word when both
+//               are memory operations, a second store of the same kernel otherwise)
+// `delayUs`: the echo kernel answers that long after it saw the release (the time a collective would take), which
+// shows how the cost of the wait depends on how long the stream has been parked on it; the result includes it.
+// Every wait is bounded by `limitNs`; a wait that runs out stores an error and the kernels return.
+#include <cuda.h>
+namespace dfccl {
+namespace {
+
+__global__ void probeEchoKernel(volatile uint64_t* a, volatile uint64_t* b, int iters, uint64_t limitNs, uint64_t delayNs, uint32_t* err) {
+  if (threadIdx.x != 0) return;
+  const uint64_t t0 = df_now_ns();
+  for (int k = 1; k <= iters; ++k) {
+    while (ld_relaxed_sys_u64(a) < (uint64_t)k) {
+      if (df_now_ns() - t0 > limitNs || *(volatile uint32_t*)err) { *err = 1; return; }
+    }
+    if (delayNs) { const uint64_t t1 = df_now_ns(); while (df_now_ns() - t1 < delayNs) {} }   // "the collective"
+    st_relaxed_sys_u64(b, (uint64_t)k);
+  }
+}
+__global__ void probeWriteKernel(volatile uint64_t* a, volatile uint64_t* mirror, uint64_t v) {
+  if (mirror) *mirror = v;
+  st_relaxed_sys_u64(a, v);
+}
+__global__ void probeWaitKernel(volatile uint64_t* b, uint64_t v, uint64_t limitNs, uint32_t* err) {
+  const uint64_t t0 = df_now_ns();
+  while (ld_relaxed_sys_u64(b) < v) {
+    if (df_now_ns() - t0 > limitNs || *(volatile uint32_t*)err) { *err = 2; return; }
+  }
+}
+
+}  // namespace
+}  // namespace dfccl
+
+extern "C" __attribute__((visibility("default")))
+ncclResult_t dfcclProbeStreamRoundTrip(int mode, int iters, int delayUs, double* usOut) {
+  if (!usOut || iters < 1 || iters > 400 || mode < 0 || mode > 7 || delayUs > 1000) return ncclInvalidArgument;
+  typedef CUresult (*FnW)(CUstream, CUdeviceptr, cuuint64_t, unsigned int);
+  typedef CUresult (*FnB)(CUstream, unsigned int, CUstreamBatchMemOpParams*, unsigned int);
+  void *fw = nullptr, *fwait = nullptr, *fb = nullptr;
+  cudaDriverEntryPointQueryResult q;
+  if (cudaGetDriverEntryPoint("cuStreamWriteValue64", &fw, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess) fw = nullptr;
+  if (cudaGetDriverEntryPoint("cuStreamWaitValue64", &fwait, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess) fwait = nullptr;
+  if (cudaGetDriverEntryPoint("cuStreamBatchMemOp", &fb, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess) fb = nullptr;
+  (void)cudaGetLastError();
+  const bool kWrite = mode & 1, kWait = mode & 2, mirror = mode & 4;
+  if ((!kWrite && !fw) || (!kWait && !fwait) || (mirror && !kWrite && !fb)) return ncclInvalidUsage;
+  uint64_t* words = nullptr;
+  uint64_t* hostWord = nullptr;
+  uint32_t* err = nullptr;
+  CUDACHECK(cudaMalloc((void**)&words, 512));
+  CUDACHECK(cudaMemset(words, 0, 512));
+  CUDACHECK(cudaMalloc((void**)&err, 4));
+  CUDACHECK(cudaMemset(err, 0, 4));
+  CUDACHECK(cudaHostAlloc((void**)&hostWord, 64, cudaHostAllocMapped));
+  *hostWord = 0;
+  volatile uint64_t* a = words;
+  volatile uint64_t* b = words + 32;       // another 256-byte line
+  cudaStream_t sEcho, s;
+  CUDACHECK(cudaStreamCreateWithFlags(&sEcho, cudaStreamNonBlocking));
+  CUDACHECK(cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking));
+  cudaEvent_t e0, e1;
+  CUDACHECK(cudaEventCreate(&e0));
+  CUDACHECK(cudaEventCreate(&e1));
+  const uint64_t limitNs = 2000000000ull;
+  ncclResult_t res = ncclSuccess;
+  CUDACHECK(cudaDeviceSynchronize());
+  probeEchoKernel<<<1, 32, 0, sEcho>>>(a, b, iters, limitNs, (uint64_t)(delayUs < 0 ? 0 : delayUs) * 1000ull, err);
+  CUDACHECK(cudaEventRecord(e0, s));
+  for (int k = 1; k <= iters && res == ncclSuccess; ++k) {
+    if (kWrite) probeWriteKernel<<<1, 1, 0, s>>>(a, mirror ? hostWord : nullptr, (uint64_t)k);
+    else if (mirror) {
+      CUstreamBatchMemOpParams ops[2];
+      memset(ops, 0, sizeof(ops));
+      ops[0].writeValue.operation = CU_STREAM_MEM_OP_WRITE_VALUE_64;
+      ops[0].writeValue.address = (CUdeviceptr)(uintptr_t)a;
+      ops[0].writeValue.value64 = (cuuint64_t)k;
+      ops[1].writeValue.operation = CU_STREAM_MEM_OP_WRITE_VALUE_64;
+      ops[1].writeValue.address = (CUdeviceptr)(uintptr_t)hostWord;
+      ops[1].writeValue.value64 = (cuuint64_t)k;
+      if (((FnB)fb)((CUstream)s, 2, ops, 0) != CUDA_SUCCESS) res = ncclUnhandledCudaError;
+    } else if (((FnW)fw)((CUstream)s, (CUdeviceptr)(uintptr_t)a, (cuuint64_t)k, 0) != CUDA_SUCCESS) res = ncclUnhandledCudaError;
+    if (kWait) probeWaitKernel<<<1, 1, 0, s>>>(b, (uint64_t)k, limitNs, err);
+    else if (((FnW)fwait)((CUstream)s, (CUdeviceptr)(uintptr_t)b, (cuuint64_t)k, CU_STREAM_WAIT_VALUE_GEQ) != CUDA_SUCCESS) res = ncclUnhandledCudaError;
+  }
+  if (res != ncclSuccess) {
+    // release the echo kernel (and any wait already enqueued): the error word ends every bounded wait
+    uint32_t one = 1;
+    cudaMemcpyAsync(err, &one, 4, cudaMemcpyHostToDevice, 0);
+    if (fw) { ((FnW)fw)((CUstream)s, (CUdeviceptr)(uintptr_t)b, (cuuint64_t)iters + 1, 0); }
+  }
+  CUDACHECK(cudaEventRecord(e1, s));
+  CUDACHECK(cudaStreamSynchronize(s));
+  CUDACHECK(cudaStreamSynchronize(sEcho));
+  float ms = 0;
+  CUDACHECK(cudaEventElapsedTime(&ms, e0, e1));
+  uint32_t herr = 0;
+  CUDACHECK(cudaMemcpy(&herr, err, 4, cudaMemcpyDeviceToHost));
+  cudaEventDestroy(e0); cudaEventDestroy(e1);
+  cudaStreamDestroy(s); cudaStreamDestroy(sEcho);
+  cudaFree(words); cudaFree(err); cudaFreeHost(hostWord);
+  if (res != ncclSuccess) return res;
+  if (herr) { DF_WARN("stream round-trip probe: a wait ran out (%u)", herr); return dfcclTimeout; }
+  *usOut = (double)ms * 1e3 / iters;
+  return ncclSuccess;
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// What single memory operations of the daemon's control path cost on this machine, measured by one thread with the
+// nanosecond timer: reads and writes of pinned host memory (every one crosses PCIe), fences of the three scopes
+// after stores to device and to host memory, a device-memory atomic.  Results in nanoseconds per operation:
+//   [0] ld.relaxed.sys of a host word          [1] st to a host word (posted), no fence
+//   [2] st host word + fence.sys               [3] st device word + fence.sys
+//   [4] st device word + fence.gpu             [5] fence.sys with nothing outstanding
+//   [6] atomicAdd on a device word             [7] ld.relaxed.sys of a device word (L2 round trip)
+namespace dfccl {
+namespace {
+__global__ void probeMemOpsKernel(volatile uint64_t* host, volatile uint64_t* dev, int iters, uint64_t* out) {
+  if (threadIdx.x != 0 || blockIdx.x != 0) return;
+  uint64_t acc = 0, t0, t1;
+  t0 = df_now_ns();
+  for (int i = 0; i < iters; ++i) acc += ld_relaxed_sys_u64(host);
+  t1 = df_now_ns(); out[0] = (t1 - t0) / iters;
+  __threadfence_system();
+  t0 = df_now_ns();
+  for (int i = 0; i < iters; ++i) st_relaxed_sys_u64(host + 8, (uint64_t)i);
+  t1 = df_now_ns(); out[1] = (t1 - t0) / iters;
+  __threadfence_system();
+  t0 = df_now_ns();
+  for (int i = 0; i < iters; ++i) { st_relaxed_sys_u64(host + 8, (uint64_t)i); __threadfence_system(); }
+  t1 = df_now_ns(); out[2] = (t1 - t0) / iters;
+  t0 = df_now_ns();
+  for (int i = 0; i < iters; ++i) { st_relaxed_sys_u64(dev + 8, (uint64_t)i); __threadfence_system(); }
+  t1 = df_now_ns(); out[3] = (t1 - t0) / iters;
+  t0 = df_now_ns();
+  for (int i = 0; i < iters; ++i) { st_relaxed_sys_u64(dev + 8, (uint64_t)i); __threadfence(); }
+  t1 = df_now_ns(); out[4] = (t1 - t0) / iters;
+  __threadfence_system();
+  t0 = df_now_ns();
+  for (int i = 0; i < iters; ++i) __threadfence_system();
+  t1 = df_now_ns(); out[5] = (t1 - t0) / iters;
+  t0 = df_now_ns();
+  for (int i = 0; i < iters; ++i) acc += atomicAdd((unsigned long long*)(dev + 16), 1ull);
+  t1 = df_now_ns(); out[6] = (t1 - t0) / iters;
+  t0 = df_now_ns();
+  for (int i = 0; i < iters; ++i) acc += ld_relaxed_sys_u64(dev + 24);
+  t1 = df_now_ns(); out[7] = (t1 - t0) / iters;
+  out[8] = acc;
+}
+}  // namespace
+}  // namespace dfccl
+
+extern "C" __attribute__((visibility("default")))
+ncclResult_t dfcclProbeMemoryOps(int iters, uint64_t nsOut[8]) {
+  if (!nsOut || iters < 1 || iters > 10000) return ncclInvalidArgument;
+  uint64_t *host = nullptr, *dev = nullptr, *out = nullptr;
+  CUDACHECK(cudaHostAlloc((void**)&host, 256, cudaHostAllocMapped));
+  memset(host, 0, 256);
+  CUDACHECK(cudaMalloc((void**)&dev, 512));
+  CUDACHECK(cudaMemset(dev, 0, 512));
+  CUDACHECK(cudaMalloc((void**)&out, 9 * sizeof(uint64_t)));
+  probeMemOpsKernel<<<1, 32>>>(host, dev, 8, out);          // warm-up
+  probeMemOpsKernel<<<1, 32>>>(host, dev, iters, out);
+  uint64_t h[9];
+  cudaError_t e = cudaMemcpy(h, out, sizeof(h), cudaMemcpyDeviceToHost);
+  cudaFree(dev); cudaFree(out); cudaFreeHost(host);
+  if (e != cudaSuccess) { (void)cudaGetLastError(); return ncclUnhandledCudaError; }
+  for (int i = 0; i < 8; ++i) nsOut[i] = h[i];
+  return ncclSuccess;
+}

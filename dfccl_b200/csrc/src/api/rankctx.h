@@ -14,6 +14,8 @@
 #pragma once
 #include <atomic>
 #include <condition_variable>
+#include <deque>
+#include <functional>
 #include <map>
 #include <memory>
 #include <mutex>
@@ -37,6 +39,21 @@ struct CollEntry {
   uint64_t triggerSeq = 0;
   uint32_t lastStatus = 0;
   std::shared_ptr<NetRing> ring;             // network-mode communicators: this collective's own ring of connections
+};
+
+// Workers of the network path.  Every submission in flight needs a thread of its own (two ranks may submit the
+// same two collectives in opposite orders, so nothing may queue behind a blocked one); threads are created when
+// more jobs are in flight than workers exist and are kept for the life of the context, so that a training run
+// costs as many threads as it has collectives in flight at once, not one per submission.
+struct NetWorkers {
+  std::mutex mu;
+  std::condition_variable cv;
+  std::deque<std::function<void()>> jobs;
+  std::vector<std::thread> threads;
+  int idle = 0;
+  bool stop = false;
+  bool post(std::function<void()> job);       // false: no thread could be created
+  void shutdown();
 };
 
 struct DaemonLauncher {
@@ -65,9 +82,11 @@ struct ofcclRankCtx {
   std::map<int, dfccl::CollEntry> colls;
   int maxCollId = -1;
   // queues (pinned)
-  dfccl::Sqe* hostSq = nullptr;
-  volatile uint64_t* hostSqTail = nullptr;
-  volatile uint64_t* hostSqHead = nullptr;
+  uint64_t sqTail = 0;                         // entries pushed into the device ring so far (guarded by mu)
+  uint64_t sqMinFrontier = 0;                  // lower bound of what every block has consumed (refreshed when the ring looks full)
+  volatile uint64_t* hostFrontier = nullptr;   // pinned, [nBlocks]: written by the blocks
+  cudaStream_t sqStream = nullptr;             // carries nothing but the memory operations that fill the device ring
+  uint32_t* devAbort = nullptr;                // device word the daemon polls for an abort request
   volatile uint64_t* hostCq = nullptr;
   dfccl::DaemonCtl* ctl = nullptr;
   uint32_t sqCap = 0, cqCap = 0;
@@ -82,8 +101,8 @@ struct ofcclRankCtx {
   int launcherSlot = 0;
   bool holdOnWait = true;                     // dfcclStreamWait keeps an instance of the daemon resident (see dfcclSetHoldOnWait)
   std::thread poller;
-  std::vector<std::thread> netThreads;        // one per submission on a network-mode communicator (joined at destroy)
-  std::mutex netMu;
+  dfccl::NetWorkers netWorkers;               // submissions on network-mode communicators run here
+  std::vector<dfccl::CollEntry*> byId;        // collId -> entry (built at finalize: no tree walk on the hot path)
   std::atomic<int64_t> netPending{0};         // submissions running on the host network path (not the daemon's business)
   std::mutex mu;                      // submissions, callbacks table, counters
   std::condition_variable pollCv;     // poller sleeps here while nothing is outstanding

@@ -2,10 +2,9 @@
 //
 // Every block of a rank runs daemonBlockMain independently; nothing in here makes
 // one block of a GPU wait for another block of the same GPU.  Each block
-//   1. mirrors newly published submission entries from the host-pinned ring into
-//      the device-resident ring (whichever block wins the fetch lock does it, so a
-//      single block polls host memory at any time),
-//   2. consumes every entry of the device ring in order (its own frontier), and
+//   1. finds new submissions in the device-resident ring (the host writes entries
+//      and tail there with stream memory operations: no block reads host memory),
+//   2. consumes every entry of that ring in order (its own frontier), and
 //      appends the collectives it takes part in (block index < nBlocks of the
 //      collective) to its task queue,
 //   3. walks the task queue: runs each collective until it finishes or a bounded
@@ -16,43 +15,24 @@
 // Same responsibilities as the reference's daemonKernel loop
 // (src/collectives_ofccl/device/enqueue_ofccl_dev.cu:1026-1483: sqRead :85-173,
 // checkSQ7TidyTaskQ :491-627, traverseTaskQ :922-1023, voluntary quit :1107-1117,
-// state save :1374-1480), with a device-resident queue mirror, time-based instead
-// of count-based quit thresholds and a two-integer cursor per parked collective.
+// state save :1374-1480), with a device-resident queue mirror, a trigger list for
+// submissions that wait for their stream (polled without loading any context),
+// time-based instead of count-based quit thresholds and a two-integer cursor per
+// parked collective.
 #pragma once
 #include "engine.h"
 
 namespace dfccl {
 
-// Try to mirror host entries into the device ring.  Thread 0 only.
-DF_HD void fetchSubmissions(RankDev* rd) {
-  if (atomic_cas_u32(&rd->fetchLock, 0u, 1u) != 0u) return;
-  uint64_t devTail = ld_relaxed_sys_u64(&rd->devSqTail);
-  uint64_t hostTail = ld_acquire_sys_u64(rd->hostSqTail);
-  if (hostTail != devTail) {
-    // do not overwrite entries some block has not consumed yet
-    uint64_t minFront = ~0ull;
-    for (uint32_t i = 0; i < rd->nBlocks; ++i) minFront = umin64(minFront, ld_relaxed_sys_u64(&rd->frontier[i]));
-    uint64_t limit = umin64(hostTail, minFront + rd->sqCap);
-    const uint32_t mask = rd->sqCap - 1;
-    for (uint64_t s = devTail; s < limit; ++s) {
-      const uint4* src = (const uint4*)&rd->hostSq[s & mask];
-      uint4* dst = (uint4*)&rd->devSq[s & mask];
-      uint4 a = ld16(src), bq = ld16(src + 1);
-      st16(dst, a); st16(dst + 1, bq);
-    }
-    if (limit != devTail) {
-      fence_gpu();
-      st_release_sys_u64(&rd->devSqTail, limit);
-      st_release_sys_u64(rd->hostSqHead, limit);
-    }
-  }
-  fence_gpu();
-  atomic_exch_u32(&rd->fetchLock, 0u);
-}
-
 // Consume new entries of the device ring.  Thread 0 only.  Returns the number consumed.
+// A submission that waits for its stream goes to the trigger list, everything else to the task queue.
 DF_HD int consumeSubmissions(BlockShared* sh, RankDev* rd, int b) {
-  uint64_t tail = ld_acquire_sys_u64(&rd->devSqTail);
+  uint64_t tail = ld_relaxed_sys_u64(&rd->devSqTail);
+  if (tail == sh->frontier) return 0;
+  // The entries were written (by the host, through stream memory operations, each preceded by a fence) before the
+  // tail that announced them.  On this side the entry loads are issued after the branch on the tail's value, which
+  // the hardware does not speculate past; the fence keeps the compiler and the memory pipeline from hoisting them.
+  fence_gpu();
   int got = 0;
   const uint32_t mask = rd->sqCap - 1;
   while (sh->frontier < tail) {
@@ -75,18 +55,57 @@ DF_HD int consumeSubmissions(BlockShared* sh, RankDev* rd, int b) {
         saveLoaded(sh, rd, b);
         sh->loadedColl = -1;
       }
+      if ((q.flags & SQE_TRIGGERED) ? sh->nTrig >= DF_MAX_ACTIVE : sh->nActive >= DF_MAX_ACTIVE) break;   // (cannot happen: one outstanding submission per id)
     }
     ++sh->frontier;
     ++got;
     sh->stats.sqesSeen++;
     if (!mine) continue;
     d->send = q.send; d->recv = q.recv; d->trigger = q.trigger; d->cursor = 0;
-    d->epoch = d->epoch + 1; d->phase = PH_TRIGGER; d->sqeFlags = q.flags; d->status = ST_OK; d->stallSinceNs = 0;
-    if (sh->nActive < DF_MAX_ACTIVE) sh->active[sh->nActive++] = (uint16_t)coll;
+    d->epoch = d->epoch + 1; d->sqeFlags = q.flags; d->status = ST_OK; d->stallSinceNs = 0; d->patience = 0;
     trace(rd, b, TR_SQE, coll);
+    if (q.flags & SQE_TRIGGERED) {
+      d->phase = PH_TRIGGER;
+      sh->trigColl[sh->nTrig] = (uint16_t)coll; sh->trigVal[sh->nTrig] = (uint32_t)q.trigger; ++sh->nTrig;
+    } else {
+      d->phase = PH_COPY_IN;          // runColl skips ahead to the first phase that has work
+      sh->active[sh->nActive++] = (uint16_t)coll;
+      trace(rd, b, TR_START, coll);
+    }
   }
-  st_release_sys_u64(&rd->frontier[b], sh->frontier);
+  if (got) st_relaxed_sys_u64(&rd->hostFrontier[b], sh->frontier);   // posted store: the host reads it when its ring looks full
   return got;
+}
+
+// Look at the trigger words of every submission that waits for its stream: one thread per entry, no context is
+// loaded.  Released ones join the task queue in list order.  Everybody calls it; returns the number released.
+DF_HD uint32_t pollTriggers(BlockShared* sh, RankDev* rd, int b) {
+  const int tid = df_tid(), nt = df_nthreads();
+  const uint32_t nTrig = sh->nTrig;
+  if (tid == 0) sh->trigFired = 0;
+  df_sync();
+  for (uint32_t i = tid; i < nTrig; i += nt) {
+    const uint32_t have = (uint32_t)ld_relaxed_sys_u64(&rd->trigger[sh->trigColl[i]]);
+    if ((int32_t)(have - sh->trigVal[i]) >= 0) { sh->trigColl[i] |= 0x8000u; atomic_add_u32(&sh->trigFired, 1u); }
+  }
+  df_sync();
+  const uint32_t fired = sh->trigFired;
+  if (fired && tid == 0) {
+    fence_sys();                     // what the stream's producers wrote, before anything this block does with it
+    uint32_t w = 0;
+    for (uint32_t i = 0; i < nTrig; ++i) {
+      const uint16_t e = sh->trigColl[i];
+      if (e & 0x8000u) {
+        const int coll = e & 0x7fff;
+        rd->dyn[(uint64_t)b * rd->maxColls + coll].phase = PH_COPY_IN;
+        if (sh->nActive < DF_MAX_ACTIVE) sh->active[sh->nActive++] = (uint16_t)coll;
+        trace(rd, b, TR_START, coll);
+      } else { sh->trigColl[w] = e; sh->trigVal[w] = sh->trigVal[i]; ++w; }
+    }
+    sh->nTrig = w;
+  }
+  if (fired) df_sync();
+  return fired;
 }
 
 DF_HD void blockRestore(BlockShared* sh, RankDev* rd, int b) {
@@ -94,13 +113,14 @@ DF_HD void blockRestore(BlockShared* sh, RankDev* rd, int b) {
   BlockSaved* sv = &rd->saved[b];
   if (tid == 0) {
     sh->loadedColl = -1; sh->standalone = 0; sh->dynDirty = 0; sh->quit = 0; sh->abortSeen = 0;
-    sh->frontier = sv->frontier; sh->nActive = sv->nActive;
+    sh->frontier = sv->frontier; sh->nActive = sv->nActive; sh->nTrig = sv->nTrig;
     DevStats z = {};
     sh->stats = z;
     sv->exited = 0;
   }
   df_sync();
   for (uint32_t i = tid; i < sh->nActive; i += nt) sh->active[i] = sv->active[i];
+  for (uint32_t i = tid; i < sh->nTrig; i += nt) { sh->trigColl[i] = sv->trigColl[i]; sh->trigVal[i] = sv->trigVal[i]; }
   df_sync();
 }
 
@@ -109,16 +129,18 @@ DF_HD void blockPark(BlockShared* sh, RankDev* rd, int b) {
   saveLoaded(sh, rd, b);
   BlockSaved* sv = &rd->saved[b];
   for (uint32_t i = tid; i < sh->nActive; i += nt) sv->active[i] = sh->active[i];
+  for (uint32_t i = tid; i < sh->nTrig; i += nt) { sv->trigColl[i] = sh->trigColl[i]; sv->trigVal[i] = sh->trigVal[i]; }
   df_sync();
   if (tid == 0) {
-    sv->frontier = sh->frontier; sv->nActive = sh->nActive;
+    sv->frontier = sh->frontier; sv->nActive = sh->nActive; sv->nTrig = sh->nTrig;
     // fold this launch's counters into the totals the host reads
     DevStats* g = &rd->stats[b];
     g->ctxSwitches += sh->stats.ctxSwitches; g->ctxSaves += sh->stats.ctxSaves; g->ctxLoads += sh->stats.ctxLoads;
     g->waitPolls += sh->stats.waitPolls; g->waitTimeouts += sh->stats.waitTimeouts;
     g->bytesReduced += sh->stats.bytesReduced; g->bytesCopied += sh->stats.bytesCopied;
     g->totalSwitchNs += sh->stats.totalSwitchNs; g->sqesSeen += sh->stats.sqesSeen; g->collsDone += sh->stats.collsDone;
-    g->visits += sh->stats.visits;
+    g->visits += sh->stats.visits; g->yields += sh->stats.yields; g->passes += sh->stats.passes;
+    g->nsTriggers += sh->stats.nsTriggers; g->nsWalk += sh->stats.nsWalk; g->nsQueues += sh->stats.nsQueues;
     if (sh->stats.maxSwitchNs > g->maxSwitchNs) g->maxSwitchNs = sh->stats.maxSwitchNs;
     trace(rd, b, TR_QUIT, (int)sh->quit);
     fence_sys();
@@ -139,15 +161,19 @@ DF_HD void daemonBlockMain(RankDev* rd, int b, BlockShared* sh) {
   const int tid = df_tid();
   blockRestore(sh, rd, b);
   if (tid == 0) trace(rd, b, TR_LAUNCH, 0);
-  uint64_t lastUseful = df_now_ns();     // only thread 0's copy is ever consulted
+  uint64_t lastUseful = df_now_ns();     // only thread 0's copies of these are ever consulted
   const uint64_t bornNs = lastUseful;
-  uint64_t lastAbortCheck = 0;
+  uint64_t lastSlowCheck = 0;
+  uint32_t winding = 0;
   uint32_t idleBackoff = 32;
 
   for (;;) {
-    // ---- 1. task queue traversal (every value steering control flow here is block-uniform)
+    // ---- 0. submissions waiting for their stream (every value steering control flow here is block-uniform)
     bool progressed = false;
-    uint32_t trigWaits = 0;          // collectives whose stream has not released them yet
+    const uint64_t tPass = tid == 0 ? df_now_ns() : 0;
+    if (sh->nTrig && pollTriggers(sh, rd, b)) progressed = true;
+    const uint64_t tWalk = tid == 0 ? df_now_ns() : 0;
+    // ---- 1. task queue traversal
     const uint32_t nAct = sh->nActive;
     for (uint32_t i = 0; i < nAct; ++i) {
       const int coll = sh->active[i];
@@ -157,30 +183,34 @@ DF_HD void daemonBlockMain(RankDev* rd, int b, BlockShared* sh) {
       const uint32_t budget = rd->spinBudget * ((i == 0 || nAct == 1) ? rd->headTries : 1u);
       bool moved = false;
       int rc = runColl(sh, rd, b, coll, budget, &moved);
-      if (rc == RC_DONE || moved) progressed = true;
-      if (rc == RC_STALLED && sh->dyn.phase == PH_TRIGGER) ++trigWaits;
+      if (rc == RC_DONE || rc == RC_YIELD || moved) progressed = true;
       if (tid == 0) {
         sh->stats.visits++;
         if (rc == RC_DONE) sh->active[i] = 0xffff;
       }
+      // a collective released by its stream should not wait for a walk over a long queue of stalled ones
+      if (sh->nTrig && i + 1 < nAct && pollTriggers(sh, rd, b)) progressed = true;
     }
     df_sync();
     // ---- 2. compaction, new submissions, idle decision: thread 0 decides, everybody obeys
     if (tid == 0) {
+      sh->stats.passes++;
       uint32_t w = 0;
       for (uint32_t i = 0; i < sh->nActive; ++i) if (sh->active[i] != 0xffff) sh->active[w++] = sh->active[i];
       sh->nActive = w;
+      const uint64_t now = df_now_ns();
+      sh->stats.nsTriggers += tWalk - tPass; sh->stats.nsWalk += now - tWalk;
+      // Words that change rarely are sampled rarely: the abort request and the "somebody left" word.  Every
+      // 20 us, or right away when this pass achieved nothing.
+      const bool slow = now - lastSlowCheck > 20000;
+      if (slow) {
+        sh->abortSeen = abortRequested(rd) ? 1u : 0u;
+        lastSlowCheck = now;
+      }
+      if (slow || !progressed || winding) winding = ld_relaxed_sys_u32(&rd->quitting);
       // once one block of this rank has left voluntarily the others take no new work and follow as
       // soon as they cannot progress: a collective needs all its blocks, so the relaunch comes sooner
-      const bool winding = ld_acquire_sys_u32(&rd->quitting) != 0;
-      if (!winding) {
-        if (ld_relaxed_sys_u64(&rd->devSqTail) == sh->frontier) fetchSubmissions(rd);
-        if (consumeSubmissions(sh, rd, b) > 0) progressed = true;
-      }
-      const uint64_t now = df_now_ns();
-      // the abort word lives in host memory: one read over PCIe costs more than a whole pass over a short
-      // task queue, so it is sampled every 20 us instead of every pass
-      if (now - lastAbortCheck > 20000) { sh->abortSeen = ctl_load(&rd->ctl->abortFlag); lastAbortCheck = now; }
+      if (!winding && consumeSubmissions(sh, rd, b) > 0) progressed = true;
       if (sh->abortSeen) sh->quit = 3;
       else if (rd->maxLifetimeNs && now - bornNs > rd->maxLifetimeNs && !sh->quit) {
         // safety net: no instance of the daemon outlives this, whatever its state; the host relaunches it
@@ -190,7 +220,7 @@ DF_HD void daemonBlockMain(RankDev* rd, int b, BlockShared* sh) {
       else if (progressed) lastUseful = now;
       // only waiting for streams to release submissions: nothing a resident daemon can speed up, and
       // the host relaunches it when a trigger fires, so leave as quickly as when idle
-      else if (!sh->quit && (winding || now - lastUseful > ((sh->nActive && trigWaits < nAct) ? rd->stallQuitNs : rd->idleQuitNs))) {
+      else if (!sh->quit && (winding || now - lastUseful > (sh->nActive ? rd->stallQuitNs : rd->idleQuitNs))) {
         // a stream parked on one of this context's completion words must not depend on a host thread's
         // relaunch: while the host holds the instance it only leaves by age (or with the others)
         if (!winding && ctl_load(&rd->ctl->hold)) lastUseful = now;
@@ -200,11 +230,12 @@ DF_HD void daemonBlockMain(RankDev* rd, int b, BlockShared* sh) {
         }
       }
       sh->ctl0 = progressed ? 1 : 0;
+      sh->stats.nsQueues += df_now_ns() - now;
     }
     df_sync();
     if (sh->quit) break;
     if (sh->ctl0) idleBackoff = 32;
-    else if (sh->nActive == 0) {            // nothing to do: poll gently
+    else if (sh->nActive == 0 && sh->nTrig == 0) {            // nothing to do: poll gently
       df_backoff(idleBackoff);
       if (idleBackoff < 1024) idleBackoff *= 2;
     }

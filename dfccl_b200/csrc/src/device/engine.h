@@ -29,11 +29,6 @@
 #include "nvls.h"
 #include "platform.h"
 #include "types.h"
-#if !defined(__CUDA_ARCH__)
-#include <cstdio>
-#include <cstdlib>
-#endif
-
 namespace dfccl {
 
 enum RunResult : int { RC_DONE = 0, RC_STALLED = 1, RC_YIELD = 2 };
@@ -55,7 +50,15 @@ struct BlockShared {
   uint32_t quit;                 // 1 = voluntary, 2 = final, 3 = abort
   uint32_t abortSeen;            // the host's abort flag as last read by thread 0 (the flag lives in host memory: one
                                  // read costs a PCIe round trip, so it is sampled once per scheduler pass, not per wait)
+  // peers' buffer offsets of the running submission, fetched by one lane per peer (one memory round trip for all)
+  uint64_t peerSend[DF_MAX_RANKS], peerRecv[DF_MAX_RANKS];
+  // stream-ordered submissions not yet released by their stream: polled all at once, one thread per entry,
+  // without loading any context; a released one joins the task queue
+  uint32_t nTrig;
+  uint32_t trigFired;
   uint16_t active[DF_MAX_ACTIVE];
+  uint16_t trigColl[DF_MAX_ACTIVE];
+  uint32_t trigVal[DF_MAX_ACTIVE];  // low 32 bits of the value the trigger word must reach
 };
 
 DF_HD void trace(RankDev* rd, int b, uint16_t ev, int coll) {
@@ -66,6 +69,10 @@ DF_HD void trace(RankDev* rd, int b, uint16_t ev, int coll) {
 }
 
 DF_HD uint64_t umin64(uint64_t a, uint64_t b) { return a < b ? a : b; }
+
+DF_HD bool abortRequested(const RankDev* rd) {
+  return ctl_load(rd->abortWord ? rd->abortWord : &rd->ctl->abortFlag) != 0;
+}
 
 // [beg,end) of part idx when [0,total) is cut into nparts pieces on `align` boundaries
 DF_HD void partRange(uint64_t total, int nparts, int idx, uint64_t align, uint64_t* beg, uint64_t* end) {
@@ -162,7 +169,7 @@ DF_HD bool boundedWait(BlockShared* sh, RankDev* rd, int b, int which, uint32_t 
         }
       }
       bool laneStop = false;
-      if ((spins & 255) == 255 && lane == 0) laneStop = ctl_load(&rd->ctl->abortFlag) != 0;
+      if ((spins & 255) == 255 && lane == 0) laneStop = abortRequested(rd);
       ok = df_warp_all(laneOk);
       const bool stop = !df_warp_all(!laneStop);      // uniform: every lane leaves the loop together
       ++spins;
@@ -182,7 +189,7 @@ DF_HD bool noteStall(BlockShared* sh, RankDev* rd) {
   if (df_tid() == 0) {
     uint64_t now = df_now_ns();
     sh->ctl0 = 0;
-    if (sh->standalone ? (ctl_load(&rd->ctl->abortFlag) != 0) : (sh->abortSeen != 0)) { sh->dyn.status = ST_ABORTED; sh->ctl0 = 1; }
+    if (sh->standalone ? abortRequested(rd) : (sh->abortSeen != 0)) { sh->dyn.status = ST_ABORTED; sh->ctl0 = 1; }
     else if (sh->dyn.stallSinceNs == 0) { sh->dyn.stallSinceNs = now; sh->dynDirty = 1; }
     else if (rd->waitTimeoutNs && now - sh->dyn.stallSinceNs > rd->waitTimeoutNs) {
       sh->dyn.status = ST_TIMEOUT; sh->ctl0 = 1; sh->stats.waitTimeouts++;
@@ -198,16 +205,26 @@ DF_HD uint64_t mySendOff(const BlockShared* sh) {
 DF_HD uint64_t myRecvOff(const BlockShared* sh) {
   return (sh->dyn.sqeFlags & SQE_RECV_STAGED) ? sh->cs.stagingRecvOff : sh->dyn.recv;
 }
-DF_HD const char* sendPtrOf(const BlockShared* sh, int b, int j) {
+// Offsets the peers posted with their arrival, one lane per peer; everybody calls it, ends with a barrier.
+DF_HD void fetchPeerOffsets(BlockShared* sh, int b) {
   const CollStatic* c = &sh->cs;
-  uint64_t off = j == c->rank ? mySendOff(sh) : ld_relaxed_sys_u64(&c->myFlags[(uint64_t)b * c->nranks + j].sendOff);
-  return c->peerHeap[j] + off;
+  const int n = c->nranks, j = df_tid();
+  if (j < n) {
+    const FlagSlot* f = &c->myFlags[(uint64_t)b * n + j];
+    sh->peerSend[j] = j == c->rank ? mySendOff(sh) : ld_relaxed_sys_u64(&f->sendOff);
+    sh->peerRecv[j] = j == c->rank ? myRecvOff(sh) : ld_relaxed_sys_u64(&f->recvOff);
+  }
+#if !DF_DEVICE_CODE
+  for (int k = 1; k < n; ++k) {                  // one host thread plays the whole block
+    const FlagSlot* f = &c->myFlags[(uint64_t)b * n + k];
+    sh->peerSend[k] = k == c->rank ? mySendOff(sh) : ld_relaxed_sys_u64(&f->sendOff);
+    sh->peerRecv[k] = k == c->rank ? myRecvOff(sh) : ld_relaxed_sys_u64(&f->recvOff);
+  }
+#endif
+  df_sync();
 }
-DF_HD char* recvPtrOf(const BlockShared* sh, int b, int j) {
-  const CollStatic* c = &sh->cs;
-  uint64_t off = j == c->rank ? myRecvOff(sh) : ld_relaxed_sys_u64(&c->myFlags[(uint64_t)b * c->nranks + j].recvOff);
-  return c->peerHeap[j] + off;
-}
+DF_HD const char* sendPtrOf(const BlockShared* sh, int j) { return sh->cs.peerHeap[j] + sh->peerSend[j]; }
+DF_HD char* recvPtrOf(const BlockShared* sh, int j) { return sh->cs.peerHeap[j] + sh->peerRecv[j]; }
 
 // Schedules in which a user buffer is touched by this rank only use it where it is (no staging copy even when it
 // lies outside the symmetric heap): both buffers of the push schedule, the input of a multimem all-gather, the
@@ -245,15 +262,25 @@ DF_HD void pushOut(BlockShared* sh, int b) {
   df_sync();
 }
 
-// ---- PH_DATA: thread 0 builds the pointer lists, everybody moves the data
-DF_HD void dataPhase(BlockShared* sh, RankDev* rd, int b) {
+// ---- PH_DATA: thread 0 builds the pointer lists, everybody moves the data.
+// The block's share is moved in slices of `rd->sliceBytes` (0 = all at once): after a slice the cursor is saved and
+// the function returns true when more is left, so that the caller can hand the block to another collective and
+// come back later - the resumable data phase (reference: slice / offset saved inside one primitive and
+// currentStep / gridOffset in the ring loop, src/collectives_ofccl/device/ofccl_prims_simple.h:239-244,326-346,
+// ofccl_all_reduce.h:86-93,192-205).  A slice never waits for anybody, so leaving between two slices has no side
+// effect beyond the cursor.  `sh->ctl0` tells the caller whether anything else wants the block.
+DF_HD bool dataPhase(BlockShared* sh, RankDev* rd, int b) {
   const CollStatic* c = &sh->cs;
   const int n = c->nranks, me = c->rank;
   const uint64_t es = dtypeSize(c->inType), eo = dtypeSize(c->outType);
-  bool reduce = true, nvls = false;
-  int nvlsKind = 0;          // 3 = reduce-scatter, 4 = all-gather on the multimem schedule
+  // schedules that read or write peers' buffers need the offsets the peers posted
+  const bool needOffsets = n > 1 && c->algo != dfcclAlgoPush && c->algo != dfcclAlgoNvls;
+  if (needOffsets) fetchPeerOffsets(sh, b);
+  else if (df_tid() == 0) { sh->peerSend[me] = mySendOff(sh); sh->peerRecv[me] = myRecvOff(sh); }   // thread 0 is the only reader
   if (df_tid() == 0) {
     DataArgs* a = &sh->args;
+    bool reduce = true, nvls = false;
+    int nvlsKind = 0;          // 3 = reduce-scatter, 4 = all-gather on the multimem schedule
     a->scale = c->scale; a->postDiv = c->postDiv; a->nsrc = 0; a->ndst = 0; a->n = 0;
     uint64_t bb, be;
     switch (c->kind) {
@@ -277,15 +304,15 @@ DF_HD void dataPhase(BlockShared* sh, RankDev* rd, int b) {
           a->n = se - sb;
           nvls = true;
         } else if (c->algo == dfcclAlgoOneShot || n == 1) {
-          for (int j = 0; j < n; ++j) a->src[a->nsrc++] = sendPtrOf(sh, b, j) + bb * es;
-          a->dst[a->ndst++] = recvPtrOf(sh, b, me) + bb * eo;
+          for (int j = 0; j < n; ++j) a->src[a->nsrc++] = sendPtrOf(sh, j) + bb * es;
+          a->dst[a->ndst++] = recvPtrOf(sh, me) + bb * eo;
           a->n = be - bb;
         } else {
           uint64_t sb, se;
           partRange(be - bb, n, me, 16, &sb, &se);
           sb += bb; se += bb;
-          for (int k = 0; k < n; ++k) { int j = (me + k) % n; a->src[a->nsrc++] = sendPtrOf(sh, b, j) + sb * es; }
-          for (int k = 0; k < n; ++k) { int j = (me + k) % n; a->dst[a->ndst++] = recvPtrOf(sh, b, j) + sb * eo; }
+          for (int k = 0; k < n; ++k) { int j = (me + k) % n; a->src[a->nsrc++] = sendPtrOf(sh, j) + sb * es; }
+          for (int k = 0; k < n; ++k) { int j = (me + k) % n; a->dst[a->ndst++] = recvPtrOf(sh, j) + sb * eo; }
           a->n = se - sb;
         }
         break;
@@ -295,8 +322,8 @@ DF_HD void dataPhase(BlockShared* sh, RankDev* rd, int b) {
         uint64_t sb, se;
         partRange(be - bb, n, me, 16, &sb, &se);
         sb += bb; se += bb;
-        for (int k = 0; k < n; ++k) { int j = (me + k) % n; a->src[a->nsrc++] = sendPtrOf(sh, b, j) + sb * es; }
-        a->dst[a->ndst++] = recvPtrOf(sh, b, c->root) + sb * eo;
+        for (int k = 0; k < n; ++k) { int j = (me + k) % n; a->src[a->nsrc++] = sendPtrOf(sh, j) + sb * es; }
+        a->dst[a->ndst++] = recvPtrOf(sh, c->root) + sb * eo;
         a->n = se - sb;
         break;
       }
@@ -311,8 +338,8 @@ DF_HD void dataPhase(BlockShared* sh, RankDev* rd, int b) {
           nvlsKind = 3;
           break;
         }
-        for (int k = 0; k < n; ++k) { int j = (me + k) % n; a->src[a->nsrc++] = sendPtrOf(sh, b, j) + ((uint64_t)me * c->count + bb) * es; }
-        a->dst[a->ndst++] = recvPtrOf(sh, b, me) + bb * eo;
+        for (int k = 0; k < n; ++k) { int j = (me + k) % n; a->src[a->nsrc++] = sendPtrOf(sh, j) + ((uint64_t)me * c->count + bb) * es; }
+        a->dst[a->ndst++] = recvPtrOf(sh, me) + bb * eo;
         a->n = be - bb;
         break;
       }
@@ -329,10 +356,10 @@ DF_HD void dataPhase(BlockShared* sh, RankDev* rd, int b) {
           nvlsKind = 4;
           break;
         }
-        a->src[0] = sendPtrOf(sh, b, me) + bb; a->nsrc = 1;
+        a->src[0] = sendPtrOf(sh, me) + bb; a->nsrc = 1;
         for (int k = 0; k < n; ++k) {
           int j = (me + k) % n;
-          char* d = recvPtrOf(sh, b, j) + (uint64_t)me * bytes + bb;
+          char* d = recvPtrOf(sh, j) + (uint64_t)me * bytes + bb;
           if (d != a->src[0]) a->dst[a->ndst++] = d;          // in-place: my own slot already holds it
         }
         a->n = be - bb;
@@ -342,22 +369,36 @@ DF_HD void dataPhase(BlockShared* sh, RankDev* rd, int b) {
         reduce = false;
         uint64_t bytes = c->count * es;
         partRange(bytes, c->nBlocks, b, 16, &bb, &be);
-        a->src[0] = sendPtrOf(sh, b, c->root) + bb; a->nsrc = 1;
-        char* d = recvPtrOf(sh, b, me) + bb;
+        a->src[0] = sendPtrOf(sh, c->root) + bb; a->nsrc = 1;
+        char* d = recvPtrOf(sh, me) + bb;
         if (d != a->src[0]) a->dst[a->ndst++] = d;
         a->n = be - bb;
         break;
       }
       default: break;
     }
+    // ---- the slice of this visit: [cursor, cursor + slice) of the block's share, in the unit of a->n (elements
+    // for reducing kinds, bytes for copying kinds); slices are multiples of 16 units, so every pointer keeps its
+    // 16-byte alignment
+    const uint64_t total = a->n;
+    const uint64_t unitIn = reduce ? es : 1, unitOut = reduce ? eo : 1;
+    uint64_t cur = sh->dyn.cursor < total ? sh->dyn.cursor : total;
+    uint64_t win = total - cur;
+    if (rd->sliceBytes && !sh->standalone) {
+      uint64_t sliceUnits = rd->sliceBytes / unitIn & ~(uint64_t)15;
+      if (sliceUnits < 16) sliceUnits = 16;
+      if (win > sliceUnits) win = sliceUnits;
+    }
+    if (cur) {
+      for (int j = 0; j < a->nsrc; ++j) a->src[j] += cur * unitIn;
+      for (int j = 0; j < a->ndst; ++j) a->dst[j] += cur * unitOut;
+    }
+    a->n = win;
+    sh->ctl64 = cur + win < total ? cur + win : 0;             // the next cursor; 0 = this was the last slice
     sh->ctl1 = nvlsKind ? nvlsKind : nvls ? 2 : reduce ? 1 : 0;
     if (reduce) sh->stats.bytesReduced += a->n * es * a->nsrc; else sh->stats.bytesCopied += a->n * (a->ndst ? a->ndst : 0);
   }
   df_sync();
-#if !DF_DEVICE_CODE
-  if (getenv("DFCCL_DEBUG_DATA")) fprintf(stderr, "[r%d b%d] kind %d algo %d op %d in %d nsrc %d ndst %d n %llu src0 %p src1 %p dst0 %p scale %f\n", me, b, c->kind, c->algo, c->op, c->inType,
-      sh->args.nsrc, sh->args.ndst, (unsigned long long)sh->args.n, sh->args.src[0], sh->args.src[1], sh->args.dst[0], sh->args.scale);
-#endif
   if (sh->args.n != 0 && sh->args.ndst != 0) {
     if (sh->ctl1 == 2) {
       if (!nvlsDispatch(c->inType, c->outType, c->mcHeap, c->nvlsPeers, n, (uint64_t)(uintptr_t)sh->args.src[0],
@@ -374,6 +415,17 @@ DF_HD void dataPhase(BlockShared* sh, RankDev* rd, int b) {
     }
   }
   df_sync();
+  if (df_tid() == 0) {
+    sh->ctl0 = 0;
+    if (sh->ctl64) {
+      sh->dyn.cursor = sh->ctl64; sh->dynDirty = 1;
+      // anything else for this block?  queued collectives, submissions waiting for their stream, or entries of the
+      // device ring this block has not consumed yet
+      sh->ctl0 = (sh->nActive > 1 || sh->nTrig > 0 || ld_relaxed_sys_u64(&rd->devSqTail) != sh->frontier) ? 1 : 0;
+    }
+  }
+  df_sync();
+  return sh->ctl64 != 0;
 }
 
 // ---- staging copies for buffers outside the symmetric heap
@@ -405,6 +457,20 @@ DF_HD void stageCopy(BlockShared* sh, int b, bool in) {
 }
 
 // ---- completion: count blocks; the last one publishes the device flag and the CQE
+DF_HD void publishCompletion(RankDev* rd, int coll, uint32_t st, uint32_t epoch) {
+  // The device flag releases a stream of THIS GPU (its wait is a stream memory operation, the consumers are kernels
+  // launched behind it): everything the blocks wrote here is ordered before it by a fence of GPU scope, a quarter
+  // of the cost of a system-scope one.  (What the blocks wrote into peers' memory was ordered by the fence before
+  // their done flags, and this rank's result was complete when every peer's done flag had arrived.)
+  fence_gpu();
+  st_relaxed_sys_u64(&rd->doneEpoch[coll], ((uint64_t)st << 56) | epoch);
+  // the host's entry: a host thread may read the result right after the callback, so the data is ordered system-wide
+  unsigned long long idx = atomic_add_u64((unsigned long long*)&rd->devCqTail, 1ull);
+  uint32_t gen = (uint32_t)(idx / rd->cqCap) + 1u;
+  fence_sys();
+  st_relaxed_sys_u64(&rd->hostCq[idx & (rd->cqCap - 1)], cqeEncode(gen, st, (uint32_t)coll));
+}
+
 DF_HD void completeColl(BlockShared* sh, RankDev* rd, int b) {
   if (sh->standalone) {                           // stream-ordered kernel: report errors only
     if (df_tid() == 0 && sh->dyn.status != ST_OK) rd->ctl->pad = sh->dyn.status;
@@ -414,32 +480,74 @@ DF_HD void completeColl(BlockShared* sh, RankDev* rd, int b) {
   if (df_tid() == 0) {
     const int coll = sh->loadedColl;
     uint32_t status = sh->dyn.status;
+    // the cached copy stays authoritative while the collective is loaded; it reaches global memory when another
+    // collective is loaded, when the block parks, or when the next submission of this id is consumed
     sh->dyn.phase = PH_COMPLETE;
-    rd->dyn[(uint64_t)b * rd->maxColls + coll] = sh->dyn;
-    sh->dynDirty = 0;
+    sh->dynDirty = 1;
     sh->stats.collsDone++;
-    if (status != ST_OK) atomic_add_u32(&rd->failCount[coll], status << 16 | 1u);
-    fence_gpu();
-    uint32_t prev = atomic_add_u32(&rd->doneCount[coll], 1u);
-    if (prev + 1 == (uint32_t)sh->cs.nBlocks) {
-      uint32_t fails = atomic_exch_u32(&rd->failCount[coll], 0u);
-      atomic_exch_u32(&rd->doneCount[coll], 0u);
-      uint32_t st = fails ? (fails >> 16) / (fails & 0xffff) : ST_OK;   // all failing blocks report the same cause
-      if (st > 255) st = ST_TIMEOUT;
-      unsigned long long idx = atomic_add_u64((unsigned long long*)&rd->devCqTail, 1ull);
-      uint32_t gen = (uint32_t)(idx / rd->cqCap) + 1u;
-      fence_sys();                  // everything every block did for this submission, before either word below
-      st_relaxed_sys_u64(&rd->doneEpoch[coll], ((uint64_t)st << 56) | sh->dyn.epoch);
-      st_relaxed_sys_u64(&rd->hostCq[idx & (rd->cqCap - 1)], cqeEncode(gen, st, (uint32_t)coll));
+    if (sh->cs.nBlocks == 1) {
+      publishCompletion(rd, coll, status > 255 ? (uint32_t)ST_TIMEOUT : status, sh->dyn.epoch);
+    } else {
+      if (status != ST_OK) atomic_add_u32(&rd->failCount[coll], status << 16 | 1u);
+      fence_gpu();
+      uint32_t prev = atomic_add_u32(&rd->doneCount[coll], 1u);
+      if (prev + 1 == (uint32_t)sh->cs.nBlocks) {
+        uint32_t fails = atomic_exch_u32(&rd->failCount[coll], 0u);
+        atomic_exch_u32(&rd->doneCount[coll], 0u);
+        uint32_t st = fails ? (fails >> 16) / (fails & 0xffff) : ST_OK;   // all failing blocks report the same cause
+        if (st > 255) st = ST_TIMEOUT;
+        publishCompletion(rd, coll, st, sh->dyn.epoch);
+      }
     }
     trace(rd, b, TR_DONE, coll);
   }
   df_sync();
 }
 
-// Run the loaded-or-to-be-loaded collective until it completes or a wait runs out.
+// The first phase from `phase` on that has something to do for the loaded submission (a phase change costs two
+// block-wide barriers, a small collective would otherwise spend more time changing phases than moving data).
+DF_HD int nextPhase(const BlockShared* sh, int phase) {
+  const CollStatic* c = &sh->cs;
+  const int n = c->nranks, me = c->rank;
+  for (;; ++phase) {
+    switch (phase) {
+      case PH_COPY_IN:
+        if ((sh->dyn.sqeFlags & SQE_SEND_STAGED) && !rawSend(c) && !(c->kind == dfcclCollBroadcast && me != c->root)) return phase;
+        break;
+      case PH_POST_ARRIVE: case PH_WAIT_ARRIVE:
+        if (n > 1) return phase;
+        break;
+      case PH_POST_DONE: case PH_WAIT_DONE:
+        if (n > 1 && c->algo != dfcclAlgoPush) return phase;
+        break;
+      case PH_COPY_OUT:
+        if ((sh->dyn.sqeFlags & SQE_RECV_STAGED) && !rawRecv(c) && !(c->kind == dfcclCollReduce && me != c->root)) return phase;
+        break;
+      default: return phase;          // PH_DATA, PH_COMPLETE (PH_TRIGGER is never skipped to)
+    }
+  }
+}
+
+// A wait of the loaded collective with its adaptive budget.  The budget is what the scheduler grants or, if larger,
+// the patience this submission has earned: after a wait succeeded within s polls the next waits of the same
+// submission may spend factor x s polls (capped), because a collective whose peers are demonstrably in it is worth
+// staying with (reference: RECV_SUCCESS_FACTOR, src/collectives_ofccl/device/ofccl_prims_simple.h:79-88,143-151).
+DF_HD bool patientWait(BlockShared* sh, RankDev* rd, int b, int which, uint32_t budget) {
+  const uint32_t eff = budget > sh->dyn.patience ? budget : sh->dyn.patience;
+  const bool ok = boundedWait(sh, rd, b, which, eff);
+  if (ok && df_tid() == 0 && !sh->standalone && rd->recvSuccessFactor) {
+    uint64_t p = (uint64_t)sh->waitSpins * rd->recvSuccessFactor;
+    const uint64_t cap = (uint64_t)rd->spinBudget * 64u;
+    if (p > cap) p = cap;
+    if (p > sh->dyn.patience) { sh->dyn.patience = (uint32_t)p; sh->dynDirty = 1; }
+  }
+  return ok;
+}
+
+// Run the loaded-or-to-be-loaded collective until it completes, a wait runs out (RC_STALLED) or its data phase
+// reaches a slice boundary while other work is queued (RC_YIELD).
 // `budget` is the number of polls one wait may spend.
-// `*moved` is set when at least one phase was left behind during this visit.
+// `*moved` is set when at least one phase (or slice) was left behind during this visit.
 DF_HD int runColl(BlockShared* sh, RankDev* rd, int b, int coll, uint32_t budget, bool* moved) {
   if (!sh->standalone) loadColl(sh, rd, b, coll);
   const int n = sh->cs.nranks, me = sh->cs.rank;
@@ -450,13 +558,13 @@ DF_HD int runColl(BlockShared* sh, RankDev* rd, int b, int coll, uint32_t budget
     if (phase != entryPhase) *moved = true;
     switch (phase) {
       case PH_TRIGGER:
+        // (the daemon releases stream-ordered submissions from its trigger list and enters at PH_COPY_IN; this
+        // phase serves entries that were parked here by an earlier instance)
         if (sh->dyn.sqeFlags & SQE_TRIGGERED) {
-          // one look is enough: the word is local, nobody is closer to writing it because this block
-          // keeps polling, and every poll spent here delays the collectives queued behind this one
           if (!boundedWait(sh, rd, b, 2, sh->standalone ? budget : 1u)) { if (noteStall(sh, rd)) { setPhase(sh, PH_COMPLETE); break; } return RC_STALLED; }
         }
-        if (tid == 0) trace(rd, b, TR_START, coll);          // released by its stream (or not stream-ordered)
-        setPhase(sh, PH_COPY_IN);
+        if (tid == 0) trace(rd, b, TR_START, coll);
+        setPhase(sh, nextPhase(sh, PH_COPY_IN));
         break;
       case PH_COPY_IN:
         if ((sh->dyn.sqeFlags & SQE_SEND_STAGED) && !rawSend(&sh->cs)) {
@@ -464,7 +572,7 @@ DF_HD int runColl(BlockShared* sh, RankDev* rd, int b, int coll, uint32_t budget
           if (needed) stageCopy(sh, b, true);
           if (tid == 0) fence_sys();
         }
-        setPhase(sh, PH_POST_ARRIVE);
+        setPhase(sh, nextPhase(sh, PH_POST_ARRIVE));
         break;
       case PH_POST_ARRIVE: {
         if (sh->cs.algo == dfcclAlgoPush && n > 1) {
@@ -485,17 +593,31 @@ DF_HD int runColl(BlockShared* sh, RankDev* rd, int b, int coll, uint32_t budget
         break;
       }
       case PH_WAIT_ARRIVE:
-        if (n > 1 && !boundedWait(sh, rd, b, 0, budget)) { if (noteStall(sh, rd)) { setPhase(sh, PH_COMPLETE); break; } return RC_STALLED; }
-        if (tid == 0) trace(rd, b, TR_RESUME, coll);         // every peer has arrived
+        if (n > 1 && !patientWait(sh, rd, b, 0, budget)) {
+          if (noteStall(sh, rd)) { setPhase(sh, PH_COMPLETE); break; }
+          if (tid == 0) trace(rd, b, TR_STALL, coll);
+          return RC_STALLED;
+        }
+        if (tid == 0) trace(rd, b, TR_ARRIVED, coll);
         setPhase(sh, PH_DATA);
         break;
-      case PH_DATA:
+      case PH_DATA: {
         if (tid == 0) trace(rd, b, TR_DATA_BEGIN, coll);
-        dataPhase(sh, rd, b);
+        const bool more = dataPhase(sh, rd, b);
         if (tid == 0) trace(rd, b, TR_DATA_END, coll);
-        // push schedule: nobody reads my buffers and my slots are not reused before the peers' next-but-one call
-        setPhase(sh, (sh->cs.algo == dfcclAlgoPush && n > 1) ? PH_COMPLETE : PH_POST_DONE);
+        if (more) {                                   // the cursor is saved; the phase stays PH_DATA
+          *moved = true;
+          if (sh->ctl0) {
+            if (tid == 0) { sh->stats.yields++; trace(rd, b, TR_YIELD, coll); }
+            return RC_YIELD;
+          }
+          break;
+        }
+        // (push schedule: no done handshake - nobody reads my buffers and my slots are not reused before the
+        // peers' next-but-one call)
+        setPhase(sh, nextPhase(sh, PH_POST_DONE));
         break;
+      }
       case PH_POST_DONE: {
         if (n > 1) {
           // all payload stores of this block were issued before the barrier inside setPhase; one fence
@@ -511,9 +633,13 @@ DF_HD int runColl(BlockShared* sh, RankDev* rd, int b, int coll, uint32_t budget
         break;
       }
       case PH_WAIT_DONE:
-        if (n > 1 && !boundedWait(sh, rd, b, 1, budget)) { if (noteStall(sh, rd)) { setPhase(sh, PH_COMPLETE); break; } return RC_STALLED; }
-        if (tid == 0) trace(rd, b, TR_STALL, coll);          // every peer is done (event name kept for the dump: 'stall' = end of the done wait)
-        setPhase(sh, PH_COPY_OUT);
+        if (n > 1 && !patientWait(sh, rd, b, 1, budget)) {
+          if (noteStall(sh, rd)) { setPhase(sh, PH_COMPLETE); break; }
+          if (tid == 0) trace(rd, b, TR_STALL, coll);
+          return RC_STALLED;
+        }
+        if (tid == 0) trace(rd, b, TR_PEERS_DONE, coll);
+        setPhase(sh, nextPhase(sh, PH_COPY_OUT));
         break;
       case PH_COPY_OUT:
         if ((sh->dyn.sqeFlags & SQE_RECV_STAGED) && !rawRecv(&sh->cs)) {

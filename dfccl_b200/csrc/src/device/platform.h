@@ -133,6 +133,23 @@ DF_HD void st_release_sys_u64(volatile uint64_t* p, uint64_t v) {
   __atomic_store_n((uint64_t*)p, v, __ATOMIC_RELEASE);
 #endif
 }
+// release at GPU scope: for words that only blocks of this GPU read (cheaper than a system-scope fence)
+DF_HD void st_release_gpu_u64(volatile uint64_t* p, uint64_t v) {
+#if DF_DEVICE_CODE
+  asm volatile("st.release.gpu.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+#else
+  __atomic_store_n((uint64_t*)p, v, __ATOMIC_RELEASE);
+#endif
+}
+DF_HD uint32_t ld_relaxed_sys_u32(const volatile uint32_t* p) {
+#if DF_DEVICE_CODE
+  uint32_t v;
+  asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+#else
+  return __atomic_load_n((const uint32_t*)p, DF_HOST_RELAXED_LD);
+#endif
+}
 DF_HD void st_relaxed_sys_u64(volatile uint64_t* p, uint64_t v) {
 #if DF_DEVICE_CODE
   asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");

@@ -107,6 +107,9 @@ struct alignas(16) CollDyn {
   uint32_t sqeFlags;
   uint32_t status;
   uint64_t stallSinceNs;  // first unsuccessful poll of the current wait (0 = not stalled)
+  uint32_t patience;      // polls a wait of this submission may spend at least: raised after every wait that succeeded
+                          // (reference: RECV_SUCCESS_FACTOR, src/collectives_ofccl/device/ofccl_prims_simple.h:79-88)
+  uint32_t pad;
 };
 
 // ---- host-pinned control words
@@ -126,12 +129,22 @@ struct DaemonCtl {
 
 struct DevStats {                  // per block, device memory
   unsigned long long ctxSwitches, ctxSaves, ctxLoads, waitPolls, waitTimeouts, bytesReduced, bytesCopied,
-      maxSwitchNs, totalSwitchNs, sqesSeen, collsDone, visits;
+      maxSwitchNs, totalSwitchNs, sqesSeen, collsDone, visits,
+      yields,        // data phases left at a slice boundary because other work was queued
+      passes,        // scheduler passes (trigger poll + task-queue walk + queue maintenance)
+      nsTriggers, nsWalk, nsQueues;   // where thread 0 saw the passes' time go: trigger list, task-queue walk, queue upkeep
 };
 
 struct TraceEvent { uint64_t ns; uint16_t block; uint16_t event; int32_t collId; };
-enum TraceKind : uint16_t { TR_SQE = 1, TR_START = 2, TR_STALL = 3, TR_RESUME = 4, TR_DATA_BEGIN = 5,
-                            TR_DATA_END = 6, TR_DONE = 7, TR_QUIT = 8, TR_LAUNCH = 9 };
+enum TraceKind : uint16_t { TR_SQE = 1,          // submission consumed by this block
+                            TR_START = 2,        // released by its stream (or submitted from the host)
+                            TR_STALL = 3,        // a wait ran out of budget: the collective stays queued, the block moves on
+                            TR_ARRIVED = 4,      // every peer has arrived
+                            TR_DATA_BEGIN = 5, TR_DATA_END = 6,
+                            TR_DONE = 7,         // this block's part is complete (the last block publishes the completion)
+                            TR_QUIT = 8, TR_LAUNCH = 9,
+                            TR_PEERS_DONE = 10,  // every peer has finished its data movement
+                            TR_YIELD = 11 };     // data phase left at a slice boundary
 
 #define DF_MAX_ACTIVE 2048   // task-queue capacity per block (>= DF_MAX_COLLS: one outstanding submit per id)
 
@@ -139,20 +152,26 @@ struct BlockSaved {                // survives a voluntary quit (reference: Dyna
   uint64_t frontier;               // SQ entries consumed by this block
   uint32_t nActive;
   uint32_t exited;
+  uint32_t nTrig;                  // stream-ordered submissions whose stream has not released them yet
+  uint32_t pad;
   uint16_t active[DF_MAX_ACTIVE];
+  uint16_t trigColl[DF_MAX_ACTIVE];
+  uint32_t trigVal[DF_MAX_ACTIVE];
 };
 
 // ---- everything the daemon needs for one rank; lives in device memory (host memory for the host backend)
 struct RankDev {
-  // submission path
-  Sqe* hostSq;                     // pinned ring written by the host
-  volatile uint64_t* hostSqTail;   // pinned doorbell: entries published
-  volatile uint64_t* hostSqHead;   // pinned: entries mirrored to the device ring (flow control for the host)
-  Sqe* devSq;                      // device-resident mirror
+  // submission path: the ring and its tail live in device memory and are written by the HOST (stream memory
+  // operations on a stream of its own: entry words first, then the tail), so that no block ever reads host
+  // memory to find work - a load of pinned host memory costs a PCIe round trip and such loads from many blocks
+  // queue behind one another
+  Sqe* devSq;
   uint64_t devSqTail;
-  uint32_t fetchLock;
   uint32_t sqCap;                  // power of two
-  uint64_t frontier[DF_MAX_BLOCKS];
+  uint32_t pad0;
+  volatile uint64_t* hostFrontier; // pinned, [nBlocks]: entries consumed by each block (posted stores; flow control for the host)
+  volatile uint32_t* abortWord;    // where this rank's abort request is polled: device memory for the daemon (the host
+                                   // writes it with a stream memory operation), the pinned control block otherwise
   // completion path
   volatile uint64_t* hostCq;       // pinned ring read by the poller
   uint64_t devCqTail;

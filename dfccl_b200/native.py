@@ -41,7 +41,8 @@ class Stats(C.Structure):
     _fields_ = [(n, C.c_uint64) for n in (
         "sqesSubmitted", "cqesDelivered", "callbacksRun", "daemonLaunches", "daemonVoluntaryQuits",
         "ctxSwitches", "ctxSaves", "ctxLoads", "waitPolls", "waitTimeouts", "bytesReduced", "bytesCopied",
-        "sqFullRetries", "maxSwitchNs", "totalSwitchNs", "deviceEvents")]
+        "sqFullRetries", "maxSwitchNs", "totalSwitchNs", "deviceEvents", "dataYields", "schedulerPasses",
+        "nsTriggers", "nsWalk", "nsQueues")]
 
     def as_dict(self) -> Dict[str, int]:
         return {n: int(getattr(self, n)) for n, _ in self._fields_}
@@ -105,6 +106,7 @@ def lib() -> C.CDLL:
             "ofcclRunBroadcast": [vp, vp, i, CALLBACK, vp, vp], "ofcclRunBcast": [vp, i, CALLBACK, vp, vp],
             "dfcclRun": [vp, vp, i, CALLBACK, vp, vp],
             "dfcclRunOnStream": [vp, vp, i, vp, CALLBACK, vp, vp],
+            "dfcclRunDeferred": [vp, vp, i, CALLBACK, vp, vp], "dfcclTriggerOnStream": [i, vp, vp],
             "dfcclStreamWait": [i, vp, vp], "dfcclWait": [i, i, vp], "dfcclWaitAll": [i, vp],
             "dfcclAbort": [vp], "dfcclGetAsyncError": [vp, C.POINTER(i)],
             "dfcclGemmReserveSms": [i], "dfcclSetHoldOnWait": [vp, i], "dfcclGetStats": [vp, C.POINTER(Stats)], "dfcclGetHostStats": [vp, C.POINTER(Stats)], "dfcclTraceDump": [vp, C.c_char_p],
@@ -118,6 +120,8 @@ def lib() -> C.CDLL:
             "dfcclHeapPeerBase": [vp, i, C.POINTER(vp)],
             "dfcclProbePeerCopy": [vp, i, sz, i, i, i, i, i, C.POINTER(C.c_double)],
             "dfcclProbeFlagRoundTrip": [vp, i, i, C.POINTER(C.c_double)],
+            "dfcclProbeMemoryOps": [i, C.POINTER(C.c_uint64)],
+            "dfcclProbeStreamRoundTrip": [i, i, i, C.POINTER(C.c_double)],
             "dfcclAllReduceNoAlloc": [vp, vp, sz, i, C.c_float, vp],
             "dfcclSetDaemonGeometry": [vp, i, i],
         }
@@ -289,6 +293,14 @@ class RankCtx:
     def run_on_stream(self, coll_id: int, send: int, recv: int, stream: int) -> None:
         check(lib().dfcclRunOnStream(C.c_void_p(send), C.c_void_p(recv), coll_id, C.c_void_p(stream), CALLBACK(0), None,
                                      self.handle), f"dfcclRunOnStream({coll_id})")
+
+    def run_deferred(self, coll_id: int, send: int, recv: int) -> None:
+        """Publish a submission that ``trigger_on_stream`` (or the replay of a graph that captured it) releases."""
+        check(lib().dfcclRunDeferred(C.c_void_p(send), C.c_void_p(recv), coll_id, CALLBACK(0), None, self.handle),
+              f"dfcclRunDeferred({coll_id})")
+
+    def trigger_on_stream(self, coll_id: int, stream: int) -> None:
+        check(lib().dfcclTriggerOnStream(coll_id, C.c_void_p(stream), self.handle), f"dfcclTriggerOnStream({coll_id})")
 
     def stream_wait(self, coll_id: int, stream: int) -> None:
         check(lib().dfcclStreamWait(coll_id, C.c_void_p(stream), self.handle), f"dfcclStreamWait({coll_id})")

@@ -8,7 +8,10 @@ scratch of the one-rank all-reduce in a static device array of the library.
 The test calls it through its exported C symbol and compares with the regular entry point
 (``ncclAllReduce`` on a one-rank communicator with a pre-multiplied-sum operator, which
 stages the same buffers through allocated scratch), twice in a row with different data:
-the second call finds the array exactly as the first one left it.  This file sorts last
+the second call finds the array exactly as the first one left it.  That nothing is allocated
+is checked on the device's own count of free bytes (``cudaMemGetInfo``), which sees every
+allocation in the process, around each call after a first one that has loaded the kernel.
+This file sorts last
 on purpose, so that a run stopping at the first failure has already run everything else.
 """
 import ctypes as C
@@ -49,18 +52,30 @@ def test_no_alloc_matches_regular_entry_point_twice(nv, dt_name, tdt):
     L = nv.lib()
     dt = getattr(nv, dt_name)
     (comm,) = nv.Comm.init_loopback(1, 0)
+    L.dfcclNoAllocStatus.argtypes = [C.POINTER(C.c_uint32)]
     g = torch.Generator(device="cpu").manual_seed(7)
+    side = torch.cuda.Stream()                                   # a non-blocking stream: not ordered after the default one
     try:
-        for n, scale in ((1_000_003, 0.125), (4099, 3.0)):       # two calls in a row, different size and data
+        # first call on this device: set-up and kernel load (the only call allowed to change the free-byte count)
+        w = torch.ones(64, dtype=tdt, device="cuda")
+        assert L.dfcclAllReduceNoAlloc(C.c_void_p(w.data_ptr()), C.c_void_p(w.data_ptr()), 64, dt, C.c_float(1.0),
+                                       C.c_void_p(torch.cuda.current_stream().cuda_stream)) == nv.SUCCESS
+        torch.cuda.synchronize()
+        for (n, scale), stream in zip(((1_000_003, 0.125), (4099, 3.0), (65_537, -1.5)),
+                                      (torch.cuda.current_stream(), torch.cuda.current_stream(), side)):
+            # calls in a row, different size and data; the last one on the non-blocking stream
             x = (torch.rand(n, generator=g) * 2 - 1).to(tdt).cuda()
             want = _regular(nv, comm, x, scale, dt)
             got = torch.empty_like(x)
-            before = torch.cuda.memory_allocated()
+            torch.cuda.synchronize()
+            free_before = torch.cuda.mem_get_info()[0]
             rc = L.dfcclAllReduceNoAlloc(C.c_void_p(x.data_ptr()), C.c_void_p(got.data_ptr()), n, dt, C.c_float(scale),
-                                         C.c_void_p(torch.cuda.current_stream().cuda_stream))
+                                         C.c_void_p(stream.cuda_stream))
             assert rc == nv.SUCCESS
             torch.cuda.synchronize()
-            assert torch.cuda.memory_allocated() == before
+            assert torch.cuda.mem_get_info()[0] == free_before, "the entry point changed the device's free memory"
+            status = C.c_uint32(99)
+            assert L.dfcclNoAllocStatus(C.byref(status)) == nv.SUCCESS and status.value == 0
             tol = 1e-6 if tdt == torch.float32 else 1e-2
             torch.testing.assert_close(got.float(), want.float(), rtol=tol, atol=tol)
             torch.testing.assert_close(got.float(), x.float() * scale, rtol=tol, atol=tol)
