@@ -39,6 +39,10 @@ def parse():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="dfccl", choices=["dfccl", "reference"])
     ap.add_argument("--graph", type=int, default=1, help="capture forward+backward in a CUDA graph (this library's arm only)")
+    ap.add_argument("--overlap", type=int, default=1, help="graphed step: release every gradient bucket from inside the captured backward pass")
+    ap.add_argument("--daemon-blocks", type=int, default=int(os.environ.get("BENCH_DAEMON_BLOCKS", "8")),
+                    help="thread blocks of the daemon kernel (SMs it holds while gradient buckets are in flight)")
+    ap.add_argument("--sweep", type=int, default=1, help="after the training runs, time a few all-reduce sizes through the daemon (N > 1)")
     ap.add_argument("--batch", type=int, default=BATCH_PER_GPU, help=argparse.SUPPRESS)
     ap.add_argument("--model", default="resnet50", help=argparse.SUPPRESS)
     return ap.parse_args()
@@ -72,6 +76,7 @@ class Trainer:
         self.batch = args.batch
         self.graphed = None
         self.use_graph = bool(args.graph) and args.impl == "dfccl"
+        self.overlap = bool(args.overlap)
 
     def loss_fn(self, out, y):
         return self.crit(out.float(), y)
@@ -80,7 +85,7 @@ class Trainer:
         if self.use_graph:
             if self.graphed is None:
                 from dfccl_b200.parallel import GraphedStep
-                self.graphed = GraphedStep(self.net, self.loss_fn, self.backend.ddp, x, y)
+                self.graphed = GraphedStep(self.net, self.loss_fn, self.backend.ddp, x, y, overlap=self.overlap)
             loss = self.graphed(x, y)
         else:
             loss = self.loss_fn(self.net(x), y)
@@ -93,14 +98,15 @@ class Trainer:
 class DaemonBackend:
     name = "dfccl"
 
-    def __init__(self, dist_info):
+    def __init__(self, dist_info, daemon_blocks=4):
         self.d = dist_info
         self.ddp = None
+        self.daemon_blocks = daemon_blocks
 
     def attach(self, net):
         from dfccl_b200.parallel import DaemonDDP
         self.ddp = DaemonDDP(net, self.d, bucket_mb=BUCKET_MB, lr=0.1, momentum=0.9, weight_decay=1e-4,
-                             randomize_order=True, window=2, seed=17)
+                             randomize_order=True, window=2, seed=17, daemon_blocks=self.daemon_blocks)
 
     def finish_backward(self):
         self.ddp.finish_backward()
@@ -113,10 +119,75 @@ class DaemonBackend:
         return st["daemonLaunches"] + self.ddp.launches
 
     def info(self):
-        return {"buckets": len(self.ddp.buckets), "bucket_mb": BUCKET_MB, "stats": self.ddp.stats()}
+        return {"buckets": len(self.ddp.buckets), "bucket_mb": BUCKET_MB, "daemon_blocks": self.daemon_blocks,
+                "schedule": self.ddp.gradient_path(), "stats": self.ddp.stats()}
 
     def close(self):
         self.ddp.close()
+
+
+def allreduce_sweep(d):
+    """The other half of the headline metric: all-reduce latency and bus bandwidth through the daemon (register, then
+    stream-ordered submit and wait, one call in flight), bf16, next to this library's stream-ordered kernel and to the
+    NCCL that ships with PyTorch on the same buffers.  Device time (CUDA events), max over ranks."""
+    import torch.distributed as dist
+    from dfccl_b200 import native as nv
+    from dfccl_b200.utils import tensor_from_ptr
+    world, L = d.world, nv.lib()
+    sizes = [1 << 10, 64 << 10, 1 << 20, 16 << 20, 256 << 20]
+    ctx = nv.RankCtx(d.rank, d.local_rank)
+    ctx.set_daemon_geometry(64, 0)
+    nvls = bool(d.comm.nvls_init(0))
+    if nvls:                                   # room left in the arena for both buffers?  (every rank sees the same numbers)
+        _uc, _mc, total, used = d.comm.nvls_info()
+        nvls = total - used >= 2 * max(sizes) + 4096
+    send_p = d.comm.nvls_alloc(max(sizes)) if nvls else d.comm.alloc(max(sizes))
+    recv_p = d.comm.nvls_alloc(max(sizes)) if nvls else d.comm.alloc(max(sizes))
+    ids = 4
+    for k, sz in enumerate(sizes):
+        for j in range(ids):
+            big = nvls and sz >= (1 << 20)
+            ctx.prepare(k * ids + j, d.comm, nv.ALLREDUCE, sz // 2, nv.BFLOAT16, algo=nv.ALGO_NVLS if big else nv.ALGO_AUTO, arena_buffers=big)
+    ctx.finalize()
+    stream = torch.cuda.current_stream()
+    x = tensor_from_ptr(send_p, (max(sizes) // 2,), torch.bfloat16, d.device)
+    x.uniform_(-1, 1)
+    nccl_buf = x.clone()
+
+    def timed(fn, iters, warm=5):
+        for _ in range(warm):
+            fn()
+        torch.cuda.synchronize()
+        dist.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(iters):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return max_over_ranks(e0.elapsed_time(e1) * 1e3 / iters, world)
+
+    rows = []
+    f = 2.0 * (world - 1) / world
+    for k, sz in enumerate(sizes):
+        turn = [0]
+
+        def daemon_op():
+            i = k * ids + turn[0] % ids
+            turn[0] += 1
+            ctx.run_on_stream(i, send_p, recv_p, stream.cuda_stream)
+            ctx.stream_wait(i, stream.cuda_stream)
+        iters = 20 if sz <= (16 << 20) else 5
+        us_d = timed(daemon_op, iters)
+        assert ctx.wait_all(60000) == nv.SUCCESS
+        us_s = timed(lambda: nv.check(L.ncclAllReduce(send_p, recv_p, sz // 2, nv.BFLOAT16, nv.SUM, d.comm.handle, stream.cuda_stream)), iters)
+        view = nccl_buf[:sz // 2]
+        us_n = timed(lambda: dist.all_reduce(view), iters)
+        rows.append({"bytes": sz, "daemon_us": round(us_d, 1), "daemon_busbw_gbs": round(sz / us_d / 1e3 * f, 1),
+                     "stream_kernel_us": round(us_s, 1), "stream_kernel_busbw_gbs": round(sz / us_s / 1e3 * f, 1),
+                     "nccl_2_28_us": round(us_n, 1), "nccl_2_28_busbw_gbs": round(sz / us_n / 1e3 * f, 1)})
+    ctx.destroy()
+    return {"dtype": "bf16", "n_gpus": world, "multimem_schedule_from_1MB": nvls, "rows": rows}
 
 
 def run(args):
@@ -140,8 +211,16 @@ def run(args):
         backend = ReferenceBackend(d)
     else:
         from dfccl_b200.parallel import init_distributed
+        if args.graph and args.overlap:
+            # The buckets of a captured backward pass are released milliseconds apart.  A daemon that stayed for all of
+            # them would hold its SMs through most of the step; it leaves soon after each bucket instead and the
+            # poller thread launches it again when the next release shows up (a few tens of microseconds).
+            os.environ.setdefault("DFCCL_IDLE_QUIT_US", "100")
         d = init_distributed()
-        backend = DaemonBackend(d)
+        if d.world > 1 and os.environ.get("DFCCL_DDP_NVLS", "1") != "0":
+            # one multicast arena for the gradient buckets (about 160 MB) and the buffers of the all-reduce sweep
+            d.comm.nvls_init(900 << 20)
+        backend = DaemonBackend(d, args.daemon_blocks)
     from dfccl_b200.utils.clocks import ClockSampler        # reads nvidia-smi only
     tr = Trainer(args, d, backend)
     dev, B = d.device, args.batch
@@ -217,6 +296,7 @@ def run(args):
 
     info = backend.info()
     backend.close()
+    sweep = allreduce_sweep(d) if (args.impl == "dfccl" and args.sweep and world > 1) else None
     if d.rank == 0:
         gb = B * world
         h2d = host_x[0].numel() * host_x[0].element_size() + host_y[0].numel() * host_y[0].element_size()
@@ -228,8 +308,12 @@ def run(args):
             "impl": args.impl,
             "config": {"model": "ResNet-50 v1.5" if args.model == "resnet50" else args.model, "global_batch": gb,
                        "batch_per_gpu": B, "seq_len": None, "parallelism": f"dp{world}",
-                       "grad_buckets_mb": BUCKET_MB, "optimizer": "SGD momentum 0.9 wd 1e-4, fp32 master weights", "cuda_graph": bool(tr.use_graph),
-                       "gradient_path": ("daemon all-reduce, fused 1/N scale + bf16->fp32 cast, per-rank randomized bucket order"
+                       "grad_buckets_mb": BUCKET_MB,
+                       "optimizer": ("fused SGD kernel, momentum 0.9 wd 1e-4, fp32 master weights" if args.impl == "dfccl"
+                                     else "torch.optim.SGD momentum 0.9 wd 1e-4 on the bf16 parameters (no master copy)"),
+                       "cuda_graph": bool(tr.use_graph), "overlap": bool(tr.use_graph and tr.overlap),
+                       "gradient_path": (f"daemon all-reduce ({info.get('schedule', '')}), fused 1/N scale + bf16->fp32 cast, per-rank randomized "
+                                         f"bucket order, {'released from inside the captured backward pass' if tr.use_graph and tr.overlap else 'submitted after the backward pass' if tr.use_graph else 'submitted from gradient hooks'}"
                                          if args.impl == "dfccl" else "reference library ncclAllReduce per bucket"),
                        "l2": "activations and gradients per step far exceed the 126 MB L2; no explicit flush"},
             "clocks": clocks,
@@ -239,6 +323,8 @@ def run(args):
             "final_loss": final_loss,
             "backend_info": info,
         }
+        if sweep is not None:
+            out["allreduce_through_daemon"] = sweep
         print(json.dumps(out))
     d.destroy()
 

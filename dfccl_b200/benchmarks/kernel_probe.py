@@ -54,9 +54,10 @@ def stream_ops_probe(iters):
     """Round trip stream -> resident kernel -> stream in its eight forms (see dfcclProbeStreamRoundTrip)."""
     L = nv.lib()
     names = {0: "memop_write+memop_wait", 1: "kernel_write+memop_wait", 2: "memop_write+kernel_wait", 3: "kernel_write+kernel_wait"}
-    ns = (C.c_uint64 * 8)()
+    ns = (C.c_uint64 * 13)()
     if L.dfcclProbeMemoryOps(200, ns) == nv.SUCCESS:
-        names_ops = ("ld_host", "st_host", "st_host+fence_sys", "st_dev+fence_sys", "st_dev+fence_gpu", "fence_sys", "atomic_dev", "ld_dev")
+        names_ops = ("ld_host", "st_host", "st_host+fence_sys", "st_dev+fence_sys", "st_dev+fence_gpu", "fence_sys", "atomic_dev", "ld_dev",
+                     "st_dev+fence_acq_rel_sys", "st_dev+fence_acq_rel_gpu", "ld_dev_dependent", "st_release_sys", "timer_read")
         print(json.dumps({"control_path_op_ns": dict(zip(names_ops, [int(v) for v in ns]))}))
     for delay in (0, 10, 50):
         out = {}

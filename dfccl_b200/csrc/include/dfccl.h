@@ -223,7 +223,12 @@ typedef struct {
   float scale;
   int algo;                 /* dfcclAlgo_t */
   int nBlocks;              /* 0 = tuner's choice */
+  int flags;                /* DFCCL_COLL_* */
 } dfcclCollInfo;
+/* The buffers of every submission of this collective lie in the communicator's multicast arena (dfcclNvlsAlloc):
+ * the multimem schedule then works on them in place and reserves no staging slots for the collective.  A submission
+ * that breaks the promise is refused. */
+#define DFCCL_COLL_ARENA_BUFFERS 1
 ncclResult_t dfcclPrepare(const dfcclCollInfo* info, ncclComm_t comm, int collId, ofcclRankCtx_t rankCtx);
 
 /* Generic submit (what every ofcclRun* wrapper calls). */

@@ -49,8 +49,10 @@ ncclResult_t dfcclProbeFlagRoundTrip(ncclComm_t comm, int peer, int iters, doubl
  * stream memory operation; bit 1: so is the wait; bit 2: the write also stores a mirror word in pinned host memory. */
 /* Cost in nanoseconds of the single memory operations the daemon's control path is made of, timed by one thread on the
  * current device: [0] load of a pinned host word, [1] store to it, [2] that store + system fence, [3] device store +
- * system fence, [4] device store + device fence, [5] system fence alone, [6] device atomic, [7] device load. */
-ncclResult_t dfcclProbeMemoryOps(int iters, uint64_t nsOut[8]);
+ * system fence, [4] device store + device fence, [5] system fence alone, [6] device atomic, [7] device load (independent
+ * loads), [8] / [9] device store + acq_rel fence of system / device scope, [10] device load (dependent chain),
+ * [11] release store of system scope, [12] one read of the nanosecond timer. */
+ncclResult_t dfcclProbeMemoryOps(int iters, uint64_t nsOut[13]);
 ncclResult_t dfcclProbeStreamRoundTrip(int mode, int iters, int delayUs, double* usOut);   /* the kernel answers delayUs late */
 
 /* ---- introspection */

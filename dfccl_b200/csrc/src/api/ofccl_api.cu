@@ -242,6 +242,8 @@ static bool spinFirst(std::unique_lock<std::mutex>& l, Quick quick, Pred pred, i
   return pred();
 }
 
+static ncclResult_t launchFromCaller(ofcclRankCtx* ctx);
+
 // Turns completion entries into callbacks: the reference's poller thread.
 static void pollerMain(ofcclRankCtx* ctx) {
   logSetRank(ctx->rank);
@@ -270,7 +272,12 @@ static void pollerMain(ofcclRankCtx* ctx) {
       }
       if (fired) {
         ctx->untriggered -= fired;
-        if (!ctl_load(&ctx->ctl->alive) && !ctl_load(&ctx->ctl->abortFlag)) wakeLauncher(ctx->launcher.get());
+        if (!ctl_load(&ctx->ctl->alive) && !ctl_load(&ctx->ctl->abortFlag)) {
+          // a released submission found the daemon parked: launch it from this thread (it is awake and has just seen
+          // the release; handing over to the observer thread would add a thread wake-up to the collective's latency)
+          if (ctx->backend == dfcclBackendCuda && ctx->launcher->expected == 1) { if (launchFromCaller(ctx) != ncclSuccess) wakeLauncher(ctx->launcher.get()); }
+          else wakeLauncher(ctx->launcher.get());
+        }
       }
     }
     const uint64_t slot = ctx->cqHead & (ctx->cqCap - 1);
@@ -382,8 +389,9 @@ DF_API ncclResult_t ofcclFinalizeRankCtx7StartHostThrds(ofcclRankCtx_t ctx) {
       // staging slots in the arena; every member walks its collectives in id order, so the offsets agree.
       // (the output of a reduce-scatter and the input of an all-gather are local to the rank and need no slot)
       NvlsArena* a = e.comm->nvls;
-      const size_t inB = e.cs.kind == dfcclCollAllGather ? 0 : sendBytes(&e.cs);
-      const size_t outB = e.cs.kind == dfcclCollReduceScatter ? 0 : recvBytes(&e.cs);
+      const bool inPlace = (e.info.flags & DFCCL_COLL_ARENA_BUFFERS) != 0;      // the caller's buffers are arena memory: no slots
+      const size_t inB = e.cs.kind == dfcclCollAllGather || inPlace ? 0 : sendBytes(&e.cs);
+      const size_t outB = e.cs.kind == dfcclCollReduceScatter || inPlace ? 0 : recvBytes(&e.cs);
       uint64_t in = 0, out = 0;
       if ((inB == 0 || a->alloc(inB, &in) == ncclSuccess) && (outB == 0 || a->alloc(outB, &out) == ncclSuccess)) {
         e.cs.mcHeap = a->mc; e.cs.nvlsPeers = a->peersDev; e.cs.nvlsIn = in; e.cs.nvlsOut = out;
@@ -492,6 +500,7 @@ DF_API ncclResult_t ofcclFinalizeRankCtx7StartHostThrds(ofcclRankCtx_t ctx) {
   const int64_t tolerant = paramI64("TOLERANT_UNPROGRESSED_CNT", 0);     // polls in the reference; here ~1 us each
   rd.idleQuitNs = (uint64_t)paramI64("IDLE_QUIT_US", tolerant ? tolerant : 1000) * 1000ull;
   rd.stallQuitNs = (uint64_t)paramI64("STALL_QUIT_US", tolerant ? tolerant : 5000) * 1000ull;
+  rd.trigQuitNs = (uint64_t)paramI64("TRIGGER_QUIT_US", (int64_t)(rd.idleQuitNs / 1000)) * 1000ull;
   rd.waitTimeoutNs = (uint64_t)paramI64("WAIT_TIMEOUT_MS", 0) * 1000000ull;
   rd.maxLifetimeNs = (uint64_t)paramI64("MAX_LIFETIME_MS", 2000) * 1000000ull;
   // a block's data phase is left after this many bytes when other work is queued (the reference parks a
@@ -662,9 +671,13 @@ static ncclResult_t submit(ofcclRankCtx* ctx, const void* send, void* recv, int 
     } else if (viaArena) {          // in place when the buffer lives in the arena, else through this collective's slots
       NvlsArena* a = e.comm->nvls;
       if (rawSend(&cs)) { if (heap->contains(send, sB)) q.send = heap->offsetOf(send); else { q.flags |= SQE_SEND_STAGED; q.send = (uint64_t)(uintptr_t)send; } }
-      else if (a->contains(send, sB)) q.send = (uint64_t)((const char*)send - a->uc); else { q.flags |= SQE_SEND_STAGED; q.send = (uint64_t)(uintptr_t)send; }
+      else if (a->contains(send, sB)) q.send = (uint64_t)((const char*)send - a->uc);
+      else if (e.info.flags & DFCCL_COLL_ARENA_BUFFERS) { DF_WARN("collective %d was registered for buffers in the multicast arena; this send buffer is not", collId); return ncclInvalidArgument; }
+      else { q.flags |= SQE_SEND_STAGED; q.send = (uint64_t)(uintptr_t)send; }
       if (rawRecv(&cs)) { if (heap->contains(recv, rB)) q.recv = heap->offsetOf(recv); else { q.flags |= SQE_RECV_STAGED; q.recv = (uint64_t)(uintptr_t)recv; } }
-      else if (a->contains(recv, rB)) q.recv = (uint64_t)((char*)recv - a->uc); else { q.flags |= SQE_RECV_STAGED; q.recv = (uint64_t)(uintptr_t)recv; }
+      else if (a->contains(recv, rB)) q.recv = (uint64_t)((char*)recv - a->uc);
+      else if (e.info.flags & DFCCL_COLL_ARENA_BUFFERS) { DF_WARN("collective %d was registered for buffers in the multicast arena; this receive buffer is not", collId); return ncclInvalidArgument; }
+      else { q.flags |= SQE_RECV_STAGED; q.recv = (uint64_t)(uintptr_t)recv; }
     }
     bool stageSend = !viaArena && needSend && !heap->contains(send, sB);
     if (needSend && cs.kind == dfcclCollAllReduce && cs.algo == dfcclAlgoOneShot && send == recv && cs.nranks > 1) stageSend = true;
@@ -964,7 +977,7 @@ static void releaseHeapParts(ofcclRankCtx* ctx) {
   // arena slots were taken in ascending id order; giving them back in descending order unwinds the bump allocator
   for (auto it = ctx->colls.rbegin(); it != ctx->colls.rend(); ++it) {
     CollEntry& e = it->second;
-    if (e.cs.algo == dfcclAlgoNvls && e.comm && e.comm->nvls) {
+    if (e.cs.algo == dfcclAlgoNvls && e.comm && e.comm->nvls && !(e.info.flags & DFCCL_COLL_ARENA_BUFFERS)) {
       if (e.cs.kind != dfcclCollReduceScatter) e.comm->nvls->release(e.cs.nvlsOut);
       if (e.cs.kind != dfcclCollAllGather) e.comm->nvls->release(e.cs.nvlsIn);
     }

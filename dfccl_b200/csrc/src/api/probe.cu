@@ -272,7 +272,10 @@ ncclResult_t dfcclProbeStreamRoundTrip(int mode, int iters, int delayUs, double*
 //   [0] ld.relaxed.sys of a host word          [1] st to a host word (posted), no fence
 //   [2] st host word + fence.sys               [3] st device word + fence.sys
 //   [4] st device word + fence.gpu             [5] fence.sys with nothing outstanding
-//   [6] atomicAdd on a device word             [7] ld.relaxed.sys of a device word (L2 round trip)
+//   [6] atomicAdd on a device word             [7] ld.relaxed.sys of a device word, loads independent of one another
+//   [8] st device word + fence.acq_rel.sys     [9] st device word + fence.acq_rel.gpu
+//   [10] ld.relaxed.sys of a device word, each load's address depending on the previous value (a round trip)
+//   [11] st.release.sys to a device word       [12] one read of the nanosecond timer
 namespace dfccl {
 namespace {
 __global__ void probeMemOpsKernel(volatile uint64_t* host, volatile uint64_t* dev, int iters, uint64_t* out) {
@@ -305,26 +308,42 @@ __global__ void probeMemOpsKernel(volatile uint64_t* host, volatile uint64_t* de
   t0 = df_now_ns();
   for (int i = 0; i < iters; ++i) acc += ld_relaxed_sys_u64(dev + 24);
   t1 = df_now_ns(); out[7] = (t1 - t0) / iters;
-  out[8] = acc;
+  t0 = df_now_ns();
+  for (int i = 0; i < iters; ++i) { st_relaxed_sys_u64(dev + 8, (uint64_t)i); asm volatile("fence.acq_rel.sys;" ::: "memory"); }
+  t1 = df_now_ns(); out[8] = (t1 - t0) / iters;
+  t0 = df_now_ns();
+  for (int i = 0; i < iters; ++i) { st_relaxed_sys_u64(dev + 8, (uint64_t)i); asm volatile("fence.acq_rel.gpu;" ::: "memory"); }
+  t1 = df_now_ns(); out[9] = (t1 - t0) / iters;
+  uint64_t idx = 0;
+  t0 = df_now_ns();
+  for (int i = 0; i < iters; ++i) idx = ld_relaxed_sys_u64(dev + 32 + (idx & 1));      // both words hold 0: a dependent chain
+  t1 = df_now_ns(); out[10] = (t1 - t0) / iters;
+  t0 = df_now_ns();
+  for (int i = 0; i < iters; ++i) st_release_sys_u64(dev + 8, (uint64_t)i);
+  t1 = df_now_ns(); out[11] = (t1 - t0) / iters;
+  t0 = df_now_ns();
+  for (int i = 0; i < iters; ++i) acc += df_now_ns();
+  t1 = df_now_ns(); out[12] = (t1 - t0) / iters;
+  out[13] = acc + idx;
 }
 }  // namespace
 }  // namespace dfccl
 
 extern "C" __attribute__((visibility("default")))
-ncclResult_t dfcclProbeMemoryOps(int iters, uint64_t nsOut[8]) {
+ncclResult_t dfcclProbeMemoryOps(int iters, uint64_t nsOut[13]) {
   if (!nsOut || iters < 1 || iters > 10000) return ncclInvalidArgument;
   uint64_t *host = nullptr, *dev = nullptr, *out = nullptr;
   CUDACHECK(cudaHostAlloc((void**)&host, 256, cudaHostAllocMapped));
   memset(host, 0, 256);
   CUDACHECK(cudaMalloc((void**)&dev, 512));
   CUDACHECK(cudaMemset(dev, 0, 512));
-  CUDACHECK(cudaMalloc((void**)&out, 9 * sizeof(uint64_t)));
+  CUDACHECK(cudaMalloc((void**)&out, 14 * sizeof(uint64_t)));
   probeMemOpsKernel<<<1, 32>>>(host, dev, 8, out);          // warm-up
   probeMemOpsKernel<<<1, 32>>>(host, dev, iters, out);
-  uint64_t h[9];
+  uint64_t h[14];
   cudaError_t e = cudaMemcpy(h, out, sizeof(h), cudaMemcpyDeviceToHost);
   cudaFree(dev); cudaFree(out); cudaFreeHost(host);
   if (e != cudaSuccess) { (void)cudaGetLastError(); return ncclUnhandledCudaError; }
-  for (int i = 0; i < 8; ++i) nsOut[i] = h[i];
+  for (int i = 0; i < 13; ++i) nsOut[i] = h[i];
   return ncclSuccess;
 }

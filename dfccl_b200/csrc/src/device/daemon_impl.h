@@ -218,9 +218,10 @@ DF_HD void daemonBlockMain(RankDev* rd, int b, BlockShared* sh) {
         st_release_sys_u32(&rd->quitting, 1u);
       }
       else if (progressed) lastUseful = now;
-      // only waiting for streams to release submissions: nothing a resident daemon can speed up, and
-      // the host relaunches it when a trigger fires, so leave as quickly as when idle
-      else if (!sh->quit && (winding || now - lastUseful > (sh->nActive ? rd->stallQuitNs : rd->idleQuitNs))) {
+      // only waiting for streams to release submissions: the host relaunches the daemon when a trigger fires, so by
+      // default it leaves as quickly as when idle; a caller whose releases come in quick succession (the buckets
+      // of a captured backward pass) can ask it to stay for longer and save the relaunches
+      else if (!sh->quit && (winding || now - lastUseful > (sh->nActive ? rd->stallQuitNs : sh->nTrig ? rd->trigQuitNs : rd->idleQuitNs))) {
         // a stream parked on one of this context's completion words must not depend on a host thread's
         // relaunch: while the host holds the instance it only leaves by age (or with the others)
         if (!winding && ctl_load(&rd->ctl->hold)) lastUseful = now;

@@ -582,9 +582,14 @@ DF_HD int runColl(BlockShared* sh, RankDev* rd, int b, int coll, uint32_t budget
           df_sync();
         }
         const uint64_t so = mySendOff(sh), ro = myRecvOff(sh), epoch = sh->dyn.epoch;
+        const bool pushed = sh->cs.algo == dfcclAlgoPush && n > 1;
         for (int j = tid; j < n; j += nt) {
           if (j == me) continue;
           FlagSlot* s = sh->cs.peerFlags[j] + (uint64_t)b * n + me;
+          // push: the fence of thread 0 above, between two block-wide barriers, already orders every thread's payload
+          // stores before these flag stores (a second fence per flag would only add its latency); the offsets are
+          // not used by that schedule
+          if (pushed) { st_relaxed_sys_u64(&s->arrive, epoch); continue; }
           st_relaxed_sys_u64(&s->sendOff, so);
           st_relaxed_sys_u64(&s->recvOff, ro);
           st_release_sys_u64(&s->arrive, epoch);

@@ -201,6 +201,7 @@ struct RankDev {
                                    // lives on the device so that a captured launch finds the right one at every replay)
   uint64_t idleQuitNs;             // leave after this long with an empty task queue and no new entry
   uint64_t stallQuitNs;            // leave after this long with only stalled collectives
+  uint64_t trigQuitNs;             // leave after this long with nothing but submissions that wait for their stream
   uint64_t waitTimeoutNs;          // a single wait older than this fails with ST_TIMEOUT (0 = never)
   uint64_t maxLifetimeNs;          // one launch of the daemon leaves after this long regardless of its state (0 = never)
   uint64_t sliceBytes;             // PH_DATA yields after this many bytes when others are queued (0 = never)

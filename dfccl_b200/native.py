@@ -21,6 +21,7 @@ INT8, UINT8, INT32, UINT32, INT64, UINT64, FLOAT16, FLOAT32, FLOAT64, BFLOAT16 =
 ALLREDUCE, ALLGATHER, REDUCESCATTER, BROADCAST, REDUCE = range(5)
 ALGO_AUTO, ALGO_ONESHOT, ALGO_TWOSHOT, ALGO_NVLS, ALGO_PUSH = range(5)
 BACKEND_CUDA, BACKEND_HOST = 0, 1
+COLL_ARENA_BUFFERS = 1
 FAULT_NONE, FAULT_DROP_SQE, FAULT_DELAY_SQE_US, FAULT_FREEZE_POLLER = range(4)
 
 DTYPE_SIZE = {INT8: 1, UINT8: 1, INT32: 4, UINT32: 4, INT64: 8, UINT64: 8, FLOAT16: 2, FLOAT32: 4, FLOAT64: 8, BFLOAT16: 2}
@@ -34,7 +35,7 @@ class UniqueId(C.Structure):
 
 class CollInfo(C.Structure):
     _fields_ = [("kind", C.c_int), ("count", C.c_size_t), ("inType", C.c_int), ("outType", C.c_int),
-                ("op", C.c_int), ("root", C.c_int), ("scale", C.c_float), ("algo", C.c_int), ("nBlocks", C.c_int)]
+                ("op", C.c_int), ("root", C.c_int), ("scale", C.c_float), ("algo", C.c_int), ("nBlocks", C.c_int), ("flags", C.c_int)]
 
 
 class Stats(C.Structure):
@@ -270,8 +271,10 @@ class RankCtx:
         self._live = True
 
     def prepare(self, coll_id: int, comm: Comm, kind: int, count: int, dtype: int, *, out_dtype: Optional[int] = None,
-                op: int = SUM, root: int = 0, scale: float = 1.0, algo: int = ALGO_AUTO, n_blocks: int = 0) -> None:
-        info = CollInfo(kind, count, dtype, dtype if out_dtype is None else out_dtype, op, root, scale, algo, n_blocks)
+                op: int = SUM, root: int = 0, scale: float = 1.0, algo: int = ALGO_AUTO, n_blocks: int = 0,
+                arena_buffers: bool = False) -> None:
+        info = CollInfo(kind, count, dtype, dtype if out_dtype is None else out_dtype, op, root, scale, algo, n_blocks,
+                        COLL_ARENA_BUFFERS if arena_buffers else 0)
         check(lib().dfcclPrepare(C.byref(info), comm.handle, coll_id, self.handle), f"dfcclPrepare({coll_id})")
 
     def set_daemon_geometry(self, blocks: int = 0, threads: int = 0) -> None:

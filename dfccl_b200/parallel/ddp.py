@@ -51,6 +51,16 @@ class Bucket:
     coll_id: int = 0
     comm: Optional[nv.Comm] = None             # the group this bucket is reduced over
     scale: float = 1.0
+    nvls: bool = False                         # arrays live in the switch-multicast arena, reduced by multimem
+    deferred: bool = False                     # published ahead of a captured step; its release is part of the graph
+
+
+def _esize(dt: torch.dtype) -> int:
+    return torch.empty((), dtype=dt).element_size()
+
+
+def _pad512(n: int) -> int:
+    return (n + 511) // 512 * 512
 
 
 def _view_like(flat: torch.Tensor, off: int, p: torch.Tensor) -> torch.Tensor:
@@ -77,10 +87,15 @@ class DaemonDDP:
                  weight_decay: float = 1e-4, randomize_order: bool = True, window: int = 2, seed: int = 0,
                  coll_id_base: int = 0, comm: Optional[nv.Comm] = None, n_blocks: int = 0,
                  daemon_blocks: int = 8, daemon_threads: int = 0, param_groups: Optional[Sequence[dict]] = None,
-                 optimizer: str = "sgd", betas=(0.9, 0.999), eps: float = 1e-8):
+                 optimizer: str = "sgd", betas=(0.9, 0.999), eps: float = 1e-8, nvls: Optional[bool] = None):
         """``param_groups`` (hybrid parallelism): a list of ``{"params": [...], "comm": Comm, "scale": float}``;
         every group gets its own buckets, reduced over its own communicator (sum times ``scale``).  All
-        groups share this rank's one daemon, so ranks may submit them in any order."""
+        groups share this rank's one daemon, so ranks may submit them in any order.
+
+        ``nvls``: keep the gradient buckets in the communicator's switch-multicast arena and reduce them with the
+        multimem schedule (the NVLink switch adds the members' copies; every GPU moves one message size instead of
+        two).  ``None`` = when the fabric offers it (``DFCCL_DDP_NVLS=0`` switches it off); memory bound to a
+        multicast object ties the ranks' fates together, so tests of failure paths pass ``False``."""
         self.module = module
         self.dist = dist
         self.comm = comm or dist.comm
@@ -99,14 +114,19 @@ class DaemonDDP:
         self._ready: List[Bucket] = []
         self._submitted: List[Bucket] = []
         self._first_step = True
+        self._capturing = False                 # gradient hooks record bucket releases into a stream capture (see graph.GraphedStep)
+        self._captured: List[Bucket] = []
         self.hooks_enabled = True               # switched off while a captured step runs (see graph.GraphedStep)
         self.launches = 0                       # kernels of this library launched by step()
         self.buckets: List[Bucket] = []
+        self._nvls_request = nvls
+        self.nvls_comms: List[nv.Comm] = []       # communicators whose buckets live in the multicast arena
         if param_groups is None:
             param_groups = [{"params": [p for p in module.parameters() if p.requires_grad], "comm": self.comm,
                              "scale": 1.0 / self.world}]
         for g in param_groups:
             self._build_buckets(int(bucket_mb * (1 << 20)), g["params"], g.get("comm") or self.comm, float(g["scale"]))
+        self._place_gradients()
         self.ctx = nv.RankCtx(dist.rank, dist.local_rank if self.device.type == "cuda" else -1)
         # gradient buckets need a fraction of the fabric: a small grid leaves the SMs to the training kernels
         if self.device.type == "cuda":
@@ -114,7 +134,8 @@ class DaemonDDP:
         for b in self.buckets:
             b.coll_id = coll_id_base + b.index
             self.ctx.prepare(b.coll_id, b.comm, nv.ALLREDUCE, b.numel, nccl_dtype(b.dtype), out_dtype=nv.FLOAT32,
-                             op=nv.SUM, scale=b.scale, n_blocks=n_blocks)
+                             op=nv.SUM, scale=b.scale, n_blocks=n_blocks,
+                             algo=nv.ALGO_NVLS if b.nvls else nv.ALGO_AUTO, arena_buffers=b.nvls)
         self.ctx.finalize()
         if self.device.type == "cuda":
             nv.check(self._lib.dfcclOpsWarm(), "dfcclOpsWarm")   # load the optimizer kernels before any stream can block
@@ -143,22 +164,66 @@ class DaemonDDP:
         for b in self.buckets[first:]:
             b.comm, b.scale = comm, scale
             b.flat_param = torch.empty(b.numel, dtype=b.dtype, device=self.device)
-            b.grad = self._pool.zeros((b.numel,), b.dtype)
-            b.grad32 = self._pool.zeros((b.numel,), torch.float32)
             b.flat_param.zero_()
             with torch.no_grad():
                 for p, off in zip(b.params, b.offsets):
                     v = _view_like(b.flat_param, off, p)
                     v.copy_(p.data)
                     p.data = v
-                    p.grad = _view_like(b.grad, off, p)
             b.master = b.flat_param.float().clone()
             b.momentum = torch.zeros_like(b.master)
             b.moment2 = torch.zeros_like(b.master) if self.optimizer == "adamw" else None
             b.pending = len(b.params)
 
+    def _place_gradients(self) -> None:
+        """Gradient arrays (input of the all-reduce, in the parameters' dtype) and fp32 results: in the multicast
+        arena of the bucket's communicator where the fabric has one, in the symmetric heap otherwise."""
+        import os
+        want = self._nvls_request
+        if want is None:
+            want = os.environ.get("DFCCL_DDP_NVLS", "1") != "0"
+        by_comm: Dict[int, List[Bucket]] = {}
+        for b in self.buckets:
+            by_comm.setdefault(id(b.comm), []).append(b)
+        for bl in by_comm.values():
+            comm = bl[0].comm
+            need = sum(_pad512(b.numel * _esize(b.dtype)) + _pad512(b.numel * 4) for b in bl)
+            use = bool(want) and self.device.type == "cuda" and comm.nranks > 1 and \
+                all(b.dtype in (torch.bfloat16, torch.float16, torch.float32) for b in bl)
+            # collective call: every member asks, and all of them get the same answer
+            if use and not comm.nvls_init(need + (80 << 20)):
+                use = False
+            if use:
+                _uc, _mc, total, used = comm.nvls_info()
+                use = total - used >= need              # an arena made earlier (by someone else) may be too small
+            if use:
+                self.nvls_comms.append(comm)
+            for b in bl:
+                b.nvls = use
+                if use:
+                    from ..utils.tensors import tensor_from_ptr
+                    b.grad = tensor_from_ptr(comm.nvls_alloc(b.numel * _esize(b.dtype)), (b.numel,), b.dtype, self.device).zero_()
+                    b.grad32 = tensor_from_ptr(comm.nvls_alloc(b.numel * 4), (b.numel,), torch.float32, self.device).zero_()
+                else:
+                    b.grad = self._pool.zeros((b.numel,), b.dtype)
+                    b.grad32 = self._pool.zeros((b.numel,), torch.float32)
+                with torch.no_grad():
+                    for p, off in zip(b.params, b.offsets):
+                        p.grad = _view_like(b.grad, off, p)
+
+    def gradient_path(self) -> str:
+        """Which schedule the buckets take, for benchmark records."""
+        kinds = sorted({"multimem (NVLS)" if b.nvls else "peer loads/stores" for b in self.buckets})
+        return " + ".join(kinds)
+
     def _make_hook(self, b: Bucket):
         def hook(_param):
+            if self._capturing:
+                b.pending -= 1
+                if b.pending == 0:
+                    self.ctx.trigger_on_stream(b.coll_id, self._stream())
+                    self._captured.append(b)
+                return
             if not self.hooks_enabled:
                 return
             b.pending -= 1
@@ -188,6 +253,37 @@ class DaemonDDP:
         """Submit every bucket now (after a captured backward pass), in this rank's shuffled order."""
         self._ready = [b for b in self.buckets if b not in self._submitted]
         self._flush()
+
+    # ---- captured steps: the release of a bucket is a kernel inside the graph, the submission is published before
+    # ---- the replay, so the bucket is reduced while the rest of the captured backward pass still runs
+    def begin_capture(self) -> None:
+        """Gradient hooks now record the buckets' releases into the stream that is being captured."""
+        self._capturing = True
+        self._captured: List[Bucket] = []
+        for b in self.buckets:
+            b.pending = len(b.params)
+
+    def end_capture(self) -> None:
+        self._capturing = False
+        for b in self.buckets:
+            b.pending = len(b.params)
+
+    def publish_deferred(self) -> None:
+        """Before a replay: publish every bucket's submission, in this rank's shuffled order."""
+        batch = [b for b in self.buckets if b not in self._submitted]
+        if self.randomize:
+            self._rng.shuffle(batch)
+        for b in batch:
+            self.ctx.run_deferred(b.coll_id, b.grad.data_ptr(), b.grad32.data_ptr())
+            self._submitted.append(b)
+
+    def release_uncaptured(self) -> None:
+        """After a replay: buckets whose release is not part of the graph (not every parameter received a gradient
+        during capture) are released now."""
+        s = self._stream()
+        for b in self.buckets:
+            if b not in self._captured:
+                self.ctx.trigger_on_stream(b.coll_id, s)
 
     def zero_grads(self) -> None:
         for b in self.buckets:

@@ -1,0 +1,197 @@
+"""Scheduler features of the daemon on the host backend: the sliced, resumable data phase, the adaptive wait
+budget, deferred submissions released by a separate (capturable) trigger, grouped send / recv with both ends in
+one thread.  No GPU is needed or touched."""
+import ctypes as C
+import os
+import random
+
+import numpy as np
+import pytest
+
+from helpers import host_array, run_ranks
+from test_host_runtime import _env
+
+
+@pytest.mark.parametrize("nranks", [2, 3])
+def test_sliced_data_phase_resumes_at_its_cursor(host_backend, nranks):
+    """Tiny slices force every collective through many yield / resume cycles while other collectives are queued:
+    every kind, odd element counts, per-rank shuffled orders.  Results must be exact and yields must have happened."""
+    nv = host_backend
+    kinds = [nv.ALLREDUCE, nv.ALLGATHER, nv.REDUCESCATTER, nv.BROADCAST, nv.REDUCE]
+    rng = random.Random(3)
+    counts = [rng.choice([4097, 30011, 12345, 65536 + 7]) for _ in kinds] * 2
+    kinds = kinds * 2
+    comms = nv.Comm.init_loopback(nranks)
+    stats = {}
+
+    def body(r):
+        c = comms[r]
+        ctx = nv.RankCtx(r)
+        bufs = []
+        for i, (k, n) in enumerate(zip(kinds, counts)):
+            ctx.prepare(i, c, k, n, nv.FLOAT32, root=i % nranks)
+            sn = n * (nranks if k == nv.REDUCESCATTER else 1)
+            rn = n * (nranks if k == nv.ALLGATHER else 1)
+            sp, rp = c.alloc(sn * 4), c.alloc(rn * 4)
+            bufs.append((sp, rp, host_array(sp, sn, np.float32), host_array(rp, rn, np.float32)))
+        ctx.finalize()
+        order_rng = random.Random(50 + r)
+        for it in range(3):
+            order = list(range(len(kinds)))
+            order_rng.shuffle(order)
+            for i in order:
+                # position-dependent data: a slice that lands at the wrong offset cannot go unnoticed
+                sn = bufs[i][2].size
+                bufs[i][2][:] = (np.arange(sn, dtype=np.float32) % 251) + (r + 1) * 1000 + it
+                ctx.run(i, bufs[i][0], bufs[i][1])
+            assert ctx.wait_all(120000) == nv.SUCCESS
+            for i, (k, n) in enumerate(zip(kinds, counts)):
+                out = bufs[i][3]
+
+                def src(q, m):
+                    return (np.arange(m, dtype=np.float32) % 251) + (q + 1) * 1000 + it
+                if k == nv.ALLREDUCE:
+                    np.testing.assert_array_equal(out, sum(src(q, n) for q in range(nranks)))
+                elif k == nv.REDUCESCATTER:
+                    np.testing.assert_array_equal(out, sum(src(q, n * nranks)[r * n:(r + 1) * n] for q in range(nranks)))
+                elif k == nv.ALLGATHER:
+                    np.testing.assert_array_equal(out, np.concatenate([src(q, n) for q in range(nranks)]))
+                elif k == nv.BROADCAST:
+                    np.testing.assert_array_equal(out, src(i % nranks, n))
+                elif k == nv.REDUCE and r == i % nranks:
+                    np.testing.assert_array_equal(out, sum(src(q, n) for q in range(nranks)))
+        import time
+        time.sleep(0.05)
+        stats[r] = ctx.stats()
+        ctx.destroy()
+
+    with _env(DFCCL_SLICE_BYTES=4096, DFCCL_DAEMON_BLOCKS=2, DFCCL_MIN_BYTES_PER_BLOCK=16384, DFCCL_IDLE_QUIT_US=2000):
+        run_ranks(nranks, body, timeout=300)
+    for c in comms:
+        c.destroy()
+    assert all(s["dataYields"] > 0 for s in stats.values()), stats
+
+
+def test_unsliced_data_phase_never_yields(host_backend):
+    nv = host_backend
+    comms = nv.Comm.init_loopback(2)
+    stats = {}
+
+    def body(r):
+        ctx = nv.RankCtx(r)
+        for i in range(4):
+            ctx.prepare(i, comms[r], nv.ALLREDUCE, 50000, nv.FLOAT32)
+        ctx.finalize()
+        p = comms[r].alloc(200000)
+        host_array(p, 50000, np.float32)[:] = 1
+        for i in range(4):
+            ctx.run(i, p, comms[r].alloc(200000))
+        assert ctx.wait_all(60000) == nv.SUCCESS
+        import time
+        time.sleep(0.05)
+        stats[r] = ctx.stats()
+        ctx.destroy()
+
+    with _env(DFCCL_SLICE_BYTES=0):
+        run_ranks(2, body)
+    for c in comms:
+        c.destroy()
+    assert all(s["dataYields"] == 0 for s in stats.values())
+
+
+@pytest.mark.parametrize("trigger_first", [False, True])
+def test_deferred_submission_runs_when_released(host_backend, trigger_first):
+    """dfcclRunDeferred publishes, dfcclTriggerOnStream releases; either order; one release per submission."""
+    nv = host_backend
+    comms = nv.Comm.init_loopback(2)
+
+    def body(r):
+        ctx = nv.RankCtx(r)
+        ctx.prepare(0, comms[r], nv.ALLREDUCE, 1000, nv.FLOAT32)
+        ctx.prepare(1, comms[r], nv.ALLREDUCE, 1000, nv.FLOAT32)
+        ctx.finalize()
+        p, q = comms[r].alloc(4000), comms[r].alloc(4000)
+        a, b = host_array(p, 1000, np.float32), host_array(q, 1000, np.float32)
+        for it in range(5):
+            a[:] = r + 1 + it
+            b[:] = 10 * (r + 1) + it
+            ids = (0, 1) if (r + it) % 2 else (1, 0)               # ranks publish in different orders
+            if trigger_first:
+                for i in ids:
+                    ctx.trigger_on_stream(i, 0)
+            for i in ids:
+                ctx.run_deferred(i, p if i == 0 else q, p if i == 0 else q)
+            if not trigger_first:
+                import time
+                time.sleep(0.002)
+                assert ctx.host_stats()["cqesDelivered"] == 2 * it          # nothing runs before its release
+                for i in reversed(ids):
+                    ctx.trigger_on_stream(i, 0)
+            assert ctx.wait_all(60000) == nv.SUCCESS
+            assert np.all(a == 3 + 2 * it) and np.all(b == 30 + 2 * it)
+        ctx.destroy()
+
+    run_ranks(2, body)
+    for c in comms:
+        c.destroy()
+
+
+def test_patience_grows_after_successful_waits(host_backend):
+    """With a tiny base budget and a large success factor, collectives still complete under disordered issue, and
+    fewer context switches are needed than with the factor switched off."""
+    nv = host_backend
+    switches = {}
+    for factor in (0, 50):
+        comms = nv.Comm.init_loopback(2)
+        st = {}
+
+        def body(r):
+            ctx = nv.RankCtx(r)
+            for i in range(8):
+                ctx.prepare(i, comms[r], nv.ALLREDUCE, 20000, nv.FLOAT32, algo=nv.ALGO_TWOSHOT)
+            ctx.finalize()
+            p = [comms[r].alloc(80000) for _ in range(8)]
+            rng = random.Random(r)
+            for it in range(10):
+                order = list(range(8))
+                rng.shuffle(order)
+                for i in order:
+                    host_array(p[i], 20000, np.float32)[:] = 1
+                    ctx.run(i, p[i], p[i])
+                assert ctx.wait_all(60000) == nv.SUCCESS
+                for i in range(8):
+                    assert np.all(host_array(p[i], 20000, np.float32) == 2)
+            import time
+            time.sleep(0.05)
+            st[r] = ctx.stats()
+            ctx.destroy()
+
+        with _env(DFCCL_BASE_CTX_SWITCH_THRESHOLD=2, DFCCL_NUM_TRY_TASKQ_HEAD=1, DFCCL_RECV_SUCCESS_FACTOR=factor):
+            run_ranks(2, body, timeout=240)
+        for c in comms:
+            c.destroy()
+        switches[factor] = sum(s["ctxSwitches"] for s in st.values())
+    assert switches[0] > 0            # the tiny budget did force preemptions; the run with patience completed as well
+
+
+def test_grouped_send_recv_with_both_ends_in_one_thread(host_backend):
+    """ncclCommInitAll, then one thread issues a group with a send and a receive on every communicator: every
+    kernel of the flush is started before any is waited for, staging pieces are released without blocking."""
+    nv = host_backend
+    L = nv.lib()
+    n = 3
+    comms = nv.Comm.init_all(n)
+    vp = C.c_void_p
+    out = [np.full(3000, 7 + r, np.int32) for r in range(n)]
+    inp = [np.zeros(3000, np.int32) for r in range(n)]           # plain host arrays: receives are staged
+    for rep in range(3):
+        nv.check(L.ncclGroupStart())
+        for r in range(n):
+            nv.check(L.ncclSend(vp(out[r].ctypes.data), 3000, nv.INT32, (r + 1) % n, comms[r].handle, None))
+            nv.check(L.ncclRecv(vp(inp[r].ctypes.data), 3000, nv.INT32, (r - 1) % n, comms[r].handle, None))
+        nv.check(L.ncclGroupEnd())
+        for r in range(n):
+            assert np.all(inp[r] == 7 + (r - 1) % n)
+            inp[r][:] = 0
+    for c in comms:
+        c.destroy()
