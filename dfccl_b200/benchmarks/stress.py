@@ -53,7 +53,11 @@ def main(argv=None):
     ap.add_argument("--seed", type=int, default=2024)
     ap.add_argument("--blocks", type=int, default=0)
     ap.add_argument("--out", default="")
+    ap.add_argument("--trace", default="", help="write the device trace (Chrome trace JSON) here, one file per rank")
     a = ap.parse_args(argv)
+    if a.trace:
+        os.environ["DFCCL_TRACE"] = "1"
+        os.environ.setdefault("DFCCL_TRACE_EVENTS", str(1 << 18))
 
     rng = random.Random(a.seed)                       # the SAME set of collectives on every rank
     kinds = [rng.choice([nv.ALLREDUCE, nv.ALLGATHER, nv.REDUCESCATTER, nv.BROADCAST]) for _ in range(a.colls)]
@@ -116,13 +120,15 @@ def main(argv=None):
     wall = time.perf_counter() - t0
     time.sleep(0.05)
     st = ctx.stats()
-    res = torch.tensor([done_iters, bad, rc, st["ctxSwitches"], st["waitTimeouts"]], device=dev, dtype=torch.float64)
+    res = torch.tensor([done_iters, bad, rc, st["ctxSwitches"], st["waitTimeouts"], st["dataYields"]], device=dev, dtype=torch.float64)
     if world > 1:
         import torch.distributed as dist
         allres = [torch.zeros_like(res) for _ in range(world)]
         dist.all_gather(allres, res)
     else:
         allres = [res]
+    if a.trace:
+        ctx.trace_dump(a.trace + (f".rank{rank}" if rank else ""))
     ctx.destroy()
     if rank == 0:
         out = {"world": world, "colls": a.colls, "iters_requested": a.iters,
@@ -130,6 +136,9 @@ def main(argv=None):
                "wrong_results": int(sum(float(r[1]) for r in allres)),
                "nonzero_status_ranks": int(sum(1 for r in allres if float(r[2]) != 0)),
                "ctx_switches_total": int(sum(float(r[3]) for r in allres)),
+               "ctx_switches_per_iter_per_rank": sum(float(r[3]) for r in allres) / world / max(done_iters, 1),
+               "data_yields_per_iter_per_rank": sum(float(r[5]) for r in allres) / world / max(done_iters, 1),
+               "daemon_blocks": a.blocks or int(os.environ.get("DFCCL_DAEMON_BLOCKS", "32")),
                "wait_timeouts_total": int(sum(float(r[4]) for r in allres)),
                "bytes_min": a.min_bytes, "bytes_max": a.max_bytes, "dtype": "bf16",
                "device_ms_per_iter": e0.elapsed_time(e1) / max(done_iters, 1), "wall_s": wall,

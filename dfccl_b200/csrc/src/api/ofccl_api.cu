@@ -16,6 +16,8 @@ using namespace dfccl;
 
 #define DF_API extern "C" __attribute__((visibility("default")))
 
+static ncclResult_t launchFromCaller(ofcclRankCtx* ctx);     // defined with the stream-ordered entry points below
+
 namespace dfccl {
 
 __global__ void dfcclWriteWordKernel(volatile uint64_t* p, uint64_t v) {
@@ -242,11 +244,12 @@ static bool spinFirst(std::unique_lock<std::mutex>& l, Quick quick, Pred pred, i
   return pred();
 }
 
-static ncclResult_t launchFromCaller(ofcclRankCtx* ctx);
-
 // Turns completion entries into callbacks: the reference's poller thread.
 static void pollerMain(ofcclRankCtx* ctx) {
   logSetRank(ctx->rank);
+  // this thread may launch the daemon: bind it to the context's device once (switching devices back and forth around
+  // a launch would make the runtime create a context on whatever device the thread started with)
+  if (ctx->backend == dfcclBackendCuda) cudaSetDevice(ctx->device);
   int64_t empty = 0;
   int idleSpins = 0;
   while (!ctx->stopPoller.load()) {
@@ -275,7 +278,7 @@ static void pollerMain(ofcclRankCtx* ctx) {
         if (!ctl_load(&ctx->ctl->alive) && !ctl_load(&ctx->ctl->abortFlag)) {
           // a released submission found the daemon parked: launch it from this thread (it is awake and has just seen
           // the release; handing over to the observer thread would add a thread wake-up to the collective's latency)
-          if (ctx->backend == dfcclBackendCuda && ctx->launcher->expected == 1) { if (launchFromCaller(ctx) != ncclSuccess) wakeLauncher(ctx->launcher.get()); }
+          if (ctx->backend == dfcclBackendCuda && ctx->launcher->expected == 1) { if (::launchFromCaller(ctx) != ncclSuccess) wakeLauncher(ctx->launcher.get()); }
           else wakeLauncher(ctx->launcher.get());
         }
       }

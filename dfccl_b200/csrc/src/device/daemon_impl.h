@@ -69,6 +69,7 @@ DF_HD int consumeSubmissions(BlockShared* sh, RankDev* rd, int b) {
       sh->trigColl[sh->nTrig] = (uint16_t)coll; sh->trigVal[sh->nTrig] = (uint32_t)q.trigger; ++sh->nTrig;
     } else {
       d->phase = PH_COPY_IN;          // runColl skips ahead to the first phase that has work
+      sh->actWait[sh->nActive] = 0;
       sh->active[sh->nActive++] = (uint16_t)coll;
       trace(rd, b, TR_START, coll);
     }
@@ -98,7 +99,7 @@ DF_HD uint32_t pollTriggers(BlockShared* sh, RankDev* rd, int b) {
       if (e & 0x8000u) {
         const int coll = e & 0x7fff;
         rd->dyn[(uint64_t)b * rd->maxColls + coll].phase = PH_COPY_IN;
-        if (sh->nActive < DF_MAX_ACTIVE) sh->active[sh->nActive++] = (uint16_t)coll;
+        if (sh->nActive < DF_MAX_ACTIVE) { sh->actWait[sh->nActive] = 0; sh->active[sh->nActive++] = (uint16_t)coll; }
         trace(rd, b, TR_START, coll);
       } else { sh->trigColl[w] = e; sh->trigVal[w] = sh->trigVal[i]; ++w; }
     }
@@ -108,18 +109,47 @@ DF_HD uint32_t pollTriggers(BlockShared* sh, RankDev* rd, int b) {
   return fired;
 }
 
+// Readiness scan: one thread per parked entry of the task queue reads that collective's flag words of this block
+// (n loads of local memory) and marks the entry for a visit when every peer has posted the epoch the entry waits
+// for.  No context is loaded and nobody spins: a queue of stalled collectives costs one scan per pass instead of a
+// context switch and a polling budget each.  Everybody calls it; returns the number of entries that became ready.
+DF_HD uint32_t scanParked(BlockShared* sh, RankDev* rd, int b) {
+  const int tid = df_tid(), nt = df_nthreads();
+  const uint32_t nAct = sh->nActive;
+  if (tid == 0) sh->nReady = 0;
+  df_sync();
+  for (uint32_t i = tid; i < nAct; i += nt) {
+    const uint32_t w = sh->actWait[i];
+    if (w == 0) continue;
+    const int coll = sh->active[i];
+    if (coll == 0xffff) continue;
+    const CollStatic* c = &rd->colls[coll];
+    const int n = c->nranks, me = c->rank;
+    const FlagSlot* f = c->myFlags + (uint64_t)b * n;
+    const uint64_t epoch = rd->dyn[(uint64_t)b * rd->maxColls + coll].epoch;
+    bool ok = true;
+    for (int j = 0; j < n; ++j) {
+      if (j == me) continue;
+      ok = ok && ld_relaxed_sys_u64(w == 1 ? &f[j].arrive : &f[j].done) >= epoch;
+    }
+    if (ok) { sh->actWait[i] = 0; atomic_add_u32(&sh->nReady, 1u); }
+  }
+  df_sync();
+  return sh->nReady;
+}
+
 DF_HD void blockRestore(BlockShared* sh, RankDev* rd, int b) {
   const int tid = df_tid(), nt = df_nthreads();
   BlockSaved* sv = &rd->saved[b];
   if (tid == 0) {
-    sh->loadedColl = -1; sh->standalone = 0; sh->dynDirty = 0; sh->quit = 0; sh->abortSeen = 0;
+    sh->loadedColl = -1; sh->standalone = 0; sh->dynDirty = 0; sh->quit = 0; sh->abortSeen = 0; sh->ctl1Full = 0;
     sh->frontier = sv->frontier; sh->nActive = sv->nActive; sh->nTrig = sv->nTrig;
     DevStats z = {};
     sh->stats = z;
     sv->exited = 0;
   }
   df_sync();
-  for (uint32_t i = tid; i < sh->nActive; i += nt) sh->active[i] = sv->active[i];
+  for (uint32_t i = tid; i < sh->nActive; i += nt) { sh->active[i] = sv->active[i]; sh->actWait[i] = 0; }    // everything gets a visit first
   for (uint32_t i = tid; i < sh->nTrig; i += nt) { sh->trigColl[i] = sv->trigColl[i]; sh->trigVal[i] = sv->trigVal[i]; }
   df_sync();
 }
@@ -163,7 +193,7 @@ DF_HD void daemonBlockMain(RankDev* rd, int b, BlockShared* sh) {
   if (tid == 0) trace(rd, b, TR_LAUNCH, 0);
   uint64_t lastUseful = df_now_ns();     // only thread 0's copies of these are ever consulted
   const uint64_t bornNs = lastUseful;
-  uint64_t lastSlowCheck = 0;
+  uint64_t lastSlowCheck = 0, lastFullPass = 0;
   uint32_t winding = 0;
   uint32_t idleBackoff = 32;
 
@@ -173,32 +203,43 @@ DF_HD void daemonBlockMain(RankDev* rd, int b, BlockShared* sh) {
     const uint64_t tPass = tid == 0 ? df_now_ns() : 0;
     if (sh->nTrig && pollTriggers(sh, rd, b)) progressed = true;
     const uint64_t tWalk = tid == 0 ? df_now_ns() : 0;
-    // ---- 1. task queue traversal
+    // ---- 1. task queue traversal: parked entries are skipped unless the scan found their flags ready; now and then
+    // every entry is visited all the same, so that a wait that will never succeed reaches its time limit
     const uint32_t nAct = sh->nActive;
-    for (uint32_t i = 0; i < nAct; ++i) {
-      const int coll = sh->active[i];
-      if (coll == 0xffff) continue;
-      // the head of the queue is the oldest submission: give it more patience
-      // with nothing else queued there is nothing to switch to: polling longer is free
-      const uint32_t budget = rd->spinBudget * ((i == 0 || nAct == 1) ? rd->headTries : 1u);
-      bool moved = false;
-      int rc = runColl(sh, rd, b, coll, budget, &moved);
-      if (rc == RC_DONE || rc == RC_YIELD || moved) progressed = true;
-      if (tid == 0) {
-        sh->stats.visits++;
-        if (rc == RC_DONE) sh->active[i] = 0xffff;
+    if (nAct) {
+      if (scanParked(sh, rd, b)) progressed = true;
+      const bool fullPass = sh->ctl1Full != 0;
+      for (uint32_t i = 0; i < nAct; ++i) {
+        const int coll = sh->active[i];
+        if (coll == 0xffff) continue;
+        if (sh->actWait[i] && !fullPass) continue;
+        // With other collectives queued a wait gives up after a few polls: the scan brings the block back when
+        // the flags are there.  The oldest submission (head of the queue) gets more patience, and with nothing
+        // else queued there is nothing to switch to: polling longer is free.
+        const uint32_t base = nAct == 1 ? rd->spinBudget : (rd->spinBudget + 7u) / 8u;
+        const uint32_t budget = base * ((i == 0 || nAct == 1) ? rd->headTries : 1u);
+        bool moved = false;
+        int rc = runColl(sh, rd, b, coll, budget, &moved);
+        if (rc == RC_DONE || rc == RC_YIELD || moved) progressed = true;
+        if (tid == 0) {
+          sh->stats.visits++;
+          if (rc == RC_DONE) sh->active[i] = 0xffff;
+          sh->actWait[i] = rc == RC_STALLED ? (sh->dyn.phase == PH_WAIT_ARRIVE ? 1 : sh->dyn.phase == PH_WAIT_DONE ? 2 : 0) : 0;
+        }
+        // a collective released by its stream should not wait for a walk over a long queue
+        if (sh->nTrig && i + 1 < nAct && pollTriggers(sh, rd, b)) progressed = true;
       }
-      // a collective released by its stream should not wait for a walk over a long queue of stalled ones
-      if (sh->nTrig && i + 1 < nAct && pollTriggers(sh, rd, b)) progressed = true;
     }
     df_sync();
     // ---- 2. compaction, new submissions, idle decision: thread 0 decides, everybody obeys
     if (tid == 0) {
       sh->stats.passes++;
       uint32_t w = 0;
-      for (uint32_t i = 0; i < sh->nActive; ++i) if (sh->active[i] != 0xffff) sh->active[w++] = sh->active[i];
+      for (uint32_t i = 0; i < sh->nActive; ++i) if (sh->active[i] != 0xffff) { sh->active[w] = sh->active[i]; sh->actWait[w] = sh->actWait[i]; ++w; }
       sh->nActive = w;
       const uint64_t now = df_now_ns();
+      sh->ctl1Full = 0;
+      if (now - lastFullPass > 2000000) { sh->ctl1Full = 1; lastFullPass = now; }     // every 2 ms: visit parked entries too
       sh->stats.nsTriggers += tWalk - tPass; sh->stats.nsWalk += now - tWalk;
       // Words that change rarely are sampled rarely: the abort request and the "somebody left" word.  Every
       // 20 us, or right away when this pass achieved nothing.

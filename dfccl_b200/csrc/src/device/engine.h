@@ -57,6 +57,12 @@ struct BlockShared {
   uint32_t nTrig;
   uint32_t trigFired;
   uint16_t active[DF_MAX_ACTIVE];
+  // per task-queue entry: 0 = needs a visit, 1 = parked in the wait for the peers' arrival, 2 = parked in the wait for
+  // their done flags.  Parked entries are not visited (a visit loads the context and polls for a while); their flag
+  // words are looked at by one thread each in a scan over the whole queue, which marks the ready ones for a visit.
+  uint8_t actWait[DF_MAX_ACTIVE];
+  uint32_t nReady;
+  uint32_t ctl1Full;               // this pass visits parked entries too (set by thread 0 at the end of the previous pass)
   uint16_t trigColl[DF_MAX_ACTIVE];
   uint32_t trigVal[DF_MAX_ACTIVE];  // low 32 bits of the value the trigger word must reach
 };

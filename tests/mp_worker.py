@@ -235,7 +235,7 @@ def scenario_fused_tp(nv, comm, rank, world, backend):
     return out
 
 
-def _gpt_hybrid(nv, comm, rank, world, backend, tp, pp, dp, port):
+def _gpt_hybrid(nv, comm, rank, world, backend, tp, pp, dp, port, schedule="1f1b", n_micro=2):
     """Hybrid tp x pp x dp training of a small GPT-2 against the same model on one rank: the loss of
     every step must agree (the second and third steps depend on the gradients and the update)."""
     import torch
@@ -250,11 +250,11 @@ def _gpt_hybrid(nv, comm, rank, world, backend, tp, pp, dp, port):
     from dfccl_b200.parallel.hybrid import HybridTrainer, build_mesh
     cfg = GPT2Config(n_layer=4, d_model=512, n_head=8, seq_len=128, vocab=512) if cuda else \
         GPT2Config(n_layer=2 if pp < 3 else pp, d_model=64, n_head=4, seq_len=32, vocab=96)
-    micro_batch, n_micro, steps = 2, 2, 3
+    micro_batch, steps = 2, 3
     d = Dist(rank, world, rank if cuda else 0, dev, comm, True)
     mesh = build_mesh(d, tp, pp, dp)
     stage = GPT2Stage(cfg, mesh.tp_group, mesh.pp_rank, pp, micro_batch)
-    tr = HybridTrainer(d, mesh, stage, n_micro=n_micro, lr=0.3, bucket_mb=0.25, seed=3)
+    tr = HybridTrainer(d, mesh, stage, n_micro=n_micro, lr=0.3, bucket_mb=0.25, seed=3, schedule=schedule)
     g = torch.Generator().manual_seed(11)
     data = torch.randint(0, cfg.vocab, (dp, n_micro, micro_batch, cfg.seq_len + 1), generator=g)
     tok, tgt = data[mesh.dp_rank, ..., :-1].to(dev), data[mesh.dp_rank, ..., 1:].to(dev)
@@ -267,6 +267,19 @@ def _gpt_hybrid(nv, comm, rank, world, backend, tp, pp, dp, port):
         nv.check(nv.lib().dfcclGemmCheck(C.byref(bad)))
         assert bad.value == 0, "a fused GEMM kernel gave up on a wait"
     st = tr.ddp.stats()
+    peak = tr.peak_live_microbatches
+    graphed = None
+    if cuda and pp == 1:
+        # the same step captured in a CUDA graph: it must really be captured and replayed, and keep training
+        tg = HybridTrainer(d, mesh, GPT2Stage(cfg, mesh.tp_group, mesh.pp_rank, pp, micro_batch), n_micro=n_micro, lr=0.3,
+                           bucket_mb=0.25, seed=3, use_graph=True, schedule=schedule)
+        gl = [float(tg.step(tok, tgt)) for _ in range(3)]
+        torch.cuda.synchronize()
+        assert tg._graph is not None, "use_graph=True did not capture a graph"
+        assert abs(gl[0] - losses[0]) < 3e-2 * max(1.0, abs(losses[0])), (gl, losses)
+        assert gl[-1] < gl[0], gl
+        graphed = gl
+        tg.close()
     tr.close()
     if rank == 0:                                           # the same model, unsharded, on this rank alone
         (c1,) = nv.Comm.init_loopback(1, rank if cuda else 0)
@@ -282,7 +295,15 @@ def _gpt_hybrid(nv, comm, rank, world, backend, tp, pp, dp, port):
         assert ref[-1] < ref[0] - 0.05, ref
     dist.barrier()
     dist.destroy_process_group()
-    return {"losses": losses, "cqes": st["cqesDelivered"]}
+    return {"losses": losses, "cqes": st["cqesDelivered"], "peak_live": peak, "pp_rank": mesh.pp_rank, "graphed": graphed}
+
+
+def scenario_gpt_pp3_gpipe(nv, comm, rank, world, backend):
+    return _gpt_hybrid(nv, comm, rank, world, backend, 1, 3, 1, 29586, schedule="gpipe", n_micro=4)
+
+
+def scenario_gpt_pp3_1f1b(nv, comm, rank, world, backend):
+    return _gpt_hybrid(nv, comm, rank, world, backend, 1, 3, 1, 29587, schedule="1f1b", n_micro=4)
 
 
 def scenario_gpt_tp2(nv, comm, rank, world, backend):

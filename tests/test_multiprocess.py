@@ -47,6 +47,20 @@ def test_host_gpt2_hybrid_parallel(layout, world):
     assert len(set(losses)) == 1, losses                     # every rank reports the same global loss
 
 
+def test_host_pipeline_schedules_agree_and_1f1b_holds_fewer_activations():
+    """Three pipeline stages, four micro-batches: GPipe and 1F1B train identically (same losses as the unsharded
+    model, checked inside the scenario); 1F1B holds at most pp - stage micro-batches of activations, GPipe all."""
+    a = mp_worker.launch(3, "host", "gpt_pp3_gpipe", timeout=300)
+    b = mp_worker.launch(3, "host", "gpt_pp3_1f1b", timeout=300)
+    for r in a.values():
+        assert r["peak_live"] == 4
+    for r in b.values():
+        assert r["peak_live"] == min(3 - r["pp_rank"], 4)
+    la = [round(x, 3) for x in next(iter(a.values()))["losses"]]
+    lb = [round(x, 3) for x in next(iter(b.values()))["losses"]]
+    assert la == lb, (la, lb)
+
+
 @pytest.mark.gpu
 @pytest.mark.multigpu
 def test_gpu_gpt2_hybrid_parallel():
