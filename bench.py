@@ -146,7 +146,7 @@ def allreduce_sweep(d):
     ids = 4
     for k, sz in enumerate(sizes):
         for j in range(ids):
-            big = nvls and sz >= (1 << 20)
+            big = nvls and world >= 4 and sz >= (1 << 20)
             ctx.prepare(k * ids + j, d.comm, nv.ALLREDUCE, sz // 2, nv.BFLOAT16, algo=nv.ALGO_NVLS if big else nv.ALGO_AUTO, arena_buffers=big)
     ctx.finalize()
     stream = torch.cuda.current_stream()
@@ -187,7 +187,7 @@ def allreduce_sweep(d):
                      "stream_kernel_us": round(us_s, 1), "stream_kernel_busbw_gbs": round(sz / us_s / 1e3 * f, 1),
                      "nccl_2_28_us": round(us_n, 1), "nccl_2_28_busbw_gbs": round(sz / us_n / 1e3 * f, 1)})
     ctx.destroy()
-    return {"dtype": "bf16", "n_gpus": world, "multimem_schedule_from_1MB": nvls, "rows": rows}
+    return {"dtype": "bf16", "n_gpus": world, "multimem_schedule_from_1MB": bool(nvls and world >= 4), "rows": rows}
 
 
 def run(args):

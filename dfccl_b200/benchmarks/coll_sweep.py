@@ -72,6 +72,9 @@ def main(argv=None):
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--algo", default="auto", choices=["auto", "oneshot", "twoshot", "nvls"])
+    ap.add_argument("--nvls-from", dest="nvls_from", type=int, default=-1,
+                    help="with --algo auto: message sizes from this many bytes up take the multimem schedule, operands in the "
+                         "multicast arena (-1 = 1 MiB on 4 or more ranks, off below; 0 = off)")
     ap.add_argument("--blocks", type=int, default=0, help="daemon blocks per rank (0 = default)")
     ap.add_argument("--ids", type=int, default=4, help="registrations per case, used round-robin so that the host can enqueue ahead")
     ap.add_argument("--skip-nccl", action="store_true")
@@ -101,17 +104,19 @@ def main(argv=None):
     bufs = {}
     max_bytes = max(sizes)
     nvls = False
-    if a.algo == "nvls" and world > 1:
+    nvls_from = a.nvls_from if a.nvls_from >= 0 else ((1 << 20) if world >= 4 else 0)
+    if a.algo == "nvls":
+        nvls_from = 1
+    if nvls_from and world > 1:
         # operands live in the switch-multicast arena, so the schedule works on them in place
-        os.environ.setdefault("DFCCL_NVLS_MIN_BYTES", "4096")
+        os.environ.setdefault("DFCCL_NVLS_MIN_BYTES", "4096" if a.algo == "nvls" else str(nvls_from))
         nvls = d.comm.nvls_init(2 * max_bytes + (96 << 20))
         if rank == 0:
-            print(json.dumps({"nvls_available": bool(nvls)}), flush=True)
+            print(json.dumps({"nvls_available": bool(nvls), "nvls_from_bytes": nvls_from}), flush=True)
     if nvls:
         send_p, recv_p = d.comm.nvls_alloc(max_bytes + 256), d.comm.nvls_alloc(max_bytes + 256)
     else:
-        send_p = d.comm.alloc(max_bytes * (world if "reducescatter" in a.kinds else 1) + 256)
-        recv_p = d.comm.alloc(max_bytes * (world if "allgather" in a.kinds else 1) + 256)
+        send_p, recv_p = d.comm.alloc(max_bytes + 256), d.comm.alloc(max_bytes + 256)
     for cid, (k, dt, sz) in enumerate(cases):
         tdt, ndt = DT[dt]
         es = torch.empty((), dtype=tdt).element_size()
@@ -119,9 +124,11 @@ def main(argv=None):
         count = total // world if k in ("allgather", "reducescatter") else total
         if count == 0:
             continue
+        big = nvls and sz >= nvls_from and (count * es) % 16 == 0 and k in ("allreduce", "allgather", "reducescatter")
         for j in range(a.ids):
-            ctx.prepare(cid * a.ids + j, d.comm, KIND[k], count, ndt, algo=algo if k == "allreduce" else nv.ALGO_AUTO)
-        bufs[cid] = (count, total)
+            ctx.prepare(cid * a.ids + j, d.comm, KIND[k], count, ndt,
+                        algo=nv.ALGO_NVLS if big else (algo if k == "allreduce" and a.algo != "nvls" else nv.ALGO_AUTO), arena_buffers=big)
+        bufs[cid] = (count, total, big)
     ctx.finalize()
     stream = torch.cuda.current_stream()
     g = torch.Generator(device="cpu").manual_seed(1234 + rank)
@@ -130,7 +137,7 @@ def main(argv=None):
         if cid not in bufs:
             continue
         tdt, ndt = DT[dt]
-        count, total = bufs[cid]
+        count, total, big = bufs[cid]
         sn = count * world if k == "reducescatter" else count
         rn = count * world if k == "allgather" else count
         sv = tensor_from_ptr(send_p, (sn,), tdt, dev)
@@ -156,7 +163,7 @@ def main(argv=None):
             for j in range(a.ids):
                 ctx.stream_wait(base + j, stream.cuda_stream)
 
-        row = {"kind": k, "dtype": dt, "bytes": sz, "n": world}
+        row = {"kind": k, "dtype": dt, "bytes": sz, "n": world, "daemon_schedule": "multimem" if big else "peer"}
         us = time_loop(daemon_op, iters, a.warmup, world)
         assert ctx.wait_all(60000) == nv.SUCCESS
         row["daemon_us"] = us

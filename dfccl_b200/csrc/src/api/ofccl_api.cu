@@ -614,7 +614,12 @@ static ncclResult_t submit(ofcclRankCtx* ctx, const void* send, void* recv, int 
   Sqe q;
   memset(&q, 0, sizeof(q));
   uint64_t trig = 0;
-  const bool deferWake = onStream && ctx->backend == dfcclBackendCuda;
+  // A stream-ordered release normally also writes a host-visible mirror of the trigger word, which the poller
+  // watches to launch a parked daemon.  While an instance is running and held resident (a stream is parked on one
+  // of this context's completions) nobody needs that wake-up: the release is then a single write to device memory -
+  // every stream memory operation is preceded by a system-wide fence, so the second write costs as much as the first.
+  const bool deferWake = onStream && ctx->backend == dfcclBackendCuda &&
+                         !(mode == SUBMIT_STREAM && ctl_load(&ctx->ctl->hold) && ctl_load(&ctx->ctl->alive) && ctx->fnWrite64);
   {
     std::unique_lock<std::mutex> l(ctx->mu);
     CollEntry* ep = collId >= 0 && collId < (int)ctx->byId.size() ? ctx->byId[collId] : nullptr;
@@ -723,7 +728,11 @@ static ncclResult_t submit(ofcclRankCtx* ctx, const void* send, void* recv, int 
     volatile uint64_t* word = ctx->rdHost.trigger + collId;
     if (ctx->backend == dfcclBackendCuda) {
       volatile uint64_t* mirror = ctx->hostTrig + collId;
-      if (ctx->fnBatch) {
+      if (!deferWake && ctx->fnWrite64) {
+        typedef CUresult (*Fn)(CUstream, CUdeviceptr, cuuint64_t, unsigned int);
+        CUresult r = ((Fn)ctx->fnWrite64)((CUstream)stream, (CUdeviceptr)(uintptr_t)word, trig, 0);
+        if (r != CUDA_SUCCESS) { DF_WARN("cuStreamWriteValue64 failed (%d)", (int)r); return ncclUnhandledCudaError; }
+      } else if (ctx->fnBatch) {
         // device trigger word and its host mirror in one driver call
         typedef CUresult (*Fn)(CUstream, unsigned int, CUstreamBatchMemOpParams*, unsigned int);
         CUstreamBatchMemOpParams ops[2];

@@ -170,34 +170,80 @@ DF_HD void packAll(uint4* ow, const A* r) {
   for (int k = 0; k < V; ++k) Lane<Tout>::put(ow[k / VO], k % VO, (typename Elem<Tout>::Acc)r[k]);
 }
 
+// ---- sources that are not 16-byte aligned.  All sources of one call share one misalignment (they are the same offset
+// into symmetric buffers), so a logical pack is 16 bytes that straddle two aligned packs: bytes [shift, shift + 16) of
+// lo:hi.  The aligned packs are loaded as usual and shifted in registers; in a full trip the upper pack of a thread is
+// the lower pack of its neighbour lane and comes by shuffle, so the memory traffic stays that of an aligned copy.
+// (Role of the reference's misaligned-load helpers, src/collectives/device/op128.h:40-68.)
+DF_HD uint4 shiftPack(const uint4& lo, const uint4& hi, uint32_t shift) {
+#if DF_DEVICE_CODE
+  const uint32_t bs = (shift & 3u) * 8u;
+  uint32_t w0, w1, w2, w3, w4;
+  switch (shift >> 2) {
+    case 0: w0 = lo.x; w1 = lo.y; w2 = lo.z; w3 = lo.w; w4 = hi.x; break;
+    case 1: w0 = lo.y; w1 = lo.z; w2 = lo.w; w3 = hi.x; w4 = hi.y; break;
+    case 2: w0 = lo.z; w1 = lo.w; w2 = hi.x; w3 = hi.y; w4 = hi.z; break;
+    default: w0 = lo.w; w1 = hi.x; w2 = hi.y; w3 = hi.z; w4 = hi.w; break;
+  }
+  return make_uint4(__funnelshift_r(w0, w1, bs), __funnelshift_r(w1, w2, bs), __funnelshift_r(w2, w3, bs), __funnelshift_r(w3, w4, bs));
+#else
+  unsigned char b[32];
+  __builtin_memcpy(b, &lo, 16);
+  __builtin_memcpy(b + 16, &hi, 16);
+  uint4 o;
+  __builtin_memcpy(&o, b + shift, 16);
+  return o;
+#endif
+}
+
+// U logical packs of one source for this thread; pack u starts `u * strideB` bytes after `s`, `shift` = s & 15.
+// SHIFT = false: s is aligned.  FULL: every thread of the block loads all of its U packs (warp shuffles are safe).
+template <bool FULL, bool SHIFT, int U>
+DF_HD void loadPacks(uint4* out, const char* s, uint32_t strideB, uint32_t shift, uint64_t p0, uint32_t stride, uint64_t nPacks) {
+  if (!SHIFT) {
+#pragma unroll
+    for (int u = 0; u < U; ++u) if (FULL || p0 + (uint64_t)u * stride < nPacks) out[u] = ld16(s + (uint64_t)u * strideB);
+    return;
+  }
+  const char* a = s - shift;                       // aligned; every aligned pack touched holds at least one wanted byte
+#pragma unroll
+  for (int u = 0; u < U; ++u) {
+    if (!(FULL || p0 + (uint64_t)u * stride < nPacks)) continue;
+    const uint4 lo = ld16(a + (uint64_t)u * strideB);
+    uint4 hi;
+#if DF_DEVICE_CODE
+    if (FULL) {
+      hi.x = __shfl_down_sync(0xffffffffu, lo.x, 1); hi.y = __shfl_down_sync(0xffffffffu, lo.y, 1);
+      hi.z = __shfl_down_sync(0xffffffffu, lo.z, 1); hi.w = __shfl_down_sync(0xffffffffu, lo.w, 1);
+      if ((threadIdx.x & 31) == 31) hi = ld16(a + (uint64_t)u * strideB + 16);
+    } else
+#endif
+      hi = ld16(a + (uint64_t)u * strideB + 16);
+    out[u] = shiftPack(lo, hi, shift);
+  }
+}
+
 // One noinline body per (input type, output type, operator): the daemon's register
 // budget is the maximum over what it inlines, so the variants stay out of line.
 // The hot loop is written for instruction count (it was issue-bound at 150 warp instructions
 // per 16-byte pack in its first form): pointers are read from shared memory once per source
 // and trip, indices are a base plus compile-time multiples of the stride, the bounds test is
 // hoisted out of full trips, the scale is a float decided once, outputs are packed pairwise.
-template <typename Tin, typename Tout, int OP, bool FULL, int U>
+template <typename Tin, typename Tout, int OP, bool FULL, bool SHIFT, int U>
 DF_HD void reduceTrip(const DataArgs* a, uint64_t p0, uint64_t nPacks, uint32_t strideB, int nsrc, int ndst,
-                      typename Elem<Tin>::Acc mul, bool doMul, int postDiv, double dscale) {
+                      typename Elem<Tin>::Acc mul, bool doMul, int postDiv, double dscale,
+                      uint64_t srcOff, uint64_t dstOff, uint32_t shift) {
   typedef typename Elem<Tin>::Acc A;
   constexpr int V = 16 / (int)sizeof(Tin);
   constexpr int OUTB = V * (int)sizeof(Tout);
   constexpr int NW = (OUTB + 15) / 16;
   const uint32_t stride = strideB >> 4;
-  const uint64_t off = p0 * 16;
+  const uint64_t off = srcOff + p0 * 16;
   A acc[U][V];
   uint4 cur[U], nxt[U];
-  {
-    const char* s0 = a->src[0] + off;
-#pragma unroll
-    for (int u = 0; u < U; ++u) if (FULL || p0 + (uint64_t)u * stride < nPacks) cur[u] = ld16(s0 + (uint64_t)u * strideB);
-  }
+  loadPacks<FULL, SHIFT, U>(cur, a->src[0] + off, strideB, shift, p0, stride, nPacks);
   for (int j = 1; j <= nsrc; ++j) {
-    if (j < nsrc) {
-      const char* sj = a->src[j] + off;
-#pragma unroll
-      for (int u = 0; u < U; ++u) if (FULL || p0 + (uint64_t)u * stride < nPacks) nxt[u] = ld16(sj + (uint64_t)u * strideB);
-    }
+    if (j < nsrc) loadPacks<FULL, SHIFT, U>(nxt, a->src[j] + off, strideB, shift, p0, stride, nPacks);
 #pragma unroll
     for (int u = 0; u < U; ++u) {
 #pragma unroll
@@ -231,7 +277,7 @@ DF_HD void reduceTrip(const DataArgs* a, uint64_t p0, uint64_t nPacks, uint32_t 
     packAll<Tout, A, V>(ow[u], acc[u]);
   }
   for (int d = 0; d < ndst; ++d) {
-    char* o = a->dst[d] + p0 * OUTB;
+    char* o = a->dst[d] + dstOff + p0 * OUTB;
 #pragma unroll
     for (int u = 0; u < U; ++u) if (FULL || p0 + (uint64_t)u * stride < nPacks) {
       char* ou = o + (uint64_t)u * stride * OUTB;
@@ -244,12 +290,32 @@ DF_HD void reduceTrip(const DataArgs* a, uint64_t p0, uint64_t nPacks, uint32_t 
   }
 }
 
+// The unrolled trips of one call, for aligned (SHIFT = false) or uniformly misaligned sources.
+template <typename Tin, typename Tout, int OP, bool SHIFT>
+DF_HD void reduceTrips(const DataArgs* a, uint64_t nPacks, int nsrc, int ndst, typename Elem<Tin>::Acc mul, bool doMul, int postDiv,
+                       double scale, uint64_t srcOff, uint64_t dstOff, uint32_t shift) {
+  constexpr int U = OP == OP_SUM ? 4 : 2;     // the sum carries the traffic; the rarer operators trade speed for code size
+  const int tid = df_tid(), nt = df_nthreads();
+  // Software-pipelined over the sources inside a trip: the U loads of source j+1 are issued before
+  // the U packs of source j are consumed, so up to 2*U 16-byte loads are in flight per thread.
+  const uint64_t step = (uint64_t)nt * U;
+  const uint32_t strideB = (uint32_t)nt * 16u;
+  uint64_t base = 0;
+  for (; base + step <= nPacks; base += step)
+    reduceTrip<Tin, Tout, OP, true, SHIFT, U>(a, base + tid, nPacks, strideB, nsrc, ndst, mul, doMul, postDiv, scale, srcOff, dstOff, shift);
+  // what the unrolled trips leave: one pack per thread per trip, the last trip partly filled
+  for (; base + nt <= nPacks; base += nt)
+    reduceTrip<Tin, Tout, OP, true, SHIFT, 1>(a, base + tid, nPacks, strideB, nsrc, ndst, mul, doMul, postDiv, scale, srcOff, dstOff, shift);
+  if (base + tid < nPacks)
+    reduceTrip<Tin, Tout, OP, false, SHIFT, 1>(a, base + tid, nPacks, strideB, nsrc, ndst, mul, doMul, postDiv, scale, srcOff, dstOff, shift);
+}
+
 template <typename Tin, typename Tout, int OP>
 DF_HD_NOINLINE void reduce_copy(const DataArgs* a) {
   typedef typename Elem<Tin>::Acc A;
   constexpr int V = 16 / (int)sizeof(Tin);
   constexpr int OUTB = V * (int)sizeof(Tout);
-  constexpr int U = OP == OP_SUM ? 4 : 2;     // the sum carries the traffic; the rarer operators trade speed for code size
+  constexpr int DA = OUTB >= 16 ? 16 : OUTB;          // alignment the vector stores need
   const int tid = df_tid(), nt = df_nthreads();
   const int nsrc = a->nsrc, ndst = a->ndst;
   const uint64_t n = a->n;
@@ -258,65 +324,80 @@ DF_HD_NOINLINE void reduce_copy(const DataArgs* a) {
   const bool doMul = scale != 1.0;
   const A mul = (A)scale;
 
-  bool aligned = true;
-  for (int j = 0; j < nsrc; ++j) aligned &= ((uintptr_t)a->src[j] & 15) == 0;
-  for (int j = 0; j < ndst; ++j) aligned &= ((uintptr_t)a->dst[j] & (OUTB >= 16 ? 15 : OUTB - 1)) == 0;
-  const uint64_t nPacks = aligned ? n / V : 0;
-
-  // Software-pipelined over the sources inside a trip: the U loads of source j+1 are issued before
-  // the U packs of source j are consumed, so up to 2*U 16-byte loads are in flight per thread.
-  const uint64_t step = (uint64_t)nt * U;
-  const uint32_t strideB = (uint32_t)nt * 16u;
-  uint64_t base = 0;
-  for (; base + step <= nPacks; base += step)
-    reduceTrip<Tin, Tout, OP, true, U>(a, base + tid, nPacks, strideB, nsrc, ndst, mul, doMul, postDiv, scale);
-  // what the unrolled trips leave: one pack per thread per trip, the last trip partly filled
-  for (; base + nt <= nPacks; base += nt)
-    reduceTrip<Tin, Tout, OP, true, 1>(a, base + tid, nPacks, strideB, nsrc, ndst, mul, doMul, postDiv, scale);
-  if (base + tid < nPacks)
-    reduceTrip<Tin, Tout, OP, false, 1>(a, base + tid, nPacks, strideB, nsrc, ndst, mul, doMul, postDiv, scale);
-  // the ragged tail, or everything when a pointer is not 16-byte aligned: element by element
-  for (uint64_t i = nPacks * V + tid; i < n; i += nt) {
-    A acc = Elem<Tin>::up(ld_elem((const Tin*)a->src[0] + i));
-    for (int j = 1; j < nsrc; ++j) acc = red<OP>(acc, Elem<Tin>::up(ld_elem((const Tin*)a->src[j] + i)));
+  // The vector path needs all sources at one misalignment and all destinations at one misalignment (true for equal
+  // offsets into symmetric buffers): `head` elements bring the destinations to their alignment, from there on the
+  // sources are read as packs shifted by `shift` bytes.  Anything else goes element by element.
+  const uint32_t sphase = (uint32_t)((uintptr_t)a->src[0] & 15), dphase = (uint32_t)((uintptr_t)a->dst[0] & (DA - 1));
+  bool vec = (dphase % sizeof(Tout)) == 0 && (sphase % sizeof(Tin)) == 0;
+  for (int j = 1; j < nsrc; ++j) vec &= ((uintptr_t)a->src[j] & 15) == sphase;
+  for (int j = 1; j < ndst; ++j) vec &= ((uintptr_t)a->dst[j] & (DA - 1)) == dphase;
+  uint64_t head = vec ? ((DA - dphase) % DA) / sizeof(Tout) : 0;
+  if (head > n) head = n;
+  const uint32_t shift = (uint32_t)((sphase + head * sizeof(Tin)) & 15);
+  const uint64_t nPacks = vec ? (n - head) / V : 0;
+  const uint64_t srcOff = head * sizeof(Tin), dstOff = head * sizeof(Tout);
+  if (nPacks) {
+    if (shift == 0) reduceTrips<Tin, Tout, OP, false>(a, nPacks, nsrc, ndst, mul, doMul, postDiv, scale, srcOff, dstOff, 0);
+    else reduceTrips<Tin, Tout, OP, true>(a, nPacks, nsrc, ndst, mul, doMul, postDiv, scale, srcOff, dstOff, shift);
+  }
+  // the head, the ragged tail, or everything when the pointers do not line up: element by element
+  const uint64_t tail0 = head + nPacks * V;
+  for (uint64_t i = tid; i < head + (n - tail0); i += nt) {
+    const uint64_t e = i < head ? i : tail0 + (i - head);
+    A acc = Elem<Tin>::up(ld_elem((const Tin*)a->src[0] + e));
+    for (int j = 1; j < nsrc; ++j) acc = red<OP>(acc, Elem<Tin>::up(ld_elem((const Tin*)a->src[j] + e)));
     Tout o = Elem<Tout>::down(finish<Tin, Tout>(acc, scale, postDiv));
-    for (int d = 0; d < ndst; ++d) st_elem((Tout*)a->dst[d] + i, o);
+    for (int d = 0; d < ndst; ++d) st_elem((Tout*)a->dst[d] + e, o);
   }
 }
 
 // Byte copy of one source to M destinations (AllGather, Broadcast, staging).
-template <bool FULL, int U>
-DF_HD void copyTrip(const DataArgs* a, uint64_t p0, uint64_t nPacks, uint32_t strideB, int ndst) {
+template <bool FULL, bool SHIFT, int U>
+DF_HD void copyTrip(const DataArgs* a, uint64_t p0, uint64_t nPacks, uint32_t strideB, int ndst, uint64_t off, uint32_t shift) {
   const uint32_t stride = strideB >> 4;
-  const char* s0 = a->src[0] + p0 * 16;
   uint4 raw[U];
-#pragma unroll
-  for (int u = 0; u < U; ++u) if (FULL || p0 + (uint64_t)u * stride < nPacks) raw[u] = ld16(s0 + (uint64_t)u * strideB);
+  loadPacks<FULL, SHIFT, U>(raw, a->src[0] + off + p0 * 16, strideB, shift, p0, stride, nPacks);
   for (int d = 0; d < ndst; ++d) {
-    char* o = a->dst[d] + p0 * 16;
+    char* o = a->dst[d] + off + p0 * 16;
 #pragma unroll
     for (int u = 0; u < U; ++u) if (FULL || p0 + (uint64_t)u * stride < nPacks) st16(o + (uint64_t)u * strideB, raw[u]);
   }
 }
 
-#ifdef DF_DATAPATH_IMPL
-__host__ __device__ void copy_multi(const DataArgs* a) {
+template <bool SHIFT>
+DF_HD void copyTrips(const DataArgs* a, uint64_t nPacks, int ndst, uint64_t off, uint32_t shift) {
   constexpr int U = 8;
   const int tid = df_tid(), nt = df_nthreads();
-  const int ndst = a->ndst;
-  const uint64_t nbytes = a->n;
-  bool aligned = ((uintptr_t)a->src[0] & 15) == 0;
-  for (int j = 0; j < ndst; ++j) aligned &= ((uintptr_t)a->dst[j] & 15) == 0;
-  const uint64_t nPacks = aligned ? nbytes / 16 : 0;
   const uint64_t step = (uint64_t)nt * U;
   const uint32_t strideB = (uint32_t)nt * 16u;
   uint64_t base = 0;
-  for (; base + step <= nPacks; base += step) copyTrip<true, U>(a, base + tid, nPacks, strideB, ndst);
-  for (; base + nt <= nPacks; base += nt) copyTrip<true, 1>(a, base + tid, nPacks, strideB, ndst);
-  if (base + tid < nPacks) copyTrip<false, 1>(a, base + tid, nPacks, strideB, ndst);
-  for (uint64_t i = nPacks * 16 + tid; i < nbytes; i += nt) {
-    uint8_t b = ld_elem((const uint8_t*)a->src[0] + i);
-    for (int d = 0; d < ndst; ++d) st_elem((uint8_t*)a->dst[d] + i, b);
+  for (; base + step <= nPacks; base += step) copyTrip<true, SHIFT, U>(a, base + tid, nPacks, strideB, ndst, off, shift);
+  for (; base + nt <= nPacks; base += nt) copyTrip<true, SHIFT, 1>(a, base + tid, nPacks, strideB, ndst, off, shift);
+  if (base + tid < nPacks) copyTrip<false, SHIFT, 1>(a, base + tid, nPacks, strideB, ndst, off, shift);
+}
+
+#ifdef DF_DATAPATH_IMPL
+__host__ __device__ void copy_multi(const DataArgs* a) {
+  const int tid = df_tid(), nt = df_nthreads();
+  const int ndst = a->ndst;
+  const uint64_t nbytes = a->n;
+  // destinations at one misalignment: `head` bytes bring them to 16, from there the source is read as shifted packs
+  const uint32_t dphase = ndst ? (uint32_t)((uintptr_t)a->dst[0] & 15) : 0;
+  bool vec = ndst > 0;
+  for (int j = 1; j < ndst; ++j) vec &= ((uintptr_t)a->dst[j] & 15) == dphase;
+  uint64_t head = vec ? (16 - dphase) % 16 : 0;
+  if (head > nbytes) head = nbytes;
+  const uint32_t shift = (uint32_t)(((uintptr_t)a->src[0] + head) & 15);
+  const uint64_t nPacks = vec ? (nbytes - head) / 16 : 0;
+  if (nPacks) {
+    if (shift == 0) copyTrips<false>(a, nPacks, ndst, head, 0);
+    else copyTrips<true>(a, nPacks, ndst, head, shift);
+  }
+  const uint64_t tail0 = head + nPacks * 16;
+  for (uint64_t i = tid; i < head + (nbytes - tail0); i += nt) {
+    const uint64_t e = i < head ? i : tail0 + (i - head);
+    uint8_t b = ld_elem((const uint8_t*)a->src[0] + e);
+    for (int d = 0; d < ndst; ++d) st_elem((uint8_t*)a->dst[d] + e, b);
   }
 }
 

@@ -94,7 +94,8 @@ class DaemonDDP:
 
         ``nvls``: keep the gradient buckets in the communicator's switch-multicast arena and reduce them with the
         multimem schedule (the NVLink switch adds the members' copies; every GPU moves one message size instead of
-        two).  ``None`` = when the fabric offers it (``DFCCL_DDP_NVLS=0`` switches it off); memory bound to a
+        two).  ``None`` = when the fabric offers it and the communicator has at least four ranks
+        (``DFCCL_DDP_NVLS=0`` switches it off); memory bound to a
         multicast object ties the ranks' fates together, so tests of failure paths pass ``False``."""
         self.module = module
         self.dist = dist
@@ -188,7 +189,10 @@ class DaemonDDP:
         for bl in by_comm.values():
             comm = bl[0].comm
             need = sum(_pad512(b.numel * _esize(b.dtype)) + _pad512(b.numel * 4) for b in bl)
-            use = bool(want) and self.device.type == "cuda" and comm.nranks > 1 and \
+            # the switch halves the bytes a GPU moves only from four ranks on (on two ranks every schedule moves one
+            # message size per direction, and plain peer loads / stores do that faster)
+            min_ranks = int(os.environ.get("DFCCL_DDP_NVLS_MIN_RANKS", "4")) if self._nvls_request is None else 2
+            use = bool(want) and self.device.type == "cuda" and comm.nranks >= min_ranks and \
                 all(b.dtype in (torch.bfloat16, torch.float16, torch.float32) for b in bl)
             # collective call: every member asks, and all of them get the same answer
             if use and not comm.nvls_init(need + (80 << 20)):

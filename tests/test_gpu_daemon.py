@@ -36,7 +36,7 @@ TORCH_OF = {"FLOAT32": torch.float32, "BFLOAT16": torch.bfloat16, "FLOAT16": tor
 
 
 def _loopback_case(nv, kind, nranks, count, dt_name, *, op="SUM", root=0, out_name=None, scale=1.0, algo=0, heap=True,
-                   in_place=False, iters=2, blocks=None):
+                   in_place=False, iters=2, blocks=None, skew=(0, 0)):
     torch.cuda.set_device(0)
     dt, out_dt = TORCH_OF[dt_name], TORCH_OF[out_name or dt_name]
     kid = getattr(nv, kind.upper())
@@ -72,6 +72,7 @@ def _loopback_case(nv, kind, nranks, count, dt_name, *, op="SUM", root=0, out_na
                     rp = sp + r * count * es
             else:
                 rp = c.alloc(recv_n * eo + 256)
+                sp, rp = sp + skew[0] * es, rp + skew[1] * eo       # buffers that start off the 16-byte grid
             sv, rv = _t(sp, send_n, dt), _t(rp, recv_n, out_dt)
         else:
             sv = torch.empty(send_n, dtype=dt, device="cuda:0")
@@ -146,6 +147,16 @@ def test_loopback_allreduce_ops(nv, op):
 @pytest.mark.parametrize("count", [1, 17, 4096, 1 << 20])
 def test_loopback_allreduce_schedules(nv, algo, count):
     _loopback_case(nv, "allreduce", 4, count, "BFLOAT16", algo=getattr(nv, algo), iters=1)
+
+
+@pytest.mark.parametrize("kind", ["allreduce", "allgather", "reducescatter", "broadcast", "reduce"])
+@pytest.mark.parametrize("dt,count,skew", [("BFLOAT16", 150001, (0, 0)), ("BFLOAT16", 150001, (3, 5)), ("UINT8", 70003, (1, 6)),
+                                           ("FLOAT32", 99999, (1, 3))])
+def test_loopback_buffers_off_the_16_byte_grid(nv, kind, dt, count, skew):
+    """Odd element counts put the per-rank pieces of all-gather / reduce-scatter at odd byte offsets, skewed pointers
+    do the same to every kind: the data path then reads its sources as shifted packs (two aligned loads and a
+    funnel shift, the upper pack by warp shuffle) and must give exactly the aligned result."""
+    _loopback_case(nv, kind, 4, count, dt, root=1, iters=1, skew=skew, blocks=4)
 
 
 def test_loopback_eight_ranks_large(nv):
