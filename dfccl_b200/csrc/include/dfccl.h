@@ -251,6 +251,32 @@ ncclResult_t dfcclStreamWait(int collId, cudaStream_t stream, ofcclRankCtx_t ran
 ncclResult_t dfcclRunDeferred(const void* sendbuff, void* recvbuff, int collId, CallbackFunc callback,
                               void* callbackArgs, ofcclRankCtx_t rankCtx);
 ncclResult_t dfcclTriggerOnStream(int collId, cudaStream_t stream, ofcclRankCtx_t rankCtx);
+/* ---- tensor-parallel operators whose collective runs inside the GEMM kernel, registered with the rank context like
+ * any other collective: their rendezvous words, epoch counter and receive areas are allocated and exchanged when the
+ * context is finalized, they are counted in dfcclGetStats, a bounded wait that ran out inside one of them surfaces in
+ * dfcclGetAsyncError, and the SMs of this context's daemon are kept out of their grids (all CTAs of a fused launch
+ * must be resident at once).  The operators themselves are stream-ordered kernels: members of a communicator issue
+ * them in the same order, in any order relative to the collectives they submit to the daemon. */
+typedef enum {
+  dfcclFusedAllGatherGemm = 1,     /* out[M, n] = all_gather(x_shard)[M, k] * w[n, k]^T,        M = rowsPerRank * nranks */
+  dfcclFusedGemmReduceScatter = 2  /* out[rowsPerRank, n] = my rows of sum over ranks of x[M, k] * w[n, k]^T */
+} dfcclFusedKind_t;
+typedef struct {
+  int kind;          /* dfcclFusedKind_t */
+  int rowsPerRank;   /* rows of the sharded operand / result each rank owns (a multiple of 128) */
+  int k;             /* contraction length on this rank (a multiple of 64) */
+  int n;             /* output columns on this rank (a multiple of 256) */
+} dfcclFusedInfo;
+ncclResult_t dfcclPrepareFusedGemm(const dfcclFusedInfo* info, ncclComm_t comm, int collId, ofcclRankCtx_t rankCtx);
+/* After finalize, all-gather -> GEMM only: *shard = where this rank's [rowsPerRank, k] rows go (writing the input there
+ * saves the copy), *gathered = the [M, k] operand, complete after a call (the weight gradient needs it). */
+ncclResult_t dfcclFusedGemmOperand(int collId, ofcclRankCtx_t rankCtx, void** shard, void** gathered);
+/* bf16 operands; x: [rowsPerRank, k] (all-gather -> GEMM) or [M, k] (GEMM -> reduce-scatter); w: [n, k]. */
+ncclResult_t dfcclRunFusedGemm(int collId, const void* x, const void* w, void* out, cudaStream_t stream, ofcclRankCtx_t rankCtx);
+/* The same with the weight handed over transposed, wT: [k, n] (a backward pass runs the operators on W^T and passes W as
+ * it is stored; no copy is made). */
+ncclResult_t dfcclRunFusedGemmT(int collId, const void* x, const void* wT, void* out, cudaStream_t stream, ofcclRankCtx_t rankCtx);
+
 /* By default dfcclStreamWait (outside a stream capture) launches an instance of the daemon before the wait and
  * keeps it resident until nothing is outstanding, so that a stream parked on a completion never depends on a
  * relaunch from a host thread - the safe choice for eager steps of thousands of launches, at the price of the
@@ -281,6 +307,7 @@ typedef struct {
   uint64_t dataYields;                            /* data phases left at a slice boundary for other queued work */
   uint64_t schedulerPasses;                       /* passes of the per-block scheduler loop, summed over blocks */
   uint64_t nsTriggers, nsWalk, nsQueues;          /* time of those passes by part: trigger list, task-queue walk, queue upkeep */
+  uint64_t fusedLaunches;                         /* registered fused GEMM + collective operators launched */
 } dfcclStats;
 ncclResult_t dfcclGetStats(ofcclRankCtx_t rankCtx, dfcclStats* stats);
 /* Host-memory counters only (submissions, completions, launches, quits; deviceEvents = daemon believed alive):

@@ -14,6 +14,10 @@ extern "C" {
  * C[M,N] (bf16, row-major) = A[M,K] * B[N,K]^T with fp32 accumulation.  M % 128 == 0, N % 256 == 0, K % 64 == 0,
  * pointers 16-byte aligned. */
 ncclResult_t dfcclGemmBf16(const void* A, const void* B, void* C, int M, int N, int K, cudaStream_t stream);
+/* The same with either operand stored transposed (contraction index slow): A as [K, M] when aTransposed, B as [K, N] when
+ * bTransposed, row-major.  No copy is made: the kernel describes such an operand to the tensor cores as MN-major. */
+ncclResult_t dfcclGemmBf16Ex(const void* A, const void* B, void* C, int M, int N, int K, int aTransposed, int bTransposed,
+                             cudaStream_t stream);
 
 /* The same kernel with a collective inside (driven by dfccl_b200/ops/fused_linear.py, which owns the symmetric
  * buffers and rendezvous words): `fusedArgs` is the argument block of csrc/src/gemm/tcgen05_gemm.cu (its size is

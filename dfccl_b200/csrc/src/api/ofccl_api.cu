@@ -6,6 +6,7 @@
 #include "../device/engine.h"
 #include "../device/launch.h"
 #include "../topo/topo.h"
+#include "../gemm/gemm.h"
 #include <algorithm>
 #include <chrono>
 #include <cstring>
@@ -360,6 +361,48 @@ DF_API ncclResult_t dfcclPrepare(const dfcclCollInfo* info, ncclComm_t comm, int
   return ncclSuccess;
 }
 
+// ---- fused tensor-parallel operators: one zeroed heap block per member, laid out alike on all of them
+struct FusedLayout { uint64_t arrive, done, doneCount, epochCounter, flags, big, bytes; };
+static FusedLayout fusedLayout(const dfcclFusedInfo& f, int n) {
+  FusedLayout L{};
+  L.arrive = 0; L.done = 8ull * n; L.doneCount = 16ull * n; L.epochCounter = 16ull * n + 8;
+  L.flags = (16ull * n + 16 + 63) & ~63ull;
+  const uint64_t m = (uint64_t)f.rowsPerRank * n;
+  // all-gather -> GEMM: one counter per 128-row block of the gathered operand, then the operand itself [M, k];
+  // GEMM -> reduce-scatter: one flag per (source rank, tile of my rows), then the receive areas [n][rowsPerRank, N]
+  const uint64_t nFlags = f.kind == dfcclFusedAllGatherGemm ? m / GEMM_BM : (uint64_t)n * (f.rowsPerRank / GEMM_BM) * (f.n / GEMM_BN);
+  L.big = (L.flags + 4 * nFlags + 1023) & ~1023ull;
+  L.bytes = L.big + (f.kind == dfcclFusedAllGatherGemm ? m * f.k * 2 : (uint64_t)n * f.rowsPerRank * f.n * 2);
+  return L;
+}
+
+DF_API ncclResult_t dfcclPrepareFusedGemm(const dfcclFusedInfo* info, ncclComm_t comm, int collId, ofcclRankCtx_t ctx) {
+  if (!ctx || !info || !comm) return ncclInvalidArgument;
+  if (info->kind != dfcclFusedAllGatherGemm && info->kind != dfcclFusedGemmReduceScatter) { DF_WARN("unknown fused operator kind %d", info->kind); return ncclInvalidArgument; }
+  if (info->rowsPerRank <= 0 || info->k <= 0 || info->n <= 0 || info->rowsPerRank % GEMM_BM || info->k % GEMM_BK || info->n % GEMM_BN) {
+    DF_WARN("fused operator %d: rows per rank, k and n must be positive multiples of %d, %d and %d (got %d, %d, %d)", collId, GEMM_BM, GEMM_BK, GEMM_BN, info->rowsPerRank, info->k, info->n);
+    return ncclInvalidArgument;
+  }
+  if (comm->nranks > 8) { DF_WARN("fused operators serve communicators of up to 8 ranks"); return ncclInvalidArgument; }
+  if (comm->netMode) { DF_WARN("fused operators need peer memory: not available on communicators that go through the network path"); return ncclInvalidUsage; }
+  std::lock_guard<std::mutex> l(ctx->mu);
+  if (ctx->finalized) { DF_WARN("operator %d registered after the context was finalized", collId); return ncclInvalidUsage; }
+  if (collId < 0 || collId >= DF_MAX_COLLS) return ncclInvalidArgument;
+  if (ctx->colls.count(collId)) { DF_WARN("collective id %d registered twice", collId); return ncclInvalidUsage; }
+  if (!ctx->colls.empty() && ctx->colls.begin()->second.comm->backend != comm->backend) return ncclInvalidUsage;
+  if (!ctx->colls.empty() && ctx->colls.begin()->second.comm->device != comm->device) return ncclInvalidUsage;
+  CollEntry e;
+  e.comm = comm;
+  e.fused = *info;
+  memset(&e.cs, 0, sizeof(e.cs));
+  // the registration check at finalize compares these fields across the members
+  e.cs.kind = 100 + info->kind; e.cs.count = (uint64_t)info->rowsPerRank; e.cs.inType = info->k; e.cs.outType = info->n;
+  e.cs.nranks = comm->nranks; e.cs.rank = comm->rank;
+  ctx->colls[collId] = e;
+  ctx->maxCollId = std::max(ctx->maxCollId, collId);
+  return ncclSuccess;
+}
+
 struct FinalizeMsg { int32_t collId, nBlocks, algo, kind, inType, outType, pad0, pad1; uint64_t count, flagsOff, pushOff; };
 
 DF_API ncclResult_t ofcclFinalizeRankCtx7StartHostThrds(ofcclRankCtx_t ctx) {
@@ -383,6 +426,12 @@ DF_API ncclResult_t ofcclFinalizeRankCtx7StartHostThrds(ofcclRankCtx_t ctx) {
   for (auto& kv : ctx->colls) {
     CollEntry& e = kv.second;
     if (e.comm->netMode) continue;               // runs on the host over its own ring (created in step 2)
+    if (e.fused.kind) {                          // rendezvous words, counters and receive areas of a fused operator
+      e.fusedBytes = fusedLayout(e.fused, e.comm->nranks).bytes;
+      DFCHECK(e.comm->heap->alloc(e.fusedBytes, &e.fusedOff, true));
+      e.flagsOff = e.fusedOff;
+      continue;
+    }
     const size_t bytes = e.info.count * (size_t)dtypeSize(e.info.inType);
     bool nv = nvlsEligible(e.comm, e.cs.kind, e.cs.inType, e.cs.outType, e.cs.op, e.cs.postDiv, e.cs.count);
     TunerChoice ch = tunerChoose(*topo, e.info.kind, bytes, e.comm->nranks, ctx->nBlocks, nv, e.info.algo, e.info.nBlocks);
@@ -462,10 +511,13 @@ DF_API ncclResult_t ofcclFinalizeRankCtx7StartHostThrds(ofcclRankCtx_t ctx) {
         e.cs.peerHeap[j] = comm->peerHeap[j];
         e.cs.peerFlags[j] = (FlagSlot*)(comm->peerHeap[j] + m.flagsOff);
         e.cs.peerPush[j] = e.pushBytes ? comm->peerHeap[j] + m.pushOff : nullptr;
+        e.peerFusedOff[j] = m.flagsOff;
       }
-      e.cs.valid = 1;
+      e.cs.valid = e.fused.kind ? 0 : 1;         // fused operators are stream kernels: the daemon never sees their ids
     }
   }
+  if (be == dfcclBackendCuda)
+    for (auto& kv : ctx->colls) if (kv.second.fused.kind) { gemmReserveSmsAtLeast(ctx->nBlocks); break; }   // all CTAs of a fused launch must be resident beside the daemon
   // 3. queues and device tables
   const uint32_t maxColls = (uint32_t)ctx->maxCollId + 1;
   ctx->byId.assign(maxColls, nullptr);
@@ -625,6 +677,7 @@ static ncclResult_t submit(ofcclRankCtx* ctx, const void* send, void* recv, int 
     CollEntry* ep = collId >= 0 && collId < (int)ctx->byId.size() ? ctx->byId[collId] : nullptr;
     if (!ep) { DF_WARN("collective %d was never prepared", collId); return ncclInvalidArgument; }
     CollEntry& e = *ep;
+    if (e.fused.kind) { DF_WARN("id %d is a fused operator: run it with dfcclRunFusedGemm", collId); return ncclInvalidUsage; }
     if (e.submitted != e.completed) {
       if (!onStream) { DF_WARN("collective %d submitted again before its callback ran", collId); return ncclInvalidUsage; }
       // Stream-ordered callers enqueue ahead of the GPU: the previous submission of this id is
@@ -784,7 +837,7 @@ DF_API ncclResult_t dfcclRunDeferred(const void* s, void* r, int collId, Callbac
 DF_API ncclResult_t dfcclTriggerOnStream(int collId, cudaStream_t stream, ofcclRankCtx_t ctx) {
   if (!ctx || !ctx->finalized || ctx->destroyed) return ncclInvalidUsage;
   if (collId < 0 || collId >= (int)ctx->byId.size() || !ctx->byId[collId]) return ncclInvalidArgument;
-  if (ctx->byId[collId]->comm->netMode) return ncclInvalidUsage;
+  if (ctx->byId[collId]->comm->netMode || ctx->byId[collId]->fused.kind) return ncclInvalidUsage;
   volatile uint64_t* word = ctx->rdHost.trigger + collId;
   if (ctx->backend == dfcclBackendCuda) {
     dfcclBumpWordKernel<<<1, 1, 0, stream>>>(word, ctx->hostTrig + collId);
@@ -903,6 +956,8 @@ DF_API ncclResult_t dfcclAbort(ofcclRankCtx_t ctx) {
 }
 DF_API ncclResult_t dfcclGetAsyncError(ofcclRankCtx_t ctx, ncclResult_t* e) {
   if (!ctx || !e) return ncclInvalidArgument;
+  // a bounded wait that ran out inside a registered fused operator left its verdict in pinned memory
+  if (ctx->asyncError == ncclSuccess && ctx->backend == dfcclBackendCuda && ctx->fusedLaunches.load() && gemmGaveUp()) ctx->asyncError = dfcclTimeout;
   *e = ctx->asyncError;
   return ncclSuccess;
 }
@@ -922,6 +977,7 @@ DF_API ncclResult_t dfcclGetStats(ofcclRankCtx_t ctx, dfcclStats* s) {
   if (!ctx || !s) return ncclInvalidArgument;
   memset(s, 0, sizeof(*s));
   s->sqesSubmitted = ctx->sqes; s->cqesDelivered = ctx->cqes; s->callbacksRun = ctx->cbs; s->sqFullRetries = ctx->sqFull;
+  s->fusedLaunches = ctx->fusedLaunches;
   if (!ctx->finalized) return ncclSuccess;
   s->daemonLaunches = ctx->ctl->launches; s->daemonVoluntaryQuits = ctx->ctl->voluntaryQuits;
   std::vector<DevStats> d(ctx->nBlocks);
@@ -998,6 +1054,7 @@ static void releaseHeapParts(ofcclRankCtx* ctx) {
     CollEntry& e = kv.second;
     e.ring.reset();
     if (e.flagsBytes) e.comm->heap->free(e.flagsOff);
+    if (e.fusedBytes) e.comm->heap->free(e.fusedOff);
     if (e.pushBytes) e.comm->heap->free(e.pushOff);
     for (int k = 0; k < 2; ++k) if (e.stagingBytes[k]) e.comm->heap->free(e.stagingOff[k]);
     e.comm = nullptr;
@@ -1067,6 +1124,118 @@ DF_API ncclResult_t ofcclDestroy(ofcclRankCtx_t ctx) {
   }
   if (be == dfcclBackendCuda) cudaSetDevice(prev);
   return ncclSuccess;
+}
+
+// ------------------------------------------------------------------ registered fused operators
+
+static CollEntry* fusedEntry(ofcclRankCtx* ctx, int collId) {
+  if (!ctx || !ctx->finalized || ctx->destroyed || collId < 0 || collId >= (int)ctx->byId.size()) return nullptr;
+  CollEntry* e = ctx->byId[collId];
+  return e && e->fused.kind ? e : nullptr;
+}
+
+DF_API ncclResult_t dfcclFusedGemmOperand(int collId, ofcclRankCtx_t ctx, void** shard, void** gathered) {
+  CollEntry* e = fusedEntry(ctx, collId);
+  if (!e || e->fused.kind != dfcclFusedAllGatherGemm) return ncclInvalidArgument;
+  const FusedLayout L = fusedLayout(e->fused, e->comm->nranks);
+  char* g = e->comm->heap->base() + e->fusedOff + L.big;
+  if (gathered) *gathered = g;
+  if (shard) *shard = g + (size_t)e->comm->rank * e->fused.rowsPerRank * e->fused.k * 2;
+  return ncclSuccess;
+}
+
+// Host backend: the operator's arithmetic with the library's own collectives around a plain loop nest, rounding where
+// the kernel rounds (bf16 operands, fp32 accumulation, partial tiles of the reduce-scatter stored as bf16).
+static float bf16ToF(uint16_t b) { uint32_t u = (uint32_t)b << 16; float f; memcpy(&f, &u, 4); return f; }
+static uint16_t fToBf16(float f) { uint32_t u; memcpy(&u, &f, 4); u += 0x7fffu + ((u >> 16) & 1u); return (uint16_t)(u >> 16); }
+static void hostGemmNt(const uint16_t* a, const uint16_t* b, uint16_t* c, int M, int N, int K) {
+  for (int i = 0; i < M; ++i)
+    for (int j = 0; j < N; ++j) {
+      float acc = 0.f;
+      for (int k = 0; k < K; ++k) acc += bf16ToF(a[(size_t)i * K + k]) * bf16ToF(b[(size_t)j * K + k]);
+      c[(size_t)i * N + j] = fToBf16(acc);
+    }
+}
+
+static ncclResult_t runFused(int collId, const void* x, const void* w, void* out, int wT, cudaStream_t stream, ofcclRankCtx_t ctx);
+DF_API ncclResult_t dfcclRunFusedGemm(int collId, const void* x, const void* w, void* out, cudaStream_t stream, ofcclRankCtx_t ctx) {
+  return runFused(collId, x, w, out, 0, stream, ctx);
+}
+// The same with the weight stored transposed, [k, n] row-major: the backward pass runs these operators on W^T and hands
+// over W as it is stored (the tensor cores read it as an MN-major operand, no transposed copy).
+DF_API ncclResult_t dfcclRunFusedGemmT(int collId, const void* x, const void* wT, void* out, cudaStream_t stream, ofcclRankCtx_t ctx) {
+  return runFused(collId, x, wT, out, 1, stream, ctx);
+}
+
+static void hostTranspose(const uint16_t* src, uint16_t* dst, int rows, int cols) {        // dst[cols, rows] = src[rows, cols]^T
+  for (int i = 0; i < rows; ++i) for (int j = 0; j < cols; ++j) dst[(size_t)j * rows + i] = src[(size_t)i * cols + j];
+}
+
+static ncclResult_t runFused(int collId, const void* x, const void* w, void* out, int wT, cudaStream_t stream, ofcclRankCtx_t ctx) {
+  CollEntry* e = fusedEntry(ctx, collId);
+  if (!e) { DF_WARN("id %d is not a registered fused operator of a finalized context", collId); return ncclInvalidArgument; }
+  if (!x || !w || !out) return ncclInvalidArgument;
+  if (ctl_load(&ctx->ctl->abortFlag)) return dfcclAborted;
+  NvtxRange range(e->fused.kind == dfcclFusedAllGatherGemm ? "dfccl:AllGatherGemm" : "dfccl:GemmReduceScatter");
+  ncclComm* comm = e->comm;
+  const int n = comm->nranks, me = comm->rank, rows = e->fused.rowsPerRank, K = e->fused.k, N = e->fused.n, M = rows * n;
+  const FusedLayout L = fusedLayout(e->fused, n);
+  char* mine = comm->heap->base() + e->fusedOff;
+  ctx->fusedLaunches++;
+  if (ctx->backend != dfcclBackendCuda) {
+    std::vector<uint16_t> wn;
+    if (wT) { wn.resize((size_t)N * K); hostTranspose((const uint16_t*)w, wn.data(), K, N); w = wn.data(); }
+    if (e->fused.kind == dfcclFusedAllGatherGemm) {
+      DFCHECK(commCollective(comm, dfcclCollAllGather, x, mine + L.big, (size_t)rows * K, ncclBfloat16, ncclSum, 0, stream));
+      hostGemmNt((const uint16_t*)(mine + L.big), (const uint16_t*)w, (uint16_t*)out, M, N, K);
+    } else {
+      std::vector<uint16_t> partial((size_t)M * N);
+      hostGemmNt((const uint16_t*)x, (const uint16_t*)w, partial.data(), M, N, K);
+      DFCHECK(commCollective(comm, dfcclCollReduceScatter, partial.data(), out, (size_t)rows * N, ncclBfloat16, ncclSum, 0, stream));
+    }
+    return ncclSuccess;
+  }
+  if (gemmGaveUp()) { ctx->asyncError = dfcclTimeout; DF_WARN("an earlier fused operator on this device gave up on a bounded wait"); return dfcclTimeout; }
+  int prev = 0;
+  cudaGetDevice(&prev);
+  if (prev != comm->device) cudaSetDevice(comm->device);
+  ncclResult_t res = ncclSuccess;
+  FusedArgs f;
+  memset(&f, 0, sizeof(f));
+  f.nranks = n; f.rank = me; f.rowsPerRank = rows;
+  f.arrive = (volatile uint64_t*)(mine + L.arrive); f.done = (volatile uint64_t*)(mine + L.done);
+  f.doneCount = (uint32_t*)(mine + L.doneCount); f.epochCounter = (uint64_t*)(mine + L.epochCounter);
+  for (int j = 0; j < n; ++j) {
+    char* theirs = comm->peerHeap[j] + e->peerFusedOff[j];
+    f.peerArrive[j] = (volatile uint64_t*)(theirs + L.arrive) + me;
+    f.peerDone[j] = (volatile uint64_t*)(theirs + L.done) + me;
+  }
+  if (e->fused.kind == dfcclFusedAllGatherGemm) {
+    char* gathered = mine + L.big;
+    char* shard = gathered + (size_t)me * rows * K * 2;
+    if ((const char*)x != shard) {
+      cudaError_t ce = cudaMemcpyAsync(shard, x, (size_t)rows * K * 2, cudaMemcpyDeviceToDevice, stream);
+      if (ce != cudaSuccess) { DF_WARN("fused operator %d: copy of the input rows failed: %s", collId, cudaGetErrorString(ce)); res = ncclUnhandledCudaError; }
+    }
+    f.mode = 1;
+    f.gathered = (__nv_bfloat16*)gathered; f.blockReady = (uint32_t*)(mine + L.flags);
+    for (int j = 0; j < n; ++j) f.peerA[j] = (const __nv_bfloat16*)(comm->peerHeap[j] + e->peerFusedOff[j] + L.big + (size_t)j * rows * K * 2);
+    if (res == ncclSuccess) res = gemmLaunch(gathered, w, out, M, N, K, n == 1 ? nullptr : &f, stream, 0, wT);
+  } else {
+    f.mode = 2;
+    const uint64_t tiles = (uint64_t)(rows / GEMM_BM) * (N / GEMM_BN);
+    f.mySlots = (const __nv_bfloat16*)(mine + L.big); f.myTileFlags = (const uint32_t*)(mine + L.flags);
+    f.reduced = (__nv_bfloat16*)out;
+    for (int j = 0; j < n; ++j) {
+      char* theirs = comm->peerHeap[j] + e->peerFusedOff[j];
+      f.slot[j] = (__nv_bfloat16*)(theirs + L.big + (size_t)me * rows * N * 2);       // my partial tiles at owner j
+      f.tileFlag[j] = (uint32_t*)(theirs + L.flags);
+    }
+    (void)tiles;
+    res = gemmLaunch(x, w, out, M, N, K, n == 1 ? nullptr : &f, stream, 0, wT);
+  }
+  if (prev != comm->device) cudaSetDevice(prev);
+  return res;
 }
 
 // ------------------------------------------------------------------ per-collective wrappers

@@ -39,6 +39,11 @@ struct CollEntry {
   uint64_t triggerSeq = 0;
   uint32_t lastStatus = 0;
   std::shared_ptr<NetRing> ring;             // network-mode communicators: this collective's own ring of connections
+  // fused tensor-parallel operator (dfcclPrepareFusedGemm): one heap block per member holds its rendezvous words,
+  // counters and receive areas; the daemon never sees these ids
+  dfcclFusedInfo fused{};                    // kind == 0: an ordinary collective
+  uint64_t fusedOff = 0, fusedBytes = 0;
+  uint64_t peerFusedOff[DF_MAX_RANKS] = {};
 };
 
 // Workers of the network path.  Every submission in flight needs a thread of its own (two ranks may submit the
@@ -112,7 +117,7 @@ struct ofcclRankCtx {
   std::atomic<bool> stopPoller{false};
   int64_t checkInterval = 10000;      // CHECK_REMAINING_SQE_INTERVAL
   // stats / faults
-  std::atomic<uint64_t> sqes{0}, cqes{0}, cbs{0}, sqFull{0};
+  std::atomic<uint64_t> sqes{0}, cqes{0}, cbs{0}, sqFull{0}, fusedLaunches{0};
   int64_t faultDrop = 0, faultDelayUs = 0, faultFreezeMs = 0;
   ncclResult_t asyncError = ncclSuccess;
   // stream memory operations (cuda backend)

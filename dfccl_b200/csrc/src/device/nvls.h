@@ -70,7 +70,7 @@ template <typename Tin, typename Tout>
 DF_HD void nvlsSlice(char* mc, char* const* peers, int n, uint64_t inOff, uint64_t outOff, uint64_t nElems, float scale) {
   constexpr int V = 16 / (int)sizeof(Tin);                 // elements per input pack
   constexpr int W = (int)(sizeof(Tout) / sizeof(Tin));     // output packs per input pack (1 or 2)
-  constexpr int U = 4;
+  constexpr int U = 8;                                     // reductions in flight per thread: a round trip through the switch is long
   const uint64_t packs = nElems / V;
   const bool plain = scale == 1.0f && W == 1;
   for (uint64_t p0 = (uint64_t)df_tid() ; p0 < packs; p0 += (uint64_t)df_nthreads() * U) {
@@ -104,25 +104,49 @@ template <typename Tin, typename Tout>
 DF_HD void nvlsSliceToLocal(char* mc, char* const* peers, int n, uint64_t inOff, char* dst, uint64_t nElems, float scale) {
   constexpr int V = 16 / (int)sizeof(Tin);
   constexpr int W = (int)(sizeof(Tout) / sizeof(Tin));
+  constexpr int U = 8;
   const uint64_t packs = nElems / V;
   const bool plain = scale == 1.0f && W == 1;
-  for (uint64_t p = (uint64_t)df_tid(); p < packs; p += (uint64_t)df_nthreads()) {
-    const uint4 v = nvlsLoad<Tin>(mc, peers, n, inOff + p * 16);
-    if (plain) { st16(dst + p * 16, v); continue; }
-    uint4 o[W];
+  for (uint64_t p0 = (uint64_t)df_tid(); p0 < packs; p0 += (uint64_t)df_nthreads() * U) {
+    uint4 v[U];
 #pragma unroll
-    for (int w = 0; w < W; ++w) o[w] = make_uint4(0, 0, 0, 0);
+    for (int u = 0; u < U; ++u) {
+      const uint64_t p = p0 + (uint64_t)u * df_nthreads();
+      if (p < packs) v[u] = nvlsLoad<Tin>(mc, peers, n, inOff + p * 16);
+    }
 #pragma unroll
-    for (int k = 0; k < V; ++k) Lane<Tout>::put(o[k / (V / W)], k % (V / W), (float)Lane<Tin>::get(v, k) * scale);
+    for (int u = 0; u < U; ++u) {
+      const uint64_t p = p0 + (uint64_t)u * df_nthreads();
+      if (p >= packs) continue;
+      if (plain) { st16(dst + p * 16, v[u]); continue; }
+      uint4 o[W];
 #pragma unroll
-    for (int w = 0; w < W; ++w) st16(dst + (p * W + w) * 16, o[w]);
+      for (int w = 0; w < W; ++w) o[w] = make_uint4(0, 0, 0, 0);
+#pragma unroll
+      for (int k = 0; k < V; ++k) Lane<Tout>::put(o[k / (V / W)], k % (V / W), (float)Lane<Tin>::get(v[u], k) * scale);
+#pragma unroll
+      for (int w = 0; w < W; ++w) st16(dst + (p * W + w) * 16, o[w]);
+    }
   }
 }
 
 // All-gather form: `bytes` (a multiple of 16) from local `src` to offset `outOff` of every member's arena.
 DF_HD void nvlsBroadcastBytes(char* mc, char* const* peers, int n, const char* src, uint64_t outOff, uint64_t bytes) {
+  constexpr int U = 8;
   const uint64_t packs = bytes / 16;
-  for (uint64_t p = (uint64_t)df_tid(); p < packs; p += (uint64_t)df_nthreads()) nvlsStore(mc, peers, n, outOff + p * 16, ld16(src + p * 16));
+  for (uint64_t p0 = (uint64_t)df_tid(); p0 < packs; p0 += (uint64_t)df_nthreads() * U) {
+    uint4 v[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const uint64_t p = p0 + (uint64_t)u * df_nthreads();
+      if (p < packs) v[u] = ld16(src + p * 16);
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const uint64_t p = p0 + (uint64_t)u * df_nthreads();
+      if (p < packs) nvlsStore(mc, peers, n, outOff + p * 16, v[u]);
+    }
+  }
 }
 
 // Which (input, output) pairs the schedule exists for.

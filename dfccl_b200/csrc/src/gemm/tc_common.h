@@ -102,10 +102,23 @@ __device__ __forceinline__ uint64_t umma_smem_desc_sw128(const void* smem) {
          | ((uint64_t)1 << 46)              // descriptor version of sm_100                    bits [46,48)
          | ((uint64_t)2 << 61);             // layout: 128-byte swizzle                        bits [61,64)
 }
-// Instruction descriptor: bf16 x bf16 -> fp32, both operands K-major, dense.
-__host__ __device__ constexpr uint32_t umma_idesc_bf16(int m, int n) {
+// Shared-memory operand, MN-major (the contraction index is the slow one: the operand is stored transposed),
+// 128-byte swizzle.  The tile is a row of blocks of 64 MN-elements; a block is [K rows] x 128 bytes, exactly what a
+// TMA tile load of 64 columns x K rows with CU_TENSOR_MAP_SWIZZLE_128B produces.  Groups of 8 K-rows are 1024 bytes
+// apart (stride byte offset), the blocks `blockBytes` apart (leading byte offset).
+__device__ __forceinline__ uint64_t umma_smem_desc_mn_sw128(const void* smem, uint32_t blockBytes) {
+  const uint64_t addr = (uint64_t)(smem_u32(smem) & 0x3FFFFu) >> 4;
+  return addr
+         | ((uint64_t)(blockBytes >> 4) << 16)   // leading byte offset: next block of 64 MN-elements
+         | ((uint64_t)(1024 >> 4) << 32)         // stride byte offset: next group of 8 K-rows
+         | ((uint64_t)1 << 46)
+         | ((uint64_t)2 << 61);
+}
+// Instruction descriptor: bf16 x bf16 -> fp32, dense; each operand K-major (0) or MN-major (1).
+__host__ __device__ constexpr uint32_t umma_idesc_bf16(int m, int n, int aMnMajor = 0, int bMnMajor = 0) {
   return (1u << 4)                          // accumulator format: fp32
          | (1u << 7) | (1u << 10)           // A and B format: bf16
+         | ((uint32_t)(aMnMajor & 1) << 15) | ((uint32_t)(bMnMajor & 1) << 16)
          | ((uint32_t)(n >> 3) << 17)       // N / 8
          | ((uint32_t)(m >> 4) << 24);      // M / 16
 }

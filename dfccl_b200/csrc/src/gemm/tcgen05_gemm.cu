@@ -16,6 +16,7 @@
 // filled by TMA (no cluster multicast anywhere), full/empty mbarriers, tcgen05.commit to release
 // stages and to hand accumulators over.  Every wait is bounded and ends in an error word.
 #include "tc_common.h"
+#include "gemm.h"
 #include "../common/param.h"
 #include "dfccl.h"
 #include "../common/log.h"
@@ -32,6 +33,8 @@ using namespace tc;
 
 constexpr int BM = 128, BN = 256, BK = 64, STAGES = 4, UMMA_K = 16;
 constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int MN_BLOCK_BYTES = 64 * BK * 2;          // MN-major operand: one block of 64 MN-columns x BK K-rows
+static_assert(BM == GEMM_BM && BN == GEMM_BN && BK == GEMM_BK, "tile constants of gemm.h");
 constexpr int TMEM_COLS = 512;                       // two accumulators of BN fp32 columns
 constexpr int NUM_THREADS = 320;                     // 10 warps
 constexpr int GATHER_PIECES = 8;                     // pieces a 128-row block is pulled in (all-gather -> GEMM)
@@ -39,34 +42,10 @@ constexpr int EPI_ROW_BYTES = 64 * 2 + 16;            // one staged row: 64 bf16
 constexpr int EPI_WARP_BYTES = 32 * EPI_ROW_BYTES;   // 32 rows per epilogue warp
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 4 * EPI_WARP_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
 
-struct FusedArgs {
-  // ---- all-gather -> GEMM
-  int nranks, rank;                 // nranks <= 1: plain GEMM
-  int rowsPerRank;                  // rows of A each rank contributes (multiple of BM)
-  const __nv_bfloat16* peerA[8];    // each rank's shard [rowsPerRank, K] as mapped here (own entry unused)
-  __nv_bfloat16* gathered;          // local [M, K] buffer the tensor map of A covers
-  uint32_t* blockReady;             // [M / BM] local counters: a block is in place when it reaches epoch * GATHER_PIECES
-  // ---- GEMM -> reduce-scatter
-  __nv_bfloat16* slot[8];           // owner j's receive area for MY partial tiles: [rowsPerRank, N] bf16, as mapped here
-  uint32_t* tileFlag[8];            // owner j's flags [nranks][tilesPerOwner] as mapped here (I write row `rank`)
-  const __nv_bfloat16* mySlots;     // my receive areas: [nranks][rowsPerRank, N]
-  const uint32_t* myTileFlags;      // my flags [nranks][tilesPerOwner]
-  __nv_bfloat16* reduced;           // my output [rowsPerRank, N]
-  // ---- rendezvous words (symmetric heap), written by peers
-  volatile uint64_t* arrive;        // [nranks] local: peer j posted epoch -> its buffers are ready
-  volatile uint64_t* done;          // [nranks] local: peer j posted epoch -> it no longer reads my buffers
-  volatile uint64_t* peerArrive[8]; // where I post for peer j (its arrive[rank])
-  volatile uint64_t* peerDone[8];
-  uint32_t* doneCount;              // local counter of CTAs that finished their communication work
-  uint64_t epoch;                   // this call's number (used when epochCounter is null)
-  uint64_t* epochCounter;           // local device word: calls finished so far; this call is that + 1.  Kept on the device
-                                    // so that a launch captured in a CUDA graph finds the right number at every replay.
-  int mode;                         // 0 plain, 1 all-gather -> GEMM, 2 GEMM -> reduce-scatter
-};
-
 struct GemmArgs {
   __nv_bfloat16* C;
   int M, N, K, ldc;
+  int aMn, bMn;                     // operand stored with the contraction index slow: A as [K, M], B as [K, N] (row-major)
   uint32_t* err;                    // device word: non-zero = a bounded wait ran out (later launches return at once)
   uint64_t waitNs;                  // limit of every wait on a word another GPU or CTA writes
   uint32_t* errHost;                // the same verdict in pinned host memory, read by the host without a synchronisation
@@ -207,8 +186,12 @@ dfcclGemmKernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
           if (!mbar_wait(&emptyBar[stage], phase ^ 1, giveUp)) { ok = false; break; }
           mbar_expect_tx(&fullBar[stage], STAGE_BYTES);
           uint8_t* sa = smem + stage * STAGE_BYTES;
-          tma_load_2d(sa, &mapA, kb * BK, mt * BM, &fullBar[stage]);
-          tma_load_2d(sa + A_BYTES, &mapB, kb * BK, nt * BN, &fullBar[stage]);
+          // K-major operand: one box of [tile rows] x 64 K-columns.  MN-major operand: the tile is a row of blocks
+          // of 64 MN-columns x 64 K-rows (8 KB each), one box per block.
+          if (!g.aMn) tma_load_2d(sa, &mapA, kb * BK, mt * BM, &fullBar[stage]);
+          else for (int i = 0; i < BM / 64; ++i) tma_load_2d(sa + i * MN_BLOCK_BYTES, &mapA, mt * BM + 64 * i, kb * BK, &fullBar[stage]);
+          if (!g.bMn) tma_load_2d(sa + A_BYTES, &mapB, kb * BK, nt * BN, &fullBar[stage]);
+          else for (int i = 0; i < BN / 64; ++i) tma_load_2d(sa + A_BYTES + i * MN_BLOCK_BYTES, &mapB, nt * BN + 64 * i, kb * BK, &fullBar[stage]);
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
       }
@@ -220,7 +203,10 @@ dfcclGemmKernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
     if (elect_one()) {
-      constexpr uint32_t idesc = umma_idesc_bf16(BM, BN);
+      const uint32_t idesc = umma_idesc_bf16(BM, BN, g.aMn, g.bMn);
+      // one instruction consumes 16 K-elements: 32 bytes along a K-major row (+2 in the 16-byte address field), two
+      // groups of 8 K-rows of an MN-major block (2048 bytes, +128)
+      const uint32_t stepA = g.aMn ? 128u : 2u, stepB = g.bMn ? 128u : 2u;
       int stage = 0;
       uint32_t phase = 0;
       int it = 0;
@@ -233,11 +219,12 @@ dfcclGemmKernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
         for (int kb = 0; kb < kBlocks; ++kb) {
           if (!mbar_wait(&fullBar[stage], phase, giveUp)) { ok = false; break; }
           tc_fence_after();
-          const uint64_t da = umma_smem_desc_sw128(smem + stage * STAGE_BYTES);
-          const uint64_t db = umma_smem_desc_sw128(smem + stage * STAGE_BYTES + A_BYTES);
+          const uint8_t* pa = smem + stage * STAGE_BYTES;
+          const uint64_t da = g.aMn ? umma_smem_desc_mn_sw128(pa, MN_BLOCK_BYTES) : umma_smem_desc_sw128(pa);
+          const uint64_t db = g.bMn ? umma_smem_desc_mn_sw128(pa + A_BYTES, MN_BLOCK_BYTES) : umma_smem_desc_sw128(pa + A_BYTES);
 #pragma unroll
-          for (int k = 0; k < BK / UMMA_K; ++k)       // +32 bytes of K per step: +2 in the 16-byte address field
-            umma_bf16(d, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0);
+          for (int k = 0; k < BK / UMMA_K; ++k)
+            umma_bf16(d, da + stepA * k, db + stepB * k, idesc, (kb | k) != 0);
           umma_commit(&emptyBar[stage]);              // the stage is free once these MMAs have read it
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
@@ -487,7 +474,8 @@ ErrWords errWords() {                       // one pair per device, created on f
   return w[dev];
 }
 
-ncclResult_t launch(const void* A, const void* B, void* C, int M, int N, int K, const FusedArgs* f, cudaStream_t stream) {
+ncclResult_t launch(const void* A, const void* B, void* C, int M, int N, int K, const FusedArgs* f, cudaStream_t stream,
+                    int aMn = 0, int bMn = 0) {
   if (M <= 0 || N <= 0 || K <= 0 || M % BM || N % BN || K % BK) {
     DF_WARN("tcgen05 GEMM needs M %% %d == 0, N %% %d == 0, K %% %d == 0 (got %d x %d x %d)", BM, BN, BK, M, N, K);
     return ncclInvalidArgument;
@@ -496,13 +484,15 @@ ncclResult_t launch(const void* A, const void* B, void* C, int M, int N, int K, 
   const ErrWords ew = errWords();
   if (*ew.host) { DF_WARN("an earlier tensor-core kernel on this device gave up on a bounded wait; call dfcclGemmCheck to clear"); return dfcclTimeout; }
   CUtensorMap ma, mb;
-  DFCHECK(makeMap(&ma, A, (uint64_t)M, (uint64_t)K, BM));
-  DFCHECK(makeMap(&mb, B, (uint64_t)N, (uint64_t)K, BN));
+  // K-major operand [rows, K]: boxes of [tile rows] x 64 K-columns; MN-major operand [K, cols]: boxes of 64 K-rows x 64 columns
+  if (!aMn) DFCHECK(makeMap(&ma, A, (uint64_t)M, (uint64_t)K, BM)); else DFCHECK(makeMap(&ma, A, (uint64_t)K, (uint64_t)M, BK));
+  if (!bMn) DFCHECK(makeMap(&mb, B, (uint64_t)N, (uint64_t)K, BN)); else DFCHECK(makeMap(&mb, B, (uint64_t)K, (uint64_t)N, BK));
   static std::once_flag once;
   std::call_once(once, [] { cudaFuncSetAttribute(dfcclGemmKernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES); });
   GemmArgs g;
   memset(&g, 0, sizeof(g));
   g.C = (__nv_bfloat16*)C; g.M = M; g.N = N; g.K = K; g.ldc = N; g.err = ew.dev; g.errHost = (uint32_t*)ew.host;
+  g.aMn = aMn ? 1 : 0; g.bMn = bMn ? 1 : 0;
   { int64_t ms = paramI64("WAIT_TIMEOUT_MS", 30000); g.waitNs = (uint64_t)(ms > 0 ? ms : 30000) * 1000000ull; }
   if (f) g.f = *f; else { g.f.nranks = 1; g.f.mode = 0; }
   int dev = 0, sms = 148;
@@ -520,6 +510,16 @@ ncclResult_t launch(const void* A, const void* B, void* C, int M, int N, int K, 
 }
 
 }  // namespace
+
+ncclResult_t gemmLaunch(const void* A, const void* B, void* C, int M, int N, int K, const FusedArgs* f, cudaStream_t stream, int aMn, int bMn) {
+  return launch(A, B, C, M, N, K, f, stream, aMn, bMn);
+}
+bool gemmGaveUp() { return *errWords().host != 0; }
+void gemmReserveSmsAtLeast(int n) {
+  int cur = g_reservedSms.load();
+  while (cur < n && !g_reservedSms.compare_exchange_weak(cur, n)) {}
+}
+
 }  // namespace dfccl
 
 using namespace dfccl;
@@ -528,6 +528,13 @@ using namespace dfccl;
 // C[M,N] (bf16, row-major) = A[M,K] * B[N,K]^T, fp32 accumulation in tensor memory.
 DF_API ncclResult_t dfcclGemmBf16(const void* A, const void* B, void* C, int M, int N, int K, cudaStream_t stream) {
   return launch(A, B, C, M, N, K, nullptr, stream);
+}
+
+// The same product with either operand stored transposed (the contraction index slow): A as [K, M] when `aTransposed`,
+// B as [K, N] when `bTransposed`, both row-major.  The weight gradient of a linear layer (both) and its data gradient
+// (B) then need no transposed copy: the tensor cores read MN-major operands as they are.
+DF_API ncclResult_t dfcclGemmBf16Ex(const void* A, const void* B, void* C, int M, int N, int K, int aTransposed, int bTransposed, cudaStream_t stream) {
+  return launch(A, B, C, M, N, K, nullptr, stream, aTransposed, bTransposed);
 }
 
 // SMs the fused launches leave free for a persistent kernel that runs beside them (e.g. the daemon's blocks).

@@ -38,12 +38,19 @@ class CollInfo(C.Structure):
                 ("op", C.c_int), ("root", C.c_int), ("scale", C.c_float), ("algo", C.c_int), ("nBlocks", C.c_int), ("flags", C.c_int)]
 
 
+class FusedInfo(C.Structure):
+    _fields_ = [("kind", C.c_int), ("rowsPerRank", C.c_int), ("k", C.c_int), ("n", C.c_int)]
+
+
+FUSED_ALLGATHER_GEMM, FUSED_GEMM_REDUCESCATTER = 1, 2
+
+
 class Stats(C.Structure):
     _fields_ = [(n, C.c_uint64) for n in (
         "sqesSubmitted", "cqesDelivered", "callbacksRun", "daemonLaunches", "daemonVoluntaryQuits",
         "ctxSwitches", "ctxSaves", "ctxLoads", "waitPolls", "waitTimeouts", "bytesReduced", "bytesCopied",
         "sqFullRetries", "maxSwitchNs", "totalSwitchNs", "deviceEvents", "dataYields", "schedulerPasses",
-        "nsTriggers", "nsWalk", "nsQueues")]
+        "nsTriggers", "nsWalk", "nsQueues", "fusedLaunches")]
 
     def as_dict(self) -> Dict[str, int]:
         return {n: int(getattr(self, n)) for n, _ in self._fields_}
@@ -105,6 +112,8 @@ def lib() -> C.CDLL:
             "ofcclRunAllReduce": [vp, vp, i, CALLBACK, vp, vp], "ofcclRunReduce": [vp, vp, i, CALLBACK, vp, vp],
             "ofcclRunReduceScatter": [vp, vp, i, CALLBACK, vp, vp], "ofcclRunAllGather": [vp, vp, i, CALLBACK, vp, vp],
             "ofcclRunBroadcast": [vp, vp, i, CALLBACK, vp, vp], "ofcclRunBcast": [vp, i, CALLBACK, vp, vp],
+            "dfcclPrepareFusedGemm": [C.POINTER(FusedInfo), vp, i, vp], "dfcclFusedGemmOperand": [i, vp, C.POINTER(vp), C.POINTER(vp)],
+            "dfcclRunFusedGemm": [i, vp, vp, vp, vp, vp], "dfcclRunFusedGemmT": [i, vp, vp, vp, vp, vp],
             "dfcclRun": [vp, vp, i, CALLBACK, vp, vp],
             "dfcclRunOnStream": [vp, vp, i, vp, CALLBACK, vp, vp],
             "dfcclRunDeferred": [vp, vp, i, CALLBACK, vp, vp], "dfcclTriggerOnStream": [i, vp, vp],
@@ -116,6 +125,7 @@ def lib() -> C.CDLL:
             "dfcclFusedAdamWStep": [vp, vp, vp, vp, vp, sz, i, C.c_float, C.c_float, C.c_float, C.c_float, C.c_float, i, vp],
             "dfcclOpsWarm": [],
             "dfcclGemmBf16": [vp, vp, vp, i, i, i, vp],
+            "dfcclGemmBf16Ex": [vp, vp, vp, i, i, i, i, i, vp],
             "dfcclGemmCheck": [C.POINTER(i)],
             "dfcclGemmFused": [vp, vp, vp, i, i, i, vp, sz, vp],
             "dfcclHeapPeerBase": [vp, i, C.POINTER(vp)],
@@ -276,6 +286,22 @@ class RankCtx:
         info = CollInfo(kind, count, dtype, dtype if out_dtype is None else out_dtype, op, root, scale, algo, n_blocks,
                         COLL_ARENA_BUFFERS if arena_buffers else 0)
         check(lib().dfcclPrepare(C.byref(info), comm.handle, coll_id, self.handle), f"dfcclPrepare({coll_id})")
+
+    def prepare_fused(self, coll_id: int, comm: Comm, kind: int, rows_per_rank: int, k: int, n: int) -> None:
+        """Register a GEMM fused with its tensor-parallel collective (``FUSED_ALLGATHER_GEMM`` / ``FUSED_GEMM_REDUCESCATTER``)."""
+        info = FusedInfo(kind, rows_per_rank, k, n)
+        check(lib().dfcclPrepareFusedGemm(C.byref(info), comm.handle, coll_id, self.handle), f"dfcclPrepareFusedGemm({coll_id})")
+
+    def fused_operand(self, coll_id: int):
+        """(address of this rank's rows, address of the gathered operand) of a registered all-gather -> GEMM."""
+        a, b = C.c_void_p(), C.c_void_p()
+        check(lib().dfcclFusedGemmOperand(coll_id, self.handle, C.byref(a), C.byref(b)), f"dfcclFusedGemmOperand({coll_id})")
+        return a.value, b.value
+
+    def run_fused(self, coll_id: int, x: int, w: int, out: int, stream: int, w_transposed: bool = False) -> None:
+        """``w``: [n, k]; with ``w_transposed`` [k, n] (read in place as an MN-major operand)."""
+        fn = lib().dfcclRunFusedGemmT if w_transposed else lib().dfcclRunFusedGemm
+        check(fn(coll_id, C.c_void_p(x), C.c_void_p(w), C.c_void_p(out), C.c_void_p(stream), self.handle), f"dfcclRunFusedGemm({coll_id})")
 
     def set_daemon_geometry(self, blocks: int = 0, threads: int = 0) -> None:
         check(lib().dfcclSetDaemonGeometry(self.handle, blocks, threads), "dfcclSetDaemonGeometry")

@@ -3,11 +3,17 @@
 ``AllGatherGemm``   y = all_gather(x_shard) @ W_local^T     (sequence-parallel column-parallel layer)
 ``GemmReduceScatter`` y_shard = reduce_scatter(x_local @ W_local^T)   (row-parallel layer, sequence-sharded output)
 
-Both own their symmetric-heap buffers and rendezvous words and drive the fused modes of
-``dfcclGemmFused`` (csrc/src/gemm/tcgen05_gemm.cu): peers' shards are pulled by communication
-warps of the GEMM kernel block by block while the tensor cores work on blocks already present;
-partial output tiles are stored straight into their owner's memory and reduced there as they
-arrive.  Heap offsets are exchanged once at construction over ``torch.distributed``.
+Both drive the fused modes of the tcgen05 GEMM kernel (csrc/src/gemm/tcgen05_gemm.cu): peers' shards are
+pulled by communication warps of the GEMM kernel block by block while the tensor cores work on blocks
+already present; partial output tiles are stored straight into their owner's memory and reduced there
+as they arrive.
+
+When the tensor-parallel group carries a rank context (``TpGroup(..., ctx=...)``) the operators are
+*registered* with it under collective ids (``dfcclPrepareFusedGemm``): the context allocates and
+exchanges their rendezvous words and receive areas when it is finalized, counts their launches,
+reports a wait that ran out through its asynchronous error and keeps its daemon's SMs out of their
+grids.  Without a context they own their symmetric-heap buffers themselves and exchange the offsets
+over ``torch.distributed`` at construction.
 """
 from __future__ import annotations
 
@@ -37,12 +43,22 @@ class TpGroup:
     """A tensor-parallel group: this library's communicator over the group plus the matching
     ``torch.distributed`` group (used only to exchange offsets at construction)."""
 
-    def __init__(self, comm: nv.Comm, pg: Optional["dist.ProcessGroup"], device: torch.device):
+    def __init__(self, comm: nv.Comm, pg: Optional["dist.ProcessGroup"], device: torch.device,
+                 ctx: Optional[nv.RankCtx] = None, first_id: int = 0):
+        """``ctx``: a rank context that is not finalized yet; fused operators of this group register with it under
+        consecutive collective ids from ``first_id`` (whoever finalizes the context registers its own collectives
+        from ``next_id`` on)."""
         self.comm, self.pg, self.device = comm, pg, device
         self.rank, self.n = comm.rank, comm.nranks
+        self.ctx, self.next_id = ctx, first_id
         assert nv.lib().dfcclGemmFusedArgsSize() == C.sizeof(_FusedArgs), "argument block layout mismatch"
         self._base = [comm.peer_base(j) for j in range(self.n)]
         self._mybase = comm.heap_info()[0]
+
+    def take_id(self) -> int:
+        i = self.next_id
+        self.next_id += 1
+        return i
 
     def alloc(self, nbytes: int, zero: bool = True):
         """Allocate in the symmetric heap; returns (local pointer, [address of every rank's copy as mapped here])."""
@@ -80,21 +96,53 @@ class AllGatherGemm:
         assert rows_per_rank % BM == 0 and k % BK == 0 and n_out % BN == 0
         self.tp, self.rows, self.k, self.n_out = tp, rows_per_rank, k, n_out
         self.m = rows_per_rank * tp.n
+        self.coll_id = None
+        if tp.ctx is not None:                          # registered operator: buffers come from the context at finalize
+            self.coll_id = tp.take_id()
+            tp.ctx.prepare_fused(self.coll_id, tp.comm, nv.FUSED_ALLGATHER_GEMM, rows_per_rank, k, n_out)
+            self._gathered = self._shard = None
+            return
         gp, peers = tp.alloc(self.m * k * 2)
-        self.gathered = tensor_from_ptr(gp, (self.m, k), torch.bfloat16, tp.device)
-        self.shard = self.gathered[tp.rank * rows_per_rank:(tp.rank + 1) * rows_per_rank]   # write the input here
+        self._gathered = tensor_from_ptr(gp, (self.m, k), torch.bfloat16, tp.device)
+        self._shard = self._gathered[tp.rank * rows_per_rank:(tp.rank + 1) * rows_per_rank]   # write the input here
         self._peer_shard = [peers[j] + j * rows_per_rank * k * 2 for j in range(tp.n)]
         self.block_ready = torch.zeros(self.m // BM, dtype=torch.int32, device=tp.device)
         self.rv = _Rendezvous(tp)
         self._args = None
         tp.barrier()
 
-    def __call__(self, x_shard: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    def _bind(self) -> None:
+        if self._gathered is None:                      # registered: the context owns the operand (valid once it is finalized)
+            sp, gp = self.tp.ctx.fused_operand(self.coll_id)
+            self._gathered = tensor_from_ptr(gp, (self.m, self.k), torch.bfloat16, self.tp.device)
+            self._shard = self._gathered[self.tp.rank * self.rows:(self.tp.rank + 1) * self.rows]
+
+    @property
+    def gathered(self) -> torch.Tensor:
+        """The [M, K] operand; complete after a call (the weight gradient reads it)."""
+        self._bind()
+        return self._gathered
+
+    @property
+    def shard(self) -> torch.Tensor:
+        """This rank's rows of the operand: writing the input here saves a copy."""
+        self._bind()
+        return self._shard
+
+    def __call__(self, x_shard: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None, w_transposed: bool = False) -> torch.Tensor:
+        """``w``: [n_out, k]; with ``w_transposed`` it is given as [k, n_out] and read in place (registered operators)."""
         tp = self.tp
-        if x_shard.data_ptr() != self.shard.data_ptr():
-            self.shard.copy_(x_shard)
         if out is None:
             out = torch.empty(self.m, self.n_out, dtype=torch.bfloat16, device=tp.device)
+        if self.coll_id is not None:
+            x_shard, w = x_shard.contiguous(), w.contiguous()
+            st = torch.cuda.current_stream(tp.device).cuda_stream if tp.device.type == "cuda" else 0
+            tp.ctx.run_fused(self.coll_id, x_shard.data_ptr(), w.data_ptr(), out.data_ptr(), st, w_transposed)
+            return out
+        if w_transposed:
+            w = w.t()
+        if x_shard.data_ptr() != self.shard.data_ptr():
+            self.shard.copy_(x_shard)
         self.rv.epoch += 1
         a = self._args
         if a is None:                                   # built once: only the epoch changes between calls
@@ -124,6 +172,11 @@ class GemmReduceScatter:
         self.tp, self.m, self.k, self.n_out = tp, m, k_local, n_out
         self.rows = m // tp.n
         self.tiles_mine = (self.rows // BM) * (n_out // BN)
+        self.coll_id = None
+        if tp.ctx is not None:
+            self.coll_id = tp.take_id()
+            tp.ctx.prepare_fused(self.coll_id, tp.comm, nv.FUSED_GEMM_REDUCESCATTER, self.rows, k_local, n_out)
+            return
         sp, speers = tp.alloc(tp.n * self.rows * n_out * 2)
         fp, fpeers = tp.alloc(tp.n * self.tiles_mine * 4)
         self._slots, self._flags = sp, fp
@@ -135,11 +188,17 @@ class GemmReduceScatter:
         self._args = None
         tp.barrier()
 
-    def __call__(self, x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    def __call__(self, x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None, w_transposed: bool = False) -> torch.Tensor:
         tp = self.tp
+        if w_transposed and self.coll_id is None:
+            w, w_transposed = w.t(), False
         x, w = x.contiguous(), w.contiguous()
         if out is None:
             out = torch.empty(self.rows, self.n_out, dtype=torch.bfloat16, device=tp.device)
+        if self.coll_id is not None:
+            st = torch.cuda.current_stream(tp.device).cuda_stream if tp.device.type == "cuda" else 0
+            tp.ctx.run_fused(self.coll_id, x.data_ptr(), w.data_ptr(), out.data_ptr(), st, w_transposed)
+            return out
         if tp.n == 1:
             nv.check(nv.lib().dfcclGemmBf16(x.data_ptr(), w.data_ptr(), out.data_ptr(), self.m, self.n_out, self.k,
                                             torch.cuda.current_stream(tp.device).cuda_stream), "dfcclGemmBf16")

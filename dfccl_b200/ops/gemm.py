@@ -32,6 +32,26 @@ def matmul_nt(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None)
     return out
 
 
+def matmul(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None, *, a_transposed: bool = False,
+           b_transposed: bool = False) -> torch.Tensor:
+    """``op(a) @ op(b).T`` on the tensor cores, where an operand flagged ``*_transposed`` is *stored* transposed:
+    ``a`` as [K, M] and / or ``b`` as [K, N] (row-major, the contraction index slow).  Nothing is copied - the kernel
+    describes such an operand to ``tcgen05.mma`` as MN-major.  With both flags this is ``a.T @ b``: the weight gradient
+    ``gy.T @ x`` of a linear layer; with ``b_transposed`` alone ``a @ b``: its data gradient ``gy @ W``."""
+    assert a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16 and a.is_cuda and b.is_cuda and a.dim() == 2 and b.dim() == 2
+    a, b = a.contiguous(), b.contiguous()
+    k, m = (a.shape if a_transposed else a.shape[::-1])
+    kb, n = (b.shape if b_transposed else b.shape[::-1])
+    assert k == kb, "contraction lengths differ"
+    if not gemm_supported(m, n, k):
+        raise ValueError(f"tcgen05 GEMM needs M % {BM} == 0, N % {BN} == 0, K % {BK} == 0, got {m} x {n} x {k}")
+    if out is None:
+        out = torch.empty(m, n, dtype=torch.bfloat16, device=a.device)
+    nv.check(nv.lib().dfcclGemmBf16Ex(a.data_ptr(), b.data_ptr(), out.data_ptr(), m, n, k, int(a_transposed), int(b_transposed),
+                                      torch.cuda.current_stream(a.device).cuda_stream), "dfcclGemmBf16Ex")
+    return out
+
+
 def check_kernels() -> bool:
     """True if no kernel of the GEMM file gave up on a bounded wait since the last check."""
     failed = C.c_int()

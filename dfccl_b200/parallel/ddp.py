@@ -87,7 +87,8 @@ class DaemonDDP:
                  weight_decay: float = 1e-4, randomize_order: bool = True, window: int = 2, seed: int = 0,
                  coll_id_base: int = 0, comm: Optional[nv.Comm] = None, n_blocks: int = 0,
                  daemon_blocks: int = 8, daemon_threads: int = 0, param_groups: Optional[Sequence[dict]] = None,
-                 optimizer: str = "sgd", betas=(0.9, 0.999), eps: float = 1e-8, nvls: Optional[bool] = None):
+                 optimizer: str = "sgd", betas=(0.9, 0.999), eps: float = 1e-8, nvls: Optional[bool] = None,
+                 ctx: Optional[nv.RankCtx] = None):
         """``param_groups`` (hybrid parallelism): a list of ``{"params": [...], "comm": Comm, "scale": float}``;
         every group gets its own buckets, reduced over its own communicator (sum times ``scale``).  All
         groups share this rank's one daemon, so ranks may submit them in any order.
@@ -96,7 +97,11 @@ class DaemonDDP:
         multimem schedule (the NVLink switch adds the members' copies; every GPU moves one message size instead of
         two).  ``None`` = when the fabric offers it and the communicator has at least four ranks
         (``DFCCL_DDP_NVLS=0`` switches it off); memory bound to a
-        multicast object ties the ranks' fates together, so tests of failure paths pass ``False``."""
+        multicast object ties the ranks' fates together, so tests of failure paths pass ``False``.
+
+        ``ctx``: a rank context that already holds registrations (the fused tensor-parallel operators of a hybrid
+        job, under ids below ``coll_id_base``) and is not finalized yet; the buckets are added to it and this
+        wrapper finalizes and, in ``close``, destroys it."""
         self.module = module
         self.dist = dist
         self.comm = comm or dist.comm
@@ -128,7 +133,7 @@ class DaemonDDP:
         for g in param_groups:
             self._build_buckets(int(bucket_mb * (1 << 20)), g["params"], g.get("comm") or self.comm, float(g["scale"]))
         self._place_gradients()
-        self.ctx = nv.RankCtx(dist.rank, dist.local_rank if self.device.type == "cuda" else -1)
+        self.ctx = ctx if ctx is not None else nv.RankCtx(dist.rank, dist.local_rank if self.device.type == "cuda" else -1)
         # gradient buckets need a fraction of the fabric: a small grid leaves the SMs to the training kernels
         if self.device.type == "cuda":
             self.ctx.set_daemon_geometry(daemon_blocks, daemon_threads)

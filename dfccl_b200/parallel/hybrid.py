@@ -53,6 +53,7 @@ class Mesh:
     stage_comm: nv.Comm
     pp_fwd: object = None        # process group that carries activations (stage s -> s + 1); None = the default group
     pp_bwd: object = None        # process group that carries activation gradients (stage s + 1 -> s)
+    ctx: object = None           # this rank's context: fused tensor-parallel operators and gradient buckets share it
 
     def close(self) -> None:
         for c in (self.tp_group.comm, self.dp_comm, self.stage_comm):
@@ -76,7 +77,10 @@ def build_mesh(d: Dist, tp: int, pp: int, dp: int) -> Mesh:
     fwd = bwd = None
     if d.world > 1 and pp > 1:                              # one group per direction of the pipeline traffic
         fwd, bwd = dist.new_group(), dist.new_group()
-    return Mesh(tp, pp, dp, tp_rank, pp_rank, dp_rank, TpGroup(tp_comm, pg, d.device), dp_comm, stage_comm, fwd, bwd)
+    # one rank context for everything this rank registers: on GPUs the fused tensor-parallel operators take the first
+    # ids (as the model is built), the gradient buckets follow (HybridTrainer)
+    ctx = nv.RankCtx(d.rank, d.local_rank) if d.device.type == "cuda" else None
+    return Mesh(tp, pp, dp, tp_rank, pp_rank, dp_rank, TpGroup(tp_comm, pg, d.device, ctx=ctx), dp_comm, stage_comm, fwd, bwd, ctx)
 
 
 class HybridTrainer:
@@ -93,13 +97,12 @@ class HybridTrainer:
         replicated = [p for p in params if getattr(p, "tp_replicated", False)]
         groups = [{"params": sharded, "comm": mesh.dp_comm, "scale": 1.0 / mesh.dp},
                   {"params": replicated, "comm": mesh.stage_comm, "scale": 1.0 / mesh.dp}]
+        # the context already holds the fused operators the stage registered while it was built; finalizing it (inside
+        # DaemonDDP) also keeps the daemon's SMs out of the fused kernels' grids
         self.ddp = DaemonDDP(stage, d, bucket_mb=bucket_mb, lr=lr, momentum=momentum, weight_decay=weight_decay,
-                             randomize_order=True, seed=seed, param_groups=groups, daemon_blocks=daemon_blocks, optimizer=optimizer)
+                             randomize_order=True, seed=seed, param_groups=groups, daemon_blocks=daemon_blocks, optimizer=optimizer,
+                             ctx=mesh.ctx, coll_id_base=mesh.tp_group.next_id if mesh.ctx is not None else 0)
         self.ddp.hooks_enabled = False
-        if d.device.type == "cuda":
-            # the fused GEMM launches need all their CTAs resident together: keep them off the SMs a daemon
-            # instance may still hold when the next forward pass starts
-            nv.check(nv.lib().dfcclGemmReserveSms(daemon_blocks), "dfcclGemmReserveSms")
         self.prev = d.rank - mesh.tp if mesh.pp_rank > 0 else None
         self.next = d.rank + mesh.tp if mesh.pp_rank < mesh.pp - 1 else None
         self._loss = torch.zeros(1, dtype=torch.float32, device=d.device)

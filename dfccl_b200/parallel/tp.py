@@ -46,6 +46,16 @@ def _fused(tp: TpGroup) -> bool:
     return tp.device.type == "cuda" and getattr(tp, "library", "dfccl") == "dfccl"
 
 
+def _wgrad(gy: torch.Tensor, x: torch.Tensor) -> torch.Tensor:
+    """gy^T @ x (the weight gradient: a contraction over the token dimension).  Both operands are stored with the
+    contraction index slow, which the tcgen05 kernel reads in place as MN-major operands; shapes it cannot tile go
+    to ``torch.matmul``."""
+    from ..ops import gemm
+    if gy.is_cuda and gemm.gemm_supported(gy.shape[1], x.shape[1], gy.shape[0]):
+        return gemm.matmul(gy, x, a_transposed=True, b_transposed=True)
+    return gy.t() @ x
+
+
 def tp_all_gather(tp: TpGroup, x: torch.Tensor) -> torch.Tensor:
     """Concatenate the ranks' tensors along dim 0 with this library's stream-ordered all-gather."""
     if tp.n == 1:
@@ -99,9 +109,10 @@ class _ColumnFn(torch.autograd.Function):
         if layer.op is None:
             x_full = tp_all_gather(tp, saved)
             return tp_reduce_scatter(tp, gy @ weight), gy.t() @ x_full, None
-        gw = gy.t() @ saved
-        # data gradient with the reduce-scatter inside the GEMM: gx = RS(gy [M, N/n] @ W [N/n, K]), B operand = W^T
-        gx = layer.bwd_op(gy, weight.t().contiguous())
+        gw = _wgrad(gy, saved)
+        # data gradient with the reduce-scatter inside the GEMM: gx = RS(gy [M, N/n] @ W [N/n, K]); the B operand is W^T,
+        # handed over as W itself (stored [contraction, output]: read in place as an MN-major operand)
+        gx = layer.bwd_op(gy, weight, w_transposed=True)
         return gx, gw, None
 
 
@@ -126,8 +137,8 @@ class _RowFn(torch.autograd.Function):
             return gy @ weight, gy.t() @ x, None
         # data gradient with the all-gather inside the GEMM: gx = AG(gy_shard) [M, N] @ W [N, K/n], B operand = W^T;
         # the operator's gathered buffer then holds the full output gradient for the weight gradient
-        gx = layer.bwd_op(gy_shard, weight.t().contiguous())
-        gw = layer.bwd_op.gathered.t() @ x
+        gx = layer.bwd_op(gy_shard, weight, w_transposed=True)
+        gw = _wgrad(layer.bwd_op.gathered, x)
         return gx, gw, None
 
 

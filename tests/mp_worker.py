@@ -235,6 +235,74 @@ def scenario_fused_tp(nv, comm, rank, world, backend):
     return out
 
 
+def scenario_tp_dp_shuffle(nv, comm, rank, world, backend):
+    """Fused tensor-parallel operators (registered with the rank context) and data-parallel gradient all-reduces of the
+    overlapping group, one context per rank: operators in model order, all-reduces in a per-rank shuffled order in
+    between, on one stream.  tp = 2, dp = world / 2.  Results against fp32 references."""
+    import torch
+    from dfccl_b200.utils import tensor_from_ptr
+    dev = torch.device("cuda", rank)
+    tp_comm = comm.split(rank // 2, rank)
+    dp_comm = comm.split(rank % 2, rank)
+    dp = world // 2
+    rows, k, n = 256, 512, 512
+    ctx = nv.RankCtx(rank, rank)
+    ctx.set_daemon_geometry(4, 0)
+    ctx.prepare_fused(0, tp_comm, nv.FUSED_ALLGATHER_GEMM, rows, k, n)
+    ctx.prepare_fused(1, tp_comm, nv.FUSED_GEMM_REDUCESCATTER, rows, k, n)
+    counts = [3000, 1 << 20, 517, 70000, 1 << 18]
+    bufs = []
+    for i, cnt in enumerate(counts):
+        ctx.prepare(2 + i, dp_comm, nv.ALLREDUCE, cnt, nv.FLOAT32)
+        p = dp_comm.alloc(cnt * 4)
+        bufs.append((p, tensor_from_ptr(p, (cnt,), torch.float32, dev)))
+    ctx.finalize()
+    g = torch.Generator().manual_seed(77)
+    tpg = rank // 2                                   # my tensor-parallel group
+    xs = torch.randn(world, rows, k, generator=g).to(torch.bfloat16)
+    ws = torch.randn(world, n, k, generator=g).to(torch.bfloat16)
+    x2 = torch.randn(world, 2 * rows, k, generator=g).to(torch.bfloat16)
+    x_d, w_d, x2_d = xs[rank].to(dev), ws[rank].to(dev), x2[rank].to(dev)
+    out_ag = torch.empty(2 * rows, n, dtype=torch.bfloat16, device=dev)
+    out_rs = torch.empty(rows, n, dtype=torch.bfloat16, device=dev)
+    st = torch.cuda.current_stream().cuda_stream
+    rng = random.Random(31 + rank)
+    for it in range(4):
+        dpart = list(range(len(counts)))
+        rng.shuffle(dpart)
+        cut = sorted(rng.sample(range(len(dpart) + 1), 2))
+        seq = [("d", i) for i in dpart[:cut[0]]] + [("f", 0)] + [("d", i) for i in dpart[cut[0]:cut[1]]] + [("f", 1)] + [("d", i) for i in dpart[cut[1]:]]
+        for kind, i in seq:
+            if kind == "d":
+                bufs[i][1].fill_(float((rank + 1) * (i + 1) + it))
+                ctx.run_on_stream(2 + i, bufs[i][0], bufs[i][0], st)
+            elif i == 0:
+                ctx.run_fused(0, x_d.data_ptr(), w_d.data_ptr(), out_ag.data_ptr(), st)
+            else:
+                ctx.run_fused(1, x2_d.data_ptr(), w_d.data_ptr(), out_rs.data_ptr(), st)
+        for i in range(len(counts)):
+            ctx.stream_wait(2 + i, st)
+        torch.cuda.synchronize()
+        assert ctx.wait_all(60000) == nv.SUCCESS
+        lo, hi = 2 * tpg, 2 * tpg + 1
+        ref = torch.cat([xs[lo], xs[hi]]).to(dev).float() @ ws[rank].to(dev).float().t()
+        err = (out_ag.float() - ref).abs().max().item() / (ref.abs().max().item() + 1e-6)
+        assert err < 1e-2, ("ag-gemm", it, err)
+        parts = [(x2[q].to(dev).float() @ ws[q].to(dev).float().t()).to(torch.bfloat16).float() for q in (lo, hi)]
+        ref2 = sum(parts)[(rank % 2) * rows:(rank % 2 + 1) * rows]
+        err2 = (out_rs.float() - ref2).abs().max().item() / (ref2.abs().max().item() + 1e-6)
+        assert err2 < 1e-2, ("gemm-rs", it, err2)
+        for i in range(len(counts)):
+            want = sum((q + 1) * (i + 1) + it for q in range(rank % 2, world, 2))
+            assert bool((bufs[i][1] == float(want)).all()), ("bucket", i, it)
+    stats = ctx.stats()
+    assert ctx.async_error() == nv.SUCCESS
+    ctx.destroy()
+    tp_comm.destroy()
+    dp_comm.destroy()
+    return {"fused": stats["fusedLaunches"], "cqes": stats["cqesDelivered"], "dp": dp}
+
+
 def _gpt_hybrid(nv, comm, rank, world, backend, tp, pp, dp, port, schedule="1f1b", n_micro=2):
     """Hybrid tp x pp x dp training of a small GPT-2 against the same model on one rank: the loss of
     every step must agree (the second and third steps depend on the gradients and the update)."""

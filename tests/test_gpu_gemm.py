@@ -25,6 +25,27 @@ def test_gemm_matches_fp32_reference(m, n, k):
     assert torch.equal(c, c2)
 
 
+@pytest.mark.parametrize("a_t,b_t", [(False, True), (True, False), (True, True)])
+@pytest.mark.parametrize("m,n,k", [(128, 256, 64), (256, 512, 192), (1024, 1024, 2048), (1536, 1024, 8192)])
+def test_gemm_reads_transposed_operands_in_place(m, n, k, a_t, b_t):
+    """Operands stored with the contraction index slow (A as [K, M], B as [K, N]) are described to the tensor cores as
+    MN-major and read as they are: the data gradient (B transposed) and the weight gradient (both) of a linear layer."""
+    from dfccl_b200.ops import gemm
+    torch.manual_seed(m * 3 + n * 5 + k)
+    a = torch.randn(m, k, device="cuda", dtype=torch.bfloat16)
+    b = torch.randn(n, k, device="cuda", dtype=torch.bfloat16)
+    a_in = a.t().contiguous() if a_t else a
+    b_in = b.t().contiguous() if b_t else b
+    c = gemm.matmul(a_in, b_in, a_transposed=a_t, b_transposed=b_t)
+    torch.cuda.synchronize()
+    assert gemm.check_kernels()
+    ref = a.float() @ b.float().t()
+    err = (c.float() - ref).abs().max().item()
+    scale = ref.abs().max().item()
+    assert err <= 1e-2 * scale + 1e-2, (err, scale)
+    assert torch.equal(c, gemm.matmul_nt(a, b))          # the same products in the same order: bit-identical to the K-major form
+
+
 def test_gemm_rejects_shapes_it_cannot_tile():
     from dfccl_b200.ops import gemm
     a = torch.randn(100, 64, device="cuda", dtype=torch.bfloat16)

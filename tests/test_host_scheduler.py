@@ -195,3 +195,74 @@ def test_grouped_send_recv_with_both_ends_in_one_thread(host_backend):
             inp[r][:] = 0
     for c in comms:
         c.destroy()
+
+
+def test_registered_fused_operators_among_shuffled_data_parallel_buckets(host_backend):
+    """tp2 x dp2 on four ranks: every rank registers two fused tensor-parallel operators (all-gather -> GEMM and
+    GEMM -> reduce-scatter, on its tensor-parallel communicator) and four gradient all-reduces (on its data-parallel
+    communicator) with ONE rank context, then issues the operators in model order and the all-reduces in its own
+    shuffled order in between.  Everything completes, results match numpy, launches are counted."""
+    from helpers import bf16_bits_to_f32, f32_to_bf16_bits
+    nv = host_backend
+    comms = nv.Comm.init_loopback(4)
+    rows, k, n = 128, 64, 256
+    rng0 = np.random.default_rng(5)
+    xs = [f32_to_bf16_bits(rng0.standard_normal((rows, k)).astype(np.float32) * 0.5) for _ in range(4)]          # AG input rows per rank
+    ws = [f32_to_bf16_bits(rng0.standard_normal((n, k)).astype(np.float32) * 0.5) for _ in range(4)]             # per-rank weights
+    x2 = [f32_to_bf16_bits(rng0.standard_normal((2 * rows, k)).astype(np.float32) * 0.5) for _ in range(4)]     # RS input per rank
+    counts = [1000, 40000, 257, 9000]
+    stats = {}
+
+    def body(r):
+        c = comms[r]
+        tp_comm = c.split(r // 2, r)              # ranks {0,1}, {2,3}
+        dp_comm = c.split(r % 2, r)               # ranks {0,2}, {1,3}
+        ctx = nv.RankCtx(r)
+        ctx.prepare_fused(0, tp_comm, nv.FUSED_ALLGATHER_GEMM, rows, k, n)
+        ctx.prepare_fused(1, tp_comm, nv.FUSED_GEMM_REDUCESCATTER, rows, k, n)
+        bufs = []
+        for i, cnt in enumerate(counts):
+            ctx.prepare(2 + i, dp_comm, nv.ALLREDUCE, cnt, nv.FLOAT32)
+            p = dp_comm.alloc(cnt * 4)
+            bufs.append((p, host_array(p, cnt, np.float32)))
+        ctx.finalize()
+        with pytest.raises(nv.DfcclError):                       # the ids of fused operators are not submittable collectives
+            ctx.run(0, bufs[0][0], bufs[0][0])
+        order_rng = random.Random(900 + r)
+        out_ag = np.zeros((2 * rows, n), np.uint16)
+        out_rs = np.zeros((rows, n), np.uint16)
+        for it in range(3):
+            plan = [("f", 0), ("f", 1)] + [("d", i) for i in range(len(counts))]
+            dp_part = [p for p in plan if p[0] == "d"]
+            order_rng.shuffle(dp_part)
+            cut = sorted(order_rng.sample(range(len(dp_part) + 1), 2))          # where the two operators sit among the buckets
+            seq = dp_part[:cut[0]] + [("f", 0)] + dp_part[cut[0]:cut[1]] + [("f", 1)] + dp_part[cut[1]:]
+            for kind, i in seq:
+                if kind == "d":
+                    bufs[i][1][:] = (r + 1) * (i + 1) + it
+                    ctx.run(2 + i, bufs[i][0], bufs[i][0])
+                elif i == 0:
+                    ctx.run_fused(0, xs[r].ctypes.data, ws[r].ctypes.data, out_ag.ctypes.data, 0)
+                else:
+                    ctx.run_fused(1, x2[r].ctypes.data, ws[r].ctypes.data, out_rs.ctypes.data, 0)
+            assert ctx.wait_all(60000) == nv.SUCCESS
+            peer = r ^ 1
+            lo, hi = min(r, peer), max(r, peer)
+            gathered = np.concatenate([bf16_bits_to_f32(xs[lo]), bf16_bits_to_f32(xs[hi])])
+            np.testing.assert_allclose(bf16_bits_to_f32(out_ag), gathered @ bf16_bits_to_f32(ws[r]).T, rtol=2e-2, atol=2e-2)
+            full = sum(bf16_bits_to_f32(x2[q]) @ bf16_bits_to_f32(ws[q]).T for q in (lo, hi))
+            mine = full[(r % 2) * rows:(r % 2 + 1) * rows]
+            np.testing.assert_allclose(bf16_bits_to_f32(out_rs), mine, rtol=3e-2, atol=3e-2)
+            for i, cnt in enumerate(counts):
+                other = r ^ 2
+                assert np.all(bufs[i][1] == (r + 1) * (i + 1) + it + (other + 1) * (i + 1) + it)
+        stats[r] = ctx.stats()
+        assert ctx.async_error() == nv.SUCCESS
+        ctx.destroy()
+        tp_comm.destroy()
+        dp_comm.destroy()
+
+    run_ranks(4, body, timeout=240)
+    for c in comms:
+        c.destroy()
+    assert all(s["fusedLaunches"] == 6 and s["cqesDelivered"] == 12 for s in stats.values()), stats

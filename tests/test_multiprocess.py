@@ -47,6 +47,17 @@ def test_host_gpt2_hybrid_parallel(layout, world):
     assert len(set(losses)) == 1, losses                     # every rank reports the same global loss
 
 
+@pytest.mark.gpu
+@pytest.mark.multigpu
+def test_gpu_fused_operators_among_shuffled_gradient_buckets():
+    """Registered fused tensor-parallel operators and daemon all-reduces of the overlapping data-parallel group, issued
+    in per-rank shuffled interleavings (tp2 x dp2 on four GPUs, tp2 x dp1 on two)."""
+    import torch
+    world = 4 if torch.cuda.device_count() >= 4 else 2
+    res = mp_worker.launch(world, "cuda", "tp_dp_shuffle", timeout=300)
+    assert all(r["fused"] == 8 and r["cqes"] == 20 for r in res.values()), res
+
+
 def test_host_pipeline_schedules_agree_and_1f1b_holds_fewer_activations():
     """Three pipeline stages, four micro-batches: GPipe and 1F1B train identically (same losses as the unsharded
     model, checked inside the scenario); 1F1B holds at most pp - stage micro-batches of activations, GPipe all."""
