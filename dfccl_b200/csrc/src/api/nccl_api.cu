@@ -103,8 +103,12 @@ DF_API ncclResult_t ncclCommDestroy(ncclComm_t comm) { return commDestroy(comm);
 
 DF_API ncclResult_t ncclCommAbort(ncclComm_t comm) {
   if (!comm) return ncclSuccess;
-  comm->ctl->abortFlag = 1;          // running kernels leave at their next poll
+  // The abort word goes up before anything that waits: kernels of this communicator (and host-backend calls running
+  // in other threads) look at it every few hundred polls and leave, so the device synchronisation inside the
+  // destroy below returns promptly instead of after the kernels' wait limit.
+  comm->ctl->abortFlag = 1;
   comm->aborted = true;
+  { std::lock_guard<std::mutex> l(comm->mu); }      // a call of another thread that is still inside the communicator has left
   return commDestroy(comm);
 }
 

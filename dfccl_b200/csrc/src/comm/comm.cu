@@ -126,18 +126,32 @@ ncclResult_t commCreate(std::shared_ptr<Bootstrap> boot, dfcclBackend_t backend,
   // members on another host cannot be mapped: the whole communicator then goes through the network path
   c->netMode = n > 1 && paramI64("FORCE_NET", 0) != 0;
   for (int j = 0; j < n; ++j) if (all[j].heap.hostHash != all[r].heap.hostHash) c->netMode = true;
+  // Transport selection, first fit (role of the reference's selectTransport, src/transport.cc:25-45): peer memory when
+  // every member can map every other member's heap, else the host-staged path over the network transport (which on
+  // one host is its loopback).  The verdict is collective: one member that cannot map a peer - no peer access between
+  // the two GPUs, or P2P_DISABLE set - moves the whole communicator, because the schedules need all pairs.
+  int32_t p2pOk = (c->netMode || paramI64("P2P_DISABLE", 0) != 0) ? 0 : 1;
   for (int j = 0; j < n; ++j) {
     c->handles[j] = all[j].heap;
     c->peerSaFlagsOff[j] = all[j].saFlagsOff;
     c->peerP2pFlagsOff[j] = all[j].p2pFlagsOff;
     c->peerPushOff[j] = all[j].pushOff;
-    if (j == r) c->peerHeap[j] = c->heap->base();
-    else if (c->netMode) c->peerHeap[j] = nullptr;
-    else DFCHECK(c->heap->importPeer(all[j].heap, &c->peerHeap[j]));
+    c->peerHeap[j] = j == r ? c->heap->base() : nullptr;
+    if (j != r && p2pOk && c->heap->importPeer(all[j].heap, &c->peerHeap[j]) != ncclSuccess) {
+      DF_INFO(SUB_INIT, "rank %d cannot map the memory of rank %d: this communicator will not use peer memory", r, j);
+      p2pOk = 0;
+    }
+  }
+  if (n > 1 && !c->netMode) {
+    std::vector<int32_t> verdicts(n, 0);
+    verdicts[r] = p2pOk;
+    DFCHECK(boot->allGather(verdicts.data(), sizeof(int32_t)));
+    for (int j = 0; j < n; ++j) if (!verdicts[j]) c->netMode = true;
+    if (c->netMode) for (int j = 0; j < n; ++j) if (j != r) c->peerHeap[j] = nullptr;
   }
   if (c->netMode) {
     DFCHECK(NetRing::create(boot.get(), &c->netRing));
-    DF_INFO(SUB_INIT | SUB_NET, "communicator of %d ranks spans hosts (or DFCCL_FORCE_NET): collectives are staged through host memory over '%s'", n, netGet()->name);
+    DF_INFO(SUB_INIT | SUB_NET, "communicator of %d ranks cannot use peer memory (members on other hosts, no peer access, P2P_DISABLE or FORCE_NET): collectives are staged through host memory over '%s'", n, netGet()->name);
   }
   // minimal RankDev for stream-ordered kernels: control words and timeouts only
   RankDev& rd = c->saRdHost;

@@ -162,3 +162,26 @@ print("OK")
     p = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True, timeout=120)
     assert p.returncode == 0 and "OK" in p.stdout, p.stdout + p.stderr
     assert "offers no device" in (p.stdout + p.stderr)
+
+
+def test_transport_selection_falls_back_when_peer_memory_is_off(host_backend, monkeypatch):
+    """No FORCE_NET: the members merely cannot (are told not to) map one another's memory - NCCL_P2P_DISABLE=1, the
+    reference's knob.  The communicator is still created, picks the host-staged path by itself (every member reaches
+    the same verdict) and computes the right result."""
+    monkeypatch.delenv("DFCCL_FORCE_NET", raising=False)
+    monkeypatch.setenv("NCCL_P2P_DISABLE", "1")
+    nv = host_backend
+    world, n = 3, 5003
+    comms = nv.Comm.init_loopback(world)
+    ins = [_data(nv, nv.FLOAT32, n, r, seed=3) for r in range(world)]
+    total = sum(a.astype(np.float64) for a in ins)
+
+    def body(r):
+        a, b = ins[r].copy(), np.zeros(n, np.float32)
+        nv.check(nv.lib().ncclAllReduce(a.ctypes.data, b.ctypes.data, n, nv.FLOAT32, nv.SUM, comms[r].handle, None))
+        np.testing.assert_allclose(b.astype(np.float64), total)
+        assert not comms[r].peer_base((r + 1) % world)          # no member maps another member's heap in this mode
+
+    run_ranks(world, body, timeout=120)
+    for c in comms:
+        c.destroy()

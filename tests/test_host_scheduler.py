@@ -266,3 +266,32 @@ def test_registered_fused_operators_among_shuffled_data_parallel_buckets(host_ba
     for c in comms:
         c.destroy()
     assert all(s["fusedLaunches"] == 6 and s["cqesDelivered"] == 12 for s in stats.values()), stats
+
+
+def test_comm_abort_ends_a_stuck_stream_collective_quickly(host_backend):
+    """One rank never joins the all-reduce.  ncclCommAbort from another thread raises the abort word first, so the
+    waiting kernel leaves at its next look at it - long before its 30 s wait limit - and the abort call returns."""
+    import threading
+    import time
+    nv = host_backend
+    L = nv.lib()
+    comms = nv.Comm.init_loopback(2)
+    buf = comms[0].alloc(4096)
+    result = {}
+
+    def stuck():
+        t0 = time.time()
+        result["rc"] = L.ncclAllReduce(C.c_void_p(buf), C.c_void_p(buf), 1024, nv.FLOAT32, nv.SUM, comms[0].handle, None)
+        result["s"] = time.time() - t0
+
+    with _env(DFCCL_WAIT_TIMEOUT_MS=30000):
+        t = threading.Thread(target=stuck, daemon=True)
+        t.start()
+        time.sleep(0.3)
+        t0 = time.time()
+        assert L.ncclCommAbort(comms[0].handle) == nv.SUCCESS
+        abort_s = time.time() - t0
+        t.join(10)
+    assert not t.is_alive() and result["s"] < 5 and abort_s < 5, (result, abort_s)
+    assert result["rc"] in (nv.ABORTED, nv.TIMEOUT)
+    comms[1].destroy()
