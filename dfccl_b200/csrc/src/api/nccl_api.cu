@@ -31,12 +31,20 @@ DF_API ncclResult_t ncclGetUniqueId(ncclUniqueId* id) {
   return bootstrapGetUniqueId(id);
 }
 
+static int groupDepth();
+static void groupRecordInit(ncclComm_t* out, int nranks, const ncclUniqueId& id, int rank, dfcclBackend_t be, int dev);
+
 DF_API ncclResult_t ncclCommInitRank(ncclComm_t* comm, int nranks, ncclUniqueId commId, int rank) {
   if (!comm) return ncclInvalidArgument;
   if (nranks < 1 || rank < 0 || rank >= nranks) { DF_WARN("invalid rank %d of %d", rank, nranks); return ncclInvalidArgument; }
   dfcclBackend_t be = defaultBackend();
   int dev = 0;
   if (be == dfcclBackendCuda) CUDACHECK(cudaGetDevice(&dev));
+  if (groupDepth() > 0) {               // inside a group: recorded for the device that is current now, created at ncclGroupEnd
+    *comm = nullptr;
+    groupRecordInit(comm, nranks, commId, rank, be, dev);
+    return ncclSuccess;
+  }
   std::unique_ptr<Bootstrap> b;
   DFCHECK(bootstrapCreateTcp(commId, rank, nranks, &b));
   return commCreate(std::shared_ptr<Bootstrap>(std::move(b)), be, dev, false, nullptr, comm);
@@ -168,34 +176,104 @@ DF_API ncclResult_t ncclRedOpDestroy(ncclRedOp_t op, ncclComm_t comm) {
   return ncclSuccess;
 }
 
-// ---- groups: collectives are independent launches, so a group only has to fuse the
-// send / recv calls made inside it into one kernel (they wait for each other)
+// ---- groups (reference: src/group.cc:96-105,150-422).  Inside ncclGroupStart / ncclGroupEnd nothing blocks and nothing
+// waits for a peer: communicator initialisations and collectives are recorded, and ncclGroupEnd runs them - the
+// initialisations on threads of their own (one thread may create the communicators of all its GPUs, each of which
+// waits for the others), then the collectives (launched back to back on the GPU; on the host backend, where a
+// collective is a blocking call, each communicator's calls on a thread of their own so that one thread may hold
+// several ranks), then the send / recv calls fused into one kernel per communicator and stream.
 static thread_local int t_groupDepth = 0;
+namespace {
+struct GroupInit { ncclComm_t* out; int nranks, rank, device; ncclUniqueId id; dfcclBackend_t be; };
+struct GroupColl { ncclComm* comm; int kind; const void* send; void* recv; size_t count; ncclDataType_t type; ncclRedOp_t op; int root; cudaStream_t stream; };
+thread_local std::vector<GroupInit> t_groupInits;
+thread_local std::vector<GroupColl> t_groupColls;
+
+ncclResult_t initRankNow(ncclComm_t* comm, int nranks, const ncclUniqueId& commId, int rank, dfcclBackend_t be, int dev) {
+  if (be == dfcclBackendCuda) CUDACHECK(cudaSetDevice(dev));
+  std::unique_ptr<Bootstrap> b;
+  DFCHECK(bootstrapCreateTcp(commId, rank, nranks, &b));
+  return commCreate(std::shared_ptr<Bootstrap>(std::move(b)), be, dev, false, nullptr, comm);
+}
+
+ncclResult_t groupCollective(ncclComm* c, int kind, const void* s, void* r, size_t count, ncclDataType_t t, ncclRedOp_t op, int root, cudaStream_t st) {
+  if (t_groupDepth > 0 && c) { t_groupColls.push_back({c, kind, s, r, count, t, op, root, st}); return ncclSuccess; }
+  return commCollective(c, kind, s, r, count, t, op, root, st);
+}
+
+ncclResult_t groupFlush() {
+  ncclResult_t res = ncclSuccess;
+  std::vector<GroupInit> inits;
+  std::vector<GroupColl> colls;
+  inits.swap(t_groupInits);
+  colls.swap(t_groupColls);
+  if (!inits.empty()) {                                   // every member of a communicator waits for the others: one thread each
+    std::vector<ncclResult_t> rs(inits.size(), ncclSuccess);
+    std::vector<std::thread> ts;
+    for (size_t i = 0; i < inits.size(); ++i)
+      ts.emplace_back([&, i] { rs[i] = initRankNow(inits[i].out, inits[i].nranks, inits[i].id, inits[i].rank, inits[i].be, inits[i].device); });
+    for (auto& t : ts) t.join();
+    for (auto r : rs) if (r != ncclSuccess && res == ncclSuccess) res = r;
+  }
+  if (!colls.empty() && res == ncclSuccess) {
+    bool host = false;
+    for (auto& g : colls) if (g.comm->backend != dfcclBackendCuda) host = true;
+    if (!host) {
+      for (auto& g : colls) {                             // asynchronous launches: program order per communicator is kept
+        ncclResult_t r = commCollective(g.comm, g.kind, g.send, g.recv, g.count, g.type, g.op, g.root, g.stream);
+        if (r != ncclSuccess && res == ncclSuccess) res = r;
+      }
+    } else {
+      std::vector<ncclComm*> order;                       // communicators in order of first appearance
+      for (auto& g : colls) if (std::find(order.begin(), order.end(), g.comm) == order.end()) order.push_back(g.comm);
+      std::vector<ncclResult_t> rs(order.size(), ncclSuccess);
+      std::vector<std::thread> ts;
+      for (size_t i = 0; i < order.size(); ++i)
+        ts.emplace_back([&, i] {
+          for (auto& g : colls) {
+            if (g.comm != order[i]) continue;
+            ncclResult_t r = commCollective(g.comm, g.kind, g.send, g.recv, g.count, g.type, g.op, g.root, g.stream);
+            if (r != ncclSuccess && rs[i] == ncclSuccess) rs[i] = r;
+          }
+        });
+      for (auto& t : ts) t.join();
+      for (auto r : rs) if (r != ncclSuccess && res == ncclSuccess) res = r;
+    }
+  }
+  ncclResult_t p = p2pFlush();
+  return res != ncclSuccess ? res : p;
+}
+}  // namespace
+
+static int groupDepth() { return t_groupDepth; }
+static void groupRecordInit(ncclComm_t* out, int nranks, const ncclUniqueId& id, int rank, dfcclBackend_t be, int dev) {
+  t_groupInits.push_back({out, nranks, rank, dev, id, be});
+}
 
 DF_API ncclResult_t ncclGroupStart(void) { ++t_groupDepth; return ncclSuccess; }
 DF_API ncclResult_t ncclGroupEnd(void) {
   if (t_groupDepth == 0) { DF_WARN("ncclGroupEnd without ncclGroupStart"); return ncclInvalidUsage; }
   if (--t_groupDepth > 0) return ncclSuccess;
-  return p2pFlush();
+  return groupFlush();
 }
 
 DF_API ncclResult_t ncclAllReduce(const void* s, void* r, size_t count, ncclDataType_t t, ncclRedOp_t op, ncclComm_t c, cudaStream_t st) {
-  return commCollective(c, dfcclCollAllReduce, s, r, count, t, op, 0, st);
+  return groupCollective(c, dfcclCollAllReduce, s, r, count, t, op, 0, st);
 }
 DF_API ncclResult_t ncclReduce(const void* s, void* r, size_t count, ncclDataType_t t, ncclRedOp_t op, int root, ncclComm_t c, cudaStream_t st) {
-  return commCollective(c, dfcclCollReduce, s, r, count, t, op, root, st);
+  return groupCollective(c, dfcclCollReduce, s, r, count, t, op, root, st);
 }
 DF_API ncclResult_t ncclBroadcast(const void* s, void* r, size_t count, ncclDataType_t t, int root, ncclComm_t c, cudaStream_t st) {
-  return commCollective(c, dfcclCollBroadcast, s, r, count, t, ncclSum, root, st);
+  return groupCollective(c, dfcclCollBroadcast, s, r, count, t, ncclSum, root, st);
 }
 DF_API ncclResult_t ncclBcast(void* buff, size_t count, ncclDataType_t t, int root, ncclComm_t c, cudaStream_t st) {
-  return commCollective(c, dfcclCollBroadcast, buff, buff, count, t, ncclSum, root, st);
+  return groupCollective(c, dfcclCollBroadcast, buff, buff, count, t, ncclSum, root, st);
 }
 DF_API ncclResult_t ncclReduceScatter(const void* s, void* r, size_t recvcount, ncclDataType_t t, ncclRedOp_t op, ncclComm_t c, cudaStream_t st) {
-  return commCollective(c, dfcclCollReduceScatter, s, r, recvcount, t, op, 0, st);
+  return groupCollective(c, dfcclCollReduceScatter, s, r, recvcount, t, op, 0, st);
 }
 DF_API ncclResult_t ncclAllGather(const void* s, void* r, size_t sendcount, ncclDataType_t t, ncclComm_t c, cudaStream_t st) {
-  return commCollective(c, dfcclCollAllGather, s, r, sendcount, t, ncclSum, 0, st);
+  return groupCollective(c, dfcclCollAllGather, s, r, sendcount, t, ncclSum, 0, st);
 }
 DF_API ncclResult_t ncclSend(const void* s, size_t count, ncclDataType_t t, int peer, ncclComm_t c, cudaStream_t st) {
   DFCHECK(p2pEnqueue(c, true, (void*)s, count, t, peer, st));

@@ -295,3 +295,37 @@ def test_comm_abort_ends_a_stuck_stream_collective_quickly(host_backend):
     assert not t.is_alive() and result["s"] < 5 and abort_s < 5, (result, abort_s)
     assert result["rc"] in (nv.ABORTED, nv.TIMEOUT)
     comms[1].destroy()
+
+
+def test_group_defers_collectives_and_communicator_creation(host_backend):
+    """One thread owns every rank: communicators created with ncclCommInitRank inside a group (each creation waits for
+    the others, so they must run concurrently at ncclGroupEnd), then collectives of all ranks issued inside a group
+    (on the host backend a collective is a blocking call: the group runs each communicator's calls on its own thread)."""
+    nv = host_backend
+    L = nv.lib()
+    n = 3
+    uid = nv.UniqueId()
+    C.memmove(C.addressof(uid), nv.get_unique_id(), 128)
+    handles = [C.c_void_p() for _ in range(n)]
+    nv.check(L.ncclGroupStart())
+    for r in range(n):
+        nv.check(L.ncclCommInitRank(C.byref(handles[r]), n, uid, r))
+        assert not handles[r].value                      # nothing is created before the group ends
+    nv.check(L.ncclGroupEnd())
+    assert all(h.value for h in handles)
+    ins = [np.full(5000, r + 1, np.float32) for r in range(n)]
+    outs = [np.zeros(5000, np.float32) for r in range(n)]
+    gath = [np.zeros(3 * 100, np.int32) for r in range(n)]
+    parts = [np.full(100, 10 * (r + 1), np.int32) for r in range(n)]
+    for rep in range(2):
+        nv.check(L.ncclGroupStart())
+        for r in range(n):
+            nv.check(L.ncclAllReduce(C.c_void_p(ins[r].ctypes.data), C.c_void_p(outs[r].ctypes.data), 5000, nv.FLOAT32, nv.SUM, handles[r], None))
+            nv.check(L.ncclAllGather(C.c_void_p(parts[r].ctypes.data), C.c_void_p(gath[r].ctypes.data), 100, nv.INT32, handles[r], None))
+        assert np.all(outs[0] == 0) or rep > 0               # recorded, not run
+        nv.check(L.ncclGroupEnd())
+        for r in range(n):
+            assert np.all(outs[r] == 6)
+            assert np.all(gath[r].reshape(3, 100) == np.array([10, 20, 30], np.int32)[:, None])
+    for h in handles:
+        nv.check(L.ncclCommDestroy(h))
