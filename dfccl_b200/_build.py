@@ -29,7 +29,7 @@ SOURCES = [
     "src/device/datapath.cu", "src/daemon/daemon.cu", "src/daemon/standalone.cu", "src/daemon/daemon_host.cu",
     "src/comm/comm.cu",
     "src/api/nccl_api.cu", "src/api/p2p.cu", "src/api/ofccl_api.cu", "src/api/debug_api.cu",
-    "src/ops/optim.cu", "src/api/noalloc.cu", "src/api/probe.cu", "src/gemm/tcgen05_gemm.cu",
+    "src/ops/optim.cu", "src/api/noalloc.cu", "src/api/probe.cu", "src/gemm/tcgen05_gemm.cu", "src/gemm/tcgen05_gemm_pair.cu",
 ]
 
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]

@@ -1,6 +1,7 @@
 // Internal interface of the tensor-core GEMM translation unit: the argument block of its communication-fused forms
 // and the launcher, for the rank context (registered tensor-parallel operators) and the C entry points.
 #pragma once
+#include <cuda.h>
 #include <cuda_bf16.h>
 #include <stdint.h>
 #include "dfccl.h"
@@ -38,6 +39,12 @@ struct FusedArgs {
 // stored with the contraction index slow (A as [K, M], B as [K, N], row-major) and read by the tensor cores as it is.
 ncclResult_t gemmLaunch(const void* A, const void* B, void* C, int M, int N, int K, const FusedArgs* f, cudaStream_t stream,
                         int aMn = 0, int bMn = 0);
+// The CTA-pair kernel (cta_group::2, tiles of 256 x 256) for plain GEMMs whose sizes allow it.
+bool gemmPairEligible(int M, int N, int K);
+ncclResult_t gemmPairLaunch(const void* A, const void* B, void* C, int M, int N, int K, cudaStream_t stream, int aMn, int bMn,
+                            uint32_t* errDev, uint32_t* errHost);
+// Cached tensor map of a row-major bf16 matrix [rows, cols] cut into boxes of boxRows x 64 columns, 128-byte swizzle.
+ncclResult_t gemmMakeMap(CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols, uint32_t boxRows);
 // True when a kernel of the current device gave up on a bounded wait (pinned word, no device access).
 bool gemmGaveUp();
 // SMs the fused launches leave to a co-resident persistent kernel: raised to at least `n`.

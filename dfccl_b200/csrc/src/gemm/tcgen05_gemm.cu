@@ -483,6 +483,9 @@ ncclResult_t launch(const void* A, const void* B, void* C, int M, int N, int K, 
   if (((uintptr_t)A | (uintptr_t)B | (uintptr_t)C) & 15) return ncclInvalidArgument;
   const ErrWords ew = errWords();
   if (*ew.host) { DF_WARN("an earlier tensor-core kernel on this device gave up on a bounded wait; call dfcclGemmCheck to clear"); return dfcclTimeout; }
+  // plain products whose sizes allow it run on CTA pairs (tiles of 256 x 256, half the shared-memory traffic per FLOP)
+  if ((!f || f->mode == 0 || f->nranks <= 1) && gemmPairEligible(M, N, K) && paramI64("GEMM_PAIR", 1) != 0)
+    return gemmPairLaunch(A, B, C, M, N, K, stream, aMn, bMn, ew.dev, (uint32_t*)ew.host);
   CUtensorMap ma, mb;
   // K-major operand [rows, K]: boxes of [tile rows] x 64 K-columns; MN-major operand [K, cols]: boxes of 64 K-rows x 64 columns
   if (!aMn) DFCHECK(makeMap(&ma, A, (uint64_t)M, (uint64_t)K, BM)); else DFCHECK(makeMap(&ma, A, (uint64_t)K, (uint64_t)M, BK));
@@ -511,6 +514,7 @@ ncclResult_t launch(const void* A, const void* B, void* C, int M, int N, int K, 
 
 }  // namespace
 
+ncclResult_t gemmMakeMap(CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols, uint32_t boxRows) { return makeMap(m, base, rows, cols, boxRows); }
 ncclResult_t gemmLaunch(const void* A, const void* B, void* C, int M, int N, int K, const FusedArgs* f, cudaStream_t stream, int aMn, int bMn) {
   return launch(A, B, C, M, N, K, f, stream, aMn, bMn);
 }
