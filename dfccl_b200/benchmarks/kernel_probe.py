@@ -124,6 +124,23 @@ def main(argv=None):
     torch.cuda.synchronize()
     us = e0.elapsed_time(e1) * 1e3 / a.iters
     out["fused_sgd"] = {"us": us, "gbs": (3 * 4 + 2 * 4 + 2) * m / us / 1e3}
+    mom2 = torch.zeros(m, device="cuda")
+
+    def adamw(step=[0]):
+        step[0] += 1
+        nv.check(L.dfcclFusedAdamWStep(master.data_ptr(), grad.data_ptr(), mom.data_ptr(), mom2.data_ptr(), par.data_ptr(), m,
+                                       nv.BFLOAT16, 1e-3, 0.9, 0.999, 1e-8, 0.01, step[0], st))
+    for _ in range(3):
+        adamw()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(a.iters):
+        adamw()
+    e1.record()
+    torch.cuda.synchronize()
+    us = e0.elapsed_time(e1) * 1e3 / a.iters
+    out["fused_adamw"] = {"us": us, "gbs": (4 * 4 + 3 * 4 + 2) * m / us / 1e3}     # reads master, grad, m, v; writes master, m, v (fp32) + bf16 param
     print(json.dumps(out))
     comm.destroy()
 

@@ -29,6 +29,8 @@ ncclResult_t dfcclGemmFused(const void* A, const void* B, void* C, int M, int N,
 size_t dfcclGemmFusedArgsSize(void);
 /* Reads and clears the "a bounded wait ran out" word of this device's GEMM kernels. */
 ncclResult_t dfcclGemmCheck(int* failed);
+// CTA pairs of the cta_group::2 GEMM kernel that can be resident together on the current device.
+ncclResult_t dfcclGemmPairResident(int* pairs);
 /* SMs the fused launches leave free for a persistent kernel that runs beside them (the daemon's blocks). */
 ncclResult_t dfcclGemmReserveSms(int n);
 
@@ -68,6 +70,9 @@ ncclResult_t dfcclTunerChoose(int kind, size_t bytes, int nranks, int maxBlocks,
 double dfcclTunerPredictUs(int kind, int algo, size_t bytes, int nranks, int nBlocks);
 const char* dfcclLastError(void);
 ncclResult_t dfcclHeapPeerBase(ncclComm_t comm, int peer, void** base);
+/* Transport the members selected together: 0 peer memory, 1 heap in registered host shared memory (GPUs of one host
+ * without peer access, or NCCL_P2P_DISABLE=1), 2 host-staged over the network transport. */
+ncclResult_t dfcclCommTransport(ncclComm_t comm, int* kind);
 
 #ifdef __cplusplus
 }

@@ -41,6 +41,14 @@ DF_API void dfcclLogReset(void) { logReset(); }
 DF_API const char* dfcclLastError(void) { return lastError(); }
 DF_API long long dfcclParam(const char* name, long long dflt) { return paramI64(name, dflt); }
 
+// Which transport the communicator's members selected together: 0 = peer memory (NVLink / same process), 1 = heap in
+// registered host shared memory (GPUs of one host without peer access), 2 = host-staged over the network transport.
+DF_API ncclResult_t dfcclCommTransport(ncclComm_t comm, int* kind) {
+  if (!comm || !kind) return ncclInvalidArgument;
+  *kind = comm->netMode ? 2 : comm->shmMode ? 1 : 0;
+  return ncclSuccess;
+}
+
 // Base address of `peer`'s symmetric heap as mapped in this process (own base for peer == rank):
 // a buffer at offset o of the peer's heap is at base + o here.
 DF_API ncclResult_t dfcclHeapPeerBase(ncclComm_t comm, int peer, void** base) {

@@ -384,7 +384,7 @@ DF_API ncclResult_t dfcclPrepareFusedGemm(const dfcclFusedInfo* info, ncclComm_t
     return ncclInvalidArgument;
   }
   if (comm->nranks > 8) { DF_WARN("fused operators serve communicators of up to 8 ranks"); return ncclInvalidArgument; }
-  if (comm->netMode) { DF_WARN("fused operators need peer memory: not available on communicators that go through the network path"); return ncclInvalidUsage; }
+  if (comm->netMode || comm->shmMode) { DF_WARN("fused operators need peer memory: not available on communicators that go through host memory"); return ncclInvalidUsage; }
   std::lock_guard<std::mutex> l(ctx->mu);
   if (ctx->finalized) { DF_WARN("operator %d registered after the context was finalized", collId); return ncclInvalidUsage; }
   if (collId < 0 || collId >= DF_MAX_COLLS) return ncclInvalidArgument;

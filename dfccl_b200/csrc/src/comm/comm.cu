@@ -96,59 +96,81 @@ ncclResult_t commCreate(std::shared_ptr<Bootstrap> boot, dfcclBackend_t backend,
   logSetRank(r);
   int prevDev = 0;
   if (backend == dfcclBackendCuda) { cudaGetDevice(&prevDev); CUDACHECK(cudaSetDevice(device)); }
-  if (inherit) {
-    c->heap = inherit;
-  } else if (privateHeap) {
-    size_t bytes = (size_t)paramI64("HEAP_BYTES", backend == dfcclBackendCuda ? (1ll << 30) : (64ll << 20));
-    DFCHECK(Heap::create(backend, device, bytes, &c->heap));
-    c->ownsHeap = true;
-  } else {
-    DFCHECK(processHeap(backend, device, &c->heap));
-  }
   DFCHECK(pinnedAlloc(backend, (void**)&c->ctl, sizeof(DaemonCtl)));
   boot->setAbortFlag(&c->ctl->abortFlag);
-  // flag words of the stream-ordered engine and of send / recv
-  DFCHECK(c->heap->alloc(sizeof(FlagSlot) * DF_MAX_BLOCKS * n, &c->saFlagsOff));
-  DFCHECK(c->heap->alloc(sizeof(FlagSlot) * 2 * n * 8, &c->p2pFlagsOff));   // [direction][peer][channel]
-  if (n > 1) {                        // slots of the push schedule: [2 parities][n writers][pushMaxBytes]
-    c->pushSlotBytes = (pushMaxBytes() + 511) & ~(size_t)511;
-    DFCHECK(c->heap->alloc(2 * (size_t)n * c->pushSlotBytes, &c->pushOff, false));
-  }
-  std::vector<PeerInfoMsg> all(n);
-  PeerInfoMsg& me = all[r];
-  c->heap->exportHandle(&me.heap);
-  me.saFlagsOff = c->saFlagsOff; me.p2pFlagsOff = c->p2pFlagsOff; me.pushOff = c->pushOff; me.device = device; me.backend = backend;
-  me.commHash = r == 0 ? ((uint64_t)getpid() << 32) ^ (uint64_t)(uintptr_t)c.get() ^ hostHash() : 0;
-  DFCHECK(boot->allGather(all.data(), sizeof(PeerInfoMsg)));
-  c->commHash = all[0].commHash;
   c->handles.resize(n); c->peerHeap.resize(n); c->peerSaFlagsOff.resize(n); c->peerP2pFlagsOff.resize(n); c->peerPushOff.resize(n);
   c->sendSeq.assign(n, 0); c->recvSeq.assign(n, 0);
-  // members on another host cannot be mapped: the whole communicator then goes through the network path
-  c->netMode = n > 1 && paramI64("FORCE_NET", 0) != 0;
-  for (int j = 0; j < n; ++j) if (all[j].heap.hostHash != all[r].heap.hostHash) c->netMode = true;
-  // Transport selection, first fit (role of the reference's selectTransport, src/transport.cc:25-45): peer memory when
-  // every member can map every other member's heap, else the host-staged path over the network transport (which on
-  // one host is its loopback).  The verdict is collective: one member that cannot map a peer - no peer access between
-  // the two GPUs, or P2P_DISABLE set - moves the whole communicator, because the schedules need all pairs.
-  int32_t p2pOk = (c->netMode || paramI64("P2P_DISABLE", 0) != 0) ? 0 : 1;
-  for (int j = 0; j < n; ++j) {
-    c->handles[j] = all[j].heap;
-    c->peerSaFlagsOff[j] = all[j].saFlagsOff;
-    c->peerP2pFlagsOff[j] = all[j].p2pFlagsOff;
-    c->peerPushOff[j] = all[j].pushOff;
-    c->peerHeap[j] = j == r ? c->heap->base() : nullptr;
-    if (j != r && p2pOk && c->heap->importPeer(all[j].heap, &c->peerHeap[j]) != ncclSuccess) {
-      DF_INFO(SUB_INIT, "rank %d cannot map the memory of rank %d: this communicator will not use peer memory", r, j);
-      p2pOk = 0;
+  // Transport selection, first fit (role of the reference's selectTransport, src/transport.cc:25-45, with its order
+  // P2P, SHM, NET): (1) peer memory, when every member can map every other member's heap; (2) on GPUs of one host
+  // that cannot - no peer access between two of them, or P2P_DISABLE - a heap in registered host shared memory that
+  // all of them reach over PCIe (the role of src/transport/shm.cc:58-167, without its FIFOs: the same kernels run on
+  // it); (3) the host-staged path over the network transport.  Every verdict is collective: one member that cannot map
+  // a peer moves the whole communicator, because the schedules need all pairs.
+  const bool forcedNet = n > 1 && paramI64("FORCE_NET", 0) != 0;
+  for (int attempt = 0;; ++attempt) {
+    if (attempt == 1) {
+      size_t bytes = (size_t)paramI64("SHM_HEAP_BYTES", 256ll << 20);
+      DFCHECK(Heap::create(backend, device, bytes, &c->heap, true));
+      c->ownsHeap = true;
+    } else if (inherit) {
+      c->heap = inherit;
+    } else if (privateHeap) {
+      size_t bytes = (size_t)paramI64("HEAP_BYTES", backend == dfcclBackendCuda ? (1ll << 30) : (64ll << 20));
+      DFCHECK(Heap::create(backend, device, bytes, &c->heap));
+      c->ownsHeap = true;
+    } else {
+      DFCHECK(processHeap(backend, device, &c->heap));
     }
+    // flag words of the stream-ordered engine and of send / recv
+    DFCHECK(c->heap->alloc(sizeof(FlagSlot) * DF_MAX_BLOCKS * n, &c->saFlagsOff));
+    DFCHECK(c->heap->alloc(sizeof(FlagSlot) * 2 * n * 8, &c->p2pFlagsOff));   // [direction][peer][channel]
+    if (n > 1) {                        // slots of the push schedule: [2 parities][n writers][pushMaxBytes]
+      c->pushSlotBytes = (pushMaxBytes() + 511) & ~(size_t)511;
+      DFCHECK(c->heap->alloc(2 * (size_t)n * c->pushSlotBytes, &c->pushOff, false));
+    }
+    std::vector<PeerInfoMsg> all(n);
+    PeerInfoMsg& me = all[r];
+    c->heap->exportHandle(&me.heap);
+    me.saFlagsOff = c->saFlagsOff; me.p2pFlagsOff = c->p2pFlagsOff; me.pushOff = c->pushOff; me.device = device; me.backend = backend;
+    me.commHash = r == 0 ? ((uint64_t)getpid() << 32) ^ (uint64_t)(uintptr_t)c.get() ^ hostHash() : 0;
+    DFCHECK(boot->allGather(all.data(), sizeof(PeerInfoMsg)));
+    c->commHash = all[0].commHash;
+    // members on another host cannot be mapped: the whole communicator then goes through the network path
+    bool otherHosts = false;
+    for (int j = 0; j < n; ++j) if (all[j].heap.hostHash != all[r].heap.hostHash) otherHosts = true;
+    c->netMode = forcedNet || otherHosts;
+    int32_t p2pOk = c->netMode ? 0 : (c->heap->hostShm() || paramI64("P2P_DISABLE", 0) == 0) ? 1 : 0;
+    for (int j = 0; j < n; ++j) {
+      c->handles[j] = all[j].heap;
+      c->peerSaFlagsOff[j] = all[j].saFlagsOff;
+      c->peerP2pFlagsOff[j] = all[j].p2pFlagsOff;
+      c->peerPushOff[j] = all[j].pushOff;
+      c->peerHeap[j] = j == r ? c->heap->base() : nullptr;
+      if (j != r && p2pOk && c->heap->importPeer(all[j].heap, &c->peerHeap[j]) != ncclSuccess) {
+        DF_INFO(SUB_INIT, "rank %d cannot map the memory of rank %d: this communicator will not use %s", r, j,
+                c->heap->hostShm() ? "the shared-memory heap" : "peer memory");
+        p2pOk = 0;
+      }
+    }
+    if (n > 1 && !c->netMode) {
+      std::vector<int32_t> verdicts(n, 0);
+      verdicts[r] = p2pOk;
+      DFCHECK(boot->allGather(verdicts.data(), sizeof(int32_t)));
+      for (int j = 0; j < n; ++j) if (!verdicts[j]) c->netMode = true;
+      if (c->netMode) for (int j = 0; j < n; ++j) if (j != r) c->peerHeap[j] = nullptr;
+    }
+    if (!c->netMode) { c->shmMode = c->heap->hostShm(); break; }
+    // second choice: the same engine on a heap in registered host shared memory (GPUs of one host only)
+    const bool tryShm = attempt == 0 && !forcedNet && !otherHosts && backend == dfcclBackendCuda && !c->heap->hostShm() &&
+                        !inherit && paramI64("SHM_DISABLE", 0) == 0;
+    if (!tryShm) break;
+    (void)c->heap->free(c->saFlagsOff); (void)c->heap->free(c->p2pFlagsOff);
+    if (n > 1) (void)c->heap->free(c->pushOff);
+    if (c->ownsHeap) { delete c->heap; c->ownsHeap = false; }
+    c->heap = nullptr;
   }
-  if (n > 1 && !c->netMode) {
-    std::vector<int32_t> verdicts(n, 0);
-    verdicts[r] = p2pOk;
-    DFCHECK(boot->allGather(verdicts.data(), sizeof(int32_t)));
-    for (int j = 0; j < n; ++j) if (!verdicts[j]) c->netMode = true;
-    if (c->netMode) for (int j = 0; j < n; ++j) if (j != r) c->peerHeap[j] = nullptr;
-  }
+  if (c->shmMode)
+    DF_INFO(SUB_INIT, "communicator of %d ranks cannot use peer memory (no peer access or P2P_DISABLE): its heap lives in registered host shared memory, %zu MiB", n, c->heap->bytes() >> 20);
   if (c->netMode) {
     DFCHECK(NetRing::create(boot.get(), &c->netRing));
     DF_INFO(SUB_INIT | SUB_NET, "communicator of %d ranks cannot use peer memory (members on other hosts, no peer access, P2P_DISABLE or FORCE_NET): collectives are staged through host memory over '%s'", n, netGet()->name);
@@ -167,7 +189,7 @@ ncclResult_t commCreate(std::shared_ptr<Bootstrap> boot, dfcclBackend_t backend,
   DFCHECK(devUpload(backend, c->saRd, &rd, sizeof(RankDev)));
   DFCHECK(boot->barrier());          // every member has mapped everything before anyone uses it
   // switch multicast is opt-in: binding memory to a multicast object ties the members' fates together
-  if (n > 1 && !c->netMode && (!loop || backend != dfcclBackendCuda) && paramI64("NVLS", 0)) DFCHECK(nvlsArenaCreate(c.get(), (size_t)paramI64("NVLS_BYTES", 512ll << 20), &c->nvls));
+  if (n > 1 && !c->netMode && !c->shmMode && (!loop || backend != dfcclBackendCuda) && paramI64("NVLS", 0)) DFCHECK(nvlsArenaCreate(c.get(), (size_t)paramI64("NVLS_BYTES", 512ll << 20), &c->nvls));
   if (backend == dfcclBackendCuda) cudaSetDevice(prevDev);
   DF_INFO(SUB_INIT, "comm %llx rank %d/%d device %d backend %s heap %zu MiB", (unsigned long long)c->commHash, r, n, device,
           backend == dfcclBackendCuda ? "cuda" : "host", c->heap->bytes() >> 20);

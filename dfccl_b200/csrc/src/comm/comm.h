@@ -68,6 +68,9 @@ struct ncclComm {
   // network mode: members that cannot map each other's memory (other hosts, or DFCCL_FORCE_NET=1);
   // collectives are staged through host memory and run over rings of network connections
   bool netMode = false;
+  // bounce mode: GPUs of one host without peer access; the heap is registered host shared memory that every member
+  // maps, and the schedules run on it unchanged (no multicast arena, no fused tensor-core operators)
+  bool shmMode = false;
   std::unique_ptr<dfccl::NetRing> netRing;     // ring of the stream-ordered entry points
 };
 

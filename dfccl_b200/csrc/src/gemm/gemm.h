@@ -41,6 +41,7 @@ ncclResult_t gemmLaunch(const void* A, const void* B, void* C, int M, int N, int
                         int aMn = 0, int bMn = 0);
 // The CTA-pair kernel (cta_group::2, tiles of 256 x 256) for plain GEMMs whose sizes allow it.
 bool gemmPairEligible(int M, int N, int K);
+int gemmPairResident();
 ncclResult_t gemmPairLaunch(const void* A, const void* B, void* C, int M, int N, int K, cudaStream_t stream, int aMn, int bMn,
                             uint32_t* errDev, uint32_t* errHost);
 // Cached tensor map of a row-major bf16 matrix [rows, cols] cut into boxes of boxRows x 64 columns, 128-byte swizzle.

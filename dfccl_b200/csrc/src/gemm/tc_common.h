@@ -202,6 +202,18 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
+// Tile visiting order of a persistent GEMM: groups of `groupM` row tiles, row index fastest inside a group.  The
+// CTAs that work at the same time then share a block of about groupM row tiles x (CTAs / groupM) column tiles, whose
+// operands fit in L2, instead of a couple of row tiles times EVERY column tile (all of B per wave).
+__device__ __forceinline__ void raster_tile(int t, int mTiles, int nTiles, int groupM, int& mt, int& nt) {
+  const int perGroup = groupM * nTiles;
+  const int grp = t / perGroup, first = grp * groupM;
+  const int gsz = min(groupM, mTiles - first);
+  const int r = t - grp * perGroup;
+  mt = first + r % gsz;
+  nt = r / gsz;
+}
+
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&h);

@@ -45,6 +45,7 @@ constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 4 * EPI_WARP_BYTES + 1024 /*al
 struct GemmArgs {
   __nv_bfloat16* C;
   int M, N, K, ldc;
+  int groupM;                       // plain GEMM: row tiles per rasterisation group (0 = row-major tile order, the fused forms)
   int aMn, bMn;                     // operand stored with the contraction index slow: A as [K, M], B as [K, N] (row-major)
   uint32_t* err;                    // device word: non-zero = a bounded wait ran out (later launches return at once)
   uint64_t waitNs;                  // limit of every wait on a word another GPU or CTA writes
@@ -127,6 +128,12 @@ __device__ __forceinline__ int orderedMTile(const FusedArgs& f, int i, int mTile
   return owner * per + i % per;
 }
 
+__device__ __forceinline__ void tileCoord(const GemmArgs& g, int t, int mTiles, int nTiles, int& mt, int& nt) {
+  if (g.groupM > 0) { raster_tile(t, mTiles, nTiles, g.groupM, mt, nt); return; }
+  mt = orderedMTile(g.f, t / nTiles, mTiles);
+  nt = t % nTiles;
+}
+
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 dfcclGemmKernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB, const GemmArgs g) {
   extern __shared__ uint8_t smemRaw[];
@@ -175,7 +182,8 @@ dfcclGemmKernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
       uint32_t phase = 0;
       bool ok = true;
       for (int t = blockIdx.x; t < numTiles && ok; t += gridDim.x) {
-        const int mt = orderedMTile(f, t / nTiles, mTiles), nt = t % nTiles;
+        int mt, nt;
+        tileCoord(g, t, mTiles, nTiles, mt, nt);
         if (f.mode == 1 && f.nranks > 1 && mt / (f.rowsPerRank / BM) != f.rank) {
           // this row block comes from a peer: wait until the communication warps have placed it
           ok = wait_flag32(&f.blockReady[mt], (uint32_t)epoch * GATHER_PIECES, giveUp, false, g.waitNs);
@@ -236,7 +244,8 @@ dfcclGemmKernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
     const int quarter = warp & 3;                     // the 32 TMEM lanes this warp may read
     int it = 0;
     for (int t = blockIdx.x; t < numTiles; t += gridDim.x, ++it) {
-      const int mt = orderedMTile(f, t / nTiles, mTiles), nt = t % nTiles;
+      int mt, nt;
+      tileCoord(g, t, mTiles, nTiles, mt, nt);
       const int ab = it & 1;
       if (!mbar_wait(&accFull[ab], (it >> 1) & 1, giveUp)) break;
       tc_fence_after();
@@ -498,6 +507,7 @@ ncclResult_t launch(const void* A, const void* B, void* C, int M, int N, int K, 
   g.aMn = aMn ? 1 : 0; g.bMn = bMn ? 1 : 0;
   { int64_t ms = paramI64("WAIT_TIMEOUT_MS", 30000); g.waitNs = (uint64_t)(ms > 0 ? ms : 30000) * 1000000ull; }
   if (f) g.f = *f; else { g.f.nranks = 1; g.f.mode = 0; }
+  if (g.f.mode == 0 || g.f.nranks <= 1) { int64_t gm = paramI64("GEMM_RASTER_GROUP", 8); g.groupM = (int)(gm < 1 ? 1 : gm > 64 ? 64 : 2 * gm); }
   int dev = 0, sms = 148;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
@@ -539,6 +549,13 @@ DF_API ncclResult_t dfcclGemmBf16(const void* A, const void* B, void* C, int M, 
 // (B) then need no transposed copy: the tensor cores read MN-major operands as they are.
 DF_API ncclResult_t dfcclGemmBf16Ex(const void* A, const void* B, void* C, int M, int N, int K, int aTransposed, int bTransposed, cudaStream_t stream) {
   return launch(A, B, C, M, N, K, nullptr, stream, aTransposed, bTransposed);
+}
+
+// CTA pairs of the cta_group::2 kernel that can be resident together on the current device.
+DF_API ncclResult_t dfcclGemmPairResident(int* pairs) {
+  if (!pairs) return ncclInvalidArgument;
+  *pairs = gemmPairResident();
+  return ncclSuccess;
 }
 
 // SMs the fused launches leave free for a persistent kernel that runs beside them (e.g. the daemon's blocks).

@@ -40,6 +40,7 @@ struct PairArgs {
   __nv_bfloat16* C;
   int M, N, K, ldc;
   int aMn, bMn;
+  int groupM;                       // row tiles per rasterisation group
   uint32_t* err;
   uint32_t* errHost;
 };
@@ -86,7 +87,8 @@ dfcclGemmPairKernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
       uint32_t phase = 0;
       bool ok = true;
       for (int t = pair; t < numTiles && ok; t += numPairs) {
-        const int mt = t / nTiles, nt = t % nTiles;
+        int mt, nt;
+        raster_tile(t, mTiles, nTiles, g.groupM, mt, nt);
         const int rowA = mt * PM + (int)cr * HALF, rowB = nt * PN + (int)cr * HALF;
         for (int kb = 0; kb < kBlocks; ++kb) {
           if (!mbar_wait(&emptyBar[stage], phase ^ 1, giveUp, WAIT_NS)) { ok = false; break; }
@@ -137,7 +139,8 @@ dfcclGemmPairKernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
     const uint32_t accEmptyLeader0 = mapa_u32(smem_u32(&accEmpty[0]), 0), accEmptyLeader1 = mapa_u32(smem_u32(&accEmpty[1]), 0);
     int it = 0;
     for (int t = pair; t < numTiles; t += numPairs, ++it) {
-      const int mt = t / nTiles, nt = t % nTiles;
+      int mt, nt;
+      raster_tile(t, mTiles, nTiles, g.groupM, mt, nt);
       const int ab = it & 1;
       if (!mbar_wait(&accFull[ab], (it >> 1) & 1, giveUp, WAIT_NS)) break;
       tc_fence_after();
@@ -189,36 +192,48 @@ dfcclGemmPairKernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
 
 bool gemmPairEligible(int M, int N, int K) { return M > 0 && N > 0 && K > 0 && M % PM == 0 && N % PN == 0 && K % BK == 0; }
 
+namespace {
+int maxResidentPairs(int dev, int sms) {
+  // pairs that can be resident together (a GPC with an odd number of free SMs leaves one unpaired)
+  static int maxPairs[64];
+  static std::mutex mu;
+  std::lock_guard<std::mutex> l(mu);
+  if (!maxPairs[dev & 63]) {
+    static std::once_flag once;
+    std::call_once(once, [] { cudaFuncSetAttribute(dfcclGemmPairKernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES); });
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = dim3(sms & ~1); cfg.blockDim = dim3(NUM_THREADS); cfg.dynamicSmemBytes = SMEM_BYTES;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, dfcclGemmPairKernel, &cfg) != cudaSuccess || n <= 0) { (void)cudaGetLastError(); n = sms / 2; }
+    maxPairs[dev & 63] = std::min(n, sms / 2);
+  }
+  return maxPairs[dev & 63];
+}
+}  // namespace
+
+int gemmPairResident() {
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  return maxResidentPairs(dev, sms);
+}
+
 ncclResult_t gemmPairLaunch(const void* A, const void* B, void* C, int M, int N, int K, cudaStream_t stream, int aMn, int bMn,
                             uint32_t* errDev, uint32_t* errHost) {
   CUtensorMap ma, mb;
   if (!aMn) DFCHECK(gemmMakeMap(&ma, A, (uint64_t)M, (uint64_t)K, HALF)); else DFCHECK(gemmMakeMap(&ma, A, (uint64_t)K, (uint64_t)M, BK));
   if (!bMn) DFCHECK(gemmMakeMap(&mb, B, (uint64_t)N, (uint64_t)K, HALF)); else DFCHECK(gemmMakeMap(&mb, B, (uint64_t)K, (uint64_t)N, BK));
-  static std::once_flag once;
-  std::call_once(once, [] { cudaFuncSetAttribute(dfcclGemmPairKernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES); });
   PairArgs g;
   memset(&g, 0, sizeof(g));
   g.C = (__nv_bfloat16*)C; g.M = M; g.N = N; g.K = K; g.ldc = N; g.aMn = aMn ? 1 : 0; g.bMn = bMn ? 1 : 0;
   g.err = errDev; g.errHost = errHost;
+  { int64_t gm = paramI64("GEMM_RASTER_GROUP", 8); g.groupM = (int)(gm < 1 ? 1 : gm > 64 ? 64 : gm); }
   int dev = 0, sms = 148;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  // pairs that can be resident together (a GPC with an odd number of free SMs leaves one unpaired)
-  static int maxPairs[64];
-  static std::mutex mu;
-  {
-    std::lock_guard<std::mutex> l(mu);
-    if (!maxPairs[dev & 63]) {
-      cudaLaunchConfig_t cfg;
-      memset(&cfg, 0, sizeof(cfg));
-      cfg.gridDim = dim3(sms & ~1); cfg.blockDim = dim3(NUM_THREADS); cfg.dynamicSmemBytes = SMEM_BYTES;
-      int n = 0;
-      if (cudaOccupancyMaxActiveClusters(&n, dfcclGemmPairKernel, &cfg) != cudaSuccess || n <= 0) { (void)cudaGetLastError(); n = sms / 2; }
-      maxPairs[dev & 63] = std::min(n, sms / 2);
-    }
-  }
   const int tiles = (M / PM) * (N / PN);
-  const int pairs = std::min(tiles, maxPairs[dev & 63]);
+  const int pairs = std::min(tiles, maxResidentPairs(dev, sms));
   dfcclGemmPairKernel<<<2 * pairs, NUM_THREADS, SMEM_BYTES, stream>>>(ma, mb, g);
   CUDACHECK(cudaGetLastError());
   return ncclSuccess;

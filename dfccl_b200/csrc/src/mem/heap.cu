@@ -69,12 +69,13 @@ static void reapStaleSegments() {
   });
 }
 
-ncclResult_t Heap::create(dfcclBackend_t backend, int device, size_t bytes, Heap** out) {
+ncclResult_t Heap::create(dfcclBackend_t backend, int device, size_t bytes, Heap** out, bool hostShm) {
   Heap* h = new Heap();
   h->backend_ = backend; h->device_ = device; h->heapId_ = g_heapSeq++;
+  h->hostShm_ = hostShm && backend == dfcclBackendCuda;
   bytes = (bytes + (2u << 20) - 1) & ~(size_t)((2u << 20) - 1);
   h->bytes_ = bytes;
-  if (backend == dfcclBackendCuda) {
+  if (backend == dfcclBackendCuda && !h->hostShm_) {
     int prev = 0;
     cudaGetDevice(&prev);
     cudaError_t e = cudaSetDevice(device);
@@ -108,10 +109,20 @@ ncclResult_t Heap::create(dfcclBackend_t backend, int device, size_t bytes, Heap
     h->base_ = (char*)p;
     h->shmName_ = name;
     rememberName(h->shmName_);
+    if (h->hostShm_) {
+      // the GPUs read and write the segment in place: pin it and map it into the CUDA address space (same address)
+      cudaError_t e = cudaHostRegister(p, bytes, cudaHostRegisterPortable | cudaHostRegisterMapped);
+      if (e != cudaSuccess) {
+        DF_WARN("symmetric heap in shared memory: cudaHostRegister(%zu MiB) failed: %s", bytes >> 20, cudaGetErrorString(e));
+        (void)cudaGetLastError();
+        delete h;
+        return ncclUnhandledCudaError;
+      }
+    }
   }
   h->free_[0] = bytes;
   DF_INFO(SUB_ALLOC, "symmetric heap %d: %zu MiB at %p (%s)", h->heapId_, bytes >> 20, (void*)h->base_,
-          backend == dfcclBackendCuda ? "cuda" : "host");
+          backend != dfcclBackendCuda ? "host" : h->hostShm_ ? "cuda, in registered shared memory" : "cuda");
   *out = h;
   return ncclSuccess;
 }
@@ -119,12 +130,16 @@ ncclResult_t Heap::create(dfcclBackend_t backend, int device, size_t bytes, Heap
 Heap::~Heap() {
   for (auto& kv : imports_) {
     if (!kv.second.ipc) continue;
-    if (backend_ == dfcclBackendCuda) cudaIpcCloseMemHandle(kv.second.base);
+    if (kv.second.registered) { cudaHostUnregister(kv.second.base); (void)cudaGetLastError(); }
+    if (backend_ == dfcclBackendCuda && !kv.second.registered) cudaIpcCloseMemHandle(kv.second.base);
     else munmap(kv.second.base, kv.second.bytes);
   }
   if (!base_) return;
-  if (backend_ == dfcclBackendCuda) { cudaFree(base_); (void)cudaGetLastError(); }
-  else { munmap(base_, bytes_); shm_unlink(shmName_.c_str()); forgetName(shmName_); }
+  if (backend_ == dfcclBackendCuda && !hostShm_) { cudaFree(base_); (void)cudaGetLastError(); }
+  else {
+    if (hostShm_) { cudaHostUnregister(base_); (void)cudaGetLastError(); }
+    munmap(base_, bytes_); shm_unlink(shmName_.c_str()); forgetName(shmName_);
+  }
 }
 
 ncclResult_t Heap::alloc(size_t bytes, uint64_t* off, bool zero) {
@@ -140,7 +155,7 @@ ncclResult_t Heap::alloc(size_t bytes, uint64_t* off, bool zero) {
     used_ += bytes;
     *off = o;
     if (zero) {
-      if (backend_ == dfcclBackendCuda) {
+      if (backend_ == dfcclBackendCuda && !hostShm_) {
         int prev = 0;
         cudaGetDevice(&prev);
         cudaSetDevice(device_);
@@ -178,7 +193,8 @@ void Heap::exportHandle(HeapHandle* h) const {
   memset(h, 0, sizeof(*h));
   h->hostHash = hostHash(); h->pid = (int32_t)getpid(); h->device = device_; h->backend = backend_;
   h->heapId = heapId_; h->bytes = bytes_; h->base = (uint64_t)(uintptr_t)base_;
-  if (backend_ == dfcclBackendCuda) {
+  h->hostShm = hostShm_ ? 1 : 0;
+  if (backend_ == dfcclBackendCuda && !hostShm_) {
     cudaIpcMemHandle_t ipc;
     if (cudaIpcGetMemHandle(&ipc, base_) == cudaSuccess) memcpy(h->blob, &ipc, sizeof(ipc));
     else (void)cudaGetLastError();                 // single-process use still works through `base`
@@ -189,6 +205,7 @@ void Heap::exportHandle(HeapHandle* h) const {
 
 ncclResult_t Heap::importPeer(const HeapHandle& h, char** base) {
   if (h.backend != (int32_t)backend_) { DF_WARN("peer uses another backend"); return ncclInvalidUsage; }
+  if ((h.hostShm != 0) != hostShm_) { DF_WARN("peer's heap is of another kind (device memory against shared memory)"); return ncclInvalidUsage; }
   if (h.hostHash != hostHash()) {
     DF_WARN("peer is on another host: the direct-access engine needs every rank of a communicator on one NVLink domain");
     return ncclInvalidUsage;
@@ -198,10 +215,10 @@ ncclResult_t Heap::importPeer(const HeapHandle& h, char** base) {
   std::lock_guard<std::mutex> l(mu_);
   auto it = imports_.find(key);
   if (it != imports_.end()) { *base = it->second.base; return ncclSuccess; }
-  Import imp{nullptr, false, (size_t)h.bytes};
+  Import imp{nullptr, false, (size_t)h.bytes, false};
   if (h.pid == (int32_t)getpid()) {
-    imp.base = (char*)(uintptr_t)h.base;
-    if (backend_ == dfcclBackendCuda && h.device != device_) {
+    imp.base = (char*)(uintptr_t)h.base;            // (a registered segment is portable: every device of the process sees it)
+    if (backend_ == dfcclBackendCuda && !hostShm_ && h.device != device_) {
       int prev = 0, can = 0;
       cudaGetDevice(&prev);
       CUDACHECK(cudaDeviceCanAccessPeer(&can, device_, h.device));
@@ -212,7 +229,7 @@ ncclResult_t Heap::importPeer(const HeapHandle& h, char** base) {
       if (e != cudaSuccess && e != cudaErrorPeerAccessAlreadyEnabled) { DF_WARN("enable peer access: %s", cudaGetErrorString(e)); return ncclUnhandledCudaError; }
       (void)cudaGetLastError();
     }
-  } else if (backend_ == dfcclBackendCuda) {
+  } else if (backend_ == dfcclBackendCuda && !hostShm_) {
     cudaIpcMemHandle_t ipc;
     memcpy(&ipc, h.blob, sizeof(ipc));
     int prev = 0;
@@ -230,6 +247,15 @@ ncclResult_t Heap::importPeer(const HeapHandle& h, char** base) {
     close(fd);
     if (p == MAP_FAILED) { DF_WARN("mmap(%s): %s", h.blob, strerror(errno)); return ncclSystemError; }
     imp.base = (char*)p; imp.ipc = true;
+    if (hostShm_) {
+      int prev = 0;
+      cudaGetDevice(&prev);
+      cudaSetDevice(device_);
+      cudaError_t e = cudaHostRegister(p, h.bytes, cudaHostRegisterPortable | cudaHostRegisterMapped);
+      cudaSetDevice(prev);
+      if (e != cudaSuccess) { DF_WARN("cudaHostRegister of the segment of pid %d: %s", h.pid, cudaGetErrorString(e)); (void)cudaGetLastError(); munmap(p, h.bytes); return ncclUnhandledCudaError; }
+      imp.registered = true;
+    }
   }
   imports_[key] = imp;
   *base = imp.base;

@@ -7,6 +7,9 @@
 //   cuda backend : cudaMalloc + cudaIpcGetMemHandle / cudaIpcOpenMemHandle across
 //                  processes, plain pointers (+ peer access) inside a process
 //   host backend : POSIX shared memory, mmap'd by peers (threads or processes)
+//   cuda backend, bounce mode : for GPUs of one host that cannot map each other's memory (no peer access, or
+//                  P2P_DISABLE): the heap itself lives in POSIX shared memory registered with CUDA, so every
+//                  GPU reaches every member's heap through host memory at PCIe speed and the same kernels run
 #pragma once
 #include <cstdint>
 #include <map>
@@ -23,6 +26,8 @@ struct HeapHandle {              // exchanged through the bootstrap, fixed size
   int32_t device;
   int32_t backend;
   int32_t heapId;                // distinguishes several heaps of one process (loopback ranks)
+  int32_t hostShm;               // cuda backend: the heap is a registered shared-memory segment (blob = its name)
+  int32_t pad;
   uint64_t bytes;
   uint64_t base;                 // address in the owning process
   char blob[64];                 // cudaIpcMemHandle_t or shm name
@@ -30,7 +35,8 @@ struct HeapHandle {              // exchanged through the bootstrap, fixed size
 
 class Heap {
  public:
-  static ncclResult_t create(dfcclBackend_t backend, int device, size_t bytes, Heap** out);
+  static ncclResult_t create(dfcclBackend_t backend, int device, size_t bytes, Heap** out, bool hostShm = false);
+  bool hostShm() const { return hostShm_; }
   ~Heap();
   char* base() const { return base_; }
   size_t bytes() const { return bytes_; }
@@ -52,13 +58,14 @@ class Heap {
   Heap() = default;
   dfcclBackend_t backend_ = dfcclBackendCuda;
   int device_ = 0, heapId_ = 0;
+  bool hostShm_ = false;         // cuda backend only: memory is host shared memory registered with CUDA
   char* base_ = nullptr;
   size_t bytes_ = 0, used_ = 0;
   std::string shmName_;
   std::mutex mu_;
   std::map<uint64_t, uint64_t> free_;     // offset -> length
   std::map<uint64_t, uint64_t> live_;     // offset -> length
-  struct Import { char* base; bool ipc; size_t bytes; };
+  struct Import { char* base; bool ipc; size_t bytes; bool registered; };
   std::map<std::string, Import> imports_;
 };
 

@@ -127,8 +127,10 @@ def lib() -> C.CDLL:
             "dfcclGemmBf16": [vp, vp, vp, i, i, i, vp],
             "dfcclGemmBf16Ex": [vp, vp, vp, i, i, i, i, i, vp],
             "dfcclGemmCheck": [C.POINTER(i)],
+            "dfcclGemmPairResident": [C.POINTER(i)],
             "dfcclGemmFused": [vp, vp, vp, i, i, i, vp, sz, vp],
             "dfcclHeapPeerBase": [vp, i, C.POINTER(vp)],
+            "dfcclCommTransport": [vp, C.POINTER(i)],
             "dfcclProbePeerCopy": [vp, i, sz, i, i, i, i, i, C.POINTER(C.c_double)],
             "dfcclProbeFlagRoundTrip": [vp, i, i, C.POINTER(C.c_double)],
             "dfcclProbeMemoryOps": [i, C.POINTER(C.c_uint64)],
@@ -248,6 +250,12 @@ class Comm:
         uc, mc, b, u = C.c_void_p(), C.c_void_p(), C.c_size_t(), C.c_size_t()
         check(lib().dfcclNvlsInfo(self.handle, C.byref(uc), C.byref(mc), C.byref(b), C.byref(u)), "dfcclNvlsInfo")
         return uc.value, mc.value, b.value, u.value
+
+    def transport(self) -> str:
+        """Transport the members selected together: 'peer' memory, 'shm' (heap in registered host shared memory) or 'net'."""
+        k = C.c_int()
+        check(lib().dfcclCommTransport(self.handle, C.byref(k)), "dfcclCommTransport")
+        return ("peer", "shm", "net")[k.value]
 
     def peer_base(self, peer: int) -> int:
         b = C.c_void_p()

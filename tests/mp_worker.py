@@ -107,6 +107,7 @@ def scenario_daemon(nv, comm, rank, world, backend):
     import time
     time.sleep(0.05)
     st = ctx.stats()
+    st["transport"] = comm.transport()
     ctx.destroy()
     return st
 

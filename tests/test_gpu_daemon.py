@@ -36,7 +36,7 @@ TORCH_OF = {"FLOAT32": torch.float32, "BFLOAT16": torch.bfloat16, "FLOAT16": tor
 
 
 def _loopback_case(nv, kind, nranks, count, dt_name, *, op="SUM", root=0, out_name=None, scale=1.0, algo=0, heap=True,
-                   in_place=False, iters=2, blocks=None, skew=(0, 0)):
+                   in_place=False, iters=2, blocks=None, skew=(0, 0), transport="peer"):
     torch.cuda.set_device(0)
     dt, out_dt = TORCH_OF[dt_name], TORCH_OF[out_name or dt_name]
     kid = getattr(nv, kind.upper())
@@ -52,6 +52,7 @@ def _loopback_case(nv, kind, nranks, count, dt_name, *, op="SUM", root=0, out_na
     old = {k: os.environ.get(k) for k in env}
     os.environ.update(env)
     comms = nv.Comm.init_loopback(nranks, 0)
+    assert all(c.transport() == (transport if nranks > 1 else "peer") for c in comms), [c.transport() for c in comms]
     results = {}
 
     def body(r):
@@ -157,6 +158,27 @@ def test_loopback_buffers_off_the_16_byte_grid(nv, kind, dt, count, skew):
     do the same to every kind: the data path then reads its sources as shifted packs (two aligned loads and a
     funnel shift, the upper pack by warp shuffle) and must give exactly the aligned result."""
     _loopback_case(nv, kind, 4, count, dt, root=1, iters=1, skew=skew, blocks=4)
+
+
+@pytest.mark.parametrize("kind", ["allreduce", "allgather", "reducescatter", "broadcast"])
+@pytest.mark.parametrize("heap", [True, False])
+def test_loopback_on_the_shared_memory_heap(nv, kind, heap, monkeypatch):
+    """GPUs of one host that may not map one another's memory (here: NCCL_P2P_DISABLE=1, the reference's knob) select
+    the second transport together: a symmetric heap in registered host shared memory.  The same daemon kernel and
+    schedules then run with every flag and every peer access going through host memory; buffers outside the heap are
+    staged into it as on the first transport."""
+    monkeypatch.setenv("NCCL_P2P_DISABLE", "1")
+    _loopback_case(nv, kind, 3, 70001, "FLOAT32", root=2, iters=2, blocks=2, heap=heap, transport="shm")
+
+
+def test_shared_memory_heap_can_be_refused(nv, monkeypatch):
+    """NCCL_SHM_DISABLE=1 on top leaves the third transport: host-staged collectives over the network transport."""
+    monkeypatch.setenv("NCCL_P2P_DISABLE", "1")
+    monkeypatch.setenv("NCCL_SHM_DISABLE", "1")
+    comms = nv.Comm.init_loopback(2, 0)
+    assert [c.transport() for c in comms] == ["net", "net"]
+    for c in comms:
+        c.destroy()
 
 
 def test_loopback_eight_ranks_large(nv):

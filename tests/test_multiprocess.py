@@ -8,7 +8,7 @@ import mp_worker
 @pytest.mark.parametrize("world", [2, 4])
 def test_host_processes_daemon(world):
     res = mp_worker.launch(world, "host", "daemon")
-    assert all(s["cqesDelivered"] == 48 and s["waitTimeouts"] == 0 for s in res.values())
+    assert all(s["cqesDelivered"] == 48 and s["waitTimeouts"] == 0 and s["transport"] == "peer" for s in res.values())
 
 
 def test_host_processes_stream_interface():
@@ -22,6 +22,16 @@ def test_gpu_processes_daemon():
     world = min(torch.cuda.device_count(), 4)
     res = mp_worker.launch(world, "cuda", "daemon")
     assert all(s["cqesDelivered"] == 48 for s in res.values())
+
+
+@pytest.mark.gpu
+@pytest.mark.multigpu
+def test_gpu_processes_shared_memory_heap(monkeypatch):
+    """Two GPUs in two processes that may not map one another's memory (NCCL_P2P_DISABLE=1) pick the heap in registered
+    host shared memory together; the daemon's mixed, disordered collectives run on it unchanged."""
+    monkeypatch.setenv("NCCL_P2P_DISABLE", "1")
+    res = mp_worker.launch(2, "cuda", "daemon")
+    assert all(s["cqesDelivered"] == 48 and s["transport"] == "shm" for s in res.values()), res
 
 
 @pytest.mark.gpu
