@@ -28,14 +28,77 @@ void CUDART_CB freeStaging(void* arg) {
 }
 
 // What one (communicator, stream) of a flush has started on the host backend and not yet waited for.
+struct NetRecv { int peer, tag; void* buf; size_t bytes; };
 struct HostLaunch {
   ncclComm* comm = nullptr;
   std::shared_ptr<std::vector<P2pList>> lists;
   std::vector<std::thread> threads;
   std::vector<uint64_t> temps;
+  // network path: receives still to be done by the flushing thread, and the verdicts of the sending threads
+  std::vector<NetRecv> netRecvs;
+  cudaStream_t stream = nullptr;
+  std::shared_ptr<std::vector<ncclResult_t>> sendResults;
 };
 
+// Messages of one (source, destination) pair match in program order: the tag carries the pair's sequence number.
+inline int netP2pTag(uint32_t seq) { return 0x8000 | (int)(seq & 0x7FFF); }   // below 0x10000: a sub-group adds its own base above that
+
+// Network path (members that cannot map one another's memory): a send is a message over the out-of-band connection
+// of the communicator, staged through host memory; it goes out from a thread of its own so that two ranks that send
+// to each other before receiving cannot block one another.  The receives of the whole flush follow once every send
+// has been started (netFinish).  The stream is drained first and the call returns with the data in place, like the
+// collectives of this path.
+ncclResult_t netLaunchFor(ncclComm* c, cudaStream_t stream, const std::vector<Pending>& ops, HostLaunch* host) {
+  host->comm = c; host->stream = stream;
+  const bool cuda = c->backend == dfcclBackendCuda;
+  if (cuda) {
+    int prev = 0;
+    cudaGetDevice(&prev);
+    if (prev != c->device) cudaSetDevice(c->device);
+    cudaError_t e = cudaStreamSynchronize(stream);
+    if (prev != c->device) cudaSetDevice(prev);
+    if (e != cudaSuccess) { DF_WARN("send / recv over the network path: %s", cudaGetErrorString(e)); return ncclUnhandledCudaError; }
+  }
+  std::lock_guard<std::mutex> l(c->mu);
+  size_t nSend = 0;
+  for (auto& p : ops) if (p.isSend) ++nSend;
+  host->sendResults = std::make_shared<std::vector<ncclResult_t>>(nSend, ncclSuccess);
+  size_t k = 0;
+  for (auto& p : ops) {
+    if (!p.isSend) { host->netRecvs.push_back({p.peer, netP2pTag(++c->recvSeq[p.peer]), p.buf, p.bytes}); continue; }
+    auto data = std::make_shared<std::vector<char>>(p.bytes);
+    if (cuda) { CUDACHECK(cudaMemcpy(data->data(), p.buf, p.bytes, cudaMemcpyDeviceToHost)); }
+    else memcpy(data->data(), p.buf, p.bytes);
+    const int tag = netP2pTag(++c->sendSeq[p.peer]), peer = p.peer;
+    auto boot = c->boot;
+    auto results = host->sendResults;
+    const size_t slot = k++;
+    host->threads.emplace_back([boot, data, tag, peer, results, slot] { (*results)[slot] = boot->send(peer, tag, data->data(), data->size()); });
+  }
+  return ncclSuccess;
+}
+
+ncclResult_t netFinish(HostLaunch* h) {
+  ncclResult_t res = ncclSuccess;
+  ncclComm* c = h->comm;
+  for (auto& r : h->netRecvs) {
+    if (res != ncclSuccess) break;
+    if (c->backend == dfcclBackendCuda) {
+      std::vector<char> tmp(r.bytes);
+      res = c->boot->recv(r.peer, r.tag, tmp.data(), r.bytes);
+      if (res == ncclSuccess && cudaMemcpy(r.buf, tmp.data(), r.bytes, cudaMemcpyHostToDevice) != cudaSuccess) { (void)cudaGetLastError(); res = ncclUnhandledCudaError; }
+    } else {
+      res = c->boot->recv(r.peer, r.tag, r.buf, r.bytes);
+    }
+  }
+  for (auto& t : h->threads) t.join();
+  h->threads.clear();
+  if (h->sendResults) for (auto r : *h->sendResults) if (res == ncclSuccess && r != ncclSuccess) res = r;
+  return res;
+}
+
 ncclResult_t launchFor(ncclComm* c, cudaStream_t stream, const std::vector<Pending>& ops, HostLaunch* host) {
+  if (c->netMode) return netLaunchFor(c, stream, ops, host);
   // lists keyed by (direction, peer), operations in program order
   std::map<std::pair<int, int>, std::vector<const Pending*>> by;
   for (auto& p : ops) by[{p.isSend ? 1 : 0, p.peer}].push_back(&p);
@@ -108,7 +171,6 @@ ncclResult_t p2pEnqueue(ncclComm* comm, bool isSend, void* buf, size_t count, nc
   if ((int)type < 0 || (int)type >= ncclNumTypes) return ncclInvalidArgument;
   if (count && !buf) return ncclInvalidArgument;
   if (peer == comm->rank) { DF_WARN("send / recv to self is not supported"); return ncclInvalidUsage; }
-  if (comm->netMode) { DF_WARN("send / recv is not available on communicators that go through the network path"); return ncclInvalidUsage; }
   t_pending.push_back({comm, isSend, buf, count * (size_t)dtypeSize(type), peer, stream});
   return ncclSuccess;
 }
@@ -128,6 +190,7 @@ ncclResult_t p2pFlush() {
     if (res != ncclSuccess) break;
   }
   for (auto& h : started) {
+    if (h.comm && h.comm->netMode) { ncclResult_t r = netFinish(&h); if (res == ncclSuccess) res = r; continue; }
     for (auto& t : h.threads) t.join();
     for (auto off : h.temps) h.comm->heap->free(off);
   }

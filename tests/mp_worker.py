@@ -521,4 +521,20 @@ def scenario_net_path(nv, comm, rank, world, backend):
     assert ctx.wait(0, 60000) == nv.SUCCESS
     assert float(b.min()) == 0.5 * want and float(b.max()) == 0.5 * want
     ctx.destroy()
+    # send / recv on this path: messages over the communicator's out-of-band connections, staged through the host.
+    # Everybody sends two messages to the next rank and receives two from the previous one inside one group.
+    L, nxt, prv = nv.lib(), (rank + 1) % world, (rank - 1) % world
+    m = 70001
+    s1 = torch.full((m,), float(10 * rank + 1), device=dev)
+    s2 = torch.full((3,), float(10 * rank + 2), device=dev)
+    r1, r2 = torch.zeros(m, device=dev), torch.zeros(3, device=dev)
+    nv.check(L.ncclGroupStart())
+    nv.check(L.ncclSend(s1.data_ptr(), m, nv.FLOAT32, nxt, comm.handle, stream))
+    nv.check(L.ncclSend(s2.data_ptr(), 3, nv.FLOAT32, nxt, comm.handle, stream))
+    nv.check(L.ncclRecv(r1.data_ptr(), m, nv.FLOAT32, prv, comm.handle, stream))
+    nv.check(L.ncclRecv(r2.data_ptr(), 3, nv.FLOAT32, prv, comm.handle, stream))
+    nv.check(L.ncclGroupEnd())
+    if cuda:
+        torch.cuda.synchronize()
+    assert float(r1.min()) == float(r1.max()) == 10 * prv + 1 and float(r2.min()) == float(r2.max()) == 10 * prv + 2
     return {"ok": True}

@@ -118,22 +118,35 @@ def test_daemon_interface_over_the_network_path_disordered(net_backend):
             np.testing.assert_allclose(got[r][i], exp, rtol=1e-2, atol=1e-2)
 
 
-def test_send_recv_and_stream_submission_are_refused_on_the_network_path(net_backend):
+@pytest.mark.parametrize("world", [2, 3])
+def test_send_recv_over_the_network_path(net_backend, world):
+    """Members that cannot map one another's memory exchange send / recv as messages over the communicator's
+    out-of-band connections.  Every rank sends to every other rank before it receives (a pattern that deadlocks an
+    implementation whose sends wait for the matching receive), two messages per pair to check their order."""
     nv = net_backend
-    comms = nv.Comm.init_loopback(2)
-    codes = {}
+    comms = nv.Comm.init_loopback(world)
+    got = {}
 
     def body(r):
         c, L = comms[r], nv.lib()
-        x = np.zeros(8, np.float32)
-        L.ncclGroupStart()
-        codes[r] = L.ncclSend(x.ctypes.data, 8, nv.FLOAT32, 1 - r, c.handle, None)
-        L.ncclGroupEnd()
+        outs = {p: [np.full(5000 + p, 100.0 * r + p, np.float32), np.full(3, -1.0 * r, np.float32)] for p in range(world) if p != r}
+        ins = {p: [np.zeros(5000 + r, np.float32), np.zeros(3, np.float32)] for p in range(world) if p != r}
+        nv.check(L.ncclGroupStart())
+        for p, (a, b) in outs.items():
+            nv.check(L.ncclSend(a.ctypes.data, a.size, nv.FLOAT32, p, c.handle, None))
+            nv.check(L.ncclSend(b.ctypes.data, b.size, nv.FLOAT32, p, c.handle, None))
+        for p, (a, b) in ins.items():
+            nv.check(L.ncclRecv(a.ctypes.data, a.size, nv.FLOAT32, p, c.handle, None))
+            nv.check(L.ncclRecv(b.ctypes.data, b.size, nv.FLOAT32, p, c.handle, None))
+        nv.check(L.ncclGroupEnd())
+        got[r] = ins
 
-    run_ranks(2, body)
+    run_ranks(world, body, timeout=120)
     for c in comms:
         c.destroy()
-    assert all(v != nv.SUCCESS for v in codes.values())
+    for r in range(world):
+        for p, (a, b) in got[r].items():
+            assert np.all(a == 100.0 * p + r) and np.all(b == -1.0 * p), (r, p)
 
 
 def test_dummy_plugin_falls_back_to_sockets(tmp_path):
