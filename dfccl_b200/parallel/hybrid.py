@@ -27,6 +27,7 @@ released to the daemon from the gradient hooks of the last micro-batch's backwar
 """
 from __future__ import annotations
 
+import os
 from dataclasses import dataclass
 from typing import List, Optional
 
@@ -60,6 +61,25 @@ class Mesh:
             c.destroy()
 
 
+PP_CTAS = int(os.environ.get("DFCCL_PP_CTAS", "2"))
+
+
+def _pp_group_options(d: Dist):
+    """A receive that is posted ahead is a kernel that holds its SMs until the matching send runs - possibly for a whole
+    pipeline stage's compute.  The fused tensor-parallel kernels need all their CTAs resident together, so the SMs such
+    receives may hold are bounded here (``PP_CTAS`` CTAs per transfer) and kept out of the fused grids
+    (``HybridTrainer``: daemon blocks + one posted receive per direction)."""
+    if d.device.type != "cuda":
+        return None
+    try:
+        opts = dist.ProcessGroupNCCL.Options()
+        opts.config.min_ctas = 1
+        opts.config.max_ctas = PP_CTAS
+        return opts
+    except Exception:                                        # a build of the bindings without communicator configuration
+        return None
+
+
 def build_mesh(d: Dist, tp: int, pp: int, dp: int) -> Mesh:
     assert tp * pp * dp == d.world, f"tp {tp} x pp {pp} x dp {dp} != world {d.world}"
     r = d.rank
@@ -76,7 +96,8 @@ def build_mesh(d: Dist, tp: int, pp: int, dp: int) -> Mesh:
                 pg = h
     fwd = bwd = None
     if d.world > 1 and pp > 1:                              # one group per direction of the pipeline traffic
-        fwd, bwd = dist.new_group(), dist.new_group()
+        opts = _pp_group_options(d)
+        fwd, bwd = dist.new_group(pg_options=opts), dist.new_group(pg_options=opts)
     # one rank context for everything this rank registers: on GPUs the fused tensor-parallel operators take the first
     # ids (as the model is built), the gradient buckets follow (HybridTrainer)
     ctx = nv.RankCtx(d.rank, d.local_rank) if d.device.type == "cuda" else None
@@ -103,6 +124,12 @@ class HybridTrainer:
                              randomize_order=True, seed=seed, param_groups=groups, daemon_blocks=daemon_blocks, optimizer=optimizer,
                              ctx=mesh.ctx, coll_id_base=mesh.tp_group.next_id if mesh.ctx is not None else 0)
         self.ddp.hooks_enabled = False
+        if d.device.type == "cuda" and mesh.pp > 1 and mesh.tp > 1:
+            # SMs that may be taken while a fused kernel starts: the daemon's blocks and one posted receive per direction
+            nv.check(nv.lib().dfcclGemmReserveSms(daemon_blocks + 2 * PP_CTAS), "dfcclGemmReserveSms")
+        # DFCCL_PP_POST_AHEAD=0: post every pipeline receive right before it is waited for (no kernel of the transfer
+        # library is then resident while this rank computes)
+        self.post_ahead = os.environ.get("DFCCL_PP_POST_AHEAD", "1") != "0"
         self.prev = d.rank - mesh.tp if mesh.pp_rank > 0 else None
         self.next = d.rank + mesh.tp if mesh.pp_rank < mesh.pp - 1 else None
         self._loss = torch.zeros(1, dtype=torch.float32, device=d.device)
@@ -143,7 +170,8 @@ class HybridTrainer:
                 x = tokens[i]
             else:
                 post_f(i)
-                post_f(i + 1)                                # the next input travels while this micro-batch computes
+                if self.post_ahead:
+                    post_f(i + 1)                            # the next input travels while this micro-batch computes
                 x, req = frecv.pop(i)
                 req.wait()
                 x.requires_grad_(True)
@@ -161,7 +189,8 @@ class HybridTrainer:
                 loss.backward()
             else:
                 post_b(i)
-                post_b(i + 1)
+                if self.post_ahead:
+                    post_b(i + 1)
                 g, req = brecv.pop(i)
                 req.wait()
                 outs[i].backward(g)
@@ -170,8 +199,9 @@ class HybridTrainer:
             del ins[i], outs[i]
 
         self._loss.zero_()
-        post_f(0)
-        post_b(0)
+        if self.post_ahead:
+            post_f(0)
+            post_b(0)
         warm = n if self.schedule == "gpipe" else min(m.pp - 1 - m.pp_rank, n)
         for i in range(warm):
             forward(i)
