@@ -144,6 +144,9 @@ def main(argv=None):
                "device_ms_per_iter": e0.elapsed_time(e1) / max(done_iters, 1), "wall_s": wall,
                "collective_bytes_per_iter_per_rank": int(sum(sizes)),
                "hangs": 0 if min(float(r[0]) for r in allres) == a.iters else 1,
+               # rank 0's daemon, summed over its blocks: scheduler passes and where their time went
+               "rank0_scheduler": {k: st[k] for k in ("schedulerPasses", "nsTriggers", "nsWalk", "nsQueues", "daemonLaunches",
+                                                       "ctxSaves", "ctxLoads", "waitPolls", "maxSwitchNs", "totalSwitchNs")},
                "inorder_library_model": inorder_verdict(a.colls, a.iters, world, a.seed)}
         print(json.dumps(out), flush=True)
         if a.out:

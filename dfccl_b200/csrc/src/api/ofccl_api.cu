@@ -455,6 +455,9 @@ DF_API ncclResult_t ofcclFinalizeRankCtx7StartHostThrds(ofcclRankCtx_t ctx) {
       }
     }
     e.cs.algo = ch.algo; e.cs.nBlocks = ch.nBlocks;
+    // collectives too small for every block start at different blocks, so that their fixed costs (flag round trips,
+    // completion) spread over the daemon instead of queueing on its first blocks
+    e.cs.blockBase = ch.nBlocks < ctx->nBlocks ? (int32_t)((((uint32_t)kv.first * 0x9E3779B1u) >> 16) % (uint32_t)ctx->nBlocks) : 0;
     if (ch.algo != dfcclAlgoNvls && pushEligible(e.comm, e.cs.kind, bytes, e.info.algo)) {
       // small all-reduce: one hop through slots at the peers ([2 parities][n writers][bytes]); a pure function of
       // what every member registered, so all members decide alike

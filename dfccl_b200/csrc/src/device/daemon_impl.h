@@ -5,7 +5,7 @@
 //   1. finds new submissions in the device-resident ring (the host writes entries
 //      and tail there with stream memory operations: no block reads host memory),
 //   2. consumes every entry of that ring in order (its own frontier), and
-//      appends the collectives it takes part in (block index < nBlocks of the
+//      appends the collectives it takes part in (relative block index < nBlocks of the
 //      collective) to its task queue,
 //   3. walks the task queue: runs each collective until it finishes or a bounded
 //      wait gives up, in which case the collective stays queued and the next one
@@ -43,7 +43,7 @@ DF_HD int consumeSubmissions(BlockShared* sh, RankDev* rd, int b) {
     __builtin_memcpy((char*)&q + 16, &w1, 16);
     if (q.flags & SQE_QUIT) { sh->quit = 2; break; }       // the frontier stays on the quit entry
     const int coll = q.collId;
-    const bool mine = coll >= 0 && (uint32_t)coll < rd->maxColls && rd->colls[coll].valid && b < rd->colls[coll].nBlocks;
+    const bool mine = coll >= 0 && (uint32_t)coll < rd->maxColls && rd->colls[coll].valid && relBlock(rd, &rd->colls[coll], b) < rd->colls[coll].nBlocks;
     CollDyn* d = mine ? &rd->dyn[(uint64_t)b * rd->maxColls + coll] : nullptr;
     if (mine) {
       // A stream-ordered caller may publish the next submission of a collective while this block
@@ -125,7 +125,7 @@ DF_HD uint32_t scanParked(BlockShared* sh, RankDev* rd, int b) {
     if (coll == 0xffff) continue;
     const CollStatic* c = &rd->colls[coll];
     const int n = c->nranks, me = c->rank;
-    const FlagSlot* f = c->myFlags + (uint64_t)b * n;
+    const FlagSlot* f = c->myFlags + (uint64_t)relBlock(rd, c, b) * n;
     const uint64_t epoch = rd->dyn[(uint64_t)b * rd->maxColls + coll].epoch;
     bool ok = true;
     for (int j = 0; j < n; ++j) {

@@ -104,6 +104,13 @@ DF_HD uint64_t recvBytes(const CollStatic* c) {
   }
 }
 
+// Relative index of daemon block b in collective c (>= c->nBlocks: b takes no part).  Flags, data partitions and
+// staging partitions are indexed by it; per-block state (saved contexts, statistics, trace) by the block itself.
+DF_HD int relBlock(const RankDev* rd, const CollStatic* c, int b) {
+  const int r = b - c->blockBase;
+  return r < 0 ? r + (int)rd->nBlocks : r;
+}
+
 // ---- context switch: load / save the (static, dynamic) context of a collective
 DF_HD void loadColl(BlockShared* sh, RankDev* rd, int b, int coll) {
   if (sh->loadedColl == coll) return;
@@ -556,6 +563,7 @@ DF_HD bool patientWait(BlockShared* sh, RankDev* rd, int b, int which, uint32_t 
 // `*moved` is set when at least one phase (or slice) was left behind during this visit.
 DF_HD int runColl(BlockShared* sh, RankDev* rd, int b, int coll, uint32_t budget, bool* moved) {
   if (!sh->standalone) loadColl(sh, rd, b, coll);
+  const int rb = sh->standalone ? b : relBlock(rd, &sh->cs, b);      // my index among this collective's blocks
   const int n = sh->cs.nranks, me = sh->cs.rank;
   const int tid = df_tid(), nt = df_nthreads();
   const int entryPhase = sh->dyn.phase;
@@ -567,7 +575,7 @@ DF_HD int runColl(BlockShared* sh, RankDev* rd, int b, int coll, uint32_t budget
         // (the daemon releases stream-ordered submissions from its trigger list and enters at PH_COPY_IN; this
         // phase serves entries that were parked here by an earlier instance)
         if (sh->dyn.sqeFlags & SQE_TRIGGERED) {
-          if (!boundedWait(sh, rd, b, 2, sh->standalone ? budget : 1u)) { if (noteStall(sh, rd)) { setPhase(sh, PH_COMPLETE); break; } return RC_STALLED; }
+          if (!boundedWait(sh, rd, rb, 2, sh->standalone ? budget : 1u)) { if (noteStall(sh, rd)) { setPhase(sh, PH_COMPLETE); break; } return RC_STALLED; }
         }
         if (tid == 0) trace(rd, b, TR_START, coll);
         setPhase(sh, nextPhase(sh, PH_COPY_IN));
@@ -575,7 +583,7 @@ DF_HD int runColl(BlockShared* sh, RankDev* rd, int b, int coll, uint32_t budget
       case PH_COPY_IN:
         if ((sh->dyn.sqeFlags & SQE_SEND_STAGED) && !rawSend(&sh->cs)) {
           bool needed = !(sh->cs.kind == dfcclCollBroadcast && me != sh->cs.root);
-          if (needed) stageCopy(sh, b, true);
+          if (needed) stageCopy(sh, rb, true);
           if (tid == 0) fence_sys();
         }
         setPhase(sh, nextPhase(sh, PH_POST_ARRIVE));
@@ -583,7 +591,7 @@ DF_HD int runColl(BlockShared* sh, RankDev* rd, int b, int coll, uint32_t budget
       case PH_POST_ARRIVE: {
         if (sh->cs.algo == dfcclAlgoPush && n > 1) {
           // the payload travels with the arrival flag: stores to a peer, one fence, then the flag
-          pushOut(sh, b);
+          pushOut(sh, rb);
           if (tid == 0) fence_sys();
           df_sync();
         }
@@ -591,7 +599,7 @@ DF_HD int runColl(BlockShared* sh, RankDev* rd, int b, int coll, uint32_t budget
         const bool pushed = sh->cs.algo == dfcclAlgoPush && n > 1;
         for (int j = tid; j < n; j += nt) {
           if (j == me) continue;
-          FlagSlot* s = sh->cs.peerFlags[j] + (uint64_t)b * n + me;
+          FlagSlot* s = sh->cs.peerFlags[j] + (uint64_t)rb * n + me;
           // push: the fence of thread 0 above, between two block-wide barriers, already orders every thread's payload
           // stores before these flag stores (a second fence per flag would only add its latency); the offsets are
           // not used by that schedule
@@ -604,7 +612,7 @@ DF_HD int runColl(BlockShared* sh, RankDev* rd, int b, int coll, uint32_t budget
         break;
       }
       case PH_WAIT_ARRIVE:
-        if (n > 1 && !patientWait(sh, rd, b, 0, budget)) {
+        if (n > 1 && !patientWait(sh, rd, rb, 0, budget)) {
           if (noteStall(sh, rd)) { setPhase(sh, PH_COMPLETE); break; }
           if (tid == 0) trace(rd, b, TR_STALL, coll);
           return RC_STALLED;
@@ -614,7 +622,7 @@ DF_HD int runColl(BlockShared* sh, RankDev* rd, int b, int coll, uint32_t budget
         break;
       case PH_DATA: {
         if (tid == 0) trace(rd, b, TR_DATA_BEGIN, coll);
-        const bool more = dataPhase(sh, rd, b);
+        const bool more = dataPhase(sh, rd, rb);
         if (tid == 0) trace(rd, b, TR_DATA_END, coll);
         if (more) {                                   // the cursor is saved; the phase stays PH_DATA
           *moved = true;
@@ -637,14 +645,14 @@ DF_HD int runColl(BlockShared* sh, RankDev* rd, int b, int coll, uint32_t budget
           if (tid == 0) {
             fence_sys();
             for (int j = 0; j < n; ++j)
-              if (j != me) st_relaxed_sys_u64(&(sh->cs.peerFlags[j] + (uint64_t)b * n + me)->done, epoch);
+              if (j != me) st_relaxed_sys_u64(&(sh->cs.peerFlags[j] + (uint64_t)rb * n + me)->done, epoch);
           }
         }
         setPhase(sh, PH_WAIT_DONE);
         break;
       }
       case PH_WAIT_DONE:
-        if (n > 1 && !patientWait(sh, rd, b, 1, budget)) {
+        if (n > 1 && !patientWait(sh, rd, rb, 1, budget)) {
           if (noteStall(sh, rd)) { setPhase(sh, PH_COMPLETE); break; }
           if (tid == 0) trace(rd, b, TR_STALL, coll);
           return RC_STALLED;
@@ -655,7 +663,7 @@ DF_HD int runColl(BlockShared* sh, RankDev* rd, int b, int coll, uint32_t budget
       case PH_COPY_OUT:
         if ((sh->dyn.sqeFlags & SQE_RECV_STAGED) && !rawRecv(&sh->cs)) {
           bool needed = !(sh->cs.kind == dfcclCollReduce && me != sh->cs.root);
-          if (needed) stageCopy(sh, b, false);
+          if (needed) stageCopy(sh, rb, false);
         }
         setPhase(sh, PH_COMPLETE);
         break;

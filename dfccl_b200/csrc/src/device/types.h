@@ -76,11 +76,14 @@ struct alignas(16) CollStatic {
   int32_t inType, outType;
   int32_t op;             // ncclSum..ncclMin (Avg is folded into scale / postDiv at prepare time)
   int32_t nranks, rank, root;
-  int32_t nBlocks;        // blocks that take part; block b handles slice b of the data
+  int32_t nBlocks;        // blocks that take part; the block at relative index b handles slice b of the data
   int32_t algo;           // dfcclAlgo_t actually used
   int32_t postDiv;        // integer average: divide the sum by this (0 = off)
   int32_t valid;
-  int32_t pad0;
+  int32_t blockBase;      // daemon block that plays relative block 0 of this collective: the nBlocks participants are
+                          // blockBase, blockBase + 1, ... (mod the daemon's block count), so that collectives too small
+                          // for every block do not all land on the first blocks.  A per-rank choice: ranks meet by
+                          // relative index only.
   double scale;           // multiplies the reduced value (1.0 = off)
   uint64_t count;         // elements, NCCL convention of the kind
   uint64_t stagingSendOff, stagingRecvOff;      // my heap offsets of staging areas (0 = none)
