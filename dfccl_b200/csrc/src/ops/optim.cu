@@ -57,49 +57,50 @@ __global__ void __launch_bounds__(256) sgdKernel(float* __restrict__ master, con
 // AdamW over the same flat arrays (decoupled weight decay; bias correction folded into the two scalars the host
 // passes: stepSize = lr / (1 - beta1^t), invBias2Sqrt = 1 / sqrt(1 - beta2^t)):
 //   m = b1 m + (1 - b1) g ; v = b2 v + (1 - b2) g^2 ; w = w (1 - lr wd) - stepSize * m / (sqrt(v) * invBias2Sqrt + eps)
+__device__ __forceinline__ void adamwOne(float& w, float g, float& m, float& v, float b1, float b2, float eps, float decay,
+                                         float stepSize, float invBias2Sqrt) {
+  m = b1 * m + (1.f - b1) * g;
+  v = b2 * v + (1.f - b2) * g * g;
+  // one square root and one fast division per element: the IEEE division's slow path costs more registers and
+  // instructions than the whole rest of the update and made the kernel instruction-bound (2 ulp is irrelevant here)
+  w = w * decay - stepSize * __fdividef(m, __fsqrt_rn(v) * invBias2Sqrt + eps);
+}
+
 template <typename P>
 __global__ void __launch_bounds__(256) adamwKernel(float* __restrict__ master, const float* __restrict__ grad,
                                                    float* __restrict__ m1, float* __restrict__ m2, P* __restrict__ param, size_t n,
                                                    float lr, float b1, float b2, float eps, float wd, float stepSize, float invBias2Sqrt) {
   const size_t stride = (size_t)gridDim.x * blockDim.x * 4;
   const float decay = 1.f - lr * wd;
-  for (size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 4; i < n; i += stride) {
-    float w[4], g[4], m[4], v[4];
-    const int cnt = i + 4 <= n ? 4 : (int)(n - i);
-    if (cnt == 4) {
-      *reinterpret_cast<float4*>(w) = *reinterpret_cast<const float4*>(master + i);
-      *reinterpret_cast<float4*>(g) = *reinterpret_cast<const float4*>(grad + i);
-      *reinterpret_cast<float4*>(m) = *reinterpret_cast<const float4*>(m1 + i);
-      *reinterpret_cast<float4*>(v) = *reinterpret_cast<const float4*>(m2 + i);
+  const size_t nFull = n & ~(size_t)3;
+  for (size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 4; i < nFull; i += stride) {
+    float4 w = *reinterpret_cast<const float4*>(master + i);
+    const float4 g = *reinterpret_cast<const float4*>(grad + i);
+    float4 m = *reinterpret_cast<const float4*>(m1 + i);
+    float4 v = *reinterpret_cast<const float4*>(m2 + i);
+    adamwOne(w.x, g.x, m.x, v.x, b1, b2, eps, decay, stepSize, invBias2Sqrt);
+    adamwOne(w.y, g.y, m.y, v.y, b1, b2, eps, decay, stepSize, invBias2Sqrt);
+    adamwOne(w.z, g.z, m.z, v.z, b1, b2, eps, decay, stepSize, invBias2Sqrt);
+    adamwOne(w.w, g.w, m.w, v.w, b1, b2, eps, decay, stepSize, invBias2Sqrt);
+    *reinterpret_cast<float4*>(master + i) = w;
+    *reinterpret_cast<float4*>(m1 + i) = m;
+    *reinterpret_cast<float4*>(m2 + i) = v;
+    if (sizeof(P) == 2) {
+      __nv_bfloat162 lo = __floats2bfloat162_rn(w.x, w.y), hi = __floats2bfloat162_rn(w.z, w.w);
+      uint2 pk;
+      pk.x = *reinterpret_cast<uint32_t*>(&lo);
+      pk.y = *reinterpret_cast<uint32_t*>(&hi);
+      *reinterpret_cast<uint2*>(param + i) = pk;
     } else {
-      for (int k = 0; k < cnt; ++k) { w[k] = master[i + k]; g[k] = grad[i + k]; m[k] = m1[i + k]; v[k] = m2[i + k]; }
+      *reinterpret_cast<float4*>(param + i) = w;
     }
-#pragma unroll
-    for (int k = 0; k < 4; ++k) {
-      if (k < cnt) {
-        m[k] = b1 * m[k] + (1.f - b1) * g[k];
-        v[k] = b2 * v[k] + (1.f - b2) * g[k] * g[k];
-        w[k] = w[k] * decay - stepSize * m[k] / (sqrtf(v[k]) * invBias2Sqrt + eps);
-      }
-    }
-    if (cnt == 4) {
-      *reinterpret_cast<float4*>(master + i) = *reinterpret_cast<float4*>(w);
-      *reinterpret_cast<float4*>(m1 + i) = *reinterpret_cast<float4*>(m);
-      *reinterpret_cast<float4*>(m2 + i) = *reinterpret_cast<float4*>(v);
-      if (sizeof(P) == 2) {
-        __nv_bfloat162 lo = __floats2bfloat162_rn(w[0], w[1]), hi = __floats2bfloat162_rn(w[2], w[3]);
-        uint2 pk;
-        pk.x = *reinterpret_cast<uint32_t*>(&lo);
-        pk.y = *reinterpret_cast<uint32_t*>(&hi);
-        *reinterpret_cast<uint2*>(param + i) = pk;
-      } else {
-        *reinterpret_cast<float4*>(param + i) = *reinterpret_cast<float4*>(w);
-      }
-    } else {
-      for (int k = 0; k < cnt; ++k) {
-        master[i + k] = w[k]; m1[i + k] = m[k]; m2[i + k] = v[k];
-        if (sizeof(P) == 2) param[i + k] = (P)__float2bfloat16_rn(w[k]); else reinterpret_cast<float*>(param)[i + k] = w[k];
-      }
+  }
+  if (blockIdx.x == 0 && threadIdx.x == 0) {             // up to three elements past the last full pack
+    for (size_t k = nFull; k < n; ++k) {
+      float w = master[k], m = m1[k], v = m2[k];
+      adamwOne(w, grad[k], m, v, b1, b2, eps, decay, stepSize, invBias2Sqrt);
+      master[k] = w; m1[k] = m; m2[k] = v;
+      if (sizeof(P) == 2) param[k] = (P)__float2bfloat16_rn(w); else reinterpret_cast<float*>(param)[k] = w;
     }
   }
 }
