@@ -19,10 +19,13 @@ Schedule: one-forward-one-backward (1F1B) by default - stage ``s`` of ``pp`` run
 forward passes ahead, then alternates forward and backward, so it holds at most ``pp - s`` micro-batches
 of activations instead of all of them; ``schedule="gpipe"`` runs all forwards, then all backwards.
 Receives are posted ahead: the input of the next forward pass and the gradient of the next backward
-pass are already being received while the current micro-batch computes.  Activations travel on one
-process group and gradients on another, so a stage's posted receive from its successor can never sit
-in front of its own send to that successor in one communicator's queue (that order, on one in-order
-queue per pair, is a deadlock).  Gradients are accumulated in the flat buckets; the buckets are
+pass are already being received while the current micro-batch computes.  Every neighbour and direction
+has a two-member process group of its own (activations to the successor, gradients back), so a stage's
+posted receive from its successor can never sit in front of its own send to that successor in one
+communicator's queue (that order, on one in-order queue per pair, is a deadlock), and every link is
+opened once while the mesh is built, both ends in the same order: the first transfer of a link blocks
+on the host until the other end joins, which receives posted ahead would turn into a cycle.
+Gradients are accumulated in the flat buckets; the buckets are
 released to the daemon from the gradient hooks of the last micro-batch's backward pass.
 """
 from __future__ import annotations
@@ -52,8 +55,12 @@ class Mesh:
     tp_group: TpGroup
     dp_comm: nv.Comm
     stage_comm: nv.Comm
-    pp_fwd: object = None        # process group that carries activations (stage s -> s + 1); None = the default group
-    pp_bwd: object = None        # process group that carries activation gradients (stage s + 1 -> s)
+    # pipeline traffic: one two-member process group per neighbour and direction, so that every transfer has a
+    # communicator (and a stream) of its own; None where there is no such neighbour
+    fwd_prev: object = None      # activations arriving from the previous stage
+    fwd_next: object = None      # activations leaving for the next stage
+    bwd_next: object = None      # activation gradients arriving from the next stage
+    bwd_prev: object = None      # activation gradients leaving for the previous stage
     ctx: object = None           # this rank's context: fused tensor-parallel operators and gradient buckets share it
 
     def close(self) -> None:
@@ -94,14 +101,39 @@ def build_mesh(d: Dist, tp: int, pp: int, dp: int) -> Mesh:
             h = dist.new_group(ranks)
             if g == r // tp:
                 pg = h
-    fwd = bwd = None
-    if d.world > 1 and pp > 1:                              # one group per direction of the pipeline traffic
+    links = {}
+    if d.world > 1 and pp > 1:
+        # every rank creates every group, in the same order: (lower rank a, its neighbour a + tp of the next stage),
+        # one group for the activations and one for their gradients
         opts = _pp_group_options(d)
-        fwd, bwd = dist.new_group(pg_options=opts), dist.new_group(pg_options=opts)
+        for a in range(d.world):
+            if (a // tp) % pp == pp - 1:
+                continue
+            f, b = dist.new_group([a, a + tp], pg_options=opts), dist.new_group([a, a + tp], pg_options=opts)
+            if r in (a, a + tp):
+                links[a] = (f, b)
+    fwd_prev, bwd_prev = links.get(r - tp, (None, None)) if pp_rank > 0 else (None, None)
+    fwd_next, bwd_next = links.get(r, (None, None)) if pp_rank < pp - 1 else (None, None)
+    if links:
+        # The first transfer between two ranks sets their connection up on the host and blocks until the other side
+        # calls its half.  Receives that are posted ahead would meet in a cycle there (stage 0 posts its gradient
+        # receive before it has sent anything, stage 1 its activation receive), so every link is opened here once,
+        # boundary by boundary, both sides in the same order.
+        tiny = torch.zeros(8, device=d.device)
+        for k in range(pp - 1):
+            if pp_rank == k:
+                dist.send(tiny, r + tp, group=fwd_next)
+                dist.recv(tiny, r + tp, group=bwd_next)
+            elif pp_rank == k + 1:
+                dist.recv(tiny, r - tp, group=fwd_prev)
+                dist.send(tiny, r - tp, group=bwd_prev)
+        if d.device.type == "cuda":
+            torch.cuda.synchronize(d.device)
     # one rank context for everything this rank registers: on GPUs the fused tensor-parallel operators take the first
     # ids (as the model is built), the gradient buckets follow (HybridTrainer)
     ctx = nv.RankCtx(d.rank, d.local_rank) if d.device.type == "cuda" else None
-    return Mesh(tp, pp, dp, tp_rank, pp_rank, dp_rank, TpGroup(tp_comm, pg, d.device, ctx=ctx), dp_comm, stage_comm, fwd, bwd, ctx)
+    return Mesh(tp, pp, dp, tp_rank, pp_rank, dp_rank, TpGroup(tp_comm, pg, d.device, ctx=ctx), dp_comm, stage_comm, fwd_prev, fwd_next, bwd_next,
+                bwd_prev, ctx)
 
 
 class HybridTrainer:
@@ -158,12 +190,12 @@ class HybridTrainer:
         def post_f(i):
             if self.prev is not None and i < n and i not in frecv:
                 x = self._hidden()
-                frecv[i] = (x, dist.irecv(x, self.prev, group=m.pp_fwd))
+                frecv[i] = (x, dist.irecv(x, self.prev, group=m.fwd_prev))
 
         def post_b(i):
             if self.next is not None and i < n and i not in brecv:
                 g = self._hidden()
-                brecv[i] = (g, dist.irecv(g, self.next, group=m.pp_bwd))
+                brecv[i] = (g, dist.irecv(g, self.next, group=m.bwd_next))
 
         def forward(i):
             if self.prev is None:
@@ -177,7 +209,7 @@ class HybridTrainer:
                 x.requires_grad_(True)
             y = st(x, targets[i] if self.next is None else None)
             if self.next is not None:
-                self._sends.append(self._send(y.detach(), self.next, m.pp_fwd))
+                self._sends.append(self._send(y.detach(), self.next, m.fwd_next))
             ins[i], outs[i] = x, y
             self.peak_live_microbatches = max(self.peak_live_microbatches, len(outs))
 
@@ -195,7 +227,7 @@ class HybridTrainer:
                 req.wait()
                 outs[i].backward(g)
             if self.prev is not None:
-                self._sends.append(self._send(ins[i].grad, self.prev, m.pp_bwd))
+                self._sends.append(self._send(ins[i].grad, self.prev, m.bwd_prev))
             del ins[i], outs[i]
 
         self._loss.zero_()
