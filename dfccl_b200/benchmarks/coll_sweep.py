@@ -74,7 +74,7 @@ def main(argv=None):
     ap.add_argument("--algo", default="auto", choices=["auto", "oneshot", "twoshot", "nvls"])
     ap.add_argument("--nvls-from", dest="nvls_from", type=int, default=-1,
                     help="with --algo auto: message sizes from this many bytes up take the multimem schedule, operands in the "
-                         "multicast arena (-1 = 1 MiB on 4 or more ranks, off below; 0 = off)")
+                         "multicast arena (-1 = 512 KiB, the first size past the push schedule, on 4 or more ranks, off below; 0 = off)")
     ap.add_argument("--blocks", type=int, default=0, help="daemon blocks per rank (0 = default)")
     ap.add_argument("--ids", type=int, default=4, help="registrations per case, used round-robin so that the host can enqueue ahead")
     ap.add_argument("--skip-nccl", action="store_true")
@@ -104,7 +104,7 @@ def main(argv=None):
     bufs = {}
     max_bytes = max(sizes)
     nvls = False
-    nvls_from = a.nvls_from if a.nvls_from >= 0 else ((1 << 20) if world >= 4 else 0)
+    nvls_from = a.nvls_from if a.nvls_from >= 0 else ((512 << 10) if world >= 4 else 0)
     if a.algo == "nvls":
         nvls_from = 1
     if nvls_from and world > 1:

@@ -459,10 +459,11 @@ DF_API ncclResult_t ofcclFinalizeRankCtx7StartHostThrds(ofcclRankCtx_t ctx) {
     // completion) spread over the daemon instead of queueing on its first blocks
     e.cs.blockBase = ch.nBlocks < ctx->nBlocks ? (int32_t)((((uint32_t)kv.first * 0x9E3779B1u) >> 16) % (uint32_t)ctx->nBlocks) : 0;
     if (ch.algo != dfcclAlgoNvls && pushEligible(e.comm, e.cs.kind, bytes, e.info.algo)) {
-      // small all-reduce: one hop through slots at the peers ([2 parities][n writers][bytes]); a pure function of
-      // what every member registered, so all members decide alike
+      // small all-reduce, all-gather or reduce-scatter: one hop through slots at the peers ([2 parities][n writers]
+      // [piece + 16 bytes: a reduce-scatter chunk keeps its misalignment]); a pure function of what every member
+      // registered, so all members decide alike
       e.cs.algo = dfcclAlgoPush;
-      e.cs.pushSlotBytes = (bytes + 511) & ~(size_t)511;
+      e.cs.pushSlotBytes = (bytes + 16 + 511) & ~(size_t)511;
       e.pushBytes = 2 * (size_t)e.comm->nranks * e.cs.pushSlotBytes;
       DFCHECK(e.comm->heap->alloc(e.pushBytes, &e.pushOff, false));
     }

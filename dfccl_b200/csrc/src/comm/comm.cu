@@ -125,7 +125,7 @@ ncclResult_t commCreate(std::shared_ptr<Bootstrap> boot, dfcclBackend_t backend,
     DFCHECK(c->heap->alloc(sizeof(FlagSlot) * DF_MAX_BLOCKS * n, &c->saFlagsOff));
     DFCHECK(c->heap->alloc(sizeof(FlagSlot) * 2 * n * 8, &c->p2pFlagsOff));   // [direction][peer][channel]
     if (n > 1) {                        // slots of the push schedule: [2 parities][n writers][pushMaxBytes]
-      c->pushSlotBytes = (pushMaxBytes() + 511) & ~(size_t)511;
+      c->pushSlotBytes = (pushMaxBytes() + 16 + 511) & ~(size_t)511;
       DFCHECK(c->heap->alloc(2 * (size_t)n * c->pushSlotBytes, &c->pushOff, false));
     }
     std::vector<PeerInfoMsg> all(n);
@@ -216,7 +216,9 @@ ncclResult_t commDestroy(ncclComm* c) {
 size_t pushMaxBytes() { return (size_t)std::max<int64_t>(0, paramI64("PUSH_MAX_BYTES", 256 << 10)); }
 
 bool pushEligible(const ncclComm* c, int kind, size_t bytes, int pinnedAlgo) {
-  if (kind != dfcclCollAllReduce || c->nranks < 2 || c->netMode || bytes == 0 || bytes > pushMaxBytes()) return false;
+  // all-reduce, all-gather and reduce-scatter whose per-member piece fits a slot (`bytes` = count x element size)
+  if ((kind != dfcclCollAllReduce && kind != dfcclCollAllGather && kind != dfcclCollReduceScatter) || c->nranks < 2 || c->netMode ||
+      bytes == 0 || bytes > pushMaxBytes()) return false;
   if (pinnedAlgo == dfcclAlgoPush) return true;
   if (pinnedAlgo != dfcclAlgoAuto) return false;
   std::string env = paramStr("ALGO", "");
@@ -320,7 +322,7 @@ ncclResult_t commCollective(ncclComm* c, int kind, const void* send, void* recv,
   const bool nvlsOk = nvlsEligible(c, kind, type, type, devOp, cs.postDiv, count);
   TunerChoice ch = tunerChoose(*topo, kind, bytes, c->nranks, maxBlocks, nvlsOk);
   cs.algo = ch.algo; cs.nBlocks = ch.nBlocks;
-  if (pushEligible(c, kind, bytes, dfcclAlgoAuto) && c->pushSlotBytes >= bytes) {
+  if (pushEligible(c, kind, bytes, dfcclAlgoAuto) && c->pushSlotBytes >= bytes + 16) {
     cs.algo = dfcclAlgoPush;
     cs.pushSlotBytes = c->pushSlotBytes;
     for (int j = 0; j < c->nranks; ++j) cs.peerPush[j] = c->peerHeap[j] + c->peerPushOff[j];

@@ -257,22 +257,69 @@ DF_HD char* pushSlot(const BlockShared* sh, int owner, int writer) {
   const CollStatic* c = &sh->cs;
   return c->peerPush[owner] + ((uint64_t)(sh->dyn.epoch & 1u) * c->nranks + writer) * c->pushSlotBytes;
 }
-// my input -> my slot at every peer (block b moves its part of the range)
+// Push schedule, outgoing half: what the peers need of my input goes into my slot at each of them (block b moves its
+// part of the range).  All-reduce: the whole input to everybody.  All-gather: my piece to everybody.
+// Reduce-scatter: chunk j of my input to member j.
 DF_HD void pushOut(BlockShared* sh, int b) {
   const CollStatic* c = &sh->cs;
+  const int n = c->nranks, me = c->rank;
+  const uint64_t es = dtypeSize(c->inType);
+  if (c->kind == dfcclCollReduceScatter) {
+    for (int k = 1; k < n; ++k) {                  // a different chunk for every member: one copy each
+      const int j = (me + k) % n;
+      if (df_tid() == 0) {
+        DataArgs* a = &sh->args;
+        uint64_t bb, be;
+        partRange(c->count, c->nBlocks, b, 16, &bb, &be);
+        a->nsrc = 1; a->ndst = 1; a->n = (be - bb) * es;
+        // the chunk sits in the slot at the misalignment it has in the input (chunks of odd length start off the
+        // 16-byte grid), so that the receiver's sources - its own chunk and the slots - all line up alike
+        a->src[0] = pushSendPtr(sh) + ((uint64_t)j * c->count + bb) * es;
+        a->dst[0] = pushSlot(sh, j, me) + (((uint64_t)j * c->count * es) & 15) + bb * es;
+        sh->stats.bytesCopied += a->n;
+      }
+      df_sync();
+      if (sh->args.n) copy_multi(&sh->args);
+      df_sync();
+    }
+    return;
+  }
   if (df_tid() == 0) {
     DataArgs* a = &sh->args;
-    const uint64_t es = dtypeSize(c->inType);
     uint64_t bb, be;
-    partRange(c->count, c->nBlocks, b, 16, &bb, &be);
-    a->nsrc = 1; a->ndst = 0; a->n = (be - bb) * es;
-    a->src[0] = pushSendPtr(sh) + bb * es;
-    for (int k = 1; k < c->nranks; ++k) { const int j = (c->rank + k) % c->nranks; a->dst[a->ndst++] = pushSlot(sh, j, c->rank) + bb * es; }
+    if (c->kind == dfcclCollAllGather) partRange(c->count * es, c->nBlocks, b, 16, &bb, &be);        // bytes, as its data phase
+    else { partRange(c->count, c->nBlocks, b, 16, &bb, &be); bb *= es; be *= es; }
+    a->nsrc = 1; a->ndst = 0; a->n = be - bb;
+    a->src[0] = pushSendPtr(sh) + bb;
+    for (int k = 1; k < n; ++k) { const int j = (me + k) % n; a->dst[a->ndst++] = pushSlot(sh, j, me) + bb; }
     sh->stats.bytesCopied += a->n * a->ndst;
   }
   df_sync();
   if (sh->args.n && sh->args.ndst) copy_multi(&sh->args);
   df_sync();
+}
+
+// Push schedule, all-gather: every member's piece is in its slot here; block b copies its part of each into the
+// output (my own piece comes from my input, unless the call is in place).  Pieces are small: no slicing.
+DF_HD void pushGatherLocal(BlockShared* sh, int b) {
+  const CollStatic* c = &sh->cs;
+  const int n = c->nranks, me = c->rank;
+  const uint64_t bytes = c->count * dtypeSize(c->inType);
+  for (int j = 0; j < n; ++j) {
+    if (df_tid() == 0) {
+      DataArgs* a = &sh->args;
+      uint64_t bb, be;
+      partRange(bytes, c->nBlocks, b, 16, &bb, &be);
+      a->nsrc = 1; a->ndst = 1; a->n = be - bb;
+      a->src[0] = (j == me ? pushSendPtr(sh) : (const char*)pushSlot(sh, me, j)) + bb;
+      a->dst[0] = pushRecvPtr(sh) + (uint64_t)j * bytes + bb;
+      if (a->dst[0] == a->src[0]) a->n = 0;                 // in place: my piece already sits where it belongs
+      sh->stats.bytesCopied += a->n;
+    }
+    df_sync();
+    if (sh->args.n) copy_multi(&sh->args);
+    df_sync();
+  }
 }
 
 // ---- PH_DATA: thread 0 builds the pointer lists, everybody moves the data.
@@ -287,6 +334,7 @@ DF_HD bool dataPhase(BlockShared* sh, RankDev* rd, int b) {
   const int n = c->nranks, me = c->rank;
   const uint64_t es = dtypeSize(c->inType), eo = dtypeSize(c->outType);
   // schedules that read or write peers' buffers need the offsets the peers posted
+  if (c->kind == dfcclCollAllGather && c->algo == dfcclAlgoPush && n > 1) { pushGatherLocal(sh, b); return false; }
   const bool needOffsets = n > 1 && c->algo != dfcclAlgoPush && c->algo != dfcclAlgoNvls;
   if (needOffsets) fetchPeerOffsets(sh, b);
   else if (df_tid() == 0) { sh->peerSend[me] = mySendOff(sh); sh->peerRecv[me] = myRecvOff(sh); }   // thread 0 is the only reader
@@ -349,6 +397,14 @@ DF_HD bool dataPhase(BlockShared* sh, RankDev* rd, int b) {
           a->dst[0] = pushRecvPtr(sh) + bb * eo; a->ndst = 1;
           a->n = be - bb;
           nvlsKind = 3;
+          break;
+        }
+        if (c->algo == dfcclAlgoPush && n > 1) {
+          // my chunk of my own input plus my chunk of every peer's input, which they put into their slots here
+          a->src[a->nsrc++] = pushSendPtr(sh) + ((uint64_t)me * c->count + bb) * es;
+          for (int k = 1; k < n; ++k) a->src[a->nsrc++] = pushSlot(sh, me, (me + k) % n) + (((uint64_t)me * c->count * es) & 15) + bb * es;
+          a->dst[a->ndst++] = pushRecvPtr(sh) + bb * eo;
+          a->n = be - bb;
           break;
         }
         for (int k = 0; k < n; ++k) { int j = (me + k) % n; a->src[a->nsrc++] = sendPtrOf(sh, j) + ((uint64_t)me * c->count + bb) * es; }

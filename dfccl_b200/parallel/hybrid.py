@@ -162,6 +162,11 @@ class HybridTrainer:
         # DFCCL_PP_POST_AHEAD=0: post every pipeline receive right before it is waited for (no kernel of the transfer
         # library is then resident while this rank computes)
         self.post_ahead = os.environ.get("DFCCL_PP_POST_AHEAD", "1") != "0"
+        # The first step of a process loads kernels and grows allocator pools, and some of that waits for the device to
+        # go idle - which it never does while a receive that was posted ahead spins for a peer that is stuck in its own
+        # first launches.  So the first step posts every receive right before its wait; posting ahead starts with the
+        # second step, when everything a step launches has been launched once.
+        self._warm = False
         self.prev = d.rank - mesh.tp if mesh.pp_rank > 0 else None
         self.next = d.rank + mesh.tp if mesh.pp_rank < mesh.pp - 1 else None
         self._loss = torch.zeros(1, dtype=torch.float32, device=d.device)
@@ -184,6 +189,7 @@ class HybridTrainer:
     def _forward_backward(self, tokens, targets, hooks: bool) -> None:
         """The micro-batches of one step in the configured order; the loss shares accumulate in ``self._loss``."""
         st, n, ddp, m = self.stage, self.n_micro, self.ddp, self.mesh
+        ahead = self.post_ahead and self._warm
         ins, outs = {}, {}
         frecv, brecv = {}, {}                                # posted receives: micro-batch -> (buffer, request)
 
@@ -202,7 +208,7 @@ class HybridTrainer:
                 x = tokens[i]
             else:
                 post_f(i)
-                if self.post_ahead:
+                if ahead:
                     post_f(i + 1)                            # the next input travels while this micro-batch computes
                 x, req = frecv.pop(i)
                 req.wait()
@@ -221,7 +227,7 @@ class HybridTrainer:
                 loss.backward()
             else:
                 post_b(i)
-                if self.post_ahead:
+                if ahead:
                     post_b(i + 1)
                 g, req = brecv.pop(i)
                 req.wait()
@@ -231,7 +237,7 @@ class HybridTrainer:
             del ins[i], outs[i]
 
         self._loss.zero_()
-        if self.post_ahead:
+        if ahead:
             post_f(0)
             post_b(0)
         warm = n if self.schedule == "gpipe" else min(m.pp - 1 - m.pp_rank, n)
@@ -260,6 +266,7 @@ class HybridTrainer:
                 for w in self._sends:
                     w.wait()
                 self._sends = []
+                self._warm = True                            # from the second pass on receives are posted ahead
         torch.cuda.current_stream(dev).wait_stream(side)
         torch.cuda.synchronize(dev)
         self.d.barrier()
@@ -307,6 +314,7 @@ class HybridTrainer:
         if self.d.device.type == "cuda":
             self._step_done = torch.cuda.Event()
             self._step_done.record()
+        self._warm = True
         return self._loss
 
     def state_dict(self):

@@ -52,6 +52,68 @@ def test_daemon_push_allreduce(host_backend, world, where):
                 assert np.all(got[r][i][2][it] == exp), (r, i, it, got[r][i][2][it][:4], exp)
 
 
+@pytest.mark.parametrize("world", [2, 3, 4])
+@pytest.mark.parametrize("where", ["heap", "user", "inplace"])
+@pytest.mark.parametrize("kind", ["allgather", "reducescatter"])
+def test_daemon_push_allgather_reducescatter(host_backend, world, where, kind):
+    """Small all-gathers and reduce-scatters take the same one-hop schedule: every member puts what each peer needs of
+    its input into its slot there (its piece; chunk j for member j) together with the arrival flag, and finishes
+    locally.  Odd counts put the chunks off the 16-byte grid; several calls per id use both slot parities."""
+    nv = host_backend
+    comms = nv.Comm.init_loopback(world)
+    counts = [1, 37, 4099, 20000]
+    iters = 4
+    kid = nv.ALLGATHER if kind == "allgather" else nv.REDUCESCATTER
+    got = {}
+
+    def val(r, it, q):                    # element value: depends on the rank, the call and (reduce-scatter) the chunk
+        return float(r + 1 + it + 3 * q)
+
+    def body(r):
+        c = comms[r]
+        ctx = nv.RankCtx(r)
+        for i, n in enumerate(counts):
+            ctx.prepare(i, c, kid, n, nv.FLOAT32, op=nv.SUM)          # schedule left to the library: push by size
+        ctx.finalize()
+        res = {}
+        for i, n in enumerate(counts):
+            sn, rn = (n, n * world) if kind == "allgather" else (n * world, n)
+            if where == "heap":
+                sv, rv = host_array(c.alloc(4 * sn + 64), sn, np.float32), host_array(c.alloc(4 * rn + 64), rn, np.float32)
+            elif where == "user":
+                sv, rv = np.zeros(sn, np.float32), np.zeros(rn, np.float32)
+            else:                                                     # in place, NCCL conventions
+                big = host_array(c.alloc(4 * n * world + 64), n * world, np.float32)
+                sv, rv = (big[r * n:(r + 1) * n], big) if kind == "allgather" else (big, big[r * n:(r + 1) * n])
+            res[i] = []
+            for it in range(iters):
+                if kind == "allgather":
+                    sv[:] = val(r, it, 0)
+                else:
+                    for q in range(world):
+                        sv[q * n:(q + 1) * n] = val(r, it, q)
+                ctx.run(i, sv.ctypes.data, rv.ctypes.data)
+                assert ctx.wait(i, 30000) == nv.SUCCESS
+                res[i].append(rv.copy())
+        got[r] = res
+        st = ctx.stats()
+        ctx.destroy()
+        assert st["waitTimeouts"] == 0
+
+    run_ranks(world, body)
+    for c in comms:
+        c.destroy()
+    for r in range(world):
+        for i, n in enumerate(counts):
+            for it in range(iters):
+                out = got[r][i][it]
+                if kind == "allgather":
+                    for q in range(world):
+                        assert np.all(out[q * n:(q + 1) * n] == val(q, it, 0)), (r, i, it, q)
+                else:
+                    assert np.all(out == sum(val(q, it, r) for q in range(world))), (r, i, it, out[:4])
+
+
 def test_stream_push_allreduce_mixed_with_other_schedules(host_backend, monkeypatch):
     """Small calls take the push schedule (DFCCL_PUSH=1), larger ones the handshaking schedules, on one communicator."""
     nv = host_backend
