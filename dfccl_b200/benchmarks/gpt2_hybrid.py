@@ -27,6 +27,7 @@ import torch.distributed as dist
 
 from dfccl_b200.models.gpt2 import GPT2Config, GPT2Stage
 from dfccl_b200.parallel import init_distributed
+from dfccl_b200.parallel import hybrid as hyb
 from dfccl_b200.parallel.hybrid import HybridTrainer, build_mesh
 from dfccl_b200.utils.clocks import ClockSampler
 
@@ -211,7 +212,8 @@ def main(argv=None):
                "model_tflops_per_gpu": flops / (ms / 1e3) / 1e12 / w,
                "config": {"model": f"GPT-2 {a.model}", "parallelism": f"tp{a.tp} x pp{a.pp} x dp{a.dp}", "micro_batch": a.micro_batch,
                           "n_micro": a.n_micro, "global_batch": a.dp * a.n_micro * a.micro_batch, "seq_len": cfg.seq_len, "cuda_graph": bool(a.graph),
-                          "schedule": "GPipe", "optimizer": "SGD momentum 0.9, fp32 master weights" if a.impl == "dfccl" else "SGD momentum 0.9 (bf16)"},
+                          "schedule": "1F1B, receives posted one micro-batch ahead" if tr.schedule == "1f1b" else "GPipe",
+                          "pipeline_link_ctas": hyb.PP_CTAS, "optimizer": "SGD momentum 0.9, fp32 master weights" if a.impl == "dfccl" else "SGD momentum 0.9 (bf16)"},
                "clocks": clk.summary(),
                "e2e": {"value": tokens / (e2e_ms / 1e3), "unit": "tokens/s", "ms_per_step": e2e_ms,
                        "h2d_bytes_per_step": host[0].numel() * 8, "d2h_bytes_per_step": 4},
