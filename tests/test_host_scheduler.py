@@ -329,3 +329,56 @@ def test_group_defers_collectives_and_communicator_creation(host_backend):
             assert np.all(gath[r].reshape(3, 100) == np.array([10, 20, 30], np.int32)[:, None])
     for h in handles:
         nv.check(L.ncclCommDestroy(h))
+
+
+def test_collectives_that_need_few_blocks_start_at_different_blocks(host_backend):
+    """Five daemon blocks and collectives that need one to five of them: each starts at a block of its own (chosen per
+    rank from the id) and wraps around the daemon's blocks; ranks meet by the relative block index only.  Every kind,
+    position-dependent data, per-rank shuffled orders, several rounds."""
+    nv = host_backend
+    nranks = 3
+    kinds = [nv.ALLREDUCE, nv.ALLGATHER, nv.REDUCESCATTER, nv.BROADCAST, nv.REDUCE] * 4
+    counts = [(1 + (7 * i) % 5) * 1024 + 3 * i for i in range(len(kinds))]          # 1 .. 5 blocks at 4 KB per block
+    comms = nv.Comm.init_loopback(nranks)
+
+    def body(r):
+        c = comms[r]
+        ctx = nv.RankCtx(r)
+        bufs = []
+        for i, (k, n) in enumerate(zip(kinds, counts)):
+            ctx.prepare(i + 40, c, k, n, nv.FLOAT32, root=i % nranks, algo=nv.ALGO_TWOSHOT if k == nv.ALLREDUCE else 0)
+            sn = n * (nranks if k == nv.REDUCESCATTER else 1)
+            rn = n * (nranks if k == nv.ALLGATHER else 1)
+            sp, rp = c.alloc(sn * 4), c.alloc(rn * 4)
+            bufs.append((sp, rp, host_array(sp, sn, np.float32), host_array(rp, rn, np.float32)))
+        ctx.finalize()
+        order_rng = random.Random(9 + r)
+        for it in range(3):
+            order = list(range(len(kinds)))
+            order_rng.shuffle(order)
+            for i in order:
+                sn = bufs[i][2].size
+                bufs[i][2][:] = (np.arange(sn, dtype=np.float32) % 127) + (r + 1) * 100 + it
+                ctx.run(i + 40, bufs[i][0], bufs[i][1])
+            assert ctx.wait_all(120000) == nv.SUCCESS
+            for i, (k, n) in enumerate(zip(kinds, counts)):
+                out = bufs[i][3]
+
+                def src(q, m):
+                    return (np.arange(m, dtype=np.float32) % 127) + (q + 1) * 100 + it
+                if k == nv.ALLREDUCE:
+                    np.testing.assert_array_equal(out, sum(src(q, n) for q in range(nranks)))
+                elif k == nv.REDUCESCATTER:
+                    np.testing.assert_array_equal(out, sum(src(q, n * nranks)[r * n:(r + 1) * n] for q in range(nranks)))
+                elif k == nv.ALLGATHER:
+                    np.testing.assert_array_equal(out, np.concatenate([src(q, n) for q in range(nranks)]))
+                elif k == nv.BROADCAST:
+                    np.testing.assert_array_equal(out, src(i % nranks, n))
+                elif k == nv.REDUCE and r == i % nranks:
+                    np.testing.assert_array_equal(out, sum(src(q, n) for q in range(nranks)))
+        ctx.destroy()
+
+    with _env(DFCCL_DAEMON_BLOCKS=5, DFCCL_MIN_BYTES_PER_BLOCK=4096, DFCCL_PUSH=0, DFCCL_IDLE_QUIT_US=2000):
+        run_ranks(nranks, body, timeout=300)
+    for c in comms:
+        c.destroy()
