@@ -16,7 +16,7 @@
 #include <stdint.h>
 #include <cuda_runtime.h>
 
-#define DF_MAX_RANKS 16        // ranks of one communicator the direct-access engine serves
+#define DF_MAX_RANKS 64        // ranks of one communicator the direct-access engine serves (one NVLink domain: 8 per node, up to 72 in a rack)
 #define DF_MAX_BLOCKS 64       // daemon thread blocks per rank
 #define DF_MAX_COLLS 2048      // collective ids per rank context (reference MAX_LENGTH = 2000)
 #define DF_WARP 32

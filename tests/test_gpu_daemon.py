@@ -134,6 +134,16 @@ def test_loopback_kinds_fp32(nv, kind, nranks):
     _loopback_case(nv, kind, nranks, 100003, "FLOAT32", root=nranks - 1)
 
 
+@pytest.mark.parametrize("kind", ["allreduce", "allgather", "reducescatter"])
+@pytest.mark.parametrize("nranks,count,heap,in_place", [(2, 1, True, False), (4, 4099, True, False), (8, 1001, False, False),
+                                                        (4, 30001, True, True), (3, 65536, False, False)])
+def test_loopback_small_messages_take_one_hop(nv, kind, nranks, count, heap, in_place):
+    """Pieces up to 256 KB: every member stores what each peer needs of its input into its slot there together with the
+    arrival flag and finishes locally (push schedule) - all-reduce, all-gather and reduce-scatter, odd counts (chunks
+    off the 16-byte grid), buffers in and outside the heap, in place, three calls per id (both slot parities)."""
+    _loopback_case(nv, kind, nranks, count, "FLOAT32", iters=3, heap=heap, in_place=in_place, blocks=4)
+
+
 @pytest.mark.parametrize("dt", ["BFLOAT16", "FLOAT16", "INT32", "FLOAT64", "INT64", "UINT8", "INT8"])
 def test_loopback_allreduce_dtypes(nv, dt):
     _loopback_case(nv, "allreduce", 4, 65537, dt, iters=1)

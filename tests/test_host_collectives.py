@@ -161,6 +161,17 @@ def test_eight_ranks(host_backend):
     _run_case(host_backend, "allreduce", 8, 4099, host_backend.FLOAT32, iters=1)
 
 
+@pytest.mark.parametrize("kind", ["allreduce", "allgather", "reducescatter", "broadcast"])
+def test_twenty_ranks(host_backend, kind, monkeypatch):
+    """More ranks than one node has GPUs (an NVLink domain may span a rack): the engine serves up to 64 members per
+    communicator; 20 thread-ranks run every schedule family (push for the small kinds, two-shot for the large one)."""
+    monkeypatch.setenv("DFCCL_HEAP_BYTES", str(16 << 20))
+    nv = host_backend
+    _run_case(nv, kind, 20, 611, nv.FLOAT32, root=17, iters=2)
+    if kind == "allreduce":
+        _run_case(nv, kind, 20, 100003, nv.FLOAT32, iters=1)
+
+
 @pytest.mark.parametrize("in_name,out_name", [("BFLOAT16", "FLOAT32"), ("FLOAT16", "FLOAT32"), ("FLOAT32", "BFLOAT16"), ("FLOAT32", "FLOAT16")])
 def test_fused_scale_and_cast(host_backend, in_name, out_name):
     """Gradient path: out = cast(scale * sum(in)), applied in registers before the only store."""
