@@ -338,9 +338,12 @@ def _gpt_hybrid(nv, comm, rank, world, backend, tp, pp, dp, port, schedule="1f1b
     st = tr.ddp.stats()
     peak = tr.peak_live_microbatches
     graphed = None
+    tr.close()
     if cuda and pp == 1:
-        # the same step captured in a CUDA graph: it must really be captured and replayed, and keep training
-        tg = HybridTrainer(d, mesh, GPT2Stage(cfg, mesh.tp_group, mesh.pp_rank, pp, micro_batch), n_micro=n_micro, lr=0.3,
+        # the same step captured in a CUDA graph: it must really be captured and replayed, and keep training.  A rank
+        # context is finalized once, so the second trainer gets a mesh (and a context) of its own.
+        mesh2 = build_mesh(d, tp, pp, dp)
+        tg = HybridTrainer(d, mesh2, GPT2Stage(cfg, mesh2.tp_group, mesh2.pp_rank, pp, micro_batch), n_micro=n_micro, lr=0.3,
                            bucket_mb=0.25, seed=3, use_graph=True, schedule=schedule)
         gl = [float(tg.step(tok, tgt)) for _ in range(3)]
         torch.cuda.synchronize()
@@ -349,7 +352,6 @@ def _gpt_hybrid(nv, comm, rank, world, backend, tp, pp, dp, port, schedule="1f1b
         assert gl[-1] < gl[0], gl
         graphed = gl
         tg.close()
-    tr.close()
     if rank == 0:                                           # the same model, unsharded, on this rank alone
         (c1,) = nv.Comm.init_loopback(1, rank if cuda else 0)
         d1 = Dist(0, 1, rank if cuda else 0, dev, c1, False)
