@@ -310,7 +310,8 @@ DF_API ncclResult_t dfcclMemFree(void* ptr, ncclComm_t comm) {
 }
 DF_API ncclResult_t dfcclNvlsInit(ncclComm_t comm, size_t bytes, int* available) {
   if (!comm) return ncclInvalidArgument;
-  if (!comm->nvls && comm->nranks > 1 && (!comm->loop || comm->backend != dfcclBackendCuda)) DFCHECK(nvlsArenaCreate(comm, bytes ? bytes : (size_t)(512u << 20), &comm->nvls));
+  // members that do not (or may not) map one another's memory get no multicast arena either
+  if (!comm->nvls && comm->nranks > 1 && !comm->netMode && !comm->shmMode && (!comm->loop || comm->backend != dfcclBackendCuda)) DFCHECK(nvlsArenaCreate(comm, bytes ? bytes : (size_t)(512u << 20), &comm->nvls));
   if (available) *available = comm->nvls ? 1 : 0;
   return ncclSuccess;
 }
