@@ -179,6 +179,16 @@ def main(argv=None):
             dist.all_reduce(ref)
             err = float((rv.float() - ref).abs().max() / (ref.abs().max() + 1e-6))
             row["max_rel_err"] = err
+        elif k == "allgather" and world > 1:                  # a copy: must be exact
+            ref = torch.empty(rn, dtype=tdt, device=dev)
+            dist.all_gather_into_tensor(ref, sv.clone())
+            row["max_rel_err"] = float((rv.float() - ref.float()).abs().max())
+            del ref
+        elif k == "reducescatter" and world > 1:              # fp32 reference of the same sum
+            ref = torch.empty(rn, dtype=torch.float32, device=dev)
+            dist.reduce_scatter_tensor(ref, sv.float())
+            row["max_rel_err"] = float((rv.float() - ref).abs().max() / (ref.abs().max() + 1e-6))
+            del ref
         if not a.skip_stream_api and k in ("allreduce", "allgather", "reducescatter"):
             fn = {"allreduce": lambda: nv.check(L.ncclAllReduce(send_p, recv_p, count, ndt, nv.SUM, d.comm.handle, stream.cuda_stream)),
                   "allgather": lambda: nv.check(L.ncclAllGather(send_p, recv_p, count, ndt, d.comm.handle, stream.cuda_stream)),
