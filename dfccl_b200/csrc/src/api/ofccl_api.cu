@@ -435,14 +435,14 @@ DF_API ncclResult_t ofcclFinalizeRankCtx7StartHostThrds(ofcclRankCtx_t ctx) {
     const size_t bytes = e.info.count * (size_t)dtypeSize(e.info.inType);
     bool nv = nvlsEligible(e.comm, e.cs.kind, e.cs.inType, e.cs.outType, e.cs.op, e.cs.postDiv, e.cs.count);
     TunerChoice ch = tunerChoose(*topo, e.info.kind, bytes, e.comm->nranks, ctx->nBlocks, nv, e.info.algo, e.info.nBlocks);
-    // reduce-scatter and all-gather take the multimem schedule only when it is pinned at registration
+    // reduce-scatter, all-gather and broadcast take the multimem schedule only when it is pinned at registration
     if (e.info.algo == dfcclAlgoNvls && nvlsEligibleRsAg(e.comm, e.cs.kind, e.cs.inType, e.cs.outType, e.cs.op, e.cs.postDiv, e.cs.count)) ch.algo = dfcclAlgoNvls;
     if (ch.algo == dfcclAlgoNvls) {
       // staging slots in the arena; every member walks its collectives in id order, so the offsets agree.
-      // (the output of a reduce-scatter and the input of an all-gather are local to the rank and need no slot)
+      // (the output of a reduce-scatter and the input of an all-gather or broadcast are local to the rank and need no slot)
       NvlsArena* a = e.comm->nvls;
       const bool inPlace = (e.info.flags & DFCCL_COLL_ARENA_BUFFERS) != 0;      // the caller's buffers are arena memory: no slots
-      const size_t inB = e.cs.kind == dfcclCollAllGather || inPlace ? 0 : sendBytes(&e.cs);
+      const size_t inB = e.cs.kind == dfcclCollAllGather || e.cs.kind == dfcclCollBroadcast || inPlace ? 0 : sendBytes(&e.cs);
       const size_t outB = e.cs.kind == dfcclCollReduceScatter || inPlace ? 0 : recvBytes(&e.cs);
       uint64_t in = 0, out = 0;
       if ((inB == 0 || a->alloc(inB, &in) == ncclSuccess) && (outB == 0 || a->alloc(outB, &out) == ncclSuccess)) {

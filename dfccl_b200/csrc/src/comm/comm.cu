@@ -233,7 +233,7 @@ bool nvlsEligible(const ncclComm* c, int kind, int inType, int outType, int devO
 
 bool nvlsEligibleRsAg(const ncclComm* c, int kind, int inType, int outType, int devOp, int postDiv, size_t count) {
   if (!c->nvls || c->nranks < 2 || (count * (size_t)dtypeSize(inType)) % 16 != 0) return false;
-  if (kind == dfcclCollAllGather) return true;
+  if (kind == dfcclCollAllGather || kind == dfcclCollBroadcast) return true;
   return kind == dfcclCollReduceScatter && devOp == OP_SUM && postDiv == 0 && nvlsTypesOk(inType, outType);
 }
 

@@ -240,9 +240,11 @@ DF_HD const char* sendPtrOf(const BlockShared* sh, int j) { return sh->cs.peerHe
 DF_HD char* recvPtrOf(const BlockShared* sh, int j) { return sh->cs.peerHeap[j] + sh->peerRecv[j]; }
 
 // Schedules in which a user buffer is touched by this rank only use it where it is (no staging copy even when it
-// lies outside the symmetric heap): both buffers of the push schedule, the input of a multimem all-gather, the
-// output of a multimem reduce-scatter.
-DF_HD bool rawSend(const CollStatic* c) { return c->algo == dfcclAlgoPush || (c->algo == dfcclAlgoNvls && c->kind == dfcclCollAllGather); }
+// lies outside the symmetric heap): both buffers of the push schedule, the input of a multimem all-gather or
+// broadcast, the output of a multimem reduce-scatter.
+DF_HD bool rawSend(const CollStatic* c) {
+  return c->algo == dfcclAlgoPush || (c->algo == dfcclAlgoNvls && (c->kind == dfcclCollAllGather || c->kind == dfcclCollBroadcast));
+}
 DF_HD bool rawRecv(const CollStatic* c) { return c->algo == dfcclAlgoPush || (c->algo == dfcclAlgoNvls && c->kind == dfcclCollReduceScatter); }
 
 // Push schedule: the user's buffers are only touched by this rank, so they are used where they are.
@@ -438,6 +440,18 @@ DF_HD bool dataPhase(BlockShared* sh, RankDev* rd, int b) {
         reduce = false;
         uint64_t bytes = c->count * es;
         partRange(bytes, c->nBlocks, b, 16, &bb, &be);
+        if (c->algo == dfcclAlgoNvls && n > 1) {
+          // the root's multicast stores put its buffer into every member's output (arena); the others move nothing and
+          // learn from the root's done flag that their output is complete
+          if (me == c->root) {
+            const uint64_t out = (sh->dyn.sqeFlags & SQE_RECV_STAGED) ? c->nvlsOut : sh->dyn.recv;
+            a->src[0] = pushSendPtr(sh) + bb; a->nsrc = 1;
+            a->dst[0] = (char*)(uintptr_t)(out + bb); a->ndst = 1;
+            a->n = be - bb;
+            nvlsKind = 4;
+          }
+          break;
+        }
         a->src[0] = sendPtrOf(sh, c->root) + bb; a->nsrc = 1;
         char* d = recvPtrOf(sh, me) + bb;
         if (d != a->src[0]) a->dst[a->ndst++] = d;

@@ -470,6 +470,7 @@ def scenario_nvls_rsag(nv, comm, rank, world, backend):
     ctx = nv.RankCtx(rank, rank if cuda else -1)
     ctx.prepare(1, comm, nv.REDUCESCATTER, count, nv.BFLOAT16, out_dtype=nv.FLOAT32, op=nv.SUM, scale=0.5, algo=nv.ALGO_NVLS)
     ctx.prepare(2, comm, nv.ALLGATHER, count, nv.FLOAT32, algo=nv.ALGO_NVLS)
+    ctx.prepare(3, comm, nv.BROADCAST, count, nv.FLOAT32, root=world - 1, algo=nv.ALGO_NVLS)
     ctx.finalize()
     g = torch.Generator().manual_seed(4)
     full = (torch.rand(world, world * count, generator=g) * 2 - 1).to(torch.bfloat16)
@@ -496,6 +497,18 @@ def scenario_nvls_rsag(nv, comm, rank, world, backend):
     assert ctx.wait(2, 30000) == nv.SUCCESS
     got = o.view(world, count).cpu()
     assert all(float(got[j].min()) == j + 1 and float(got[j].max()) == j + 1 for j in range(world)), "nvls all-gather"
+    # broadcast: the root's multicast stores fill every member's output (an ordinary tensor here: staged through the
+    # collective's arena slot), twice with different data
+    b = torch.zeros(count, device=dev)
+    for it in range(2):
+        src = torch.arange(count, dtype=torch.float32, device=dev) + 7 * it + 100 * rank
+        b.fill_(-1)
+        if cuda:
+            torch.cuda.synchronize()
+        ctx.run(3, src.data_ptr() if rank == world - 1 else 0, b.data_ptr())
+        assert ctx.wait(3, 30000) == nv.SUCCESS
+        want = torch.arange(count, dtype=torch.float32) + 7 * it + 100 * (world - 1)
+        assert torch.equal(b.cpu(), want), ("nvls broadcast", it)
     ctx.destroy()
     return {"available": True}
 

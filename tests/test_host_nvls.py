@@ -182,3 +182,50 @@ def test_daemon_reducescatter_allgather_nvls(host_backend, kind, where):
         exp = np.concatenate(ins)
         for r in range(nranks):
             np.testing.assert_array_equal(got[r], exp)
+
+
+@pytest.mark.parametrize("where", ["arena", "heap", "user"])
+@pytest.mark.parametrize("root", [0, 2])
+def test_daemon_broadcast_nvls(host_backend, where, root):
+    """Broadcast on the multimem schedule, pinned at registration: the root's multicast stores put its buffer into
+    every member's output (in the arena, or this collective's arena slot when the caller's buffer lives elsewhere);
+    the others move nothing and wait for the root's done flag.  The root's input is used where it is."""
+    nv = host_backend
+    nranks, count = 4, 20 * 1024 + 4
+    comms = nv.Comm.init_loopback(nranks)
+    got = {}
+
+    def body(r):
+        c = comms[r]
+        assert c.nvls_init(8 << 20)
+        ctx = nv.RankCtx(r)
+        ctx.prepare(7, c, nv.BROADCAST, count, nv.FLOAT32, root=root, algo=nv.ALGO_NVLS)
+        ctx.finalize()
+        keep = []
+        if where == "arena":
+            rp = c.nvls_alloc(count * 4)
+        elif where == "heap":
+            rp = c.alloc(count * 4)
+        else:
+            keep.append(np.zeros(count, np.float32))
+            rp = keep[-1].ctypes.data
+        rv = host_array(rp, count, np.float32)
+        sv = np.zeros(count, np.float32)
+        res = []
+        for it in range(3):
+            sv[:] = np.arange(count, dtype=np.float32) + 1000 * (r + 1) + it
+            rv[:] = -1
+            ctx.run(7, sv.ctypes.data if r == root else 0, rp)
+            assert ctx.wait(7, 30000) == nv.SUCCESS
+            res.append(rv.copy())
+        got[r] = res
+        st = ctx.stats()
+        ctx.destroy()
+        assert st["waitTimeouts"] == 0
+
+    run_ranks(nranks, body)
+    for c in comms:
+        c.destroy()
+    for r in range(nranks):
+        for it in range(3):
+            np.testing.assert_array_equal(got[r][it], np.arange(count, dtype=np.float32) + 1000 * (root + 1) + it)
