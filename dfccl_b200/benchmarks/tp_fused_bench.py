@@ -42,7 +42,7 @@ def timeit(fn, iters, world):
 def main(argv=None):
     ap = argparse.ArgumentParser()
     ap.add_argument("--tokens", type=int, default=8192, help="rows of the full activation (micro-batch x sequence)")
-    ap.add_argument("--d", type=int, default=1024)
+    ap.add_argument("--d-model", dest="d", type=int, default=1024, help="model width (the launcher module of torch treats a bare --d as an abbreviation of its own options)")
     ap.add_argument("--iters", type=int, default=30)
     ap.add_argument("--peak-tflops", type=float, default=1658.4)
     ap.add_argument("--link-gbs", type=float, default=655.0)
