@@ -65,6 +65,9 @@ ncclResult_t dfcclProbeStreamRoundTrip(int mode, int iters, int delayUs, double*
 int dfcclTopoXml(char* buf, int cap);          /* the detected (or injected) topology as XML; returns the length */
 void dfcclTopoReset(void);
 int dfcclTopoGpuCount(void);
+/* Path policy: 1 when devices a and b may use one another's memory directly (peer access exists, P2P_DISABLE is not
+ * set, the path is within P2P_LEVEL = LOC | NVL | PIX | PXB | PHB | SYS), 0 when not, -1 on error. */
+int dfcclTopoP2pAllowed(int a, int b);
 ncclResult_t dfcclTunerChoose(int kind, size_t bytes, int nranks, int maxBlocks, int nvls, int pinnedAlgo, int* algo,
                               int* nBlocks, double* predictedUs);
 double dfcclTunerPredictUs(int kind, int algo, size_t bytes, int nranks, int nBlocks);

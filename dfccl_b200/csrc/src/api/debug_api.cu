@@ -22,6 +22,12 @@ DF_API int dfcclTopoGpuCount(void) {
   if (topoGet(&t) != ncclSuccess) return -1;
   return (int)t->gpus.size();
 }
+// Path policy of the (detected or injected) topology: may devices a and b use one another's memory directly?
+DF_API int dfcclTopoP2pAllowed(int a, int b) {
+  const Topology* t = nullptr;
+  if (topoGet(&t) != ncclSuccess) return -1;
+  return topoP2pAllowed(*t, a, b) ? 1 : 0;
+}
 DF_API ncclResult_t dfcclTunerChoose(int kind, size_t bytes, int nranks, int maxBlocks, int nvls, int pinnedAlgo, int* algo,
                                      int* nBlocks, double* predictedUs) {
   const Topology* t = nullptr;

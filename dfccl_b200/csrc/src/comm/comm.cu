@@ -140,6 +140,16 @@ ncclResult_t commCreate(std::shared_ptr<Bootstrap> boot, dfcclBackend_t backend,
     for (int j = 0; j < n; ++j) if (all[j].heap.hostHash != all[r].heap.hostHash) otherHosts = true;
     c->netMode = forcedNet || otherHosts;
     int32_t p2pOk = c->netMode ? 0 : (c->heap->hostShm() || paramI64("P2P_DISABLE", 0) == 0) ? 1 : 0;
+    if (p2pOk && backend == dfcclBackendCuda && !c->heap->hostShm()) {
+      // path policy: peer access that exists may still be ruled out (P2P_LEVEL), for the whole communicator
+      const Topology* topo = nullptr;
+      if (topoGet(&topo) == ncclSuccess)
+        for (int j = 0; j < n; ++j)
+          if (j != r && all[j].device != device && !topoP2pAllowed(*topo, device, all[j].device)) {
+            DF_INFO(SUB_INIT, "path policy rules out peer memory between devices %d and %d", device, all[j].device);
+            p2pOk = 0;
+          }
+    }
     for (int j = 0; j < n; ++j) {
       c->handles[j] = all[j].heap;
       c->peerSaFlagsOff[j] = all[j].saFlagsOff;

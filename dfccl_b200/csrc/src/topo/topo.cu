@@ -1,6 +1,7 @@
 #include "topo.h"
 #include "../common/log.h"
 #include "../common/param.h"
+#include <cctype>
 #include <algorithm>
 #include <cmath>
 #include <cstring>
@@ -172,6 +173,19 @@ std::string topoToXml(const Topology& t) {
     }
   o << "</system>\n";
   return o.str();
+}
+
+bool topoP2pAllowed(const Topology& t, int a, int b) {
+  if (paramI64("P2P_DISABLE", 0) != 0) return false;
+  const int n = (int)t.gpus.size();
+  if (a < 0 || b < 0 || a >= n || b >= n) return true;
+  const int type = t.p2pType(a, b);
+  if (type == P2P_NONE) return false;
+  std::string level = paramStr("P2P_LEVEL", "SYS");
+  for (auto& ch : level) ch = (char)toupper((unsigned char)ch);
+  if (level == "LOC" || level == "0") return type == P2P_SELF;
+  if (level == "NVL" || level == "1") return type == P2P_SELF || type == P2P_NVLINK;
+  return true;                                        // PIX, PXB, PHB, SYS (2..5): any peer path the driver offers
 }
 
 namespace {

@@ -50,6 +50,13 @@ std::string topoToXml(const Topology& t);
 ncclResult_t topoGet(const Topology** t);
 void topoResetCache();                                        // tests
 
+// Path policy (role of the reference's ncclTopoCheckP2p and its NCCL_P2P_LEVEL knob, src/graph/paths.cc:251-341): may
+// members on devices a and b use one another's memory directly?  No when the pair has no peer access, when
+// P2P_DISABLE is set, or when the pair's path is farther than P2P_LEVEL allows: LOC = the same device only,
+// NVL = NVLink only, PIX / PXB / PHB / SYS = PCIe paths too (the driver reports one kind of PCIe peer path; the four
+// names are accepted for compatibility).  Devices the topology does not know are left to the mapping attempt.
+bool topoP2pAllowed(const Topology& t, int a, int b);
+
 struct TunerChoice { int algo; int nBlocks; double predictedUs; };
 // bytes: payload per rank as NCCL counts it (AllGather: sendcount bytes, ReduceScatter: recvcount bytes)
 double tunerPredictUs(const Topology& t, int kind, int algo, size_t bytes, int nranks, int nBlocks);

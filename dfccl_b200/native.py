@@ -131,6 +131,9 @@ def lib() -> C.CDLL:
             "dfcclGemmFused": [vp, vp, vp, i, i, i, vp, sz, vp],
             "dfcclHeapPeerBase": [vp, i, C.POINTER(vp)],
             "dfcclCommTransport": [vp, C.POINTER(i)],
+            "dfcclTopoXml": [C.c_char_p, i], "dfcclTopoReset": [], "dfcclTopoGpuCount": [], "dfcclTopoP2pAllowed": [i, i],
+            "dfcclTunerChoose": [i, sz, i, i, i, i, C.POINTER(i), C.POINTER(i), C.POINTER(C.c_double)],
+            "dfcclTunerPredictUs": [i, i, sz, i, i],
             "dfcclProbePeerCopy": [vp, i, sz, i, i, i, i, i, C.POINTER(C.c_double)],
             "dfcclProbeFlagRoundTrip": [vp, i, i, C.POINTER(C.c_double)],
             "dfcclProbeMemoryOps": [i, C.POINTER(C.c_uint64)],
@@ -146,6 +149,8 @@ def lib() -> C.CDLL:
         L.dfcclGemmFusedArgsSize.restype = C.c_size_t
         L.ncclGetErrorString.argtypes = [i]
         L.ncclGetErrorString.restype = C.c_char_p
+        L.dfcclTunerPredictUs.restype = C.c_double
+        L.dfcclTopoReset.restype = None
         _lib = L
         return L
 
@@ -167,6 +172,45 @@ def get_backend() -> str:
     b = C.c_int()
     check(lib().dfcclGetBackend(C.byref(b)))
     return "host" if b.value == BACKEND_HOST else "cuda"
+
+
+def topo_xml() -> str:
+    """The system topology the library works with (detected, or injected with ``DFCCL_TOPO_FILE``) as XML."""
+    n = lib().dfcclTopoXml(None, 0)
+    if n < 0:
+        raise DfcclError(2, "dfcclTopoXml")
+    buf = C.create_string_buffer(n + 1)
+    lib().dfcclTopoXml(buf, n + 1)
+    return buf.value.decode()
+
+
+def topo_reset() -> None:
+    """Forget the cached topology (the next use detects or loads it again)."""
+    lib().dfcclTopoReset()
+
+
+def topo_gpu_count() -> int:
+    return lib().dfcclTopoGpuCount()
+
+
+def topo_p2p_allowed(a: int, b: int) -> bool:
+    """Path policy: may devices ``a`` and ``b`` use one another's memory directly (peer access, ``P2P_DISABLE``, ``P2P_LEVEL``)?"""
+    r = lib().dfcclTopoP2pAllowed(a, b)
+    if r < 0:
+        raise DfcclError(2, "dfcclTopoP2pAllowed")
+    return bool(r)
+
+
+def tuner_choose(kind: int, nbytes: int, nranks: int, max_blocks: int, nvls: bool = False, pinned_algo: int = 0):
+    """(schedule, blocks, predicted microseconds) the size -> schedule tuner picks for one collective."""
+    algo, nb, us = C.c_int(), C.c_int(), C.c_double()
+    check(lib().dfcclTunerChoose(kind, nbytes, nranks, max_blocks, 1 if nvls else 0, pinned_algo, C.byref(algo), C.byref(nb), C.byref(us)),
+          "dfcclTunerChoose")
+    return algo.value, nb.value, us.value
+
+
+def tuner_predict_us(kind: int, algo: int, nbytes: int, nranks: int, blocks: int) -> float:
+    return float(lib().dfcclTunerPredictUs(kind, algo, nbytes, nranks, blocks))
 
 
 def get_unique_id() -> bytes:
