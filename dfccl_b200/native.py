@@ -151,6 +151,12 @@ def lib() -> C.CDLL:
         L.ncclGetErrorString.restype = C.c_char_p
         L.dfcclTunerPredictUs.restype = C.c_double
         L.dfcclTopoReset.restype = None
+        L.dfcclParam.argtypes = [C.c_char_p, C.c_longlong]
+        L.dfcclParam.restype = C.c_longlong
+        L.dfcclLogReset.argtypes = []
+        L.dfcclLogReset.restype = None
+        L.dfcclLastError.argtypes = []
+        L.dfcclLastError.restype = C.c_char_p
         _lib = L
         return L
 
@@ -172,6 +178,24 @@ def get_backend() -> str:
     b = C.c_int()
     check(lib().dfcclGetBackend(C.byref(b)))
     return "host" if b.value == BACKEND_HOST else "cuda"
+
+
+def param(name: str, default: int = 0) -> int:
+    """Value of a configuration parameter as the library reads it: ``DFCCL_<name>``, then ``NCCL_<name>``, then (for the
+    reference's unprefixed scheduler knobs) ``<name>``; the environment first, then ``~/.dfccl.conf``, ``~/.nccl.conf``,
+    ``/etc/dfccl.conf``, ``/etc/nccl.conf``; ``k`` / ``m`` / ``g`` suffixes scale byte counts."""
+    return int(lib().dfcclParam(name.encode(), default))
+
+
+def log_reset() -> None:
+    """Re-read ``DEBUG``, ``DEBUG_SUBSYS`` and ``DEBUG_FILE`` (they are read once, at the first message)."""
+    lib().dfcclLogReset()
+
+
+def last_error() -> str:
+    """Text of the calling thread's most recent warning (what went wrong in the call that just failed)."""
+    s = lib().dfcclLastError()
+    return s.decode() if s else ""
 
 
 def topo_xml() -> str:
