@@ -67,3 +67,38 @@ def test_log_levels_subsystems_and_file(tmp_path):
     assert "DFCCL WARN" in out and "DFCCL INFO" not in out
     out = _run(code, {}, tmp_path)
     assert "DFCCL WARN" not in out and "LAST null buffer" in out
+
+
+def test_rendezvous_by_comm_id_without_exchanging_a_unique_id(tmp_path):
+    """``NCCL_COMM_ID=host:port`` (the reference's knob): every rank derives the same unique id from the environment
+    and rank 0 serves the rendezvous there, so nothing has to be passed between the processes."""
+    import socket
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    code = """
+        import sys
+        import numpy as np
+        from dfccl_b200 import native as nv
+        rank, world = int(sys.argv[1]), 3
+        nv.set_backend("host")
+        comm = nv.Comm.init_rank(world, nv.get_unique_id(), rank)
+        x = np.full(1000, float(rank + 1), np.float32)
+        nv.check(nv.lib().ncclAllReduce(x.ctypes.data, x.ctypes.data, x.size, nv.FLOAT32, nv.SUM, comm.handle, None))
+        assert float(x.min()) == float(x.max()) == 6.0, x[:4]
+        comm.destroy()
+        print("RANK_OK", rank)
+    """
+    env = dict(os.environ, NCCL_COMM_ID=f"127.0.0.1:{port}", HOME=str(tmp_path), PYTHONPATH=ROOT)
+    procs = [subprocess.Popen([sys.executable, "-c", textwrap.dedent(code), str(r)], env=env, stdout=subprocess.PIPE,
+                              stderr=subprocess.STDOUT, text=True, cwd=ROOT) for r in range(3)]
+    outs = []
+    try:
+        for p in procs:
+            out, _ = p.communicate(timeout=120)
+            outs.append((p.returncode, out))
+    finally:
+        for p in procs:
+            if p.poll() is None:
+                p.kill()                     # the exact children started above
+    assert all(rc == 0 and "RANK_OK" in out for rc, out in outs), outs
