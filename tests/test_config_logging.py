@@ -102,3 +102,43 @@ def test_rendezvous_by_comm_id_without_exchanging_a_unique_id(tmp_path):
             if p.poll() is None:
                 p.kill()                     # the exact children started above
     assert all(rc == 0 and "RANK_OK" in out for rc, out in outs), outs
+
+
+def test_ranks_that_report_different_hosts_take_the_network_path(tmp_path):
+    """``NCCL_HOSTID`` (the reference's knob for pretending to be on other hardware) gives two processes of this machine
+    different host identities: they cannot map one another's memory, so the communicator selects the network
+    transport by itself and the collectives still give the right answer."""
+    import socket
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    code = """
+        import sys
+        import numpy as np
+        from dfccl_b200 import native as nv
+        rank, world = int(sys.argv[1]), 2
+        nv.set_backend("host")
+        comm = nv.Comm.init_rank(world, nv.get_unique_id(), rank)
+        assert comm.transport() == "net", comm.transport()
+        x = (np.arange(5003, dtype=np.float32) % 13) + rank
+        nv.check(nv.lib().ncclAllReduce(x.ctypes.data, x.ctypes.data, x.size, nv.FLOAT32, nv.SUM, comm.handle, None))
+        assert np.array_equal(x, 2 * (np.arange(5003, dtype=np.float32) % 13) + 1)
+        comm.destroy()
+        print("RANK_OK", rank)
+    """
+    procs = []
+    for r in range(2):
+        env = dict(os.environ, NCCL_COMM_ID=f"127.0.0.1:{port}", NCCL_HOSTID=f"machine-{r}", HOME=str(tmp_path), PYTHONPATH=ROOT)
+        env.pop("DFCCL_FORCE_NET", None)
+        procs.append(subprocess.Popen([sys.executable, "-c", textwrap.dedent(code), str(r)], env=env, stdout=subprocess.PIPE,
+                                      stderr=subprocess.STDOUT, text=True, cwd=ROOT))
+    outs = []
+    try:
+        for p in procs:
+            out, _ = p.communicate(timeout=120)
+            outs.append((p.returncode, out))
+    finally:
+        for p in procs:
+            if p.poll() is None:
+                p.kill()                     # the exact children started above
+    assert all(rc == 0 and "RANK_OK" in out for rc, out in outs), outs
