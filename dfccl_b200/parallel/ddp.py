@@ -197,10 +197,11 @@ class DaemonDDP:
             # the switch halves the bytes a GPU moves only from four ranks on (on two ranks every schedule moves one
             # message size per direction, and plain peer loads / stores do that faster)
             min_ranks = int(os.environ.get("DFCCL_DDP_NVLS_MIN_RANKS", "4")) if self._nvls_request is None else 2
-            use = bool(want) and self.device.type == "cuda" and comm.nranks >= min_ranks and \
+            # (on the host backend only when asked for by name: the arena is emulated there, for tests)
+            use = bool(want) and (self.device.type == "cuda" or self._nvls_request is True) and comm.nranks >= min_ranks and \
                 all(b.dtype in (torch.bfloat16, torch.float16, torch.float32) for b in bl)
             # collective call: every member asks, and all of them get the same answer
-            if use and not comm.nvls_init(need + (80 << 20)):
+            if use and not comm.nvls_init(need + ((80 << 20) if self.device.type == "cuda" else (1 << 20))):
                 use = False
             if use:
                 _uc, _mc, total, used = comm.nvls_info()

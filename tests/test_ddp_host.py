@@ -123,6 +123,44 @@ def test_parameter_groups_reduce_over_their_own_communicators(host_backend):
         assert abs(out[r][1] - 10 * (1 + 2 + 3 + 4)) < 1e-4, out
 
 
+def test_gradient_buckets_in_the_multicast_arena(host_backend):
+    """``nvls=True`` places the buckets' gradient arrays in the communicator's multicast arena and registers their
+    all-reduces on the multimem schedule (bf16 in, fp32 out, 1/N scale); the training trajectory is the one of the
+    heap-resident buckets.  Buckets whose size is not a 16-byte multiple keep the peer schedule."""
+    nv = host_backend
+    from dfccl_b200.parallel import DaemonDDP, Dist
+    world, steps = 3, 3
+    xs = [[torch.randn(8, 32, generator=torch.Generator().manual_seed(7 * s + r)) for r in range(world)] for s in range(steps)]
+    finals = {}
+    for mode in (False, True):
+        comms = nv.Comm.init_loopback(world)
+        nets = [_mlp() for _ in range(world)]
+        paths = {}
+
+        def body(r):
+            d = Dist(r, world, 0, torch.device("cpu"), comms[r], False)
+            ddp = DaemonDDP(nets[r], d, bucket_mb=0.004, lr=0.05, momentum=0.9, weight_decay=0.0, seed=5, nvls=mode)
+            for s in range(steps):
+                nets[r](xs[s][r]).square().mean().backward()
+                ddp.finish_backward()
+                assert ddp.ctx.wait_all(30000) == nv.SUCCESS
+                ddp.step()
+            paths[r] = (ddp.gradient_path(), [b.nvls for b in ddp.buckets])
+            finals[(mode, r)] = [p.detach().clone() for p in nets[r].parameters()]
+            ddp.close()
+
+        run_ranks(world, body)
+        for c in comms:
+            c.destroy()
+        if mode:
+            assert all("multimem" in p[0] and any(p[1]) for p in paths.values()), paths
+        else:
+            assert all(p[0] == "peer loads/stores" for p in paths.values()), paths
+    for r in range(world):
+        for a, b in zip(finals[(False, r)], finals[(True, r)]):
+            torch.testing.assert_close(a, b, rtol=1e-5, atol=1e-6)
+
+
 def test_stress_orders_deadlock_an_inorder_library():
     from dfccl_b200.benchmarks.stress import inorder_verdict
     v = inorder_verdict(64, 20, 8, 2024)
