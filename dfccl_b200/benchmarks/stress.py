@@ -69,7 +69,7 @@ def main(argv=None):
         per = max(8, n // world) if k in (nv.ALLGATHER, nv.REDUCESCATTER) else n
         counts.append(per)
         total += 2 * (per * world if k in (nv.ALLGATHER, nv.REDUCESCATTER) else per) * 2 + 4096
-    os.environ.setdefault("DFCCL_HEAP_BYTES", str(total + (256 << 20)))
+    os.environ.setdefault("DFCCL_HEAP_BYTES", str(total + (768 << 20)))      # buffers + flag words, push slots (up to 4 MB per small collective), staging
     os.environ.setdefault("DFCCL_WAIT_TIMEOUT_MS", "60000")
     d = init_distributed()
     rank, dev = d.rank, d.device
